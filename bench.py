@@ -1,0 +1,450 @@
+#!/usr/bin/env python
+"""Benchmark of the attention/encoder hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload prefill|decode|encoder] [--impl ours|reference]
+
+One JSON line on stdout (rank 0). The headline workload is the long-sequence prefill attention of the
+baseline's config 4 (batch 4 x 16 heads, head_dim 128, bf16, seq 8192, no mask), sharded by head across the
+ranks (strong scaling, no data-path collective: outputs stay sharded). A step is one pass of the fused
+attention kernel over the rank's heads. `value` is measured with inputs resident in HBM; `e2e` is the same
+metric through the C-ABI with pinned HOST buffers (vkc_upload -> kernel -> vkc_download inside the timed
+region). `extra` carries the other parts of the baseline's composite metric (decode GB/s, encoder tok/s, the
+rest of the prefill sweep), measured with the same rules right after the headline run.
+
+Inputs are synthetic (seeded N(0,1)); they stand in for the shapes the baseline names. Between timed steps the
+kernels cycle through several input sets so that every step reads data that is not L2 resident.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+L2_BYTES = 126 * 1024 * 1024
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+PREFILL = dict(B=4, H=16, S=8192, D=128, causal=False, dtype="bf16", seed=1005)
+DECODE = dict(B=32, Hq=32, Hkv=8, L=8192, D=128, seed=1005)
+ENCODER = dict(B=8, T=197, d=768, H=12, dmlp=3072, seed=1002)
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            d = json.load(f)
+        d["_source"] = "measured"
+        return d
+    d = dict(FALLBACK_PEAKS)
+    d["_source"] = "fallback"
+    return d
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    Q = "clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown," \
+        "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+
+    def __init__(self, index):
+        self.rows, self.proc, self.index = [], None, index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q, "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        self.thread.join(timeout=2)
+        sm, mx, reasons = [], None, set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[0]))
+                mx = float(r[1])
+            except (ValueError, IndexError):
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ---------------------------------------------------------------------------------------------------------------
+def dist_setup(n):
+    import torch
+    import torch.distributed as dist
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    else:
+        torch.cuda.set_device(0)
+    return rank, world, local
+
+
+def barrier(world):
+    import torch
+    import torch.distributed as dist
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+
+
+def max_over_ranks(x, world):
+    import torch
+    import torch.distributed as dist
+    if world == 1:
+        return float(x)
+    t = torch.tensor([float(x)], device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def sum_over_ranks(x, world):
+    import torch
+    import torch.distributed as dist
+    if world == 1:
+        return float(x)
+    t = torch.tensor([float(x)], device="cuda", dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.SUM)
+    return float(t.item())
+
+
+def timed_loop(fn, steps, warmup, world):
+    """W untimed steps, then exactly K steps between barrier+synchronize; per-step CUDA events on the launching
+    stream. Returns (total_ms as max over ranks, mean per-launch ms on this rank)."""
+    import torch
+    for i in range(warmup):
+        fn(i)
+    barrier(world)
+    evs = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+    evs[0].record()
+    for i in range(steps):
+        fn(warmup + i)
+        evs[i + 1].record()
+    barrier(world)
+    total = evs[0].elapsed_time(evs[-1])
+    per = [evs[i].elapsed_time(evs[i + 1]) for i in range(steps)]
+    return max_over_ranks(total, world), float(np.mean(per))
+
+
+def n_sets_for(bytes_per_step):
+    return max(2, int(np.ceil(2.0 * L2_BYTES / max(bytes_per_step, 1))) + 1)
+
+
+# ---------------------------------------------------------------------------------------------------------------
+def bench_prefill(ctx, cfg, steps, warmup, rank, world, e2e_steps=3):
+    import torch
+    B, H, S, D = cfg["B"], cfg["H"], cfg["S"], cfg["D"]
+    assert H % world == 0, "heads must divide across ranks"
+    Hl = H // world
+    dt = torch.bfloat16
+    g = torch.Generator(device="cuda").manual_seed(cfg["seed"] + rank)
+    bytes_step = 4 * B * Hl * S * D * 2
+    ns = min(n_sets_for(bytes_step), 6)
+    sets = []
+    for _ in range(ns):
+        q, k, v = (torch.randn(B, Hl, S, D, generator=g, device="cuda", dtype=torch.float32).to(dt) for _ in range(3))
+        sets.append((q, k, v, torch.empty_like(q)))
+    scale = 1.0 / float(np.sqrt(D))
+
+    def step(i):
+        q, k, v, o = sets[i % ns]
+        ctx.attn_prefill(q, k, v, o, scale, causal=cfg["causal"])
+
+    n0 = ctx.launch_count()
+    total_ms, per_launch_ms = timed_loop(step, steps, warmup, world)
+    launches = ctx.launch_count() - n0 - warmup
+    ctx.sync()
+    flops_rank = (2 * B * Hl * S * (S + 1) * D) if cfg["causal"] else (4 * B * Hl * S * S * D)
+    flops_all = flops_rank * world
+    res = dict(total_ms=total_ms, per_launch_ms=per_launch_ms, flops_step_all=flops_all, flops_step_rank=flops_rank, launches=launches,
+               bytes_step_rank=bytes_step, n_sets=ns)
+
+    # end to end through the C-ABI with host buffers
+    if e2e_steps > 0:
+        q, k, v, o = sets[0]
+        hq, hk, hv = (torch.empty(t.shape, dtype=dt).pin_memory() for t in (q, k, v))
+        ho = torch.empty(o.shape, dtype=dt).pin_memory()
+        hq.copy_(q)
+        hk.copy_(k)
+        hv.copy_(v)
+
+        def e2e(i):
+            ctx.upload_ptr(q, hq.data_ptr(), 2)
+            ctx.upload_ptr(k, hk.data_ptr(), 2)
+            ctx.upload_ptr(v, hv.data_ptr(), 2)
+            ctx.attn_prefill(q, k, v, o, scale, causal=cfg["causal"])
+            ctx.download_ptr(ho.data_ptr(), 2, o)
+        t_ms, _ = timed_loop(e2e, e2e_steps, 1, world)
+        res["e2e_ms_per_step"] = t_ms / e2e_steps
+        res["h2d"] = 3 * q.numel() * 2
+        res["d2h"] = o.numel() * 2
+    return res
+
+
+def bench_decode(ctx, cfg, steps, warmup, rank, world):
+    import torch
+    B, Hq, Hkv, L, D = cfg["B"], cfg["Hq"], cfg["Hkv"], cfg["L"], cfg["D"]
+    assert B % world == 0
+    Bl = B // world
+    rng = np.random.default_rng(cfg["seed"])
+    kv_len_all = rng.integers(1024, L + 1, B).astype(np.int32)
+    kv_len = kv_len_all[rank * Bl:(rank + 1) * Bl]
+    g = torch.Generator(device="cuda").manual_seed(cfg["seed"] + rank)
+    dt = torch.float16
+    bytes_alg = int(2 * Hkv * int(kv_len.sum()) * D * 2 + 2 * Bl * Hq * D * 2)
+    ns = min(n_sets_for(bytes_alg), 4)
+    sets = []
+    for _ in range(ns):
+        k = torch.randn(Bl, Hkv, L, D, generator=g, device="cuda", dtype=dt)
+        v = torch.randn(Bl, Hkv, L, D, generator=g, device="cuda", dtype=dt)
+        q = torch.randn(Bl, Hq, D, generator=g, device="cuda", dtype=dt)
+        sets.append((q, k, v, torch.empty_like(q)))
+    lens = torch.from_numpy(kv_len).cuda()
+    ws = torch.empty(ctx.attn_decode_workspace_bytes(Bl, Hq, Hkv, L, D), dtype=torch.uint8, device="cuda")
+    scale = 1.0 / float(np.sqrt(D))
+
+    def step(i):
+        q, k, v, o = sets[i % ns]
+        ctx.attn_decode(q, k, v, o, scale, kv_len=lens, workspace=ws)
+
+    total_ms, per_ms = timed_loop(step, steps, warmup, world)
+    ctx.sync()
+    bytes_all = sum_over_ranks(bytes_alg, world)
+    return dict(total_ms=total_ms, per_launch_ms=per_ms, bytes_step_all=bytes_all, bytes_step_rank=bytes_alg, gbs=bytes_all * steps / (total_ms * 1e-3) / 1e9)
+
+
+def bench_encoder(ctx, cfg, steps, warmup, rank, world):
+    import torch
+    from vknn_b200.synthetic import encoder_weights
+    from vknn_b200.encoder import EncoderLayer
+    B, T, d, H, dm = cfg["B"], cfg["T"], cfg["d"], cfg["H"], cfg["dmlp"]
+    assert B % world == 0
+    Bl = B // world
+    w = encoder_weights(np.random.default_rng(cfg["seed"]), d, dm)
+    layer = EncoderLayer(ctx, w, H, dtype=torch.float16)
+    g = torch.Generator(device="cuda").manual_seed(cfg["seed"] + rank)
+    # the layer's weights (14 MB) are reused every step by design; activations cycle through enough sets to leave L2
+    ns = 8
+    xs = [torch.randn(Bl, T, d, generator=g, device="cuda", dtype=torch.float32).half() for _ in range(ns)]
+    ys = [torch.empty_like(x) for x in xs]
+
+    def step(i):
+        layer.forward(xs[i % ns], out=ys[i % ns])
+
+    total_ms, per_ms = timed_loop(step, steps, warmup, world)
+    ctx.sync()
+    tokens_all = B * T
+    return dict(total_ms=total_ms, tok_s=tokens_all * steps / (total_ms * 1e-3), flops_step_all=layer.flops(Bl, T) * world,
+                tflops=layer.flops(Bl, T) * world * steps / (total_ms * 1e-3) / 1e12)
+
+
+# ---------------------------------------------------------------------------------------------------------------
+def cpu_baseline_prefill(cfg, budget_rows=256):
+    """Times the reference's own CPU backend (oracle/_ref, one core) on a bounded sample of the headline workload:
+    `budget_rows` query rows of one (batch, head) unit against all S keys (rows are independent without a mask)."""
+    from oracle import vko
+    S, D = cfg["S"], cfg["D"]
+    rng = np.random.default_rng(cfg["seed"])
+    q = rng.standard_normal((1, 1, budget_rows, D)).astype(np.float32)
+    k = rng.standard_normal((1, 1, S, D)).astype(np.float32)
+    v = rng.standard_normal((1, 1, S, D)).astype(np.float32)
+    flops = 4.0 * budget_rows * S * D
+    sample = "%d query rows x %d keys of one (batch, head) unit, D=%d, fp32" % (budget_rows, S, D)
+    if vko.have_ref():
+        _, info = vko.attention_graph(q, k, v, 1.0 / np.sqrt(D)).run(iters=3, warmup=1)
+        sec = info["median_ms"] * 1e-3
+        kind = "reference"
+    else:
+        t0 = time.perf_counter()
+        vko.attention(q, k, v, 1.0 / np.sqrt(D), threads=1)
+        sec = time.perf_counter() - t0
+        kind = "port"
+    return {"value": flops / sec / 1e12, "unit": "TFLOP/s", "cores": 1, "kind": kind, "sample": sample, "seconds": sec}
+
+
+def run_reference(args):
+    """Reference arm: the reference's own CPU implementation of the path on the host cores (one process per core,
+    each an unmodified single-threaded reference Session on its own slice of query rows)."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    from concurrent.futures import ThreadPoolExecutor
+    from oracle import vko
+    cfg = PREFILL
+    S, D = cfg["S"], cfg["D"]
+    cores = max(1, min(os.cpu_count() or 1, 32))
+    rows = 128
+    flops_proc = 4.0 * rows * S * D
+    kind = "reference" if vko.have_ref() else "port"
+
+    def one(i):
+        rng = np.random.default_rng(cfg["seed"] + i)
+        q = rng.standard_normal((1, 1, rows, D)).astype(np.float32)
+        k = rng.standard_normal((1, 1, S, D)).astype(np.float32)
+        v = rng.standard_normal((1, 1, S, D)).astype(np.float32)
+        if kind == "reference":
+            _, info = vko.attention_graph(q, k, v, 1.0 / np.sqrt(D)).run(iters=args.steps, warmup=args.warmup)
+            return info["median_ms"]
+        for _ in range(args.warmup):
+            vko.attention(q, k, v, 1.0 / np.sqrt(D), threads=1)
+        ts = []
+        for _ in range(args.steps):
+            t0 = time.perf_counter()
+            vko.attention(q, k, v, 1.0 / np.sqrt(D), threads=1)
+            ts.append((time.perf_counter() - t0) * 1e3)
+        return float(np.median(ts))
+
+    with ThreadPoolExecutor(max_workers=cores) as ex:
+        ms = list(ex.map(one, range(cores)))
+    step_ms = max(ms)
+    value = flops_proc * cores / (step_ms * 1e-3) / 1e12
+    line = {
+        "impl": "reference", "metric": "attention TFLOP/s", "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": step_ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic", "config": headline_config(cfg, args.gpus),
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": cores, "kind": kind,
+                         "sample": "per step: %d processes x %d query rows x %d keys of (batch, head) units, D=%d, fp32, reference CPU backend" %
+                                   (cores, rows, S, D)},
+        "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+    return 0
+
+
+def headline_config(cfg, n):
+    return {"workload": "config 4: prefill attention, batch %d x %d heads, head_dim %d, seq %d, %s, %s" %
+                        (cfg["B"], cfg["H"], cfg["D"], cfg["S"], cfg["dtype"], "causal" if cfg["causal"] else "no mask"),
+            "parallelism": "heads sharded over %d GPU(s), outputs left sharded (no collective)" % n,
+            "l2": "inputs cycle through sets larger than L2 (126 MB) between timed steps"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="prefill", choices=["prefill", "decode", "encoder"])
+    ap.add_argument("--seq", type=int, default=None, help="prefill sequence length (default 8192)")
+    ap.add_argument("--causal", action="store_true")
+    ap.add_argument("--no-extra", action="store_true", help="skip the decode / encoder / sweep extras")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.impl == "reference":
+        return run_reference(args)
+
+    import torch
+    import vknn_b200
+    rank, world, local = dist_setup(args.gpus)
+    ctx = vknn_b200.Context(local)
+    pk = peaks()
+    cfg = dict(PREFILL)
+    if args.seq:
+        cfg["S"] = args.seq
+    cfg["causal"] = bool(args.causal)
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    if args.workload == "prefill":
+        r = bench_prefill(ctx, cfg, args.steps, args.warmup, rank, world)
+    elif args.workload == "decode":
+        r = bench_decode(ctx, DECODE, args.steps, args.warmup, rank, world)
+    else:
+        r = bench_encoder(ctx, ENCODER, args.steps, args.warmup, rank, world)
+    clocks = sampler.stop() if rank == 0 else None
+
+    extra = {}
+    if not args.no_extra:
+        k = min(args.steps, 10)
+        if args.workload != "decode":
+            d = bench_decode(ctx, DECODE, k, 3, rank, world)
+            extra["decode"] = {"workload": "config 5: GQA decode, batch 32, 32q/8kv heads, D=128, fp16 cache 8192, kv_len U[1024,8192], batch sharded",
+                               "GB/s": d["gbs"], "frac_hbm_per_gpu": d["bytes_step_rank"] / (d["per_launch_ms"] * 1e-3) / 1e9 / pk["hbm_gbs"],
+                               "ms_per_step": d["total_ms"] / k}
+        if args.workload != "encoder":
+            e = bench_encoder(ctx, ENCODER, k, 3, rank, world)
+            extra["encoder"] = {"workload": "config 2: ViT-B/16 layer, batch 8 x 197 tokens, fp16, batch sharded", "tok/s": e["tok_s"],
+                                "TFLOP/s": e["tflops"], "ms_per_step": e["total_ms"] / k}
+        if args.workload == "prefill" and not args.seq:
+            sweep = {}
+            for S, causal in ((4096, False), (16384, False), (8192, True), (16384, True)):
+                c2 = dict(cfg, S=S, causal=causal)
+                s = bench_prefill(ctx, c2, max(3, k // 2), 3, rank, world, e2e_steps=0)
+                sweep["S%d%s" % (S, "_causal" if causal else "")] = s["flops_step_all"] * max(3, k // 2) / (s["total_ms"] * 1e-3) / 1e12
+            extra["prefill_sweep_TFLOP/s"] = sweep
+
+    if rank != 0:
+        return 0
+    line = {"n_gpus": world, "steps": args.steps, "warmup": args.warmup, "higher_is_better": True, "vs_baseline": None, "data": "synthetic",
+            "clocks": clocks, "extra": extra}
+    if args.workload == "prefill":
+        secs = r["total_ms"] * 1e-3
+        value = r["flops_step_all"] * args.steps / secs / 1e12
+        achieved = r["flops_step_rank"] / (r["per_launch_ms"] * 1e-3) / 1e12
+        peak = pk["bf16_tflops"]
+        line.update({
+            "metric": "attention TFLOP/s", "value": value, "unit": "TFLOP/s", "ms_per_step": r["total_ms"] / args.steps, "scaling": "strong",
+            "dtype": "bf16", "config": headline_config(cfg, world), "gpu_launches": int(r["launches"]),
+            "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                         "peak_source": "%s bf16 burst (cuBLAS)" % pk["_source"], "frac_of_sustained": achieved / pk["bf16_tflops_sustained"],
+                         "traffic": None, "kernel": "attn_prefill_kernel", "flops_per_launch": r["flops_step_rank"]},
+        })
+        if "e2e_ms_per_step" in r:
+            line["e2e"] = {"value": r["flops_step_all"] / (r["e2e_ms_per_step"] * 1e-3) / 1e12, "unit": "TFLOP/s",
+                           "h2d_bytes_per_step": int(r["h2d"]), "d2h_bytes_per_step": int(r["d2h"]), "ms_per_step": r["e2e_ms_per_step"]}
+    elif args.workload == "decode":
+        achieved = r["bytes_step_rank"] / (r["per_launch_ms"] * 1e-3) / 1e9
+        line.update({"metric": "decode GB/s", "value": r["gbs"], "unit": "GB/s", "ms_per_step": r["total_ms"] / args.steps, "scaling": "strong",
+                     "dtype": "f16", "config": {"workload": "config 5: GQA decode batch 32, 32q/8kv heads, D=128, cache 8192", "parallelism": "batch sharded"},
+                     "gpu_launches": 2 * args.steps,
+                     "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": achieved / pk["hbm_gbs"],
+                                  "peak_source": pk["_source"], "traffic": None, "kernel": "attn_decode_kernel (+combine)"}})
+    else:
+        line.update({"metric": "encoder tok/s", "value": r["tok_s"], "unit": "tok/s", "ms_per_step": r["total_ms"] / args.steps, "scaling": "strong",
+                     "dtype": "f16", "config": {"workload": "config 2: ViT-B/16 encoder layer batch 8 x 197", "parallelism": "batch sharded"},
+                     "gpu_launches": 7 * args.steps,
+                     "roofline": {"bound": "tensor", "achieved": r["tflops"] / world, "peak": pk["bf16_tflops"], "unit": "TFLOP/s",
+                                  "frac": r["tflops"] / world / pk["bf16_tflops"], "peak_source": pk["_source"], "traffic": None}})
+    if world == 1 and not args.no_cpu and args.workload == "prefill":
+        try:
+            line["cpu_baseline"] = cpu_baseline_prefill(cfg)
+        except Exception as e:  # the baseline is informational; its failure must not hide the GPU numbers
+            line["cpu_baseline"] = {"value": None, "unit": "TFLOP/s", "cores": 1, "kind": "unavailable", "sample": str(e)[:200]}
+    print(json.dumps(line))
+    if world > 1:
+        import torch.distributed as dist
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

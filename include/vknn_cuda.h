@@ -1,0 +1,149 @@
+/* libvknn_cuda — C-ABI of the B200 (sm_100a) attention/encoder kernels that sit behind VKNN's pluggable
+ * Backend/Segment interface.
+ *
+ * Conventions
+ *   - every entry point returns an int status: VKC_OK (0) or a negative VKC_ERR_* code; nothing throws;
+ *     vkc_last_error(ctx) gives the message of the last failure on that context;
+ *   - handles are opaque; buffers are plain pointers + sizes; a context is bound to one CUDA device and is
+ *     driven by one host thread at a time (the reference's Session has the same rule, src/core/session.cpp:649);
+ *   - `stream` is a cudaStream_t passed as void*; NULL selects the context's own stream;
+ *   - device tensors are row-major, exactly like the reference's host tensors (include/vknn/rt_tensor.h:15-43);
+ *     storage types: VKC_F32 (Precision::High), VKC_F16 (Precision::Low/Normal), VKC_BF16; accumulation,
+ *     softmax and LayerNorm statistics are always fp32 (include/vknn/precision.h:7-11);
+ *   - there is no CPU fallback: when no usable device or kernel exists the call fails with an error.
+ *
+ * Each entry point names the reference interface it stands in for (file:line inside the reference tree).
+ */
+#ifndef VKNN_CUDA_H
+#define VKNN_CUDA_H
+#include <stddef.h>
+#include <stdint.h>
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define VKC_API __attribute__((visibility("default")))
+
+typedef struct vkc_ctx vkc_ctx;
+typedef void          *vkc_stream;
+
+enum { VKC_F32 = 0, VKC_F16 = 1, VKC_BF16 = 2, VKC_I32 = 3 };
+
+enum {
+    VKC_OK              = 0,
+    VKC_ERR_INVALID     = -1, /* bad argument (maps to vknn::Status::InvalidArgument, include/vknn/status.h:7-15) */
+    VKC_ERR_UNSUPPORTED = -2, /* shape/dtype the kernels do not cover (Status::Unsupported) */
+    VKC_ERR_CUDA        = -3, /* a CUDA runtime/driver call failed (Status::RuntimeError) */
+    VKC_ERR_OOM         = -4, /* device allocation failed (Status::RuntimeError) */
+    VKC_ERR_DEVICE      = -5, /* a kernel reported a device-side error, e.g. a bounded wait ran out (Status::DeviceLost) */
+    VKC_ERR_NO_DEVICE   = -6  /* no CUDA device / not an sm_100 part (Backend::available() == false) */
+};
+
+/* GEMM epilogue, applied in this order on the fp32 accumulator: +bias[n], GELU(erf), +residual[m,n]. */
+enum { VKC_EPI_NONE = 0, VKC_EPI_BIAS = 1, VKC_EPI_GELU_ERF = 2, VKC_EPI_RESIDUAL = 4 };
+/* Layout of the B operand: row-major [K,N] (the reference's MatMul B, and what an initializer holds after the
+ * weight Transpose is const-folded, src/import/const_fold.cpp:30-60) or row-major [N,K] (Q.K^T without a Transpose). */
+enum { VKC_B_KN = 0, VKC_B_NK = 1 };
+/* Kernel family selection, for tests and A/B measurements. AUTO is what the backend uses. */
+enum { VKC_IMPL_AUTO = 0, VKC_IMPL_SIMT = 1, VKC_IMPL_TCGEN05 = 2 };
+
+/* ---- context: stands in for the device half of a Backend instance. Reference: Backend::available/configure,
+ * include/vknn/backend_class.h:15-31; VulkanContext creation in src/backend/vulkan/vk_backend.cpp:152-188. ---- */
+VKC_API int         vkc_device_count(int *count);
+VKC_API int         vkc_ctx_create(int device_ordinal, vkc_ctx **out);
+VKC_API int         vkc_ctx_destroy(vkc_ctx *ctx);
+VKC_API const char *vkc_last_error(const vkc_ctx *ctx);
+VKC_API int         vkc_ctx_set_impl(vkc_ctx *ctx, int impl);
+/* Blocks until `stream` is idle, then reports (and clears) any device-side error word the kernels wrote. */
+VKC_API int vkc_sync(vkc_ctx *ctx, vkc_stream stream);
+/* Number of kernels of this library launched through `ctx` since it was created. */
+VKC_API int64_t vkc_launch_count(const vkc_ctx *ctx);
+
+/* ---- memory and boundary transfers. Reference: boundary pack/unpack of a device segment, host fp32 <->
+ * device storage precision, src/backend/vulkan/vk_backend.cpp:558-696,1324-1382; weight upload helpers
+ * src/backend/vulkan/ops/vk_op_common.h:82-196. Conversion runs on the device. ---- */
+VKC_API int vkc_alloc(vkc_ctx *ctx, size_t bytes, void **dptr);
+VKC_API int vkc_free(vkc_ctx *ctx, void *dptr);
+VKC_API int vkc_upload(vkc_ctx *ctx, void *dst_dev, int dst_dtype, const void *src_host, int src_dtype, int64_t n, vkc_stream stream);
+VKC_API int vkc_download(vkc_ctx *ctx, void *dst_host, int dst_dtype, const void *src_dev, int src_dtype, int64_t n, vkc_stream stream);
+VKC_API int vkc_convert(vkc_ctx *ctx, void *dst_dev, int dst_dtype, const void *src_dev, int src_dtype, int64_t n, vkc_stream stream);
+
+/* ---- K1: batched GEMM with fused epilogue. Reference: MatMulCpu::run src/backend/cpu/ops/matmul.cpp:14-116
+ * (oracle), shaders/matmul_tiled.comp:13-95 and matmul_tiled_bias.comp:8-87 with host MatMulOp
+ * src/backend/vulkan/ops/matmul.cpp:22-181 (device path replaced); the GELU tail Div/Erf/Add/FusedPointwise
+ * (src/backend/cpu/ops/unary.cpp:44, fused_pointwise.cpp:107-167) and the residual Add (ops/add.cpp:66-84).
+ *   D[b,m,n] = epi( sum_k A[b,m,k] * B[b,k,n] ),  A: lda-strided rows [M,K]; B per b_layout with row stride ldb;
+ *   D and residual: rows of stride ldd; bias: fp32 [N]; batch strides in elements (0 broadcasts an operand). ---- */
+VKC_API int vkc_gemm(vkc_ctx *ctx, const void *A, const void *B, const float *bias, const void *residual, void *D, int64_t M, int64_t N,
+                     int64_t K, int64_t batch, int64_t stride_a, int64_t stride_b, int64_t stride_d, int64_t lda, int64_t ldb,
+                     int64_t ldd, int b_layout, int epilogue, int dtype, vkc_stream stream);
+
+/* ---- K2: fused prefill attention O = softmax(Q.K^T * scale + mask) . V, never materialising the scores.
+ * Reference: the node run Transpose(K) -> MatMul -> Binary Mul / FusedPointwise{Mul,Add mask} -> Softmax -> MatMul
+ * executed by CpuSegment::run src/backend/cpu/cpu_backend.cpp:94-144 with ops/matmul.cpp:14-116, ops/binary.cpp:31-140,
+ * ops/softmax.cpp:9-47; device path replaced: matmul_tiled.comp + flat_softmax.comp:9-50.
+ *   Q [B,Hq,Sq,D], K/V [B,Hkv,Skv,D], O [B,Hq,Sq,D]; query head h uses kv head h / (Hq/Hkv);
+ *   *_strides = element strides {batch, head, seq} with D contiguous, or NULL for the dense layout (this is how
+ *   the head split/merge Reshape/Transpose/Gather nodes are absorbed: ops/transpose.cpp:8-63, ops/gather.cpp:12-63);
+ *   causal masks key j > i + (Skv - Sq); kv_len (device int32 [B] or NULL) masks keys >= kv_len[b];
+ *   mask (device fp32 [Sq,Skv] additive, or NULL). ---- */
+VKC_API int vkc_attn_prefill(vkc_ctx *ctx, const void *Q, const void *K, const void *V, void *O, int64_t B, int64_t Hq, int64_t Hkv,
+                             int64_t Sq, int64_t Skv, int64_t D, const int64_t *q_strides, const int64_t *k_strides,
+                             const int64_t *v_strides, const int64_t *o_strides, float scale, int causal, const float *mask,
+                             const int32_t *kv_len, int dtype, vkc_stream stream);
+
+/* ---- K3: single-query (decode) attention over a KV cache, split along the cache length. Reference: the same
+ * node run as K2 in its decode shape, which the reference executes as naive MatMul (M < 32 path,
+ * src/backend/vulkan/ops/matmul.cpp:137-141, shaders/matmul.comp:15-29) -> scale+mask -> flat_softmax -> MatMul.
+ *   Q [B,Hq,D], Kc/Vc [B,Hkv,Lmax,D], O [B,Hq,D]; kv_len device int32 [B] (NULL = Lmax for all).
+ *   workspace: device scratch of at least vkc_attn_decode_workspace_bytes(...) bytes holding the per-split
+ *   partial (max, sum, o) triples; NULL lets the context keep (and grow) its own. ---- */
+VKC_API size_t vkc_attn_decode_workspace_bytes(int64_t B, int64_t Hq, int64_t Hkv, int64_t Lmax, int64_t D);
+VKC_API int    vkc_attn_decode(vkc_ctx *ctx, const void *Q, const void *Kc, const void *Vc, void *O, int64_t B, int64_t Hq, int64_t Hkv,
+                               int64_t Lmax, int64_t D, const int32_t *kv_len, float scale, void *workspace, size_t workspace_bytes,
+                               int dtype, vkc_stream stream);
+
+/* ---- K4: LayerNorm over the trailing `norm` elements. Reference: LayerNormCpu::run
+ * src/backend/cpu/ops/layernorm.cpp:12-75 (oracle), shaders/flat_layernorm.comp:8-50 + LayerNormOp
+ * src/backend/vulkan/ops/layernorm.cpp:19-76 (device path replaced). gamma/beta fp32 [norm]; beta may be NULL. ---- */
+VKC_API int vkc_layernorm(vkc_ctx *ctx, const void *X, const float *gamma, const float *beta, void *Y, int64_t rows, int64_t norm,
+                          float eps, int dtype, vkc_stream stream);
+
+/* ---- K5: generic per-element step program. Reference: applyPwEpilogue / FusedPointwiseCpu
+ * src/backend/cpu/ops/fused_pointwise.cpp:107-185, BinaryCpu ops/binary.cpp:31-140, UnaryCpu ops/unary.cpp:10-69,
+ * AddCpu ops/add.cpp:14-125; device path replaced: shaders/fused_pw_flat.comp + pw_epilogue.glsl:10-39.
+ *   Y = program(X); steps: 4 ints per step {kind 0 binary/1 unary/2 act, code, operand index (1-based into
+ *   operands[]), unused}; params: 2 floats per step; operand i has element strides op_strides[i*rank .. +rank)
+ *   against the output shape (0 on broadcast dims). At most 8 steps, 6 operands, rank 8
+ *   (include/vknn/op_type.h:65-67). Operands share the storage dtype. ---- */
+VKC_API int vkc_pointwise(vkc_ctx *ctx, const void *X, void *Y, const int64_t *shape, int rank, int nsteps, const int32_t *steps,
+                          const float *params, int noperands, const void *const *operands, const int64_t *op_strides, int dtype,
+                          vkc_stream stream);
+
+/* ---- standalone Softmax over rows of `inner` contiguous elements, for Softmax nodes outside an attention
+ * pattern. Reference: SoftmaxCpu::run src/backend/cpu/ops/softmax.cpp:9-47; shaders/flat_softmax.comp:9-50. ---- */
+VKC_API int vkc_softmax(vkc_ctx *ctx, const void *X, void *Y, int64_t outer, int64_t inner, int dtype, vkc_stream stream);
+
+/* ---- strided gather copy Y[i] = X[sum_d idx_d(i) * in_strides[d]] over an output of `shape`, for Transpose /
+ * Gather / Slice nodes that cannot be absorbed as strides. Reference: TransposeCpu::run ops/transpose.cpp:8-63;
+ * shaders/flat_gather.comp:11-21. ---- */
+VKC_API int vkc_strided_copy(vkc_ctx *ctx, const void *X, void *Y, const int64_t *shape, const int64_t *in_strides, int rank,
+                             int64_t in_offset, int dtype, vkc_stream stream);
+
+/* ---- segment replay. Reference: the pre-recorded command buffer of a device segment,
+ * src/backend/vulkan/vk_backend.cpp:1009-1210 (record) and :1353-1357 (submit). Calls made between begin and
+ * end on the context's own stream are captured into a CUDA graph; launch replays it. ---- */
+typedef struct vkc_graph vkc_graph;
+VKC_API int vkc_graph_begin(vkc_ctx *ctx);
+VKC_API int vkc_graph_end(vkc_ctx *ctx, vkc_graph **out);
+VKC_API int vkc_graph_launch(vkc_ctx *ctx, vkc_graph *g);
+VKC_API int vkc_graph_destroy(vkc_ctx *ctx, vkc_graph *g);
+
+/* ---- profiling. Reference: per-segment timestamps, src/backend/vulkan/vk_backend.cpp:1437-1457. ---- */
+VKC_API int vkc_timer_start(vkc_ctx *ctx, vkc_stream stream);
+VKC_API int vkc_timer_stop(vkc_ctx *ctx, vkc_stream stream, float *ms);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

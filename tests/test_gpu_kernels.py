@@ -1,0 +1,351 @@
+"""GPU parity tests: every kernel, called through the C-ABI, against the CPU oracle on the same seeded inputs.
+
+Tolerances (stated by the task for this path, versus the reference's CPU backend):
+  f16 / bf16 storage with fp32 accumulation: max|d| <= 1e-2 and cosine >= 0.9999;  fp32 storage: rel <= 1e-4.
+For 16-bit storage the oracle is fed the inputs already rounded to the storage type.
+"""
+import numpy as np
+import pytest
+import torch
+
+import vknn_b200
+from oracle import vko
+from tests.util import assert_high, assert_low, encoder_weights, metrics, round_to
+
+pytestmark = pytest.mark.gpu
+
+DT = {"f32": torch.float32, "f16": torch.float16, "bf16": torch.bfloat16}
+
+
+def dev(x, dtype):
+    return torch.from_numpy(np.ascontiguousarray(x, dtype=np.float32)).cuda().to(dtype).contiguous()
+
+
+def host(t):
+    return t.float().cpu().numpy()
+
+
+# ------------------------------------------------------------------------------------------------ GEMM
+@pytest.mark.parametrize("impl", [vknn_b200.IMPL_SIMT, vknn_b200.IMPL_TCGEN05], ids=["simt", "tc"])
+@pytest.mark.parametrize("dt", ["f16", "bf16"])
+@pytest.mark.parametrize("layout", [vknn_b200.B_KN, vknn_b200.B_NK])
+@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (197, 192, 72), (300, 520, 264), (64, 40, 128)])
+def test_gemm_16bit(ctx, impl, dt, layout, M, N, K):
+    rng = np.random.default_rng(M * 7 + N * 3 + K)
+    a = round_to(rng.standard_normal((M, K)), DT[dt])
+    b = round_to(rng.standard_normal((K, N)) * 0.1, DT[dt])
+    bias = rng.standard_normal(N).astype(np.float32)
+    ref = vko.matmul(a, b, bias)
+    ctx.set_impl(impl)
+    try:
+        A = dev(a, DT[dt])
+        Bm = dev(b if layout == vknn_b200.B_KN else b.T, DT[dt])
+        D = torch.zeros(M, N, dtype=DT[dt], device="cuda")
+        ctx.gemm(A, Bm, D, bias=torch.from_numpy(bias).cuda(), b_layout=layout)
+        ctx.sync()
+    finally:
+        ctx.set_impl(vknn_b200.IMPL_AUTO)
+    m = metrics(host(D), ref)
+    # outputs are O(1): the storage rounding of D itself is up to 2^-9 relative for bf16
+    assert m["cosine"] >= 0.9999 and m["max_abs"] <= (4e-2 if dt == "bf16" else 1e-2), m
+
+
+@pytest.mark.parametrize("epi", ["bias", "bias_gelu", "bias_residual"])
+@pytest.mark.parametrize("impl", [vknn_b200.IMPL_SIMT, vknn_b200.IMPL_TCGEN05], ids=["simt", "tc"])
+def test_gemm_epilogues(ctx, impl, epi):
+    rng = np.random.default_rng(11)
+    M, N, K = 200, 256, 128
+    a = round_to(rng.standard_normal((M, K)), torch.float16)
+    b = round_to(0.05 * rng.standard_normal((K, N)), torch.float16)
+    bias = (0.1 * rng.standard_normal(N)).astype(np.float32)
+    res = round_to(rng.standard_normal((M, N)), torch.float16)
+    ref = vko.matmul(a, b, bias)
+    flags = vknn_b200.EPI_BIAS
+    if epi == "bias_gelu":
+        t = vko.binary(ref, np.array([np.float32(1.41421356237)], np.float32), 2)
+        t = vko.unary(t, 15)
+        t = vko.binary(t, np.array([1.0], np.float32), 6)
+        ref = vko.pw_epilogue(t, [0, 0, 1, 0, 0, 0, 2, 0], [0, 0, 0, 0], [ref, np.array([0.5], np.float32)])
+        flags |= vknn_b200.EPI_GELU_ERF
+    if epi == "bias_residual":
+        ref = ref + res
+        flags |= vknn_b200.EPI_RESIDUAL
+    ctx.set_impl(impl)
+    try:
+        D = torch.zeros(M, N, dtype=torch.float16, device="cuda")
+        ctx.gemm(dev(a, torch.float16), dev(b, torch.float16), D, bias=torch.from_numpy(bias).cuda(),
+                 residual=dev(res, torch.float16) if epi == "bias_residual" else None, epilogue=flags)
+        ctx.sync()
+    finally:
+        ctx.set_impl(vknn_b200.IMPL_AUTO)
+    assert_low(host(D), ref, epi)
+
+
+def test_gemm_batched_broadcast(ctx):
+    """MatMul batch broadcast [B,M,K] @ [K,N] and [B,M,K] @ [B,K,N], tensor-core path."""
+    rng = np.random.default_rng(5)
+    Bn, M, N, K = 3, 130, 128, 64
+    a = round_to(rng.standard_normal((Bn, M, K)), torch.float16)
+    b1 = round_to(0.1 * rng.standard_normal((K, N)), torch.float16)
+    b3 = round_to(0.1 * rng.standard_normal((Bn, K, N)), torch.float16)
+    for b in (b1, b3):
+        D = torch.zeros(Bn, M, N, dtype=torch.float16, device="cuda")
+        ctx.gemm(dev(a, torch.float16), dev(b, torch.float16), D)
+        ctx.sync()
+        assert_low(host(D), vko.matmul(a, b), "batched")
+
+
+def test_gemm_fp32_high(ctx):
+    rng = np.random.default_rng(3)
+    a = rng.standard_normal((2, 197, 64)).astype(np.float32)
+    b = rng.standard_normal((2, 64, 197)).astype(np.float32)
+    D = torch.zeros(2, 197, 197, dtype=torch.float32, device="cuda")
+    ctx.gemm(dev(a, torch.float32), dev(b, torch.float32), D)
+    ctx.sync()
+    assert_high(host(D), vko.matmul(a, b), "gemm fp32")
+
+
+def test_gemm_known_answer(ctx):
+    """Ops.MatMul of the reference's unit tests: [2,3] @ [3,2] -> {4,5,10,11} (tests/test_ops.cpp:309-313)."""
+    a = np.array([[1, 2, 3], [4, 5, 6]], np.float32)
+    b = np.array([[1, 0], [0, 1], [1, 1]], np.float32)
+    D = torch.zeros(2, 2, dtype=torch.float32, device="cuda")
+    ctx.gemm(dev(a, torch.float32), dev(b, torch.float32), D)
+    ctx.sync()
+    np.testing.assert_allclose(host(D).ravel(), [4, 5, 10, 11], atol=1e-4)
+
+
+# ------------------------------------------------------------------------------------------------ LayerNorm
+@pytest.mark.parametrize("dt", ["f32", "f16", "bf16"])
+@pytest.mark.parametrize("rows,norm", [(1576, 768), (2738, 1024), (256, 1024), (7, 100), (33, 2056)])
+def test_layernorm(ctx, dt, rows, norm):
+    rng = np.random.default_rng(rows + norm)
+    x = round_to(rng.standard_normal((rows, norm)) * 2 + 0.5, DT[dt])
+    g = (1 + 0.1 * rng.standard_normal(norm)).astype(np.float32)
+    b = (0.1 * rng.standard_normal(norm)).astype(np.float32)
+    ref = vko.layernorm(x, g, b, 1e-6)
+    Y = torch.zeros(rows, norm, dtype=DT[dt], device="cuda")
+    ctx.layernorm(dev(x, DT[dt]), torch.from_numpy(g).cuda(), torch.from_numpy(b).cuda(), Y, 1e-6)
+    ctx.sync()
+    if dt == "f32":
+        assert_high(host(Y), ref, "layernorm")
+    else:
+        m = metrics(host(Y), ref)
+        assert m["cosine"] >= 0.9999 and m["max_abs"] <= (4e-2 if dt == "bf16" else 1e-2), m
+    # no beta
+    ctx.layernorm(dev(x, DT[dt]), torch.from_numpy(g).cuda(), None, Y, 1e-6)
+    ctx.sync()
+    m = metrics(host(Y), vko.layernorm(x, g, None, 1e-6))
+    assert m["cosine"] >= 0.9999, m
+
+
+# ------------------------------------------------------------------------------------------------ prefill attention
+def run_attn(ctx, q, k, v, scale, dt, causal=False, kv_len=None, mask=None, impl=vknn_b200.IMPL_AUTO):
+    Q, K, V = dev(q, DT[dt]), dev(k, DT[dt]), dev(v, DT[dt])
+    O = torch.zeros_like(Q)
+    ctx.set_impl(impl)
+    try:
+        ctx.attn_prefill(Q, K, V, O, scale, causal=causal, mask=torch.from_numpy(mask).cuda() if mask is not None else None,
+                         kv_len=torch.from_numpy(kv_len).cuda() if kv_len is not None else None)
+        ctx.sync()
+    finally:
+        ctx.set_impl(vknn_b200.IMPL_AUTO)
+    return host(O)
+
+
+def test_attention_config1_fp32(ctx):
+    """Config 1: Q,K,V fp32 [1,12,197,64] ~ N(0,1), seed 1001, scale 0.125, no mask; 'high' precision."""
+    rng = np.random.default_rng(1001)
+    q, k, v = (rng.standard_normal((1, 12, 197, 64)).astype(np.float32) for _ in range(3))
+    ref = vko.attention(q, k, v, 0.125)
+    assert_high(run_attn(ctx, q, k, v, 0.125, "f32"), ref, "config 1 fp32")
+
+
+@pytest.mark.parametrize("impl", [vknn_b200.IMPL_SIMT, vknn_b200.IMPL_TCGEN05], ids=["simt", "tc"])
+@pytest.mark.parametrize("dt", ["f16", "bf16"])
+def test_attention_config1_low(ctx, impl, dt):
+    rng = np.random.default_rng(1001)
+    q, k, v = (round_to(rng.standard_normal((1, 12, 197, 64)), DT[dt]) for _ in range(3))
+    ref = vko.attention(q, k, v, 0.125)
+    assert_low(run_attn(ctx, q, k, v, 0.125, dt, impl=impl), ref, "config 1 %s" % dt)
+
+
+@pytest.mark.parametrize("impl", [vknn_b200.IMPL_SIMT, vknn_b200.IMPL_TCGEN05], ids=["simt", "tc"])
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("B,Hq,Hkv,Sq,Skv,D", [(2, 4, 4, 256, 256, 128), (1, 4, 2, 200, 333, 128), (1, 2, 1, 1, 130, 64), (2, 2, 2, 7, 65, 64),
+                                               (1, 2, 2, 640, 640, 128)])
+def test_attention_shapes(ctx, impl, causal, B, Hq, Hkv, Sq, Skv, D):
+    """Ragged sizes (not tile multiples), GQA head mapping, Sq != Skv causal offset, multi-tile sequences."""
+    rng = np.random.default_rng(B * 1000 + Sq + Skv + D + int(causal))
+    q = round_to(rng.standard_normal((B, Hq, Sq, D)), torch.bfloat16)
+    k = round_to(rng.standard_normal((B, Hkv, Skv, D)), torch.bfloat16)
+    v = round_to(rng.standard_normal((B, Hkv, Skv, D)), torch.bfloat16)
+    scale = 1.0 / np.sqrt(D)
+    ref = vko.attention(q, k, v, scale, causal=causal)
+    assert_low(run_attn(ctx, q, k, v, scale, "bf16", causal=causal, impl=impl), ref, "attn")
+
+
+@pytest.mark.parametrize("impl", [vknn_b200.IMPL_SIMT, vknn_b200.IMPL_TCGEN05], ids=["simt", "tc"])
+def test_attention_kv_len(ctx, impl):
+    rng = np.random.default_rng(77)
+    B, H, Sq, Skv, D = 3, 2, 130, 300, 64
+    q, k, v = (round_to(rng.standard_normal(s), torch.float16) for s in ((B, H, Sq, D), (B, H, Skv, D), (B, H, Skv, D)))
+    kv_len = np.array([300, 1, 129], np.int32)
+    ref = vko.attention(q, k, v, 0.125, kv_len=kv_len)
+    assert_low(run_attn(ctx, q, k, v, 0.125, "f16", kv_len=kv_len, impl=impl), ref, "kv_len")
+
+
+def test_attention_additive_mask(ctx):
+    """FusedPointwise{Mul scale, Add mask} form (the reference's gqa graph), fp32."""
+    rng = np.random.default_rng(9)
+    q, k, v = (rng.standard_normal((1, 3, 40, 64)).astype(np.float32) for _ in range(3))
+    mask = np.where(rng.random((40, 40)) < 0.3, -np.inf, 0.0).astype(np.float32)
+    mask[:, 0] = 0
+    ref = vko.attention(q, k, v, 0.125, mask=mask)
+    assert_high(run_attn(ctx, q, k, v, 0.125, "f32", mask=mask), ref, "mask")
+
+
+def test_attention_strided_views(ctx):
+    """Head split/merge absorbed as strides: Q/K/V are views of a packed [B,T,3,H,D] buffer, O of [B,T,H,D]."""
+    rng = np.random.default_rng(21)
+    B, T, H, D = 2, 197, 4, 64
+    qkv = round_to(rng.standard_normal((B, T, 3, H, D)), torch.float16)
+    t = dev(qkv, torch.float16)
+    q, k, v = (t[:, :, i].permute(0, 2, 1, 3) for i in range(3))
+    o = torch.zeros(B, T, H, D, dtype=torch.float16, device="cuda")
+    ctx.attn_prefill(q, k, v, o.permute(0, 2, 1, 3), 0.125)
+    ctx.sync()
+    qh, kh, vh = (np.ascontiguousarray(qkv[:, :, i].transpose(0, 2, 1, 3)) for i in range(3))
+    ref = vko.attention(qh, kh, vh, 0.125).transpose(0, 2, 1, 3)
+    assert_low(host(o), ref, "strided")
+
+
+def test_attention_deterministic(ctx):
+    rng = np.random.default_rng(4)
+    q, k, v = (round_to(rng.standard_normal((1, 2, 300, 128)), torch.bfloat16) for _ in range(3))
+    a = run_attn(ctx, q, k, v, 0.1, "bf16", causal=True)
+    b = run_attn(ctx, q, k, v, 0.1, "bf16", causal=True)
+    assert np.array_equal(a, b)
+
+
+# ------------------------------------------------------------------------------------------------ decode attention
+@pytest.mark.parametrize("dt", ["f16", "bf16"])
+@pytest.mark.parametrize("B,Hq,Hkv,L,D", [(4, 32, 8, 1024, 128), (2, 8, 8, 300, 64), (3, 4, 2, 777, 128), (1, 8, 1, 130, 128)])
+def test_decode(ctx, dt, B, Hq, Hkv, L, D):
+    rng = np.random.default_rng(B + Hq + L)
+    q = round_to(rng.standard_normal((B, Hq, D)), DT[dt])
+    k = round_to(rng.standard_normal((B, Hkv, L, D)), DT[dt])
+    v = round_to(rng.standard_normal((B, Hkv, L, D)), DT[dt])
+    kv_len = rng.integers(1, L + 1, B).astype(np.int32)
+    kv_len[0] = L
+    scale = 1.0 / np.sqrt(D)
+    ref = vko.attention(q[:, :, None, :], k, v, scale, kv_len=kv_len)[:, :, 0, :]
+    O = torch.zeros(B, Hq, D, dtype=DT[dt], device="cuda")
+    ctx.attn_decode(dev(q, DT[dt]), dev(k, DT[dt]), dev(v, DT[dt]), O, scale, kv_len=torch.from_numpy(kv_len).cuda())
+    ctx.sync()
+    assert_low(host(O), ref, "decode")
+    # caller-provided workspace gives the same bits
+    ws = torch.empty(ctx.attn_decode_workspace_bytes(B, Hq, Hkv, L, D), dtype=torch.uint8, device="cuda")
+    O2 = torch.zeros_like(O)
+    ctx.attn_decode(dev(q, DT[dt]), dev(k, DT[dt]), dev(v, DT[dt]), O2, scale, kv_len=torch.from_numpy(kv_len).cuda(), workspace=ws)
+    ctx.sync()
+    assert torch.equal(O, O2)
+
+
+# ------------------------------------------------------------------------------------------------ pointwise family
+def test_pointwise_known_answers(ctx):
+    """FusedPwMulAddClip and FusedPwUnaryChannelMul of the reference's tests (tests/test_ops.cpp:502-515)."""
+    x = dev(np.array([1, 2, 3, 4], np.float32).reshape(1, 1, 2, 2), torch.float32)
+    y = torch.zeros_like(x)
+    ops = [dev(np.full((1, 1, 2, 2), 2, np.float32), torch.float32), dev(np.ones((1, 1, 2, 2), np.float32), torch.float32)]
+    ctx.pointwise(x, y, [0, 0, 1, 0, 0, 6, 2, 0, 2, 3, -1, 0], [0, 0, 0, 0, 0.0, 10.0], ops)
+    ctx.sync()
+    np.testing.assert_allclose(host(y).ravel(), [3, 5, 7, 9], atol=1e-5)
+    x = dev(np.zeros((1, 3, 1, 2), np.float32), torch.float32)
+    y = torch.zeros_like(x)
+    ctx.pointwise(x, y, [1, 0, -1, 0, 0, 0, 1, 1], [0, 0, 0, 0], [dev(np.array([10, 20, 30], np.float32).reshape(1, 3, 1, 1), torch.float32)])
+    ctx.sync()
+    np.testing.assert_allclose(host(y).ravel(), [5, 5, 10, 10, 15, 15], atol=1e-5)
+
+
+def test_pointwise_gelu_chain_and_softmax(ctx):
+    rng = np.random.default_rng(8)
+    h = rng.standard_normal((37, 300)).astype(np.float32) * 2
+    X = dev(h, torch.float32)
+    Y = torch.zeros_like(X)
+    # Div(sqrt2) -> Erf -> Add(1) -> Mul(h) -> Mul(0.5) as one step program
+    ops = [dev(np.array([np.float32(1.41421356237)]), torch.float32), dev(np.array([1.0], np.float32), torch.float32), X,
+           dev(np.array([0.5], np.float32), torch.float32)]
+    ctx.pointwise(X, Y, [0, 2, 1, 0, 1, 15, -1, 0, 0, 6, 2, 0, 0, 0, 3, 0, 0, 0, 4, 0], [0] * 10, ops)
+    ctx.sync()
+    t = vko.unary(vko.binary(h, np.array([np.float32(1.41421356237)]), 2), 15)
+    ref = vko.pw_epilogue(vko.binary(t, np.array([1.0], np.float32), 6), [0, 0, 1, 0, 0, 0, 2, 0], [0, 0, 0, 0], [h, np.array([0.5], np.float32)])
+    assert_high(host(Y), ref, "gelu chain")
+    S = torch.zeros_like(X)
+    ctx.softmax(X, S)
+    ctx.sync()
+    assert_high(host(S), vko.softmax(h), "softmax")
+
+
+def test_softmax_epilogue_known_answer(ctx):
+    """CpuEpilogueHookOnProducer: softmax([1,2,3,4]) * 3 (tests/test_ops.cpp:520-608)."""
+    x = dev(np.array([[1, 2, 3, 4]], np.float32), torch.float32)
+    s, y = torch.zeros_like(x), torch.zeros_like(x)
+    ctx.softmax(x, s)
+    ctx.pointwise(s, y, [0, 0, 1, 0], [0, 0], [dev(np.array([3.0], np.float32), torch.float32)])
+    ctx.sync()
+    e = np.exp(np.array([1, 2, 3, 4], np.float32) - 4)
+    np.testing.assert_allclose(host(y).ravel(), e / e.sum() * 3, atol=1e-4)
+
+
+def test_strided_copy_transpose(ctx):
+    rng = np.random.default_rng(2)
+    x = rng.standard_normal((2, 5, 3, 4, 6)).astype(np.float32)
+    perm = [2, 0, 3, 1, 4]
+    ref = vko.transpose(x, perm)
+    X = dev(x, torch.float32)
+    Y = torch.zeros(ref.shape, dtype=torch.float32, device="cuda")
+    ist = [X.stride(p) for p in perm]
+    ctx.strided_copy(X, Y, list(ref.shape), ist)
+    ctx.sync()
+    assert np.array_equal(host(Y), ref)
+
+
+def test_upload_download_roundtrip(ctx):
+    rng = np.random.default_rng(1)
+    x = rng.standard_normal(10007).astype(np.float32)
+    d = torch.zeros(10007, dtype=torch.float16, device="cuda")
+    ctx.upload(d, x)
+    back = np.zeros(10007, np.float32)
+    ctx.download(back, d)
+    ctx.sync()
+    assert np.array_equal(back, x.astype(np.float16).astype(np.float32))
+
+
+# ------------------------------------------------------------------------------------------------ encoder block
+@pytest.mark.parametrize("B,T,d,H,dm", [(2, 197, 768, 12, 3072), (1, 300, 1024, 16, 4096)])
+def test_encoder_layer(ctx, B, T, d, H, dm):
+    """A pre-LN block at ViT-B (config 2) and d=1024 (config 3) widths, small batch so the oracle takes seconds."""
+    from vknn_b200.encoder import EncoderLayer
+    rng = np.random.default_rng(1002)
+    w = encoder_weights(rng, d, dm, bias_scale=0.01)
+    x = round_to(rng.standard_normal((B, T, d)), torch.float16)
+    ref = vko.encoder_layer(x, w, H, eps=1e-6)
+    layer = EncoderLayer(ctx, w, H, dtype=torch.float16)
+    y = layer.forward(dev(x, torch.float16))
+    ctx.sync()
+    assert_low(host(y), ref, "encoder layer")
+
+
+def test_invalid_arguments(ctx):
+    """Error behaviour: bad arguments are refused with a status and a message; nothing is launched."""
+    q = torch.zeros(1, 3, 8, 64, dtype=torch.float16, device="cuda")
+    k = torch.zeros(1, 2, 8, 64, dtype=torch.float16, device="cuda")
+    n0 = ctx.launch_count()
+    with pytest.raises(vknn_b200.VkcError) as e:
+        ctx.attn_prefill(q, k, k, q, 0.125)
+    assert e.value.code == -1 and "multiple" in str(e.value)
+    with pytest.raises(vknn_b200.VkcError):
+        ctx.attn_decode(torch.zeros(1, 4, 96, dtype=torch.float16, device="cuda"), torch.zeros(1, 4, 8, 96, dtype=torch.float16, device="cuda"),
+                        torch.zeros(1, 4, 8, 96, dtype=torch.float16, device="cuda"), torch.zeros(1, 4, 96, dtype=torch.float16, device="cuda"), 1.0)
+    assert ctx.launch_count() == n0

@@ -1,0 +1,243 @@
+"""ctypes binding of include/vknn_cuda.h. Tensors are torch CUDA tensors (device memory only); every compute
+call goes through the C-ABI entry point of the same name."""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import re
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+HEADER = os.path.join(os.path.dirname(HERE), "include", "vknn_cuda.h")
+
+F32, F16, BF16 = 0, 1, 2
+EPI_NONE, EPI_BIAS, EPI_GELU_ERF, EPI_RESIDUAL = 0, 1, 2, 4
+B_KN, B_NK = 0, 1
+IMPL_AUTO, IMPL_SIMT, IMPL_TCGEN05 = 0, 1, 2
+
+_lib = None
+
+
+class VkcError(RuntimeError):
+    def __init__(self, code, msg):
+        super().__init__("libvknn_cuda error %d: %s" % (code, msg))
+        self.code = code
+
+
+def lib_path():
+    return os.path.join(HERE, "libvknn_cuda.so")
+
+
+def declared_symbols():
+    """Names of the entry points include/vknn_cuda.h declares."""
+    with open(HEADER) as f:
+        return sorted(set(re.findall(r"VKC_API[^;(]*?\b(vkc_\w+)\s*\(", f.read())))
+
+
+def exported_symbols():
+    lib = load_library()
+    return [s for s in declared_symbols() if hasattr(lib, s)]
+
+
+def load_library():
+    """Loads libvknn_cuda.so. There is no fallback: a missing library is an error."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    path = lib_path()
+    if not os.path.exists(path):
+        raise ImportError("libvknn_cuda.so is not built (%s); run `python -m vknn_b200.build`" % path)
+    L = C.CDLL(path)
+    vp, i64, i32, f32, sz = C.c_void_p, C.c_int64, C.c_int, C.c_float, C.c_size_t
+    L.vkc_device_count.argtypes = [C.POINTER(C.c_int)]
+    L.vkc_ctx_create.argtypes = [i32, C.POINTER(vp)]
+    L.vkc_ctx_destroy.argtypes = [vp]
+    L.vkc_last_error.argtypes = [vp]
+    L.vkc_last_error.restype = C.c_char_p
+    L.vkc_ctx_set_impl.argtypes = [vp, i32]
+    L.vkc_sync.argtypes = [vp, vp]
+    L.vkc_launch_count.argtypes = [vp]
+    L.vkc_launch_count.restype = i64
+    L.vkc_alloc.argtypes = [vp, sz, C.POINTER(vp)]
+    L.vkc_free.argtypes = [vp, vp]
+    L.vkc_upload.argtypes = [vp, vp, i32, vp, i32, i64, vp]
+    L.vkc_download.argtypes = [vp, vp, i32, vp, i32, i64, vp]
+    L.vkc_convert.argtypes = [vp, vp, i32, vp, i32, i64, vp]
+    L.vkc_gemm.argtypes = [vp, vp, vp, vp, vp, vp] + [i64] * 10 + [i32, i32, i32, vp]
+    L.vkc_attn_prefill.argtypes = [vp, vp, vp, vp, vp] + [i64] * 6 + [vp, vp, vp, vp, f32, i32, vp, vp, i32, vp]
+    L.vkc_attn_decode_workspace_bytes.argtypes = [i64] * 5
+    L.vkc_attn_decode_workspace_bytes.restype = sz
+    L.vkc_attn_decode.argtypes = [vp, vp, vp, vp, vp] + [i64] * 5 + [vp, f32, vp, sz, i32, vp]
+    L.vkc_layernorm.argtypes = [vp, vp, vp, vp, vp, i64, i64, f32, i32, vp]
+    L.vkc_pointwise.argtypes = [vp, vp, vp, vp, i32, i32, vp, vp, i32, vp, vp, i32, vp]
+    L.vkc_softmax.argtypes = [vp, vp, vp, i64, i64, i32, vp]
+    L.vkc_strided_copy.argtypes = [vp, vp, vp, vp, vp, i32, i64, i32, vp]
+    L.vkc_graph_begin.argtypes = [vp]
+    L.vkc_graph_end.argtypes = [vp, C.POINTER(vp)]
+    L.vkc_graph_launch.argtypes = [vp, vp]
+    L.vkc_graph_destroy.argtypes = [vp, vp]
+    L.vkc_timer_start.argtypes = [vp, vp]
+    L.vkc_timer_stop.argtypes = [vp, vp, C.POINTER(C.c_float)]
+    if hasattr(L, "vkc_debug_set_attn_p_in_tmem"):
+        L.vkc_debug_set_attn_p_in_tmem.argtypes = [i32]
+        L.vkc_debug_set_attn_p_in_tmem.restype = None
+    _lib = L
+    return L
+
+
+def _dtype_code(t):
+    import torch
+    return {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16}[t.dtype]
+
+
+def _np_dtype_code(a):
+    import numpy as np
+    if a.dtype == np.float32:
+        return F32
+    if a.dtype == np.float16:
+        return F16
+    raise TypeError("host arrays must be float32 or float16")
+
+
+def _i64arr(vals):
+    return (C.c_int64 * len(vals))(*[int(v) for v in vals])
+
+
+class Context:
+    """One libvknn_cuda context (one device). `stream` arguments default to torch's current stream so that
+    torch.cuda.Event timing and torch allocations order correctly with the kernels."""
+
+    def __init__(self, device=0):
+        self.lib = load_library()
+        h = C.c_void_p()
+        rc = self.lib.vkc_ctx_create(int(device), C.byref(h))
+        if rc != 0:
+            raise VkcError(rc, "vkc_ctx_create(%d) failed (no usable sm_100 device?)" % device)
+        self.h = h
+        self.device = int(device)
+
+    def close(self):
+        if getattr(self, "h", None):
+            self.lib.vkc_ctx_destroy(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def _check(self, rc):
+        if rc != 0:
+            raise VkcError(rc, self.lib.vkc_last_error(self.h).decode())
+
+    def _stream(self, stream):
+        if stream is not None:
+            return C.c_void_p(stream)
+        import torch
+        return C.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
+
+    def set_impl(self, impl):
+        self._check(self.lib.vkc_ctx_set_impl(self.h, impl))
+
+    def sync(self, stream=None):
+        self._check(self.lib.vkc_sync(self.h, self._stream(stream)))
+
+    def launch_count(self):
+        return int(self.lib.vkc_launch_count(self.h))
+
+    # ---- boundary transfers (host numpy <-> device torch) ----
+    def upload(self, dst, src_host, stream=None):
+        assert dst.is_contiguous() and src_host.flags["C_CONTIGUOUS"] and dst.numel() == src_host.size
+        self._check(self.lib.vkc_upload(self.h, dst.data_ptr(), _dtype_code(dst), src_host.ctypes.data, _np_dtype_code(src_host), dst.numel(),
+                                        self._stream(stream)))
+
+    def upload_ptr(self, dst, host_ptr, host_dtype, stream=None):
+        self._check(self.lib.vkc_upload(self.h, dst.data_ptr(), _dtype_code(dst), host_ptr, host_dtype, dst.numel(), self._stream(stream)))
+
+    def download(self, dst_host, src, stream=None):
+        assert src.is_contiguous() and dst_host.flags["C_CONTIGUOUS"] and src.numel() == dst_host.size
+        self._check(self.lib.vkc_download(self.h, dst_host.ctypes.data, _np_dtype_code(dst_host), src.data_ptr(), _dtype_code(src), src.numel(),
+                                          self._stream(stream)))
+
+    def download_ptr(self, host_ptr, host_dtype, src, stream=None):
+        self._check(self.lib.vkc_download(self.h, host_ptr, host_dtype, src.data_ptr(), _dtype_code(src), src.numel(), self._stream(stream)))
+
+    def convert(self, dst, src, stream=None):
+        self._check(self.lib.vkc_convert(self.h, dst.data_ptr(), _dtype_code(dst), src.data_ptr(), _dtype_code(src), src.numel(), self._stream(stream)))
+
+    # ---- kernels ----
+    def gemm(self, A, B, D, bias=None, residual=None, b_layout=B_KN, epilogue=None, stream=None):
+        """A [batch?,M,K], B [batch?,K,N] (B_KN) or [batch?,N,K] (B_NK), D [batch?,M,N]; a 2-D operand broadcasts."""
+        M, K = A.shape[-2:]
+        N = D.shape[-1]
+        batch = D.shape[0] if D.dim() == 3 else 1
+        sa = A.stride(0) if A.dim() == 3 else 0
+        sb = B.stride(0) if B.dim() == 3 else 0
+        sd = D.stride(0) if D.dim() == 3 else 0
+        if epilogue is None:
+            epilogue = (EPI_BIAS if bias is not None else 0) | (EPI_RESIDUAL if residual is not None else 0)
+        self._check(self.lib.vkc_gemm(self.h, A.data_ptr(), B.data_ptr(), bias.data_ptr() if bias is not None else None,
+                                      residual.data_ptr() if residual is not None else None, D.data_ptr(), M, N, K, batch, sa, sb, sd,
+                                      A.stride(-2), B.stride(-2), D.stride(-2), b_layout, epilogue, _dtype_code(A), self._stream(stream)))
+
+    def attn_prefill(self, Q, K, V, O, scale, causal=False, mask=None, kv_len=None, stream=None):
+        """Q/O [B,Hq,Sq,D], K/V [B,Hkv,Skv,D]; any strides with D contiguous (views of a packed qkv buffer are fine)."""
+        B, Hq, Sq, D = Q.shape
+        _, Hkv, Skv, _ = K.shape
+        for t in (Q, K, V, O):
+            assert t.stride(-1) == 1
+        st = lambda t: _i64arr([t.stride(0), t.stride(1), t.stride(2)])  # noqa: E731
+        self._check(self.lib.vkc_attn_prefill(self.h, Q.data_ptr(), K.data_ptr(), V.data_ptr(), O.data_ptr(), B, Hq, Hkv, Sq, Skv, D,
+                                              st(Q), st(K), st(V), st(O), float(scale), int(bool(causal)),
+                                              mask.data_ptr() if mask is not None else None, kv_len.data_ptr() if kv_len is not None else None,
+                                              _dtype_code(Q), self._stream(stream)))
+
+    def attn_decode_workspace_bytes(self, B, Hq, Hkv, Lmax, D):
+        return int(self.lib.vkc_attn_decode_workspace_bytes(B, Hq, Hkv, Lmax, D))
+
+    def attn_decode(self, Q, Kc, Vc, O, scale, kv_len=None, workspace=None, stream=None):
+        """Q/O [B,Hq,D], Kc/Vc [B,Hkv,Lmax,D] contiguous."""
+        B, Hq, D = Q.shape
+        _, Hkv, Lmax, _ = Kc.shape
+        assert Q.is_contiguous() and Kc.is_contiguous() and Vc.is_contiguous() and O.is_contiguous()
+        self._check(self.lib.vkc_attn_decode(self.h, Q.data_ptr(), Kc.data_ptr(), Vc.data_ptr(), O.data_ptr(), B, Hq, Hkv, Lmax, D,
+                                             kv_len.data_ptr() if kv_len is not None else None, float(scale),
+                                             workspace.data_ptr() if workspace is not None else None,
+                                             workspace.numel() * workspace.element_size() if workspace is not None else 0, _dtype_code(Q),
+                                             self._stream(stream)))
+
+    def layernorm(self, X, gamma, beta, Y, eps, stream=None):
+        norm = gamma.numel()
+        assert X.is_contiguous() and Y.is_contiguous()
+        self._check(self.lib.vkc_layernorm(self.h, X.data_ptr(), gamma.data_ptr(), beta.data_ptr() if beta is not None else None, Y.data_ptr(),
+                                           X.numel() // norm, norm, float(eps), _dtype_code(X), self._stream(stream)))
+
+    def pointwise(self, X, Y, steps, params, operands=(), stream=None):
+        """steps: flat ints, 4 per step (kind, code, operand index 1-based, unused); operands broadcast NumPy-style."""
+        assert X.is_contiguous() and Y.is_contiguous()
+        shape = list(X.shape) or [1]
+        rank = len(shape)
+        nsteps = len(steps) // 4
+        strides = []
+        for o in operands:
+            assert o.is_contiguous()
+            oshape = [1] * (rank - o.dim()) + list(o.shape)
+            s, acc = [0] * rank, 1
+            for d in range(rank - 1, -1, -1):
+                s[d] = 0 if oshape[d] == 1 else acc
+                acc *= oshape[d]
+            strides += s
+        ptrs = (C.c_void_p * max(len(operands), 1))(*[o.data_ptr() for o in operands])
+        self._check(self.lib.vkc_pointwise(self.h, X.data_ptr(), Y.data_ptr(), _i64arr(shape), rank, nsteps,
+                                           (C.c_int32 * max(len(steps), 1))(*[int(s) for s in steps]),
+                                           (C.c_float * max(len(params), 1))(*[float(p) for p in params]), len(operands), ptrs,
+                                           _i64arr(strides or [0]), _dtype_code(X), self._stream(stream)))
+
+    def softmax(self, X, Y, stream=None):
+        inner = X.shape[-1]
+        assert X.is_contiguous() and Y.is_contiguous()
+        self._check(self.lib.vkc_softmax(self.h, X.data_ptr(), Y.data_ptr(), X.numel() // inner, inner, _dtype_code(X), self._stream(stream)))
+
+    def strided_copy(self, X, Y, shape, in_strides, in_offset=0, stream=None):
+        self._check(self.lib.vkc_strided_copy(self.h, X.data_ptr(), Y.data_ptr(), _i64arr(shape), _i64arr(in_strides), len(shape), in_offset,
+                                              _dtype_code(X), self._stream(stream)))

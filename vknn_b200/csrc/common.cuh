@@ -1,0 +1,107 @@
+// Shared host/device helpers of libvknn_cuda: the context object, status plumbing and storage-type traits.
+#pragma once
+#include "vknn_cuda.h"
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <string>
+#include <type_traits>
+
+// Device-side error codes written to vkc_ctx::dev_err (first writer wins).
+enum : int {
+    VKC_DEVERR_NONE         = 0,
+    VKC_DEVERR_WAIT_TIMEOUT = 1, // a bounded mbarrier wait ran out
+    VKC_DEVERR_TMEM_ALLOC   = 2,
+};
+
+struct vkc_ctx {
+    int          device     = 0;
+    int          sm_count   = 0;
+    int          cc_major   = 0;
+    int          impl       = VKC_IMPL_AUTO;
+    cudaStream_t stream     = nullptr;
+    int         *dev_err    = nullptr; // device word; 0 = ok
+    void        *scratch    = nullptr; // grown on demand: decode partials, upload staging
+    size_t       scratch_sz = 0;
+    cudaEvent_t  ev0 = nullptr, ev1 = nullptr;
+    int64_t      launches = 0;
+    bool         capturing = false;
+    std::string  err;
+    // driver entry point for tensor-map encoding (resolved once; no link-time dependency on libcuda)
+    void *encode_tiled = nullptr;
+};
+
+struct vkc_graph {
+    cudaGraph_t     graph = nullptr;
+    cudaGraphExec_t exec  = nullptr;
+};
+
+inline int vkc_fail(vkc_ctx *ctx, int code, const char *fmt, ...) {
+    char    buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof buf, fmt, ap);
+    va_end(ap);
+    if (ctx) ctx->err = buf;
+    return code;
+}
+
+#define VKC_CUDA(ctx, expr)                                                                                  \
+    do {                                                                                                     \
+        cudaError_t e_ = (expr);                                                                             \
+        if (e_ != cudaSuccess) return vkc_fail(ctx, VKC_ERR_CUDA, "%s: %s", #expr, cudaGetErrorString(e_)); \
+    } while (0)
+
+#define VKC_REQUIRE(ctx, cond, ...)                                  \
+    do {                                                             \
+        if (!(cond)) return vkc_fail(ctx, VKC_ERR_INVALID, __VA_ARGS__); \
+    } while (0)
+
+inline cudaStream_t vkc_pick_stream(vkc_ctx *ctx, vkc_stream s) { return s ? (cudaStream_t) s : ctx->stream; }
+
+inline int vkc_post_launch(vkc_ctx *ctx, const char *what) {
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return vkc_fail(ctx, VKC_ERR_CUDA, "launch %s: %s", what, cudaGetErrorString(e));
+    ctx->launches++;
+    return VKC_OK;
+}
+
+inline size_t vkc_dtype_size(int dt) { return dt == VKC_F32 || dt == VKC_I32 ? 4 : 2; }
+
+int vkc_ensure_scratch(vkc_ctx *ctx, size_t bytes);
+
+// ---- storage-type traits ------------------------------------------------------------------------------------
+template <typename T> struct St;
+template <> struct St<float> {
+    static __device__ __forceinline__ float ld(const float *p) { return *p; }
+    static __device__ __forceinline__ void  st(float *p, float v) { *p = v; }
+};
+template <> struct St<__half> {
+    static __device__ __forceinline__ float ld(const __half *p) { return __half2float(*p); }
+    static __device__ __forceinline__ void  st(__half *p, float v) { *p = __float2half_rn(v); }
+};
+template <> struct St<__nv_bfloat16> {
+    static __device__ __forceinline__ float ld(const __nv_bfloat16 *p) { return __bfloat162float(*p); }
+    static __device__ __forceinline__ void  st(__nv_bfloat16 *p, float v) { *p = __float2bfloat16_rn(v); }
+};
+
+// GELU in the exact operation order of the reference's node chain Div(sqrt2) -> Erf -> Add(1) -> Mul(h) -> Mul(0.5).
+__device__ __forceinline__ float vkc_gelu_erf(float h) {
+    float t = h / 1.41421356237f;
+    t       = erff(t);
+    t       = t + 1.0f;
+    t       = t * h;
+    return t * 0.5f;
+}
+
+#define VKC_DISPATCH_DTYPE(dtype, T, ...)                  \
+    switch (dtype) {                                       \
+        case VKC_F32: { using T = float; __VA_ARGS__; } break;         \
+        case VKC_F16: { using T = __half; __VA_ARGS__; } break;        \
+        case VKC_BF16: { using T = __nv_bfloat16; __VA_ARGS__; } break; \
+        default: break;                                    \
+    }

@@ -1,0 +1,255 @@
+// Context, memory, boundary transfers, graph capture and timers of libvknn_cuda.
+#include "common.cuh"
+#include "tensormap.cuh"
+
+namespace {
+
+    template <typename TS, typename TD> __global__ void convert_kernel(const TS *__restrict__ src, TD *__restrict__ dst, int64_t n) {
+        int64_t i      = (int64_t) blockIdx.x * blockDim.x + threadIdx.x;
+        int64_t stride = (int64_t) gridDim.x * blockDim.x;
+        for (; i < n; i += stride) St<TD>::st(dst + i, St<TS>::ld(src + i));
+    }
+
+    template <typename TS> int convert_from(vkc_ctx *ctx, const void *src, void *dst, int dst_dtype, int64_t n, cudaStream_t st) {
+        int     threads = 256;
+        int64_t blocks  = (n + threads - 1) / threads;
+        int     cap     = ctx->sm_count * 16;
+        int     grid    = (int) (blocks < cap ? (blocks > 0 ? blocks : 1) : cap);
+        switch (dst_dtype) {
+            case VKC_F32: convert_kernel<TS, float><<<grid, threads, 0, st>>>((const TS *) src, (float *) dst, n); break;
+            case VKC_F16: convert_kernel<TS, __half><<<grid, threads, 0, st>>>((const TS *) src, (__half *) dst, n); break;
+            case VKC_BF16: convert_kernel<TS, __nv_bfloat16><<<grid, threads, 0, st>>>((const TS *) src, (__nv_bfloat16 *) dst, n); break;
+            default: return vkc_fail(ctx, VKC_ERR_INVALID, "convert: bad dst dtype %d", dst_dtype);
+        }
+        return vkc_post_launch(ctx, "convert");
+    }
+
+} // namespace
+
+int vkc_ensure_scratch(vkc_ctx *ctx, size_t bytes) {
+    if (bytes <= ctx->scratch_sz) return VKC_OK;
+    if (ctx->capturing) return vkc_fail(ctx, VKC_ERR_INVALID, "context scratch cannot grow during graph capture; run the segment once first");
+    if (ctx->scratch) {
+        VKC_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+        VKC_CUDA(ctx, cudaFree(ctx->scratch));
+        ctx->scratch    = nullptr;
+        ctx->scratch_sz = 0;
+    }
+    size_t want = (bytes + ((size_t) 1 << 20) - 1) & ~(((size_t) 1 << 20) - 1);
+    if (cudaMalloc(&ctx->scratch, want) != cudaSuccess) {
+        cudaGetLastError();
+        return vkc_fail(ctx, VKC_ERR_OOM, "scratch allocation of %zu bytes failed", want);
+    }
+    ctx->scratch_sz = want;
+    return VKC_OK;
+}
+
+extern "C" {
+
+int vkc_device_count(int *count) {
+    if (!count) return VKC_ERR_INVALID;
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess) {
+        cudaGetLastError();
+        *count = 0;
+        return VKC_ERR_NO_DEVICE;
+    }
+    *count = n;
+    return VKC_OK;
+}
+
+int vkc_ctx_create(int device_ordinal, vkc_ctx **out) {
+    if (!out) return VKC_ERR_INVALID;
+    *out  = nullptr;
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess || n == 0) {
+        cudaGetLastError();
+        return VKC_ERR_NO_DEVICE;
+    }
+    if (device_ordinal < 0 || device_ordinal >= n) return VKC_ERR_INVALID;
+    cudaDeviceProp prop;
+    if (cudaGetDeviceProperties(&prop, device_ordinal) != cudaSuccess) return VKC_ERR_CUDA;
+    if (prop.major != 10) return VKC_ERR_NO_DEVICE; // kernels are built for sm_100a only
+    vkc_ctx *ctx  = new vkc_ctx();
+    ctx->device   = device_ordinal;
+    ctx->sm_count = prop.multiProcessorCount;
+    ctx->cc_major = prop.major;
+    if (cudaSetDevice(device_ordinal) != cudaSuccess || cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking) != cudaSuccess ||
+        cudaMalloc(&ctx->dev_err, sizeof(int)) != cudaSuccess || cudaMemset(ctx->dev_err, 0, sizeof(int)) != cudaSuccess ||
+        cudaEventCreate(&ctx->ev0) != cudaSuccess || cudaEventCreate(&ctx->ev1) != cudaSuccess) {
+        delete ctx;
+        return VKC_ERR_CUDA;
+    }
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ctx->encode_tiled, cudaEnableDefault, &qres) != cudaSuccess ||
+        qres != cudaDriverEntryPointSuccess) {
+        ctx->encode_tiled = nullptr; // tcgen05 paths report an error when asked; SIMT paths still work
+        cudaGetLastError();
+    }
+    *out = ctx;
+    return VKC_OK;
+}
+
+int vkc_ctx_destroy(vkc_ctx *ctx) {
+    if (!ctx) return VKC_OK;
+    cudaSetDevice(ctx->device);
+    if (ctx->stream) cudaStreamSynchronize(ctx->stream);
+    if (ctx->scratch) cudaFree(ctx->scratch);
+    if (ctx->dev_err) cudaFree(ctx->dev_err);
+    if (ctx->ev0) cudaEventDestroy(ctx->ev0);
+    if (ctx->ev1) cudaEventDestroy(ctx->ev1);
+    if (ctx->stream) cudaStreamDestroy(ctx->stream);
+    delete ctx;
+    return VKC_OK;
+}
+
+const char *vkc_last_error(const vkc_ctx *ctx) { return ctx ? ctx->err.c_str() : "null context"; }
+
+int vkc_ctx_set_impl(vkc_ctx *ctx, int impl) {
+    if (!ctx) return VKC_ERR_INVALID;
+    VKC_REQUIRE(ctx, impl >= VKC_IMPL_AUTO && impl <= VKC_IMPL_TCGEN05, "bad impl %d", impl);
+    ctx->impl = impl;
+    return VKC_OK;
+}
+
+int vkc_sync(vkc_ctx *ctx, vkc_stream stream) {
+    if (!ctx) return VKC_ERR_INVALID;
+    cudaStream_t st = vkc_pick_stream(ctx, stream);
+    VKC_CUDA(ctx, cudaStreamSynchronize(st));
+    int code = 0;
+    VKC_CUDA(ctx, cudaMemcpy(&code, ctx->dev_err, sizeof(int), cudaMemcpyDeviceToHost));
+    if (code != 0) {
+        cudaMemset(ctx->dev_err, 0, sizeof(int));
+        return vkc_fail(ctx, VKC_ERR_DEVICE, "device-side error word %d (1 = bounded wait ran out, 2 = tensor-memory allocation)", code);
+    }
+    return VKC_OK;
+}
+
+int64_t vkc_launch_count(const vkc_ctx *ctx) { return ctx ? ctx->launches : 0; }
+
+int vkc_alloc(vkc_ctx *ctx, size_t bytes, void **dptr) {
+    if (!ctx || !dptr) return VKC_ERR_INVALID;
+    *dptr = nullptr;
+    if (bytes == 0) return VKC_OK;
+    if (cudaMalloc(dptr, bytes) != cudaSuccess) {
+        cudaGetLastError();
+        return vkc_fail(ctx, VKC_ERR_OOM, "cudaMalloc(%zu) failed", bytes);
+    }
+    return VKC_OK;
+}
+
+int vkc_free(vkc_ctx *ctx, void *dptr) {
+    if (!ctx) return VKC_ERR_INVALID;
+    if (dptr) VKC_CUDA(ctx, cudaFree(dptr));
+    return VKC_OK;
+}
+
+int vkc_convert(vkc_ctx *ctx, void *dst, int dst_dtype, const void *src, int src_dtype, int64_t n, vkc_stream stream) {
+    if (!ctx) return VKC_ERR_INVALID;
+    VKC_REQUIRE(ctx, n >= 0 && (n == 0 || (dst && src)), "convert: null buffer");
+    if (n == 0) return VKC_OK;
+    cudaStream_t st = vkc_pick_stream(ctx, stream);
+    if (src_dtype == dst_dtype) {
+        VKC_CUDA(ctx, cudaMemcpyAsync(dst, src, (size_t) n * vkc_dtype_size(src_dtype), cudaMemcpyDeviceToDevice, st));
+        return VKC_OK;
+    }
+    switch (src_dtype) {
+        case VKC_F32: return convert_from<float>(ctx, src, dst, dst_dtype, n, st);
+        case VKC_F16: return convert_from<__half>(ctx, src, dst, dst_dtype, n, st);
+        case VKC_BF16: return convert_from<__nv_bfloat16>(ctx, src, dst, dst_dtype, n, st);
+        default: return vkc_fail(ctx, VKC_ERR_INVALID, "convert: bad src dtype %d", src_dtype);
+    }
+}
+
+int vkc_upload(vkc_ctx *ctx, void *dst_dev, int dst_dtype, const void *src_host, int src_dtype, int64_t n, vkc_stream stream) {
+    if (!ctx) return VKC_ERR_INVALID;
+    VKC_REQUIRE(ctx, n >= 0 && (n == 0 || (dst_dev && src_host)), "upload: null buffer");
+    if (n == 0) return VKC_OK;
+    cudaStream_t st = vkc_pick_stream(ctx, stream);
+    if (src_dtype == dst_dtype) {
+        VKC_CUDA(ctx, cudaMemcpyAsync(dst_dev, src_host, (size_t) n * vkc_dtype_size(src_dtype), cudaMemcpyHostToDevice, st));
+        return VKC_OK;
+    }
+    // stage in the source type on the device, then convert there (the reference converts on the host)
+    size_t bytes = (size_t) n * vkc_dtype_size(src_dtype);
+    int    rc    = vkc_ensure_scratch(ctx, bytes);
+    if (rc) return rc;
+    VKC_CUDA(ctx, cudaMemcpyAsync(ctx->scratch, src_host, bytes, cudaMemcpyHostToDevice, st));
+    return vkc_convert(ctx, dst_dev, dst_dtype, ctx->scratch, src_dtype, n, stream);
+}
+
+int vkc_download(vkc_ctx *ctx, void *dst_host, int dst_dtype, const void *src_dev, int src_dtype, int64_t n, vkc_stream stream) {
+    if (!ctx) return VKC_ERR_INVALID;
+    VKC_REQUIRE(ctx, n >= 0 && (n == 0 || (dst_host && src_dev)), "download: null buffer");
+    if (n == 0) return VKC_OK;
+    cudaStream_t st = vkc_pick_stream(ctx, stream);
+    if (src_dtype == dst_dtype) {
+        VKC_CUDA(ctx, cudaMemcpyAsync(dst_host, src_dev, (size_t) n * vkc_dtype_size(src_dtype), cudaMemcpyDeviceToHost, st));
+        return VKC_OK;
+    }
+    size_t bytes = (size_t) n * vkc_dtype_size(dst_dtype);
+    int    rc    = vkc_ensure_scratch(ctx, bytes);
+    if (rc) return rc;
+    rc = vkc_convert(ctx, ctx->scratch, dst_dtype, src_dev, src_dtype, n, stream);
+    if (rc) return rc;
+    VKC_CUDA(ctx, cudaMemcpyAsync(dst_host, ctx->scratch, bytes, cudaMemcpyDeviceToHost, st));
+    return VKC_OK;
+}
+
+int vkc_graph_begin(vkc_ctx *ctx) {
+    if (!ctx) return VKC_ERR_INVALID;
+    VKC_REQUIRE(ctx, !ctx->capturing, "graph capture already active");
+    VKC_CUDA(ctx, cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
+    ctx->capturing = true;
+    return VKC_OK;
+}
+
+int vkc_graph_end(vkc_ctx *ctx, vkc_graph **out) {
+    if (!ctx || !out) return VKC_ERR_INVALID;
+    VKC_REQUIRE(ctx, ctx->capturing, "no graph capture active");
+    ctx->capturing = false;
+    cudaGraph_t g  = nullptr;
+    VKC_CUDA(ctx, cudaStreamEndCapture(ctx->stream, &g));
+    cudaGraphExec_t ex = nullptr;
+    cudaError_t     e  = cudaGraphInstantiate(&ex, g, 0);
+    if (e != cudaSuccess) {
+        cudaGraphDestroy(g);
+        return vkc_fail(ctx, VKC_ERR_CUDA, "cudaGraphInstantiate: %s", cudaGetErrorString(e));
+    }
+    vkc_graph *vg = new vkc_graph();
+    vg->graph     = g;
+    vg->exec      = ex;
+    *out          = vg;
+    return VKC_OK;
+}
+
+int vkc_graph_launch(vkc_ctx *ctx, vkc_graph *g) {
+    if (!ctx || !g) return VKC_ERR_INVALID;
+    VKC_CUDA(ctx, cudaGraphLaunch(g->exec, ctx->stream));
+    return VKC_OK;
+}
+
+int vkc_graph_destroy(vkc_ctx *ctx, vkc_graph *g) {
+    if (!g) return VKC_OK;
+    if (g->exec) cudaGraphExecDestroy(g->exec);
+    if (g->graph) cudaGraphDestroy(g->graph);
+    delete g;
+    (void) ctx;
+    return VKC_OK;
+}
+
+int vkc_timer_start(vkc_ctx *ctx, vkc_stream stream) {
+    if (!ctx) return VKC_ERR_INVALID;
+    VKC_CUDA(ctx, cudaEventRecord(ctx->ev0, vkc_pick_stream(ctx, stream)));
+    return VKC_OK;
+}
+
+int vkc_timer_stop(vkc_ctx *ctx, vkc_stream stream, float *ms) {
+    if (!ctx || !ms) return VKC_ERR_INVALID;
+    VKC_CUDA(ctx, cudaEventRecord(ctx->ev1, vkc_pick_stream(ctx, stream)));
+    VKC_CUDA(ctx, cudaEventSynchronize(ctx->ev1));
+    VKC_CUDA(ctx, cudaEventElapsedTime(ms, ctx->ev0, ctx->ev1));
+    return VKC_OK;
+}
+
+} // extern "C"

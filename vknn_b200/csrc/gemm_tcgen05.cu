@@ -1,0 +1,257 @@
+// K1 — batched GEMM on the 5th-generation tensor cores with a fused bias / GELU(erf) / residual epilogue.
+//
+//   D[b,m,n] = epi( sum_k A[b,m,k] * B[b,k,n] ),  A/B/D in f16 or bf16, fp32 accumulation in tensor memory.
+//
+// One CTA computes one 128 x BN output tile. Warp roles:
+//   warp 0   : TMA producer  — one elected lane streams 128x64 A tiles and BNx64 B tiles (128-byte swizzle)
+//              through a 4-stage shared-memory ring, completion on per-stage "full" mbarriers;
+//   warp 1   : MMA issuer    — owns the tensor-memory allocation; one elected lane issues four
+//              tcgen05.mma (M=128, N=BN, K=16) per stage and commits the stage's "empty" mbarrier;
+//   warps 2-5: epilogue      — each warp owns the 32 TMEM lanes (= output rows) it may address, reads the
+//              accumulator with tcgen05.ld in 32-column slabs, applies the epilogue in fp32 and stores.
+// B is taken either as [N,K] rows (K contiguous, "K-major") or as [K,N] rows (N contiguous, "MN-major"),
+// so weights in the reference's row-major [K,N] initializer layout are consumed without a transpose.
+// M/N/K tails rely on TMA zero fill for loads and on predicated stores.
+#include "common.cuh"
+#include "ptx.cuh"
+#include "tensormap.cuh"
+
+namespace {
+
+    constexpr int BM      = 128;
+    constexpr int BK      = 64;
+    constexpr int kStages = 4;
+    constexpr int kThreads = 192;
+
+    struct GemmParams {
+        const float *bias;
+        const void  *residual;
+        void        *D;
+        int64_t      M, N, K;
+        int64_t      ldd, stride_d;
+        int          epilogue;
+        int          a_bcast, b_bcast; // batch stride 0: always read batch slice 0
+        int         *dev_err;
+    };
+
+    template <int BN> constexpr int smem_bytes() { return kStages * (BM * BK * 2 + BN * BK * 2) + 1024 /*align*/ + 256 /*barriers*/; }
+
+    template <int BN, typename T, bool B_KN>
+    __global__ void __launch_bounds__(kThreads, 1)
+        gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmParams p) {
+        constexpr uint32_t A_BYTES = BM * BK * 2;
+        constexpr uint32_t B_BYTES = BN * BK * 2;
+        constexpr bool     kBf16   = std::is_same<T, __nv_bfloat16>::value;
+        constexpr uint32_t kIdesc  = ptx::idesc_f16(BM, BN, kBf16, false, B_KN);
+
+        extern __shared__ uint8_t smem_raw[];
+        const uint32_t raw   = ptx::smem_u32(smem_raw);
+        const uint32_t base  = (raw + 1023u) & ~1023u;
+        uint8_t       *gbase = smem_raw + (base - raw);
+        const uint32_t sA    = base;
+        const uint32_t sB    = base + kStages * A_BYTES;
+        const uint32_t sBar  = sB + kStages * B_BYTES; // full[kStages], empty[kStages], accum : 8 bytes each
+        volatile int  *ctl   = (volatile int *) (gbase + kStages * (A_BYTES + B_BYTES) + 8 * (2 * kStages + 1));
+        // ctl[0] = tmem base (written by tcgen05.alloc), ctl[1] = abort flag
+        const uint32_t sSlot = sBar + 8 * (2 * kStages + 1);
+
+        const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+        const int m0 = blockIdx.x * BM, n0 = blockIdx.y * BN, bz = blockIdx.z;
+        const int num_kb = (int) ((p.K + BK - 1) / BK);
+
+        if (threadIdx.x == 0) {
+            for (int s = 0; s < kStages; ++s) {
+                ptx::mbar_init(sBar + 8 * s, 1);
+                ptx::mbar_init(sBar + 8 * (kStages + s), 1);
+            }
+            ptx::mbar_init(sBar + 8 * 2 * kStages, 1);
+            ctl[1] = 0;
+            ptx::fence_mbar_init();
+            ptx::prefetch_tmap(&tmA);
+            ptx::prefetch_tmap(&tmB);
+        }
+        if (warp == 1) {
+            ptx::tmem_alloc(sSlot, BN);
+            ptx::tmem_relinquish();
+        }
+        ptx::tc_fence_before();
+        __syncthreads();
+        ptx::tc_fence_after();
+        const uint32_t tmem = (uint32_t) ctl[0];
+
+        if (warp == 0) {
+            if (ptx::elect_one()) {
+                const int za = p.a_bcast ? 0 : bz, zb = p.b_bcast ? 0 : bz;
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    const int      s  = kb % kStages;
+                    const uint32_t ph = (kb / kStages) & 1;
+                    if (!ptx::mbar_wait(sBar + 8 * (kStages + s), ph ^ 1, ctl + 1, p.dev_err)) break;
+                    const uint32_t full = sBar + 8 * s;
+                    ptx::mbar_expect_tx(full, A_BYTES + B_BYTES);
+                    ptx::tma_load_3d(sA + s * A_BYTES, &tmA, kb * BK, m0, za, full);
+                    if (!B_KN) {
+                        ptx::tma_load_3d(sB + s * B_BYTES, &tmB, kb * BK, n0, zb, full);
+                    } else {
+#pragma unroll
+                        for (int c = 0; c < BN / 64; ++c) ptx::tma_load_3d(sB + s * B_BYTES + c * (BK * 128), &tmB, n0 + c * 64, kb * BK, zb, full);
+                    }
+                }
+            }
+        } else if (warp == 1) {
+            if (ptx::elect_one()) {
+                bool ok = true;
+                for (int kb = 0; kb < num_kb && ok; ++kb) {
+                    const int      s  = kb % kStages;
+                    const uint32_t ph = (kb / kStages) & 1;
+                    ok                = ptx::mbar_wait(sBar + 8 * s, ph, ctl + 1, p.dev_err);
+                    if (!ok) break;
+                    ptx::tc_fence_after();
+#pragma unroll
+                    for (int k = 0; k < BK / 16; ++k) {
+                        const uint64_t ad = ptx::smem_desc_sw128(sA + s * A_BYTES + k * 32, 16, 1024);
+                        const uint64_t bd = B_KN ? ptx::smem_desc_sw128(sB + s * B_BYTES + k * (16 * 128), BK * 128, 1024)
+                                                 : ptx::smem_desc_sw128(sB + s * B_BYTES + k * 32, 16, 1024);
+                        ptx::mma_f16_ss(tmem, ad, bd, kIdesc, (kb | k) != 0 ? 1u : 0u);
+                    }
+                    ptx::tc_commit(sBar + 8 * (kStages + s)); // frees the stage once these MMAs have read it
+                }
+                if (ok) ptx::tc_commit(sBar + 8 * 2 * kStages); // accumulator complete
+            }
+        } else {
+            const bool ok = ptx::mbar_wait(sBar + 8 * 2 * kStages, 0, ctl + 1, p.dev_err);
+            ptx::tc_fence_after();
+            if (ok) {
+                const int     q   = warp & 3; // the TMEM lane quarter this warp may address
+                const int64_t m   = (int64_t) m0 + q * 32 + lane;
+                T            *drow = (T *) p.D + (int64_t) bz * p.stride_d + m * p.ldd;
+                const T      *rrow = p.residual ? (const T *) p.residual + (int64_t) bz * p.stride_d + m * p.ldd : nullptr;
+                const bool    vec_ok = (p.ldd % 8 == 0) && (p.stride_d % 8 == 0) && (((uintptr_t) p.D & 15) == 0) &&
+                                    (!p.residual || ((uintptr_t) p.residual & 15) == 0);
+#pragma unroll 1
+                for (int c = 0; c < BN / 32; ++c) {
+                    const int64_t nb = (int64_t) n0 + c * 32;
+                    if (nb >= p.N) break; // uniform across the CTA
+                    uint32_t r[32];
+                    ptx::tmem_ld_x32(tmem + ((uint32_t) (q * 32) << 16) + (uint32_t) (c * 32), r);
+                    ptx::tc_wait_ld();
+                    if (m < p.M) {
+                        float v[32];
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+                        const bool full = nb + 32 <= p.N;
+                        if (p.epilogue & VKC_EPI_BIAS) {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                if (full || nb + j < p.N) v[j] += __ldg(p.bias + nb + j);
+                        }
+                        if (p.epilogue & VKC_EPI_GELU_ERF) {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) v[j] = vkc_gelu_erf(v[j]);
+                        }
+                        if (full && vec_ok) {
+#pragma unroll
+                            for (int g = 0; g < 4; ++g) {
+                                if (p.epilogue & VKC_EPI_RESIDUAL) {
+                                    uint4    rv = *reinterpret_cast<const uint4 *>(rrow + nb + g * 8);
+                                    const T *rt = reinterpret_cast<const T *>(&rv);
+#pragma unroll
+                                    for (int j = 0; j < 8; ++j) v[g * 8 + j] += St<T>::ld(rt + j);
+                                }
+                                uint4 ov;
+                                T    *ot = reinterpret_cast<T *>(&ov);
+#pragma unroll
+                                for (int j = 0; j < 8; ++j) St<T>::st(ot + j, v[g * 8 + j]);
+                                *reinterpret_cast<uint4 *>(drow + nb + g * 8) = ov;
+                            }
+                        } else {
+                            for (int j = 0; j < 32; ++j) {
+                                if (nb + j < p.N) {
+                                    float o = v[j];
+                                    if (p.epilogue & VKC_EPI_RESIDUAL) o += St<T>::ld(rrow + nb + j);
+                                    St<T>::st(drow + nb + j, o);
+                                }
+                            }
+                        }
+                    }
+                }
+            }
+        }
+        if (ctl[1]) {
+            // aborted: give copies still in flight time to land before the CTA releases its shared memory
+            for (int i = 0; i < 50; ++i) __nanosleep(20000);
+        }
+        ptx::tc_fence_before();
+        __syncthreads();
+        if (warp == 1) ptx::tmem_dealloc(tmem, BN);
+    }
+
+    template <int BN, typename T, bool B_KN>
+    int launch(vkc_ctx *ctx, const CUtensorMap &tmA, const CUtensorMap &tmB, const GemmParams &p, int64_t batch, cudaStream_t st) {
+        auto        kern = gemm_tcgen05_kernel<BN, T, B_KN>;
+        constexpr int smem = smem_bytes<BN>();
+        static bool attr_set = false; // per template instance; one device per process
+        if (!attr_set) {
+            VKC_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+            attr_set = true;
+        }
+        dim3 grid((unsigned) ((p.M + BM - 1) / BM), (unsigned) ((p.N + BN - 1) / BN), (unsigned) batch);
+        kern<<<grid, kThreads, smem, st>>>(tmA, tmB, p);
+        return vkc_post_launch(ctx, "gemm_tcgen05");
+    }
+
+} // namespace
+
+// Returns VKC_ERR_UNSUPPORTED (without touching ctx->err semantics beyond the message) when the operands do not
+// meet the TMA alignment rules; the caller then uses the SIMT kernel.
+int vkc_gemm_tcgen05(vkc_ctx *ctx, const void *A, const void *B, const float *bias, const void *residual, void *D, int64_t M, int64_t N,
+                     int64_t K, int64_t batch, int64_t stride_a, int64_t stride_b, int64_t stride_d, int64_t lda, int64_t ldb, int64_t ldd,
+                     int b_layout, int epilogue, int dtype, cudaStream_t st) {
+    if (dtype != VKC_F16 && dtype != VKC_BF16) return vkc_fail(ctx, VKC_ERR_UNSUPPORTED, "gemm_tcgen05: 16-bit storage only");
+    if ((lda % 8) || (ldb % 8) || (stride_a % 8) || (stride_b % 8) || ((uintptr_t) A & 15) || ((uintptr_t) B & 15))
+        return vkc_fail(ctx, VKC_ERR_UNSUPPORTED, "gemm_tcgen05: operand strides/bases must be multiples of 16 bytes");
+    if (M > INT32_MAX || N > INT32_MAX || K > INT32_MAX || batch > 65535) return vkc_fail(ctx, VKC_ERR_UNSUPPORTED, "gemm_tcgen05: extent too large");
+
+    const bool a_bcast = stride_a == 0 || batch == 1, b_bcast = stride_b == 0 || batch == 1;
+    const int  BN      = (N > 128 && ((M + BM - 1) / BM) * ((N + 255) / 256) * batch >= (int64_t) ctx->sm_count) ? 256 : 128;
+
+    CUtensorMap tmA, tmB;
+    {
+        uint64_t dims[3] = {(uint64_t) K, (uint64_t) M, (uint64_t) (a_bcast ? 1 : batch)};
+        uint64_t str[2]  = {(uint64_t) lda * 2, (uint64_t) (a_bcast ? (uint64_t) lda * 2 * (uint64_t) M : (uint64_t) stride_a * 2)};
+        uint32_t box[3]  = {BK, BM, 1};
+        int      rc      = vkc_make_tmap(ctx, &tmA, dtype, A, 3, dims, str, box);
+        if (rc) return rc;
+    }
+    if (b_layout == VKC_B_NK) {
+        uint64_t dims[3] = {(uint64_t) K, (uint64_t) N, (uint64_t) (b_bcast ? 1 : batch)};
+        uint64_t str[2]  = {(uint64_t) ldb * 2, (uint64_t) (b_bcast ? (uint64_t) ldb * 2 * (uint64_t) N : (uint64_t) stride_b * 2)};
+        uint32_t box[3]  = {BK, (uint32_t) BN, 1};
+        int      rc      = vkc_make_tmap(ctx, &tmB, dtype, B, 3, dims, str, box);
+        if (rc) return rc;
+    } else {
+        uint64_t dims[3] = {(uint64_t) N, (uint64_t) K, (uint64_t) (b_bcast ? 1 : batch)};
+        uint64_t str[2]  = {(uint64_t) ldb * 2, (uint64_t) (b_bcast ? (uint64_t) ldb * 2 * (uint64_t) K : (uint64_t) stride_b * 2)};
+        uint32_t box[3]  = {64, BK, 1};
+        int      rc      = vkc_make_tmap(ctx, &tmB, dtype, B, 3, dims, str, box);
+        if (rc) return rc;
+    }
+    GemmParams p;
+    p.bias     = bias;
+    p.residual = residual;
+    p.D        = D;
+    p.M        = M;
+    p.N        = N;
+    p.K        = K;
+    p.ldd      = ldd;
+    p.stride_d = stride_d;
+    p.epilogue = epilogue;
+    p.a_bcast  = a_bcast;
+    p.b_bcast  = b_bcast;
+    p.dev_err  = ctx->dev_err;
+
+#define VKC_GEMM_LAUNCH(BN_, T_)                                                                    \
+    (b_layout == VKC_B_KN ? launch<BN_, T_, true>(ctx, tmA, tmB, p, batch, st) : launch<BN_, T_, false>(ctx, tmA, tmB, p, batch, st))
+    if (dtype == VKC_F16) return BN == 256 ? VKC_GEMM_LAUNCH(256, __half) : VKC_GEMM_LAUNCH(128, __half);
+    return BN == 256 ? VKC_GEMM_LAUNCH(256, __nv_bfloat16) : VKC_GEMM_LAUNCH(128, __nv_bfloat16);
+#undef VKC_GEMM_LAUNCH
+}

@@ -1,0 +1,147 @@
+// K4 — LayerNorm over the trailing `norm` elements, HBM-bound: one warp per row, 128-bit loads, the row held in
+// registers between the two statistics passes (mean first, then the centred second moment, the same two-pass
+// form as the CPU reference) and the normalise/scale/shift pass, warp-shuffle reductions only. Each row is
+// read once and written once: algorithmic bytes = rows * norm * 2 * sizeof(T) + 8 * norm.
+#include "common.cuh"
+
+namespace {
+
+    template <typename T> struct Vec16 {
+        static constexpr int N = 16 / sizeof(T);
+    };
+
+    __device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+        return v;
+    }
+
+    // CHUNKS = 16-byte vectors per lane kept in registers; covers norm <= 32 * CHUNKS * (16/sizeof(T)).
+    template <typename T, int CHUNKS>
+    __global__ void __launch_bounds__(256) layernorm_kernel(const T *__restrict__ X, const float *__restrict__ gamma,
+                                                            const float *__restrict__ beta, T *__restrict__ Y, int64_t rows, int norm, float eps) {
+        constexpr int VN   = Vec16<T>::N;
+        const int     lane = threadIdx.x & 31;
+        const int64_t row  = (int64_t) blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+        if (row >= rows) return;
+        const T *xr = X + row * norm;
+        T       *yr = Y + row * norm;
+        float    v[CHUNKS][VN];
+        float    s = 0.f;
+#pragma unroll
+        for (int c = 0; c < CHUNKS; ++c) {
+            const int e = (c * 32 + lane) * VN;
+            if (e < norm) {
+                const uint4 raw = *reinterpret_cast<const uint4 *>(xr + e);
+                const T    *t   = reinterpret_cast<const T *>(&raw);
+#pragma unroll
+                for (int j = 0; j < VN; ++j) {
+                    v[c][j] = St<T>::ld(t + j);
+                    s += v[c][j];
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < VN; ++j) v[c][j] = 0.f;
+            }
+        }
+        const float mean = warp_sum(s) / (float) norm;
+        float       q    = 0.f;
+#pragma unroll
+        for (int c = 0; c < CHUNKS; ++c) {
+            const int e = (c * 32 + lane) * VN;
+            if (e < norm) {
+#pragma unroll
+                for (int j = 0; j < VN; ++j) {
+                    const float d = v[c][j] - mean;
+                    q += d * d;
+                }
+            }
+        }
+        const float var = warp_sum(q) / (float) norm;
+        const float inv = 1.0f / sqrtf(var + eps);
+#pragma unroll
+        for (int c = 0; c < CHUNKS; ++c) {
+            const int e = (c * 32 + lane) * VN;
+            if (e < norm) {
+                uint4 out;
+                T    *t = reinterpret_cast<T *>(&out);
+#pragma unroll
+                for (int j = 0; j < VN; ++j) {
+                    float o = (v[c][j] - mean) * inv * __ldg(gamma + e + j);
+                    if (beta) o += __ldg(beta + e + j);
+                    St<T>::st(t + j, o);
+                }
+                *reinterpret_cast<uint4 *>(yr + e) = out;
+            }
+        }
+    }
+
+    // Any norm / alignment: one warp per row, three passes over global memory (rows stay L1/L2 resident).
+    template <typename T>
+    __global__ void __launch_bounds__(256) layernorm_generic_kernel(const T *__restrict__ X, const float *__restrict__ gamma,
+                                                                    const float *__restrict__ beta, T *__restrict__ Y, int64_t rows, int64_t norm,
+                                                                    float eps) {
+        const int     lane = threadIdx.x & 31;
+        const int64_t row  = (int64_t) blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+        if (row >= rows) return;
+        const T *xr = X + row * norm;
+        T       *yr = Y + row * norm;
+        float    s  = 0.f;
+        for (int64_t j = lane; j < norm; j += 32) s += St<T>::ld(xr + j);
+        const float mean = warp_sum(s) / (float) norm;
+        float       q    = 0.f;
+        for (int64_t j = lane; j < norm; j += 32) {
+            const float d = St<T>::ld(xr + j) - mean;
+            q += d * d;
+        }
+        const float inv = 1.0f / sqrtf(warp_sum(q) / (float) norm + eps);
+        for (int64_t j = lane; j < norm; j += 32) {
+            float o = (St<T>::ld(xr + j) - mean) * inv * gamma[j];
+            if (beta) o += beta[j];
+            St<T>::st(yr + j, o);
+        }
+    }
+
+    template <typename T>
+    int launch_ln(vkc_ctx *ctx, const void *X, const float *gamma, const float *beta, void *Y, int64_t rows, int64_t norm, float eps, cudaStream_t st) {
+        constexpr int VN      = Vec16<T>::N;
+        const int     wpb     = 8; // warps (= rows) per block
+        const int64_t blocks  = (rows + wpb - 1) / wpb;
+        const bool    aligned = (norm % VN == 0) && (((uintptr_t) X & 15) == 0) && (((uintptr_t) Y & 15) == 0);
+        const int64_t chunks  = (norm + 32 * VN - 1) / (32 * VN);
+        if (blocks > INT32_MAX) return vkc_fail(ctx, VKC_ERR_UNSUPPORTED, "layernorm: too many rows");
+#define VKC_LN(C) layernorm_kernel<T, C><<<(unsigned) blocks, wpb * 32, 0, st>>>((const T *) X, gamma, beta, (T *) Y, rows, (int) norm, eps)
+        if (aligned && chunks <= 8) {
+            switch (chunks) {
+                case 1: VKC_LN(1); break;
+                case 2: VKC_LN(2); break;
+                case 3: VKC_LN(3); break;
+                case 4: VKC_LN(4); break;
+                case 5: VKC_LN(5); break;
+                case 6: VKC_LN(6); break;
+                case 7: VKC_LN(7); break;
+                default: VKC_LN(8); break;
+            }
+        } else {
+            layernorm_generic_kernel<T><<<(unsigned) blocks, wpb * 32, 0, st>>>((const T *) X, gamma, beta, (T *) Y, rows, norm, eps);
+        }
+#undef VKC_LN
+        return vkc_post_launch(ctx, "layernorm");
+    }
+
+} // namespace
+
+extern "C" int vkc_layernorm(vkc_ctx *ctx, const void *X, const float *gamma, const float *beta, void *Y, int64_t rows, int64_t norm, float eps,
+                             int dtype, vkc_stream stream) {
+    if (!ctx) return VKC_ERR_INVALID;
+    VKC_REQUIRE(ctx, rows >= 0 && norm >= 1, "layernorm: bad extents rows=%lld norm=%lld", (long long) rows, (long long) norm);
+    VKC_REQUIRE(ctx, dtype == VKC_F32 || dtype == VKC_F16 || dtype == VKC_BF16, "layernorm: bad dtype %d", dtype);
+    if (rows == 0) return VKC_OK;
+    VKC_REQUIRE(ctx, X && Y && gamma, "layernorm: null operand");
+    cudaStream_t st = vkc_pick_stream(ctx, stream);
+    switch (dtype) {
+        case VKC_F32: return launch_ln<float>(ctx, X, gamma, beta, Y, rows, norm, eps, st);
+        case VKC_F16: return launch_ln<__half>(ctx, X, gamma, beta, Y, rows, norm, eps, st);
+        default: return launch_ln<__nv_bfloat16>(ctx, X, gamma, beta, Y, rows, norm, eps, st);
+    }
+}

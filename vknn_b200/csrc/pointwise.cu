@@ -1,0 +1,236 @@
+// K5 — per-element step programs (the reference's FusedPointwise / Binary / Unary / Add family), standalone row
+// Softmax and the strided gather copy used for Transpose/Gather/Slice nodes that cannot be absorbed as strides.
+// All arithmetic is fp32, in the reference's step order; only loads and the final store touch the storage type.
+#include "common.cuh"
+
+namespace {
+
+    constexpr int kMaxSteps = 8, kMaxOperands = 6, kMaxRank = 8;
+
+    struct PwProgram {
+        int         nsteps, rank, noperands;
+        int         kind[kMaxSteps], code[kMaxSteps], opidx[kMaxSteps];
+        float       p0[kMaxSteps], p1[kMaxSteps];
+        int64_t     shape[kMaxRank];
+        int64_t     ostride[kMaxOperands][kMaxRank];
+        const void *operand[kMaxOperands];
+        int         same_shape[kMaxOperands]; // operand is dense with the output's shape: index = linear index
+    };
+
+    __device__ __forceinline__ float pw_binary(float a, float b, int op) {
+        switch (op) {
+            case 0: return a * b;
+            case 1: return a - b;
+            case 2: return a / b;
+            case 3: return fmaxf(a, b);
+            case 4: return fminf(a, b);
+            case 5: return powf(a, b);
+            default: return a + b;
+        }
+    }
+    __device__ __forceinline__ float pw_unary(float x, int op, float a, float b) {
+        switch (op) {
+            case 0: return 1.f / (1.f + expf(-x));
+            case 1: return tanhf(x);
+            case 2: return x * fminf(fmaxf(x + 3.f, 0.f), 6.f) / 6.f;
+            case 3: return fminf(fmaxf(a * x + b, 0.f), 1.f);
+            case 4: return x > 0 ? x : a * x;
+            case 5: return x > 0 ? x : a * (expf(x) - 1.f);
+            case 6: return fabsf(x);
+            case 7: return -x;
+            case 8: return expf(x);
+            case 9: return logf(x);
+            case 10: return sqrtf(x);
+            case 11: return floorf(x);
+            case 12: return ceilf(x);
+            case 13: return x > 0 ? x : 0.f;
+            case 14: return x / (1.f + expf(-x));
+            case 15: return erff(x);
+            case 16: return cosf(x);
+            case 17: return sinf(x);
+            case 18: return 1.f / x;
+            case 19: return fmaxf(x, 0.f) + log1pf(expf(-fabsf(x)));
+            default: return x;
+        }
+    }
+    __device__ __forceinline__ float pw_act(float x, int act, float lo, float hi) {
+        switch (act) {
+            case 1: return x > 0 ? x : 0.f;
+            case 2: return x < 0 ? 0.f : (x > 6.f ? 6.f : x);
+            case 3: return x < lo ? lo : (x > hi ? hi : x);
+            case 4: return x * fminf(fmaxf(x + 3.f, 0.f), 6.f) / 6.f;
+            case 5: return x / (1.f + expf(-x));
+            default: return x;
+        }
+    }
+
+    template <typename T> __global__ void __launch_bounds__(256) pointwise_kernel(const T *__restrict__ X, T *__restrict__ Y, int64_t n, PwProgram pg) {
+        int64_t       i      = (int64_t) blockIdx.x * blockDim.x + threadIdx.x;
+        const int64_t stride = (int64_t) gridDim.x * blockDim.x;
+        for (; i < n; i += stride) {
+            float acc = St<T>::ld(X + i);
+            for (int s = 0; s < pg.nsteps; ++s) {
+                if (pg.kind[s] == 0) {
+                    const int oi = pg.opidx[s];
+                    int64_t   io = 0;
+                    if (pg.same_shape[oi]) {
+                        io = i;
+                    } else {
+                        int64_t rem = i;
+                        for (int d = pg.rank - 1; d >= 0; --d) {
+                            const int64_t c = rem % pg.shape[d];
+                            rem /= pg.shape[d];
+                            io += c * pg.ostride[oi][d];
+                        }
+                    }
+                    acc = pw_binary(acc, St<T>::ld((const T *) pg.operand[oi] + io), pg.code[s]);
+                } else if (pg.kind[s] == 1) {
+                    acc = pw_unary(acc, pg.code[s], pg.p0[s], pg.p1[s]);
+                } else {
+                    acc = pw_act(acc, pg.code[s], pg.p0[s], pg.p1[s]);
+                }
+            }
+            St<T>::st(Y + i, acc);
+        }
+    }
+
+    // One warp per row: max, sum of exp (fp32), normalise. Rows are re-read from L1/L2 between passes.
+    template <typename T> __global__ void __launch_bounds__(256) softmax_kernel(const T *__restrict__ X, T *__restrict__ Y, int64_t outer, int64_t inner) {
+        const int     lane = threadIdx.x & 31;
+        const int64_t row  = (int64_t) blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+        if (row >= outer) return;
+        const T *xr = X + row * inner;
+        T       *yr = Y + row * inner;
+        float    mx = -INFINITY;
+        for (int64_t j = lane; j < inner; j += 32) mx = fmaxf(mx, St<T>::ld(xr + j));
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        float s = 0.f;
+        for (int64_t j = lane; j < inner; j += 32) s += expf(St<T>::ld(xr + j) - mx);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+        for (int64_t j = lane; j < inner; j += 32) St<T>::st(yr + j, expf(St<T>::ld(xr + j) - mx) / s);
+    }
+
+    struct CopyDesc {
+        int     rank;
+        int64_t shape[kMaxRank], istride[kMaxRank], offset;
+    };
+
+    template <typename T> __global__ void __launch_bounds__(256) strided_copy_kernel(const T *__restrict__ X, T *__restrict__ Y, int64_t n, CopyDesc cd) {
+        int64_t       i      = (int64_t) blockIdx.x * blockDim.x + threadIdx.x;
+        const int64_t stride = (int64_t) gridDim.x * blockDim.x;
+        for (; i < n; i += stride) {
+            int64_t rem = i, src = cd.offset;
+            for (int d = cd.rank - 1; d >= 0; --d) {
+                const int64_t c = rem % cd.shape[d];
+                rem /= cd.shape[d];
+                src += c * cd.istride[d];
+            }
+            Y[i] = X[src];
+        }
+    }
+
+    inline int grid_for(vkc_ctx *ctx, int64_t n) {
+        int64_t blocks = (n + 255) / 256;
+        int64_t cap    = (int64_t) ctx->sm_count * 16;
+        return (int) (blocks < cap ? (blocks > 0 ? blocks : 1) : cap);
+    }
+
+} // namespace
+
+extern "C" {
+
+int vkc_pointwise(vkc_ctx *ctx, const void *X, void *Y, const int64_t *shape, int rank, int nsteps, const int32_t *steps, const float *params,
+                  int noperands, const void *const *operands, const int64_t *op_strides, int dtype, vkc_stream stream) {
+    if (!ctx) return VKC_ERR_INVALID;
+    VKC_REQUIRE(ctx, rank >= 1 && rank <= kMaxRank && shape, "pointwise: rank %d out of range", rank);
+    VKC_REQUIRE(ctx, nsteps >= 0 && nsteps <= kMaxSteps, "pointwise: %d steps exceed the limit of %d", nsteps, kMaxSteps);
+    VKC_REQUIRE(ctx, noperands >= 0 && noperands <= kMaxOperands, "pointwise: %d operands exceed the limit of %d", noperands, kMaxOperands);
+    VKC_REQUIRE(ctx, dtype == VKC_F32 || dtype == VKC_F16 || dtype == VKC_BF16, "pointwise: bad dtype %d", dtype);
+    PwProgram pg;
+    memset(&pg, 0, sizeof pg);
+    pg.nsteps    = nsteps;
+    pg.rank      = rank;
+    pg.noperands = noperands;
+    int64_t n    = 1;
+    for (int d = 0; d < rank; ++d) {
+        VKC_REQUIRE(ctx, shape[d] >= 0, "pointwise: negative dim");
+        pg.shape[d] = shape[d];
+        n *= shape[d];
+    }
+    for (int o = 0; o < noperands; ++o) {
+        VKC_REQUIRE(ctx, operands && operands[o] && op_strides, "pointwise: null operand %d", o);
+        pg.operand[o] = operands[o];
+        int64_t dense = 1;
+        bool    same  = true;
+        for (int d = rank - 1; d >= 0; --d) {
+            pg.ostride[o][d] = op_strides[o * rank + d];
+            if (shape[d] != 1 && pg.ostride[o][d] != dense) same = false;
+            dense *= shape[d];
+        }
+        pg.same_shape[o] = same;
+    }
+    for (int s = 0; s < nsteps; ++s) {
+        pg.kind[s]  = steps[s * 4 + 0];
+        pg.code[s]  = steps[s * 4 + 1];
+        pg.opidx[s] = steps[s * 4 + 2] - 1; // the reference numbers operands from 1 (0 is the primary)
+        pg.p0[s]    = params ? params[s * 2 + 0] : 0.f;
+        pg.p1[s]    = params ? params[s * 2 + 1] : 0.f;
+        VKC_REQUIRE(ctx, pg.kind[s] >= 0 && pg.kind[s] <= 2, "pointwise: bad step kind %d", pg.kind[s]);
+        if (pg.kind[s] == 0) VKC_REQUIRE(ctx, pg.opidx[s] >= 0 && pg.opidx[s] < noperands, "pointwise: step %d names operand %d of %d", s, pg.opidx[s] + 1, noperands);
+    }
+    if (n == 0) return VKC_OK;
+    VKC_REQUIRE(ctx, X && Y, "pointwise: null tensor");
+    cudaStream_t st = vkc_pick_stream(ctx, stream);
+    const int    g  = grid_for(ctx, n);
+    switch (dtype) {
+        case VKC_F32: pointwise_kernel<float><<<g, 256, 0, st>>>((const float *) X, (float *) Y, n, pg); break;
+        case VKC_F16: pointwise_kernel<__half><<<g, 256, 0, st>>>((const __half *) X, (__half *) Y, n, pg); break;
+        default: pointwise_kernel<__nv_bfloat16><<<g, 256, 0, st>>>((const __nv_bfloat16 *) X, (__nv_bfloat16 *) Y, n, pg); break;
+    }
+    return vkc_post_launch(ctx, "pointwise");
+}
+
+int vkc_softmax(vkc_ctx *ctx, const void *X, void *Y, int64_t outer, int64_t inner, int dtype, vkc_stream stream) {
+    if (!ctx) return VKC_ERR_INVALID;
+    VKC_REQUIRE(ctx, outer >= 0 && inner >= 1, "softmax: bad extents");
+    VKC_REQUIRE(ctx, dtype == VKC_F32 || dtype == VKC_F16 || dtype == VKC_BF16, "softmax: bad dtype %d", dtype);
+    if (outer == 0) return VKC_OK;
+    VKC_REQUIRE(ctx, X && Y, "softmax: null tensor");
+    cudaStream_t  st     = vkc_pick_stream(ctx, stream);
+    const int64_t blocks = (outer + 7) / 8;
+    VKC_REQUIRE(ctx, blocks <= INT32_MAX, "softmax: too many rows");
+    switch (dtype) {
+        case VKC_F32: softmax_kernel<float><<<(unsigned) blocks, 256, 0, st>>>((const float *) X, (float *) Y, outer, inner); break;
+        case VKC_F16: softmax_kernel<__half><<<(unsigned) blocks, 256, 0, st>>>((const __half *) X, (__half *) Y, outer, inner); break;
+        default: softmax_kernel<__nv_bfloat16><<<(unsigned) blocks, 256, 0, st>>>((const __nv_bfloat16 *) X, (__nv_bfloat16 *) Y, outer, inner); break;
+    }
+    return vkc_post_launch(ctx, "softmax");
+}
+
+int vkc_strided_copy(vkc_ctx *ctx, const void *X, void *Y, const int64_t *shape, const int64_t *in_strides, int rank, int64_t in_offset, int dtype,
+                     vkc_stream stream) {
+    if (!ctx) return VKC_ERR_INVALID;
+    VKC_REQUIRE(ctx, rank >= 1 && rank <= kMaxRank && shape && in_strides, "strided_copy: rank %d out of range", rank);
+    CopyDesc cd;
+    cd.rank   = rank;
+    cd.offset = in_offset;
+    int64_t n = 1;
+    for (int d = 0; d < rank; ++d) {
+        cd.shape[d]   = shape[d];
+        cd.istride[d] = in_strides[d];
+        n *= shape[d];
+    }
+    if (n == 0) return VKC_OK;
+    VKC_REQUIRE(ctx, X && Y, "strided_copy: null tensor");
+    cudaStream_t st = vkc_pick_stream(ctx, stream);
+    const int    g  = grid_for(ctx, n);
+    if (vkc_dtype_size(dtype) == 4)
+        strided_copy_kernel<uint32_t><<<g, 256, 0, st>>>((const uint32_t *) X, (uint32_t *) Y, n, cd);
+    else
+        strided_copy_kernel<uint16_t><<<g, 256, 0, st>>>((const uint16_t *) X, (uint16_t *) Y, n, cd);
+    return vkc_post_launch(ctx, "strided_copy");
+}
+
+} // extern "C"

@@ -1,0 +1,67 @@
+"""Host-side sequencing of one pre-LayerNorm encoder block on the C-ABI kernels — the fused form of the node run
+the reference's passes produce for a ViT block:
+
+    LayerNorm -> MatMul(Wqkv)+fusedBias -> Reshape/Transpose/Gather (head split) -> Transpose(K) -> MatMul(Q,K^T)
+    -> Binary Mul(scale) -> Softmax -> MatMul(P,V) -> Transpose/Reshape (head merge) -> MatMul(Wo)+fusedBias
+    -> Add(residual) -> LayerNorm -> MatMul(W1)+fusedBias -> Div/Erf/Add/FusedPointwise (GELU) -> MatMul(W2)+fusedBias
+    -> Add(residual)
+
+becomes 7 launches: LN, GEMM(+bias), attention (head split/merge absorbed as strides of the packed qkv buffer),
+GEMM(+bias+residual), LN, GEMM(+bias+GELU), GEMM(+bias+residual). The C++ CudaSegment issues the same sequence
+after pattern matching; this module exists so tests and the benchmark can drive it without the C++ engine.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import capi
+
+
+class EncoderLayer:
+    def __init__(self, ctx, weights, heads, dtype=torch.float16, eps=1e-6, device="cuda"):
+        """weights: dict of fp32 numpy arrays ln1_g ln1_b wqkv bqkv wo bo ln2_g ln2_b w1 b1 w2 b2; matrices [K,N]."""
+        self.ctx, self.H, self.dtype, self.eps = ctx, heads, dtype, eps
+        mats = ("wqkv", "wo", "w1", "w2")
+        self.w = {}
+        for k, v in weights.items():
+            t = torch.from_numpy(v).to(device)
+            self.w[k] = t.to(dtype).contiguous() if k in mats else t.float().contiguous()
+        self.d = self.w["wo"].shape[0]
+        self.dmlp = self.w["w1"].shape[1]
+        self._buf = {}
+
+    def _buffers(self, B, T, device):
+        key = (B, T)
+        if key not in self._buf:
+            d, dm, dt = self.d, self.dmlp, self.dtype
+            mk = lambda *s: torch.empty(*s, dtype=dt, device=device)  # noqa: E731
+            self._buf[key] = dict(h=mk(B * T, d), qkv=mk(B, T, 3, self.H, d // self.H), att=mk(B, T, self.H, d // self.H), x1=mk(B * T, d),
+                                  f=mk(B * T, dm))
+        return self._buf[key]
+
+    def forward(self, x, out=None):
+        """x [B,T,d] in the layer's storage dtype, contiguous. Returns [B,T,d]."""
+        c, w = self.ctx, self.w
+        B, T, d = x.shape
+        H, D = self.H, d // self.H
+        buf = self._buffers(B, T, x.device)
+        x2 = x.view(B * T, d)
+        y = out if out is not None else torch.empty_like(x)
+        c.layernorm(x2, w["ln1_g"], w["ln1_b"], buf["h"], self.eps)
+        c.gemm(buf["h"], w["wqkv"], buf["qkv"].view(B * T, 3 * d), bias=w["bqkv"])
+        qkv = buf["qkv"]                                  # [B,T,3,H,D]
+        q, k, v = (qkv[:, :, i].permute(0, 2, 1, 3) for i in range(3))   # [B,H,T,D] strided views, no copy
+        o = buf["att"].permute(0, 2, 1, 3)                # attention writes straight into the merged [B,T,H*D] layout
+        c.attn_prefill(q, k, v, o, scale=1.0 / (D ** 0.5))
+        c.gemm(buf["att"].view(B * T, d), w["wo"], buf["x1"], bias=w["bo"], residual=x2)
+        c.layernorm(buf["x1"], w["ln2_g"], w["ln2_b"], buf["h"], self.eps)
+        c.gemm(buf["h"], w["w1"], buf["f"], bias=w["b1"], epilogue=capi.EPI_BIAS | capi.EPI_GELU_ERF)
+        c.gemm(buf["f"], w["w2"], y.view(B * T, d), bias=w["b2"], residual=buf["x1"])
+        return y
+
+    LAUNCHES_PER_FORWARD = 7
+
+    def flops(self, B, T):
+        d, dm, H = self.d, self.dmlp, self.H
+        M = B * T
+        return 2 * M * d * 3 * d + 4 * B * H * T * T * (d // H) + 2 * M * d * d + 4 * M * d * dm

@@ -134,7 +134,10 @@ class Context:
         if stream is not None:
             return C.c_void_p(stream)
         import torch
-        return C.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
+        h = torch.cuda.current_stream(self.device).cuda_stream
+        # torch's default stream is the legacy NULL stream; NULL means "the context's own stream" in the C-ABI,
+        # so name the legacy stream by its explicit handle (cudaStreamLegacy == 0x1) to keep torch ordering.
+        return C.c_void_p(h if h else 1)
 
     def set_impl(self, impl):
         self._check(self.lib.vkc_ctx_set_impl(self.h, impl))

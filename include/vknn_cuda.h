@@ -103,6 +103,24 @@ VKC_API int    vkc_attn_decode(vkc_ctx *ctx, const void *Q, const void *Kc, cons
                                int64_t Lmax, int64_t D, const int32_t *kv_len, float scale, void *workspace, size_t workspace_bytes,
                                int dtype, vkc_stream stream);
 
+/* ---- K3, allocation-free form. It has no counterpart in the reference. Some hosts may not allocate device memory
+ * at the moment they need a decode step: a serving loop that runs inside a memory budget fixed at start-up, a
+ * plug-in loaded into a process whose allocator owns the whole device, or a call made from a context where
+ * cudaMalloc is forbidden or would stall the device (allocation synchronises). This entry point does the same
+ * work as vkc_attn_decode but keeps the per-split partial results in a fixed area compiled into the library
+ * (vkc_attn_decode_noalloc_max_bytes() = 16 MiB, resident on every GPU that loads the library until the process
+ * ends) and performs no cudaMalloc / cudaFree or any other allocating call. The caller still passes Q, the cache
+ * and O. Shapes whose partials need more than the fixed area (B*Hq*ceil(Lmax/chunk)*(D+2)*4 bytes, see
+ * vkc_attn_decode_workspace_bytes) are refused with VKC_ERR_INVALID and a message; nothing is launched.
+ * The first call on a device resolves the area's device address (cudaGetSymbolAddress, with that device made
+ * current for the lookup); make that first call before starting any stream capture. All calls on a device share
+ * the one area and it keeps whatever the last call left there: nothing in it needs clearing between calls, but
+ * two calls that run concurrently on the same GPU (different streams or contexts) race on it. ---- */
+VKC_API size_t vkc_attn_decode_noalloc_max_bytes(void);
+VKC_API int    vkc_attn_decode_noalloc(vkc_ctx *ctx, const void *Q, const void *Kc, const void *Vc, void *O, int64_t B, int64_t Hq,
+                                       int64_t Hkv, int64_t Lmax, int64_t D, const int32_t *kv_len, float scale, int dtype,
+                                       vkc_stream stream);
+
 /* ---- K4: LayerNorm over the trailing `norm` elements. Reference: LayerNormCpu::run
  * src/backend/cpu/ops/layernorm.cpp:12-75 (oracle), shaders/flat_layernorm.comp:8-50 + LayerNormOp
  * src/backend/vulkan/ops/layernorm.cpp:19-76 (device path replaced). gamma/beta fp32 [norm]; beta may be NULL. ---- */

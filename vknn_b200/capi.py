@@ -67,6 +67,9 @@ def load_library():
     L.vkc_attn_decode_workspace_bytes.argtypes = [i64] * 5
     L.vkc_attn_decode_workspace_bytes.restype = sz
     L.vkc_attn_decode.argtypes = [vp, vp, vp, vp, vp] + [i64] * 5 + [vp, f32, vp, sz, i32, vp]
+    L.vkc_attn_decode_noalloc_max_bytes.argtypes = []
+    L.vkc_attn_decode_noalloc_max_bytes.restype = sz
+    L.vkc_attn_decode_noalloc.argtypes = [vp, vp, vp, vp, vp] + [i64] * 5 + [vp, f32, i32, vp]
     L.vkc_layernorm.argtypes = [vp, vp, vp, vp, vp, i64, i64, f32, i32, vp]
     L.vkc_pointwise.argtypes = [vp, vp, vp, vp, i32, i32, vp, vp, i32, vp, vp, i32, vp]
     L.vkc_softmax.argtypes = [vp, vp, vp, i64, i64, i32, vp]
@@ -208,6 +211,16 @@ class Context:
                                              workspace.data_ptr() if workspace is not None else None,
                                              workspace.numel() * workspace.element_size() if workspace is not None else 0, _dtype_code(Q),
                                              self._stream(stream)))
+
+    def attn_decode_noalloc(self, Q, Kc, Vc, O, scale, kv_len=None, stream=None):
+        """Same as attn_decode, but the per-split partials live in the library's fixed 16 MiB area and the call
+        allocates nothing. Raises VkcError(-1) when the shape needs more than that."""
+        B, Hq, D = Q.shape
+        _, Hkv, Lmax, _ = Kc.shape
+        assert Q.is_contiguous() and Kc.is_contiguous() and Vc.is_contiguous() and O.is_contiguous()
+        self._check(self.lib.vkc_attn_decode_noalloc(self.h, Q.data_ptr(), Kc.data_ptr(), Vc.data_ptr(), O.data_ptr(), B, Hq, Hkv, Lmax, D,
+                                                     kv_len.data_ptr() if kv_len is not None else None, float(scale), _dtype_code(Q),
+                                                     self._stream(stream)))
 
     def layernorm(self, X, gamma, beta, Y, eps, stream=None):
         norm = gamma.numel()

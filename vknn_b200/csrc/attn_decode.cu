@@ -268,6 +268,15 @@ namespace {
 
 } // namespace
 
+// ---- fixed scratch for vkc_attn_decode_noalloc ------------------------------------------------------------------
+// The array lives in every GPU's memory from the moment the library is loaded there until the process exits.
+// On the host its name is only a handle: the device address has to be asked for, once per device, with that
+// device current.
+constexpr size_t kStaticScratchBytes = (size_t) 16 << 20;
+static __device__ __align__(256) unsigned char g_decode_static_scratch[kStaticScratchBytes];
+constexpr int kMaxDevices = 64;
+static void *g_decode_static_ptr[kMaxDevices] = {nullptr};
+
 extern "C" size_t vkc_attn_decode_workspace_bytes(int64_t B, int64_t Hq, int64_t Hkv, int64_t Lmax, int64_t D) {
     if (B <= 0 || Hq <= 0 || Hkv <= 0 || Lmax <= 0 || D <= 0) return 0;
     const int    chunk      = decode_chunk(B, Hkv, Lmax);
@@ -304,4 +313,33 @@ extern "C" int vkc_attn_decode(vkc_ctx *ctx, const void *Q, const void *Kc, cons
     if (dtype == VKC_F16) return VKC_DEC_T(__half);
     return VKC_DEC_T(__nv_bfloat16);
 #undef VKC_DEC_T
+}
+
+extern "C" size_t vkc_attn_decode_noalloc_max_bytes(void) { return kStaticScratchBytes; }
+
+extern "C" int vkc_attn_decode_noalloc(vkc_ctx *ctx, const void *Q, const void *Kc, const void *Vc, void *O, int64_t B, int64_t Hq, int64_t Hkv,
+                                       int64_t Lmax, int64_t D, const int32_t *kv_len, float scale, int dtype, vkc_stream stream) {
+    if (!ctx) return VKC_ERR_INVALID;
+    VKC_REQUIRE(ctx, ctx->device >= 0 && ctx->device < kMaxDevices, "attn_decode_noalloc: device ordinal %d out of range", ctx->device);
+    const size_t need = vkc_attn_decode_workspace_bytes(B, Hq, Hkv, Lmax, D);
+    if (need > kStaticScratchBytes)
+        return vkc_fail(ctx, VKC_ERR_INVALID,
+                        "attn_decode_noalloc: this shape needs %zu bytes of partial-result scratch, more than the fixed %zu-byte area; "
+                        "use vkc_attn_decode with a caller workspace instead",
+                        need, kStaticScratchBytes);
+    if (!g_decode_static_ptr[ctx->device]) {
+        // one-time set-up for this device: resolve the device address of the file-scope array
+        int cur = -1;
+        VKC_CUDA(ctx, cudaGetDevice(&cur));
+        if (cur != ctx->device) VKC_CUDA(ctx, cudaSetDevice(ctx->device));
+        void       *ptr = nullptr;
+        cudaError_t e   = cudaGetSymbolAddress(&ptr, g_decode_static_scratch);
+        if (cur != ctx->device) cudaSetDevice(cur);
+        if (e != cudaSuccess || !ptr) return vkc_fail(ctx, VKC_ERR_CUDA, "cudaGetSymbolAddress(decode scratch): %s", cudaGetErrorString(e));
+        g_decode_static_ptr[ctx->device] = ptr;
+    }
+    // Nothing in the area has to start at zero: the split kernel writes every (row, split) partial that the merge
+    // kernel reads for this call, and stale contents beyond them are never read.
+    return vkc_attn_decode(ctx, Q, Kc, Vc, O, B, Hq, Hkv, Lmax, D, kv_len, scale, g_decode_static_ptr[ctx->device], kStaticScratchBytes, dtype,
+                           stream);
 }

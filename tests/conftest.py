@@ -20,8 +20,6 @@ def ctx():
     assert torch.cuda.is_available(), "gpu tests need a CUDA device"
     torch.cuda.set_device(0)
     c = vknn_b200.Context(0)
-    if os.environ.get("VKNN_ATTN_P_SMEM") == "1":  # A/B switch: hand P to the P.V MMA through shared memory
-        c.lib.vkc_debug_set_attn_p_in_tmem(0)
     yield c
     c.sync()
     c.close()

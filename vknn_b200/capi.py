@@ -80,9 +80,6 @@ def load_library():
     L.vkc_graph_destroy.argtypes = [vp, vp]
     L.vkc_timer_start.argtypes = [vp, vp]
     L.vkc_timer_stop.argtypes = [vp, vp, C.POINTER(C.c_float)]
-    if hasattr(L, "vkc_debug_set_attn_p_in_tmem"):
-        L.vkc_debug_set_attn_p_in_tmem.argtypes = [i32]
-        L.vkc_debug_set_attn_p_in_tmem.restype = None
     _lib = L
     return L
 

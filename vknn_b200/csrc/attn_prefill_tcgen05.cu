@@ -1,32 +1,35 @@
 // K2 — fused prefill attention on the 5th-generation tensor cores (flash style: the score matrix never leaves
-// the SM). One CTA owns one 128-row query tile of one (batch, head) and walks the key/value sequence in tiles
-// of 128 keys.
+// the SM). One CTA owns TWO 128-row query tiles (A and B) of one (batch, head) and walks the key/value
+// sequence in tiles of 128 keys; while the softmax warps of one query tile work, the tensor core runs the
+// MMAs of the other.
 //
-//   warp 0    TMA producer: Q once, then K and V tiles through two independent 2-stage shared-memory rings
-//             (128-byte swizzle, plain per-CTA tiled loads; out-of-range rows arrive as zeros).
-//   warp 1    MMA issuer (one elected lane) and owner of the tensor-memory allocation (512 columns):
-//               S[j%2]  (128 fp32 cols each)  = Q . K_j^T      tcgen05.mma, both operands from shared memory
-//               O       (D fp32 cols)        += P_j . V_j      P from tensor memory (or shared memory), V MN-major
-//             S is double buffered so Q.K_{j+1}^T runs while the softmax warps work on S_j.
-//   warps 2-5 softmax: thread r owns row r. Pass 1 reads S_j from TMEM for the row maximum, pass 2 re-reads it,
-//             computes P = exp2(S*scale*log2e - m) in fp32, packs to the storage type and writes P to TMEM
-//             (tcgen05.st) for the P.V MMA. The running maximum is only raised when it grows by more than 8
-//             (a factor 256), so the O accumulator in TMEM is rescaled rarely; sums stay in fp32.
-//             After the last tile the same warps read O, divide by the row sum and store the tile.
+//   warp 0     TMA producer: both Q tiles once, then K and V tiles through two independent 2-stage
+//              shared-memory rings (128-byte swizzle, plain per-CTA tiled loads; rows past the end read as zeros).
+//   warp 1     MMA issuer (one elected lane) and owner of the tensor-memory allocation (512 columns):
+//                S_t (128 fp32 columns)  = Q_t . K_j^T     both operands from shared memory (K-major)
+//                O_t (D fp32 columns)   += P_t . V_j       P_t from tensor memory, V_j MN-major from its row-major tile
+//              issue order per key tile j:  P.V_A(j), Q.K_A(j+1), P.V_B(j), Q.K_B(j+1).
+//   warps 2-5  softmax of tile A, warps 6-9 softmax of tile B; thread r owns row r of its tile. The row of S is
+//              read from TMEM once into registers; P = exp2(S*scale*log2e - m) in fp32 is packed to the storage
+//              type and written over the first 64 columns of S_t (tcgen05.st), which the P.V MMA reads as its A
+//              operand. The running maximum is raised only when it grows by more than 8 (factor 256), so O_t in
+//              TMEM is rescaled rarely; row sums stay in fp32. After the last key tile the same warps read O_t,
+//              divide by the row sum and store.
+// Ordering notes: tcgen05.commit covers every MMA issued before it, so "S_t(j) ready" also means P.V_t(j-1) has
+// finished and O_t may be rescaled; Q.K_t(j+1) overwrites the columns P_t(j) lives in and is issued after
+// P.V_t(j) by the same thread, which the tensor pipe executes in order.
 // Masking: keys >= kv_len[b] (or >= Skv) and, for causal, keys > row + (Skv - Sq) get probability 0; key tiles
-// entirely above the diagonal are skipped.
+// entirely above a query tile's diagonal are skipped for that tile.
 #include "common.cuh"
 #include "ptx.cuh"
 #include "tensormap.cuh"
 
 namespace {
 
-    constexpr int BM = 128, BN = 128;
-    constexpr int kThreads   = 192;
+    constexpr int BM = 128, BN = 128; // rows per query tile, keys per key tile
+    constexpr int kQTiles    = 2;
+    constexpr int kThreads   = 64 + kQTiles * 128;
     constexpr int kTmemCols  = 512;
-    constexpr int kColS      = 0;   // S0 at 0, S1 at 128
-    constexpr int kColO      = 256; // D columns
-    constexpr int kColP      = 384; // P0 at 384, P1 at 448 (64 columns each: 128 packed 16-bit values per row)
     constexpr float kRescaleThreshold = 8.0f;
 
     struct AttnParams {
@@ -39,17 +42,15 @@ namespace {
         int           *dev_err;
     };
 
-    template <int D, int KS, int VS, bool P_TMEM> struct Smem {
-        static constexpr uint32_t Q_BYTES  = BM * D * 2;
+    template <int D, int KS, int VS> struct Smem {
+        static constexpr uint32_t Q_BYTES  = BM * D * 2; // per query tile
         static constexpr uint32_t KV_BYTES = BN * D * 2;
-        static constexpr uint32_t P_BYTES  = P_TMEM ? 0 : BM * BN * 2;
         static constexpr uint32_t oQ   = 0;
-        static constexpr uint32_t oK   = oQ + Q_BYTES;
+        static constexpr uint32_t oK   = oQ + kQTiles * Q_BYTES;
         static constexpr uint32_t oV   = oK + KS * KV_BYTES;
-        static constexpr uint32_t oP   = oV + VS * KV_BYTES;
-        static constexpr uint32_t oBar = oP + P_BYTES;
-        // barriers: q_full, k_full[KS], k_empty[KS], v_full[VS], v_empty[VS], s_full[2], s_empty[2], p_full[2], pv_done[2]
-        static constexpr int nBar = 1 + 2 * KS + 2 * VS + 8;
+        static constexpr uint32_t oBar = oV + VS * KV_BYTES;
+        // barriers: q_full, k_full[KS], k_empty[KS], v_full[VS], v_empty[VS], s_full[2], p_full[2], o_final[2]
+        static constexpr int nBar = 1 + 2 * KS + 2 * VS + 6;
         static constexpr uint32_t oCtl  = oBar + 8 * nBar;
         static constexpr uint32_t total = oCtl + 16 + 1024;
     };
@@ -69,51 +70,59 @@ namespace {
         return *reinterpret_cast<uint32_t *>(&h);
     }
 
-    template <typename T, int D, bool P_TMEM>
+    template <typename T, int D>
     __global__ void __launch_bounds__(kThreads, 1)
         attn_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                             AttnParams p) {
         constexpr int KS = 2, VS = 2;
-        using L               = Smem<D, KS, VS, P_TMEM>;
+        using L               = Smem<D, KS, VS>;
         constexpr bool kBf16  = std::is_same<T, __nv_bfloat16>::value;
         constexpr uint32_t kIdescQK = ptx::idesc_f16(BM, BN, kBf16, false, false);
         constexpr uint32_t kIdescPV = ptx::idesc_f16(BM, D, kBf16, false, true);
         constexpr int      DCH      = D / 64; // 64-element (128-byte) spans per row
+        constexpr int      kColS    = 0;      // S_A at 0, S_B at 128; P_t aliases the first 64 columns of S_t
+        constexpr int      kColO    = 256;    // O_A at 256, O_B at 256 + D
 
         extern __shared__ uint8_t smem_raw[];
         const uint32_t raw   = ptx::smem_u32(smem_raw);
         const uint32_t base  = (raw + 1023u) & ~1023u;
         uint8_t       *gbase = smem_raw + (base - raw);
-        const uint32_t sQ = base + L::oQ, sK = base + L::oK, sV = base + L::oV, sP = base + L::oP, sBar = base + L::oBar;
+        const uint32_t sQ = base + L::oQ, sK = base + L::oK, sV = base + L::oV, sBar = base + L::oBar;
         volatile int  *ctl = (volatile int *) (gbase + L::oCtl); // ctl[0] = tmem base, ctl[1] = abort flag
         auto           bar = [&](int i) { return sBar + 8u * (uint32_t) i; };
-        constexpr int  bQ = 0, bKF = 1, bKE = 1 + KS, bVF = 1 + 2 * KS, bVE = 1 + 2 * KS + VS, bSF = 1 + 2 * KS + 2 * VS, bSE = bSF + 2,
-                      bPF = bSF + 4, bPV = bSF + 6;
+        constexpr int  bQ = 0, bKF = 1, bKE = 1 + KS, bVF = 1 + 2 * KS, bVE = 1 + 2 * KS + VS, bSF = 1 + 2 * KS + 2 * VS, bPF = bSF + 2,
+                      bOF = bSF + 4;
 
         const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
         const int b = blockIdx.z, h = blockIdx.y;
         const int hk = h / (int) (p.Hq / p.Hkv);
         // heavy (late) query tiles first when causal
         const int     mt = p.causal ? (int) gridDim.x - 1 - (int) blockIdx.x : (int) blockIdx.x;
-        const int64_t m0 = (int64_t) mt * BM;
+        const int64_t m0 = (int64_t) mt * (kQTiles * BM);
 
         int64_t len = p.kv_len ? (int64_t) p.kv_len[b] : p.Skv;
         if (len > p.Skv) len = p.Skv;
         if (len < 0) len = 0;
-        int64_t kend = len;
-        if (p.causal) {
-            int64_t last = m0 + BM - 1;
-            if (last > p.Sq - 1) last = p.Sq - 1;
-            const int64_t lim = last + (p.Skv - p.Sq) + 1;
-            if (lim < kend) kend = lim;
+        // key tiles each query tile needs
+        int n_t[kQTiles];
+#pragma unroll
+        for (int t = 0; t < kQTiles; ++t) {
+            int64_t kend = len;
+            const int64_t first = m0 + (int64_t) t * BM;
+            if (first >= p.Sq) kend = 0; // tile entirely past the end of the query sequence
+            if (p.causal && kend > 0) {
+                int64_t last = first + BM - 1;
+                if (last > p.Sq - 1) last = p.Sq - 1;
+                const int64_t lim = last + (p.Skv - p.Sq) + 1;
+                if (lim < kend) kend = lim;
+                if (kend < 0) kend = 0;
+            }
+            n_t[t] = (int) ((kend + BN - 1) / BN);
         }
-        const int n_tiles = kend > 0 ? (int) ((kend + BN - 1) / BN) : 0;
+        const int n_max = n_t[0] > n_t[1] ? n_t[0] : n_t[1];
 
         if (threadIdx.x == 0) {
-            for (int i = 0; i < L::nBar; ++i) {
-                const bool many = (i >= bSE && i < bSE + 2) || (i >= bPF && i < bPF + 2); // arrived on by all 128 softmax threads
-                ptx::mbar_init(bar(i), many ? 128 : 1);
-            }
+            for (int i = 0; i < L::nBar; ++i) ptx::mbar_init(bar(i), (i >= bPF && i < bPF + 2) ? 128 : 1);
             ctl[1] = 0;
             ptx::fence_mbar_init();
             ptx::prefetch_tmap(&tmQ);
@@ -131,11 +140,14 @@ namespace {
 
         if (warp == 0) {
             // ------------------------------------------------------------------ TMA producer
-            if (n_tiles > 0 && ptx::elect_one()) {
-                ptx::mbar_expect_tx(bar(bQ), L::Q_BYTES);
+            if (n_max > 0 && ptx::elect_one()) {
+                ptx::mbar_expect_tx(bar(bQ), kQTiles * L::Q_BYTES);
 #pragma unroll
-                for (int c = 0; c < DCH; ++c) ptx::tma_load_4d(sQ + c * (BM * 128), &tmQ, c * 64, (int) m0, h, b, bar(bQ));
-                for (int j = 0; j < n_tiles; ++j) {
+                for (int t = 0; t < kQTiles; ++t)
+#pragma unroll
+                    for (int c = 0; c < DCH; ++c)
+                        ptx::tma_load_4d(sQ + t * L::Q_BYTES + c * (BM * 128), &tmQ, c * 64, (int) (m0 + t * BM), h, b, bar(bQ));
+                for (int j = 0; j < n_max; ++j) {
                     const int ks = j % KS, vs = j % VS;
                     if (!ptx::mbar_wait(bar(bKE + ks), ((j / KS) & 1) ^ 1, ctl + 1, p.dev_err)) break;
                     ptx::mbar_expect_tx(bar(bKF + ks), L::KV_BYTES);
@@ -149,158 +161,148 @@ namespace {
             }
         } else if (warp == 1) {
             // ------------------------------------------------------------------ MMA issuer
-            if (n_tiles > 0 && ptx::elect_one()) {
-                auto issue_qk = [&](int j) -> bool {
-                    const int ks = j % KS, sb = j & 1;
-                    if (!ptx::mbar_wait(bar(bKF + ks), (j / KS) & 1, ctl + 1, p.dev_err)) return false;
-                    if (!ptx::mbar_wait(bar(bSE + sb), ((j / 2) & 1) ^ 1, ctl + 1, p.dev_err)) return false;
-                    ptx::tc_fence_after();
+            if (n_max > 0 && ptx::elect_one()) {
+                auto issue_qk = [&](int t, int j) {
+                    const int ks = j % KS;
 #pragma unroll
                     for (int k = 0; k < D / 16; ++k) {
                         const uint32_t off = (uint32_t) (k / 4) * (BM * 128) + (uint32_t) (k % 4) * 32;
-                        const uint64_t ad  = ptx::smem_desc_sw128(sQ + off, 16, 1024);
+                        const uint64_t ad  = ptx::smem_desc_sw128(sQ + t * L::Q_BYTES + off, 16, 1024);
                         const uint64_t bd  = ptx::smem_desc_sw128(sK + ks * L::KV_BYTES + off, 16, 1024);
-                        ptx::mma_f16_ss(tmem + kColS + sb * BN, ad, bd, kIdescQK, k != 0 ? 1u : 0u);
+                        ptx::mma_f16_ss(tmem + kColS + t * BN, ad, bd, kIdescQK, k != 0 ? 1u : 0u);
                     }
-                    ptx::tc_commit(bar(bKE + ks));
-                    ptx::tc_commit(bar(bSF + sb));
-                    return true;
+                    ptx::tc_commit(bar(bSF + t));
                 };
-                bool ok = ptx::mbar_wait(bar(bQ), 0, ctl + 1, p.dev_err);
-                ok      = ok && issue_qk(0);
-                for (int j = 0; j < n_tiles && ok; ++j) {
-                    if (j + 1 < n_tiles) ok = issue_qk(j + 1);
-                    if (!ok) break;
-                    const int vs = j % VS, pb = j & 1;
-                    if (!ptx::mbar_wait(bar(bVF + vs), (j / VS) & 1, ctl + 1, p.dev_err)) break;
-                    if (!ptx::mbar_wait(bar(bPF + pb), (j / 2) & 1, ctl + 1, p.dev_err)) break;
-                    ptx::tc_fence_after();
+                auto issue_pv = [&](int t, int j) {
+                    const int vs = j % VS;
 #pragma unroll
                     for (int k = 0; k < BN / 16; ++k) {
                         // V tile: D/64 spans of [128 keys x 128 B]; 16 keys per MMA step = 2048 B
                         const uint64_t bd = ptx::smem_desc_sw128(sV + vs * L::KV_BYTES + k * 2048, BN * 128, 1024);
-                        if (P_TMEM) {
-                            ptx::mma_f16_ts(tmem + kColO, tmem + kColP + pb * 64 + k * 8, bd, kIdescPV, (j | k) != 0 ? 1u : 0u);
-                        } else {
-                            const uint32_t off = (uint32_t) (k / 4) * (BM * 128) + (uint32_t) (k % 4) * 32;
-                            const uint64_t ad  = ptx::smem_desc_sw128(sP + off, 16, 1024);
-                            ptx::mma_f16_ss(tmem + kColO, ad, bd, kIdescPV, (j | k) != 0 ? 1u : 0u);
+                        ptx::mma_f16_ts(tmem + kColO + t * D, tmem + kColS + t * BN + k * 8, bd, kIdescPV, (j | k) != 0 ? 1u : 0u);
+                    }
+                };
+                bool ok = ptx::mbar_wait(bar(bQ), 0, ctl + 1, p.dev_err);
+                ok      = ok && ptx::mbar_wait(bar(bKF + 0), 0, ctl + 1, p.dev_err);
+                if (ok) {
+                    ptx::tc_fence_after();
+#pragma unroll
+                    for (int t = 0; t < kQTiles; ++t)
+                        if (n_t[t] > 0) issue_qk(t, 0);
+                    ptx::tc_commit(bar(bKE + 0));
+                }
+                for (int j = 0; j < n_max && ok; ++j) {
+                    const int vs = j % VS;
+                    ok = ptx::mbar_wait(bar(bVF + vs), (j / VS) & 1, ctl + 1, p.dev_err);
+                    const bool more = j + 1 < n_max;
+#pragma unroll
+                    for (int t = 0; t < kQTiles && ok; ++t) {
+                        if (j < n_t[t]) {
+                            ok = ptx::mbar_wait(bar(bPF + t), j & 1, ctl + 1, p.dev_err);
+                            if (!ok) break;
+                            ptx::tc_fence_after();
+                            issue_pv(t, j);
+                            if (j + 1 < n_t[t]) {
+                                ok = ptx::mbar_wait(bar(bKF + (j + 1) % KS), ((j + 1) / KS) & 1, ctl + 1, p.dev_err);
+                                if (!ok) break;
+                                ptx::tc_fence_after();
+                                issue_qk(t, j + 1);
+                            } else {
+                                ptx::tc_commit(bar(bOF + t)); // O_t complete
+                            }
                         }
                     }
+                    if (!ok) break;
                     ptx::tc_commit(bar(bVE + vs));
-                    ptx::tc_commit(bar(bPV + pb));
+                    if (more) ptx::tc_commit(bar(bKE + (j + 1) % KS));
                 }
             }
         } else {
             // ------------------------------------------------------------------ softmax + epilogue (thread = row)
-            const int      q      = warp & 3;
+            const int      t      = (warp - 2) >> 2;       // query tile of this warpgroup
+            const int      q      = warp & 3;              // TMEM lane quarter this warp may address
             const int      r      = q * 32 + lane;
-            const int64_t  row    = m0 + r;
-            const uint32_t tlane  = (uint32_t) (q * 32) << 16;
+            const int64_t  row    = m0 + (int64_t) t * BM + r;
+            const uint32_t tS     = tmem + ((uint32_t) (q * 32) << 16) + kColS + t * BN;
+            const uint32_t tO     = tmem + ((uint32_t) (q * 32) << 16) + kColO + t * D;
             const int64_t  my_lim = p.causal ? row + (p.Skv - p.Sq) : p.Skv; // keys <= my_lim visible
+            const int      n      = n_t[t];
             float          m_used = -INFINITY, l = 0.f;
             bool           ok     = true;
-            for (int j = 0; j < n_tiles; ++j) {
-                const int     sb = j & 1;
+            for (int j = 0; j < n; ++j) {
                 const int64_t kv0 = (int64_t) j * BN;
-                ok = ptx::mbar_wait(bar(bSF + sb), (j / 2) & 1, ctl + 1, p.dev_err);
+                ok = ptx::mbar_wait(bar(bSF + t), j & 1, ctl + 1, p.dev_err);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 ptx::tc_fence_after();
-                const bool need_mask = (kv0 + BN > len) || (p.causal && kv0 + BN - 1 > m0 + (p.Skv - p.Sq));
-                // pass 1: row maximum (raw scores)
-                float mx = -INFINITY;
-#pragma unroll 1
-                for (int c = 0; c < BN / 32; ++c) {
-                    uint32_t v[32];
-                    ptx::tmem_ld_x32(tmem + tlane + kColS + sb * BN + c * 32, v);
-                    ptx::tc_wait_ld();
-                    if (need_mask) {
+                uint32_t s[4][32];
+#pragma unroll
+                for (int c = 0; c < 4; ++c) ptx::tmem_ld_x32(tS + c * 32, s[c]);
+                ptx::tc_wait_ld();
+                const bool need_mask = (kv0 + BN > len) || (p.causal && kv0 + BN - 1 > m0 + (int64_t) t * BM + (p.Skv - p.Sq));
+                if (need_mask) {
+#pragma unroll
+                    for (int c = 0; c < 4; ++c)
 #pragma unroll
                         for (int i = 0; i < 32; ++i) {
                             const int64_t key = kv0 + c * 32 + i;
-                            if (key < len && key <= my_lim) mx = fmaxf(mx, __uint_as_float(v[i]));
+                            if (!(key < len && key <= my_lim)) s[c][i] = 0xff800000u; // -inf
                         }
-                    } else {
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(v[i]));
-                    }
                 }
-                const float mx2 = mx * p.scale_log2; // scale > 0
+                float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    mx0 = fmaxf(mx0, __uint_as_float(s[0][i]));
+                    mx1 = fmaxf(mx1, __uint_as_float(s[1][i]));
+                    mx2 = fmaxf(mx2, __uint_as_float(s[2][i]));
+                    mx3 = fmaxf(mx3, __uint_as_float(s[3][i]));
+                }
+                const float mxs = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale_log2; // scale > 0
                 float       alpha = 1.f;
                 bool        rescale = false;
-                if (mx2 > m_used + kRescaleThreshold || m_used == -INFINITY) {
-                    if (mx2 > m_used) {
-                        alpha   = m_used == -INFINITY ? 0.f : fast_exp2(m_used - mx2);
-                        rescale = j > 0 && m_used != -INFINITY;
-                        m_used  = mx2;
-                    }
+                if (mxs > m_used + kRescaleThreshold || (m_used == -INFINITY && mxs > m_used)) {
+                    alpha   = m_used == -INFINITY ? 0.f : fast_exp2(m_used - mxs);
+                    rescale = j > 0 && m_used != -INFINITY;
+                    m_used  = mxs;
                 }
-                const float m_safe = m_used == -INFINITY ? 0.f : m_used;
                 l *= alpha;
-                // O rescale first (it needs P.V of the previous tile finished), then P
                 if (__any_sync(0xffffffffu, rescale)) {
-                    ok = ptx::mbar_wait(bar(bPV + ((j - 1) & 1)), ((j - 1) / 2) & 1, ctl + 1, p.dev_err);
-                    ok = __all_sync(0xffffffffu, ok);
-                    if (!ok) break;
-                    ptx::tc_fence_after();
+                    // P.V_t(j-1) finished before S_t(j) was signalled, so O_t is quiescent here
 #pragma unroll 1
                     for (int c = 0; c < D / 32; ++c) {
                         uint32_t v[32];
-                        ptx::tmem_ld_x32(tmem + tlane + kColO + c * 32, v);
+                        ptx::tmem_ld_x32(tO + c * 32, v);
                         ptx::tc_wait_ld();
 #pragma unroll
                         for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
-                        ptx::tmem_st_x32(tmem + tlane + kColO + c * 32, v);
+                        ptx::tmem_st_x32(tO + c * 32, v);
                     }
                 }
-                // pass 2: probabilities
-                if (!P_TMEM && j > 0) {
-                    // the single shared-memory P buffer is free once P.V of the previous tile has read it
-                    ok = ptx::mbar_wait(bar(bPV + ((j - 1) & 1)), ((j - 1) / 2) & 1, ctl + 1, p.dev_err);
-                    ok = __all_sync(0xffffffffu, ok);
-                    if (!ok) break;
-                }
-#pragma unroll 1
-                for (int c = 0; c < BN / 32; ++c) {
-                    uint32_t v[32];
-                    ptx::tmem_ld_x32(tmem + tlane + kColS + sb * BN + c * 32, v);
-                    ptx::tc_wait_ld();
-                    uint32_t pk[16];
+                const float neg_m = m_used == -INFINITY ? 0.f : -m_used;
+                float       l0 = 0.f, l1 = 0.f;
 #pragma unroll
-                    for (int i = 0; i < 32; i += 2) {
-                        float p0 = fast_exp2(fmaf(__uint_as_float(v[i]), p.scale_log2, -m_safe));
-                        float p1 = fast_exp2(fmaf(__uint_as_float(v[i + 1]), p.scale_log2, -m_safe));
-                        if (need_mask) {
-                            const int64_t key = kv0 + c * 32 + i;
-                            if (!(key < len && key <= my_lim)) p0 = 0.f;
-                            if (!(key + 1 < len && key + 1 <= my_lim)) p1 = 0.f;
-                        }
-                        l += p0 + p1;
-                        pk[i / 2] = pack2<T>(p0, p1);
-                    }
-                    if (P_TMEM) {
-                        ptx::tmem_st_x16(tmem + tlane + kColP + sb * 64 + c * 16, pk);
-                    } else {
-                        // K-major 128-byte-swizzled rows: two spans of 64 keys, 16-byte units XORed with (row % 8)
-                        const uint32_t rowoff = (uint32_t) (c / 2) * (BM * 128) + (uint32_t) (r / 8) * 1024 + (uint32_t) (r % 8) * 128;
+                for (int c = 0; c < 4; c += 2) {
+                    uint32_t pk[32];
 #pragma unroll
-                        for (int u = 0; u < 4; ++u) {
-                            const uint32_t unit = (uint32_t) ((c & 1) * 4 + u) ^ (uint32_t) (r & 7);
-                            uint4          val  = make_uint4(pk[4 * u], pk[4 * u + 1], pk[4 * u + 2], pk[4 * u + 3]);
-                            *reinterpret_cast<uint4 *>(gbase + L::oP + rowoff + unit * 16) = val;
+                    for (int cc = 0; cc < 2; ++cc)
+#pragma unroll
+                        for (int i = 0; i < 32; i += 2) {
+                            const float p0 = fast_exp2(fmaf(__uint_as_float(s[c + cc][i]), p.scale_log2, neg_m));
+                            const float p1 = fast_exp2(fmaf(__uint_as_float(s[c + cc][i + 1]), p.scale_log2, neg_m));
+                            l0 += p0;
+                            l1 += p1;
+                            pk[cc * 16 + i / 2] = pack2<T>(p0, p1);
                         }
-                    }
+                    ptx::tmem_st_x32(tS + (c / 2) * 32, pk);
                 }
+                l += l0 + l1;
                 ptx::tc_wait_st();
-                if (!P_TMEM) ptx::fence_proxy_async();
                 ptx::tc_fence_before();
-                ptx::mbar_arrive(bar(bSE + sb));
-                ptx::mbar_arrive(bar(bPF + sb));
+                ptx::mbar_arrive(bar(bPF + t));
             }
             // epilogue
-            if (n_tiles > 0 && ok) {
-                ok = ptx::mbar_wait(bar(bPV + ((n_tiles - 1) & 1)), ((n_tiles - 1) / 2) & 1, ctl + 1, p.dev_err);
+            if (n > 0 && ok) {
+                ok = ptx::mbar_wait(bar(bOF + t), 0, ctl + 1, p.dev_err);
                 ok = __all_sync(0xffffffffu, ok);
             }
             if (ok) {
@@ -311,8 +313,8 @@ namespace {
 #pragma unroll 1
                 for (int c = 0; c < D / 32; ++c) {
                     uint32_t v[32];
-                    if (n_tiles > 0) {
-                        ptx::tmem_ld_x32(tmem + tlane + kColO + c * 32, v);
+                    if (n > 0) {
+                        ptx::tmem_ld_x32(tO + c * 32, v);
                         ptx::tc_wait_ld();
                     } else {
 #pragma unroll
@@ -345,16 +347,16 @@ namespace {
         if (warp == 1) ptx::tmem_dealloc(tmem, kTmemCols);
     }
 
-    template <typename T, int D, bool P_TMEM>
+    template <typename T, int D>
     int launch_attn(vkc_ctx *ctx, const CUtensorMap &tq, const CUtensorMap &tk, const CUtensorMap &tv, const AttnParams &p, int64_t B, cudaStream_t st) {
-        auto          kern = attn_prefill_kernel<T, D, P_TMEM>;
-        constexpr int smem = (int) Smem<D, 2, 2, P_TMEM>::total;
+        auto          kern = attn_prefill_kernel<T, D>;
+        constexpr int smem = (int) Smem<D, 2, 2>::total;
         static bool   attr_set = false;
         if (!attr_set) {
             VKC_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
             attr_set = true;
         }
-        dim3 grid((unsigned) ((p.Sq + BM - 1) / BM), (unsigned) p.Hq, (unsigned) B);
+        dim3 grid((unsigned) ((p.Sq + kQTiles * BM - 1) / (kQTiles * BM)), (unsigned) p.Hq, (unsigned) B);
         kern<<<grid, kThreads, smem, st>>>(tq, tk, tv, p);
         return vkc_post_launch(ctx, "attn_prefill_tcgen05");
     }
@@ -372,10 +374,6 @@ namespace {
 
 } // namespace
 
-// Whether P is handed to the P.V MMA through tensor memory (default) or through shared memory.
-static int g_p_in_tmem = 1;
-extern "C" VKC_API void vkc_debug_set_attn_p_in_tmem(int on) { g_p_in_tmem = on ? 1 : 0; }
-
 int vkc_attn_prefill_tcgen05(vkc_ctx *ctx, const void *Q, const void *K, const void *V, void *O, int64_t B, int64_t Hq, int64_t Hkv, int64_t Sq,
                              int64_t Skv, int64_t D, const int64_t *qs, const int64_t *ks, const int64_t *vs, const int64_t *os, float scale,
                              int causal, const int32_t *kv_len, int dtype, cudaStream_t st) {
@@ -387,7 +385,7 @@ int vkc_attn_prefill_tcgen05(vkc_ctx *ctx, const void *Q, const void *K, const v
             return vkc_fail(ctx, VKC_ERR_UNSUPPORTED, "attn_prefill_tcgen05: Q/K/V strides must be multiples of 16 bytes");
     }
     if (((uintptr_t) Q | (uintptr_t) K | (uintptr_t) V) & 15) return vkc_fail(ctx, VKC_ERR_UNSUPPORTED, "attn_prefill_tcgen05: Q/K/V must be 16-byte aligned");
-    if (Sq > INT32_MAX - BM || Skv > INT32_MAX - BN) return vkc_fail(ctx, VKC_ERR_UNSUPPORTED, "attn_prefill_tcgen05: sequence too long");
+    if (Sq > INT32_MAX - 2 * BM || Skv > INT32_MAX - BN) return vkc_fail(ctx, VKC_ERR_UNSUPPORTED, "attn_prefill_tcgen05: sequence too long");
 
     CUtensorMap tq, tk, tv;
     int         rc;
@@ -402,8 +400,6 @@ int vkc_attn_prefill_tcgen05(vkc_ctx *ctx, const void *Q, const void *K, const v
     p.causal     = causal;
     p.kv_len     = kv_len;
     p.dev_err    = ctx->dev_err;
-#define VKC_ATTN(T_, D_) (g_p_in_tmem ? launch_attn<T_, D_, true>(ctx, tq, tk, tv, p, B, st) : launch_attn<T_, D_, false>(ctx, tq, tk, tv, p, B, st))
-    if (dtype == VKC_F16) return D == 64 ? VKC_ATTN(__half, 64) : VKC_ATTN(__half, 128);
-    return D == 64 ? VKC_ATTN(__nv_bfloat16, 64) : VKC_ATTN(__nv_bfloat16, 128);
-#undef VKC_ATTN
+    if (dtype == VKC_F16) return D == 64 ? launch_attn<__half, 64>(ctx, tq, tk, tv, p, B, st) : launch_attn<__half, 128>(ctx, tq, tk, tv, p, B, st);
+    return D == 64 ? launch_attn<__nv_bfloat16, 64>(ctx, tq, tk, tv, p, B, st) : launch_attn<__nv_bfloat16, 128>(ctx, tq, tk, tv, p, B, st);
 }

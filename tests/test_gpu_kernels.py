@@ -229,27 +229,63 @@ def test_attention_deterministic(ctx):
 
 
 # ------------------------------------------------------------------------------------------------ decode attention
+@pytest.mark.parametrize("impl", [vknn_b200.IMPL_SIMT, vknn_b200.IMPL_TCGEN05], ids=["simt", "tc"])
 @pytest.mark.parametrize("dt", ["f16", "bf16"])
-@pytest.mark.parametrize("B,Hq,Hkv,L,D", [(4, 32, 8, 1024, 128), (2, 8, 8, 300, 64), (3, 4, 2, 777, 128), (1, 8, 1, 130, 128)])
-def test_decode(ctx, dt, B, Hq, Hkv, L, D):
+@pytest.mark.parametrize("B,Hq,Hkv,L,D", [(4, 32, 8, 1024, 128), (2, 8, 8, 300, 64), (3, 4, 2, 777, 128), (1, 8, 1, 130, 128), (5, 16, 1, 2100, 128),
+                                          (2, 6, 2, 129, 128)])
+def test_decode(ctx, impl, dt, B, Hq, Hkv, L, D):
+    """Ragged valid lengths (1 .. L), GQA group sizes 1..16, caches that are not tile multiples. Everything past
+    kv_len in the cache is NaN: a correct kernel never lets it reach the output."""
+    G = Hq // Hkv
+    if impl == vknn_b200.IMPL_TCGEN05 and D != 128:
+        pytest.skip("the tensor-core decode kernel covers head dim 128")
+    if impl == vknn_b200.IMPL_SIMT and G not in (1, 2, 4, 8):
+        pytest.skip("the SIMT decode kernel covers group sizes 1, 2, 4, 8")
     rng = np.random.default_rng(B + Hq + L)
     q = round_to(rng.standard_normal((B, Hq, D)), DT[dt])
     k = round_to(rng.standard_normal((B, Hkv, L, D)), DT[dt])
     v = round_to(rng.standard_normal((B, Hkv, L, D)), DT[dt])
     kv_len = rng.integers(1, L + 1, B).astype(np.int32)
     kv_len[0] = L
+    if B > 1:
+        kv_len[1] = 1
     scale = 1.0 / np.sqrt(D)
     ref = vko.attention(q[:, :, None, :], k, v, scale, kv_len=kv_len)[:, :, 0, :]
+    Kd, Vd = dev(k, DT[dt]), dev(v, DT[dt])
+    for b in range(B):
+        Kd[b, :, int(kv_len[b]):] = float("nan")
+        Vd[b, :, int(kv_len[b]):] = float("nan")
     O = torch.zeros(B, Hq, D, dtype=DT[dt], device="cuda")
-    ctx.attn_decode(dev(q, DT[dt]), dev(k, DT[dt]), dev(v, DT[dt]), O, scale, kv_len=torch.from_numpy(kv_len).cuda())
-    ctx.sync()
-    assert_low(host(O), ref, "decode")
-    # caller-provided workspace gives the same bits
-    ws = torch.empty(ctx.attn_decode_workspace_bytes(B, Hq, Hkv, L, D), dtype=torch.uint8, device="cuda")
-    O2 = torch.zeros_like(O)
-    ctx.attn_decode(dev(q, DT[dt]), dev(k, DT[dt]), dev(v, DT[dt]), O2, scale, kv_len=torch.from_numpy(kv_len).cuda(), workspace=ws)
-    ctx.sync()
+    lens = torch.from_numpy(kv_len).cuda()
+    ctx.set_impl(impl)
+    try:
+        ctx.attn_decode(dev(q, DT[dt]), Kd, Vd, O, scale, kv_len=lens)
+        ctx.sync()
+        assert_low(host(O), ref, "decode")
+        # caller-provided workspace gives the same bits
+        ws = torch.empty(ctx.attn_decode_workspace_bytes(B, Hq, Hkv, L, D), dtype=torch.uint8, device="cuda")
+        O2 = torch.zeros_like(O)
+        ctx.attn_decode(dev(q, DT[dt]), Kd, Vd, O2, scale, kv_len=lens, workspace=ws)
+        ctx.sync()
+    finally:
+        ctx.set_impl(vknn_b200.IMPL_AUTO)
     assert torch.equal(O, O2)
+
+
+def test_decode_config5_shape_slice(ctx):
+    """Config 5 geometry (32 q / 8 kv heads, D=128, cache 8192, kv_len in [1024, 8192]) on 4 sequences."""
+    rng = np.random.default_rng(1005)
+    B, Hq, Hkv, L, D = 4, 32, 8, 8192, 128
+    q = round_to(rng.standard_normal((B, Hq, D)), torch.float16)
+    k = round_to(rng.standard_normal((B, Hkv, L, D)), torch.float16)
+    v = round_to(rng.standard_normal((B, Hkv, L, D)), torch.float16)
+    kv_len = rng.integers(1024, L + 1, B).astype(np.int32)
+    scale = 1.0 / np.sqrt(D)
+    ref = vko.attention(q[:, :, None, :], k, v, scale, kv_len=kv_len)[:, :, 0, :]
+    O = torch.zeros(B, Hq, D, dtype=torch.float16, device="cuda")
+    ctx.attn_decode(dev(q, torch.float16), dev(k, torch.float16), dev(v, torch.float16), O, scale, kv_len=torch.from_numpy(kv_len).cuda())
+    ctx.sync()
+    assert_low(host(O), ref, "decode config 5")
 
 
 # ------------------------------------------------------------------------------------------------ pointwise family

@@ -11,6 +11,9 @@
 // Algorithmic bytes per call: sum_b 2 * Hkv * kv_len[b] * D * sizeof(T)  (+ Q and O).
 #include "common.cuh"
 
+int vkc_attn_decode_tcgen05(vkc_ctx *ctx, const void *Q, const void *Kc, const void *Vc, int64_t B, int64_t Hq, int64_t Hkv, int64_t Lmax, int64_t D,
+                            const int32_t *kv_len, float scale, float *part_ml, float *part_o, int chunk, int parts_stride, int dtype, cudaStream_t st);
+
 namespace {
 
     constexpr int kWarps = 4;
@@ -20,6 +23,10 @@ namespace {
         while (chunk > 128 && B * Hkv * ((Lmax + chunk - 1) / chunk) < 2 * 148) chunk >>= 1;
         return chunk;
     }
+
+    // Partial slots per (sequence, query head) the scratch must hold: enough for either kernel form (the
+    // tensor-core form uses chunks twice as long with two slots each).
+    __host__ __device__ inline int decode_slots(int64_t Lmax, int chunk) { return 2 * (int) ((Lmax + 2 * chunk - 1) / (2 * chunk)); }
 
     template <typename T> __device__ __forceinline__ void unpack8(const uint4 &raw, float (&f)[8]);
     template <> __device__ __forceinline__ void unpack8<__half>(const uint4 &raw, float (&f)[8]) {
@@ -218,18 +225,20 @@ namespace {
     // One CTA per (sequence, query head): merges the per-chunk partials and writes the output row.
     template <typename T>
     __global__ void attn_decode_combine_kernel(const float *__restrict__ part_ml, const float *__restrict__ part_o, T *__restrict__ O,
-                                               const int32_t *__restrict__ kv_len, int64_t Hq, int64_t Lmax, int D, int chunk, int max_splits) {
+                                               const int32_t *__restrict__ kv_len, int64_t Hq, int64_t Lmax, int D, int chunk, int parts,
+                                               int max_splits) {
         const int b = blockIdx.y, hq = blockIdx.x;
         int64_t   len = kv_len ? (int64_t) kv_len[b] : Lmax;
         if (len > Lmax) len = Lmax;
-        const int     ns  = (int) ((len + chunk - 1) / chunk);
+        const int     ns  = parts * (int) ((len + chunk - 1) / chunk); // partial slots this sequence filled
         const int64_t row = ((int64_t) b * Hq + hq) * max_splits;
         float         mt  = -INFINITY;
         for (int s = 0; s < ns; ++s) mt = fmaxf(mt, part_ml[(row + s) * 2]);
         for (int d = threadIdx.x; d < D; d += blockDim.x) {
             float lt = 0.f, ot = 0.f;
             for (int s = 0; s < ns; ++s) {
-                const float a = exp2f(part_ml[(row + s) * 2] - mt);
+                const float ms = part_ml[(row + s) * 2];
+                const float a  = ms == -INFINITY ? 0.f : exp2f(ms - mt);
                 lt += part_ml[(row + s) * 2 + 1] * a;
                 ot += part_o[(row + s) * D + d] * a;
             }
@@ -242,16 +251,28 @@ namespace {
                       const int32_t *kv_len, float scale, float *ws, cudaStream_t st) {
         const int     G          = (int) (Hq / Hkv);
         const int     chunk      = decode_chunk(B, Hkv, Lmax);
-        const int     max_splits = (int) ((Lmax + chunk - 1) / chunk);
+        const int     max_splits = decode_slots(Lmax, chunk); // slot stride; the SIMT form fills ceil(Lmax/chunk) of them
         constexpr int D          = CH * 64;
+        int           eff_chunk = chunk, parts = 1;
         float        *part_ml    = ws;
         float        *part_o     = ws + (size_t) B * Hq * max_splits * 2;
         const float   sl2        = scale * 1.4426950408889634f;
         dim3          grid((unsigned) max_splits, (unsigned) Hkv, (unsigned) B);
+        bool          split_done = false;
+        if (ctx->impl != VKC_IMPL_SIMT) {
+            const int dtype = std::is_same<T, __half>::value ? VKC_F16 : VKC_BF16;
+            int       rc    = vkc_attn_decode_tcgen05(ctx, Q, Kc, Vc, B, Hq, Hkv, Lmax, D, kv_len, scale, part_ml, part_o, 2 * chunk, max_splits, dtype, st);
+            if (rc == VKC_OK) {
+                split_done = true;
+                eff_chunk  = 2 * chunk;
+                parts      = 2;
+            }
+            else if (rc != VKC_ERR_UNSUPPORTED || ctx->impl == VKC_IMPL_TCGEN05) return rc;
+        }
 #define VKC_DEC(G_)                                                                                                                    \
     attn_decode_kernel<T, CH, G_><<<grid, kWarps * 32, 0, st>>>((const T *) Q, (const T *) Kc, (const T *) Vc, part_ml, part_o, kv_len, Hkv, \
                                                                 Lmax, sl2, chunk, max_splits)
-        switch (G) {
+        if (!split_done) switch (G) {
             case 1: VKC_DEC(1); break;
             case 2: VKC_DEC(2); break;
             case 4: VKC_DEC(4); break;
@@ -259,10 +280,12 @@ namespace {
             default: return vkc_fail(ctx, VKC_ERR_UNSUPPORTED, "attn_decode: group size %d (Hq/Hkv) must be 1, 2, 4 or 8", G);
         }
 #undef VKC_DEC
-        int rc = vkc_post_launch(ctx, "attn_decode");
-        if (rc) return rc;
+        if (!split_done) {
+            int rc = vkc_post_launch(ctx, "attn_decode");
+            if (rc) return rc;
+        }
         dim3 cgrid((unsigned) Hq, (unsigned) B);
-        attn_decode_combine_kernel<T><<<cgrid, D < 128 ? D : 128, 0, st>>>(part_ml, part_o, (T *) O, kv_len, Hq, Lmax, D, chunk, max_splits);
+        attn_decode_combine_kernel<T><<<cgrid, D < 128 ? D : 128, 0, st>>>(part_ml, part_o, (T *) O, kv_len, Hq, Lmax, D, eff_chunk, parts, max_splits);
         return vkc_post_launch(ctx, "attn_decode_combine");
     }
 
@@ -280,7 +303,7 @@ static void *g_decode_static_ptr[kMaxDevices] = {nullptr};
 extern "C" size_t vkc_attn_decode_workspace_bytes(int64_t B, int64_t Hq, int64_t Hkv, int64_t Lmax, int64_t D) {
     if (B <= 0 || Hq <= 0 || Hkv <= 0 || Lmax <= 0 || D <= 0) return 0;
     const int    chunk      = decode_chunk(B, Hkv, Lmax);
-    const size_t max_splits = (size_t) ((Lmax + chunk - 1) / chunk);
+    const size_t max_splits = (size_t) decode_slots(Lmax, chunk);
     return (size_t) B * (size_t) Hq * max_splits * (size_t) (D + 2) * sizeof(float);
 }
 

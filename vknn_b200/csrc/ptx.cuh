@@ -84,6 +84,28 @@ namespace ptx {
             "l"(map), "r"(x), "r"(y), "r"(z), "r"(w), "r"(bar)
             : "memory");
     }
+    // Untiled bulk copy of `bytes` contiguous bytes (both addresses 16-byte aligned, size a multiple of 16).
+    __device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src), "r"(bytes),
+                     "r"(bar)
+                     : "memory");
+    }
+    // Packed fp32 pair arithmetic (two independent fp32 FMAs per instruction).
+    __device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) {
+        float2 d;
+        asm("fma.rn.f32x2 %0, %1, %2, %3;"
+            : "=l"(reinterpret_cast<unsigned long long &>(d))
+            : "l"(reinterpret_cast<const unsigned long long &>(a)), "l"(reinterpret_cast<const unsigned long long &>(b)),
+              "l"(reinterpret_cast<const unsigned long long &>(c)));
+        return d;
+    }
+    __device__ __forceinline__ float2 fmul2(float2 a, float2 b) {
+        float2 d;
+        asm("mul.rn.f32x2 %0, %1, %2;"
+            : "=l"(reinterpret_cast<unsigned long long &>(d))
+            : "l"(reinterpret_cast<const unsigned long long &>(a)), "l"(reinterpret_cast<const unsigned long long &>(b)));
+        return d;
+    }
     __device__ __forceinline__ void prefetch_tmap(const CUtensorMap *map) {
         asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
     }

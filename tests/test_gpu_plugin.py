@@ -1,0 +1,68 @@
+"""The drop-in boundary end to end: graphs planned by the UNMODIFIED reference engine (its importer-side passes,
+Session::plan partitioning, Session::run) with the CUDA backend plug-in selected and no CPU backend active, against
+the same engine on its own CPU backend. Both run inside oracle/_ref/vknn_ref_driver(_cuda), which is compiled
+from the reference sources plus vknn_b200/backend/cuda_backend.cpp where those sources are present."""
+import os
+
+import numpy as np
+import pytest
+
+from oracle import vko
+from tests.util import assert_high, assert_low
+from vknn_b200.synthetic import encoder_weights
+
+pytestmark = [pytest.mark.gpu, pytest.mark.skipif(not os.path.exists(vko.REF_DRIVER_CUDA), reason="plug-in driver not built (needs the reference headers)")]
+
+CUDA_KIND = 2
+
+
+def both(graph_fn, precision, iters=3):
+    (ref,), info_cpu = graph_fn().run(backend="cpu")
+    (got,), info = graph_fn().run(backend="cuda", precision=precision, iters=iters)
+    assert all(n[1] == CUDA_KIND for n in info["nodes"]), info["nodes"]  # every node was assigned to the plug-in
+    assert [n[0] for n in info["nodes"]] == [n[0] for n in info_cpu["nodes"]]  # same passes, same node run
+    return got, ref, info
+
+
+def test_config1_attention_high_and_low():
+    rng = np.random.default_rng(1001)
+    q, k, v = (rng.standard_normal((1, 12, 197, 64)).astype(np.float32) for _ in range(3))
+    got, ref, info = both(lambda: vko.attention_graph(q, k, v, 0.125), "high")
+    assert [n[0] for n in info["nodes"]] == ["Transpose", "MatMul", "Binary", "Softmax", "MatMul"]
+    assert_high(got, ref, "config 1 through the plug-in, fp32")
+    got, ref, _ = both(lambda: vko.attention_graph(q, k, v, 0.125), "low")
+    assert_low(got, ref, "config 1 through the plug-in, f16 storage")
+
+
+def test_gqa_decode_graph_with_mask():
+    rng = np.random.default_rng(7)
+    B, Hkv, G, D, L = 2, 2, 4, 64, 96
+    q, k, v = (rng.standard_normal(s).astype(np.float32) for s in ((B, Hkv, G, D), (B, Hkv, L, D), (B, Hkv, L, D)))
+    mask = np.zeros((1, 1, G, L), np.float32)
+    mask[..., 70:] = -np.inf
+    got, ref, info = both(lambda: vko.attention_graph(q, k, v, 0.125, mask=mask), "high")
+    assert "FusedPointwise" in [n[0] for n in info["nodes"]]
+    assert_high(got, ref, "gqa with mask")
+
+
+@pytest.mark.parametrize("B,T,d,H,dm", [(2, 130, 256, 4, 512), (1, 197, 768, 12, 3072)])
+def test_encoder_layer_graph(B, T, d, H, dm):
+    rng = np.random.default_rng(1002)
+    w = encoder_weights(rng, d, dm, bias_scale=0.01)
+    x = rng.standard_normal((B, T, d)).astype(np.float32)
+    got, ref, info = both(lambda: vko.encoder_layer_graph(x, w, H), "low")
+    assert_low(got, ref, "encoder layer through the plug-in")
+    got, ref, _ = both(lambda: vko.encoder_layer_graph(x, w, H), "high", iters=1)
+    assert_high(got, ref, "encoder layer through the plug-in, fp32")
+
+
+def test_unsupported_node_is_refused_not_run_on_cpu():
+    """No CPU backend is active for the CUDA session, so a node the plug-in declines fails the plan."""
+    x = np.ones((4, 5), np.float32)
+    g = vko.RefGraph()
+    g.input("x", x)
+    g.output("y", ())
+    g.node("Softmax", "sm", ["x"], ["y"], axis=0)
+    with pytest.raises(RuntimeError) as e:
+        g.run(backend="cuda")
+    assert "plan" in str(e.value) or "null" in str(e.value)

@@ -1,0 +1,877 @@
+// CudaBackend / CudaSegment — the host side of the B200 backend, written against VKNN's pluggable backend
+// interface (include/vknn/backend_class.h:15-47, include/vknn/segment.h:12-23) and registered with
+// VKNN_REGISTER_BACKEND (include/vknn/backend_registry.h:29-32). It never touches CUDA directly: all device
+// work goes through the C-ABI of libvknn_cuda (include/vknn_cuda.h).
+//
+// What the reference's planner hands over (src/core/session.cpp:393-422,486-585): a contiguous run of nodes in
+// topological order and, after compileSegment() returns, the segment's boundary input/output sets. Initializers
+// used by MatMul are erased from the graph once all segments are compiled (session.cpp:594-625), so weights are
+// uploaded inside compileSegment(); everything that depends on the boundary sets (which intermediates must stay
+// materialised) is planned lazily on the first run().
+//
+// Planning turns the node run into a short list of kernel launches:
+//   * Reshape / Transpose / Gather(scalar index) / Squeeze / Unsqueeze / Flatten / Identity become VIEWS (offset +
+//     strides over a device buffer); a copy is made only where a consumer cannot take the strides;
+//   * Transpose(K) -> MatMul -> Mul(scale) [FusedPointwise{Mul, Add mask}] -> Softmax -> MatMul collapses into one
+//     fused attention launch reading Q/K/V through their strides, and writes its output directly in the layout
+//     the following head-merge Transpose/Reshape asks for;
+//   * MatMul carries its fusedBias, an exported erf-GELU tail (Div, Erf, Add, FusedPointwise{Mul, Mul}) and a
+//     following residual Add in the GEMM epilogue;
+//   * anything else on the supported list runs as its own kernel (LayerNorm, Softmax, pointwise programs).
+// After one eager run the launch list is captured into a CUDA graph (the analogue of the reference's pre-recorded
+// command buffer, src/backend/vulkan/vk_backend.cpp:1009-1210) and replayed.
+//
+// There is no CPU fallback: what supportsNode() declines is refused by the planner (Status::Unsupported) when no
+// other backend is configured, and a failing device call surfaces as vknn::Error.
+#include "vknn/backend.h"
+#include "vknn/binary_type.h"
+#include "vknn/error.h"
+#include "vknn/logging.h"
+#include "vknn/unary_type.h"
+#include "vknn_cuda.h"
+
+#include <algorithm>
+#include <cmath>
+#include <cstring>
+#include <map>
+#include <memory>
+#include <set>
+#include <string>
+#include <vector>
+
+namespace vknn {
+
+    // The reference leaves DeviceStorage to the backend (include/vknn/device_storage.h:8). Host builds contain no
+    // other definition.
+    struct DeviceStorage {
+        void  *ptr   = nullptr;
+        size_t bytes = 0;
+    };
+
+    namespace {
+
+        constexpr BackendKind kCuda = static_cast<BackendKind>(2); // first value after Vulkan = 0, Cpu = 1
+
+        [[noreturn]] void fail(Status s, const std::string &msg) { throw Error(s, "CUDA backend: " + msg); }
+
+        void check(vkc_ctx *ctx, int rc, const char *what) {
+            if (rc == VKC_OK) return;
+            std::string msg = std::string(what) + ": " + (ctx ? vkc_last_error(ctx) : "no context");
+            switch (rc) {
+                case VKC_ERR_INVALID: fail(Status::InvalidArgument, msg);
+                case VKC_ERR_UNSUPPORTED: fail(Status::Unsupported, msg);
+                case VKC_ERR_DEVICE: fail(Status::DeviceLost, msg);
+                default: fail(Status::RuntimeError, msg);
+            }
+        }
+
+        int64_t prod(const Shape &s) {
+            int64_t n = 1;
+            for (int64_t d : s) n *= d;
+            return n;
+        }
+        std::vector<int64_t> denseStrides(const Shape &s) {
+            std::vector<int64_t> st(s.size(), 1);
+            for (int i = (int) s.size() - 2; i >= 0; --i) st[i] = st[i + 1] * s[i + 1];
+            return st;
+        }
+
+        struct View {
+            int                  buf = -1; // index into CudaSegment::bufs_
+            int64_t              offset = 0;
+            Shape                shape;
+            std::vector<int64_t> strides;
+            bool                 contiguous() const {
+                int64_t expect = 1;
+                for (int i = (int) shape.size() - 1; i >= 0; --i) {
+                    if (shape[i] != 1 && strides[i] != expect) return false;
+                    expect *= shape[i];
+                }
+                return true;
+            }
+        };
+
+        struct Step {
+            enum Kind { Gemm, Attn, LayerNorm, Pointwise, Softmax, Copy } kind;
+            // generic operands (device pointers resolved at plan time)
+            const void *a = nullptr, *b = nullptr, *c = nullptr;
+            void       *d = nullptr;
+            const float *bias = nullptr, *gamma = nullptr, *beta = nullptr, *mask = nullptr;
+            int64_t     M = 0, N = 0, K = 0, batch = 1, sa = 0, sb = 0, sd = 0, lda = 0, ldb = 0, ldd = 0;
+            int         bLayout = VKC_B_KN, epilogue = 0;
+            int64_t     B = 0, Hq = 0, Hkv = 0, Sq = 0, Skv = 0, D = 0;
+            int64_t     qs[3], ks[3], vs[3], os[3];
+            float       scale = 1.f, eps = 1e-5f;
+            int64_t     rows = 0, norm = 0;
+            std::vector<int64_t>      shape, opStrides, inStrides;
+            std::vector<int32_t>      pwSteps;
+            std::vector<float>        pwParams;
+            std::vector<const void *> operands;
+            int64_t                   inOffset = 0;
+            std::string               label;
+        };
+
+        bool isScalarInit(const Graph &g, TensorId id, float *value) {
+            auto it = g.initializers.find(id);
+            if (it == g.initializers.end()) return false;
+            const TensorDesc &d = g.desc(id);
+            if (prod(d.shape) != 1 && !d.shape.empty()) return false;
+            if (d.dtype == DType::Float32) *value = it->second.f32()[0];
+            else if (d.dtype == DType::Float16) *value = halfToFloat(reinterpret_cast<const fp16_t *>(it->second.bytes.data())[0]);
+            else return false;
+            return true;
+        }
+
+    } // namespace
+
+    class CudaBackend;
+
+    class CudaSegment: public Segment {
+      public:
+        CudaSegment(CudaBackend *be, vkc_ctx *ctx, const std::vector<int> &nodes, Graph &g, const Config &cfg);
+        ~CudaSegment() override;
+        void run(ExecContext &ctx) override;
+
+      private:
+        struct DevBuf {
+            void  *ptr   = nullptr;
+            size_t bytes = 0;
+        };
+        vkc_ctx     *ctx_;
+        const Graph *g_;
+        int          dtype_;     // storage type of activations and matrices
+        size_t       esize_;
+        bool         useGraph_ = true;
+        bool         planned_  = false;
+        int          runs_     = 0;
+        vkc_graph   *graph_    = nullptr;
+
+        std::vector<DevBuf>         bufs_;
+        std::map<TensorId, View>    views_;     // every tensor the segment touches on the device
+        std::map<TensorId, float *> f32Inits_;  // biases, LayerNorm gamma/beta, masks: kept fp32
+        std::map<TensorId, std::vector<int64_t>> i64Inits_; // Reshape shapes, Gather indices (host only)
+        std::map<TensorId, float>   scalarInits_;
+        std::set<TensorId>          initIds_;   // initializers seen at compile time (the graph forgets MatMul weights afterwards)
+        std::vector<Step>           steps_;
+        std::set<TensorId>          boundaryOut_;
+
+        int   newBuffer(size_t bytes);
+        View  newTensor(TensorId id, const Shape &shape);
+        const void *ptrOf(const View &v) const { return static_cast<const char *>(bufs_[v.buf].ptr) + v.offset * (int64_t) esize_; }
+        void *ptrOf(const View &v) { return static_cast<char *>(bufs_[v.buf].ptr) + v.offset * (int64_t) esize_; }
+        View  materialize(const View &v, const std::string &why);
+        const float *f32Init(TensorId id);
+        void  uploadInitializers(const std::vector<int> &nodes, Graph &g);
+        void  plan();
+        void  launch(const Step &s);
+        int   consumersInSegment(TensorId id, std::vector<int> *who) const;
+        bool  internalOnly(TensorId id) const { return boundaryOut_.count(id) == 0; }
+
+        bool tryAttention(size_t pos, std::set<int> &done);
+        void planMatMul(size_t pos, std::set<int> &done);
+        void planPointwise(const Node &n);
+    };
+
+    class CudaBackend: public Backend {
+      public:
+        CudaBackend() {
+            int n = 0;
+            if (vkc_device_count(&n) == VKC_OK && n > 0 && vkc_ctx_create(0, &ctx_) != VKC_OK) ctx_ = nullptr;
+        }
+        ~CudaBackend() override {
+            if (ctx_) vkc_ctx_destroy(ctx_);
+        }
+        BackendKind kind() const override { return kCuda; }
+        const char *name() const override { return "CUDA"; }
+        bool        available() const override { return ctx_ != nullptr; }
+        void        configure(const Config &cfg) override { precision_ = cfg.precision; }
+
+        bool supports(OpType t, DType dt) const override {
+            if (dt != DType::Float32 && dt != DType::Float16) return false;
+            switch (t) {
+                case OpType::MatMul:
+                case OpType::Softmax:
+                case OpType::LayerNorm:
+                case OpType::Binary:
+                case OpType::Add:
+                case OpType::Unary:
+                case OpType::FusedPointwise:
+                case OpType::Transpose:
+                case OpType::Reshape:
+                case OpType::Gather:
+                case OpType::Squeeze:
+                case OpType::Unsqueeze:
+                case OpType::Flatten:
+                case OpType::Identity: return true;
+                default: return false;
+            }
+        }
+
+        // Shape-aware refusals mirror what the kernels cover; the reference's Vulkan backend gates the same way
+        // (src/backend/vulkan/vk_backend.cpp:189-434).
+        bool supportsNode(const Graph &g, const Node &nd, DType dt) const override {
+            if (!supports(nd.type, dt)) return false;
+            if (nd.type != OpType::FusedPointwise && nd.attr.has("pw_steps")) return false; // producer-carried epilogue: not emitted today
+            auto rank = [&](TensorId id) { return (int) g.desc(id).shape.size(); };
+            for (TensorId o : nd.outputs)
+                if (o != kNoTensor && (rank(o) == 0 || rank(o) > 8)) return false;
+            switch (nd.type) {
+                case OpType::Softmax: {
+                    int64_t axis = nd.attr.geti("axis", -1), r = rank(nd.inputs[0]);
+                    return axis == -1 || axis == r - 1;
+                }
+                case OpType::LayerNorm: {
+                    if (nd.inputs.size() < 2 || !g.isInitializer(nd.inputs[1])) return false;
+                    if (nd.inputs.size() > 2 && nd.inputs[2] != kNoTensor && !g.isInitializer(nd.inputs[2])) return false;
+                    int64_t axis = nd.attr.geti("axis", -1), r = rank(nd.inputs[0]);
+                    return axis == -1 || axis == r - 1;
+                }
+                case OpType::Gather: {
+                    if (!g.isInitializer(nd.inputs[1])) return false;
+                    const TensorDesc &d = g.desc(nd.inputs[1]);
+                    return d.dtype == DType::Int64 && prod(d.shape) == 1;
+                }
+                case OpType::MatMul: {
+                    const Shape &a = g.desc(nd.inputs[0]).shape, &b = g.desc(nd.inputs[1]).shape;
+                    if (a.size() < 2 || b.size() < 2) return false;
+                    if (b.size() > 2 && b.size() != a.size()) return false; // mixed-rank batch broadcast: not covered
+                    for (size_t i = 0; i + 2 < b.size() && b.size() > 2; ++i)
+                        if (b[i] != a[i] && b[i] != 1) return false;
+                    return true;
+                }
+                case OpType::Binary:
+                case OpType::Add: {
+                    // one operand must already have the output shape (it becomes the primary of the step program)
+                    const Shape &o = g.desc(nd.outputs[0]).shape;
+                    bool         a = g.desc(nd.inputs[0]).shape == o && !g.isInitializer(nd.inputs[0]);
+                    bool         b = g.desc(nd.inputs[1]).shape == o && !g.isInitializer(nd.inputs[1]);
+                    if (a) return true;
+                    int code = nd.type == OpType::Add ? (int) BinaryType::Add : nd.subOp;
+                    bool commutative = code == (int) BinaryType::Mul || code == (int) BinaryType::Add || code == (int) BinaryType::Max ||
+                                       code == (int) BinaryType::Min;
+                    return b && commutative;
+                }
+                case OpType::FusedPointwise: return !g.isInitializer(nd.inputs[0]);
+                default: return true;
+            }
+        }
+
+        std::unique_ptr<Segment> compileSegment(const std::vector<int> &nodeIdx, Graph &g, const Config &cfg) override {
+            if (!ctx_) fail(Status::RuntimeError, "no usable sm_100 device");
+            return std::unique_ptr<Segment>(new CudaSegment(this, ctx_, nodeIdx, g, cfg));
+        }
+
+        Precision precision() const { return precision_; }
+
+      private:
+        vkc_ctx  *ctx_       = nullptr;
+        Precision precision_ = Precision::Low;
+    };
+
+    VKNN_REGISTER_BACKEND(kCuda, CudaBackend);
+
+    // ------------------------------------------------------------------------------------------------------------
+    CudaSegment::CudaSegment(CudaBackend *be, vkc_ctx *ctx, const std::vector<int> &nodes, Graph &g, const Config &cfg): ctx_(ctx), g_(&g) {
+        backend = be;
+        nodeIdx = nodes;
+        dtype_  = cfg.precision == Precision::High ? VKC_F32 : VKC_F16;
+        esize_  = dtype_ == VKC_F32 ? 4 : 2;
+        uploadInitializers(nodes, g);
+    }
+
+    CudaSegment::~CudaSegment() {
+        if (graph_) vkc_graph_destroy(ctx_, graph_);
+        vkc_sync(ctx_, nullptr);
+        for (auto &b : bufs_)
+            if (b.ptr) vkc_free(ctx_, b.ptr);
+        for (auto &kv : f32Inits_)
+            if (kv.second) vkc_free(ctx_, kv.second);
+    }
+
+    int CudaSegment::newBuffer(size_t bytes) {
+        DevBuf b;
+        b.bytes = std::max<size_t>(bytes, 16);
+        check(ctx_, vkc_alloc(ctx_, b.bytes, &b.ptr), "vkc_alloc");
+        bufs_.push_back(b);
+        return (int) bufs_.size() - 1;
+    }
+
+    View CudaSegment::newTensor(TensorId id, const Shape &shape) {
+        View v;
+        v.buf     = newBuffer((size_t) prod(shape) * esize_);
+        v.shape   = shape;
+        v.strides = denseStrides(shape);
+        if (id != kNoTensor) views_[id] = v;
+        return v;
+    }
+
+    // Weights and constants go to the device while the graph still holds them.
+    void CudaSegment::uploadInitializers(const std::vector<int> &nodes, Graph &g) {
+        for (int ni : nodes) {
+            const Node &n = g.nodes[ni];
+            for (TensorId in : n.inputs) {
+                if (in == kNoTensor || !g.isInitializer(in) || views_.count(in) || f32Inits_.count(in) || i64Inits_.count(in)) continue;
+                const TensorDesc &d  = g.desc(in);
+                const HostBuffer &hb = g.initializers.at(in);
+                initIds_.insert(in);
+                const int64_t     ne = std::max<int64_t>(prod(d.shape), d.shape.empty() ? 1 : 0);
+                if (d.dtype == DType::Int64) {
+                    i64Inits_[in].assign(hb.i64(), hb.i64() + ne);
+                    continue;
+                }
+                if (d.dtype != DType::Float32 && d.dtype != DType::Float16) fail(Status::Unsupported, "initializer " + d.name + " has an unsupported dtype");
+                const int src = d.dtype == DType::Float32 ? VKC_F32 : VKC_F16;
+                float     sv;
+                if (isScalarInit(g, in, &sv)) scalarInits_[in] = sv;
+                const bool keepF32 = (n.type == OpType::MatMul && in == n.fusedBias) || (n.type == OpType::LayerNorm && (in == n.inputs[1] || (n.inputs.size() > 2 && in == n.inputs[2])));
+                if (keepF32) {
+                    void *p = nullptr;
+                    check(ctx_, vkc_alloc(ctx_, (size_t) ne * 4, &p), "vkc_alloc");
+                    check(ctx_, vkc_upload(ctx_, p, VKC_F32, hb.bytes.data(), src, ne, nullptr), "vkc_upload");
+                    f32Inits_[in] = static_cast<float *>(p);
+                    continue;
+                }
+                Shape shape = d.shape.empty() ? Shape {1} : d.shape;
+                View  v     = newTensor(in, shape);
+                check(ctx_, vkc_upload(ctx_, ptrOf(v), dtype_, hb.bytes.data(), src, ne, nullptr), "vkc_upload");
+            }
+        }
+        check(ctx_, vkc_sync(ctx_, nullptr), "vkc_sync"); // the host buffers may be freed right after compileSegment
+    }
+
+    const float *CudaSegment::f32Init(TensorId id) {
+        auto it = f32Inits_.find(id);
+        if (it != f32Inits_.end()) return it->second;
+        // an initializer that was uploaded in storage precision for another use: convert a private fp32 copy
+        auto vt = views_.find(id);
+        if (vt == views_.end()) fail(Status::RuntimeError, "missing initializer on the device");
+        const int64_t ne = prod(vt->second.shape);
+        void         *p  = nullptr;
+        check(ctx_, vkc_alloc(ctx_, (size_t) ne * 4, &p), "vkc_alloc");
+        check(ctx_, vkc_convert(ctx_, p, VKC_F32, ptrOf(vt->second), dtype_, ne, nullptr), "vkc_convert");
+        f32Inits_[id] = static_cast<float *>(p);
+        return f32Inits_[id];
+    }
+
+    int CudaSegment::consumersInSegment(TensorId id, std::vector<int> *who) const {
+        int c = 0;
+        for (size_t k = 0; k < nodeIdx.size(); ++k) {
+            const Node &n = g_->nodes[nodeIdx[k]];
+            for (TensorId in : n.inputs)
+                if (in == id) {
+                    ++c;
+                    if (who) who->push_back((int) k);
+                }
+        }
+        return c;
+    }
+
+    View CudaSegment::materialize(const View &v, const std::string &why) {
+        if (v.contiguous()) {
+            View d    = v;
+            d.strides = denseStrides(v.shape);
+            return d;
+        }
+        View d = newTensor(kNoTensor, v.shape);
+        Step s;
+        s.kind      = Step::Copy;
+        s.a         = bufs_[v.buf].ptr;
+        s.d         = ptrOf(d);
+        s.shape     = v.shape;
+        s.inStrides = v.strides;
+        s.inOffset  = v.offset;
+        s.label     = "copy(" + why + ")";
+        steps_.push_back(s);
+        return d;
+    }
+
+    // Transpose(K) -> MatMul(Q,K^T) -> Mul(scale) | FusedPointwise{Mul scale, Add mask} -> Softmax -> MatMul(P,V)
+    bool CudaSegment::tryAttention(size_t pos, std::set<int> &done) {
+        const Graph &g  = *g_;
+        const Node  &m1 = g.nodes[nodeIdx[pos]];
+        if (m1.type != OpType::MatMul || m1.fusedBias != kNoTensor) return false;
+        auto single = [&](TensorId t, int *k) {
+            std::vector<int> who;
+            if (consumersInSegment(t, &who) != 1 || !internalOnly(t)) return false;
+            *k = who[0];
+            return true;
+        };
+        int kScale, kSoft, kPV;
+        if (!single(m1.outputs[0], &kScale)) return false;
+        const Node &sc    = g.nodes[nodeIdx[kScale]];
+        float       scale = 0.f;
+        const float *mask = nullptr;
+        TensorId    maskId = kNoTensor;
+        if (sc.type == OpType::Binary && sc.subOp == (int) BinaryType::Mul) {
+            TensorId other = sc.inputs[0] == m1.outputs[0] ? sc.inputs[1] : sc.inputs[0];
+            if (!scalarInits_.count(other)) return false;
+            scale = scalarInits_[other];
+        } else if (sc.type == OpType::FusedPointwise && sc.inputs[0] == m1.outputs[0]) {
+            const auto &st = sc.attr.getints("pw_steps");
+            if (st.size() != 8 || st[0] != 0 || st[1] != (int) BinaryType::Mul || st[4] != 0 || st[5] != (int) BinaryType::Add) return false;
+            TensorId sId = sc.inputs[(size_t) st[2]], mId = sc.inputs[(size_t) st[6]];
+            if (!scalarInits_.count(sId) || !initIds_.count(mId)) return false;
+            scale  = scalarInits_[sId];
+            maskId = mId;
+        } else {
+            return false;
+        }
+        if (!(scale > 0.f)) return false;
+        if (!single(sc.outputs[0], &kSoft)) return false;
+        const Node &sm = g.nodes[nodeIdx[kSoft]];
+        if (sm.type != OpType::Softmax) return false;
+        if (!single(sm.outputs[0], &kPV)) return false;
+        const Node &m2 = g.nodes[nodeIdx[kPV]];
+        if (m2.type != OpType::MatMul || m2.inputs[0] != sm.outputs[0] || m2.fusedBias != kNoTensor) return false;
+
+        View q = views_.at(m1.inputs[0]), kt = views_.at(m1.inputs[1]), v = views_.at(m2.inputs[1]);
+        const size_t r = q.shape.size();
+        if (r < 2 || r > 4 || kt.shape.size() != r || v.shape.size() != r) return false;
+        // K^T must be a transposed view of a tensor whose head dim is contiguous
+        if (kt.strides[r - 2] != 1 || q.strides[r - 1] != 1 || v.strides[r - 1] != 1) return false;
+        auto pad4 = [&](View x) {
+            while (x.shape.size() < 4) {
+                x.shape.insert(x.shape.begin(), 1);
+                x.strides.insert(x.strides.begin(), x.shape[1] * x.strides[0]);
+            }
+            return x;
+        };
+        q  = pad4(q);
+        kt = pad4(kt);
+        v  = pad4(v);
+        const int64_t B = q.shape[0], Hq = q.shape[1], Sq = q.shape[2], D = q.shape[3], Skv = kt.shape[3];
+        const int64_t Hkv = kt.shape[1];
+        if (kt.shape[0] != B || kt.shape[2] != D || v.shape[0] != B || v.shape[1] != Hkv || v.shape[2] != Skv || v.shape[3] != D) return false;
+        if (Hkv != Hq) return false; // grouped heads reach this backend as the batch-broadcast MatMul form, see supportsNode
+        if (maskId != kNoTensor) {
+            const Shape &ms = g.desc(maskId).shape;
+            if (prod(ms) != Sq * Skv || ms.size() < 2 || ms[ms.size() - 1] != Skv || ms[ms.size() - 2] != Sq) return false; // one [Sq,Skv] mask shared by all units
+            mask = f32Init(maskId);
+        }
+        // Output layout: if the only consumer is the head-merge Transpose(0,2,1,3), write [B,Sq,H,D] directly.
+        const TensorId outId = m2.outputs[0];
+        const Shape    oshape = g.desc(outId).shape;
+        int            kT;
+        bool           merged = false;
+        View           o;
+        if (r == 4 && single(outId, &kT)) {
+            const Node &tn = g.nodes[nodeIdx[kT]];
+            std::vector<int64_t> perm = tn.attr.getints("perm");
+            if (tn.type == OpType::Transpose && perm == std::vector<int64_t> {0, 2, 1, 3}) {
+                View t = newTensor(tn.outputs[0], Shape {B, Sq, Hq, D});
+                o      = t; // view of the same buffer in [B,H,Sq,D] index order
+                o.shape   = Shape {B, Hq, Sq, D};
+                o.strides = {t.strides[0], t.strides[2], t.strides[1], t.strides[3]};
+                views_[outId] = o;
+                done.insert(kT);
+                merged = true;
+            }
+        }
+        if (!merged) {
+            o = newTensor(outId, oshape);
+            o = pad4(o);
+        }
+        Step s;
+        s.kind = Step::Attn;
+        s.a = ptrOf(q), s.b = static_cast<const char *>(bufs_[kt.buf].ptr) + kt.offset * (int64_t) esize_, s.c = ptrOf(v), s.d = ptrOf(o);
+        s.B = B, s.Hq = Hq, s.Hkv = Hkv, s.Sq = Sq, s.Skv = Skv, s.D = D;
+        for (int i = 0; i < 3; ++i) {
+            s.qs[i] = q.strides[i];
+            s.vs[i] = v.strides[i];
+            s.os[i] = o.strides[i];
+        }
+        s.ks[0] = kt.strides[0], s.ks[1] = kt.strides[1], s.ks[2] = kt.strides[3]; // undo the transpose: seq stride is K^T's last
+        s.scale = scale;
+        s.mask  = mask;
+        s.label = "attention";
+        steps_.push_back(s);
+        done.insert(kScale);
+        done.insert(kSoft);
+        done.insert(kPV);
+        return true;
+    }
+
+    void CudaSegment::planMatMul(size_t pos, std::set<int> &done) {
+        const Graph &g = *g_;
+        const Node  &n = g.nodes[nodeIdx[pos]];
+        View         a = views_.at(n.inputs[0]), b = views_.at(n.inputs[1]);
+        const size_t ra = a.shape.size(), rb = b.shape.size();
+        const int64_t M = a.shape[ra - 2], K = a.shape[ra - 1], N = b.shape[rb - 1];
+        // A: rows with unit stride along K and a dense batch; otherwise copy
+        if (a.strides[ra - 1] != 1) a = materialize(a, "matmul A");
+        int64_t batch = 1;
+        for (size_t i = 0; i + 2 < ra; ++i) batch *= a.shape[i];
+        bool aDenseBatch = true;
+        {
+            int64_t expect = a.strides[ra - 2] * M;
+            for (int i = (int) ra - 3; i >= 0; --i) {
+                if (a.shape[i] != 1 && a.strides[i] != expect) aDenseBatch = false;
+                expect *= a.shape[i];
+            }
+        }
+        if (!aDenseBatch) a = materialize(a, "matmul A batch");
+        Step s;
+        s.kind = Step::Gemm;
+        s.K = K, s.N = N;
+        s.lda = a.strides[ra - 2];
+        if (b.strides[rb - 1] == 1) {
+            s.bLayout = VKC_B_KN;
+            s.ldb     = b.strides[rb - 2];
+        } else if (b.strides[rb - 2] == 1) {
+            s.bLayout = VKC_B_NK; // a transposed view: read it as [N,K] rows
+            s.ldb     = b.strides[rb - 1];
+        } else {
+            b         = materialize(b, "matmul B");
+            s.bLayout = VKC_B_KN;
+            s.ldb     = b.strides[rb - 2];
+        }
+        bool bBatched = false;
+        if (rb > 2) {
+            for (size_t i = 0; i + 2 < rb; ++i)
+                if (b.shape[i] != 1) bBatched = true;
+        }
+        if (!bBatched && s.lda == K) {
+            // weights shared by every batch element: fold the batch into M
+            s.M = batch * M, s.batch = 1, s.sa = 0, s.sb = 0;
+        } else {
+            s.M = M, s.batch = batch, s.sa = M * s.lda;
+            if (bBatched) {
+                // dense batch over B (partial broadcast was refused in supportsNode unless all-ones or equal)
+                bool dense = true;
+                int64_t expect = (s.bLayout == VKC_B_KN ? K : N) * s.ldb;
+                for (int i = (int) rb - 3; i >= 0; --i) {
+                    if (b.shape[i] != 1 && b.strides[i] != expect) dense = false;
+                    if (b.shape[i] == 1 && a.shape[i] != 1) dense = false;
+                    expect *= b.shape[i];
+                }
+                if (!dense) {
+                    b = materialize(b, "matmul B batch");
+                    if (s.bLayout == VKC_B_NK) { // materialize() keeps the logical [.., K, N] shape: now row-major KN
+                        s.bLayout = VKC_B_KN;
+                    }
+                    s.ldb = N;
+                    // broadcast along some batch dims only is not covered
+                    for (size_t i = 0; i + 2 < rb; ++i)
+                        if (b.shape[i] != a.shape[i]) fail(Status::Unsupported, "MatMul with a partially broadcast B batch");
+                }
+                s.sb = (s.bLayout == VKC_B_KN ? K : N) * s.ldb;
+            } else {
+                s.sb = 0;
+            }
+        }
+        s.a = ptrOf(a);
+        s.b = ptrOf(b);
+        if (n.fusedBias != kNoTensor) {
+            s.bias = f32Init(n.fusedBias);
+            s.epilogue |= VKC_EPI_BIAS;
+        }
+        TensorId outId = n.outputs[0];
+        // --- erf-GELU tail: Div(sqrt2) -> Erf -> Add(1) -> FusedPointwise{Mul h, Mul 0.5}
+        std::vector<int> who;
+        if (internalOnly(outId) && consumersInSegment(outId, &who) == 2) {
+            int kDiv = -1, kFp = -1;
+            for (int k : who) {
+                const Node &c = g.nodes[nodeIdx[k]];
+                if (c.type == OpType::Binary && c.subOp == (int) BinaryType::Div && c.inputs[0] == outId) kDiv = k;
+                if (c.type == OpType::FusedPointwise) kFp = k;
+            }
+            if (kDiv >= 0 && kFp >= 0) {
+                const Node &dv = g.nodes[nodeIdx[kDiv]];
+                auto it = scalarInits_.find(dv.inputs[1]);
+                std::vector<int> w2;
+                if (it != scalarInits_.end() && std::fabs(it->second - 1.41421356f) < 1e-5f && internalOnly(dv.outputs[0]) &&
+                    consumersInSegment(dv.outputs[0], &w2) == 1) {
+                    const Node &er = g.nodes[nodeIdx[w2[0]]];
+                    std::vector<int> w3;
+                    if (er.type == OpType::Unary && er.subOp == (int) UnaryType::Erf && internalOnly(er.outputs[0]) &&
+                        consumersInSegment(er.outputs[0], &w3) == 1) {
+                        const Node &ad = g.nodes[nodeIdx[w3[0]]];
+                        TensorId    one = ad.inputs[0] == er.outputs[0] ? ad.inputs[1] : ad.inputs[0];
+                        std::vector<int> w4;
+                        const bool isAdd = ad.type == OpType::Add || (ad.type == OpType::Binary && ad.subOp == (int) BinaryType::Add);
+                        if (isAdd && scalarInits_.count(one) && scalarInits_[one] == 1.0f && internalOnly(ad.outputs[0]) &&
+                            consumersInSegment(ad.outputs[0], &w4) == 1 && w4[0] == kFp) {
+                            const Node &fp = g.nodes[nodeIdx[kFp]];
+                            const auto &st = fp.attr.getints("pw_steps");
+                            if (fp.inputs[0] == ad.outputs[0] && st.size() == 8 && st[0] == 0 && st[1] == (int) BinaryType::Mul && st[4] == 0 &&
+                                st[5] == (int) BinaryType::Mul) {
+                                TensorId o1 = fp.inputs[(size_t) st[2]], o2 = fp.inputs[(size_t) st[6]];
+                                TensorId hId = o1 == outId ? o1 : o2, cId = o1 == outId ? o2 : o1;
+                                if (hId == outId && scalarInits_.count(cId) && scalarInits_[cId] == 0.5f) {
+                                    s.epilogue |= VKC_EPI_GELU_ERF;
+                                    done.insert(kDiv);
+                                    done.insert(w2[0]);
+                                    done.insert(w3[0]);
+                                    done.insert(kFp);
+                                    outId = fp.outputs[0];
+                                }
+                            }
+                        }
+                    }
+                }
+            }
+        }
+        // --- residual Add
+        who.clear();
+        if (!(s.epilogue & VKC_EPI_GELU_ERF) && internalOnly(outId) && consumersInSegment(outId, &who) == 1) {
+            const Node &ad = g.nodes[nodeIdx[who[0]]];
+            const bool  isAdd = (ad.type == OpType::Add && ad.fusedAct == ActType::None) || (ad.type == OpType::Binary && ad.subOp == (int) BinaryType::Add);
+            if (isAdd && !done.count(who[0])) {
+                TensorId other = ad.inputs[0] == outId ? ad.inputs[1] : ad.inputs[0];
+                auto     ov    = views_.find(other);
+                if (ov != views_.end() && !initIds_.count(other) && g.desc(other).shape == g.desc(outId).shape && ov->second.contiguous()) {
+                    s.c = ptrOf(ov->second);
+                    s.epilogue |= VKC_EPI_RESIDUAL;
+                    done.insert(who[0]);
+                    outId = ad.outputs[0];
+                }
+            }
+        }
+        View d = newTensor(outId, g.desc(outId).shape);
+        s.d    = ptrOf(d);
+        s.ldd  = N;
+        s.sd   = s.batch > 1 ? M * N : 0;
+        s.label = "matmul";
+        steps_.push_back(s);
+    }
+
+    void CudaSegment::planPointwise(const Node &n) {
+        const Graph &g = *g_;
+        Step         s;
+        s.kind = Step::Pointwise;
+        const Shape oshape = g.desc(n.outputs[0]).shape;
+        s.shape.assign(oshape.begin(), oshape.end());
+        const int rank = (int) oshape.size();
+        auto addOperand = [&](TensorId id) -> int {
+            View v = materialize(views_.at(id), "pointwise operand");
+            s.operands.push_back(ptrOf(v));
+            const int off = rank - (int) v.shape.size();
+            for (int d = 0; d < rank; ++d) {
+                int64_t dim = d < off ? 1 : v.shape[d - off];
+                s.opStrides.push_back(dim == 1 ? 0 : v.strides[d - off]);
+            }
+            return (int) s.operands.size(); // 1-based
+        };
+        TensorId primary = n.inputs[0];
+        if (n.type == OpType::Binary || n.type == OpType::Add) {
+            const int code = n.type == OpType::Add ? (int) BinaryType::Add : n.subOp;
+            TensorId  other = n.inputs[1];
+            if (!(g.desc(primary).shape == oshape && !initIds_.count(primary))) std::swap(primary, other);
+            const int oi = addOperand(other);
+            s.pwSteps = {0, code, oi, 0};
+            s.pwParams = {0.f, 0.f};
+            if (n.type == OpType::Add && n.fusedAct != ActType::None) {
+                s.pwSteps.insert(s.pwSteps.end(), {2, (int) n.fusedAct, -1, 0});
+                s.pwParams.insert(s.pwParams.end(), {n.actLo, n.actHi});
+            }
+        } else if (n.type == OpType::Unary) {
+            s.pwSteps  = {1, n.subOp, -1, 0};
+            s.pwParams = {n.actLo, n.actHi};
+        } else { // FusedPointwise
+            const auto &st = n.attr.getints("pw_steps");
+            const auto &pr = n.attr.getfloats("pw_params");
+            std::map<int, int> remap; // reference operand index (into node.inputs) -> step-program operand index
+            for (size_t i = 0; i + 3 < st.size(); i += 4) {
+                int oi = -1;
+                if (st[i] == 0) {
+                    const int ref = (int) st[i + 2];
+                    if (!remap.count(ref)) remap[ref] = addOperand(n.inputs[(size_t) ref]);
+                    oi = remap[ref];
+                }
+                s.pwSteps.insert(s.pwSteps.end(), {(int32_t) st[i], (int32_t) st[i + 1], oi, 0});
+            }
+            s.pwParams.assign(pr.begin(), pr.end());
+            s.pwParams.resize(s.pwSteps.size() / 2, 0.f);
+        }
+        View x = materialize(views_.at(primary), "pointwise primary");
+        View y = newTensor(n.outputs[0], oshape);
+        s.a = ptrOf(x);
+        s.d = ptrOf(y);
+        s.label = "pointwise";
+        steps_.push_back(s);
+    }
+
+    void CudaSegment::plan() {
+        const Graph &g = *g_;
+        boundaryOut_.insert(boundaryOutputs.begin(), boundaryOutputs.end());
+        // boundary inputs that are not initializers get a device buffer each
+        for (TensorId id : boundaryInputs)
+            if (!initIds_.count(id) && !views_.count(id)) newTensor(id, g.desc(id).shape);
+
+        std::set<int> done;
+        for (size_t pos = 0; pos < nodeIdx.size(); ++pos) {
+            if (done.count((int) pos)) continue;
+            const Node &n = g.nodes[nodeIdx[pos]];
+            switch (n.type) {
+                case OpType::Reshape:
+                case OpType::Squeeze:
+                case OpType::Unsqueeze:
+                case OpType::Flatten:
+                case OpType::Identity: {
+                    View v    = materialize(views_.at(n.inputs[0]), "reshape");
+                    v.shape   = g.desc(n.outputs[0]).shape; // inferred statically; the shape initializer is not needed
+                    v.strides = denseStrides(v.shape);
+                    views_[n.outputs[0]] = v;
+                    break;
+                }
+                case OpType::Transpose: {
+                    const View          &x    = views_.at(n.inputs[0]);
+                    std::vector<int64_t> perm = n.attr.getints("perm");
+                    const int            r    = (int) x.shape.size();
+                    if ((int) perm.size() != r) {
+                        perm.clear();
+                        for (int i = r - 1; i >= 0; --i) perm.push_back(i);
+                    }
+                    View y = x;
+                    for (int i = 0; i < r; ++i) {
+                        int64_t p = perm[i] < 0 ? perm[i] + r : perm[i];
+                        y.shape[i]   = x.shape[p];
+                        y.strides[i] = x.strides[p];
+                    }
+                    views_[n.outputs[0]] = y;
+                    break;
+                }
+                case OpType::Gather: {
+                    const View &x    = views_.at(n.inputs[0]);
+                    int64_t     axis = n.attr.geti("axis", 0);
+                    const int   r    = (int) x.shape.size();
+                    if (axis < 0) axis += r;
+                    int64_t idx = i64Inits_.at(n.inputs[1])[0];
+                    if (idx < 0) idx += x.shape[axis];
+                    View y = x;
+                    y.offset += idx * x.strides[axis];
+                    const TensorDesc &id = g.desc(n.inputs[1]);
+                    const bool scalar    = id.shape.empty() || (id.shape.size() == 1 && id.shape[0] == 1);
+                    if (scalar) {
+                        y.shape.erase(y.shape.begin() + axis);
+                        y.strides.erase(y.strides.begin() + axis);
+                        if (y.shape.empty()) {
+                            y.shape   = {1};
+                            y.strides = {1};
+                        }
+                    } else {
+                        y.shape[axis] = 1;
+                    }
+                    views_[n.outputs[0]] = y;
+                    break;
+                }
+                case OpType::MatMul:
+                    if (!tryAttention(pos, done)) planMatMul(pos, done);
+                    break;
+                case OpType::LayerNorm: {
+                    View x = materialize(views_.at(n.inputs[0]), "layernorm");
+                    View y = newTensor(n.outputs[0], g.desc(n.outputs[0]).shape);
+                    Step s;
+                    s.kind  = Step::LayerNorm;
+                    s.a     = ptrOf(x);
+                    s.d     = ptrOf(y);
+                    s.norm  = x.shape.back();
+                    s.rows  = prod(x.shape) / s.norm;
+                    s.gamma = f32Init(n.inputs[1]);
+                    s.beta  = (n.inputs.size() > 2 && n.inputs[2] != kNoTensor) ? f32Init(n.inputs[2]) : nullptr;
+                    s.eps   = n.attr.getf("epsilon", 1e-5f);
+                    s.label = "layernorm";
+                    steps_.push_back(s);
+                    break;
+                }
+                case OpType::Softmax: {
+                    View x = materialize(views_.at(n.inputs[0]), "softmax");
+                    View y = newTensor(n.outputs[0], g.desc(n.outputs[0]).shape);
+                    Step s;
+                    s.kind  = Step::Softmax;
+                    s.a     = ptrOf(x);
+                    s.d     = ptrOf(y);
+                    s.norm  = x.shape.back();
+                    s.rows  = prod(x.shape) / s.norm;
+                    s.label = "softmax";
+                    steps_.push_back(s);
+                    break;
+                }
+                case OpType::Binary:
+                case OpType::Add:
+                case OpType::Unary:
+                case OpType::FusedPointwise: planPointwise(n); break;
+                default: fail(Status::Unsupported, std::string("node type ") + opTypeName(n.type));
+            }
+        }
+        // boundary outputs must be contiguous buffers for the download
+        for (TensorId id : boundaryOutputs) {
+            auto it = views_.find(id);
+            if (it == views_.end()) fail(Status::RuntimeError, "boundary output was not produced");
+            if (!it->second.contiguous()) it->second = materialize(it->second, "boundary output");
+        }
+        planned_ = true;
+    }
+
+    void CudaSegment::launch(const Step &s) {
+        switch (s.kind) {
+            case Step::Gemm:
+                check(ctx_, vkc_gemm(ctx_, s.a, s.b, s.bias, s.c, s.d, s.M, s.N, s.K, s.batch, s.sa, s.sb, s.sd, s.lda, s.ldb, s.ldd, s.bLayout, s.epilogue,
+                                     dtype_, nullptr), "vkc_gemm");
+                break;
+            case Step::Attn:
+                check(ctx_, vkc_attn_prefill(ctx_, s.a, s.b, s.c, s.d, s.B, s.Hq, s.Hkv, s.Sq, s.Skv, s.D, s.qs, s.ks, s.vs, s.os, s.scale, 0, s.mask,
+                                             nullptr, dtype_, nullptr), "vkc_attn_prefill");
+                break;
+            case Step::LayerNorm:
+                check(ctx_, vkc_layernorm(ctx_, s.a, s.gamma, s.beta, s.d, s.rows, s.norm, s.eps, dtype_, nullptr), "vkc_layernorm");
+                break;
+            case Step::Softmax: check(ctx_, vkc_softmax(ctx_, s.a, s.d, s.rows, s.norm, dtype_, nullptr), "vkc_softmax"); break;
+            case Step::Pointwise:
+                check(ctx_, vkc_pointwise(ctx_, s.a, s.d, s.shape.data(), (int) s.shape.size(), (int) s.pwSteps.size() / 4, s.pwSteps.data(),
+                                          s.pwParams.data(), (int) s.operands.size(), s.operands.data(), s.opStrides.data(), dtype_, nullptr),
+                      "vkc_pointwise");
+                break;
+            case Step::Copy:
+                check(ctx_, vkc_strided_copy(ctx_, s.a, s.d, s.shape.data(), s.inStrides.data(), (int) s.shape.size(), s.inOffset, dtype_, nullptr),
+                      "vkc_strided_copy");
+                break;
+        }
+    }
+
+    void CudaSegment::run(ExecContext &ctx) {
+        if (!planned_) plan();
+        const Graph &g = *g_;
+        // boundary inputs: host fp32 -> device storage precision (conversion on the device)
+        for (TensorId id : boundaryInputs) {
+            if (initIds_.count(id)) continue; // uploaded in compileSegment; the pool holds no host data for it
+            RtTensor &rt = ctx.t(id);
+            if (!rt.hostValid) fail(Status::RuntimeError, "boundary input " + g.desc(id).name + " has no host data");
+            const View &v = views_.at(id);
+            if (rt.elems() != prod(v.shape)) fail(Status::InvalidArgument, "boundary input " + g.desc(id).name + " has an unexpected size");
+            check(ctx_, vkc_upload(ctx_, ptrOf(v), dtype_, rt.host.bytes.data(), VKC_F32, rt.elems(), nullptr), "vkc_upload");
+        }
+        if (graph_) {
+            check(ctx_, vkc_graph_launch(ctx_, graph_), "vkc_graph_launch");
+        } else if (useGraph_ && runs_ == 1) {
+            // the eager first run sized every scratch buffer; record the launch list once and replay it from now on
+            check(ctx_, vkc_graph_begin(ctx_), "vkc_graph_begin");
+            try {
+                for (const Step &s : steps_) launch(s);
+            } catch (...) {
+                vkc_graph *tmp = nullptr;
+                vkc_graph_end(ctx_, &tmp);
+                if (tmp) vkc_graph_destroy(ctx_, tmp);
+                throw;
+            }
+            check(ctx_, vkc_graph_end(ctx_, &graph_), "vkc_graph_end");
+            check(ctx_, vkc_graph_launch(ctx_, graph_), "vkc_graph_launch");
+        } else {
+            for (const Step &s : steps_) launch(s);
+        }
+        // boundary outputs: device -> host fp32
+        for (TensorId id : boundaryOutputs) {
+            RtTensor   &rt = ctx.t(id);
+            const View &v  = views_.at(id);
+            rt.shape = g.desc(id).shape;
+            rt.dtype = DType::Float32;
+            rt.allocHost();
+            check(ctx_, vkc_download(ctx_, rt.host.bytes.data(), VKC_F32, ptrOf(v), dtype_, rt.elems(), nullptr), "vkc_download");
+            rt.hostValid   = true;
+            rt.deviceValid = false;
+        }
+        check(ctx_, vkc_sync(ctx_, nullptr), "vkc_sync");
+        ++runs_;
+    }
+
+} // namespace vknn

@@ -35,6 +35,7 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 PREFILL = dict(B=4, H=16, S=8192, D=128, causal=False, dtype="bf16", seed=1005)
 DECODE = dict(B=32, Hq=32, Hkv=8, L=8192, D=128, seed=1005)
 ENCODER = dict(B=8, T=197, d=768, H=12, dmlp=3072, seed=1002)
+LAYERNORM = dict(rows=131072, norm=1024, seed=1003)  # config 3's width; enough rows that the pass streams from HBM
 
 
 def peaks():
@@ -255,14 +256,38 @@ def bench_encoder(ctx, cfg, steps, warmup, rank, world):
     xs = [torch.randn(Bl, T, d, generator=g, device="cuda", dtype=torch.float32).half() for _ in range(ns)]
     ys = [torch.empty_like(x) for x in xs]
 
+    # the layer is 7 short launches: replay it as a CUDA graph (what the C++ segment does), one graph per input set
+    for i in range(ns):
+        layer.forward(xs[i], out=ys[i])
+    torch.cuda.synchronize()
+    graphs = [layer.capture(xs[i], ys[i]) for i in range(ns)]
+
     def step(i):
-        layer.forward(xs[i % ns], out=ys[i % ns])
+        graphs[i % ns].replay()
 
     total_ms, per_ms = timed_loop(step, steps, warmup, world)
     ctx.sync()
     tokens_all = B * T
     return dict(total_ms=total_ms, tok_s=tokens_all * steps / (total_ms * 1e-3), flops_step_all=layer.flops(Bl, T) * world,
                 tflops=layer.flops(Bl, T) * world * steps / (total_ms * 1e-3) / 1e12)
+
+
+def bench_layernorm(ctx, cfg, steps, warmup, rank, world):
+    import torch
+    rows, norm = cfg["rows"], cfg["norm"]
+    g = torch.Generator(device="cuda").manual_seed(cfg["seed"] + rank)
+    xs = [torch.randn(rows, norm, generator=g, device="cuda", dtype=torch.float32).half() for _ in range(2)]
+    ys = [torch.empty_like(x) for x in xs]
+    gamma = torch.ones(norm, device="cuda")
+    beta = torch.zeros(norm, device="cuda")
+
+    def step(i):
+        ctx.layernorm(xs[i % 2], gamma, beta, ys[i % 2], 1e-6)
+
+    total_ms, per_ms = timed_loop(step, steps, warmup, world)
+    ctx.sync()
+    bytes_rank = rows * norm * 2 * 2 + 8 * norm
+    return dict(total_ms=total_ms, per_launch_ms=per_ms, bytes_step_rank=bytes_rank, gbs=bytes_rank * world * steps / (total_ms * 1e-3) / 1e9)
 
 
 # ---------------------------------------------------------------------------------------------------------------
@@ -351,7 +376,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="prefill", choices=["prefill", "decode", "encoder"])
+    ap.add_argument("--workload", default="prefill", choices=["prefill", "decode", "encoder", "layernorm"])
     ap.add_argument("--seq", type=int, default=None, help="prefill sequence length (default 8192)")
     ap.add_argument("--causal", action="store_true")
     ap.add_argument("--no-extra", action="store_true", help="skip the decode / encoder / sweep extras")
@@ -378,6 +403,8 @@ def main():
         r = bench_prefill(ctx, cfg, args.steps, args.warmup, rank, world)
     elif args.workload == "decode":
         r = bench_decode(ctx, DECODE, args.steps, args.warmup, rank, world)
+    elif args.workload == "layernorm":
+        r = bench_layernorm(ctx, LAYERNORM, args.steps, args.warmup, rank, world)
     else:
         r = bench_encoder(ctx, ENCODER, args.steps, args.warmup, rank, world)
     clocks = sampler.stop() if rank == 0 else None
@@ -394,6 +421,11 @@ def main():
             e = bench_encoder(ctx, ENCODER, k, 3, rank, world)
             extra["encoder"] = {"workload": "config 2: ViT-B/16 layer, batch 8 x 197 tokens, fp16, batch sharded", "tok/s": e["tok_s"],
                                 "TFLOP/s": e["tflops"], "ms_per_step": e["total_ms"] / k}
+        if args.workload != "layernorm":
+            ln = bench_layernorm(ctx, LAYERNORM, k, 3, rank, world)
+            extra["layernorm"] = {"workload": "LayerNorm over 131072 rows x 1024 (config 3 width), fp16, replicated per rank",
+                                  "GB/s_per_gpu": ln["bytes_step_rank"] / (ln["per_launch_ms"] * 1e-3) / 1e9,
+                                  "frac_hbm_per_gpu": ln["bytes_step_rank"] / (ln["per_launch_ms"] * 1e-3) / 1e9 / pk["hbm_gbs"]}
         if args.workload == "prefill" and not args.seq:
             sweep = {}
             for S, causal in ((4096, False), (16384, False), (8192, True), (16384, True)):
@@ -428,6 +460,13 @@ def main():
                      "gpu_launches": 2 * args.steps,
                      "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": achieved / pk["hbm_gbs"],
                                   "peak_source": pk["_source"], "traffic": None, "kernel": "attn_decode_kernel (+combine)"}})
+    elif args.workload == "layernorm":
+        achieved = r["bytes_step_rank"] / (r["per_launch_ms"] * 1e-3) / 1e9
+        line.update({"metric": "layernorm GB/s", "value": r["gbs"], "unit": "GB/s", "ms_per_step": r["total_ms"] / args.steps, "scaling": "weak",
+                     "dtype": "f16", "config": {"workload": "LayerNorm 131072 rows x 1024, fp16", "parallelism": "replicated"},
+                     "gpu_launches": args.steps,
+                     "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": achieved / pk["hbm_gbs"],
+                                  "peak_source": pk["_source"], "traffic": None, "kernel": "layernorm_kernel"}})
     else:
         line.update({"metric": "encoder tok/s", "value": r["tok_s"], "unit": "tok/s", "ms_per_step": r["total_ms"] / args.steps, "scaling": "strong",
                      "dtype": "f16", "config": {"workload": "config 2: ViT-B/16 encoder layer batch 8 x 197", "parallelism": "batch sharded"},

@@ -98,6 +98,28 @@ __device__ __forceinline__ float vkc_gelu_erf(float h) {
     return t * 0.5f;
 }
 
+// GELU for 16-bit storage: same operation order, with erf evaluated by the Abramowitz-Stegun 7.1.26 rational form
+// (absolute error < 1.5e-7, far below half-precision output rounding). The reference's own device kernels evaluate
+// Erf with this formula (shaders/common.glsl:44-50); fp32 storage keeps erff.
+__device__ __forceinline__ float vkc_erf_as(float x) {
+    const float ax = fabsf(x);
+    const float t  = __fdividef(1.0f, fmaf(0.3275911f, ax, 1.0f));
+    float       p  = fmaf(1.061405429f, t, -1.453152027f);
+    p              = fmaf(p, t, 1.421413741f);
+    p              = fmaf(p, t, -0.284496736f);
+    p              = fmaf(p, t, 0.254829592f);
+    const float e  = __expf(-ax * ax);
+    const float r  = fmaf(-p * t, e, 1.0f);
+    return copysignf(r, x);
+}
+__device__ __forceinline__ float vkc_gelu_erf_fast(float h) {
+    float t = h * 0.70710678118f;
+    t       = vkc_erf_as(t);
+    t       = t + 1.0f;
+    t       = t * h;
+    return t * 0.5f;
+}
+
 #define VKC_DISPATCH_DTYPE(dtype, T, ...)                  \
     switch (dtype) {                                       \
         case VKC_F32: { using T = float; __VA_ARGS__; } break;         \

@@ -2,9 +2,11 @@
 //
 //   D[b,m,n] = epi( sum_k A[b,m,k] * B[b,k,n] ),  A/B/D in f16 or bf16, fp32 accumulation in tensor memory.
 //
-// One CTA computes one 128 x BN output tile. Warp roles:
+// One CTA computes one 128 x BN output tile (BN in {64, 128, 192, 256}, chosen per problem to fill the 148 SMs in
+// as few waves as possible). Small and medium problems run two CTAs per SM so that one CTA's epilogue overlaps the
+// other's main loop. Warp roles:
 //   warp 0   : TMA producer  — one elected lane streams 128x64 A tiles and BNx64 B tiles (128-byte swizzle)
-//              through a 4-stage shared-memory ring, completion on per-stage "full" mbarriers;
+//              through a multi-stage shared-memory ring, completion on per-stage "full" mbarriers;
 //   warp 1   : MMA issuer    — owns the tensor-memory allocation; one elected lane issues four
 //              tcgen05.mma (M=128, N=BN, K=16) per stage and commits the stage's "empty" mbarrier;
 //   warps 2-5: epilogue      — each warp owns the 32 TMEM lanes (= output rows) it may address, reads the
@@ -15,12 +17,12 @@
 #include "common.cuh"
 #include "ptx.cuh"
 #include "tensormap.cuh"
+#include <cmath>
 
 namespace {
 
-    constexpr int BM      = 128;
-    constexpr int BK      = 64;
-    constexpr int kStages = 4;
+    constexpr int BM       = 128;
+    constexpr int BK       = 64;
     constexpr int kThreads = 192;
 
     struct GemmParams {
@@ -34,10 +36,13 @@ namespace {
         int         *dev_err;
     };
 
-    template <int BN> constexpr int smem_bytes() { return kStages * (BM * BK * 2 + BN * BK * 2) + 1024 /*align*/ + 256 /*barriers*/; }
+    template <int BN, int kStages> constexpr int smem_bytes() {
+        return kStages * (BM * BK * 2 + BN * BK * 2) + 1024 /*align*/ + 256 /*barriers*/ + BN * 4 /*bias*/;
+    }
+    __host__ __device__ constexpr int tmem_cols(int bn) { return bn <= 32 ? 32 : bn <= 64 ? 64 : bn <= 128 ? 128 : 256; } // power of two >= BN
 
-    template <int BN, typename T, bool B_KN>
-    __global__ void __launch_bounds__(kThreads, 1)
+    template <int BN, int kStages, int kCtasPerSm, typename T, bool B_KN>
+    __global__ void __launch_bounds__(kThreads, kCtasPerSm)
         gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmParams p) {
         constexpr uint32_t A_BYTES = BM * BK * 2;
         constexpr uint32_t B_BYTES = BN * BK * 2;
@@ -54,6 +59,7 @@ namespace {
         volatile int  *ctl   = (volatile int *) (gbase + kStages * (A_BYTES + B_BYTES) + 8 * (2 * kStages + 1));
         // ctl[0] = tmem base (written by tcgen05.alloc), ctl[1] = abort flag
         const uint32_t sSlot = sBar + 8 * (2 * kStages + 1);
+        float         *sbias = (float *) (gbase + kStages * (A_BYTES + B_BYTES) + 256); // BN floats
 
         const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
         const int m0 = blockIdx.x * BM, n0 = blockIdx.y * BN, bz = blockIdx.z;
@@ -71,8 +77,11 @@ namespace {
             ptx::prefetch_tmap(&tmB);
         }
         if (warp == 1) {
-            ptx::tmem_alloc(sSlot, BN);
+            ptx::tmem_alloc(sSlot, tmem_cols(BN));
             ptx::tmem_relinquish();
+        }
+        if (warp >= 2 && (p.epilogue & VKC_EPI_BIAS)) {
+            for (int j = threadIdx.x - 64; j < BN; j += kThreads - 64) sbias[j] = (int64_t) n0 + j < p.N ? __ldg(p.bias + n0 + j) : 0.f;
         }
         ptx::tc_fence_before();
         __syncthreads();
@@ -141,12 +150,14 @@ namespace {
                         const bool full = nb + 32 <= p.N;
                         if (p.epilogue & VKC_EPI_BIAS) {
 #pragma unroll
-                            for (int j = 0; j < 32; ++j)
-                                if (full || nb + j < p.N) v[j] += __ldg(p.bias + nb + j);
+                            for (int j = 0; j < 32; j += 4) {
+                                const float4 bv = *reinterpret_cast<const float4 *>(sbias + c * 32 + j);
+                                v[j] += bv.x, v[j + 1] += bv.y, v[j + 2] += bv.z, v[j + 3] += bv.w;
+                            }
                         }
                         if (p.epilogue & VKC_EPI_GELU_ERF) {
 #pragma unroll
-                            for (int j = 0; j < 32; ++j) v[j] = vkc_gelu_erf(v[j]);
+                            for (int j = 0; j < 32; ++j) v[j] = vkc_gelu_erf_fast(v[j]);
                         }
                         if (full && vec_ok) {
 #pragma unroll
@@ -182,13 +193,14 @@ namespace {
         }
         ptx::tc_fence_before();
         __syncthreads();
-        if (warp == 1) ptx::tmem_dealloc(tmem, BN);
+        if (warp == 1) ptx::tmem_dealloc(tmem, tmem_cols(BN));
     }
 
-    template <int BN, typename T, bool B_KN>
+    template <int BN, int kStages, int kCtasPerSm, typename T, bool B_KN>
     int launch(vkc_ctx *ctx, const CUtensorMap &tmA, const CUtensorMap &tmB, const GemmParams &p, int64_t batch, cudaStream_t st) {
-        auto        kern = gemm_tcgen05_kernel<BN, T, B_KN>;
-        constexpr int smem = smem_bytes<BN>();
+        auto          kern = gemm_tcgen05_kernel<BN, kStages, kCtasPerSm, T, B_KN>;
+        constexpr int smem = smem_bytes<BN, kStages>();
+        static_assert(smem * kCtasPerSm <= 227 * 1024, "shared memory budget");
         static bool attr_set = false; // per template instance; one device per process
         if (!attr_set) {
             VKC_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
@@ -197,6 +209,31 @@ namespace {
         dim3 grid((unsigned) ((p.M + BM - 1) / BM), (unsigned) ((p.N + BN - 1) / BN), (unsigned) batch);
         kern<<<grid, kThreads, smem, st>>>(tmA, tmB, p);
         return vkc_post_launch(ctx, "gemm_tcgen05");
+    }
+
+    // Tile width: fewest waves over the SMs first, then the least padded work. Wide tiles re-read A less often.
+    struct TileChoice {
+        int bn;
+        bool two_ctas;
+    };
+    TileChoice choose_tile(int64_t M, int64_t N, int64_t batch, int sms) {
+        const int64_t mt = (M + BM - 1) / BM;
+        TileChoice    best {128, true};
+        double        best_cost = 1e300;
+        const int     cands[4]  = {256, 192, 128, 64};
+        for (int bn : cands) {
+            const int64_t tiles = mt * ((N + bn - 1) / bn) * batch;
+            // two co-resident CTAs share one tensor pipe: model a slot as half an SM
+            const double waves = std::ceil((double) tiles / (2.0 * sms));
+            const double cost  = waves * (bn + 48.0); // per-tile time ~ width + fixed prologue/epilogue
+            if (cost < best_cost - 1e-9) {
+                best_cost = cost;
+                best      = {bn, true};
+            }
+        }
+        // very large problems: the deep 4-stage 256-wide pipeline, one CTA per SM
+        if (mt * ((N + 255) / 256) * batch >= 4 * (int64_t) sms) best = {256, false};
+        return best;
     }
 
 } // namespace
@@ -212,7 +249,8 @@ int vkc_gemm_tcgen05(vkc_ctx *ctx, const void *A, const void *B, const float *bi
     if (M > INT32_MAX || N > INT32_MAX || K > INT32_MAX || batch > 65535) return vkc_fail(ctx, VKC_ERR_UNSUPPORTED, "gemm_tcgen05: extent too large");
 
     const bool a_bcast = stride_a == 0 || batch == 1, b_bcast = stride_b == 0 || batch == 1;
-    const int  BN      = (N > 128 && ((M + BM - 1) / BM) * ((N + 255) / 256) * batch >= (int64_t) ctx->sm_count) ? 256 : 128;
+    const TileChoice tc = choose_tile(M, N, batch, ctx->sm_count);
+    const int        BN = tc.bn;
 
     CUtensorMap tmA, tmB;
     {
@@ -249,9 +287,20 @@ int vkc_gemm_tcgen05(vkc_ctx *ctx, const void *A, const void *B, const float *bi
     p.b_bcast  = b_bcast;
     p.dev_err  = ctx->dev_err;
 
-#define VKC_GEMM_LAUNCH(BN_, T_)                                                                    \
-    (b_layout == VKC_B_KN ? launch<BN_, T_, true>(ctx, tmA, tmB, p, batch, st) : launch<BN_, T_, false>(ctx, tmA, tmB, p, batch, st))
-    if (dtype == VKC_F16) return BN == 256 ? VKC_GEMM_LAUNCH(256, __half) : VKC_GEMM_LAUNCH(128, __half);
-    return BN == 256 ? VKC_GEMM_LAUNCH(256, __nv_bfloat16) : VKC_GEMM_LAUNCH(128, __nv_bfloat16);
+#define VKC_GEMM_LAUNCH(BN_, ST_, C_, T_)                                                                       \
+    (b_layout == VKC_B_KN ? launch<BN_, ST_, C_, T_, true>(ctx, tmA, tmB, p, batch, st) : launch<BN_, ST_, C_, T_, false>(ctx, tmA, tmB, p, batch, st))
+#define VKC_GEMM_BY_TILE(T_)                                                         \
+    do {                                                                             \
+        if (!tc.two_ctas) return VKC_GEMM_LAUNCH(256, 4, 1, T_);                     \
+        switch (BN) {                                                                \
+            case 256: return VKC_GEMM_LAUNCH(256, 2, 2, T_);                         \
+            case 192: return VKC_GEMM_LAUNCH(192, 2, 2, T_);                         \
+            case 128: return VKC_GEMM_LAUNCH(128, 3, 2, T_);                         \
+            default: return VKC_GEMM_LAUNCH(64, 4, 2, T_);                           \
+        }                                                                            \
+    } while (0)
+    if (dtype == VKC_F16) VKC_GEMM_BY_TILE(__half);
+    VKC_GEMM_BY_TILE(__nv_bfloat16);
+#undef VKC_GEMM_BY_TILE
 #undef VKC_GEMM_LAUNCH
 }

@@ -3,6 +3,7 @@
 // form as the CPU reference) and the normalise/scale/shift pass, warp-shuffle reductions only. Each row is
 // read once and written once: algorithmic bytes = rows * norm * 2 * sizeof(T) + 8 * norm.
 #include "common.cuh"
+#include <algorithm>
 
 namespace {
 
@@ -16,62 +17,93 @@ namespace {
         return v;
     }
 
-    // CHUNKS = 16-byte vectors per lane kept in registers; covers norm <= 32 * CHUNKS * (16/sizeof(T)).
+    // CHUNKS = 16-byte vectors per lane; covers norm <= 32 * CHUNKS * (16/sizeof(T)). Warps are persistent: each
+    // walks rows warp_id, warp_id + total_warps, ... with its slice of gamma / beta held in registers for the whole
+    // kernel, so the only memory instructions per row are the 128-bit loads of x and stores of y. For 16-bit
+    // storage the next row's loads are issued before the current row is reduced (more bytes in flight per SM).
     template <typename T, int CHUNKS>
-    __global__ void __launch_bounds__(256) layernorm_kernel(const T *__restrict__ X, const float *__restrict__ gamma,
-                                                            const float *__restrict__ beta, T *__restrict__ Y, int64_t rows, int norm, float eps) {
-        constexpr int VN   = Vec16<T>::N;
-        const int     lane = threadIdx.x & 31;
-        const int64_t row  = (int64_t) blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    __global__ void __launch_bounds__(256, 2) layernorm_kernel(const T *__restrict__ X, const float *__restrict__ gamma,
+                                                               const float *__restrict__ beta, T *__restrict__ Y, int64_t rows, int norm, float eps) {
+        constexpr int  VN       = Vec16<T>::N;
+        constexpr bool PREFETCH = sizeof(T) == 2;
+        const int      lane     = threadIdx.x & 31;
+        const int64_t  nwarps   = (int64_t) gridDim.x * (blockDim.x >> 5);
+        int64_t        row      = (int64_t) blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
         if (row >= rows) return;
-        const T *xr = X + row * norm;
-        T       *yr = Y + row * norm;
-        float    v[CHUNKS][VN];
-        float    s = 0.f;
+
+        float g[CHUNKS][VN], bt[CHUNKS][VN];
 #pragma unroll
         for (int c = 0; c < CHUNKS; ++c) {
             const int e = (c * 32 + lane) * VN;
-            if (e < norm) {
-                const uint4 raw = *reinterpret_cast<const uint4 *>(xr + e);
-                const T    *t   = reinterpret_cast<const T *>(&raw);
+#pragma unroll
+            for (int j = 0; j < VN; j += 4) {
+                float4 gv = make_float4(0.f, 0.f, 0.f, 0.f), bv = gv;
+                if (e < norm) {
+                    gv = __ldg(reinterpret_cast<const float4 *>(gamma + e + j));
+                    if (beta) bv = __ldg(reinterpret_cast<const float4 *>(beta + e + j));
+                }
+                g[c][j] = gv.x, g[c][j + 1] = gv.y, g[c][j + 2] = gv.z, g[c][j + 3] = gv.w;
+                bt[c][j] = bv.x, bt[c][j + 1] = bv.y, bt[c][j + 2] = bv.z, bt[c][j + 3] = bv.w;
+            }
+        }
+        auto load_row = [&](int64_t r, uint4(&raw)[CHUNKS]) {
+#pragma unroll
+            for (int c = 0; c < CHUNKS; ++c) {
+                const int e = (c * 32 + lane) * VN;
+                raw[c]      = (e < norm && r < rows) ? *reinterpret_cast<const uint4 *>(X + r * norm + e) : make_uint4(0, 0, 0, 0);
+            }
+        };
+        uint4 cur[CHUNKS], nxt[CHUNKS];
+        load_row(row, cur);
+        for (; row < rows; row += nwarps) {
+            if (PREFETCH) load_row(row + nwarps, nxt);
+            float v[CHUNKS][VN];
+            float s = 0.f;
+#pragma unroll
+            for (int c = 0; c < CHUNKS; ++c) {
+                const T *t = reinterpret_cast<const T *>(&cur[c]);
 #pragma unroll
                 for (int j = 0; j < VN; ++j) {
                     v[c][j] = St<T>::ld(t + j);
                     s += v[c][j];
                 }
+            }
+            const float mean = warp_sum(s) / (float) norm;
+            float       q    = 0.f;
+#pragma unroll
+            for (int c = 0; c < CHUNKS; ++c) {
+                const int e = (c * 32 + lane) * VN;
+                if (e < norm) {
+#pragma unroll
+                    for (int j = 0; j < VN; ++j) {
+                        const float d = v[c][j] - mean;
+                        q += d * d;
+                    }
+                }
+            }
+            const float var = warp_sum(q) / (float) norm;
+            const float inv = 1.0f / sqrtf(var + eps);
+            T          *yr  = Y + row * norm;
+#pragma unroll
+            for (int c = 0; c < CHUNKS; ++c) {
+                const int e = (c * 32 + lane) * VN;
+                if (e < norm) {
+                    uint4 out;
+                    T    *t = reinterpret_cast<T *>(&out);
+#pragma unroll
+                    for (int j = 0; j < VN; ++j) {
+                        float o = (v[c][j] - mean) * inv * g[c][j];
+                        if (beta) o += bt[c][j];
+                        St<T>::st(t + j, o);
+                    }
+                    *reinterpret_cast<uint4 *>(yr + e) = out;
+                }
+            }
+            if (PREFETCH) {
+#pragma unroll
+                for (int c = 0; c < CHUNKS; ++c) cur[c] = nxt[c];
             } else {
-#pragma unroll
-                for (int j = 0; j < VN; ++j) v[c][j] = 0.f;
-            }
-        }
-        const float mean = warp_sum(s) / (float) norm;
-        float       q    = 0.f;
-#pragma unroll
-        for (int c = 0; c < CHUNKS; ++c) {
-            const int e = (c * 32 + lane) * VN;
-            if (e < norm) {
-#pragma unroll
-                for (int j = 0; j < VN; ++j) {
-                    const float d = v[c][j] - mean;
-                    q += d * d;
-                }
-            }
-        }
-        const float var = warp_sum(q) / (float) norm;
-        const float inv = 1.0f / sqrtf(var + eps);
-#pragma unroll
-        for (int c = 0; c < CHUNKS; ++c) {
-            const int e = (c * 32 + lane) * VN;
-            if (e < norm) {
-                uint4 out;
-                T    *t = reinterpret_cast<T *>(&out);
-#pragma unroll
-                for (int j = 0; j < VN; ++j) {
-                    float o = (v[c][j] - mean) * inv * __ldg(gamma + e + j);
-                    if (beta) o += __ldg(beta + e + j);
-                    St<T>::st(t + j, o);
-                }
-                *reinterpret_cast<uint4 *>(yr + e) = out;
+                load_row(row + nwarps, cur);
             }
         }
     }
@@ -107,10 +139,12 @@ namespace {
         constexpr int VN      = Vec16<T>::N;
         const int     wpb     = 8; // warps (= rows) per block
         const int64_t blocks  = (rows + wpb - 1) / wpb;
-        const bool    aligned = (norm % VN == 0) && (((uintptr_t) X & 15) == 0) && (((uintptr_t) Y & 15) == 0);
+        const int64_t pblocks = std::min<int64_t>(blocks, (int64_t) ctx->sm_count * 2); // persistent warps: two 256-thread blocks per SM
+        const bool    aligned = (norm % VN == 0) && (((uintptr_t) X & 15) == 0) && (((uintptr_t) Y & 15) == 0) && (((uintptr_t) gamma & 15) == 0) &&
+                                (!beta || ((uintptr_t) beta & 15) == 0);
         const int64_t chunks  = (norm + 32 * VN - 1) / (32 * VN);
         if (blocks > INT32_MAX) return vkc_fail(ctx, VKC_ERR_UNSUPPORTED, "layernorm: too many rows");
-#define VKC_LN(C) layernorm_kernel<T, C><<<(unsigned) blocks, wpb * 32, 0, st>>>((const T *) X, gamma, beta, (T *) Y, rows, (int) norm, eps)
+#define VKC_LN(C) layernorm_kernel<T, C><<<(unsigned) pblocks, wpb * 32, 0, st>>>((const T *) X, gamma, beta, (T *) Y, rows, (int) norm, eps)
         if (aligned && chunks <= 8) {
             switch (chunks) {
                 case 1: VKC_LN(1); break;

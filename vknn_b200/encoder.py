@@ -61,6 +61,14 @@ class EncoderLayer:
 
     LAUNCHES_PER_FORWARD = 7
 
+    def capture(self, x, out):
+        """Records forward(x, out) into a CUDA graph (the launch list of a segment, replayable with .replay()).
+        One eager call must have run before so that every kernel's one-time set-up is done."""
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            self.forward(x, out=out)
+        return g
+
     def flops(self, B, T):
         d, dm, H = self.d, self.dmlp, self.H
         M = B * T

@@ -32,6 +32,13 @@ sys.path.insert(0, ROOT)
 L2_BYTES = 126 * 1024 * 1024
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
+# DRAM traffic per unit from the ncu captures summarised under profiles/ (dram__bytes_read.sum + dram__bytes_write.sum):
+#   prefill: 113.87 MB for 4 x 16 x 2048 (batch, head, query row) units  (profiles/attn_prefill_bf16_d128_seq2048.md);
+#            K/V re-reads are served by L2, so DRAM traffic grows with the number of row units;
+#   decode : 1.0266 x the algorithmic bytes of the launch                 (profiles/attn_decode_f16_config5.md).
+NCU_PREFILL_DRAM_BYTES_PER_ROW_UNIT = 868.8
+NCU_DECODE_DRAM_OVER_ALGORITHMIC = 1.0266
+
 PREFILL = dict(B=4, H=16, S=8192, D=128, causal=False, dtype="bf16", seed=1005)
 DECODE = dict(B=32, Hq=32, Hkv=8, L=8192, D=128, seed=1005)
 ENCODER = dict(B=8, T=197, d=768, H=12, dmlp=3072, seed=1002)
@@ -448,7 +455,9 @@ def main():
             "dtype": "bf16", "config": headline_config(cfg, world), "gpu_launches": int(r["launches"]),
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
                          "peak_source": "%s bf16 burst (cuBLAS)" % pk["_source"], "frac_of_sustained": achieved / pk["bf16_tflops_sustained"],
-                         "traffic": None, "kernel": "attn_prefill_kernel", "flops_per_launch": r["flops_step_rank"]},
+                         "traffic": NCU_PREFILL_DRAM_BYTES_PER_ROW_UNIT * cfg["B"] * (cfg["H"] // world) * cfg["S"],
+                         "traffic_note": "ncu capture at seq 2048 scaled by (batch, head, query row) units; algorithmic bytes %d" % r["bytes_step_rank"],
+                         "kernel": "attn_prefill_kernel", "flops_per_launch": r["flops_step_rank"]},
         })
         if "e2e_ms_per_step" in r:
             line["e2e"] = {"value": r["flops_step_all"] / (r["e2e_ms_per_step"] * 1e-3) / 1e12, "unit": "TFLOP/s",
@@ -459,7 +468,8 @@ def main():
                      "dtype": "f16", "config": {"workload": "config 5: GQA decode batch 32, 32q/8kv heads, D=128, cache 8192", "parallelism": "batch sharded"},
                      "gpu_launches": 2 * args.steps,
                      "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": achieved / pk["hbm_gbs"],
-                                  "peak_source": pk["_source"], "traffic": None, "kernel": "attn_decode_kernel (+combine)"}})
+                                  "peak_source": pk["_source"], "traffic": NCU_DECODE_DRAM_OVER_ALGORITHMIC * r["bytes_step_rank"],
+                                  "kernel": "attn_decode_tc_kernel (+ attn_decode_combine_kernel)"}})
     elif args.workload == "layernorm":
         achieved = r["bytes_step_rank"] / (r["per_launch_ms"] * 1e-3) / 1e9
         line.update({"metric": "layernorm GB/s", "value": r["gbs"], "unit": "GB/s", "ms_per_step": r["total_ms"] / args.steps, "scaling": "weak",

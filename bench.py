@@ -4,8 +4,9 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload prefill|decode|encoder] [--impl ours|reference]
 
 One JSON line on stdout (rank 0). The headline workload is the long-sequence prefill attention of the
-baseline's config 4 (batch 4 x 16 heads, head_dim 128, bf16, seq 8192, no mask), sharded by head across the
-ranks (strong scaling, no data-path collective: outputs stay sharded). A step is one pass of the fused
+baseline's config 4 (batch 4 x 16 heads, head_dim 128, bf16, seq 8192, no mask). The path shards into independent
+(batch, head) units, so at N GPUs every rank runs the named configuration's units (N x 16 heads in total, sharded
+by head; weak scaling, no data-path collective: outputs stay sharded). A step is one pass of the fused
 attention kernel over the rank's heads. `value` is measured with inputs resident in HBM; `e2e` is the same
 metric through the C-ABI with pinned HOST buffers (vkc_upload -> kernel -> vkc_download inside the timed
 region). `extra` carries the other parts of the baseline's composite metric (decode GB/s, encoder tok/s, the
@@ -42,6 +43,7 @@ NCU_DECODE_DRAM_OVER_ALGORITHMIC = 1.0266
 PREFILL = dict(B=4, H=16, S=8192, D=128, causal=False, dtype="bf16", seed=1005)
 DECODE = dict(B=32, Hq=32, Hkv=8, L=8192, D=128, seed=1005)
 ENCODER = dict(B=8, T=197, d=768, H=12, dmlp=3072, seed=1002)
+STACK = dict(B=1, T=2738, d=1024, H=16, dmlp=4096, layers=24, seed=1003)  # config 3
 LAYERNORM = dict(rows=131072, norm=1024, seed=1003)  # config 3's width; enough rows that the pass streams from HBM
 
 
@@ -169,8 +171,7 @@ def n_sets_for(bytes_per_step):
 def bench_prefill(ctx, cfg, steps, warmup, rank, world, e2e_steps=3):
     import torch
     B, H, S, D = cfg["B"], cfg["H"], cfg["S"], cfg["D"]
-    assert H % world == 0, "heads must divide across ranks"
-    Hl = H // world
+    Hl = H  # weak scaling: every rank owns the named configuration's 16 heads (world x 16 heads in total)
     dt = torch.bfloat16
     g = torch.Generator(device="cuda").manual_seed(cfg["seed"] + rank)
     bytes_step = 4 * B * Hl * S * D * 2
@@ -219,11 +220,9 @@ def bench_prefill(ctx, cfg, steps, warmup, rank, world, e2e_steps=3):
 def bench_decode(ctx, cfg, steps, warmup, rank, world):
     import torch
     B, Hq, Hkv, L, D = cfg["B"], cfg["Hq"], cfg["Hkv"], cfg["L"], cfg["D"]
-    assert B % world == 0
-    Bl = B // world
-    rng = np.random.default_rng(cfg["seed"])
-    kv_len_all = rng.integers(1024, L + 1, B).astype(np.int32)
-    kv_len = kv_len_all[rank * Bl:(rank + 1) * Bl]
+    Bl = B  # weak scaling: every rank serves the named configuration's 32 sequences (world x 32 in total)
+    rng = np.random.default_rng(cfg["seed"] + 1000 * rank)
+    kv_len = rng.integers(1024, L + 1, B).astype(np.int32)
     g = torch.Generator(device="cuda").manual_seed(cfg["seed"] + rank)
     dt = torch.float16
     bytes_alg = int(2 * Hkv * int(kv_len.sum()) * D * 2 + 2 * Bl * Hq * D * 2)
@@ -238,11 +237,25 @@ def bench_decode(ctx, cfg, steps, warmup, rank, world):
     ws = torch.empty(ctx.attn_decode_workspace_bytes(Bl, Hq, Hkv, L, D), dtype=torch.uint8, device="cuda")
     scale = 1.0 / float(np.sqrt(D))
 
-    def step(i):
+    def eager(i):
         q, k, v, o = sets[i % ns]
         ctx.attn_decode(q, k, v, o, scale, kv_len=lens, workspace=ws)
 
-    total_ms, per_ms = timed_loop(step, steps, warmup, world)
+    # a decode step is one short launch: replay it from a CUDA graph, as a serving loop would
+    for i in range(ns):
+        eager(i)
+    torch.cuda.synchronize()
+    graphs = []
+    for i in range(ns):
+        g_ = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g_):
+            eager(i)
+        graphs.append(g_)
+
+    def step(i):
+        graphs[i % ns].replay()
+
+    total_ms, per_ms = timed_loop(eager if os.environ.get("VKNN_BENCH_EAGER") == "1" else step, steps, warmup, world)
     ctx.sync()
     bytes_all = sum_over_ranks(bytes_alg, world)
     return dict(total_ms=total_ms, per_launch_ms=per_ms, bytes_step_all=bytes_all, bytes_step_rank=bytes_alg, gbs=bytes_all * steps / (total_ms * 1e-3) / 1e9)
@@ -253,8 +266,7 @@ def bench_encoder(ctx, cfg, steps, warmup, rank, world):
     from vknn_b200.synthetic import encoder_weights
     from vknn_b200.encoder import EncoderLayer
     B, T, d, H, dm = cfg["B"], cfg["T"], cfg["d"], cfg["H"], cfg["dmlp"]
-    assert B % world == 0
-    Bl = B // world
+    Bl = B  # weak scaling: every rank runs the named batch of 8 images (world x 8 in total), weights replicated
     w = encoder_weights(np.random.default_rng(cfg["seed"]), d, dm)
     layer = EncoderLayer(ctx, w, H, dtype=torch.float16)
     g = torch.Generator(device="cuda").manual_seed(cfg["seed"] + rank)
@@ -274,9 +286,42 @@ def bench_encoder(ctx, cfg, steps, warmup, rank, world):
 
     total_ms, per_ms = timed_loop(step, steps, warmup, world)
     ctx.sync()
-    tokens_all = B * T
+    tokens_all = B * T * world
     return dict(total_ms=total_ms, tok_s=tokens_all * steps / (total_ms * 1e-3), flops_step_all=layer.flops(Bl, T) * world,
                 tflops=layer.flops(Bl, T) * world * steps / (total_ms * 1e-3) / 1e12)
+
+
+def bench_stack(ctx, cfg, steps, warmup, rank, world):
+    """Config 3: 24 pre-LN blocks, d=1024, 16 heads, MLP 4096, 2738 tokens, batch 1. Weak scaling runs one sequence
+    per rank (graph replay); with more than one rank the same stack is also run head-sharded on ONE shared sequence
+    (QKV + attention sharded by head, one NCCL all-gather per layer at the attention output, the rest replicated)."""
+    import torch
+    from vknn_b200.encoder import EncoderStack
+    from vknn_b200.synthetic import encoder_weights
+    T, d, H, dm, L = cfg["T"], cfg["d"], cfg["H"], cfg["dmlp"], cfg["layers"]
+    rng = np.random.default_rng(cfg["seed"])
+    stack = EncoderStack(ctx, [encoder_weights(rng, d, dm) for _ in range(L)], H, dtype=torch.float16)
+    g = torch.Generator(device="cuda").manual_seed(cfg["seed"] + rank)
+    x = torch.randn(1, T, d, generator=g, device="cuda", dtype=torch.float32).half()
+    stack.forward(x)
+    torch.cuda.synchronize()
+    graph, _ = stack.capture(x)
+    total_ms, _ = timed_loop(lambda i: graph.replay(), steps, warmup, world)
+    ctx.sync()
+    res = dict(tok_s=T * world * steps / (total_ms * 1e-3), ms_per_forward=total_ms / steps,
+               tflops=stack.flops(1, T) * world * steps / (total_ms * 1e-3) / 1e12)
+    if world > 1:
+        import torch.distributed as dist
+        stack.shard_heads(rank, world)
+        xs = x.clone()
+        dist.broadcast(xs, 0)
+        stack.forward_head_sharded(xs)
+        t_ms, _ = timed_loop(lambda i: stack.forward_head_sharded(xs), steps, warmup, world)
+        ctx.sync()
+        res["head_sharded_one_sequence"] = dict(tok_s=T * steps / (t_ms * 1e-3), ms_per_forward=t_ms / steps,
+                                                note="strong scaling of a single sequence: QKV+attention sharded by head, all-gather per layer, "
+                                                     "out-projection and MLP replicated (about half of the flops do not shard)")
+    return res
 
 
 def bench_layernorm(ctx, cfg, steps, warmup, rank, world):
@@ -359,7 +404,7 @@ def run_reference(args):
     value = flops_proc * cores / (step_ms * 1e-3) / 1e12
     line = {
         "impl": "reference", "metric": "attention TFLOP/s", "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": step_ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+        "warmup": args.warmup, "ms_per_step": step_ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic", "config": headline_config(cfg, args.gpus),
         "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": cores, "kind": kind,
                          "sample": "per step: %d processes x %d query rows x %d keys of (batch, head) units, D=%d, fp32, reference CPU backend" %
@@ -373,7 +418,8 @@ def run_reference(args):
 def headline_config(cfg, n):
     return {"workload": "config 4: prefill attention, batch %d x %d heads, head_dim %d, seq %d, %s, %s" %
                         (cfg["B"], cfg["H"], cfg["D"], cfg["S"], cfg["dtype"], "causal" if cfg["causal"] else "no mask"),
-            "parallelism": "heads sharded over %d GPU(s), outputs left sharded (no collective)" % n,
+            "parallelism": "weak scaling: %d rank(s) x the named configuration (%d heads in total, sharded by head, 16 per GPU), "
+                           "outputs left sharded (no collective)" % (n, 16 * n),
             "l2": "inputs cycle through sets larger than L2 (126 MB) between timed steps"}
 
 
@@ -421,13 +467,16 @@ def main():
         k = min(args.steps, 10)
         if args.workload != "decode":
             d = bench_decode(ctx, DECODE, k, 3, rank, world)
-            extra["decode"] = {"workload": "config 5: GQA decode, batch 32, 32q/8kv heads, D=128, fp16 cache 8192, kv_len U[1024,8192], batch sharded",
+            extra["decode"] = {"workload": "config 5: GQA decode, batch 32, 32q/8kv heads, D=128, fp16 cache 8192, kv_len U[1024,8192], per rank (weak scaling, batch sharded)",
                                "GB/s": d["gbs"], "frac_hbm_per_gpu": d["bytes_step_rank"] / (d["per_launch_ms"] * 1e-3) / 1e9 / pk["hbm_gbs"],
                                "ms_per_step": d["total_ms"] / k}
         if args.workload != "encoder":
             e = bench_encoder(ctx, ENCODER, k, 3, rank, world)
-            extra["encoder"] = {"workload": "config 2: ViT-B/16 layer, batch 8 x 197 tokens, fp16, batch sharded", "tok/s": e["tok_s"],
+            extra["encoder"] = {"workload": "config 2: ViT-B/16 layer, batch 8 x 197 tokens per rank, fp16 (weak scaling, batch sharded)", "tok/s": e["tok_s"],
                                 "TFLOP/s": e["tflops"], "ms_per_step": e["total_ms"] / k}
+        if args.workload == "prefill" and not args.seq:
+            st = bench_stack(ctx, STACK, max(3, k // 3), 3, rank, world)
+            extra["encoder_stack"] = dict(st, workload="config 3: 24 layers, d=1024, 16 heads, MLP 4096, 2738 tokens, batch 1 per rank, fp16")
         if args.workload != "layernorm":
             ln = bench_layernorm(ctx, LAYERNORM, k, 3, rank, world)
             extra["layernorm"] = {"workload": "LayerNorm over 131072 rows x 1024 (config 3 width), fp16, replicated per rank",
@@ -451,11 +500,11 @@ def main():
         achieved = r["flops_step_rank"] / (r["per_launch_ms"] * 1e-3) / 1e12
         peak = pk["bf16_tflops"]
         line.update({
-            "metric": "attention TFLOP/s", "value": value, "unit": "TFLOP/s", "ms_per_step": r["total_ms"] / args.steps, "scaling": "strong",
+            "metric": "attention TFLOP/s", "value": value, "unit": "TFLOP/s", "ms_per_step": r["total_ms"] / args.steps, "scaling": "weak",
             "dtype": "bf16", "config": headline_config(cfg, world), "gpu_launches": int(r["launches"]),
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
                          "peak_source": "%s bf16 burst (cuBLAS)" % pk["_source"], "frac_of_sustained": achieved / pk["bf16_tflops_sustained"],
-                         "traffic": NCU_PREFILL_DRAM_BYTES_PER_ROW_UNIT * cfg["B"] * (cfg["H"] // world) * cfg["S"],
+                         "traffic": NCU_PREFILL_DRAM_BYTES_PER_ROW_UNIT * cfg["B"] * cfg["H"] * cfg["S"],
                          "traffic_note": "ncu capture at seq 2048 scaled by (batch, head, query row) units; algorithmic bytes %d" % r["bytes_step_rank"],
                          "kernel": "attn_prefill_kernel", "flops_per_launch": r["flops_step_rank"]},
         })
@@ -464,8 +513,8 @@ def main():
                            "h2d_bytes_per_step": int(r["h2d"]), "d2h_bytes_per_step": int(r["d2h"]), "ms_per_step": r["e2e_ms_per_step"]}
     elif args.workload == "decode":
         achieved = r["bytes_step_rank"] / (r["per_launch_ms"] * 1e-3) / 1e9
-        line.update({"metric": "decode GB/s", "value": r["gbs"], "unit": "GB/s", "ms_per_step": r["total_ms"] / args.steps, "scaling": "strong",
-                     "dtype": "f16", "config": {"workload": "config 5: GQA decode batch 32, 32q/8kv heads, D=128, cache 8192", "parallelism": "batch sharded"},
+        line.update({"metric": "decode GB/s", "value": r["gbs"], "unit": "GB/s", "ms_per_step": r["total_ms"] / args.steps, "scaling": "weak",
+                     "dtype": "f16", "config": {"workload": "config 5: GQA decode batch 32, 32q/8kv heads, D=128, cache 8192", "parallelism": "weak scaling: the named configuration per rank, sharded by batch, no collective"},
                      "gpu_launches": 2 * args.steps,
                      "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": achieved / pk["hbm_gbs"],
                                   "peak_source": pk["_source"], "traffic": NCU_DECODE_DRAM_OVER_ALGORITHMIC * r["bytes_step_rank"],
@@ -478,8 +527,8 @@ def main():
                      "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": achieved / pk["hbm_gbs"],
                                   "peak_source": pk["_source"], "traffic": None, "kernel": "layernorm_kernel"}})
     else:
-        line.update({"metric": "encoder tok/s", "value": r["tok_s"], "unit": "tok/s", "ms_per_step": r["total_ms"] / args.steps, "scaling": "strong",
-                     "dtype": "f16", "config": {"workload": "config 2: ViT-B/16 encoder layer batch 8 x 197", "parallelism": "batch sharded"},
+        line.update({"metric": "encoder tok/s", "value": r["tok_s"], "unit": "tok/s", "ms_per_step": r["total_ms"] / args.steps, "scaling": "weak",
+                     "dtype": "f16", "config": {"workload": "config 2: ViT-B/16 encoder layer batch 8 x 197", "parallelism": "weak scaling: the named configuration per rank, sharded by batch, no collective"},
                      "gpu_launches": 7 * args.steps,
                      "roofline": {"bound": "tensor", "achieved": r["tflops"] / world, "peak": pk["bf16_tflops"], "unit": "TFLOP/s",
                                   "frac": r["tflops"] / world / pk["bf16_tflops"], "peak_source": pk["_source"], "traffic": None}})

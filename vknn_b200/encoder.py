@@ -69,7 +69,90 @@ class EncoderLayer:
             self.forward(x, out=out)
         return g
 
+    # ---- head-sharded form for a single long sequence (batch 1 cannot be sharded by batch) ---------------------
+    def shard_heads(self, rank, world):
+        """Keeps only this rank's heads of the QKV projection (columns of Wqkv / entries of bqkv). Attention then runs
+        on H/world heads per rank; the attention output is all-gathered before the replicated out-projection + MLP."""
+        assert self.H % world == 0
+        H, d = self.H, self.d
+        D, Hl = d // H, H // world
+        wq = self.w["wqkv"].view(d, 3, H, D)[:, :, rank * Hl:(rank + 1) * Hl].reshape(d, 3 * Hl * D).contiguous()
+        bq = self.w["bqkv"].view(3, H, D)[:, rank * Hl:(rank + 1) * Hl].reshape(3 * Hl * D).contiguous()
+        self.w["wqkv_local"], self.w["bqkv_local"] = wq, bq
+        self.rank, self.world, self.Hl = rank, world, Hl
+
+    def forward_head_sharded(self, x, group=None, out=None):
+        """x [1,T,d] replicated on every rank. One NCCL all-gather per layer, at the attention-output boundary."""
+        import torch.distributed as dist
+        c, w = self.ctx, self.w
+        B, T, d = x.shape
+        assert B == 1
+        H, Hl, D, world = self.H, self.Hl, d // self.H, self.world
+        dl = Hl * D
+        buf = self._buffers(B, T, x.device)
+        key = ("hs", T)
+        if key not in self._buf:
+            mk = lambda *s_: torch.empty(*s_, dtype=self.dtype, device=x.device)  # noqa: E731
+            self._buf[key] = dict(qkv=mk(T, 3, Hl, D), att=mk(T, Hl, D), gathered=mk(world, T, dl))
+        hs = self._buf[key]
+        x2 = x.view(T, d)
+        y = out if out is not None else torch.empty_like(x)
+        c.layernorm(x2, w["ln1_g"], w["ln1_b"], buf["h"], self.eps)
+        c.gemm(buf["h"], w["wqkv_local"], hs["qkv"].view(T, 3 * dl), bias=w["bqkv_local"])
+        q, k, v = (hs["qkv"][:, i].permute(1, 0, 2).unsqueeze(0) for i in range(3))      # [1,Hl,T,D] views
+        c.attn_prefill(q, k, v, hs["att"].permute(1, 0, 2).unsqueeze(0), scale=1.0 / (D ** 0.5))
+        dist.all_gather_into_tensor(hs["gathered"].view(world * T, dl), hs["att"].view(T, dl), group=group)
+        # [world,T,dl] -> [T, world*dl]: heads are contiguous per rank, so this restores the merged-head layout
+        att_full = buf["att"].view(T, d)
+        c.strided_copy(hs["gathered"], att_full, [T, world, dl], [dl, T * dl, 1])
+        c.gemm(att_full, w["wo"], buf["x1"], bias=w["bo"], residual=x2)
+        c.layernorm(buf["x1"], w["ln2_g"], w["ln2_b"], buf["h"], self.eps)
+        c.gemm(buf["h"], w["w1"], buf["f"], bias=w["b1"], epilogue=capi.EPI_BIAS | capi.EPI_GELU_ERF)
+        c.gemm(buf["f"], w["w2"], y.view(T, d), bias=w["b2"], residual=buf["x1"])
+        return y
+
     def flops(self, B, T):
         d, dm, H = self.d, self.dmlp, self.H
         M = B * T
         return 2 * M * d * 3 * d + 4 * B * H * T * T * (d // H) + 2 * M * d * d + 4 * M * d * dm
+
+
+class EncoderStack:
+    """A stack of identical-shape pre-LN blocks with independent weights (the 24-layer encoder of config 3)."""
+
+    def __init__(self, ctx, weights_per_layer, heads, dtype=torch.float16, eps=1e-6):
+        self.layers = [EncoderLayer(ctx, w, heads, dtype=dtype, eps=eps) for w in weights_per_layer]
+        self._pp = {}
+
+    def _pingpong(self, x):
+        key = tuple(x.shape)
+        if key not in self._pp:
+            self._pp[key] = [torch.empty_like(x), torch.empty_like(x)]
+        return self._pp[key]
+
+    def forward(self, x):
+        """Ping-pongs between two internal buffers; the caller's input is left untouched."""
+        cur, bufs = x, self._pingpong(x)
+        for i, layer in enumerate(self.layers):
+            cur = layer.forward(cur, out=bufs[i % 2])
+        return cur
+
+    def shard_heads(self, rank, world):
+        for layer in self.layers:
+            layer.shard_heads(rank, world)
+
+    def forward_head_sharded(self, x, group=None):
+        cur, bufs = x, self._pingpong(x)
+        for i, layer in enumerate(self.layers):
+            cur = layer.forward_head_sharded(cur, group=group, out=bufs[i % 2])
+        return cur
+
+    def capture(self, x):
+        """CUDA graph of forward(x); returns (graph, output tensor). Needs one eager forward beforehand."""
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            y = self.forward(x)
+        return g, y
+
+    def flops(self, B, T):
+        return sum(layer.flops(B, T) for layer in self.layers)

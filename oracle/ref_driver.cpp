@@ -7,7 +7,7 @@
 // oracle/_ref/ only. When the Makefile also links the CUDA backend plug-in, `--backend cuda`
 // plans the same graph on the plug-in through the reference's own planner.
 //
-// The graph is described by a line-oriented text spec (written by tests/graphspec.py):
+// The graph is described by a line-oriented text spec (written by oracle/vko.py, class RefGraph):
 //
 //   tensor <name> <input|init|inter|output> <f32|i64> <rank> <d0> <d1> ...
 //   node <OpType> <name> subop=<int> in=<a,b,c> out=<y> [fusedbias=<name>] [i:<k>=<int>] [f:<k>=<float>]
@@ -17,12 +17,16 @@
 // in <data.bin>; outputs are written concatenated in graph-output order to <out.bin> as fp32.
 //
 // usage: vknn_ref_driver <spec.txt> <data.bin> <out.bin> [--backend cpu|cuda] [--precision low|high]
-//                        [--iters N] [--warmup W] [--quiet]
+//                        [--iters N] [--warmup W] [--quiet] [--vxm-fp16 <file.vxm>]
+// --vxm-fp16 takes the route of the reference's model compiler (convert/compile.cpp:36-96): run the standard
+// passes, store every fp32 initializer as fp16, write the ".vxm" file, and create the Session from that file
+// (Session::createFromVxm, include/vknn/session_class.h:24), so the backend sees fp16 weights.
 // prints one line of JSON: node list after the reference's passes, per-node backend, median run ms.
 //
 // Reference interfaces used: Session::create(Graph&&, Config) include/vknn/session_class.h:26,
 // Session::run session_class.h:36, Graph/Node/TensorDesc include/vknn/graph.h:12-39, node.h:14-32,
 // and the graph-in-code idiom of tests/test_ops.cpp:42-107.
+#include "import/passes.h"
 #include "vknn/graph.h"
 #include "vknn/session.h"
 #include <algorithm>
@@ -88,6 +92,7 @@ int main(int argc, char **argv) {
     std::string backend = "cpu", precision = "high";
     int         iters = 1, warmup = 0;
     bool        quiet = false;
+    std::string vxmPath;
     for (int i = 4; i < argc; ++i) {
         std::string a = argv[i];
         if (a == "--backend" && i + 1 < argc) backend = argv[++i];
@@ -95,6 +100,7 @@ int main(int argc, char **argv) {
         else if (a == "--iters" && i + 1 < argc) iters = std::atoi(argv[++i]);
         else if (a == "--warmup" && i + 1 < argc) warmup = std::atoi(argv[++i]);
         else if (a == "--quiet") quiet = true;
+        else if (a == "--vxm-fp16" && i + 1 < argc) vxmPath = argv[++i];
     }
 
     std::ifstream spec(specPath);
@@ -213,7 +219,25 @@ int main(int argc, char **argv) {
 
     std::unique_ptr<Session> sess;
     try {
-        sess = Session::create(std::move(g), cfg);
+        if (!vxmPath.empty()) {
+            runStandardPasses(g, PassOptions {});
+            for (auto &kv : g.initializers) {
+                TensorDesc &d = g.tensors[kv.first];
+                if (d.dtype != DType::Float32) continue;
+                const int64_t        n   = numElements(d.shape);
+                const float         *src = kv.second.f32();
+                std::vector<uint8_t> half((size_t) n * 2);
+                for (int64_t i = 0; i < n; ++i) reinterpret_cast<fp16_t *>(half.data())[i] = floatToHalf(src[i]);
+                kv.second.bytes = std::move(half);
+                d.dtype         = DType::Float16;
+            }
+            if (!saveGraphBin(g, vxmPath)) {
+                std::printf("{\"ok\": false, \"error\": \"saveGraphBin failed\"}\n");
+                return 1;
+            }
+            sess = Session::createFromVxm(vxmPath, cfg);
+        } else
+            sess = Session::create(std::move(g), cfg);
     } catch (const std::exception &e) {
         std::printf("{\"ok\": false, \"error\": \"plan: %s\"}\n", e.what());
         return 1;

@@ -66,3 +66,19 @@ def test_unsupported_node_is_refused_not_run_on_cpu():
     with pytest.raises(RuntimeError) as e:
         g.run(backend="cuda")
     assert "plan" in str(e.value) or "null" in str(e.value)
+
+
+def test_fp16_vxm_weights_are_consumed_directly():
+    """The on-disk format on the weight side of the path: an encoder layer compiled to a ".vxm" with fp16 initializers
+    (what the reference's vknn_compile --fp16 writes) and loaded with Session::createFromVxm on both backends."""
+    rng = np.random.default_rng(11)
+    w = encoder_weights(rng, 256, 512, bias_scale=0.01)
+    x = rng.standard_normal((2, 130, 256)).astype(np.float32)
+    (ref,), info_cpu = vko.encoder_layer_graph(x, w, 4).run(backend="cpu", vxm_fp16=True)
+    (got,), info = vko.encoder_layer_graph(x, w, 4).run(backend="cuda", precision="low", vxm_fp16=True, iters=2)
+    assert all(n[1] == CUDA_KIND for n in info["nodes"])
+    assert_low(got, ref, "fp16 .vxm through the plug-in")
+    # and the file route gives the CPU backend the same answer as fp16-rounded weights fed directly
+    w16 = {k: (v.astype(np.float16).astype(np.float32)) for k, v in w.items()}
+    (ref2,), _ = vko.encoder_layer_graph(x, w16, 4).run(backend="cpu")
+    assert np.abs(ref - ref2).max() <= 2e-3

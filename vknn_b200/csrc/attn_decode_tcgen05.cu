@@ -485,12 +485,8 @@ int vkc_attn_decode_tcgen05(vkc_ctx *ctx, const void *Q, const void *Kc, const v
     const int     grid      = (int) (max_items < ctx->sm_count ? max_items : ctx->sm_count);
 #define VKC_DTC(T_)                                                                                                  \
     do {                                                                                                             \
-        auto        kern_ = attn_decode_tc_kernel<T_>;                                                               \
-        static bool attr_ = false;                                                                                   \
-        if (!attr_) {                                                                                                \
-            VKC_CUDA(ctx, cudaFuncSetAttribute(kern_, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) kSmemTotal)); \
-            attr_ = true;                                                                                            \
-        }                                                                                                            \
+        auto kern_ = attn_decode_tc_kernel<T_>;                                                                      \
+        if (int rc_ = vkc_configure_smem(ctx, kern_, (int) kSmemTotal)) return rc_;                                  \
         kern_<<<grid, kThreads, kSmemTotal, st>>>(tq, tk, tv, p);                                                    \
     } while (0)
     if (dtype == VKC_F16)

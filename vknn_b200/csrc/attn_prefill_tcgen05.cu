@@ -351,11 +351,7 @@ namespace {
     int launch_attn(vkc_ctx *ctx, const CUtensorMap &tq, const CUtensorMap &tk, const CUtensorMap &tv, const AttnParams &p, int64_t B, cudaStream_t st) {
         auto          kern = attn_prefill_kernel<T, D>;
         constexpr int smem = (int) Smem<D, 2, 2>::total;
-        static bool   attr_set = false;
-        if (!attr_set) {
-            VKC_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-            attr_set = true;
-        }
+        if (int rc = vkc_configure_smem(ctx, kern, smem)) return rc;
         dim3 grid((unsigned) ((p.Sq + kQTiles * BM - 1) / (kQTiles * BM)), (unsigned) p.Hq, (unsigned) B);
         kern<<<grid, kThreads, smem, st>>>(tq, tk, tv, p);
         return vkc_post_launch(ctx, "attn_prefill_tcgen05");

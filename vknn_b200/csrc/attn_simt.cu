@@ -115,7 +115,9 @@ namespace {
     int launch_attn_simt(vkc_ctx *ctx, const void *Q, const void *K, const void *V, void *O, const AttnSimtParams &p, cudaStream_t st) {
         const size_t smem = sizeof(float) * (size_t) (kKeys * (p.D + 1) + kKeys * p.D + kRows * p.D);
         auto         kern = attn_simt_kernel<T>;
-        if (smem > 48 * 1024) VKC_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
+        if (smem > 48 * 1024) {
+            if (int rc = vkc_configure_smem(ctx, kern, 100 * 1024)) return rc;
+        }
         dim3 grid((unsigned) ((p.Sq + kRows - 1) / kRows), (unsigned) p.Hq, (unsigned) p.B);
         kern<<<grid, kRows * 32, smem, st>>>((const T *) Q, (const T *) K, (const T *) V, (T *) O, p);
         return vkc_post_launch(ctx, "attn_simt");

@@ -8,6 +8,7 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <set>
 #include <string>
 #include <type_traits>
 
@@ -33,6 +34,8 @@ struct vkc_ctx {
     std::string  err;
     // driver entry point for tensor-map encoding (resolved once; no link-time dependency on libcuda)
     void *encode_tiled = nullptr;
+    // kernels whose dynamic shared-memory limit has been raised on this context's device
+    std::set<const void *> smem_configured;
 };
 
 struct vkc_graph {
@@ -73,6 +76,15 @@ inline int vkc_post_launch(vkc_ctx *ctx, const char *what) {
 inline size_t vkc_dtype_size(int dt) { return dt == VKC_F32 || dt == VKC_I32 ? 4 : 2; }
 
 int vkc_ensure_scratch(vkc_ctx *ctx, size_t bytes);
+
+// Opt a kernel into more than 48 KB of dynamic shared memory, once per context (the attribute is per device).
+template <typename Kernel> inline int vkc_configure_smem(vkc_ctx *ctx, Kernel kern, int bytes) {
+    const void *key = reinterpret_cast<const void *>(kern);
+    if (ctx->smem_configured.count(key)) return VKC_OK;
+    VKC_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+    ctx->smem_configured.insert(key);
+    return VKC_OK;
+}
 
 // ---- storage-type traits ------------------------------------------------------------------------------------
 template <typename T> struct St;

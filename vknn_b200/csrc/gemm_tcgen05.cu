@@ -201,11 +201,7 @@ namespace {
         auto          kern = gemm_tcgen05_kernel<BN, kStages, kCtasPerSm, T, B_KN>;
         constexpr int smem = smem_bytes<BN, kStages>();
         static_assert(smem * kCtasPerSm <= 227 * 1024, "shared memory budget");
-        static bool attr_set = false; // per template instance; one device per process
-        if (!attr_set) {
-            VKC_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-            attr_set = true;
-        }
+        if (int rc = vkc_configure_smem(ctx, kern, smem)) return rc;
         dim3 grid((unsigned) ((p.M + BM - 1) / BM), (unsigned) ((p.N + BN - 1) / BN), (unsigned) batch);
         kern<<<grid, kThreads, smem, st>>>(tmA, tmB, p);
         return vkc_post_launch(ctx, "gemm_tcgen05");

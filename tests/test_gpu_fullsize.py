@@ -1,0 +1,123 @@
+"""Full-size configurations (where the CPU oracle would take minutes to hours) checked through size-independent
+properties, and edge cases of the C-ABI (empty tensors, single rows)."""
+import numpy as np
+import pytest
+import torch
+
+import vknn_b200
+from oracle import vko
+from tests.util import assert_low, metrics
+
+pytestmark = pytest.mark.gpu
+
+
+def test_prefill_config4_s16384_properties(ctx):
+    """Config 4 at its largest point: batch 4 x 16 heads, seq 16384, head_dim 128, bf16, causal on and off.
+    (1) softmax rows sum to one: with V = const the output is that constant; (2) a key that dominates every row
+    (huge q.k) makes the output equal to its V row; (3) the tensor-core kernel agrees with the fp32-pipe kernel on
+    two full-length heads; (4) the oracle agrees on a few query rows of one head."""
+    B, H, S, D = 4, 16, 16384, 128
+    g = torch.Generator(device="cuda").manual_seed(1006)
+    q = torch.randn(B, H, S, D, generator=g, device="cuda").bfloat16()
+    k = torch.randn(B, H, S, D, generator=g, device="cuda").bfloat16()
+    v = torch.full((B, H, S, D), 0.75, device="cuda", dtype=torch.bfloat16)
+    o = torch.empty_like(q)
+    scale = D ** -0.5
+    for causal in (False, True):
+        ctx.attn_prefill(q, k, v, o, scale, causal=causal)
+        ctx.sync()
+        assert float((o.float() - 0.75).abs().max()) <= 4e-3, causal
+    # (2) key 0 is visible to every row also under the causal mask
+    v = torch.randn(B, H, S, D, generator=g, device="cuda").bfloat16()
+    q2, k2 = q.clone(), k.clone()
+    q2[..., 0] = 60.0              # dimension 0 carries the dominant term
+    k2[..., 0] = 0
+    k2[:, :, 0] = 0
+    k2[:, :, 0, 0] = 60.0          # q.k for key 0 = 3600 * scale, far above every other score
+    ctx.attn_prefill(q2, k2, v, o, scale, causal=True)
+    ctx.sync()
+    assert float((o.float() - v[:, :, :1].float()).abs().max()) <= 1e-2
+    # (3) two heads, full length, against the SIMT kernel
+    qs, ks, vs = q[:1, :2].contiguous(), k[:1, :2].contiguous(), v[:1, :2].contiguous()
+    o_tc, o_simt = torch.empty_like(qs), torch.empty_like(qs)
+    ctx.attn_prefill(qs, ks, vs, o_tc, scale, causal=True)
+    ctx.set_impl(vknn_b200.IMPL_SIMT)
+    try:
+        ctx.attn_prefill(qs, ks, vs, o_simt, scale, causal=True)
+        ctx.sync()
+    finally:
+        ctx.set_impl(vknn_b200.IMPL_AUTO)
+    assert_low(o_tc.float().cpu().numpy(), o_simt.float().cpu().numpy(), "tc vs simt at S=16384")
+    # (4) oracle on 8 query rows of one head (non-causal rows are independent)
+    rows = [0, 1, 127, 128, 8191, 8192, 16000, 16383]
+    qh = q[0, 0, rows].float().cpu().numpy()[None, None]
+    ref = vko.attention(qh, k[0, 0].float().cpu().numpy()[None, None], v[0, 0].float().cpu().numpy()[None, None], scale)
+    ctx.attn_prefill(q, k, v, o, scale, causal=False)
+    ctx.sync()
+    assert_low(o[0, 0, rows].float().cpu().numpy(), ref[0, 0], "oracle rows at S=16384")
+
+
+def test_decode_config5_full_size_properties(ctx):
+    """Config 5 at full size (batch 32, 32 q / 8 kv heads, cache 8192, valid lengths 1024..8192): constant V gives the
+    constant; the tensor-core and SIMT forms agree; the oracle agrees on the two shortest sequences."""
+    B, Hq, Hkv, L, D = 32, 32, 8, 8192, 128
+    g = torch.Generator(device="cuda").manual_seed(1005)
+    q = torch.randn(B, Hq, D, generator=g, device="cuda").half()
+    k = torch.randn(B, Hkv, L, D, generator=g, device="cuda").half()
+    v = torch.randn(B, Hkv, L, D, generator=g, device="cuda").half()
+    lens_np = np.random.default_rng(1005).integers(1024, L + 1, B).astype(np.int32)
+    lens = torch.from_numpy(lens_np).cuda()
+    o = torch.empty_like(q)
+    vc = torch.full_like(v, -1.5)
+    ctx.attn_decode(q, k, vc, o, D ** -0.5, kv_len=lens)
+    ctx.sync()
+    assert float((o.float() + 1.5).abs().max()) <= 2e-3
+    o_tc, o_simt = torch.empty_like(q), torch.empty_like(q)
+    ctx.attn_decode(q, k, v, o_tc, D ** -0.5, kv_len=lens)
+    ctx.set_impl(vknn_b200.IMPL_SIMT)
+    try:
+        ctx.attn_decode(q, k, v, o_simt, D ** -0.5, kv_len=lens)
+        ctx.sync()
+    finally:
+        ctx.set_impl(vknn_b200.IMPL_AUTO)
+    assert_low(o_tc.float().cpu().numpy(), o_simt.float().cpu().numpy(), "decode tc vs simt")
+    for b in np.argsort(lens_np)[:2]:
+        ref = vko.attention(q[b:b + 1, :, None].float().cpu().numpy(), k[b:b + 1].float().cpu().numpy(), v[b:b + 1].float().cpu().numpy(),
+                            D ** -0.5, kv_len=lens_np[b:b + 1])[:, :, 0]
+        assert_low(o_tc[b:b + 1].float().cpu().numpy(), ref, "decode oracle seq %d" % b)
+
+
+def test_encoder_stack_config3_width_two_layers(ctx):
+    """Config 3 geometry (d=1024, 16 heads, MLP 4096, 2738 tokens = 2 views x 37 x 37) on 2 of its 24 layers, against
+    the oracle's encoder block applied twice (about 20 s of CPU on 8 cores)."""
+    from vknn_b200.encoder import EncoderStack
+    from vknn_b200.synthetic import encoder_weights
+    rng = np.random.default_rng(1003)
+    ws = [encoder_weights(rng, 1024, 4096) for _ in range(2)]
+    x = rng.standard_normal((1, 2738, 1024)).astype(np.float32).astype(np.float16).astype(np.float32)
+    ref = x
+    for w in ws:
+        ref = vko.encoder_layer(ref, w, 16, eps=1e-6)
+    y = EncoderStack(ctx, ws, 16).forward(torch.from_numpy(x).cuda().half())
+    ctx.sync()
+    m = metrics(y.float().cpu().numpy(), ref)
+    # activations grow to O(10) over the residual stream; the storage rounding of fp16 at that magnitude is 8e-3
+    assert m["cosine"] >= 0.9999 and m["max_abs"] <= 4e-2, m
+
+
+def test_empty_and_degenerate_inputs(ctx):
+    """Empty tensors are accepted and launch nothing; a single query row / single key work."""
+    n0 = ctx.launch_count()
+    z = torch.zeros(0, 4, 16, 64, dtype=torch.float16, device="cuda")
+    ctx.attn_prefill(z, z, z, z, 0.125)
+    e = torch.zeros(0, 64, dtype=torch.float16, device="cuda")
+    ctx.layernorm(e, torch.ones(64, device="cuda"), None, e, 1e-5)
+    ctx.gemm(torch.zeros(0, 64, dtype=torch.float16, device="cuda"), torch.zeros(64, 32, dtype=torch.float16, device="cuda"),
+             torch.zeros(0, 32, dtype=torch.float16, device="cuda"))
+    assert ctx.launch_count() == n0
+    q = torch.randn(1, 1, 1, 64, device="cuda").half()
+    kv = torch.randn(1, 1, 1, 64, device="cuda").half()
+    o = torch.zeros_like(q)
+    ctx.attn_prefill(q, kv, kv, o, 0.125)
+    ctx.sync()
+    assert torch.equal(o, kv)  # one key: softmax = 1, output = V

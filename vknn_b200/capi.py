@@ -57,6 +57,7 @@ def load_library():
     L.vkc_sync.argtypes = [vp, vp]
     L.vkc_launch_count.argtypes = [vp]
     L.vkc_launch_count.restype = i64
+    L.vkc_debug_timeline.argtypes = [vp, C.POINTER(C.c_longlong)]
     L.vkc_alloc.argtypes = [vp, sz, C.POINTER(vp)]
     L.vkc_free.argtypes = [vp, vp]
     L.vkc_upload.argtypes = [vp, vp, i32, vp, i32, i64, vp]

@@ -96,6 +96,7 @@ int vkc_ctx_destroy(vkc_ctx *ctx) {
     if (ctx->stream) cudaStreamSynchronize(ctx->stream);
     if (ctx->scratch) cudaFree(ctx->scratch);
     if (ctx->dev_err) cudaFree(ctx->dev_err);
+    if (ctx->timeline) cudaFree(ctx->timeline);
     if (ctx->ev0) cudaEventDestroy(ctx->ev0);
     if (ctx->ev1) cudaEventDestroy(ctx->ev1);
     if (ctx->stream) cudaStreamDestroy(ctx->stream);
@@ -126,6 +127,17 @@ int vkc_sync(vkc_ctx *ctx, vkc_stream stream) {
 }
 
 int64_t vkc_launch_count(const vkc_ctx *ctx) { return ctx ? ctx->launches : 0; }
+
+// Development aid: after this call, GEMM launches record clock64 stamps of their first CTA; read them back with a second call.
+int vkc_debug_timeline(vkc_ctx *ctx, long long *host16) {
+    if (!ctx) return VKC_ERR_INVALID;
+    if (!ctx->timeline) {
+        VKC_CUDA(ctx, cudaMalloc(&ctx->timeline, 16 * sizeof(long long)));
+        VKC_CUDA(ctx, cudaMemset(ctx->timeline, 0, 16 * sizeof(long long)));
+    }
+    if (host16) VKC_CUDA(ctx, cudaMemcpy(host16, ctx->timeline, 16 * sizeof(long long), cudaMemcpyDeviceToHost));
+    return VKC_OK;
+}
 
 int vkc_alloc(vkc_ctx *ctx, size_t bytes, void **dptr) {
     if (!ctx || !dptr) return VKC_ERR_INVALID;

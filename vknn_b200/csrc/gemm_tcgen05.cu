@@ -18,6 +18,11 @@
 #include "ptx.cuh"
 #include "tensormap.cuh"
 #include <cmath>
+#include <cstdlib>
+
+int vkc_gemm_tcgen05_pair(vkc_ctx *ctx, const void *A, const void *B, const float *bias, const void *residual, void *D, int64_t M, int64_t N,
+                          int64_t K, int64_t batch, int64_t stride_a, int64_t stride_b, int64_t stride_d, int64_t lda, int64_t ldb, int64_t ldd,
+                          int b_layout, int epilogue, int dtype, int bn, cudaStream_t st);
 
 namespace {
 
@@ -34,7 +39,34 @@ namespace {
         int          epilogue;
         int          a_bcast, b_bcast; // batch stride 0: always read batch slice 0
         int         *dev_err;
+        long long   *timeline; // optional clock64 stamps of CTA (0,0,0)
+        int          tma_out;  // D (and the residual) meet the TMA alignment rules: staged, coalesced epilogue
     };
+
+    // GELU(erf) on two values at once with packed fp32 arithmetic and no special-function unit: erf(x), x = h/sqrt(2)
+    // clamped to [-3, 3] (erf(3) = 1 - 2.2e-5), is x * P(x^2) with a degree-8 polynomial fitted to |error| < 2.1e-5,
+    // so GELU is within 5e-5 of the erff form everywhere, far below the rounding of the 16-bit output. The operation
+    // order of the reference chain (erf, +1, *h, *0.5) is kept.
+    __device__ __forceinline__ float2 gelu_erf_pair(float2 h) {
+        const float2 k = make_float2(0.70710678118f, 0.70710678118f);
+        float2       x = ptx::fmul2(h, k);
+        x.x            = fminf(fmaxf(x.x, -3.0f), 3.0f);
+        x.y            = fminf(fmaxf(x.y, -3.0f), 3.0f);
+        const float2 u = ptx::fmul2(x, x);
+        auto         c = [](float v) { return make_float2(v, v); };
+        float2       p = c(3.912539981e-08f);
+        p              = ptx::ffma2(p, u, c(-1.883036475e-06f));
+        p              = ptx::ffma2(p, u, c(4.008835822e-05f));
+        p              = ptx::ffma2(p, u, c(-5.029218737e-04f));
+        p              = ptx::ffma2(p, u, c(4.196857568e-03f));
+        p              = ptx::ffma2(p, u, c(-2.499890141e-02f));
+        p              = ptx::ffma2(p, u, c(1.109308004e-01f));
+        p              = ptx::ffma2(p, u, c(-3.752196431e-01f));
+        p              = ptx::ffma2(p, u, c(1.128250599e+00f));
+        float2 t       = ptx::ffma2(p, x, c(1.0f)); // erf + 1
+        t              = ptx::fmul2(t, h);
+        return ptx::fmul2(t, c(0.5f));
+    }
 
     template <int BN, int kStages> constexpr int smem_bytes() {
         return kStages * (BM * BK * 2 + BN * BK * 2) + 1024 /*align*/ + 256 /*barriers*/ + BN * 4 /*bias*/;
@@ -43,7 +75,9 @@ namespace {
 
     template <int BN, int kStages, int kCtasPerSm, typename T, bool B_KN>
     __global__ void __launch_bounds__(kThreads, kCtasPerSm)
-        gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmParams p) {
+        gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmD,
+                            const __grid_constant__ CUtensorMap tmR, GemmParams p) {
+        static_assert((BN / 64 + (BN % 64 != 0)) * 16384 <= kStages * (BM * BK * 2 + BN * BK * 2), "epilogue staging must fit in the operand ring");
         constexpr uint32_t A_BYTES = BM * BK * 2;
         constexpr uint32_t B_BYTES = BN * BK * 2;
         constexpr bool     kBf16   = std::is_same<T, __nv_bfloat16>::value;
@@ -63,6 +97,8 @@ namespace {
 
         const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
         const int m0 = blockIdx.x * BM, n0 = blockIdx.y * BN, bz = blockIdx.z;
+        long long *tl = (p.timeline && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) ? p.timeline : nullptr;
+        if (tl && threadIdx.x == 0) tl[0] = clock64();
         const int num_kb = (int) ((p.K + BK - 1) / BK);
 
         if (threadIdx.x == 0) {
@@ -71,6 +107,7 @@ namespace {
                 ptx::mbar_init(sBar + 8 * (kStages + s), 1);
             }
             ptx::mbar_init(sBar + 8 * 2 * kStages, 1);
+            for (int w = 0; w < 4; ++w) ptx::mbar_init(sBar + 8 * (2 * kStages + 2 + w), 1); // residual tile landed, per epilogue warp
             ctl[1] = 0;
             ptx::fence_mbar_init();
             ptx::prefetch_tmap(&tmA);
@@ -87,6 +124,7 @@ namespace {
         __syncthreads();
         ptx::tc_fence_after();
         const uint32_t tmem = (uint32_t) ctl[0];
+        if (tl && threadIdx.x == 0) tl[1] = clock64();
 
         if (warp == 0) {
             if (ptx::elect_one()) {
@@ -114,6 +152,7 @@ namespace {
                     const uint32_t ph = (kb / kStages) & 1;
                     ok                = ptx::mbar_wait(sBar + 8 * s, ph, ctl + 1, p.dev_err);
                     if (!ok) break;
+                    if (tl && kb == 0) tl[2] = clock64();
                     ptx::tc_fence_after();
 #pragma unroll
                     for (int k = 0; k < BK / 16; ++k) {
@@ -125,10 +164,12 @@ namespace {
                     ptx::tc_commit(sBar + 8 * (kStages + s)); // frees the stage once these MMAs have read it
                 }
                 if (ok) ptx::tc_commit(sBar + 8 * 2 * kStages); // accumulator complete
+                if (tl) tl[3] = clock64();
             }
         } else {
             const bool ok = ptx::mbar_wait(sBar + 8 * 2 * kStages, 0, ctl + 1, p.dev_err);
             ptx::tc_fence_after();
+            if (tl && threadIdx.x == 64) tl[4] = clock64();
             if (ok) {
                 const int     q   = warp & 3; // the TMEM lane quarter this warp may address
                 const int64_t m   = (int64_t) m0 + q * 32 + lane;
@@ -136,6 +177,78 @@ namespace {
                 const T      *rrow = p.residual ? (const T *) p.residual + (int64_t) bz * p.stride_d + m * p.ldd : nullptr;
                 const bool    vec_ok = (p.ldd % 8 == 0) && (p.stride_d % 8 == 0) && (((uintptr_t) p.D & 15) == 0) &&
                                     (!p.residual || ((uintptr_t) p.residual & 15) == 0);
+                if (p.tma_out) {
+                    // Staged epilogue. The operand ring is idle now; each warp owns 32 output rows and, per 64-column
+                    // slab, a 32 x 128 B staging block there (128-byte swizzle so that 8 lanes writing 8 different rows
+                    // hit different banks). The residual slab is TMA-loaded into the same block, the result is written
+                    // over it and leaves with one TMA store: global traffic is full 128-byte lines both ways.
+                    constexpr int kSlabs = (BN + 63) / 64;
+                    const uint32_t rbar  = sBar + 8 * (2 * kStages + 2 + q);
+                    const int      row0  = m0 + q * 32;
+                    const bool     rows_in = row0 < p.M; // warp-uniform
+                    int            nslab = 0;
+                    for (int sl = 0; sl < kSlabs; ++sl)
+                        if ((int64_t) n0 + sl * 64 < p.N) nslab = sl + 1;
+                    bool rok = true;
+                    if ((p.epilogue & VKC_EPI_RESIDUAL) && rows_in) {
+                        if (lane == 0) {
+                            ptx::mbar_expect_tx(rbar, (uint32_t) nslab * 4096u);
+                            for (int sl = 0; sl < nslab; ++sl) ptx::tma_load_3d(base + sl * 16384 + q * 4096, &tmR, n0 + sl * 64, row0, bz, rbar);
+                        }
+                        rok = ptx::mbar_wait(rbar, 0, ctl + 1, p.dev_err);
+                        rok = __all_sync(0xffffffffu, rok);
+                    }
+#pragma unroll 1
+                    for (int sl = 0; sl < nslab && rok; ++sl) {
+                        uint8_t *blk = gbase + sl * 16384 + q * 4096 + lane * 128;
+#pragma unroll
+                        for (int hf = 0; hf < 2; ++hf) {
+                            uint32_t r[32];
+                            ptx::tmem_ld_x32(tmem + ((uint32_t) (q * 32) << 16) + (uint32_t) (sl * 64 + hf * 32), r);
+                            ptx::tc_wait_ld();
+                            float v[32];
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+                            if (p.epilogue & VKC_EPI_BIAS) {
+#pragma unroll
+                                for (int j = 0; j < 32; j += 4) {
+                                    const float4 bv = *reinterpret_cast<const float4 *>(sbias + sl * 64 + hf * 32 + j);
+                                    v[j] += bv.x, v[j + 1] += bv.y, v[j + 2] += bv.z, v[j + 3] += bv.w;
+                                }
+                            }
+                            if (p.epilogue & VKC_EPI_GELU_ERF) {
+#pragma unroll
+                                for (int j = 0; j < 32; j += 2) {
+                                    const float2 g2 = gelu_erf_pair(make_float2(v[j], v[j + 1]));
+                                    v[j] = g2.x, v[j + 1] = g2.y;
+                                }
+                            }
+#pragma unroll
+                            for (int u = 0; u < 4; ++u) {
+                                uint4 *slot = reinterpret_cast<uint4 *>(blk + (((hf * 4 + u) ^ (lane & 7)) << 4));
+                                if (p.epilogue & VKC_EPI_RESIDUAL) {
+                                    const uint4 rv = *slot;
+                                    const T    *rt = reinterpret_cast<const T *>(&rv);
+#pragma unroll
+                                    for (int j = 0; j < 8; ++j) v[u * 8 + j] += St<T>::ld(rt + j);
+                                }
+                                uint4 ov;
+                                T    *ot = reinterpret_cast<T *>(&ov);
+#pragma unroll
+                                for (int j = 0; j < 8; ++j) St<T>::st(ot + j, v[u * 8 + j]);
+                                *slot = ov;
+                            }
+                        }
+                        ptx::fence_proxy_async();
+                        __syncwarp();
+                        if (lane == 0 && rows_in) {
+                            ptx::tma_store_3d(&tmD, base + sl * 16384 + q * 4096, n0 + sl * 64, row0, bz);
+                            ptx::bulk_commit_group();
+                        }
+                    }
+                    if (lane == 0) ptx::bulk_wait_group_0();
+                    __syncwarp();
+                } else
 #pragma unroll 1
                 for (int c = 0; c < BN / 32; ++c) {
                     const int64_t nb = (int64_t) n0 + c * 32;
@@ -187,6 +300,7 @@ namespace {
                 }
             }
         }
+        if (tl && threadIdx.x == 64) tl[5] = clock64();
         if (ctl[1]) {
             // aborted: give copies still in flight time to land before the CTA releases its shared memory
             for (int i = 0; i < 50; ++i) __nanosleep(20000);
@@ -194,16 +308,18 @@ namespace {
         ptx::tc_fence_before();
         __syncthreads();
         if (warp == 1) ptx::tmem_dealloc(tmem, tmem_cols(BN));
+        if (tl && threadIdx.x == 0) tl[6] = clock64();
     }
 
     template <int BN, int kStages, int kCtasPerSm, typename T, bool B_KN>
-    int launch(vkc_ctx *ctx, const CUtensorMap &tmA, const CUtensorMap &tmB, const GemmParams &p, int64_t batch, cudaStream_t st) {
+    int launch(vkc_ctx *ctx, const CUtensorMap &tmA, const CUtensorMap &tmB, const CUtensorMap &tmD, const CUtensorMap &tmR, const GemmParams &p,
+               int64_t batch, cudaStream_t st) {
         auto          kern = gemm_tcgen05_kernel<BN, kStages, kCtasPerSm, T, B_KN>;
         constexpr int smem = smem_bytes<BN, kStages>();
         static_assert(smem * kCtasPerSm <= 227 * 1024, "shared memory budget");
         if (int rc = vkc_configure_smem(ctx, kern, smem)) return rc;
         dim3 grid((unsigned) ((p.M + BM - 1) / BM), (unsigned) ((p.N + BN - 1) / BN), (unsigned) batch);
-        kern<<<grid, kThreads, smem, st>>>(tmA, tmB, p);
+        kern<<<grid, kThreads, smem, st>>>(tmA, tmB, tmD, tmR, p);
         return vkc_post_launch(ctx, "gemm_tcgen05");
     }
 
@@ -244,6 +360,14 @@ int vkc_gemm_tcgen05(vkc_ctx *ctx, const void *A, const void *B, const float *bi
         return vkc_fail(ctx, VKC_ERR_UNSUPPORTED, "gemm_tcgen05: operand strides/bases must be multiples of 16 bytes");
     if (M > INT32_MAX || N > INT32_MAX || K > INT32_MAX || batch > 65535) return vkc_fail(ctx, VKC_ERR_UNSUPPORTED, "gemm_tcgen05: extent too large");
 
+    {
+        // CTA-pair form (256-row tiles over two SMs); selection heuristics live here
+        static const char *force = getenv("VKNN_GEMM_PAIR");
+        const int          bn    = force ? atoi(force) : 0;
+        if ((bn == 128 || bn == 256) && M > 128)
+            return vkc_gemm_tcgen05_pair(ctx, A, B, bias, residual, D, M, N, K, batch, stride_a, stride_b, stride_d, lda, ldb, ldd, b_layout, epilogue,
+                                         dtype, bn, st);
+    }
     const bool a_bcast = stride_a == 0 || batch == 1, b_bcast = stride_b == 0 || batch == 1;
     const TileChoice tc = choose_tile(M, N, batch, ctx->sm_count);
     const int        BN = tc.bn;
@@ -282,9 +406,22 @@ int vkc_gemm_tcgen05(vkc_ctx *ctx, const void *A, const void *B, const float *bi
     p.a_bcast  = a_bcast;
     p.b_bcast  = b_bcast;
     p.dev_err  = ctx->dev_err;
+    p.timeline = ctx->timeline;
+    // output / residual maps for the staged epilogue (box = 64 columns x 32 rows, one per epilogue warp and slab)
+    CUtensorMap tmD = tmA, tmR = tmA;
+    p.tma_out       = 0;
+    if ((ldd % 8 == 0) && (stride_d % 8 == 0) && (((uintptr_t) D & 15) == 0) && (!(epilogue & VKC_EPI_RESIDUAL) || (((uintptr_t) residual & 15) == 0))) {
+        uint64_t dims[3] = {(uint64_t) N, (uint64_t) M, (uint64_t) batch};
+        uint64_t str[2]  = {(uint64_t) ldd * 2, (uint64_t) (batch > 1 ? (uint64_t) stride_d * 2 : (uint64_t) ldd * 2 * (uint64_t) M)};
+        uint32_t box[3]  = {64, 32, 1};
+        int      rc      = vkc_make_tmap(ctx, &tmD, dtype, D, 3, dims, str, box);
+        if (rc == VKC_OK && (epilogue & VKC_EPI_RESIDUAL)) rc = vkc_make_tmap(ctx, &tmR, dtype, residual, 3, dims, str, box);
+        p.tma_out = rc == VKC_OK ? 1 : 0;
+    }
 
 #define VKC_GEMM_LAUNCH(BN_, ST_, C_, T_)                                                                       \
-    (b_layout == VKC_B_KN ? launch<BN_, ST_, C_, T_, true>(ctx, tmA, tmB, p, batch, st) : launch<BN_, ST_, C_, T_, false>(ctx, tmA, tmB, p, batch, st))
+    (b_layout == VKC_B_KN ? launch<BN_, ST_, C_, T_, true>(ctx, tmA, tmB, tmD, tmR, p, batch, st) \
+                          : launch<BN_, ST_, C_, T_, false>(ctx, tmA, tmB, tmD, tmR, p, batch, st))
 #define VKC_GEMM_BY_TILE(T_)                                                         \
     do {                                                                             \
         if (!tc.two_ctas) return VKC_GEMM_LAUNCH(256, 4, 1, T_);                     \

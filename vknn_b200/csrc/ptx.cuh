@@ -84,6 +84,14 @@ namespace ptx {
             "l"(map), "r"(x), "r"(y), "r"(z), "r"(w), "r"(bar)
             : "memory");
     }
+    // Tiled store shared memory -> global (clipped at the tensor bounds); completion is tracked per thread in bulk groups.
+    __device__ __forceinline__ void tma_store_3d(const CUtensorMap *map, uint32_t src, int x, int y, int z) {
+        asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(map), "r"(src), "r"(x), "r"(y),
+                     "r"(z)
+                     : "memory");
+    }
+    __device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+    __device__ __forceinline__ void bulk_wait_group_0() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
     // Untiled bulk copy of `bytes` contiguous bytes (both addresses 16-byte aligned, size a multiple of 16).
     __device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
         asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src), "r"(bytes),
@@ -169,6 +177,53 @@ namespace ptx {
             "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n"
             "}\n" ::"r"(d_tmem),
             "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
+            : "memory");
+    }
+
+    // ---- CTA pairs (cluster of two CTAs driving one cta_group::2 MMA) ------------------------------------
+    __device__ __forceinline__ uint32_t cluster_ctarank() {
+        uint32_t r;
+        asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+        return r;
+    }
+    // Address of the same shared-memory location in CTA `rank` of the cluster (shared::cluster window).
+    __device__ __forceinline__ uint32_t mapa(uint32_t addr, uint32_t rank) {
+        uint32_t r;
+        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+        return r;
+    }
+    __device__ __forceinline__ void cluster_sync() {
+        asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+    }
+    // Tiled load issued by either CTA of a pair; the completion bytes go to the mbarrier at `bar`, which may live in
+    // the other CTA of the pair (a shared::cluster address).
+    __device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap *map, int x, int y, int z, uint32_t bar) {
+        asm volatile(
+            "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::"r"(dst),
+            "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar)
+            : "memory");
+    }
+    __device__ __forceinline__ void tmem_alloc_pair(uint32_t slot, uint32_t ncols) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot), "r"(ncols) : "memory");
+    }
+    __device__ __forceinline__ void tmem_relinquish_pair() { asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory"); }
+    __device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+    }
+    // Arrive on the mbarrier at `bar` (a shared::cluster address, own or peer CTA) once every pair MMA issued so far
+    // by this thread has completed.
+    __device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
+        asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+    }
+    // D[tmem of both CTAs, 256 rows] (+)= A[smem of both CTAs] * B[smem halves of both CTAs]; issued by the leader CTA.
+    __device__ __forceinline__ void mma_f16_ss_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+        asm volatile(
+            "{\n"
+            ".reg .pred p;\n"
+            "setp.ne.b32 p, %4, 0;\n"
+            "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n"
+            "}\n" ::"r"(d_tmem),
+            "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
             : "memory");
     }
 

@@ -59,10 +59,11 @@ VKC_API int vkc_sync(vkc_ctx *ctx, vkc_stream stream);
 /* Number of kernels of this library launched through `ctx` since it was created. */
 VKC_API int64_t vkc_launch_count(const vkc_ctx *ctx);
 
-/* Development aid (no reference counterpart): the first call arms a 16-slot device buffer in which GEMM launches record
- * clock64 stamps of their first CTA (entry, set-up done, first operands landed, MMAs issued, accumulator ready,
- * epilogue done, exit); a later call with host16 != NULL copies the stamps of the last launch back. */
-VKC_API int vkc_debug_timeline(vkc_ctx *ctx, long long *host16);
+/* Development aid (no reference counterpart): the first call arms a 64-slot device buffer in which GEMM launches record
+ * clock64 stamps of their first CTA (slots 0-6: entry, set-up done, first operands landed, MMAs issued, accumulator
+ * ready, epilogue done, exit) and tensor-core prefill launches record two steady-state key tiles of their first CTA
+ * (slots 0-31); a later call with host64 != NULL copies the 64 slots of the last launch back. */
+VKC_API int vkc_debug_timeline(vkc_ctx *ctx, long long *host64);
 
 /* ---- memory and boundary transfers. Reference: boundary pack/unpack of a device segment, host fp32 <->
  * device storage precision, src/backend/vulkan/vk_backend.cpp:558-696,1324-1382; weight upload helpers

@@ -3,13 +3,13 @@
 // sequence in tiles of 128 keys; while the softmax warps of one query tile work, the tensor core runs the
 // MMAs of the other.
 //
-//   warp 0     TMA producer: both Q tiles once, then K and V tiles through two independent 2-stage
+//   warp 8     TMA producer: both Q tiles once, then K and V tiles through two independent 2-stage
 //              shared-memory rings (128-byte swizzle, plain per-CTA tiled loads; rows past the end read as zeros).
-//   warp 1     MMA issuer (one elected lane) and owner of the tensor-memory allocation (512 columns):
+//   warp 9     MMA issuer (one elected lane) and owner of the tensor-memory allocation (512 columns):
 //                S_t (128 fp32 columns)  = Q_t . K_j^T     both operands from shared memory (K-major)
 //                O_t (D fp32 columns)   += P_t . V_j       P_t from tensor memory, V_j MN-major from its row-major tile
 //              issue order per key tile j:  P.V_A(j), Q.K_A(j+1), P.V_B(j), Q.K_B(j+1).
-//   warps 2-5  softmax of tile A, warps 6-9 softmax of tile B; thread r owns row r of its tile. The row of S is
+//   warps 0-3  softmax of tile A, warps 4-7 softmax of tile B; thread r owns row r of its tile. The row of S is
 //              read from TMEM once into registers; P = exp2(S*scale*log2e - m) in fp32 is packed to the storage
 //              type and written over the first 64 columns of S_t (tcgen05.st), which the P.V MMA reads as its A
 //              operand. The running maximum is raised only when it grows by more than 8 (factor 256), so O_t in
@@ -20,6 +20,7 @@
 // P.V_t(j) by the same thread, which the tensor pipe executes in order.
 // Masking: keys >= kv_len[b] (or >= Skv) and, for causal, keys > row + (Skv - Sq) get probability 0; key tiles
 // entirely above a query tile's diagonal are skipped for that tile.
+#include <type_traits>
 #include "common.cuh"
 #include "ptx.cuh"
 #include "tensormap.cuh"
@@ -28,7 +29,8 @@ namespace {
 
     constexpr int BM = 128, BN = 128; // rows per query tile, keys per key tile
     constexpr int kQTiles    = 2;
-    constexpr int kThreads   = 64 + kQTiles * 128;
+    constexpr int kThreads   = 128 + kQTiles * 128; // two softmax warpgroups, then the control warpgroup
+    constexpr int kWarpTma = 8, kWarpMma = 9;        // warps 10 and 11 only give up their registers
     constexpr int kTmemCols  = 512;
     constexpr float kRescaleThreshold = 8.0f;
 
@@ -40,7 +42,9 @@ namespace {
         int            causal;
         const int32_t *kv_len;
         int           *dev_err;
+        long long     *timeline; // optional clock64 stamps of CTA (0,0,0): key tiles kTlTile and kTlTile + 1
     };
+    constexpr int kTlTile = 20;
 
     template <int D, int KS, int VS> struct Smem {
         static constexpr uint32_t Q_BYTES  = BM * D * 2; // per query tile
@@ -49,8 +53,8 @@ namespace {
         static constexpr uint32_t oK   = oQ + kQTiles * Q_BYTES;
         static constexpr uint32_t oV   = oK + KS * KV_BYTES;
         static constexpr uint32_t oBar = oV + VS * KV_BYTES;
-        // barriers: q_full, k_full[KS], k_empty[KS], v_full[VS], v_empty[VS], s_full[2], p_full[2], o_final[2]
-        static constexpr int nBar = 1 + 2 * KS + 2 * VS + 6;
+        // barriers: q_full, k_full[KS], k_empty[KS], v_full[VS], v_empty[VS], s_full[2], p_full[2][2 halves], o_final[2]
+        static constexpr int nBar = 1 + 2 * KS + 2 * VS + 8;
         static constexpr uint32_t oCtl  = oBar + 8 * nBar;
         static constexpr uint32_t total = oCtl + 16 + 1024;
     };
@@ -60,6 +64,12 @@ namespace {
         asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
         return y;
     }
+    // Polynomial 2^x (its steps are written inline in the softmax loop): every fourth column pair is exponentiated on
+    // the fp32 pipes, so that the exponentials of a score tile are shared between the special-function unit and the FMA pipes: x = n + f with n = round(x) taken by the magic-number addition
+    // (1.5 * 2^23) and f in [-0.5, 0.5]; 2^f by a cubic with relative error < 7.5e-5 (below half an ulp of either
+    // 16-bit storage type); n is added into the exponent field. Inputs are clamped at -125, so a masked score
+    // (-inf) yields 2^-125 rather than 0: invisible next to any visible key, and rows with no visible key are
+    // detected by their running maximum instead of by a zero sum.
     template <typename T> __device__ __forceinline__ uint32_t pack2(float a, float b);
     template <> __device__ __forceinline__ uint32_t pack2<__half>(float a, float b) {
         __half2 h = __floats2half2_rn(a, b);
@@ -70,11 +80,61 @@ namespace {
         return *reinterpret_cast<uint32_t *>(&h);
     }
 
-    template <typename T, int D>
+    // Order-pinned (volatile) forms of the softmax arithmetic, operating on 32-bit registers in place.
+    __device__ __forceinline__ void v_ex2(uint32_t &x) { asm volatile("ex2.approx.ftz.f32 %0, %0;" : "+r"(x)); }
+    __device__ __forceinline__ void v_max(uint32_t &x, float lo) { asm volatile("max.f32 %0, %0, %1;" : "+r"(x) : "f"(lo)); }
+    // {dx,dy} = {ax,ay} * b + c
+    __device__ __forceinline__ void v_ffma2(uint32_t &dx, uint32_t &dy, uint32_t ax, uint32_t ay, float2 b, float2 c) {
+        asm volatile("{.reg .b64 a, d; mov.b64 a, {%2, %3}; fma.rn.f32x2 d, a, %4, %5; mov.b64 {%0, %1}, d;}"
+                     : "=r"(dx), "=r"(dy)
+                     : "r"(ax), "r"(ay), "l"(reinterpret_cast<const unsigned long long &>(b)), "l"(reinterpret_cast<const unsigned long long &>(c)));
+    }
+    // {dx,dy} = a * {bx,by} + c
+    __device__ __forceinline__ void v_ffma2to(uint32_t &dx, uint32_t &dy, float2 a, uint32_t bx, uint32_t by, float2 c) {
+        asm volatile("{.reg .b64 b, d; mov.b64 b, {%2, %3}; fma.rn.f32x2 d, %4, b, %5; mov.b64 {%0, %1}, d;}"
+                     : "=r"(dx), "=r"(dy)
+                     : "r"(bx), "r"(by), "l"(reinterpret_cast<const unsigned long long &>(a)), "l"(reinterpret_cast<const unsigned long long &>(c)));
+    }
+    // {px,py} = {px,py} * {fx,fy} + c
+    __device__ __forceinline__ void v_ffma2acc(uint32_t &px, uint32_t &py, uint32_t fx, uint32_t fy, float2 c) {
+        asm volatile("{.reg .b64 p, f; mov.b64 p, {%0, %1}; mov.b64 f, {%2, %3}; fma.rn.f32x2 p, p, f, %4; mov.b64 {%0, %1}, p;}"
+                     : "+r"(px), "+r"(py)
+                     : "r"(fx), "r"(fy), "l"(reinterpret_cast<const unsigned long long &>(c)));
+    }
+    // {dx,dy} = {ax,ay} + b
+    __device__ __forceinline__ void v_fadd2to(uint32_t &dx, uint32_t &dy, uint32_t ax, uint32_t ay, float2 b) {
+        asm volatile("{.reg .b64 a, d; mov.b64 a, {%2, %3}; add.rn.f32x2 d, a, %4; mov.b64 {%0, %1}, d;}"
+                     : "=r"(dx), "=r"(dy)
+                     : "r"(ax), "r"(ay), "l"(reinterpret_cast<const unsigned long long &>(b)));
+    }
+    // acc += {ax,ay}
+    __device__ __forceinline__ void v_fadd2(float2 &acc, uint32_t ax, uint32_t ay) {
+        asm volatile("{.reg .b64 a; mov.b64 a, {%1, %2}; add.rn.f32x2 %0, %0, a;}"
+                     : "+l"(reinterpret_cast<unsigned long long &>(acc))
+                     : "r"(ax), "r"(ay));
+    }
+    // d = bits(p) + (bits(t) << 23): the integer part held in the low bits of t goes into the exponent of p
+    __device__ __forceinline__ void v_expo(uint32_t &d, uint32_t p, uint32_t t) {
+        asm volatile("{.reg .b32 e; shl.b32 e, %2, 23; add.u32 %0, %1, e;}" : "=r"(d) : "r"(p), "r"(t));
+    }
+    template <typename T> __device__ __forceinline__ uint32_t v_pack2(uint32_t lo, uint32_t hi);
+    template <> __device__ __forceinline__ uint32_t v_pack2<__half>(uint32_t lo, uint32_t hi) {
+        uint32_t d;
+        asm volatile("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(__uint_as_float(hi)), "f"(__uint_as_float(lo)));
+        return d;
+    }
+    template <> __device__ __forceinline__ uint32_t v_pack2<__nv_bfloat16>(uint32_t lo, uint32_t hi) {
+        uint32_t d;
+        asm volatile("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(__uint_as_float(hi)), "f"(__uint_as_float(lo)));
+        return d;
+    }
+
+    template <typename T, int D, int kMode>
     __global__ void __launch_bounds__(kThreads, 1)
         attn_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                             AttnParams p) {
-        constexpr int KS = 2, VS = 2;
+        constexpr int KS = 2, VS = 2; // the MMA issuer selects ring stages by the parity of the key tile
+        static_assert(KS == 2 && VS == 2, "stage selection assumes two-stage rings");
         using L               = Smem<D, KS, VS>;
         constexpr bool kBf16  = std::is_same<T, __nv_bfloat16>::value;
         constexpr uint32_t kIdescQK = ptx::idesc_f16(BM, BN, kBf16, false, false);
@@ -91,7 +151,7 @@ namespace {
         volatile int  *ctl = (volatile int *) (gbase + L::oCtl); // ctl[0] = tmem base, ctl[1] = abort flag
         auto           bar = [&](int i) { return sBar + 8u * (uint32_t) i; };
         constexpr int  bQ = 0, bKF = 1, bKE = 1 + KS, bVF = 1 + 2 * KS, bVE = 1 + 2 * KS + VS, bSF = 1 + 2 * KS + 2 * VS, bPF = bSF + 2,
-                      bOF = bSF + 4;
+                      bOF = bSF + 6;
 
         const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
         const int b = blockIdx.z, h = blockIdx.y;
@@ -122,14 +182,14 @@ namespace {
         const int n_max = n_t[0] > n_t[1] ? n_t[0] : n_t[1];
 
         if (threadIdx.x == 0) {
-            for (int i = 0; i < L::nBar; ++i) ptx::mbar_init(bar(i), (i >= bPF && i < bPF + 2) ? 128 : 1);
+            for (int i = 0; i < L::nBar; ++i) ptx::mbar_init(bar(i), (i >= bPF && i < bPF + 4) ? 4 : 1); // p_full: one arrival per softmax warp
             ctl[1] = 0;
             ptx::fence_mbar_init();
             ptx::prefetch_tmap(&tmQ);
             ptx::prefetch_tmap(&tmK);
             ptx::prefetch_tmap(&tmV);
         }
-        if (warp == 1) {
+        if (warp == kWarpMma) {
             ptx::tmem_alloc(base + L::oCtl, kTmemCols);
             ptx::tmem_relinquish();
         }
@@ -138,7 +198,9 @@ namespace {
         ptx::tc_fence_after();
         const uint32_t tmem = (uint32_t) ctl[0];
 
-        if (warp == 0) {
+        if (warp >= kWarpTma) {
+          ptx::setmaxnreg_dec<88>();
+          if (warp == kWarpTma) {
             // ------------------------------------------------------------------ TMA producer
             if (n_max > 0 && ptx::elect_one()) {
                 ptx::mbar_expect_tx(bar(bQ), kQTiles * L::Q_BYTES);
@@ -159,28 +221,29 @@ namespace {
                     for (int c = 0; c < DCH; ++c) ptx::tma_load_4d(sV + vs * L::KV_BYTES + c * (BN * 128), &tmV, c * 64, j * BN, hk, b, bar(bVF + vs));
                 }
             }
-        } else if (warp == 1) {
+          } else if (warp == kWarpMma) {
             // ------------------------------------------------------------------ MMA issuer
             if (n_max > 0 && ptx::elect_one()) {
+                // Base descriptors once; a step along K only moves the 14-bit start-address field (16-byte units).
+                const uint64_t dQ0 = ptx::smem_desc_sw128(sQ, 16, 1024), dQ1 = ptx::smem_desc_sw128(sQ + L::Q_BYTES, 16, 1024);
+                const uint64_t dK0 = ptx::smem_desc_sw128(sK, 16, 1024), dK1 = ptx::smem_desc_sw128(sK + L::KV_BYTES, 16, 1024);
+                const uint64_t dV0 = ptx::smem_desc_sw128(sV, BN * 128, 1024), dV1 = ptx::smem_desc_sw128(sV + L::KV_BYTES, BN * 128, 1024);
                 auto issue_qk = [&](int t, int j) {
-                    const int ks = j % KS;
+                    const uint64_t aq = t ? dQ1 : dQ0, bk = (j & 1) ? dK1 : dK0;
+                    const uint32_t d  = tmem + kColS + t * BN;
 #pragma unroll
                     for (int k = 0; k < D / 16; ++k) {
-                        const uint32_t off = (uint32_t) (k / 4) * (BM * 128) + (uint32_t) (k % 4) * 32;
-                        const uint64_t ad  = ptx::smem_desc_sw128(sQ + t * L::Q_BYTES + off, 16, 1024);
-                        const uint64_t bd  = ptx::smem_desc_sw128(sK + ks * L::KV_BYTES + off, 16, 1024);
-                        ptx::mma_f16_ss(tmem + kColS + t * BN, ad, bd, kIdescQK, k != 0 ? 1u : 0u);
+                        const uint32_t off = ((uint32_t) (k / 4) * (BM * 128) + (uint32_t) (k % 4) * 32) >> 4;
+                        ptx::mma_f16_ss(d, aq + off, bk + off, kIdescQK, k != 0 ? 1u : 0u);
                     }
                     ptx::tc_commit(bar(bSF + t));
                 };
-                auto issue_pv = [&](int t, int j) {
-                    const int vs = j % VS;
+                auto issue_pv = [&](int t, int j, int half) {
+                    // V tile: D/64 spans of [128 keys x 128 B]; 16 keys per MMA step = 2048 B; `half` = keys 0-63 or 64-127
+                    const uint64_t bv = (j & 1) ? dV1 : dV0;
+                    const uint32_t d = tmem + kColO + t * D, a = tmem + kColS + t * BN;
 #pragma unroll
-                    for (int k = 0; k < BN / 16; ++k) {
-                        // V tile: D/64 spans of [128 keys x 128 B]; 16 keys per MMA step = 2048 B
-                        const uint64_t bd = ptx::smem_desc_sw128(sV + vs * L::KV_BYTES + k * 2048, BN * 128, 1024);
-                        ptx::mma_f16_ts(tmem + kColO + t * D, tmem + kColS + t * BN + k * 8, bd, kIdescPV, (j | k) != 0 ? 1u : 0u);
-                    }
+                    for (int k = half * 4; k < half * 4 + 4; ++k) ptx::mma_f16_ts(d, a + k * 8, bv + (uint64_t) (k * 128), kIdescPV, (j | k) != 0 ? 1u : 0u);
                 };
                 bool ok = ptx::mbar_wait(bar(bQ), 0, ctl + 1, p.dev_err);
                 ok      = ok && ptx::mbar_wait(bar(bKF + 0), 0, ctl + 1, p.dev_err);
@@ -198,15 +261,23 @@ namespace {
 #pragma unroll
                     for (int t = 0; t < kQTiles && ok; ++t) {
                         if (j < n_t[t]) {
-                            ok = ptx::mbar_wait(bar(bPF + t), j & 1, ctl + 1, p.dev_err);
+                            ok = ptx::mbar_wait(bar(bPF + 2 * t), j & 1, ctl + 1, p.dev_err);
+                            if (!ok) break;
+                            long long *tl = (p.timeline && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (j == kTlTile || j == kTlTile + 1))
+                                                ? p.timeline + (j - kTlTile) * 16 + 10 + t * 2 : nullptr;
+                            if (tl) tl[0] = clock64();
+                            ptx::tc_fence_after();
+                            issue_pv(t, j, 0);
+                            ok = ptx::mbar_wait(bar(bPF + 2 * t + 1), j & 1, ctl + 1, p.dev_err);
                             if (!ok) break;
                             ptx::tc_fence_after();
-                            issue_pv(t, j);
+                            issue_pv(t, j, 1);
                             if (j + 1 < n_t[t]) {
                                 ok = ptx::mbar_wait(bar(bKF + (j + 1) % KS), ((j + 1) / KS) & 1, ctl + 1, p.dev_err);
                                 if (!ok) break;
                                 ptx::tc_fence_after();
                                 issue_qk(t, j + 1);
+                                if (tl) tl[1] = clock64();
                             } else {
                                 ptx::tc_commit(bar(bOF + t)); // O_t complete
                             }
@@ -217,9 +288,11 @@ namespace {
                     if (more) ptx::tc_commit(bar(bKE + (j + 1) % KS));
                 }
             }
+          }
         } else {
+            ptx::setmaxnreg_inc<208>();
             // ------------------------------------------------------------------ softmax + epilogue (thread = row)
-            const int      t      = (warp - 2) >> 2;       // query tile of this warpgroup
+            const int      t      = warp >> 2;             // query tile of this warpgroup
             const int      q      = warp & 3;              // TMEM lane quarter this warp may address
             const int      r      = q * 32 + lane;
             const int64_t  row    = m0 + (int64_t) t * BM + r;
@@ -227,37 +300,55 @@ namespace {
             const uint32_t tO     = tmem + ((uint32_t) (q * 32) << 16) + kColO + t * D;
             const int64_t  my_lim = p.causal ? row + (p.Skv - p.Sq) : p.Skv; // keys <= my_lim visible
             const int      n      = n_t[t];
+            long long     *tl0    = (p.timeline && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) ? p.timeline : nullptr;
             float          m_used = -INFINITY, l = 0.f;
             bool           ok     = true;
-            for (int j = 0; j < n; ++j) {
-                const int64_t kv0 = (int64_t) j * BN;
+            // One key tile; kMask selects the body that replaces invisible scores by -inf (only the tiles that
+            // straddle kv_len or the causal diagonal take it, every other tile runs free of any mask arithmetic).
+            auto tile = [&](auto mask_tag, int j) -> bool {
+                constexpr bool kMask = decltype(mask_tag)::value;
+                const int64_t  kv0   = (int64_t) j * BN;
                 ok = ptx::mbar_wait(bar(bSF + t), j & 1, ctl + 1, p.dev_err);
                 ok = __all_sync(0xffffffffu, ok);
-                if (!ok) break;
+                if (!ok) return false;
+                long long *tl = (tl0 && lane == 0 && q == 0 && (j == kTlTile || j == kTlTile + 1)) ? tl0 + (j - kTlTile) * 16 + t * 5 : nullptr;
+                if (tl) tl[0] = clock64();
                 ptx::tc_fence_after();
                 uint32_t s[4][32];
 #pragma unroll
                 for (int c = 0; c < 4; ++c) ptx::tmem_ld_x32(tS + c * 32, s[c]);
                 ptx::tc_wait_ld();
-                const bool need_mask = (kv0 + BN > len) || (p.causal && kv0 + BN - 1 > m0 + (int64_t) t * BM + (p.Skv - p.Sq));
-                if (need_mask) {
+                if (tl) tl[1] = clock64();
+                if (kMask) {
+                    // visible columns of this row in this tile: [0, nvis)
+                    int64_t lim = len < my_lim + 1 ? len : my_lim + 1;
+                    lim -= kv0;
+                    const int nvis = lim < 0 ? 0 : (lim > BN ? BN : (int) lim);
 #pragma unroll
                     for (int c = 0; c < 4; ++c)
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) {
-                            const int64_t key = kv0 + c * 32 + i;
-                            if (!(key < len && key <= my_lim)) s[c][i] = 0xff800000u; // -inf
-                        }
+                        for (int i = 0; i < 32; ++i)
+                            if (c * 32 + i >= nvis) s[c][i] = 0xff800000u; // -inf
                 }
-                float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+                // row maximum: 16 independent chains over 8 columns each (3-input max), then a short tree
+                float mx[16];
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    mx0 = fmaxf(mx0, __uint_as_float(s[0][i]));
-                    mx1 = fmaxf(mx1, __uint_as_float(s[1][i]));
-                    mx2 = fmaxf(mx2, __uint_as_float(s[2][i]));
-                    mx3 = fmaxf(mx3, __uint_as_float(s[3][i]));
-                }
-                const float mxs = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale_log2; // scale > 0
+                for (int k = 0; k < 16; ++k)
+                    mx[k] = ptx::fmax3(__uint_as_float(s[k >> 2][(k & 3) * 8]), __uint_as_float(s[k >> 2][(k & 3) * 8 + 1]),
+                                       __uint_as_float(s[k >> 2][(k & 3) * 8 + 2]));
+#pragma unroll
+                for (int u = 3; u < 7; u += 2)
+#pragma unroll
+                    for (int k = 0; k < 16; ++k)
+                        mx[k] = ptx::fmax3(mx[k], __uint_as_float(s[k >> 2][(k & 3) * 8 + u]), __uint_as_float(s[k >> 2][(k & 3) * 8 + u + 1]));
+#pragma unroll
+                for (int k = 0; k < 8; ++k) mx[k] = ptx::fmax3(mx[k], mx[k + 8], __uint_as_float(s[k >> 1][(k & 1) * 16 + 7]));
+#pragma unroll
+                for (int k = 0; k < 8; ++k) mx[k] = fmaxf(mx[k], __uint_as_float(s[k >> 1][(k & 1) * 16 + 15]));
+                mx[0] = ptx::fmax3(mx[0], mx[1], mx[2]);
+                mx[3] = ptx::fmax3(mx[3], mx[4], mx[5]);
+                mx[6] = fmaxf(mx[6], mx[7]);
+                const float mxs = ptx::fmax3(mx[0], mx[3], mx[6]) * p.scale_log2; // scale > 0
                 float       alpha = 1.f;
                 bool        rescale = false;
                 if (mxs > m_used + kRescaleThreshold || (m_used == -INFINITY && mxs > m_used)) {
@@ -279,26 +370,109 @@ namespace {
                     }
                 }
                 const float neg_m = m_used == -INFINITY ? 0.f : -m_used;
-                float       l0 = 0.f, l1 = 0.f;
+                if (tl) tl[2] = clock64();
+                const float2 sc2 = make_float2(p.scale_log2, p.scale_log2), nm2 = make_float2(neg_m, neg_m);
+                float2       ls  = make_float2(0.f, 0.f);
+                // P for keys [64*half, 64*half + 64) of this row is in TMEM: one arrival per warp on that half's barrier
+                auto p_ready = [&](int half) {
+                    ptx::tc_wait_st();
+                    ptx::tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) ptx::mbar_arrive(bar(bPF + 2 * t + half));
+                };
+                if (kMode == 0) {
 #pragma unroll
-                for (int c = 0; c < 4; c += 2) {
+                    for (int c = 0; c < 4; c += 2) {
+                        uint32_t pk[32];
+#pragma unroll
+                        for (int cc = 0; cc < 2; ++cc)
+#pragma unroll
+                            for (int i = 0; i < 32; i += 2) {
+                                const float2 x = ptx::ffma2(make_float2(__uint_as_float(s[c + cc][i]), __uint_as_float(s[c + cc][i + 1])), sc2, nm2);
+                                const float2 e = make_float2(fast_exp2(x.x), fast_exp2(x.y));
+                                ls             = ptx::fadd2(ls, e);
+                                pk[cc * 16 + i / 2] = pack2<T>(e.x, e.y);
+                            }
+                        ptx::tmem_st_x32(tS + (c / 2) * 32, pk);
+                        if (c == 0) p_ready(0);
+                    }
+                } else {
+                    // The 64 column pairs of the row as a three-stage software pipeline written out in issue order, so
+                    // that the two exponentials of a pair (special-function unit, 8 cycles per warp instruction) always
+                    // sit between fp32-pipe instructions of other pairs: stage 0 scales (x = s*scale*log2e - m), stage 1
+                    // exponentiates in place, stage 2 adds to the row sum and packs to 16 bits. In mode 2 every fourth
+                    // pair takes the polynomial 2^x, whose steps are spread between the exponentials of the other three.
                     uint32_t pk[32];
-#pragma unroll
-                    for (int cc = 0; cc < 2; ++cc)
-#pragma unroll
-                        for (int i = 0; i < 32; i += 2) {
-                            const float p0 = fast_exp2(fmaf(__uint_as_float(s[c + cc][i]), p.scale_log2, neg_m));
-                            const float p1 = fast_exp2(fmaf(__uint_as_float(s[c + cc][i + 1]), p.scale_log2, neg_m));
-                            l0 += p0;
-                            l1 += p1;
-                            pk[cc * 16 + i / 2] = pack2<T>(p0, p1);
+                    auto     X  = [&](int g) -> uint32_t & { return s[g >> 4][(g & 15) * 2]; };
+                    auto     Y  = [&](int g) -> uint32_t & { return s[g >> 4][(g & 15) * 2 + 1]; };
+                    auto     S0 = [&](int g) {
+                        if (g < 64) v_ffma2(X(g), Y(g), X(g), Y(g), sc2, nm2);
+                    };
+                    auto S2 = [&](int g) {
+                        if (g >= 0) {
+                            v_fadd2(ls, X(g), Y(g));
+                            pk[g & 31] = v_pack2<T>(X(g), Y(g));
+                            if ((g & 31) == 31) ptx::tmem_st_x32(tS + (g >> 5) * 32, pk);
+                            if (g == 35) p_ready(0); // a few pairs after the first half's store was issued
                         }
-                    ptx::tmem_st_x32(tS + (c / 2) * 32, pk);
+                    };
+                    const float2 kMagic = make_float2(12582912.0f, 12582912.0f), kNegMagic = make_float2(-12582912.0f, -12582912.0f);
+                    const float2 kNegOne = make_float2(-1.f, -1.f);
+                    const float2 kC3 = make_float2(5.517164618e-02f, 5.517164618e-02f), kC2 = make_float2(2.426111251e-01f, 2.426111251e-01f);
+                    const float2 kC1 = make_float2(6.932609677e-01f, 6.932609677e-01f), kC0 = make_float2(9.999280572e-01f, 9.999280572e-01f);
+                    uint32_t     tx, ty, nx, ny, px, py; // the polynomial pair in flight
+                    S0(0), S0(1), S0(2), S0(3);
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        const int m0 = 4 * i, m1 = m0 + 1, m2 = m0 + 2, q = m0 + 3;
+                        v_ex2(X(m0));
+                        S0(m0 + 4);
+                        if (kMode == 2) v_max(X(q), -125.0f), v_max(Y(q), -125.0f);
+                        v_ex2(Y(m0));
+                        if (kMode == 2) {
+                            v_fadd2to(tx, ty, X(q), Y(q), kMagic);
+                            v_fadd2to(nx, ny, tx, ty, kNegMagic);
+                        }
+                        S2(m0 - 4);
+                        v_ex2(X(m1));
+                        S0(m1 + 4);
+                        if (kMode == 2) {
+                            v_ffma2(nx, ny, nx, ny, kNegOne, make_float2(__uint_as_float(X(q)), __uint_as_float(Y(q)))); // f = x - n
+                            v_ffma2to(px, py, kC3, nx, ny, kC2);
+                        }
+                        v_ex2(Y(m1));
+                        if (kMode == 2) v_ffma2acc(px, py, nx, ny, kC1);
+                        S2(m1 - 4);
+                        v_ex2(X(m2));
+                        S0(m2 + 4);
+                        if (kMode == 2) {
+                            v_ffma2acc(px, py, nx, ny, kC0);
+                            v_expo(X(q), px, tx);
+                        } else {
+                            v_ex2(X(q));
+                        }
+                        v_ex2(Y(m2));
+                        S0(q + 4);
+                        if (kMode == 2) {
+                            v_expo(Y(q), py, ty);
+                        } else {
+                            v_ex2(Y(q));
+                        }
+                        S2(m2 - 4);
+                        S2(q - 4);
+                    }
+                    S2(60), S2(61), S2(62), S2(63);
                 }
-                l += l0 + l1;
-                ptx::tc_wait_st();
-                ptx::tc_fence_before();
-                ptx::mbar_arrive(bar(bPF + t));
+                l += ls.x + ls.y;
+                if (tl) tl[3] = clock64();
+                p_ready(1);
+                if (tl) tl[4] = clock64();
+                return true;
+            };
+            for (int j = 0; j < n; ++j) {
+                const int64_t kv0       = (int64_t) j * BN;
+                const bool    need_mask = (kv0 + BN > len) || (p.causal && kv0 + BN - 1 > m0 + (int64_t) t * BM + (p.Skv - p.Sq));
+                if (!(need_mask ? tile(std::true_type{}, j) : tile(std::false_type{}, j))) break;
             }
             // epilogue
             if (n > 0 && ok) {
@@ -307,7 +481,8 @@ namespace {
             }
             if (ok) {
                 ptx::tc_fence_after();
-                const float inv = 1.0f / l; // l == 0 (no visible key) stores NaN like the reference's 0/0
+                // a row with no visible key stores NaN like the reference's 0/0
+                const float inv = (n > 0 && m_used == -INFINITY) ? __int_as_float(0x7fc00000) : 1.0f / l;
                 T          *orow = (T *) p.O + (int64_t) b * p.os[0] + (int64_t) h * p.os[1] + row * p.os[2];
                 const bool  vec_ok = (p.os[0] % 8 == 0) && (p.os[1] % 8 == 0) && (p.os[2] % 8 == 0) && (((uintptr_t) p.O & 15) == 0);
 #pragma unroll 1
@@ -344,12 +519,18 @@ namespace {
         }
         ptx::tc_fence_before();
         __syncthreads();
-        if (warp == 1) ptx::tmem_dealloc(tmem, kTmemCols);
+        if (warp == kWarpMma) ptx::tmem_dealloc(tmem, kTmemCols);
     }
 
-    template <typename T, int D>
+    template <typename T, int D, int kMode = 2>
     int launch_attn(vkc_ctx *ctx, const CUtensorMap &tq, const CUtensorMap &tk, const CUtensorMap &tv, const AttnParams &p, int64_t B, cudaStream_t st) {
-        auto          kern = attn_prefill_kernel<T, D>;
+        if (kMode == 2 && D == 128 && std::is_same<T, __nv_bfloat16>::value) { // development switch between the softmax forms
+            static const char *e = getenv("VKNN_PREFILL_POLY");
+            const int          v = e ? atoi(e) : 2;
+            if (v == 0) return launch_attn<T, D, 0>(ctx, tq, tk, tv, p, B, st);
+            if (v == 1) return launch_attn<T, D, 1>(ctx, tq, tk, tv, p, B, st);
+        }
+        auto          kern = attn_prefill_kernel<T, D, kMode>;
         constexpr int smem = (int) Smem<D, 2, 2>::total;
         if (int rc = vkc_configure_smem(ctx, kern, smem)) return rc;
         dim3 grid((unsigned) ((p.Sq + kQTiles * BM - 1) / (kQTiles * BM)), (unsigned) p.Hq, (unsigned) B);
@@ -396,6 +577,7 @@ int vkc_attn_prefill_tcgen05(vkc_ctx *ctx, const void *Q, const void *K, const v
     p.causal     = causal;
     p.kv_len     = kv_len;
     p.dev_err    = ctx->dev_err;
+    p.timeline   = ctx->timeline;
     if (dtype == VKC_F16) return D == 64 ? launch_attn<__half, 64>(ctx, tq, tk, tv, p, B, st) : launch_attn<__half, 128>(ctx, tq, tk, tv, p, B, st);
     return D == 64 ? launch_attn<__nv_bfloat16, 64>(ctx, tq, tk, tv, p, B, st) : launch_attn<__nv_bfloat16, 128>(ctx, tq, tk, tv, p, B, st);
 }

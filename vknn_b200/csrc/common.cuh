@@ -34,7 +34,7 @@ struct vkc_ctx {
     std::string  err;
     // driver entry point for tensor-map encoding (resolved once; no link-time dependency on libcuda)
     void *encode_tiled = nullptr;
-    long long *timeline = nullptr; // optional 16-slot device buffer: clock64 stamps of CTA (0,0,0) of the last GEMM launch
+    long long *timeline = nullptr; // optional 64-slot device buffer: clock64 stamps of CTA (0,0,0) of the last GEMM or prefill launch
     // kernels whose dynamic shared-memory limit has been raised on this context's device
     std::set<const void *> smem_configured;
 };

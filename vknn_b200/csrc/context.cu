@@ -128,14 +128,14 @@ int vkc_sync(vkc_ctx *ctx, vkc_stream stream) {
 
 int64_t vkc_launch_count(const vkc_ctx *ctx) { return ctx ? ctx->launches : 0; }
 
-// Development aid: after this call, GEMM launches record clock64 stamps of their first CTA; read them back with a second call.
-int vkc_debug_timeline(vkc_ctx *ctx, long long *host16) {
+// Development aid: after this call, GEMM and prefill-attention launches record clock64 stamps of their first CTA; read them back with a second call.
+int vkc_debug_timeline(vkc_ctx *ctx, long long *host64) {
     if (!ctx) return VKC_ERR_INVALID;
     if (!ctx->timeline) {
-        VKC_CUDA(ctx, cudaMalloc(&ctx->timeline, 16 * sizeof(long long)));
-        VKC_CUDA(ctx, cudaMemset(ctx->timeline, 0, 16 * sizeof(long long)));
+        VKC_CUDA(ctx, cudaMalloc(&ctx->timeline, 64 * sizeof(long long)));
+        VKC_CUDA(ctx, cudaMemset(ctx->timeline, 0, 64 * sizeof(long long)));
     }
-    if (host16) VKC_CUDA(ctx, cudaMemcpy(host16, ctx->timeline, 16 * sizeof(long long), cudaMemcpyDeviceToHost));
+    if (host64) VKC_CUDA(ctx, cudaMemcpy(host64, ctx->timeline, 64 * sizeof(long long), cudaMemcpyDeviceToHost));
     return VKC_OK;
 }
 

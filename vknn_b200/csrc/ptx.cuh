@@ -114,6 +114,21 @@ namespace ptx {
             : "l"(reinterpret_cast<const unsigned long long &>(a)), "l"(reinterpret_cast<const unsigned long long &>(b)));
         return d;
     }
+    __device__ __forceinline__ float2 fadd2(float2 a, float2 b) {
+        float2 d;
+        asm("add.rn.f32x2 %0, %1, %2;"
+            : "=l"(reinterpret_cast<unsigned long long &>(d))
+            : "l"(reinterpret_cast<const unsigned long long &>(a)), "l"(reinterpret_cast<const unsigned long long &>(b)));
+        return d;
+    }
+    __device__ __forceinline__ float fmax3(float a, float b, float c) {
+        float d;
+        asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+        return d;
+    }
+    // Register re-partitioning between warpgroups (all four warps of a warpgroup execute the same one).
+    template <int N> __device__ __forceinline__ void setmaxnreg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
+    template <int N> __device__ __forceinline__ void setmaxnreg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
     __device__ __forceinline__ void prefetch_tmap(const CUtensorMap *map) {
         asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
     }

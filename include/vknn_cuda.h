@@ -60,8 +60,8 @@ VKC_API int vkc_sync(vkc_ctx *ctx, vkc_stream stream);
 VKC_API int64_t vkc_launch_count(const vkc_ctx *ctx);
 
 /* Development aid (no reference counterpart): the first call arms a 64-slot device buffer in which GEMM launches record
- * clock64 stamps of their first CTA (slots 0-6: entry, set-up done, first operands landed, MMAs issued, accumulator
- * ready, epilogue done, exit) and tensor-core prefill launches record two steady-state key tiles of their first CTA
+ * clock64 stamps of their first CTA (slots 0-8: entry, set-up done, first operands landed, MMAs issued, accumulator
+ * ready, epilogue done, exit, split-K partials sent, split-K partials received) and tensor-core prefill launches record two steady-state key tiles of their first CTA
  * (slots 0-31); a later call with host64 != NULL copies the 64 slots of the last launch back. */
 VKC_API int vkc_debug_timeline(vkc_ctx *ctx, long long *host64);
 

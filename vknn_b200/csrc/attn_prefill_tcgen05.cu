@@ -12,9 +12,15 @@
 //   warps 0-3  softmax of tile A, warps 4-7 softmax of tile B; thread r owns row r of its tile. The row of S is
 //              read from TMEM once into registers; P = exp2(S*scale*log2e - m) in fp32 is packed to the storage
 //              type and written over the first 64 columns of S_t (tcgen05.st), which the P.V MMA reads as its A
-//              operand. The running maximum is raised only when it grows by more than 8 (factor 256), so O_t in
-//              TMEM is rescaled rarely; row sums stay in fp32. After the last key tile the same warps read O_t,
-//              divide by the row sum and store.
+//              operand. P_t is handed over in two column groups (keys 0-63, 64-127), each on its own mbarrier with
+//              one arrival per warp, so the first four P.V MMA steps run while the second half is exponentiated.
+//              The exponentials are the scarce resource (16 per clock per SM): the row is processed as a software
+//              pipeline written in issue order, packed fp32 arithmetic (f32x2) around the MUFU ex2, and every fourth
+//              column pair takes a cubic-polynomial 2^x on the FMA pipes instead. The running maximum is raised
+//              only when it grows by more than 8 (factor 256), so O_t in TMEM is rescaled rarely; row sums stay in
+//              fp32. After the last key tile the same warps read O_t, divide by the row sum and store.
+//   warps 8-11 form the control warpgroup (8 = TMA, 9 = MMA); it gives registers up (setmaxnreg) so that the two
+//              softmax warpgroups hold a whole score row plus the packed probabilities without spilling.
 // Ordering notes: tcgen05.commit covers every MMA issued before it, so "S_t(j) ready" also means P.V_t(j-1) has
 // finished and O_t may be rescaled; Q.K_t(j+1) overwrites the columns P_t(j) lives in and is issued after
 // P.V_t(j) by the same thread, which the tensor pipe executes in order.
@@ -33,6 +39,7 @@ namespace {
     constexpr int kWarpTma = 8, kWarpMma = 9;        // warps 10 and 11 only give up their registers
     constexpr int kTmemCols  = 512;
     constexpr float kRescaleThreshold = 8.0f;
+    constexpr int   kPParts = 2; // P_t is handed to the MMA issuer in this many column groups (BN / kPParts keys each)
 
     struct AttnParams {
         void          *O;
@@ -53,8 +60,8 @@ namespace {
         static constexpr uint32_t oK   = oQ + kQTiles * Q_BYTES;
         static constexpr uint32_t oV   = oK + KS * KV_BYTES;
         static constexpr uint32_t oBar = oV + VS * KV_BYTES;
-        // barriers: q_full, k_full[KS], k_empty[KS], v_full[VS], v_empty[VS], s_full[2], p_full[2][2 halves], o_final[2]
-        static constexpr int nBar = 1 + 2 * KS + 2 * VS + 8;
+        // barriers: q_full, k_full[KS], k_empty[KS], v_full[VS], v_empty[VS], s_full[2], p_full[2][kPParts], o_final[2]
+        static constexpr int nBar = 1 + 2 * KS + 2 * VS + 4 + 2 * kPParts;
         static constexpr uint32_t oCtl  = oBar + 8 * nBar;
         static constexpr uint32_t total = oCtl + 16 + 1024;
     };
@@ -151,7 +158,7 @@ namespace {
         volatile int  *ctl = (volatile int *) (gbase + L::oCtl); // ctl[0] = tmem base, ctl[1] = abort flag
         auto           bar = [&](int i) { return sBar + 8u * (uint32_t) i; };
         constexpr int  bQ = 0, bKF = 1, bKE = 1 + KS, bVF = 1 + 2 * KS, bVE = 1 + 2 * KS + VS, bSF = 1 + 2 * KS + 2 * VS, bPF = bSF + 2,
-                      bOF = bSF + 6;
+                      bOF = bPF + 2 * kPParts;
 
         const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
         const int b = blockIdx.z, h = blockIdx.y;
@@ -182,7 +189,7 @@ namespace {
         const int n_max = n_t[0] > n_t[1] ? n_t[0] : n_t[1];
 
         if (threadIdx.x == 0) {
-            for (int i = 0; i < L::nBar; ++i) ptx::mbar_init(bar(i), (i >= bPF && i < bPF + 4) ? 4 : 1); // p_full: one arrival per softmax warp
+            for (int i = 0; i < L::nBar; ++i) ptx::mbar_init(bar(i), (i >= bPF && i < bOF) ? 4 : 1); // p_full: one arrival per softmax warp
             ctl[1] = 0;
             ptx::fence_mbar_init();
             ptx::prefetch_tmap(&tmQ);
@@ -197,6 +204,8 @@ namespace {
         __syncthreads();
         ptx::tc_fence_after();
         const uint32_t tmem = (uint32_t) ctl[0];
+        vkc_grid_dep_wait(); // set-up above overlaps the previous kernel's tail; global memory from here on
+        vkc_grid_dep_launch();
 
         if (warp >= kWarpTma) {
           ptx::setmaxnreg_dec<88>();
@@ -238,12 +247,12 @@ namespace {
                     }
                     ptx::tc_commit(bar(bSF + t));
                 };
-                auto issue_pv = [&](int t, int j, int half) {
-                    // V tile: D/64 spans of [128 keys x 128 B]; 16 keys per MMA step = 2048 B; `half` = keys 0-63 or 64-127
+                auto issue_pv = [&](int t, int j, int part) {
+                    // V tile: D/64 spans of [128 keys x 128 B]; 16 keys per MMA step = 2048 B; `part` selects BN / kPParts keys
                     const uint64_t bv = (j & 1) ? dV1 : dV0;
                     const uint32_t d = tmem + kColO + t * D, a = tmem + kColS + t * BN;
 #pragma unroll
-                    for (int k = half * 4; k < half * 4 + 4; ++k) ptx::mma_f16_ts(d, a + k * 8, bv + (uint64_t) (k * 128), kIdescPV, (j | k) != 0 ? 1u : 0u);
+                    for (int k = part * (8 / kPParts); k < (part + 1) * (8 / kPParts); ++k) ptx::mma_f16_ts(d, a + k * 8, bv + (uint64_t) (k * 128), kIdescPV, (j | k) != 0 ? 1u : 0u);
                 };
                 bool ok = ptx::mbar_wait(bar(bQ), 0, ctl + 1, p.dev_err);
                 ok      = ok && ptx::mbar_wait(bar(bKF + 0), 0, ctl + 1, p.dev_err);
@@ -261,17 +270,22 @@ namespace {
 #pragma unroll
                     for (int t = 0; t < kQTiles && ok; ++t) {
                         if (j < n_t[t]) {
-                            ok = ptx::mbar_wait(bar(bPF + 2 * t), j & 1, ctl + 1, p.dev_err);
+                            ok = ptx::mbar_wait(bar(bPF + kPParts * t), j & 1, ctl + 1, p.dev_err);
                             if (!ok) break;
                             long long *tl = (p.timeline && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (j == kTlTile || j == kTlTile + 1))
                                                 ? p.timeline + (j - kTlTile) * 16 + 10 + t * 2 : nullptr;
                             if (tl) tl[0] = clock64();
                             ptx::tc_fence_after();
                             issue_pv(t, j, 0);
-                            ok = ptx::mbar_wait(bar(bPF + 2 * t + 1), j & 1, ctl + 1, p.dev_err);
+#pragma unroll
+                            for (int part = 1; part < kPParts && ok; ++part) {
+                                ok = ptx::mbar_wait(bar(bPF + kPParts * t + part), j & 1, ctl + 1, p.dev_err);
+                                if (ok) {
+                                    ptx::tc_fence_after();
+                                    issue_pv(t, j, part);
+                                }
+                            }
                             if (!ok) break;
-                            ptx::tc_fence_after();
-                            issue_pv(t, j, 1);
                             if (j + 1 < n_t[t]) {
                                 ok = ptx::mbar_wait(bar(bKF + (j + 1) % KS), ((j + 1) / KS) & 1, ctl + 1, p.dev_err);
                                 if (!ok) break;
@@ -373,12 +387,12 @@ namespace {
                 if (tl) tl[2] = clock64();
                 const float2 sc2 = make_float2(p.scale_log2, p.scale_log2), nm2 = make_float2(neg_m, neg_m);
                 float2       ls  = make_float2(0.f, 0.f);
-                // P for keys [64*half, 64*half + 64) of this row is in TMEM: one arrival per warp on that half's barrier
-                auto p_ready = [&](int half) {
+                // P for column group `part` of this row is in TMEM: one arrival per warp on that group's barrier
+                auto p_ready = [&](int part) {
                     ptx::tc_wait_st();
                     ptx::tc_fence_before();
                     __syncwarp();
-                    if (lane == 0) ptx::mbar_arrive(bar(bPF + 2 * t + half));
+                    if (lane == 0) ptx::mbar_arrive(bar(bPF + kPParts * t + part));
                 };
                 if (kMode == 0) {
 #pragma unroll
@@ -394,7 +408,9 @@ namespace {
                                 pk[cc * 16 + i / 2] = pack2<T>(e.x, e.y);
                             }
                         ptx::tmem_st_x32(tS + (c / 2) * 32, pk);
-                        if (c == 0) p_ready(0);
+#pragma unroll
+                        for (int part = (c / 2) * (kPParts / 2); part < (c / 2 + 1) * (kPParts / 2); ++part)
+                            if (part != kPParts - 1) p_ready(part);
                     }
                 } else {
                     // The 64 column pairs of the row as a three-stage software pipeline written out in issue order, so
@@ -402,7 +418,8 @@ namespace {
                     // sit between fp32-pipe instructions of other pairs: stage 0 scales (x = s*scale*log2e - m), stage 1
                     // exponentiates in place, stage 2 adds to the row sum and packs to 16 bits. In mode 2 every fourth
                     // pair takes the polynomial 2^x, whose steps are spread between the exponentials of the other three.
-                    uint32_t pk[32];
+                    constexpr int kPairs = 64 / kPParts; // column pairs per hand-off group
+                    uint32_t      pk[32];
                     auto     X  = [&](int g) -> uint32_t & { return s[g >> 4][(g & 15) * 2]; };
                     auto     Y  = [&](int g) -> uint32_t & { return s[g >> 4][(g & 15) * 2 + 1]; };
                     auto     S0 = [&](int g) {
@@ -412,8 +429,13 @@ namespace {
                         if (g >= 0) {
                             v_fadd2(ls, X(g), Y(g));
                             pk[g & 31] = v_pack2<T>(X(g), Y(g));
-                            if ((g & 31) == 31) ptx::tmem_st_x32(tS + (g >> 5) * 32, pk);
-                            if (g == 35) p_ready(0); // a few pairs after the first half's store was issued
+                            if (kPairs == 16 && (g & 15) == 15) {
+                                if (g & 16) ptx::tmem_st_x16(tS + (g >> 4) * 16, *reinterpret_cast<uint32_t(*)[16]>(pk + 16));
+                                else ptx::tmem_st_x16(tS + (g >> 4) * 16, *reinterpret_cast<uint32_t(*)[16]>(pk));
+                            }
+                            if (kPairs == 32 && (g & 31) == 31) ptx::tmem_st_x32(tS + (g >> 5) * 32, pk);
+                            // signal a group a few pairs after its store was issued
+                            if (g >= kPairs && g < 64 && (g % kPairs) == 3) p_ready(g / kPairs - 1);
                         }
                     };
                     const float2 kMagic = make_float2(12582912.0f, 12582912.0f), kNegMagic = make_float2(-12582912.0f, -12582912.0f);
@@ -465,7 +487,7 @@ namespace {
                 }
                 l += ls.x + ls.y;
                 if (tl) tl[3] = clock64();
-                p_ready(1);
+                p_ready(kPParts - 1);
                 if (tl) tl[4] = clock64();
                 return true;
             };
@@ -524,17 +546,11 @@ namespace {
 
     template <typename T, int D, int kMode = 2>
     int launch_attn(vkc_ctx *ctx, const CUtensorMap &tq, const CUtensorMap &tk, const CUtensorMap &tv, const AttnParams &p, int64_t B, cudaStream_t st) {
-        if (kMode == 2 && D == 128 && std::is_same<T, __nv_bfloat16>::value) { // development switch between the softmax forms
-            static const char *e = getenv("VKNN_PREFILL_POLY");
-            const int          v = e ? atoi(e) : 2;
-            if (v == 0) return launch_attn<T, D, 0>(ctx, tq, tk, tv, p, B, st);
-            if (v == 1) return launch_attn<T, D, 1>(ctx, tq, tk, tv, p, B, st);
-        }
         auto          kern = attn_prefill_kernel<T, D, kMode>;
         constexpr int smem = (int) Smem<D, 2, 2>::total;
         if (int rc = vkc_configure_smem(ctx, kern, smem)) return rc;
         dim3 grid((unsigned) ((p.Sq + kQTiles * BM - 1) / (kQTiles * BM)), (unsigned) p.Hq, (unsigned) B);
-        kern<<<grid, kThreads, smem, st>>>(tq, tk, tv, p);
+        vkc_launch(ctx, kern, grid, dim3(kThreads), smem, st, tq, tk, tv, p);
         return vkc_post_launch(ctx, "attn_prefill_tcgen05");
     }
 

@@ -10,6 +10,7 @@
 #include <cstring>
 #include <set>
 #include <string>
+#include <utility>
 #include <type_traits>
 
 // Device-side error codes written to vkc_ctx::dev_err (first writer wins).
@@ -31,6 +32,7 @@ struct vkc_ctx {
     cudaEvent_t  ev0 = nullptr, ev1 = nullptr;
     int64_t      launches = 0;
     bool         capturing = false;
+    bool         dep_launch = true; // programmatic dependent launch between consecutive kernels (VKNN_PDL=0 turns it off)
     std::string  err;
     // driver entry point for tensor-map encoding (resolved once; no link-time dependency on libcuda)
     void *encode_tiled = nullptr;
@@ -73,6 +75,48 @@ inline int vkc_post_launch(vkc_ctx *ctx, const char *what) {
     ctx->launches++;
     return VKC_OK;
 }
+
+// Launch with programmatic stream serialization: the kernel may start (set up shared memory, barriers, tensor
+// memory) while the previous kernel of the stream is still draining; it must execute griddepcontrol.wait
+// (vkc_grid_dep_wait) before its first access to global memory, which returns once the previous kernel has completed
+// and its writes are visible. Inside a stream capture the dependency becomes a programmatic graph edge.
+// `cluster_x` > 1 launches thread-block clusters of that many consecutive CTAs along x.
+template <typename... KArgs, typename... Args>
+inline void vkc_launch_cluster(vkc_ctx *ctx, void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, unsigned cluster_x,
+                               Args &&...args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim            = grid;
+    cfg.blockDim           = block;
+    cfg.dynamicSmemBytes   = smem;
+    cfg.stream             = st;
+    cudaLaunchAttribute at[2];
+    unsigned            n = 0;
+    if (ctx->dep_launch) {
+        at[n].id                                         = cudaLaunchAttributeProgrammaticStreamSerialization;
+        at[n].val.programmaticStreamSerializationAllowed = 1;
+        ++n;
+    }
+    if (cluster_x > 1) {
+        at[n].id               = cudaLaunchAttributeClusterDimension;
+        at[n].val.clusterDim.x = cluster_x;
+        at[n].val.clusterDim.y = 1;
+        at[n].val.clusterDim.z = 1;
+        ++n;
+    }
+    cfg.attrs    = at;
+    cfg.numAttrs = n;
+    cudaLaunchKernelEx(&cfg, kern, std::forward<Args>(args)...); // errors surface in vkc_post_launch
+}
+template <typename... KArgs, typename... Args>
+inline void vkc_launch(vkc_ctx *ctx, void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args &&...args) {
+    vkc_launch_cluster(ctx, kern, grid, block, smem, st, 1u, std::forward<Args>(args)...);
+}
+
+#ifdef __CUDACC__
+// Device side of the above. Both are no-ops in a kernel launched without the attribute.
+__device__ __forceinline__ void vkc_grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void vkc_grid_dep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+#endif
 
 inline size_t vkc_dtype_size(int dt) { return dt == VKC_F32 || dt == VKC_I32 ? 4 : 2; }
 

@@ -1,5 +1,6 @@
 // Context, memory, boundary transfers, graph capture and timers of libvknn_cuda.
 #include "common.cuh"
+#include <cstdlib>
 #include "tensormap.cuh"
 
 namespace {
@@ -73,6 +74,7 @@ int vkc_ctx_create(int device_ordinal, vkc_ctx **out) {
     vkc_ctx *ctx  = new vkc_ctx();
     ctx->device   = device_ordinal;
     ctx->sm_count = prop.multiProcessorCount;
+    if (const char *e = getenv("VKNN_PDL")) ctx->dep_launch = atoi(e) != 0;
     ctx->cc_major = prop.major;
     if (cudaSetDevice(device_ordinal) != cudaSuccess || cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking) != cudaSuccess ||
         cudaMalloc(&ctx->dev_err, sizeof(int)) != cudaSuccess || cudaMemset(ctx->dev_err, 0, sizeof(int)) != cudaSuccess ||

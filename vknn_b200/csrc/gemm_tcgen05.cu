@@ -68,16 +68,24 @@ namespace {
         return ptx::fmul2(t, c(0.5f));
     }
 
-    template <int BN, int kStages> constexpr int smem_bytes() {
-        return kStages * (BM * BK * 2 + BN * BK * 2) + 1024 /*align*/ + 256 /*barriers*/ + BN * 4 /*bias*/;
+    // Split-K: kSplit CTAs of a cluster each accumulate a K range of the same output tile; the 64-column slabs of the
+    // tile are dealt out round-robin to the CTAs, which receive the other CTAs' fp32 partials for their slabs in a
+    // dedicated shared-memory area (32 KB per slab and sender) and run the epilogue on the sum.
+    constexpr int recv_bytes(int bn, int split) {
+        return split > 1 ? (split - 1) * (((bn + 63) / 64 + split - 1) / split) * 32768 : 0;
+    }
+    template <int BN, int kStages, int kSplit = 1> constexpr int smem_bytes() {
+        return kStages * (BM * BK * 2 + BN * BK * 2) + 1024 /*align*/ + 256 /*barriers*/ + 1024 /*bias, BN <= 256 floats*/ + recv_bytes(BN, kSplit);
     }
     __host__ __device__ constexpr int tmem_cols(int bn) { return bn <= 32 ? 32 : bn <= 64 ? 64 : bn <= 128 ? 128 : 256; } // power of two >= BN
 
-    template <int BN, int kStages, int kCtasPerSm, typename T, bool B_KN>
+    template <int BN, int kStages, int kCtasPerSm, typename T, bool B_KN, int kSplit = 1>
     __global__ void __launch_bounds__(kThreads, kCtasPerSm)
         gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmD,
                             const __grid_constant__ CUtensorMap tmR, GemmParams p) {
         static_assert((BN / 64 + (BN % 64 != 0)) * 16384 <= kStages * (BM * BK * 2 + BN * BK * 2), "epilogue staging must fit in the operand ring");
+        static_assert(kSplit == 1 || 65536 + ((BN + 63) / 64 - ((BN + 63) / 64) / kSplit) * 32768 <= kStages * (BM * BK * 2 + BN * BK * 2),
+                      "split-K send staging must fit in the operand ring behind the epilogue staging");
         constexpr uint32_t A_BYTES = BM * BK * 2;
         constexpr uint32_t B_BYTES = BN * BK * 2;
         constexpr bool     kBf16   = std::is_same<T, __nv_bfloat16>::value;
@@ -94,12 +102,20 @@ namespace {
         // ctl[0] = tmem base (written by tcgen05.alloc), ctl[1] = abort flag
         const uint32_t sSlot = sBar + 8 * (2 * kStages + 1);
         float         *sbias = (float *) (gbase + kStages * (A_BYTES + B_BYTES) + 256); // BN floats
+        // split-K only: receive area for the other CTAs' partials and the mbarrier their arrivals complete
+        constexpr int  kSlabsAll = (BN + 63) / 64, kOwnMax = (kSlabsAll + kSplit - 1) / kSplit;
+        const uint32_t sRecv     = base + kStages * (A_BYTES + B_BYTES) + 256 + 1024;
+        const uint32_t sRecvBar  = sBar + 8 * (2 * kStages + 6);
 
         const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-        const int m0 = blockIdx.x * BM, n0 = blockIdx.y * BN, bz = blockIdx.z;
+        const int krank = kSplit > 1 ? (int) ptx::cluster_ctarank() : 0; // = blockIdx.x % kSplit
+        const int m0 = (blockIdx.x / kSplit) * BM, n0 = blockIdx.y * BN, bz = blockIdx.z;
         long long *tl = (p.timeline && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) ? p.timeline : nullptr;
         if (tl && threadIdx.x == 0) tl[0] = clock64();
-        const int num_kb = (int) ((p.K + BK - 1) / BK);
+        const int num_kb_all = (int) ((p.K + BK - 1) / BK);
+        const int kb_per     = (num_kb_all + kSplit - 1) / kSplit; // the launcher guarantees every rank a non-empty range
+        const int kb0        = krank * kb_per;
+        const int num_kb     = (kb0 + kb_per < num_kb_all ? kb0 + kb_per : num_kb_all) - kb0;
 
         if (threadIdx.x == 0) {
             for (int s = 0; s < kStages; ++s) {
@@ -108,6 +124,7 @@ namespace {
             }
             ptx::mbar_init(sBar + 8 * 2 * kStages, 1);
             for (int w = 0; w < 4; ++w) ptx::mbar_init(sBar + 8 * (2 * kStages + 2 + w), 1); // residual tile landed, per epilogue warp
+            if (kSplit > 1) ptx::mbar_init(sRecvBar, 1); // this CTA's own arrival; the partials arrive as transaction bytes
             ctl[1] = 0;
             ptx::fence_mbar_init();
             ptx::prefetch_tmap(&tmA);
@@ -117,6 +134,17 @@ namespace {
             ptx::tmem_alloc(sSlot, tmem_cols(BN));
             ptx::tmem_relinquish();
         }
+        if (kSplit > 1) {
+            if (threadIdx.x == 0) {
+                int mine = 0;
+                for (int sl = krank; sl < kSlabsAll; sl += kSplit)
+                    if ((int64_t) n0 + sl * 64 < p.N) ++mine;
+                ptx::mbar_expect_tx(sRecvBar, (uint32_t) ((kSplit - 1) * mine) * 32768u);
+            }
+            ptx::cluster_arrive(); // barriers exist; the matching wait sits in front of each role's first use of a peer
+        }
+        vkc_grid_dep_wait(); // everything above overlapped the previous kernel's tail; global memory from here on
+        vkc_grid_dep_launch();
         if (warp >= 2 && (p.epilogue & VKC_EPI_BIAS)) {
             for (int j = threadIdx.x - 64; j < BN; j += kThreads - 64) sbias[j] = (int64_t) n0 + j < p.N ? __ldg(p.bias + n0 + j) : 0.f;
         }
@@ -132,18 +160,20 @@ namespace {
                 for (int kb = 0; kb < num_kb; ++kb) {
                     const int      s  = kb % kStages;
                     const uint32_t ph = (kb / kStages) & 1;
+                    const int      kx = (kb0 + kb) * BK; // element offset along K
                     if (!ptx::mbar_wait(sBar + 8 * (kStages + s), ph ^ 1, ctl + 1, p.dev_err)) break;
                     const uint32_t full = sBar + 8 * s;
                     ptx::mbar_expect_tx(full, A_BYTES + B_BYTES);
-                    ptx::tma_load_3d(sA + s * A_BYTES, &tmA, kb * BK, m0, za, full);
+                    ptx::tma_load_3d(sA + s * A_BYTES, &tmA, kx, m0, za, full);
                     if (!B_KN) {
-                        ptx::tma_load_3d(sB + s * B_BYTES, &tmB, kb * BK, n0, zb, full);
+                        ptx::tma_load_3d(sB + s * B_BYTES, &tmB, kx, n0, zb, full);
                     } else {
 #pragma unroll
-                        for (int c = 0; c < BN / 64; ++c) ptx::tma_load_3d(sB + s * B_BYTES + c * (BK * 128), &tmB, n0 + c * 64, kb * BK, zb, full);
+                        for (int c = 0; c < BN / 64; ++c) ptx::tma_load_3d(sB + s * B_BYTES + c * (BK * 128), &tmB, n0 + c * 64, kx, zb, full);
                     }
                 }
             }
+            if (kSplit > 1) ptx::cluster_wait();
         } else if (warp == 1) {
             if (ptx::elect_one()) {
                 bool ok = true;
@@ -166,11 +196,51 @@ namespace {
                 if (ok) ptx::tc_commit(sBar + 8 * 2 * kStages); // accumulator complete
                 if (tl) tl[3] = clock64();
             }
+            if (kSplit > 1) ptx::cluster_wait();
         } else {
             const bool ok = ptx::mbar_wait(sBar + 8 * 2 * kStages, 0, ctl + 1, p.dev_err);
             ptx::tc_fence_after();
             if (tl && threadIdx.x == 64) tl[4] = clock64();
-            if (ok) {
+            bool recv_ok = true;
+            if (kSplit > 1) {
+                // Send this CTA's partial of every slab it does not own to the owner: each warp stages its 32 rows of the
+                // slab (256 bytes per row, 16-byte chunks XOR-swizzled by row & 7) in the idle operand ring behind the
+                // epilogue's own staging blocks, then one bulk copy moves the 8 KB into the owner's receive area and
+                // credits the owner's mbarrier.
+                const int q = warp & 3;
+                ptx::cluster_wait();
+                if (ok) {
+                    int nth = 0; // ordinal of the slab among the ones this CTA sends
+#pragma unroll 1
+                    for (int sl = 0; sl < kSlabsAll; ++sl) {
+                        const int owner = sl % kSplit;
+                        if (owner == krank) continue;
+                        if ((int64_t) n0 + sl * 64 >= p.N) break;
+                        const int      slot  = (krank - owner - 1 + kSplit) % kSplit;
+                        const uint32_t stage = base + 65536u + (uint32_t) (nth * 32768 + q * 8192);
+                        const uint32_t dst   = sRecv + (uint32_t) ((slot * kOwnMax + sl / kSplit) * 32768 + q * 8192);
+                        ++nth;
+#pragma unroll
+                        for (int hf = 0; hf < 2; ++hf) {
+                            uint32_t r[32];
+                            ptx::tmem_ld_x32(tmem + ((uint32_t) (q * 32) << 16) + (uint32_t) (sl * 64 + hf * 32), r);
+                            ptx::tc_wait_ld();
+#pragma unroll
+                            for (int u = 0; u < 8; ++u)
+                                ptx::st_shared_v4(stage + (uint32_t) (lane * 256 + (((hf * 8 + u) ^ (lane & 7)) << 4)), r[4 * u], r[4 * u + 1], r[4 * u + 2],
+                                                  r[4 * u + 3]);
+                        }
+                        ptx::fence_proxy_async();
+                        __syncwarp();
+                        if (lane == 0) ptx::bulk_copy_to_peer(ptx::mapa(dst, (uint32_t) owner), stage, 8192u, ptx::mapa(sRecvBar, (uint32_t) owner));
+                    }
+                }
+                if (tl && threadIdx.x == 64) tl[7] = clock64();
+                recv_ok = ptx::mbar_wait_cluster(sRecvBar, 0, ctl + 1, p.dev_err);
+                recv_ok = __all_sync(0xffffffffu, recv_ok);
+                if (tl && threadIdx.x == 64) tl[8] = clock64();
+            }
+            if (ok && recv_ok) {
                 const int     q   = warp & 3; // the TMEM lane quarter this warp may address
                 const int64_t m   = (int64_t) m0 + q * 32 + lane;
                 T            *drow = (T *) p.D + (int64_t) bz * p.stride_d + m * p.ldd;
@@ -183,32 +253,50 @@ namespace {
                     // hit different banks). The residual slab is TMA-loaded into the same block, the result is written
                     // over it and leaves with one TMA store: global traffic is full 128-byte lines both ways.
                     constexpr int kSlabs = (BN + 63) / 64;
-                    const uint32_t rbar  = sBar + 8 * (2 * kStages + 2 + q);
                     const int      row0  = m0 + q * 32;
                     const bool     rows_in = row0 < p.M; // warp-uniform
-                    int            nslab = 0;
+                    const uint32_t rbar  = sBar + 8 * (2 * kStages + 2 + q);
+                    int            nslab = 0, nmine = 0; // slabs inside N; of those, the ones this CTA finishes
                     for (int sl = 0; sl < kSlabs; ++sl)
-                        if ((int64_t) n0 + sl * 64 < p.N) nslab = sl + 1;
+                        if ((int64_t) n0 + sl * 64 < p.N) {
+                            nslab = sl + 1;
+                            if (sl % kSplit == krank) ++nmine;
+                        }
                     bool rok = true;
-                    if ((p.epilogue & VKC_EPI_RESIDUAL) && rows_in) {
+                    if ((p.epilogue & VKC_EPI_RESIDUAL) && rows_in && nmine > 0) {
                         if (lane == 0) {
-                            ptx::mbar_expect_tx(rbar, (uint32_t) nslab * 4096u);
-                            for (int sl = 0; sl < nslab; ++sl) ptx::tma_load_3d(base + sl * 16384 + q * 4096, &tmR, n0 + sl * 64, row0, bz, rbar);
+                            ptx::mbar_expect_tx(rbar, (uint32_t) nmine * 4096u);
+                            for (int sl = krank; sl < nslab; sl += kSplit) ptx::tma_load_3d(base + sl * 16384 + q * 4096, &tmR, n0 + sl * 64, row0, bz, rbar);
                         }
                         rok = ptx::mbar_wait(rbar, 0, ctl + 1, p.dev_err);
                         rok = __all_sync(0xffffffffu, rok);
                     }
 #pragma unroll 1
-                    for (int sl = 0; sl < nslab && rok; ++sl) {
+                    for (int sl = krank; sl < nslab && rok; sl += kSplit) {
                         uint8_t *blk = gbase + sl * 16384 + q * 4096 + lane * 128;
+                        // both 32-column halves are fetched before the single wait, so that their arithmetic interleaves
+                        uint32_t r2[2][32];
+                        ptx::tmem_ld_x32(tmem + ((uint32_t) (q * 32) << 16) + (uint32_t) (sl * 64), r2[0]);
+                        ptx::tmem_ld_x32(tmem + ((uint32_t) (q * 32) << 16) + (uint32_t) (sl * 64 + 32), r2[1]);
+                        ptx::tc_wait_ld();
 #pragma unroll
                         for (int hf = 0; hf < 2; ++hf) {
-                            uint32_t r[32];
-                            ptx::tmem_ld_x32(tmem + ((uint32_t) (q * 32) << 16) + (uint32_t) (sl * 64 + hf * 32), r);
-                            ptx::tc_wait_ld();
                             float v[32];
 #pragma unroll
-                            for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+                            for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r2[hf][j]);
+                            if (kSplit > 1) {
+                                // add the other CTAs' partials of this row (fixed order: slot 0, 1, ...)
+#pragma unroll
+                                for (int slot = 0; slot < kSplit - 1; ++slot) {
+                                    const uint8_t *rrow_ = gbase + kStages * (A_BYTES + B_BYTES) + 256 + 1024 +
+                                                           (slot * kOwnMax + sl / kSplit) * 32768 + (q * 32 + lane) * 256;
+#pragma unroll
+                                    for (int u = 0; u < 8; ++u) {
+                                        const float4 pv = *reinterpret_cast<const float4 *>(rrow_ + (((hf * 8 + u) ^ (lane & 7)) << 4));
+                                        v[4 * u] += pv.x, v[4 * u + 1] += pv.y, v[4 * u + 2] += pv.z, v[4 * u + 3] += pv.w;
+                                    }
+                                }
+                            }
                             if (p.epilogue & VKC_EPI_BIAS) {
 #pragma unroll
                                 for (int j = 0; j < 32; j += 4) {
@@ -246,7 +334,7 @@ namespace {
                             ptx::bulk_commit_group();
                         }
                     }
-                    if (lane == 0) ptx::bulk_wait_group_0();
+                    if (lane == 0) ptx::bulk_wait_group_read_0();
                     __syncwarp();
                 } else
 #pragma unroll 1
@@ -308,43 +396,80 @@ namespace {
         ptx::tc_fence_before();
         __syncthreads();
         if (warp == 1) ptx::tmem_dealloc(tmem, tmem_cols(BN));
+        if (kSplit > 1) ptx::cluster_sync(); // no CTA releases its shared memory while another may still write into it
         if (tl && threadIdx.x == 0) tl[6] = clock64();
     }
 
-    template <int BN, int kStages, int kCtasPerSm, typename T, bool B_KN>
+    template <int BN, int kStages, int kCtasPerSm, typename T, bool B_KN, int kSplit = 1>
     int launch(vkc_ctx *ctx, const CUtensorMap &tmA, const CUtensorMap &tmB, const CUtensorMap &tmD, const CUtensorMap &tmR, const GemmParams &p,
                int64_t batch, cudaStream_t st) {
-        auto          kern = gemm_tcgen05_kernel<BN, kStages, kCtasPerSm, T, B_KN>;
-        constexpr int smem = smem_bytes<BN, kStages>();
+        auto          kern = gemm_tcgen05_kernel<BN, kStages, kCtasPerSm, T, B_KN, kSplit>;
+        constexpr int smem = smem_bytes<BN, kStages, kSplit>();
         static_assert(smem * kCtasPerSm <= 227 * 1024, "shared memory budget");
+        static_assert(8 * (2 * kStages + 7) <= 256, "barrier area");
         if (int rc = vkc_configure_smem(ctx, kern, smem)) return rc;
-        dim3 grid((unsigned) ((p.M + BM - 1) / BM), (unsigned) ((p.N + BN - 1) / BN), (unsigned) batch);
-        kern<<<grid, kThreads, smem, st>>>(tmA, tmB, tmD, tmR, p);
+        dim3 grid((unsigned) ((p.M + BM - 1) / BM) * kSplit, (unsigned) ((p.N + BN - 1) / BN), (unsigned) batch);
+        vkc_launch_cluster(ctx, kern, grid, dim3(kThreads), smem, st, (unsigned) kSplit, tmA, tmB, tmD, tmR, p);
         return vkc_post_launch(ctx, "gemm_tcgen05");
     }
 
     // Tile width: fewest waves over the SMs first, then the least padded work. Wide tiles re-read A less often.
-    struct TileChoice {
-        int bn;
-        bool two_ctas;
+    // Configurations the launcher can pick: tile width, ring depth, CTAs per SM, split-K factor.
+    enum TileConfig {
+        kCfg256x4x1, // 256 wide, 4 stages, one CTA per SM: large problems
+        kCfg256x2x2,
+        kCfg192x2x2,
+        kCfg128x3x2,
+        kCfg64x4x2,
+        kCfg192x5x1,   // deep ring, one CTA per SM: a single wave of long-K tiles
+        kCfg128x6x1,
+        kCfg192x4x1s2, // split-K over a cluster of two CTAs
+        kCfg256x3x1s2,
+        kCfg128x5x1s2,
     };
-    TileChoice choose_tile(int64_t M, int64_t N, int64_t batch, int sms) {
-        const int64_t mt = (M + BM - 1) / BM;
-        TileChoice    best {128, true};
+    struct TileChoice {
+        TileConfig cfg;
+        int        bn;
+    };
+    // Measured behaviour behind the rules: a tile's K loop is fed at 55-85 bytes per clock per SM from L2, so long-K
+    // problems that fit one wave want the deepest ring that fits (one CTA per SM); when even the widest tiles leave most
+    // SMs idle, splitting K over a cluster of two fills them; short-K problems are dominated by prologue and epilogue
+    // and run best as two co-resident CTAs per SM.
+    TileChoice choose_tile(int64_t M, int64_t N, int64_t K, int64_t batch, int sms, bool can_split) {
+        const int64_t mt     = (M + BM - 1) / BM;
+        auto          tiles  = [&](int bn) { return mt * ((N + bn - 1) / bn) * batch; };
+        const int64_t num_kb = (K + BK - 1) / BK;
+        if (tiles(256) >= 4 * (int64_t) sms) return {kCfg256x4x1, 256};
+        if (num_kb >= 16) {
+            // one-wave candidates, scored by busy SMs (ties: wider tile = less operand traffic)
+            struct Cand {
+                TileConfig cfg;
+                int        bn, split;
+            };
+            const Cand cands[5] = {{kCfg192x5x1, 192, 1}, {kCfg128x6x1, 128, 1}, {kCfg192x4x1s2, 192, 2}, {kCfg256x3x1s2, 256, 2}, {kCfg128x5x1s2, 128, 2}};
+            int64_t    best_ctas = 0;
+            int        best      = -1;
+            for (int i = 0; i < 5; ++i) {
+                if (cands[i].split > 1 && (!can_split || num_kb < 8 * cands[i].split)) continue;
+                const int64_t ctas = tiles(cands[i].bn) * cands[i].split;
+                if (ctas > sms) continue;
+                if (ctas > best_ctas) best_ctas = ctas, best = i;
+            }
+            if (best >= 0 && best_ctas * 10 >= (int64_t) sms * 6) return {cands[best].cfg, cands[best].bn};
+        }
+        TileChoice    best {kCfg128x3x2, 128};
         double        best_cost = 1e300;
         const int     cands[4]  = {256, 192, 128, 64};
-        for (int bn : cands) {
-            const int64_t tiles = mt * ((N + bn - 1) / bn) * batch;
+        const TileConfig cfgs[4] = {kCfg256x2x2, kCfg192x2x2, kCfg128x3x2, kCfg64x4x2};
+        for (int i = 0; i < 4; ++i) {
             // two co-resident CTAs share one tensor pipe: model a slot as half an SM
-            const double waves = std::ceil((double) tiles / (2.0 * sms));
-            const double cost  = waves * (bn + 48.0); // per-tile time ~ width + fixed prologue/epilogue
+            const double waves = std::ceil((double) tiles(cands[i]) / (2.0 * sms));
+            const double cost  = waves * (cands[i] + 48.0); // per-tile time ~ width + fixed prologue/epilogue
             if (cost < best_cost - 1e-9) {
                 best_cost = cost;
-                best      = {bn, true};
+                best      = {cfgs[i], cands[i]};
             }
         }
-        // very large problems: the deep 4-stage 256-wide pipeline, one CTA per SM
-        if (mt * ((N + 255) / 256) * batch >= 4 * (int64_t) sms) best = {256, false};
         return best;
     }
 
@@ -369,7 +494,29 @@ int vkc_gemm_tcgen05(vkc_ctx *ctx, const void *A, const void *B, const float *bi
                                          dtype, bn, st);
     }
     const bool a_bcast = stride_a == 0 || batch == 1, b_bcast = stride_b == 0 || batch == 1;
-    const TileChoice tc = choose_tile(M, N, batch, ctx->sm_count);
+    // split-K needs the staged (TMA) epilogue; its alignment conditions are the ones checked for tma_out below
+    const bool can_stage = (ldd % 8 == 0) && (stride_d % 8 == 0) && (((uintptr_t) D & 15) == 0) &&
+                           (!(epilogue & VKC_EPI_RESIDUAL) || (((uintptr_t) residual & 15) == 0));
+    // output / residual maps for the staged epilogue (box = 64 columns x 32 rows, one per epilogue warp and slab)
+    CUtensorMap tmD, tmR;
+    memset(&tmD, 0, sizeof tmD);
+    memset(&tmR, 0, sizeof tmR);
+    bool tma_out = false;
+    if (can_stage) {
+        uint64_t dims[3] = {(uint64_t) N, (uint64_t) M, (uint64_t) batch};
+        uint64_t str[2]  = {(uint64_t) ldd * 2, (uint64_t) (batch > 1 ? (uint64_t) stride_d * 2 : (uint64_t) ldd * 2 * (uint64_t) M)};
+        uint32_t box[3]  = {64, 32, 1};
+        int      rc      = vkc_make_tmap(ctx, &tmD, dtype, D, 3, dims, str, box);
+        if (rc == VKC_OK && (epilogue & VKC_EPI_RESIDUAL)) rc = vkc_make_tmap(ctx, &tmR, dtype, residual, 3, dims, str, box);
+        tma_out = rc == VKC_OK;
+    }
+
+    TileChoice tc = choose_tile(M, N, K, batch, ctx->sm_count, tma_out);
+    if (const char *e = getenv("VKNN_GEMM_TILE")) { // development switch: force a configuration by its enum index
+        const int v = atoi(e);
+        const int bns[10] = {256, 256, 192, 128, 64, 192, 128, 192, 256, 128};
+        if (v >= 0 && v < 10 && (v < 7 || (tma_out && (K + BK - 1) / BK >= 4))) tc = {(TileConfig) v, bns[v]};
+    }
     const int        BN = tc.bn;
 
     CUtensorMap tmA, tmB;
@@ -407,33 +554,31 @@ int vkc_gemm_tcgen05(vkc_ctx *ctx, const void *A, const void *B, const float *bi
     p.b_bcast  = b_bcast;
     p.dev_err  = ctx->dev_err;
     p.timeline = ctx->timeline;
-    // output / residual maps for the staged epilogue (box = 64 columns x 32 rows, one per epilogue warp and slab)
-    CUtensorMap tmD = tmA, tmR = tmA;
-    p.tma_out       = 0;
-    if ((ldd % 8 == 0) && (stride_d % 8 == 0) && (((uintptr_t) D & 15) == 0) && (!(epilogue & VKC_EPI_RESIDUAL) || (((uintptr_t) residual & 15) == 0))) {
-        uint64_t dims[3] = {(uint64_t) N, (uint64_t) M, (uint64_t) batch};
-        uint64_t str[2]  = {(uint64_t) ldd * 2, (uint64_t) (batch > 1 ? (uint64_t) stride_d * 2 : (uint64_t) ldd * 2 * (uint64_t) M)};
-        uint32_t box[3]  = {64, 32, 1};
-        int      rc      = vkc_make_tmap(ctx, &tmD, dtype, D, 3, dims, str, box);
-        if (rc == VKC_OK && (epilogue & VKC_EPI_RESIDUAL)) rc = vkc_make_tmap(ctx, &tmR, dtype, residual, 3, dims, str, box);
-        p.tma_out = rc == VKC_OK ? 1 : 0;
-    }
-
+    p.tma_out  = tma_out ? 1 : 0;
 #define VKC_GEMM_LAUNCH(BN_, ST_, C_, T_)                                                                       \
     (b_layout == VKC_B_KN ? launch<BN_, ST_, C_, T_, true>(ctx, tmA, tmB, tmD, tmR, p, batch, st) \
                           : launch<BN_, ST_, C_, T_, false>(ctx, tmA, tmB, tmD, tmR, p, batch, st))
+#define VKC_GEMM_LAUNCH_S(BN_, ST_, C_, T_, S_)                                                                    \
+    (b_layout == VKC_B_KN ? launch<BN_, ST_, C_, T_, true, S_>(ctx, tmA, tmB, tmD, tmR, p, batch, st) \
+                          : launch<BN_, ST_, C_, T_, false, S_>(ctx, tmA, tmB, tmD, tmR, p, batch, st))
 #define VKC_GEMM_BY_TILE(T_)                                                         \
     do {                                                                             \
-        if (!tc.two_ctas) return VKC_GEMM_LAUNCH(256, 4, 1, T_);                     \
-        switch (BN) {                                                                \
-            case 256: return VKC_GEMM_LAUNCH(256, 2, 2, T_);                         \
-            case 192: return VKC_GEMM_LAUNCH(192, 2, 2, T_);                         \
-            case 128: return VKC_GEMM_LAUNCH(128, 3, 2, T_);                         \
-            default: return VKC_GEMM_LAUNCH(64, 4, 2, T_);                           \
+        switch (tc.cfg) {                                                            \
+            case kCfg256x4x1: return VKC_GEMM_LAUNCH(256, 4, 1, T_);                 \
+            case kCfg256x2x2: return VKC_GEMM_LAUNCH(256, 2, 2, T_);                 \
+            case kCfg192x2x2: return VKC_GEMM_LAUNCH(192, 2, 2, T_);                 \
+            case kCfg128x3x2: return VKC_GEMM_LAUNCH(128, 3, 2, T_);                 \
+            case kCfg64x4x2: return VKC_GEMM_LAUNCH(64, 4, 2, T_);                   \
+            case kCfg192x5x1: return VKC_GEMM_LAUNCH(192, 5, 1, T_);                 \
+            case kCfg128x6x1: return VKC_GEMM_LAUNCH(128, 6, 1, T_);                 \
+            case kCfg192x4x1s2: return VKC_GEMM_LAUNCH_S(192, 4, 1, T_, 2);          \
+            case kCfg256x3x1s2: return VKC_GEMM_LAUNCH_S(256, 3, 1, T_, 2);          \
+            default: return VKC_GEMM_LAUNCH_S(128, 5, 1, T_, 2);                     \
         }                                                                            \
     } while (0)
     if (dtype == VKC_F16) VKC_GEMM_BY_TILE(__half);
     VKC_GEMM_BY_TILE(__nv_bfloat16);
 #undef VKC_GEMM_BY_TILE
 #undef VKC_GEMM_LAUNCH
+#undef VKC_GEMM_LAUNCH_S
 }

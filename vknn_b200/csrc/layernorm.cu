@@ -30,6 +30,8 @@ namespace {
         const int64_t  nwarps   = (int64_t) gridDim.x * (blockDim.x >> 5);
         int64_t        row      = (int64_t) blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
         if (row >= rows) return;
+        vkc_grid_dep_wait();
+        vkc_grid_dep_launch();
 
         float g[CHUNKS][VN], bt[CHUNKS][VN];
 #pragma unroll
@@ -116,6 +118,8 @@ namespace {
         const int     lane = threadIdx.x & 31;
         const int64_t row  = (int64_t) blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
         if (row >= rows) return;
+        vkc_grid_dep_wait();
+        vkc_grid_dep_launch();
         const T *xr = X + row * norm;
         T       *yr = Y + row * norm;
         float    s  = 0.f;
@@ -144,7 +148,7 @@ namespace {
                                 (!beta || ((uintptr_t) beta & 15) == 0);
         const int64_t chunks  = (norm + 32 * VN - 1) / (32 * VN);
         if (blocks > INT32_MAX) return vkc_fail(ctx, VKC_ERR_UNSUPPORTED, "layernorm: too many rows");
-#define VKC_LN(C) layernorm_kernel<T, C><<<(unsigned) pblocks, wpb * 32, 0, st>>>((const T *) X, gamma, beta, (T *) Y, rows, (int) norm, eps)
+#define VKC_LN(C) vkc_launch(ctx, layernorm_kernel<T, C>, dim3((unsigned) pblocks), dim3(wpb * 32), 0, st, (const T *) X, gamma, beta, (T *) Y, rows, (int) norm, eps)
         if (aligned && chunks <= 8) {
             switch (chunks) {
                 case 1: VKC_LN(1); break;
@@ -157,7 +161,7 @@ namespace {
                 default: VKC_LN(8); break;
             }
         } else {
-            layernorm_generic_kernel<T><<<(unsigned) blocks, wpb * 32, 0, st>>>((const T *) X, gamma, beta, (T *) Y, rows, norm, eps);
+            vkc_launch(ctx, layernorm_generic_kernel<T>, dim3((unsigned) blocks), dim3(wpb * 32), 0, st, (const T *) X, gamma, beta, (T *) Y, rows, norm, eps);
         }
 #undef VKC_LN
         return vkc_post_launch(ctx, "layernorm");

@@ -92,6 +92,9 @@ namespace ptx {
     }
     __device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
     __device__ __forceinline__ void bulk_wait_group_0() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+    // Waits only until the committed bulk stores have read their shared-memory source (enough before the CTA exits or
+    // reuses the staging area; the global writes complete on their own).
+    __device__ __forceinline__ void bulk_wait_group_read_0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
     // Untiled bulk copy of `bytes` contiguous bytes (both addresses 16-byte aligned, size a multiple of 16).
     __device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
         asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src), "r"(bytes),
@@ -209,6 +212,54 @@ namespace ptx {
     }
     __device__ __forceinline__ void cluster_sync() {
         asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+    }
+    // Split-K reduction through distributed shared memory: 16-byte store into a peer CTA's shared memory, arrival on a
+    // peer's mbarrier with cluster-scope release, and the matching bounded wait with cluster-scope acquire.
+    __device__ __forceinline__ void st_cluster_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+        asm volatile("st.shared::cluster.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+    }
+    __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+    }
+    __device__ __forceinline__ void fence_acq_rel_cluster() { asm volatile("fence.acq_rel.cluster;" ::: "memory"); }
+    __device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster_addr) {
+        asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster_addr) : "memory");
+    }
+    // Bulk copy from this CTA's shared memory into a peer CTA's (shared::cluster addresses for destination and barrier);
+    // the bytes are credited to the peer's mbarrier. Addresses and size are multiples of 16.
+    __device__ __forceinline__ void bulk_copy_to_peer(uint32_t dst_cluster, uint32_t src_cta, uint32_t bytes, uint32_t bar_cluster) {
+        asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst_cluster), "r"(src_cta),
+                     "r"(bytes), "r"(bar_cluster)
+                     : "memory");
+    }
+    // The two halves of a cluster barrier, so that work can sit between the arrival and the wait.
+    __device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release;" ::: "memory"); }
+    __device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire;" ::: "memory"); }
+    __device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
+        uint32_t ok;
+        asm volatile(
+            "{\n"
+            ".reg .pred p;\n"
+            "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n"
+            "selp.u32 %0, 1, 0, p;\n"
+            "}\n"
+            : "=r"(ok)
+            : "r"(bar), "r"(parity)
+            : "memory");
+        return ok != 0;
+    }
+    __device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, volatile int *abort_flag, int *dev_err) {
+        if (mbar_try_wait_cluster(bar, parity)) return true;
+        const long long t0 = clock64();
+        for (;;) {
+            if (mbar_try_wait_cluster(bar, parity)) return true;
+            if (*abort_flag) return false;
+            if (clock64() - t0 > kWaitLimitCycles) {
+                *abort_flag = 1;
+                atomicCAS(dev_err, 0, 1 /* VKC_DEVERR_WAIT_TIMEOUT */);
+                return false;
+            }
+        }
     }
     // Tiled load issued by either CTA of a pair; the completion bytes go to the mbarrier at `bar`, which may live in
     // the other CTA of the pair (a shared::cluster address).

@@ -2,15 +2,25 @@
 //
 //   D[b,m,n] = epi( sum_k A[b,m,k] * B[b,k,n] ),  A/B/D in f16 or bf16, fp32 accumulation in tensor memory.
 //
-// One CTA computes one 128 x BN output tile (BN in {64, 128, 192, 256}, chosen per problem to fill the 148 SMs in
-// as few waves as possible). Small and medium problems run two CTAs per SM so that one CTA's epilogue overlaps the
-// other's main loop. Warp roles:
+// One CTA computes one 128 x BN output tile (BN in {64, 128, 192, 256}). The launcher picks tile width, ring depth,
+// CTAs per SM and a split-K factor per problem: short-K problems run two CTAs per SM so that one CTA's epilogue
+// overlaps the other's main loop; long-K problems that fit a single wave run one CTA per SM with the deepest operand
+// ring that fits; when even the widest tiles leave most SMs idle, K is split over a thread-block cluster of two CTAs.
+// Warp roles:
 //   warp 0   : TMA producer  — one elected lane streams 128x64 A tiles and BNx64 B tiles (128-byte swizzle)
 //              through a multi-stage shared-memory ring, completion on per-stage "full" mbarriers;
 //   warp 1   : MMA issuer    — owns the tensor-memory allocation; one elected lane issues four
 //              tcgen05.mma (M=128, N=BN, K=16) per stage and commits the stage's "empty" mbarrier;
 //   warps 2-5: epilogue      — each warp owns the 32 TMEM lanes (= output rows) it may address, reads the
-//              accumulator with tcgen05.ld in 32-column slabs, applies the epilogue in fp32 and stores.
+//              accumulator with tcgen05.ld, applies the epilogue in fp32, packs to the storage type into a
+//              128-byte-swizzled staging block in the idle operand ring and stores each 64-column slab with one
+//              TMA store (the residual slab is TMA-loaded into the same block first).
+// Split-K: the CTAs of a cluster accumulate disjoint K ranges of the same tile; the tile's 64-column slabs are dealt
+// out round-robin; every CTA stages its fp32 partial of the slabs it does not own in its ring and bulk-copies it
+// (cp.async.bulk shared::cta -> shared::cluster) into the owner's receive area, crediting the owner's mbarrier with
+// the bytes; the owner adds the partials in a fixed order and runs the epilogue. No global scratch, no second kernel.
+// The kernel sets up barriers and tensor memory before griddepcontrol.wait, so under programmatic dependent launch
+// its prologue overlaps the previous kernel's tail.
 // B is taken either as [N,K] rows (K contiguous, "K-major") or as [K,N] rows (N contiguous, "MN-major"),
 // so weights in the reference's row-major [K,N] initializer layout are consumed without a transpose.
 // M/N/K tails rely on TMA zero fill for loads and on predicated stores.

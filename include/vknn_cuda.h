@@ -74,6 +74,17 @@ VKC_API int vkc_upload(vkc_ctx *ctx, void *dst_dev, int dst_dtype, const void *s
 VKC_API int vkc_download(vkc_ctx *ctx, void *dst_host, int dst_dtype, const void *src_dev, int src_dtype, int64_t n, vkc_stream stream);
 VKC_API int vkc_convert(vkc_ctx *ctx, void *dst_dev, int dst_dtype, const void *src_dev, int src_dtype, int64_t n, vkc_stream stream);
 
+/* ---- device-resident inputs and outputs. Reference: IOTensor::dmaBufFd / Tensor::fromDmaBuf / toDmaBuf
+ * (include/vknn/io_tensor.h:11-23, include/vknn/tensor_class.h:17-29) — the caller names a device buffer by an integer
+ * that Session::run passes through untouched (src/core/session.cpp:688-696,715-728) and the device segment binds it as
+ * the boundary buffer (src/backend/vulkan/vk_backend.cpp:1218-1260,1339-1382). A CUDA pointer has no file descriptor, so
+ * the caller registers it here and hands the returned handle (>= 0x40000000, never a valid fd) to fromDmaBuf/toDmaBuf;
+ * the CUDA segment resolves it and converts on the device, with no host staging. The table is process-wide like the
+ * fd namespace; the caller keeps ownership of the memory and unregisters before freeing it. ---- */
+VKC_API int vkc_extbuf_register(void *dptr, size_t bytes, int *handle);
+VKC_API int vkc_extbuf_unregister(int handle);
+VKC_API int vkc_extbuf_lookup(int handle, void **dptr, size_t *bytes);
+
 /* ---- K1: batched GEMM with fused epilogue. Reference: MatMulCpu::run src/backend/cpu/ops/matmul.cpp:14-116
  * (oracle), shaders/matmul_tiled.comp:13-95 and matmul_tiled_bias.comp:8-87 with host MatMulOp
  * src/backend/vulkan/ops/matmul.cpp:22-181 (device path replaced); the GELU tail Div/Erf/Add/FusedPointwise

@@ -29,6 +29,9 @@
 #include "import/passes.h"
 #include "vknn/graph.h"
 #include "vknn/session.h"
+#ifdef VKNN_DRIVER_HAS_CUDA
+#include "vknn_cuda.h"
+#endif
 #include <algorithm>
 #include <chrono>
 #include <cstdio>
@@ -85,7 +88,7 @@ namespace {
 
 int main(int argc, char **argv) {
     if (argc < 4) {
-        std::fprintf(stderr, "usage: %s spec.txt data.bin out.bin [--backend cpu|cuda] [--precision low|high] [--iters N] [--warmup W]\n", argv[0]);
+        std::fprintf(stderr, "usage: %s spec.txt data.bin out.bin [--backend cpu|cuda] [--precision low|high] [--iters N] [--warmup W] [--vxm-fp16 file] [--device-io]\n", argv[0]);
         return 2;
     }
     std::string specPath = argv[1], dataPath = argv[2], outPath = argv[3];
@@ -93,6 +96,7 @@ int main(int argc, char **argv) {
     int         iters = 1, warmup = 0;
     bool        quiet = false;
     std::string vxmPath;
+    bool        deviceIo = false;
     for (int i = 4; i < argc; ++i) {
         std::string a = argv[i];
         if (a == "--backend" && i + 1 < argc) backend = argv[++i];
@@ -101,6 +105,7 @@ int main(int argc, char **argv) {
         else if (a == "--warmup" && i + 1 < argc) warmup = std::atoi(argv[++i]);
         else if (a == "--quiet") quiet = true;
         else if (a == "--vxm-fp16" && i + 1 < argc) vxmPath = argv[++i];
+        else if (a == "--device-io") deviceIo = true;
     }
 
     std::ifstream spec(specPath);
@@ -249,8 +254,65 @@ int main(int argc, char **argv) {
 
     std::vector<IOTensor> outs;
     std::vector<double>   ms;
+#ifdef VKNN_DRIVER_HAS_CUDA
+    // --device-io: inputs and outputs live in caller-owned CUDA buffers registered with the CUDA library; the Session
+    // carries only their handles (IOTensor::dmaBufFd), exactly as it carries dma-buf fds for the reference's GPU backend.
+    vkc_ctx            *ioCtx = nullptr;
+    std::vector<void *> inDev, outDev;
+    std::vector<int>    outHandle;
+    std::vector<int64_t> outElems;
+    if (deviceIo) {
+        if (backend != "cuda" || vkc_ctx_create(0, &ioCtx) != VKC_OK) {
+            std::printf("{\"ok\": false, \"error\": \"--device-io needs the cuda backend and a device\"}\n");
+            return 1;
+        }
+        for (auto &t : ioIn) {
+            void *d = nullptr;
+            int   h = -1;
+            const int64_t n = numElements(t.shape);
+            if (vkc_alloc(ioCtx, t.data.size(), &d) || vkc_upload(ioCtx, d, VKC_F32, t.data.data(), VKC_F32, n, nullptr) || vkc_sync(ioCtx, nullptr) ||
+                vkc_extbuf_register(d, t.data.size(), &h)) {
+                std::printf("{\"ok\": false, \"error\": \"device-io input set-up: %s\"}\n", vkc_last_error(ioCtx));
+                return 1;
+            }
+            inDev.push_back(d);
+            t.dmaBufFd    = h;
+            t.dmaBufDtype = DType::Float32;
+            t.data.clear();
+        }
+        for (TensorId oid : sess->graph().outputs) {
+            const int64_t n = numElements(sess->graph().tensors[oid].shape);
+            void         *d = nullptr;
+            int           h = -1;
+            if (vkc_alloc(ioCtx, (size_t) n * 4, &d) || vkc_extbuf_register(d, (size_t) n * 4, &h)) {
+                std::printf("{\"ok\": false, \"error\": \"device-io output set-up\"}\n");
+                return 1;
+            }
+            outDev.push_back(d);
+            outHandle.push_back(h);
+            outElems.push_back(n);
+        }
+    }
+#else
+    if (deviceIo) {
+        std::printf("{\"ok\": false, \"error\": \"--device-io is only built into the cuda driver\"}\n");
+        return 1;
+    }
+#endif
     for (int it = 0; it < warmup + iters; ++it) {
         outs.clear();
+#ifdef VKNN_DRIVER_HAS_CUDA
+        if (deviceIo) {
+            size_t k = 0;
+            for (TensorId oid : sess->graph().outputs) {
+                IOTensor b;
+                b.name        = sess->graph().tensors[oid].name;
+                b.dmaBufFd    = outHandle[k++];
+                b.dmaBufDtype = DType::Float32;
+                outs.push_back(std::move(b));
+            }
+        }
+#endif
         auto   t0 = std::chrono::steady_clock::now();
         Status st = sess->run(ioIn, outs);
         auto   t1 = std::chrono::steady_clock::now();
@@ -262,6 +324,28 @@ int main(int argc, char **argv) {
     }
     std::sort(ms.begin(), ms.end());
 
+#ifdef VKNN_DRIVER_HAS_CUDA
+    if (deviceIo) {
+        // the results never touched host memory inside the Session: fetch them from the registered buffers now
+        for (size_t k = 0; k < outs.size(); ++k) {
+            if (!outs[k].data.empty() || outs[k].dmaBufFd != outHandle[k]) {
+                std::printf("{\"ok\": false, \"error\": \"device-io output %zu came back through host memory\"}\n", k);
+                return 1;
+            }
+            outs[k].data.resize((size_t) outElems[k] * 4);
+            if (vkc_download(ioCtx, outs[k].data.data(), VKC_F32, outDev[k], VKC_F32, outElems[k], nullptr) || vkc_sync(ioCtx, nullptr)) {
+                std::printf("{\"ok\": false, \"error\": \"device-io download: %s\"}\n", vkc_last_error(ioCtx));
+                return 1;
+            }
+            vkc_extbuf_unregister(outHandle[k]);
+            vkc_free(ioCtx, outDev[k]);
+        }
+        for (size_t k = 0; k < inDev.size(); ++k) {
+            vkc_extbuf_unregister(ioIn[k].dmaBufFd);
+            vkc_free(ioCtx, inDev[k]);
+        }
+    }
+#endif
     std::ofstream out(outPath, std::ios::binary);
     for (auto &o : outs) {
         out.write(reinterpret_cast<const char *>(o.data.data()), (std::streamsize) o.data.size());

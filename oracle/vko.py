@@ -267,7 +267,7 @@ class RefGraph:
                 s += " ints:%s=%s" % (k, ",".join(str(int(x)) for x in v))
         self.lines.append(s)
 
-    def run(self, backend="cpu", precision="high", iters=1, warmup=0, timeout=3600, vxm_fp16=False):
+    def run(self, backend="cpu", precision="high", iters=1, warmup=0, timeout=3600, vxm_fp16=False, device_io=False):
         exe = REF_DRIVER_CUDA if backend == "cuda" else REF_DRIVER
         if not os.path.exists(exe):
             raise FileNotFoundError(exe)
@@ -281,6 +281,8 @@ class RefGraph:
             cmd = [exe, sp, dp, op, "--backend", backend, "--precision", precision, "--iters", str(iters), "--warmup", str(warmup), "--quiet"]
             if vxm_fp16:  # compile to a .vxm with fp16 weights first, then load the session from the file
                 cmd += ["--vxm-fp16", os.path.join(td, "model.vxm")]
+            if device_io:  # inputs/outputs in registered CUDA buffers (cuda driver only)
+                cmd += ["--device-io"]
             r = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout)
             info = None
             for ln in r.stdout.splitlines():

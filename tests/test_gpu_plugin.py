@@ -82,3 +82,23 @@ def test_fp16_vxm_weights_are_consumed_directly():
     w16 = {k: (v.astype(np.float16).astype(np.float32)) for k, v in w.items()}
     (ref2,), _ = vko.encoder_layer_graph(x, w16, 4).run(backend="cpu")
     assert np.abs(ref - ref2).max() <= 2e-3
+
+
+def test_device_resident_io_matches_host_io():
+    """The CUDA form of the reference's dma-buf I/O: inputs and outputs are caller-owned device buffers named by a
+    registered handle that travels through Session::run in IOTensor::dmaBufFd; the segment converts on the device and
+    the Session performs no host read-back. Results must be bit-identical to the host-buffer route."""
+    rng = np.random.default_rng(12)
+    w = encoder_weights(rng, 256, 512, bias_scale=0.01)
+    x = rng.standard_normal((2, 130, 256)).astype(np.float32)
+    for precision in ("low", "high"):
+        (host,), info_h = vko.encoder_layer_graph(x, w, 4).run(backend="cuda", precision=precision, iters=2)
+        (dev,), info_d = vko.encoder_layer_graph(x, w, 4).run(backend="cuda", precision=precision, iters=2, device_io=True)
+        assert all(n[1] == CUDA_KIND for n in info_d["nodes"])
+        assert dev.shape == host.shape
+        assert np.array_equal(dev, host), precision
+    # attention graph (two MatMuls around a Softmax): same check on the fused attention path
+    q, k, v = (rng.standard_normal((1, 4, 100, 64)).astype(np.float32) for _ in range(3))
+    (host,), _ = vko.attention_graph(q, k, v, 0.125).run(backend="cuda", precision="low")
+    (dev,), _ = vko.attention_graph(q, k, v, 0.125).run(backend="cuda", precision="low", device_io=True)
+    assert np.array_equal(dev, host)

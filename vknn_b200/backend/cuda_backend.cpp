@@ -65,6 +65,13 @@ namespace vknn {
             }
         }
 
+        // dtype of a caller-registered device buffer: fp32 or fp16, row-major (the only boundary formats this backend has)
+        int extDtype(DType d, const std::string &name) {
+            if (d == DType::Float32) return VKC_F32;
+            if (d == DType::Float16) return VKC_F16;
+            fail(Status::Unsupported, "device-resident tensor " + name + ": only Float32 and Float16 buffers are supported");
+        }
+
         int64_t prod(const Shape &s) {
             int64_t n = 1;
             for (int64_t d : s) n *= d;
@@ -835,9 +842,22 @@ namespace vknn {
         // boundary inputs: host fp32 -> device storage precision (conversion on the device)
         for (TensorId id : boundaryInputs) {
             if (initIds_.count(id)) continue; // uploaded in compileSegment; the pool holds no host data for it
-            RtTensor &rt = ctx.t(id);
+            RtTensor   &rt = ctx.t(id);
+            const View &v  = views_.at(id);
+            if (rt.dmaBufFd >= 0) {
+                // device-resident input: the integer names a registered CUDA buffer (the CUDA form of the reference's
+                // dma-buf input, src/backend/vulkan/vk_backend.cpp:1218-1260); converted on the device, no host staging
+                void  *ext   = nullptr;
+                size_t bytes = 0;
+                if (vkc_extbuf_lookup(rt.dmaBufFd, &ext, &bytes) != VKC_OK)
+                    fail(Status::InvalidArgument, "boundary input " + g.desc(id).name + ": handle is not a registered device buffer");
+                const int     sdt = extDtype(rt.dmaBufDtype, g.desc(id).name);
+                const int64_t n   = prod(v.shape);
+                if ((size_t) n * (sdt == VKC_F32 ? 4 : 2) > bytes) fail(Status::InvalidArgument, "boundary input " + g.desc(id).name + ": device buffer too small");
+                check(ctx_, vkc_convert(ctx_, ptrOf(v), dtype_, ext, sdt, n, nullptr), "vkc_convert");
+                continue;
+            }
             if (!rt.hostValid) fail(Status::RuntimeError, "boundary input " + g.desc(id).name + " has no host data");
-            const View &v = views_.at(id);
             if (rt.elems() != prod(v.shape)) fail(Status::InvalidArgument, "boundary input " + g.desc(id).name + " has an unexpected size");
             check(ctx_, vkc_upload(ctx_, ptrOf(v), dtype_, rt.host.bytes.data(), VKC_F32, rt.elems(), nullptr), "vkc_upload");
         }
@@ -864,6 +884,22 @@ namespace vknn {
             RtTensor   &rt = ctx.t(id);
             const View &v  = views_.at(id);
             rt.shape = g.desc(id).shape;
+            if (rt.dmaBufFd >= 0) {
+                // device-resident output (the reference's toDmaBuf binding, vk_backend.cpp:1339-1382): written into the
+                // caller's registered buffer in the declared dtype; the Session then skips its host read-back
+                void  *ext   = nullptr;
+                size_t bytes = 0;
+                if (vkc_extbuf_lookup(rt.dmaBufFd, &ext, &bytes) != VKC_OK)
+                    fail(Status::InvalidArgument, "output " + g.desc(id).name + ": handle is not a registered device buffer");
+                const int     ddt = extDtype(rt.dmaBufDtype, g.desc(id).name);
+                const int64_t n   = prod(v.shape);
+                if ((size_t) n * (ddt == VKC_F32 ? 4 : 2) > bytes) fail(Status::InvalidArgument, "output " + g.desc(id).name + ": device buffer too small");
+                check(ctx_, vkc_convert(ctx_, ext, ddt, ptrOf(v), dtype_, n, nullptr), "vkc_convert");
+                rt.dtype       = rt.dmaBufDtype;
+                rt.hostValid   = false;
+                rt.deviceValid = false;
+                continue;
+            }
             rt.dtype = DType::Float32;
             rt.allocHost();
             check(ctx_, vkc_download(ctx_, rt.host.bytes.data(), VKC_F32, ptrOf(v), dtype_, rt.elems(), nullptr), "vkc_download");

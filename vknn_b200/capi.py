@@ -58,6 +58,9 @@ def load_library():
     L.vkc_launch_count.argtypes = [vp]
     L.vkc_launch_count.restype = i64
     L.vkc_debug_timeline.argtypes = [vp, C.POINTER(C.c_longlong)]
+    L.vkc_extbuf_register.argtypes = [vp, C.c_size_t, C.POINTER(C.c_int)]
+    L.vkc_extbuf_unregister.argtypes = [C.c_int]
+    L.vkc_extbuf_lookup.argtypes = [C.c_int, C.POINTER(vp), C.POINTER(C.c_size_t)]
     L.vkc_alloc.argtypes = [vp, sz, C.POINTER(vp)]
     L.vkc_free.argtypes = [vp, vp]
     L.vkc_upload.argtypes = [vp, vp, i32, vp, i32, i64, vp]

@@ -1,5 +1,8 @@
 // Context, memory, boundary transfers, graph capture and timers of libvknn_cuda.
 #include "common.cuh"
+#include <climits>
+#include <map>
+#include <mutex>
 #include <cstdlib>
 #include "tensormap.cuh"
 
@@ -173,6 +176,38 @@ int vkc_convert(vkc_ctx *ctx, void *dst, int dst_dtype, const void *src, int src
         case VKC_BF16: return convert_from<__nv_bfloat16>(ctx, src, dst, dst_dtype, n, st);
         default: return vkc_fail(ctx, VKC_ERR_INVALID, "convert: bad src dtype %d", src_dtype);
     }
+}
+
+// ---- registry of caller-owned device buffers used as segment inputs / outputs ------------------------------------
+namespace {
+    struct ExtBuf {
+        void  *ptr;
+        size_t bytes;
+    };
+    std::mutex            g_ext_mu;
+    std::map<int, ExtBuf> g_ext;
+    int                   g_ext_next = 0x40000000;
+} // namespace
+
+int vkc_extbuf_register(void *dptr, size_t bytes, int *handle) {
+    if (!dptr || !handle || bytes == 0) return VKC_ERR_INVALID;
+    std::lock_guard<std::mutex> lk(g_ext_mu);
+    if (g_ext_next == INT32_MAX) return VKC_ERR_INVALID;
+    *handle        = g_ext_next++;
+    g_ext[*handle] = {dptr, bytes};
+    return VKC_OK;
+}
+int vkc_extbuf_unregister(int handle) {
+    std::lock_guard<std::mutex> lk(g_ext_mu);
+    return g_ext.erase(handle) ? VKC_OK : VKC_ERR_INVALID;
+}
+int vkc_extbuf_lookup(int handle, void **dptr, size_t *bytes) {
+    std::lock_guard<std::mutex> lk(g_ext_mu);
+    auto                        it = g_ext.find(handle);
+    if (it == g_ext.end()) return VKC_ERR_INVALID;
+    if (dptr) *dptr = it->second.ptr;
+    if (bytes) *bytes = it->second.bytes;
+    return VKC_OK;
 }
 
 int vkc_upload(vkc_ctx *ctx, void *dst_dev, int dst_dtype, const void *src_host, int src_dtype, int64_t n, vkc_stream stream) {

@@ -276,6 +276,8 @@ def bench_encoder(ctx, cfg, steps, warmup, rank, world):
     ys = [torch.empty_like(x) for x in xs]
 
     # the layer is 7 short launches: replay it as a CUDA graph (what the C++ segment does), one graph per input set
+    layer.forward(xs[0], out=ys[0])
+    layer.tune(xs[0])  # per-shape GEMM configuration by measurement, as the C++ segment does at plan time (Hint::Tuning)
     for i in range(ns):
         layer.forward(xs[i], out=ys[i])
     torch.cuda.synchronize()
@@ -303,6 +305,8 @@ def bench_stack(ctx, cfg, steps, warmup, rank, world):
     stack = EncoderStack(ctx, [encoder_weights(rng, d, dm) for _ in range(L)], H, dtype=torch.float16)
     g = torch.Generator(device="cuda").manual_seed(cfg["seed"] + rank)
     x = torch.randn(1, T, d, generator=g, device="cuda", dtype=torch.float32).half()
+    stack.forward(x)
+    stack.tune(x)
     stack.forward(x)
     torch.cuda.synchronize()
     graph, _ = stack.capture(x)

@@ -94,6 +94,16 @@ VKC_API int vkc_extbuf_lookup(int handle, void **dptr, size_t *bytes);
 VKC_API int vkc_gemm(vkc_ctx *ctx, const void *A, const void *B, const float *bias, const void *residual, void *D, int64_t M, int64_t N,
                      int64_t K, int64_t batch, int64_t stride_a, int64_t stride_b, int64_t stride_d, int64_t lda, int64_t ldb,
                      int64_t ldd, int b_layout, int epilogue, int dtype, vkc_stream stream);
+/* The same with the tensor-core kernel's configuration (tile width, ring depth, CTAs per SM, split-K) chosen by the
+ * caller: config in [0, vkc_gemm_config_count()), or -1 for the built-in choice. VKC_ERR_UNSUPPORTED when that
+ * configuration cannot run the problem. Reference counterpart: the per-shape kernel autotune behind Hint::Tuning
+ * (include/vknn/hint.h:8-22; timing loop and table src/backend/vulkan/ops/vk_op_common.h, WeightCache tuning section
+ * src/backend/vulkan/vk_backend.cpp:507-517) — the plug-in times the configurations once per GEMM shape and keeps the
+ * table in the session's cache file. */
+VKC_API int vkc_gemm_config_count(void);
+VKC_API int vkc_gemm_ex(vkc_ctx *ctx, const void *A, const void *B, const float *bias, const void *residual, void *D, int64_t M, int64_t N,
+                        int64_t K, int64_t batch, int64_t stride_a, int64_t stride_b, int64_t stride_d, int64_t lda, int64_t ldb,
+                        int64_t ldd, int b_layout, int epilogue, int dtype, int config, vkc_stream stream);
 
 /* ---- K2: fused prefill attention O = softmax(Q.K^T * scale + mask) . V, never materialising the scores.
  * Reference: the node run Transpose(K) -> MatMul -> Binary Mul / FusedPointwise{Mul,Add mask} -> Softmax -> MatMul

@@ -88,7 +88,7 @@ namespace {
 
 int main(int argc, char **argv) {
     if (argc < 4) {
-        std::fprintf(stderr, "usage: %s spec.txt data.bin out.bin [--backend cpu|cuda] [--precision low|high] [--iters N] [--warmup W] [--vxm-fp16 file] [--device-io]\n", argv[0]);
+        std::fprintf(stderr, "usage: %s spec.txt data.bin out.bin [--backend cpu|cuda] [--precision low|high] [--iters N] [--warmup W] [--vxm-fp16 file] [--device-io] [--cache-file path] [--tuning off|fast|thorough]\n", argv[0]);
         return 2;
     }
     std::string specPath = argv[1], dataPath = argv[2], outPath = argv[3];
@@ -97,6 +97,7 @@ int main(int argc, char **argv) {
     bool        quiet = false;
     std::string vxmPath;
     bool        deviceIo = false;
+    std::string cacheFile, tuning;
     for (int i = 4; i < argc; ++i) {
         std::string a = argv[i];
         if (a == "--backend" && i + 1 < argc) backend = argv[++i];
@@ -106,6 +107,8 @@ int main(int argc, char **argv) {
         else if (a == "--quiet") quiet = true;
         else if (a == "--vxm-fp16" && i + 1 < argc) vxmPath = argv[++i];
         else if (a == "--device-io") deviceIo = true;
+        else if (a == "--cache-file" && i + 1 < argc) cacheFile = argv[++i];
+        else if (a == "--tuning" && i + 1 < argc) tuning = argv[++i];
     }
 
     std::ifstream spec(specPath);
@@ -220,6 +223,8 @@ int main(int argc, char **argv) {
         cfg.backend  = BackendKind::Cpu;
         cfg.fallback = {};
     }
+    cfg.cacheFile = cacheFile; // empty: no cache file (the default of a session built from an in-memory graph)
+    if (!tuning.empty()) cfg.setHint(Hint::Tuning, tuning == "off" ? Mode::NoTune : tuning == "thorough" ? Mode::Thorough : Mode::Fast);
     cfg.applyLogLevel();
 
     std::unique_ptr<Session> sess;

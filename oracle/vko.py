@@ -267,7 +267,7 @@ class RefGraph:
                 s += " ints:%s=%s" % (k, ",".join(str(int(x)) for x in v))
         self.lines.append(s)
 
-    def run(self, backend="cpu", precision="high", iters=1, warmup=0, timeout=3600, vxm_fp16=False, device_io=False):
+    def run(self, backend="cpu", precision="high", iters=1, warmup=0, timeout=3600, vxm_fp16=False, device_io=False, cache_file=None, tuning=None):
         exe = REF_DRIVER_CUDA if backend == "cuda" else REF_DRIVER
         if not os.path.exists(exe):
             raise FileNotFoundError(exe)
@@ -283,6 +283,10 @@ class RefGraph:
                 cmd += ["--vxm-fp16", os.path.join(td, "model.vxm")]
             if device_io:  # inputs/outputs in registered CUDA buffers (cuda driver only)
                 cmd += ["--device-io"]
+            if cache_file:  # Config::cacheFile: the CUDA backend keeps its GEMM autotune table in <cache_file>.cuda
+                cmd += ["--cache-file", cache_file]
+            if tuning:  # Hint::Tuning: off | fast | thorough
+                cmd += ["--tuning", tuning]
             r = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout)
             info = None
             for ln in r.stdout.splitlines():

@@ -373,6 +373,61 @@ def test_encoder_layer(ctx, B, T, d, H, dm):
     assert_low(host(y), ref, "encoder layer")
 
 
+@pytest.mark.parametrize("epi", ["bias", "bias_gelu", "bias_residual"])
+@pytest.mark.parametrize("M,N,K", [(300, 520, 1096), (1000, 256, 2048), (130, 200, 96)])
+def test_gemm_every_configuration(ctx, epi, M, N, K):
+    """Every tile / ring / occupancy / split-K configuration of the tensor-core GEMM (what the autotune chooses from)
+    against the oracle, including ragged M, N and K tails; a configuration may refuse a shape, never mis-compute it."""
+    rng = np.random.default_rng(21)
+    a = round_to(rng.standard_normal((M, K)), torch.float16)
+    b = round_to(0.05 * rng.standard_normal((K, N)), torch.float16)
+    bias = (0.1 * rng.standard_normal(N)).astype(np.float32)
+    res = round_to(rng.standard_normal((M, N)), torch.float16)
+    ref = vko.matmul(a, b, bias)
+    flags = vknn_b200.EPI_BIAS
+    if epi == "bias_gelu":
+        t = vko.binary(ref, np.array([np.float32(1.41421356237)], np.float32), 2)
+        t = vko.unary(t, 15)
+        t = vko.binary(t, np.array([1.0], np.float32), 6)
+        ref = vko.pw_epilogue(t, [0, 0, 1, 0, 0, 0, 2, 0], [0, 0, 0, 0], [ref, np.array([0.5], np.float32)])
+        flags |= vknn_b200.EPI_GELU_ERF
+    if epi == "bias_residual":
+        ref = ref + res
+        flags |= vknn_b200.EPI_RESIDUAL
+    A, Bm, R, bs = dev(a, torch.float16), dev(b, torch.float16), dev(res, torch.float16), torch.from_numpy(bias).cuda()
+    ran = 0
+    for cfg in range(ctx.gemm_config_count()):
+        D = torch.zeros(M, N, dtype=torch.float16, device="cuda")
+        try:
+            ctx.gemm(A, Bm, D, bias=bs, residual=R if epi == "bias_residual" else None, epilogue=flags, config=cfg)
+        except vknn_b200.VkcError as e:
+            assert e.code == -2, str(e)  # VKC_ERR_UNSUPPORTED: this configuration does not take the shape
+            continue
+        ctx.sync()
+        assert_low(host(D), ref, "config %d %s" % (cfg, epi))
+        ran += 1
+    assert ran >= 7
+    with pytest.raises(vknn_b200.VkcError):
+        ctx.gemm(A, Bm, torch.zeros(M, N, dtype=torch.float16, device="cuda"), bias=bs, epilogue=vknn_b200.EPI_BIAS, config=ctx.gemm_config_count())
+
+
+def test_encoder_layer_tuned_matches_untuned(ctx):
+    """EncoderLayer.tune (the Python mirror of CudaSegment::tuneGemms) only changes which configuration runs."""
+    from vknn_b200.encoder import EncoderLayer
+    rng = np.random.default_rng(1003)
+    w = encoder_weights(rng, 256, 1024, bias_scale=0.01)
+    x = round_to(rng.standard_normal((4, 197, 256)), torch.float16)
+    ref = vko.encoder_layer(x, w, 4, eps=1e-6)
+    layer = EncoderLayer(ctx, w, 4, dtype=torch.float16)
+    xd = dev(x, torch.float16)
+    layer.forward(xd)
+    table = layer.tune(xd)
+    assert len(table) == 4 and all(-1 <= v < ctx.gemm_config_count() for v in table.values())
+    y = layer.forward(xd)
+    ctx.sync()
+    assert_low(host(y), ref, "tuned encoder layer")
+
+
 def test_invalid_arguments(ctx):
     """Error behaviour: bad arguments are refused with a status and a message; nothing is launched."""
     q = torch.zeros(1, 3, 8, 64, dtype=torch.float16, device="cuda")

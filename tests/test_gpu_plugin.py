@@ -102,3 +102,30 @@ def test_device_resident_io_matches_host_io():
     (host,), _ = vko.attention_graph(q, k, v, 0.125).run(backend="cuda", precision="low")
     (dev,), _ = vko.attention_graph(q, k, v, 0.125).run(backend="cuda", precision="low", device_io=True)
     assert np.array_equal(dev, host)
+
+
+def test_gemm_autotune_table_is_cached_and_reused(tmp_path):
+    """Hint::Tuning + Config::cacheFile through the plug-in: the first session times the tensor-core GEMM configurations
+    per shape and finalize() writes "<cacheFile>.cuda"; a second session loads the table instead of measuring (the
+    file stays byte-identical) and produces the same output; with tuning off no file appears."""
+    rng = np.random.default_rng(13)
+    w = encoder_weights(rng, 256, 1024, bias_scale=0.01)
+    x = rng.standard_normal((4, 160, 256)).astype(np.float32)
+    cache = str(tmp_path / "model.cache")
+    (ref,), _ = vko.encoder_layer_graph(x, w, 4).run(backend="cpu")
+    (a,), info = vko.encoder_layer_graph(x, w, 4).run(backend="cuda", precision="low", cache_file=cache, tuning="fast", iters=2)
+    assert all(n[1] == CUDA_KIND for n in info["nodes"])
+    assert_low(a, ref, "tuned encoder layer")
+    table = tmp_path / "model.cache.cuda"
+    assert table.exists()
+    lines = table.read_text().splitlines()
+    assert lines[0] == "VKNNCUDA-TUNE-1" and len(lines) >= 2 + 4, lines     # header, GPU tag, the layer's four GEMM shapes
+    assert all(ln.startswith("gemm:") for ln in lines[2:])
+    before = table.read_bytes()
+    (b,), _ = vko.encoder_layer_graph(x, w, 4).run(backend="cuda", precision="low", cache_file=cache, tuning="fast", iters=2)
+    assert table.read_bytes() == before
+    assert np.array_equal(a, b)
+    cache2 = str(tmp_path / "other.cache")
+    (c,), _ = vko.encoder_layer_graph(x, w, 4).run(backend="cuda", precision="low", cache_file=cache2, tuning="off")
+    assert not (tmp_path / "other.cache.cuda").exists()
+    assert_low(c, ref, "untuned encoder layer")

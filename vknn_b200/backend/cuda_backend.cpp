@@ -33,6 +33,8 @@
 #include <algorithm>
 #include <cmath>
 #include <cstring>
+#include <fstream>
+#include <sstream>
 #include <map>
 #include <memory>
 #include <set>
@@ -106,6 +108,7 @@ namespace vknn {
             const float *bias = nullptr, *gamma = nullptr, *beta = nullptr, *mask = nullptr;
             int64_t     M = 0, N = 0, K = 0, batch = 1, sa = 0, sb = 0, sd = 0, lda = 0, ldb = 0, ldd = 0;
             int         bLayout = VKC_B_KN, epilogue = 0;
+            int         gemmConfig = -1; // tensor-core kernel configuration chosen by the autotune (-1: built-in choice)
             int64_t     B = 0, Hq = 0, Hkv = 0, Sq = 0, Skv = 0, D = 0;
             int64_t     qs[3], ks[3], vs[3], os[3];
             float       scale = 1.f, eps = 1e-5f;
@@ -173,6 +176,10 @@ namespace vknn {
         void  launch(const Step &s);
         int   consumersInSegment(TensorId id, std::vector<int> *who) const;
         bool  internalOnly(TensorId id) const { return boundaryOut_.count(id) == 0; }
+
+        void tuneGemms();
+        CudaBackend *be_ = nullptr;
+        int          tuning_ = 0; // Hint::Tuning: 0 none, 1 fast, 2 thorough
 
         bool tryAttention(size_t pos, std::set<int> &done);
         void planMatMul(size_t pos, std::set<int> &done);
@@ -270,9 +277,57 @@ namespace vknn {
 
         Precision precision() const { return precision_; }
 
+        // ---- GEMM autotune table and its file (the CUDA counterpart of the tuning section of the reference's unified
+        // cache, src/backend/vulkan/vk_backend.cpp:445-545; flushed by finalize() like saveCaches there). The file is
+        // "<cfg.cacheFile>.cuda": text, one "key config" pair per line under a header that names the format and the GPU,
+        // so a table measured on another device is ignored. Weights need no cache section: the kernels read the
+        // reference's row-major [K,N] initializers as they are (fp16 ".vxm" weights upload byte for byte).
+        void loadTuning(const Config &cfg) {
+            if (tuneLoaded_) return;
+            tuneLoaded_ = true;
+            if (cfg.cacheFile.empty() || !cfg.cachesTuning()) return;
+            tuneFile_ = cfg.cacheFile + ".cuda";
+            std::ifstream f(tuneFile_);
+            std::string   magic, gpu;
+            if (!f || !std::getline(f, magic) || magic != "VKNNCUDA-TUNE-1" || !std::getline(f, gpu) || gpu != gpuTag()) return;
+            std::string key;
+            int         cfgIdx;
+            while (f >> key >> cfgIdx)
+                if (cfgIdx >= -1 && cfgIdx < vkc_gemm_config_count()) tune_[key] = cfgIdx;
+        }
+        bool lookupTuning(const std::string &key, int *cfgIdx) const {
+            auto it = tune_.find(key);
+            if (it == tune_.end()) return false;
+            *cfgIdx = it->second;
+            return true;
+        }
+        void storeTuning(const std::string &key, int cfgIdx) {
+            tune_[key]  = cfgIdx;
+            tuneDirty_ = true;
+        }
+        void finalize() override {
+            if (!tuneDirty_ || tuneFile_.empty()) return;
+            std::ofstream f(tuneFile_, std::ios::trunc);
+            if (!f) {
+                VKNN_WARN << "CUDA backend: cannot write " << tuneFile_;
+                return;
+            }
+            f << "VKNNCUDA-TUNE-1\n" << gpuTag() << "\n";
+            for (const auto &kv : tune_) f << kv.first << " " << kv.second << "\n";
+            tuneDirty_ = false;
+        }
+        std::string gpuTag() const {
+            int n = 0;
+            vkc_device_count(&n);
+            return "sm_100a/configs=" + std::to_string(vkc_gemm_config_count());
+        }
+
       private:
         vkc_ctx  *ctx_       = nullptr;
         Precision precision_ = Precision::Low;
+        std::map<std::string, int> tune_;
+        std::string                tuneFile_;
+        bool                       tuneLoaded_ = false, tuneDirty_ = false;
     };
 
     VKNN_REGISTER_BACKEND(kCuda, CudaBackend);
@@ -282,6 +337,9 @@ namespace vknn {
         backend = be;
         nodeIdx = nodes;
         dtype_  = cfg.precision == Precision::High ? VKC_F32 : VKC_F16;
+        be_     = be;
+        tuning_ = cfg.hint(Hint::Tuning, (int) Mode::Fast);
+        be->loadTuning(cfg);
         esize_  = dtype_ == VKC_F32 ? 4 : 2;
         uploadInitializers(nodes, g);
     }
@@ -808,13 +866,57 @@ namespace vknn {
             if (!it->second.contiguous()) it->second = materialize(it->second, "boundary output");
         }
         planned_ = true;
+        if (tuning_ != (int) Mode::NoTune && dtype_ != VKC_F32) tuneGemms();
+    }
+
+    // Per-shape choice of the tensor-core GEMM configuration by measurement (Hint::Tuning: Fast = 10 timed launches per
+    // configuration, Thorough = 40), as the reference times its convolution kernels per shape. The buffers exist by now;
+    // their contents are irrelevant for timing and every tuned output is overwritten by the first real run.
+    void CudaSegment::tuneGemms() {
+        const int nCfg  = vkc_gemm_config_count();
+        const int iters = tuning_ == (int) Mode::Thorough ? 40 : 10;
+        for (Step &s : steps_) {
+            if (s.kind != Step::Gemm || s.M < 32 || s.N < 32 || s.K < 32) continue;
+            std::ostringstream key;
+            key << "gemm:" << dtype_ << ":" << s.M << "x" << s.N << "x" << s.K << "x" << s.batch << ":" << s.bLayout << ":" << s.epilogue << ":"
+                << (s.lda % 8 == 0) << (s.ldb % 8 == 0) << (s.ldd % 8 == 0);
+            if (be_->lookupTuning(key.str(), &s.gemmConfig)) continue;
+            int   best   = -1;
+            float bestMs = 1e30f;
+            for (int c = -1; c < nCfg; ++c) {
+                auto once = [&]() {
+                    return vkc_gemm_ex(ctx_, s.a, s.b, s.bias, s.c, s.d, s.M, s.N, s.K, s.batch, s.sa, s.sb, s.sd, s.lda, s.ldb, s.ldd, s.bLayout, s.epilogue,
+                                       dtype_, c, nullptr);
+                };
+                if (once() != VKC_OK) continue; // a configuration this shape cannot run
+                // time on the device: the launches are recorded into a graph and replayed, so that host launch cost
+                // (tensor-map encoding, driver calls) does not rank the configurations
+                vkc_graph *tg = nullptr;
+                if (vkc_graph_begin(ctx_) != VKC_OK) break;
+                bool okc = true;
+                for (int i = 0; i < iters && okc; ++i) okc = once() == VKC_OK;
+                if (vkc_graph_end(ctx_, &tg) != VKC_OK || !tg || !okc) {
+                    if (tg) vkc_graph_destroy(ctx_, tg);
+                    continue;
+                }
+                float ms = 1e30f;
+                if (vkc_graph_launch(ctx_, tg) == VKC_OK && vkc_timer_start(ctx_, nullptr) == VKC_OK && vkc_graph_launch(ctx_, tg) == VKC_OK) {
+                    if (vkc_timer_stop(ctx_, nullptr, &ms) != VKC_OK) ms = 1e30f;
+                }
+                vkc_graph_destroy(ctx_, tg);
+                if (ms < bestMs * 0.97f) bestMs = ms, best = c; // a later configuration must win clearly
+            }
+            s.gemmConfig = best;
+            be_->storeTuning(key.str(), best);
+        }
+        check(ctx_, vkc_sync(ctx_, nullptr), "vkc_sync after GEMM tuning");
     }
 
     void CudaSegment::launch(const Step &s) {
         switch (s.kind) {
             case Step::Gemm:
-                check(ctx_, vkc_gemm(ctx_, s.a, s.b, s.bias, s.c, s.d, s.M, s.N, s.K, s.batch, s.sa, s.sb, s.sd, s.lda, s.ldb, s.ldd, s.bLayout, s.epilogue,
-                                     dtype_, nullptr), "vkc_gemm");
+                check(ctx_, vkc_gemm_ex(ctx_, s.a, s.b, s.bias, s.c, s.d, s.M, s.N, s.K, s.batch, s.sa, s.sb, s.sd, s.lda, s.ldb, s.ldd, s.bLayout,
+                                        s.epilogue, dtype_, s.gemmConfig, nullptr), "vkc_gemm");
                 break;
             case Step::Attn:
                 check(ctx_, vkc_attn_prefill(ctx_, s.a, s.b, s.c, s.d, s.B, s.Hq, s.Hkv, s.Sq, s.Skv, s.D, s.qs, s.ks, s.vs, s.os, s.scale, 0, s.mask,

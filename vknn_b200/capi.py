@@ -67,6 +67,8 @@ def load_library():
     L.vkc_download.argtypes = [vp, vp, i32, vp, i32, i64, vp]
     L.vkc_convert.argtypes = [vp, vp, i32, vp, i32, i64, vp]
     L.vkc_gemm.argtypes = [vp, vp, vp, vp, vp, vp] + [i64] * 10 + [i32, i32, i32, vp]
+    L.vkc_gemm_ex.argtypes = [vp, vp, vp, vp, vp, vp] + [i64] * 10 + [i32, i32, i32, i32, vp]
+    L.vkc_gemm_config_count.argtypes = []
     L.vkc_attn_prefill.argtypes = [vp, vp, vp, vp, vp] + [i64] * 6 + [vp, vp, vp, vp, f32, i32, vp, vp, i32, vp]
     L.vkc_attn_decode_workspace_bytes.argtypes = [i64] * 5
     L.vkc_attn_decode_workspace_bytes.restype = sz
@@ -173,8 +175,9 @@ class Context:
         self._check(self.lib.vkc_convert(self.h, dst.data_ptr(), _dtype_code(dst), src.data_ptr(), _dtype_code(src), src.numel(), self._stream(stream)))
 
     # ---- kernels ----
-    def gemm(self, A, B, D, bias=None, residual=None, b_layout=B_KN, epilogue=None, stream=None):
-        """A [batch?,M,K], B [batch?,K,N] (B_KN) or [batch?,N,K] (B_NK), D [batch?,M,N]; a 2-D operand broadcasts."""
+    def gemm(self, A, B, D, bias=None, residual=None, b_layout=B_KN, epilogue=None, stream=None, config=-1):
+        """A [batch?,M,K], B [batch?,K,N] (B_KN) or [batch?,N,K] (B_NK), D [batch?,M,N]; a 2-D operand broadcasts.
+        config >= 0 forces one of the tensor-core kernel's configurations (see gemm_config_count)."""
         M, K = A.shape[-2:]
         N = D.shape[-1]
         batch = D.shape[0] if D.dim() == 3 else 1
@@ -183,9 +186,13 @@ class Context:
         sd = D.stride(0) if D.dim() == 3 else 0
         if epilogue is None:
             epilogue = (EPI_BIAS if bias is not None else 0) | (EPI_RESIDUAL if residual is not None else 0)
-        self._check(self.lib.vkc_gemm(self.h, A.data_ptr(), B.data_ptr(), bias.data_ptr() if bias is not None else None,
-                                      residual.data_ptr() if residual is not None else None, D.data_ptr(), M, N, K, batch, sa, sb, sd,
-                                      A.stride(-2), B.stride(-2), D.stride(-2), b_layout, epilogue, _dtype_code(A), self._stream(stream)))
+        self._check(self.lib.vkc_gemm_ex(self.h, A.data_ptr(), B.data_ptr(), bias.data_ptr() if bias is not None else None,
+                                         residual.data_ptr() if residual is not None else None, D.data_ptr(), M, N, K, batch, sa, sb, sd,
+                                         A.stride(-2), B.stride(-2), D.stride(-2), b_layout, epilogue, _dtype_code(A), int(config),
+                                         self._stream(stream)))
+
+    def gemm_config_count(self):
+        return int(self.lib.vkc_gemm_config_count())
 
     def attn_prefill(self, Q, K, V, O, scale, causal=False, mask=None, kv_len=None, stream=None):
         """Q/O [B,Hq,Sq,D], K/V [B,Hkv,Skv,D]; any strides with D contiguous (views of a packed qkv buffer are fine)."""

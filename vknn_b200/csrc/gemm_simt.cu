@@ -6,7 +6,7 @@
 
 int vkc_gemm_tcgen05(vkc_ctx *ctx, const void *A, const void *B, const float *bias, const void *residual, void *D, int64_t M, int64_t N,
                      int64_t K, int64_t batch, int64_t stride_a, int64_t stride_b, int64_t stride_d, int64_t lda, int64_t ldb, int64_t ldd,
-                     int b_layout, int epilogue, int dtype, cudaStream_t st);
+                     int b_layout, int epilogue, int dtype, int config, cudaStream_t st);
 
 namespace {
 
@@ -103,7 +103,14 @@ namespace {
 extern "C" int vkc_gemm(vkc_ctx *ctx, const void *A, const void *B, const float *bias, const void *residual, void *D, int64_t M, int64_t N,
                         int64_t K, int64_t batch, int64_t stride_a, int64_t stride_b, int64_t stride_d, int64_t lda, int64_t ldb, int64_t ldd,
                         int b_layout, int epilogue, int dtype, vkc_stream stream) {
+    return vkc_gemm_ex(ctx, A, B, bias, residual, D, M, N, K, batch, stride_a, stride_b, stride_d, lda, ldb, ldd, b_layout, epilogue, dtype, -1, stream);
+}
+
+extern "C" int vkc_gemm_ex(vkc_ctx *ctx, const void *A, const void *B, const float *bias, const void *residual, void *D, int64_t M, int64_t N,
+                           int64_t K, int64_t batch, int64_t stride_a, int64_t stride_b, int64_t stride_d, int64_t lda, int64_t ldb, int64_t ldd,
+                           int b_layout, int epilogue, int dtype, int config, vkc_stream stream) {
     if (!ctx) return VKC_ERR_INVALID;
+    VKC_REQUIRE(ctx, config >= -1 && config < vkc_gemm_config_count(), "gemm: bad configuration index %d", config);
     VKC_REQUIRE(ctx, M >= 0 && N >= 0 && K >= 0 && batch >= 0, "gemm: negative extent");
     VKC_REQUIRE(ctx, dtype == VKC_F32 || dtype == VKC_F16 || dtype == VKC_BF16, "gemm: bad dtype %d", dtype);
     VKC_REQUIRE(ctx, b_layout == VKC_B_KN || b_layout == VKC_B_NK, "gemm: bad b_layout %d", b_layout);
@@ -120,8 +127,10 @@ extern "C" int vkc_gemm(vkc_ctx *ctx, const void *A, const void *B, const float 
     if (ctx->impl == VKC_IMPL_AUTO) want_tc = want_tc && M >= 32 && N >= 32 && K >= 32; // the reference's tiled-path rule (ops/matmul.cpp:141)
     if (want_tc) {
         int rc = vkc_gemm_tcgen05(ctx, A, B, bias, residual, D, M, N, K, batch, stride_a, stride_b, stride_d, lda, ldb, ldd, b_layout, epilogue,
-                                  dtype, st);
-        if (rc != VKC_ERR_UNSUPPORTED || ctx->impl == VKC_IMPL_TCGEN05) return rc;
+                                  dtype, config, st);
+        if (rc != VKC_ERR_UNSUPPORTED || ctx->impl == VKC_IMPL_TCGEN05 || config >= 0) return rc;
+    } else if (config >= 0) {
+        return vkc_fail(ctx, VKC_ERR_UNSUPPORTED, "gemm: a tensor-core configuration was requested for a problem the tensor-core kernel does not take");
     }
     switch (dtype) {
         case VKC_F32:

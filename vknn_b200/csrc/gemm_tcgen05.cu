@@ -436,6 +436,7 @@ namespace {
         kCfg192x4x1s2, // split-K over a cluster of two CTAs
         kCfg256x3x1s2,
         kCfg128x5x1s2,
+        kNumConfigs
     };
     struct TileChoice {
         TileConfig cfg;
@@ -485,11 +486,13 @@ namespace {
 
 } // namespace
 
+extern "C" int vkc_gemm_config_count(void) { return kNumConfigs; }
+
 // Returns VKC_ERR_UNSUPPORTED (without touching ctx->err semantics beyond the message) when the operands do not
 // meet the TMA alignment rules; the caller then uses the SIMT kernel.
 int vkc_gemm_tcgen05(vkc_ctx *ctx, const void *A, const void *B, const float *bias, const void *residual, void *D, int64_t M, int64_t N,
                      int64_t K, int64_t batch, int64_t stride_a, int64_t stride_b, int64_t stride_d, int64_t lda, int64_t ldb, int64_t ldd,
-                     int b_layout, int epilogue, int dtype, cudaStream_t st) {
+                     int b_layout, int epilogue, int dtype, int config, cudaStream_t st) {
     if (dtype != VKC_F16 && dtype != VKC_BF16) return vkc_fail(ctx, VKC_ERR_UNSUPPORTED, "gemm_tcgen05: 16-bit storage only");
     if ((lda % 8) || (ldb % 8) || (stride_a % 8) || (stride_b % 8) || ((uintptr_t) A & 15) || ((uintptr_t) B & 15))
         return vkc_fail(ctx, VKC_ERR_UNSUPPORTED, "gemm_tcgen05: operand strides/bases must be multiples of 16 bytes");
@@ -522,10 +525,12 @@ int vkc_gemm_tcgen05(vkc_ctx *ctx, const void *A, const void *B, const float *bi
     }
 
     TileChoice tc = choose_tile(M, N, K, batch, ctx->sm_count, tma_out);
-    if (const char *e = getenv("VKNN_GEMM_TILE")) { // development switch: force a configuration by its enum index
-        const int v = atoi(e);
-        const int bns[10] = {256, 256, 192, 128, 64, 192, 128, 192, 256, 128};
-        if (v >= 0 && v < 10 && (v < 7 || (tma_out && (K + BK - 1) / BK >= 4))) tc = {(TileConfig) v, bns[v]};
+    if (config >= 0) { // caller-chosen configuration (autotuning); refuse what this problem cannot run
+        const int  bns[kNumConfigs] = {256, 256, 192, 128, 64, 192, 128, 192, 256, 128};
+        const bool split            = config >= kCfg192x4x1s2;
+        if (split && (!tma_out || (K + BK - 1) / BK < 4))
+            return vkc_fail(ctx, VKC_ERR_UNSUPPORTED, "gemm_tcgen05: split-K configuration %d needs a TMA-storable output and at least 4 k-steps", config);
+        tc = {(TileConfig) config, bns[config]};
     }
     const int        BN = tc.bn;
 

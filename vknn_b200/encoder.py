@@ -29,6 +29,7 @@ class EncoderLayer:
         self.d = self.w["wo"].shape[0]
         self.dmlp = self.w["w1"].shape[1]
         self._buf = {}
+        self.cfg = {"qkv": -1, "proj": -1, "fc1": -1, "fc2": -1}  # tensor-core GEMM configuration per GEMM (-1: built-in)
 
     def _buffers(self, B, T, device):
         key = (B, T)
@@ -48,16 +49,60 @@ class EncoderLayer:
         x2 = x.view(B * T, d)
         y = out if out is not None else torch.empty_like(x)
         c.layernorm(x2, w["ln1_g"], w["ln1_b"], buf["h"], self.eps)
-        c.gemm(buf["h"], w["wqkv"], buf["qkv"].view(B * T, 3 * d), bias=w["bqkv"])
+        c.gemm(buf["h"], w["wqkv"], buf["qkv"].view(B * T, 3 * d), bias=w["bqkv"], config=self.cfg["qkv"])
         qkv = buf["qkv"]                                  # [B,T,3,H,D]
         q, k, v = (qkv[:, :, i].permute(0, 2, 1, 3) for i in range(3))   # [B,H,T,D] strided views, no copy
         o = buf["att"].permute(0, 2, 1, 3)                # attention writes straight into the merged [B,T,H*D] layout
         c.attn_prefill(q, k, v, o, scale=1.0 / (D ** 0.5))
-        c.gemm(buf["att"].view(B * T, d), w["wo"], buf["x1"], bias=w["bo"], residual=x2)
+        c.gemm(buf["att"].view(B * T, d), w["wo"], buf["x1"], bias=w["bo"], residual=x2, config=self.cfg["proj"])
         c.layernorm(buf["x1"], w["ln2_g"], w["ln2_b"], buf["h"], self.eps)
-        c.gemm(buf["h"], w["w1"], buf["f"], bias=w["b1"], epilogue=capi.EPI_BIAS | capi.EPI_GELU_ERF)
-        c.gemm(buf["f"], w["w2"], y.view(B * T, d), bias=w["b2"], residual=buf["x1"])
+        c.gemm(buf["h"], w["w1"], buf["f"], bias=w["b1"], epilogue=capi.EPI_BIAS | capi.EPI_GELU_ERF, config=self.cfg["fc1"])
+        c.gemm(buf["f"], w["w2"], y.view(B * T, d), bias=w["b2"], residual=buf["x1"], config=self.cfg["fc2"])
         return y
+
+    def tune(self, x, iters=10, table=None):
+        """Per-shape choice of the GEMM configuration by measurement, as CudaSegment::tuneGemms does at plan time
+        (Hint::Tuning). `table` (dict) carries choices between layers of the same shape so each shape is timed once."""
+        c, w = self.ctx, self.w
+        B, T, d = x.shape
+        buf = self._buffers(B, T, x.device)
+        x2, y = x.view(B * T, d), torch.empty_like(x).view(B * T, d)
+        gemms = {
+            "qkv": lambda cfg: c.gemm(buf["h"], w["wqkv"], buf["qkv"].view(B * T, 3 * d), bias=w["bqkv"], config=cfg),
+            "proj": lambda cfg: c.gemm(buf["att"].view(B * T, d), w["wo"], buf["x1"], bias=w["bo"], residual=x2, config=cfg),
+            "fc1": lambda cfg: c.gemm(buf["h"], w["w1"], buf["f"], bias=w["b1"], epilogue=capi.EPI_BIAS | capi.EPI_GELU_ERF, config=cfg),
+            "fc2": lambda cfg: c.gemm(buf["f"], w["w2"], y, bias=w["b2"], residual=buf["x1"], config=cfg),
+        }
+        table = {} if table is None else table
+        for name, fn in gemms.items():
+            key = (name, B * T, d, self.dmlp)
+            if key not in table:
+                best, best_ms = -1, float("inf")
+                for cfg in range(-1, c.gemm_config_count()):
+                    try:
+                        fn(cfg), fn(cfg)
+                    except RuntimeError:
+                        continue  # a configuration this shape cannot run
+                    # time on the device: `iters` launches replayed as one CUDA graph (eager launches from Python are
+                    # host-bound at these kernel lengths and would rank the configurations by noise)
+                    torch.cuda.synchronize()
+                    g = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(g):
+                        for _ in range(iters):
+                            fn(cfg)
+                    g.replay()
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record()
+                    g.replay()
+                    g.replay()
+                    e1.record()
+                    e1.synchronize()
+                    ms = e0.elapsed_time(e1)
+                    if ms < best_ms * 0.97:
+                        best, best_ms = cfg, ms
+                table[key] = best
+            self.cfg[name] = table[key]
+        return table
 
     LAUNCHES_PER_FORWARD = 7
 
@@ -129,6 +174,12 @@ class EncoderStack:
         if key not in self._pp:
             self._pp[key] = [torch.empty_like(x), torch.empty_like(x)]
         return self._pp[key]
+
+    def tune(self, x):
+        table = {}
+        for layer in self.layers:
+            layer.tune(x, table=table)
+        return table
 
     def forward(self, x):
         """Ping-pongs between two internal buffers; the caller's input is left untouched."""

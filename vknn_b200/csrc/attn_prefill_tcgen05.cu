@@ -1,7 +1,9 @@
 // K2 — fused prefill attention on the 5th-generation tensor cores (flash style: the score matrix never leaves
 // the SM). One CTA owns TWO 128-row query tiles (A and B) of one (batch, head) and walks the key/value
 // sequence in tiles of 128 keys; while the softmax warps of one query tile work, the tensor core runs the
-// MMAs of the other.
+// MMAs of the other. For head size 64 and grids of only a few rounds a one-tile form runs instead, two CTAs per SM:
+// the same overlap happens between the co-resident CTAs and single tiles balance better over the 148 SMs.
+// Warp numbers below are those of the two-tile form.
 //
 //   warp 8     TMA producer: both Q tiles once, then K and V tiles through two independent 2-stage
 //              shared-memory rings (128-byte swizzle, plain per-CTA tiled loads; rows past the end read as zeros).
@@ -34,10 +36,11 @@
 namespace {
 
     constexpr int BM = 128, BN = 128; // rows per query tile, keys per key tile
-    constexpr int kQTiles    = 2;
-    constexpr int kThreads   = 128 + kQTiles * 128; // two softmax warpgroups, then the control warpgroup
-    constexpr int kWarpTma = 8, kWarpMma = 9;        // warps 10 and 11 only give up their registers
-    constexpr int kTmemCols  = 512;
+    // QT = query tiles per CTA: 2 (one CTA per SM, the two tiles' softmax and MMAs overlap inside the CTA) or, for
+    // head size 64 where two CTAs fit an SM, 1 (the overlap happens between the two co-resident CTAs and the hardware
+    // block scheduler balances single tiles over the SMs: 176 two-tile CTAs on 148 SMs take two rounds, 352 one-tile CTAs
+    // on 296 slots a little over one).
+    __host__ __device__ constexpr int threads_for(int qt) { return 128 + qt * 128; } // QT softmax warpgroups, then the control warpgroup
     constexpr float kRescaleThreshold = 8.0f;
     constexpr int   kPParts = 2; // P_t is handed to the MMA issuer in this many column groups (BN / kPParts keys each)
 
@@ -53,15 +56,15 @@ namespace {
     };
     constexpr int kTlTile = 20;
 
-    template <int D, int KS, int VS> struct Smem {
+    template <int D, int KS, int VS, int QT> struct Smem {
         static constexpr uint32_t Q_BYTES  = BM * D * 2; // per query tile
         static constexpr uint32_t KV_BYTES = BN * D * 2;
         static constexpr uint32_t oQ   = 0;
-        static constexpr uint32_t oK   = oQ + kQTiles * Q_BYTES;
+        static constexpr uint32_t oK   = oQ + QT * Q_BYTES;
         static constexpr uint32_t oV   = oK + KS * KV_BYTES;
         static constexpr uint32_t oBar = oV + VS * KV_BYTES;
-        // barriers: q_full, k_full[KS], k_empty[KS], v_full[VS], v_empty[VS], s_full[2], p_full[2][kPParts], o_final[2]
-        static constexpr int nBar = 1 + 2 * KS + 2 * VS + 4 + 2 * kPParts;
+        // barriers: q_full, k_full[KS], k_empty[KS], v_full[VS], v_empty[VS], s_full[QT], p_full[QT][kPParts], o_final[QT]
+        static constexpr int nBar = 1 + 2 * KS + 2 * VS + QT * (2 + kPParts);
         static constexpr uint32_t oCtl  = oBar + 8 * nBar;
         static constexpr uint32_t total = oCtl + 16 + 1024;
     };
@@ -136,19 +139,30 @@ namespace {
         return d;
     }
 
-    template <typename T, int D, int kMode>
-    __global__ void __launch_bounds__(kThreads, 1)
+    template <typename T, int D, int kMode, int QT>
+    __global__ void __launch_bounds__(threads_for(QT), QT == 1 ? 2 : 1)
         attn_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                             AttnParams p) {
         constexpr int KS = 2, VS = 2; // the MMA issuer selects ring stages by the parity of the key tile
         static_assert(KS == 2 && VS == 2, "stage selection assumes two-stage rings");
-        using L               = Smem<D, KS, VS>;
+        using L               = Smem<D, KS, VS, QT>;
+        constexpr int kQTiles = QT, kThreads = threads_for(QT);
+        constexpr int kWarpTma = 4 * QT, kWarpMma = 4 * QT + 1; // the other two warps of the control warpgroup only give up registers
+        constexpr int kTmemCols = QT == 2 ? 512 : 256;
+        // Register re-partitioning. The CTA is launched with kRegsBase registers per thread (what the launch bounds allow);
+        // setmaxnreg.inc blocks in hardware until the CTA's own pool holds the registers, so the control warpgroup must
+        // give up at least what the softmax warpgroups take (checked here: a shortfall would hang the kernel).
+        constexpr int kRegsBase    = (65536 / (threads_for(QT) * (QT == 1 ? 2 : 1))) / 8 * 8;
+        constexpr int kRegsControl = QT == 2 ? 88 : 56;
+        constexpr int kRegsSoftmax = QT == 2 ? 208 : 200;
+        static_assert(QT * (kRegsSoftmax - kRegsBase) <= kRegsBase - kRegsControl, "softmax warpgroups would wait forever for registers");
+        (void) kThreads;
         constexpr bool kBf16  = std::is_same<T, __nv_bfloat16>::value;
         constexpr uint32_t kIdescQK = ptx::idesc_f16(BM, BN, kBf16, false, false);
         constexpr uint32_t kIdescPV = ptx::idesc_f16(BM, D, kBf16, false, true);
         constexpr int      DCH      = D / 64; // 64-element (128-byte) spans per row
         constexpr int      kColS    = 0;      // S_A at 0, S_B at 128; P_t aliases the first 64 columns of S_t
-        constexpr int      kColO    = 256;    // O_A at 256, O_B at 256 + D
+        constexpr int      kColO    = QT * 128; // O_A behind the S tiles, O_B at + D
 
         extern __shared__ uint8_t smem_raw[];
         const uint32_t raw   = ptx::smem_u32(smem_raw);
@@ -157,8 +171,8 @@ namespace {
         const uint32_t sQ = base + L::oQ, sK = base + L::oK, sV = base + L::oV, sBar = base + L::oBar;
         volatile int  *ctl = (volatile int *) (gbase + L::oCtl); // ctl[0] = tmem base, ctl[1] = abort flag
         auto           bar = [&](int i) { return sBar + 8u * (uint32_t) i; };
-        constexpr int  bQ = 0, bKF = 1, bKE = 1 + KS, bVF = 1 + 2 * KS, bVE = 1 + 2 * KS + VS, bSF = 1 + 2 * KS + 2 * VS, bPF = bSF + 2,
-                      bOF = bPF + 2 * kPParts;
+        constexpr int  bQ = 0, bKF = 1, bKE = 1 + KS, bVF = 1 + 2 * KS, bVE = 1 + 2 * KS + VS, bSF = 1 + 2 * KS + 2 * VS, bPF = bSF + QT,
+                      bOF = bPF + QT * kPParts;
 
         const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
         const int b = blockIdx.z, h = blockIdx.y;
@@ -186,7 +200,9 @@ namespace {
             }
             n_t[t] = (int) ((kend + BN - 1) / BN);
         }
-        const int n_max = n_t[0] > n_t[1] ? n_t[0] : n_t[1];
+        int n_max = 0;
+#pragma unroll
+        for (int t = 0; t < kQTiles; ++t) n_max = n_t[t] > n_max ? n_t[t] : n_max;
 
         if (threadIdx.x == 0) {
             for (int i = 0; i < L::nBar; ++i) ptx::mbar_init(bar(i), (i >= bPF && i < bOF) ? 4 : 1); // p_full: one arrival per softmax warp
@@ -208,7 +224,7 @@ namespace {
         vkc_grid_dep_launch();
 
         if (warp >= kWarpTma) {
-          ptx::setmaxnreg_dec<88>();
+          ptx::setmaxnreg_dec<kRegsControl>();
           if (warp == kWarpTma) {
             // ------------------------------------------------------------------ TMA producer
             if (n_max > 0 && ptx::elect_one()) {
@@ -304,7 +320,7 @@ namespace {
             }
           }
         } else {
-            ptx::setmaxnreg_inc<208>();
+            ptx::setmaxnreg_inc<kRegsSoftmax>();
             // ------------------------------------------------------------------ softmax + epilogue (thread = row)
             const int      t      = warp >> 2;             // query tile of this warpgroup
             const int      q      = warp & 3;              // TMEM lane quarter this warp may address
@@ -544,14 +560,24 @@ namespace {
         if (warp == kWarpMma) ptx::tmem_dealloc(tmem, kTmemCols);
     }
 
-    template <typename T, int D, int kMode = 2>
-    int launch_attn(vkc_ctx *ctx, const CUtensorMap &tq, const CUtensorMap &tk, const CUtensorMap &tv, const AttnParams &p, int64_t B, cudaStream_t st) {
-        auto          kern = attn_prefill_kernel<T, D, kMode>;
-        constexpr int smem = (int) Smem<D, 2, 2>::total;
+    template <typename T, int D, int QT>
+    int launch_attn_qt(vkc_ctx *ctx, const CUtensorMap &tq, const CUtensorMap &tk, const CUtensorMap &tv, const AttnParams &p, int64_t B, cudaStream_t st) {
+        auto          kern = attn_prefill_kernel<T, D, 2, QT>;
+        constexpr int smem = (int) Smem<D, 2, 2, QT>::total;
+        static_assert(smem * (QT == 1 && D == 64 ? 2 : 1) <= 227 * 1024, "shared memory budget");
         if (int rc = vkc_configure_smem(ctx, kern, smem)) return rc;
-        dim3 grid((unsigned) ((p.Sq + kQTiles * BM - 1) / (kQTiles * BM)), (unsigned) p.Hq, (unsigned) B);
-        vkc_launch(ctx, kern, grid, dim3(kThreads), smem, st, tq, tk, tv, p);
+        dim3 grid((unsigned) ((p.Sq + QT * BM - 1) / (QT * BM)), (unsigned) p.Hq, (unsigned) B);
+        vkc_launch(ctx, kern, grid, dim3(threads_for(QT)), smem, st, tq, tk, tv, p);
         return vkc_post_launch(ctx, "attn_prefill_tcgen05");
+    }
+    template <typename T, int D>
+    int launch_attn(vkc_ctx *ctx, const CUtensorMap &tq, const CUtensorMap &tk, const CUtensorMap &tv, const AttnParams &p, int64_t B, cudaStream_t st) {
+        if (D == 64) {
+            // two one-tile CTAs per SM unless the grid is many rounds deep anyway (then sharing K/V between two tiles wins)
+            const int64_t pairs = ((p.Sq + 2 * BM - 1) / (2 * BM)) * p.Hq * B;
+            if (pairs < 6 * (int64_t) ctx->sm_count) return launch_attn_qt<T, 64, 1>(ctx, tq, tk, tv, p, B, st);
+        }
+        return launch_attn_qt<T, D, 2>(ctx, tq, tk, tv, p, B, st);
     }
 
     int make_qkv_map(vkc_ctx *ctx, CUtensorMap *map, int dtype, const void *base, int64_t B, int64_t H, int64_t S, int64_t D, const int64_t *str) {

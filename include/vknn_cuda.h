@@ -174,6 +174,10 @@ VKC_API int vkc_softmax(vkc_ctx *ctx, const void *X, void *Y, int64_t outer, int
  * shaders/flat_gather.comp:11-21. ---- */
 VKC_API int vkc_strided_copy(vkc_ctx *ctx, const void *X, void *Y, const int64_t *shape, const int64_t *in_strides, int rank,
                              int64_t in_offset, int dtype, vkc_stream stream);
+/* The same with a strided destination, Y[sum_d idx_d(i) * out_strides[d]] = X[...]: writes one input of a Concat node
+ * into its slab of the output. Reference: ConcatCpu::run src/backend/cpu/ops/concat.cpp:9-66. */
+VKC_API int vkc_strided_copy2(vkc_ctx *ctx, const void *X, void *Y, const int64_t *shape, const int64_t *in_strides, const int64_t *out_strides,
+                              int rank, int64_t in_offset, int dtype, vkc_stream stream);
 
 /* ---- segment replay. Reference: the pre-recorded command buffer of a device segment,
  * src/backend/vulkan/vk_backend.cpp:1009-1210 (record) and :1353-1357 (submit). Calls made between begin and

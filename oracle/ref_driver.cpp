@@ -68,6 +68,9 @@ namespace {
             {"Binary", OpType::Binary},       {"Add", OpType::Add},             {"Unary", OpType::Unary},
             {"Transpose", OpType::Transpose}, {"Reshape", OpType::Reshape},     {"Gather", OpType::Gather},
             {"FusedPointwise", OpType::FusedPointwise}, {"Identity", OpType::Identity},
+            {"Conv", OpType::Conv},           {"Slice", OpType::Slice},         {"Split", OpType::Split},
+            {"Expand", OpType::Expand},       {"Tile", OpType::Tile},           {"Concat", OpType::Concat},
+            {"Squeeze", OpType::Squeeze},     {"Unsqueeze", OpType::Unsqueeze},
         };
         auto it = m.find(n);
         if (it == m.end()) {

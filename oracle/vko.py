@@ -389,3 +389,49 @@ def encoder_layer_graph(x, w, H, eps=1e-6):
     g.node("Add", "fc2_b", ["m0", "b2"], ["m1"])
     g.node("Add", "res2", ["x1", "m1"], ["y"])
     return g
+
+
+def vit_frontend_graph(img, wconv, bconv, cls, pos, cos, sin):
+    """The caller's graph around the encoder blocks, as a ViT / RoPE exporter emits it: patch-embedding Conv (kernel =
+    stride) -> Reshape -> Transpose -> Concat with the Expand-ed class token -> Add(pos) -> Slice (drop the class token) ->
+    rotary embedding by Split / Neg / Concat / Mul / Add -> Tile. img [B,C,H,W]; wconv [O,C,p,p]; cls [1,1,O]; pos [1,N+1,O];
+    cos, sin [N,O]. Outputs: the token sequence with the class token, the rotated patch tokens and a Tile of a Slice."""
+    B, C, H, W = img.shape
+    O, _, p, _ = wconv.shape
+    hp, wp = H // p, W // p
+    N = hp * wp
+    g = RefGraph()
+    g.input("img", img)
+    g.input("cls", cls)  # a runtime input, so that Expand is not folded away at load time
+    g.init("wconv", wconv)
+    g.init("bconv", bconv)
+    g.init("pos", pos)
+    g.init("cos", cos)
+    g.init("sin", sin)
+    g.init("shape_bon", np.array([B, O, N], dtype=np.int64))
+    g.init("shape_cls", np.array([B, 1, O], dtype=np.int64))
+    g.init("starts", np.array([1], dtype=np.int64))
+    g.init("ends", np.array([N + 1], dtype=np.int64))
+    g.init("axes", np.array([1], dtype=np.int64))
+    g.init("reps", np.array([1, 2, 3], dtype=np.int64))
+    for n in ("pe", "pe3", "tok", "clsb", "seq", "patches", "x1", "x2", "nx2", "rot", "xc", "rs", "strided"):
+        g.inter(n)
+    g.output("seqpos", (B, N + 1, O))
+    g.output("roped", (B, N, O))
+    g.output("tiled", (B, 2 * ((N + 1) // 2), 3 * (O // 2)))
+    g.node("Conv", "patch_embed", ["img", "wconv", "bconv"], ["pe"], strides=[p, p], pads=[0, 0, 0, 0], dilations=[1, 1], kernel_shape=[p, p], group=1)
+    g.node("Reshape", "flat", ["pe", "shape_bon"], ["pe3"])
+    g.node("Transpose", "tokens", ["pe3"], ["tok"], perm=[0, 2, 1])
+    g.node("Expand", "cls_b", ["cls", "shape_cls"], ["clsb"])
+    g.node("Concat", "with_cls", ["clsb", "tok"], ["seq"], axis=1)
+    g.node("Add", "add_pos", ["seq", "pos"], ["seqpos"])
+    g.node("Slice", "drop_cls", ["seqpos", "starts", "ends", "axes"], ["patches"])
+    g.node("Split", "halves", ["patches"], ["x1", "x2"], axis=2)
+    g.node("Unary", "neg", ["x2"], ["nx2"], subop=7)
+    g.node("Concat", "rotate_half", ["nx2", "x1"], ["rot"], axis=2)
+    g.node("Binary", "x_cos", ["patches", "cos"], ["xc"], subop=0)
+    g.node("Binary", "rot_sin", ["rot", "sin"], ["rs"], subop=0)
+    g.node("Add", "rope", ["xc", "rs"], ["roped"])
+    g.node("Slice", "every_other", ["seqpos"], ["strided"], starts=[0, 0], ends=[N + 1, O // 2], axes=[1, 2], steps=[2, 1])
+    g.node("Tile", "tile", ["strided", "reps"], ["tiled"])
+    return g

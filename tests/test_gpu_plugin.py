@@ -129,3 +129,30 @@ def test_gemm_autotune_table_is_cached_and_reused(tmp_path):
     (c,), _ = vko.encoder_layer_graph(x, w, 4).run(backend="cuda", precision="low", cache_file=cache2, tuning="off")
     assert not (tmp_path / "other.cache.cuda").exists()
     assert_low(c, ref, "untuned encoder layer")
+
+
+@pytest.mark.parametrize("precision", ["low", "high"])
+def test_vit_frontend_ops_run_on_the_cuda_backend(precision):
+    """The graph around the encoder blocks: patch-embedding Conv (as a GEMM over patches), Reshape/Transpose, Expand,
+    Concat, Add, Slice (with and without a step), Split, Neg, rotary Mul/Add (FusedPointwise after the passes) and Tile
+    all plan into one CUDA segment and match the reference CPU backend."""
+    rng = np.random.default_rng(5)
+    B, C, H, W, p, O = 2, 3, 64, 48, 16, 64
+    N = (H // p) * (W // p)
+    img = rng.standard_normal((B, C, H, W)).astype(np.float32)
+    args = (img, (0.05 * rng.standard_normal((O, C, p, p))).astype(np.float32), (0.1 * rng.standard_normal(O)).astype(np.float32),
+            rng.standard_normal((1, 1, O)).astype(np.float32), rng.standard_normal((1, N + 1, O)).astype(np.float32),
+            np.cos(rng.standard_normal((N, O))).astype(np.float32), np.sin(rng.standard_normal((N, O))).astype(np.float32))
+    ref, info_cpu = vko.vit_frontend_graph(*args).run(backend="cpu")
+    got, info = vko.vit_frontend_graph(*args).run(backend="cuda", precision=precision, iters=2)
+    kinds = [n[0] for n in info["nodes"]]
+    for op in ("Conv", "Expand", "Concat", "Slice", "Split", "Tile"):
+        assert op in kinds, kinds
+    assert all(n[1] == CUDA_KIND for n in info["nodes"]), info["nodes"]
+    assert len(got) == 3
+    for a, b, what in zip(got, ref, ("sequence with class token", "rotary patches", "tile of a strided slice")):
+        assert a.shape == b.shape
+        if precision == "high":
+            assert np.abs(a - b).max() <= 1e-4 * max(1.0, np.abs(b).max()), what
+        else:
+            assert_low(a, b, what)

@@ -113,7 +113,7 @@ namespace vknn {
             int64_t     qs[3], ks[3], vs[3], os[3];
             float       scale = 1.f, eps = 1e-5f;
             int64_t     rows = 0, norm = 0;
-            std::vector<int64_t>      shape, opStrides, inStrides;
+            std::vector<int64_t>      shape, opStrides, inStrides, outStrides; // outStrides empty: dense output
             std::vector<int32_t>      pwSteps;
             std::vector<float>        pwParams;
             std::vector<const void *> operands;
@@ -184,6 +184,7 @@ namespace vknn {
         bool tryAttention(size_t pos, std::set<int> &done);
         void planMatMul(size_t pos, std::set<int> &done);
         void planPointwise(const Node &n);
+        void planPatchConv(const Node &n);
     };
 
     class CudaBackend: public Backend {
@@ -216,7 +217,13 @@ namespace vknn {
                 case OpType::Squeeze:
                 case OpType::Unsqueeze:
                 case OpType::Flatten:
-                case OpType::Identity: return true;
+                case OpType::Identity:
+                case OpType::Slice:
+                case OpType::Split:
+                case OpType::Expand:
+                case OpType::Tile:
+                case OpType::Concat:
+                case OpType::Conv: return true;
                 default: return false;
             }
         }
@@ -266,6 +273,40 @@ namespace vknn {
                     return b && commutative;
                 }
                 case OpType::FusedPointwise: return !g.isInitializer(nd.inputs[0]);
+                case OpType::Slice:
+                case OpType::Expand:
+                case OpType::Tile: {
+                    // parameters must be attributes or int64 initializers (they are read at plan time); Slice steps > 0
+                    for (size_t i = 1; i < nd.inputs.size(); ++i)
+                        if (nd.inputs[i] != kNoTensor && !g.isInitializer(nd.inputs[i])) return false;
+                    if (nd.type == OpType::Slice) {
+                        std::vector<int64_t> steps = nd.attr.getints("steps");
+                        if (steps.empty() && nd.inputs.size() > 4 && nd.inputs[4] != kNoTensor) {
+                            auto it = g.initializers.find(nd.inputs[4]);
+                            if (it != g.initializers.end()) steps.assign(it->second.i64(), it->second.i64() + prod(g.desc(nd.inputs[4]).shape));
+                        }
+                        for (int64_t st : steps)
+                            if (st <= 0) return false;
+                    }
+                    return !g.isInitializer(nd.inputs[0]);
+                }
+                case OpType::Conv: {
+                    // patch embedding only: kernel == stride, no padding, no dilation, one group, constant weights —
+                    // a non-overlapping convolution is a GEMM over [B*outH*outW, C*kh*kw] patches
+                    if (nd.inputs.size() < 2 || !g.isInitializer(nd.inputs[1]) || g.isInitializer(nd.inputs[0])) return false;
+                    if (nd.inputs.size() > 2 && nd.inputs[2] != kNoTensor && !g.isInitializer(nd.inputs[2])) return false;
+                    const Shape &x = g.desc(nd.inputs[0]).shape, &w = g.desc(nd.inputs[1]).shape;
+                    if (x.size() != 4 || w.size() != 4 || w[1] != x[1]) return false;
+                    auto ints = [&](const char *k, std::vector<int64_t> d) {
+                        const auto &v = nd.attr.getints(k);
+                        return v.empty() ? d : v;
+                    };
+                    const auto st = ints("strides", {1, 1}), pad = ints("pads", {0, 0, 0, 0}), dil = ints("dilations", {1, 1});
+                    if (nd.attr.geti("group", 1) != 1 || st[0] != w[2] || st[1] != w[3] || dil[0] != 1 || dil[1] != 1) return false;
+                    for (int64_t v : pad)
+                        if (v != 0) return false;
+                    return nd.fusedAct == ActType::None && nd.fusedResidual == kNoTensor && x[2] >= w[2] && x[3] >= w[3];
+                }
                 default: return true;
             }
         }
@@ -388,7 +429,7 @@ namespace vknn {
                 const int src = d.dtype == DType::Float32 ? VKC_F32 : VKC_F16;
                 float     sv;
                 if (isScalarInit(g, in, &sv)) scalarInits_[in] = sv;
-                const bool keepF32 = (n.type == OpType::MatMul && in == n.fusedBias) || (n.type == OpType::LayerNorm && (in == n.inputs[1] || (n.inputs.size() > 2 && in == n.inputs[2])));
+                const bool keepF32 = (n.type == OpType::MatMul && in == n.fusedBias) || (n.type == OpType::Conv && n.inputs.size() > 2 && in == n.inputs[2]) || (n.type == OpType::LayerNorm && (in == n.inputs[1] || (n.inputs.size() > 2 && in == n.inputs[2])));
                 if (keepF32) {
                     void *p = nullptr;
                     check(ctx_, vkc_alloc(ctx_, (size_t) ne * 4, &p), "vkc_alloc");
@@ -756,6 +797,41 @@ namespace vknn {
         steps_.push_back(s);
     }
 
+    // Patch embedding: Conv with kernel == stride and no padding over X [B,C,H,W] is Y^T = patches . W^T with
+    // patches [B*oh*ow, C*kh*kw] (one strided copy of the [B,oh,ow,C,kh,kw] view of X) and W [O, C*kh*kw] read as [N,K] rows;
+    // the GEMM writes [B, oh*ow, O] and the node's NCHW output [B,O,oh,ow] is the transposed view of that buffer.
+    // Reference arithmetic: src/backend/cpu/ops/conv.cpp:10-75 (bias, then products in (c, ky, kx) order).
+    void CudaSegment::planPatchConv(const Node &n) {
+        const Graph &g = *g_;
+        const View  &x = views_.at(n.inputs[0]);
+        const View  &w = views_.at(n.inputs[1]);
+        const int64_t B = x.shape[0], C = x.shape[1], O = w.shape[0], kh = w.shape[2], kw = w.shape[3];
+        const Shape  &os = g.desc(n.outputs[0]).shape;
+        const int64_t oh = os[2], ow = os[3];
+        View p6 = x;
+        p6.shape   = {B, oh, ow, C, kh, kw};
+        p6.strides = {x.strides[0], x.strides[2] * kh, x.strides[3] * kw, x.strides[1], x.strides[2], x.strides[3]};
+        View a = materialize(p6, "conv patches"); // dense [B, oh, ow, C*kh*kw]
+        View d = newTensor(kNoTensor, Shape {B, oh * ow, O});
+        Step s;
+        s.kind = Step::Gemm;
+        s.M = B * oh * ow, s.N = O, s.K = C * kh * kw;
+        s.batch = 1, s.sa = 0, s.sb = 0, s.sd = 0;
+        s.lda = s.K, s.ldb = s.K, s.ldd = O;
+        s.bLayout = VKC_B_NK;
+        s.a = ptrOf(a), s.b = ptrOf(w), s.d = ptrOf(d);
+        if (n.inputs.size() > 2 && n.inputs[2] != kNoTensor) {
+            s.bias = f32Init(n.inputs[2]);
+            s.epilogue |= VKC_EPI_BIAS;
+        }
+        s.label = "conv (patch embedding)";
+        steps_.push_back(s);
+        View y    = d;
+        y.shape   = {B, O, oh, ow};
+        y.strides = {oh * ow * O, 1, ow * O, O};
+        views_[n.outputs[0]] = y;
+    }
+
     void CudaSegment::plan() {
         const Graph &g = *g_;
         boundaryOut_.insert(boundaryOutputs.begin(), boundaryOutputs.end());
@@ -820,6 +896,113 @@ namespace vknn {
                     views_[n.outputs[0]] = y;
                     break;
                 }
+                case OpType::Slice: {
+                    // a view: offset and strides (reference semantics src/backend/cpu/ops/slice.cpp:24-52; steps > 0 here)
+                    const View &x = views_.at(n.inputs[0]);
+                    const int   r = (int) x.shape.size();
+                    auto rd = [&](const char *attr, size_t idx) {
+                        std::vector<int64_t> v = n.attr.getints(attr);
+                        if (v.empty() && idx < n.inputs.size() && n.inputs[idx] != kNoTensor) v = i64Inits_.at(n.inputs[idx]);
+                        return v;
+                    };
+                    const auto starts = rd("starts", 1), ends = rd("ends", 2), axes = rd("axes", 3), steps = rd("steps", 4);
+                    View       y      = x;
+                    for (size_t k = 0; k < starts.size(); ++k) {
+                        int ax = (int) (axes.empty() ? (int64_t) k : axes[k]);
+                        if (ax < 0) ax += r;
+                        if (ax < 0 || ax >= r) continue;
+                        const int64_t dim = x.shape[ax], sp = k < steps.size() ? steps[k] : 1;
+                        int64_t       st  = starts[k] < 0 ? starts[k] + dim : starts[k];
+                        int64_t       en  = ends[k] < 0 ? ends[k] + dim : ends[k];
+                        st                = std::max<int64_t>(0, std::min(st, dim));
+                        en                = std::max<int64_t>(0, std::min(en, dim));
+                        y.offset += st * x.strides[ax];
+                        y.strides[ax] = x.strides[ax] * sp;
+                        y.shape[ax]   = std::max<int64_t>(0, (en - st + sp - 1) / sp);
+                    }
+                    if (y.shape != g.desc(n.outputs[0]).shape) fail(Status::RuntimeError, "Slice: planned shape differs from the inferred one");
+                    views_[n.outputs[0]] = y;
+                    break;
+                }
+                case OpType::Split: {
+                    // views at running offsets along the axis (src/backend/cpu/ops/split.cpp:9-62)
+                    const View &x    = views_.at(n.inputs[0]);
+                    int64_t     axis = n.attr.geti("axis", 0);
+                    if (axis < 0) axis += (int64_t) x.shape.size();
+                    int64_t off = 0;
+                    for (TensorId o : n.outputs) {
+                        if (o == kNoTensor) continue;
+                        View y = x;
+                        y.shape[axis] = g.desc(o).shape[axis];
+                        y.offset += off * x.strides[axis];
+                        off += y.shape[axis];
+                        views_[o] = y;
+                    }
+                    break;
+                }
+                case OpType::Expand: {
+                    // a view with stride 0 along the broadcast dimensions (src/backend/cpu/ops/expand.cpp:17-45)
+                    const View  &x   = views_.at(n.inputs[0]);
+                    const Shape &out = g.desc(n.outputs[0]).shape;
+                    const int    r = (int) out.size(), off = r - (int) x.shape.size();
+                    View         y = x;
+                    y.shape        = out;
+                    y.strides.assign(r, 0);
+                    for (int k = 0; k < r; ++k) {
+                        const int64_t dim = k < off ? 1 : x.shape[k - off];
+                        if (dim != 1) {
+                            if (dim != out[k]) fail(Status::InvalidArgument, "Expand: shapes do not broadcast");
+                            y.strides[k] = x.strides[k - off];
+                        }
+                    }
+                    views_[n.outputs[0]] = y;
+                    break;
+                }
+                case OpType::Tile: {
+                    // [d0, d1, ..] repeated [r0, r1, ..]: the view [r0, d0, r1, d1, ..] with stride 0 on the repeat axes, copied
+                    // once into a dense buffer and read as [r0*d0, r1*d1, ..] (src/backend/cpu/ops/tile.cpp:17-30)
+                    const View &x    = views_.at(n.inputs[0]);
+                    const int   r    = (int) x.shape.size();
+                    std::vector<int64_t> reps = n.attr.getints("repeats");
+                    if (reps.empty() && n.inputs.size() > 1 && n.inputs[1] != kNoTensor) reps = i64Inits_.at(n.inputs[1]);
+                    View v2 = x;
+                    v2.shape.clear(), v2.strides.clear();
+                    for (int k = 0; k < r; ++k) {
+                        v2.shape.push_back(std::max<int64_t>(k < (int) reps.size() ? reps[k] : 1, 1));
+                        v2.strides.push_back(0);
+                        v2.shape.push_back(x.shape[k]);
+                        v2.strides.push_back(x.strides[k]);
+                    }
+                    View y    = materialize(v2, "tile");
+                    y.shape   = g.desc(n.outputs[0]).shape;
+                    y.strides = denseStrides(y.shape);
+                    views_[n.outputs[0]] = y;
+                    break;
+                }
+                case OpType::Concat: {
+                    // each input is copied into its slab of the output (src/backend/cpu/ops/concat.cpp:9-66)
+                    const Shape &out  = g.desc(n.outputs[0]).shape;
+                    int64_t      axis = n.attr.geti("axis", 0);
+                    if (axis < 0) axis += (int64_t) out.size();
+                    View    y   = newTensor(n.outputs[0], out);
+                    int64_t off = 0;
+                    for (TensorId in : n.inputs) {
+                        const View &x = views_.at(in);
+                        Step        s;
+                        s.kind = Step::Copy;
+                        s.a    = bufs_[x.buf].ptr;
+                        s.shape.assign(x.shape.begin(), x.shape.end());
+                        s.inStrides = x.strides;
+                        s.inOffset  = x.offset;
+                        s.outStrides = y.strides;
+                        s.d          = static_cast<char *>(ptrOf(y)) + off * y.strides[axis] * (int64_t) esize_;
+                        s.label      = "concat";
+                        steps_.push_back(s);
+                        off += x.shape[axis];
+                    }
+                    break;
+                }
+                case OpType::Conv: planPatchConv(n); break;
                 case OpType::MatMul:
                     if (!tryAttention(pos, done)) planMatMul(pos, done);
                     break;
@@ -932,8 +1115,12 @@ namespace vknn {
                       "vkc_pointwise");
                 break;
             case Step::Copy:
-                check(ctx_, vkc_strided_copy(ctx_, s.a, s.d, s.shape.data(), s.inStrides.data(), (int) s.shape.size(), s.inOffset, dtype_, nullptr),
-                      "vkc_strided_copy");
+                if (s.outStrides.empty())
+                    check(ctx_, vkc_strided_copy(ctx_, s.a, s.d, s.shape.data(), s.inStrides.data(), (int) s.shape.size(), s.inOffset, dtype_, nullptr),
+                          "vkc_strided_copy");
+                else
+                    check(ctx_, vkc_strided_copy2(ctx_, s.a, s.d, s.shape.data(), s.inStrides.data(), s.outStrides.data(), (int) s.shape.size(), s.inOffset,
+                                                  dtype_, nullptr), "vkc_strided_copy2");
                 break;
         }
     }

@@ -228,8 +228,6 @@ namespace {
                                                const int32_t *__restrict__ kv_len, int64_t Hq, int64_t Lmax, int D, int chunk, int parts,
                                                int max_splits) {
         const int b = blockIdx.y, hq = blockIdx.x;
-        vkc_grid_dep_wait();
-        vkc_grid_dep_launch();
         int64_t   len = kv_len ? (int64_t) kv_len[b] : Lmax;
         if (len > Lmax) len = Lmax;
         const int     ns  = parts * (int) ((len + chunk - 1) / chunk); // partial slots this sequence filled
@@ -287,8 +285,7 @@ namespace {
             if (rc) return rc;
         }
         dim3 cgrid((unsigned) Hq, (unsigned) B);
-        vkc_launch(ctx, attn_decode_combine_kernel<T>, cgrid, dim3(D < 128 ? D : 128), 0, st, (const float *) part_ml, (const float *) part_o, (T *) O, kv_len, Hq, Lmax, (int) D,
-                   (int) eff_chunk, (int) parts, (int) max_splits);
+        attn_decode_combine_kernel<T><<<cgrid, D < 128 ? D : 128, 0, st>>>(part_ml, part_o, (T *) O, kv_len, Hq, Lmax, D, eff_chunk, parts, max_splits);
         return vkc_post_launch(ctx, "attn_decode_combine");
     }
 

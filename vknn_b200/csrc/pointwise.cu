@@ -114,20 +114,22 @@ namespace {
 
     struct CopyDesc {
         int     rank;
-        int64_t shape[kMaxRank], istride[kMaxRank], offset;
+        int64_t shape[kMaxRank], istride[kMaxRank], ostride[kMaxRank], offset;
+        int     dense_out; // output strides are the dense ones: Y[i]
     };
 
     template <typename T> __global__ void __launch_bounds__(256) strided_copy_kernel(const T *__restrict__ X, T *__restrict__ Y, int64_t n, CopyDesc cd) {
         int64_t       i      = (int64_t) blockIdx.x * blockDim.x + threadIdx.x;
         const int64_t stride = (int64_t) gridDim.x * blockDim.x;
         for (; i < n; i += stride) {
-            int64_t rem = i, src = cd.offset;
+            int64_t rem = i, src = cd.offset, dst = 0;
             for (int d = cd.rank - 1; d >= 0; --d) {
                 const int64_t c = rem % cd.shape[d];
                 rem /= cd.shape[d];
                 src += c * cd.istride[d];
+                dst += c * cd.ostride[d];
             }
-            Y[i] = X[src];
+            Y[cd.dense_out ? i : dst] = X[src];
         }
     }
 
@@ -209,17 +211,19 @@ int vkc_softmax(vkc_ctx *ctx, const void *X, void *Y, int64_t outer, int64_t inn
     return vkc_post_launch(ctx, "softmax");
 }
 
-int vkc_strided_copy(vkc_ctx *ctx, const void *X, void *Y, const int64_t *shape, const int64_t *in_strides, int rank, int64_t in_offset, int dtype,
-                     vkc_stream stream) {
+int vkc_strided_copy2(vkc_ctx *ctx, const void *X, void *Y, const int64_t *shape, const int64_t *in_strides, const int64_t *out_strides, int rank,
+                      int64_t in_offset, int dtype, vkc_stream stream) {
     if (!ctx) return VKC_ERR_INVALID;
     VKC_REQUIRE(ctx, rank >= 1 && rank <= kMaxRank && shape && in_strides, "strided_copy: rank %d out of range", rank);
     CopyDesc cd;
-    cd.rank   = rank;
-    cd.offset = in_offset;
-    int64_t n = 1;
+    cd.rank      = rank;
+    cd.offset    = in_offset;
+    cd.dense_out = out_strides ? 0 : 1;
+    int64_t n    = 1;
     for (int d = 0; d < rank; ++d) {
         cd.shape[d]   = shape[d];
         cd.istride[d] = in_strides[d];
+        cd.ostride[d] = out_strides ? out_strides[d] : 0;
         n *= shape[d];
     }
     if (n == 0) return VKC_OK;
@@ -231,6 +235,11 @@ int vkc_strided_copy(vkc_ctx *ctx, const void *X, void *Y, const int64_t *shape,
     else
         strided_copy_kernel<uint16_t><<<g, 256, 0, st>>>((const uint16_t *) X, (uint16_t *) Y, n, cd);
     return vkc_post_launch(ctx, "strided_copy");
+}
+
+int vkc_strided_copy(vkc_ctx *ctx, const void *X, void *Y, const int64_t *shape, const int64_t *in_strides, int rank, int64_t in_offset, int dtype,
+                     vkc_stream stream) {
+    return vkc_strided_copy2(ctx, X, Y, shape, in_strides, nullptr, rank, in_offset, dtype, stream);
 }
 
 } // extern "C"

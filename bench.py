@@ -37,7 +37,7 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 #   prefill: 113.87 MB for 4 x 16 x 2048 (batch, head, query row) units  (profiles/attn_prefill_bf16_d128_seq2048.md);
 #            K/V re-reads are served by L2, so DRAM traffic grows with the number of row units;
 #   decode : 1.0266 x the algorithmic bytes of the launch                 (profiles/attn_decode_f16_config5.md).
-NCU_PREFILL_DRAM_BYTES_PER_ROW_UNIT = 868.8
+NCU_PREFILL_DRAM_BYTES_PER_ROW_UNIT = 855.2
 NCU_DECODE_DRAM_OVER_ALGORITHMIC = 1.0266
 
 PREFILL = dict(B=4, H=16, S=8192, D=128, causal=False, dtype="bf16", seed=1005)
@@ -261,6 +261,9 @@ def bench_decode(ctx, cfg, steps, warmup, rank, world):
     return dict(total_ms=total_ms, per_launch_ms=per_ms, bytes_step_all=bytes_all, bytes_step_rank=bytes_alg, gbs=bytes_all * steps / (total_ms * 1e-3) / 1e9)
 
 
+NO_TUNE = False
+
+
 def bench_encoder(ctx, cfg, steps, warmup, rank, world):
     import torch
     from vknn_b200.synthetic import encoder_weights
@@ -277,7 +280,8 @@ def bench_encoder(ctx, cfg, steps, warmup, rank, world):
 
     # the layer is 7 short launches: replay it as a CUDA graph (what the C++ segment does), one graph per input set
     layer.forward(xs[0], out=ys[0])
-    layer.tune(xs[0])  # per-shape GEMM configuration by measurement, as the C++ segment does at plan time (Hint::Tuning)
+    if not NO_TUNE:
+        layer.tune(xs[0])  # per-shape GEMM configuration by measurement, as the C++ segment does at plan time (Hint::Tuning)
     for i in range(ns):
         layer.forward(xs[i], out=ys[i])
     torch.cuda.synchronize()
@@ -306,7 +310,8 @@ def bench_stack(ctx, cfg, steps, warmup, rank, world):
     g = torch.Generator(device="cuda").manual_seed(cfg["seed"] + rank)
     x = torch.randn(1, T, d, generator=g, device="cuda", dtype=torch.float32).half()
     stack.forward(x)
-    stack.tune(x)
+    if not NO_TUNE:
+        stack.tune(x)
     stack.forward(x)
     torch.cuda.synchronize()
     graph, _ = stack.capture(x)
@@ -438,7 +443,10 @@ def main():
     ap.add_argument("--causal", action="store_true")
     ap.add_argument("--no-extra", action="store_true", help="skip the decode / encoder / sweep extras")
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--no-tune", action="store_true", help="encoder workloads: keep the built-in GEMM configurations (no per-shape timing)")
     args = ap.parse_args()
+    global NO_TUNE
+    NO_TUNE = args.no_tune
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
         return run_reference(args)

@@ -34,7 +34,7 @@ L2_BYTES = 126 * 1024 * 1024
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 # DRAM traffic per unit from the ncu captures summarised under profiles/ (dram__bytes_read.sum + dram__bytes_write.sum):
-#   prefill: 113.87 MB for 4 x 16 x 2048 (batch, head, query row) units  (profiles/attn_prefill_bf16_d128_seq2048.md);
+#   prefill: 112.10 MB for 4 x 16 x 2048 (batch, head, query row) units  (profiles/attn_prefill_bf16_d128_seq2048.md);
 #            K/V re-reads are served by L2, so DRAM traffic grows with the number of row units;
 #   decode : 1.0266 x the algorithmic bytes of the launch                 (profiles/attn_decode_f16_config5.md).
 NCU_PREFILL_DRAM_BYTES_PER_ROW_UNIT = 855.2

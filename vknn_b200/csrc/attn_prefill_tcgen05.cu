@@ -7,7 +7,7 @@
 //
 //   warp 8     TMA producer: both Q tiles once, then K and V tiles through two independent 2-stage
 //              shared-memory rings (128-byte swizzle, plain per-CTA tiled loads; rows past the end read as zeros).
-//   warp 9     MMA issuer (one elected lane) and owner of the tensor-memory allocation (512 columns):
+//   warp 9     MMA issuer (the warp runs the loop, one elected lane issues) and owner of the tensor-memory allocation (512 columns):
 //                S_t (128 fp32 columns)  = Q_t . K_j^T     both operands from shared memory (K-major)
 //                O_t (D fp32 columns)   += P_t . V_j       P_t from tensor memory, V_j MN-major from its row-major tile
 //              issue order per key tile j:  P.V_A(j), Q.K_A(j+1), P.V_B(j), Q.K_B(j+1).
@@ -248,54 +248,59 @@ namespace {
             }
           } else if (warp == kWarpMma) {
             // ------------------------------------------------------------------ MMA issuer
-            if (n_max > 0 && ptx::elect_one()) {
+            // The whole warp runs the loop (waits, descriptor arithmetic) convergently and one elected lane issues the
+            // tcgen05 instructions. One issuer serves both query tiles in strict alternation: that alternation is what
+            // keeps the two tiles half a period apart, so that one tile's exponentials run under the other's MMAs
+            // (an issuer per tile lets the tiles fall into step and share the exponential unit: 949 vs 1265 TFLOP/s).
+            const bool leader = ptx::elect_one();
+            if (n_max > 0) {
                 // Base descriptors once; a step along K only moves the 14-bit start-address field (16-byte units).
                 const uint64_t dQ0 = ptx::smem_desc_sw128(sQ, 16, 1024), dQ1 = ptx::smem_desc_sw128(sQ + L::Q_BYTES, 16, 1024);
                 const uint64_t dK0 = ptx::smem_desc_sw128(sK, 16, 1024), dK1 = ptx::smem_desc_sw128(sK + L::KV_BYTES, 16, 1024);
                 const uint64_t dV0 = ptx::smem_desc_sw128(sV, BN * 128, 1024), dV1 = ptx::smem_desc_sw128(sV + L::KV_BYTES, BN * 128, 1024);
+                long long *tlm = (p.timeline && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && leader) ? p.timeline : nullptr;
+                auto wait = [&](int barIdx, uint32_t parity) { return __all_sync(0xffffffffu, ptx::mbar_wait(bar(barIdx), parity, ctl + 1, p.dev_err)); };
                 auto issue_qk = [&](int t, int j) {
                     const uint64_t aq = t ? dQ1 : dQ0, bk = (j & 1) ? dK1 : dK0;
                     const uint32_t d  = tmem + kColS + t * BN;
 #pragma unroll
                     for (int k = 0; k < D / 16; ++k) {
                         const uint32_t off = ((uint32_t) (k / 4) * (BM * 128) + (uint32_t) (k % 4) * 32) >> 4;
-                        ptx::mma_f16_ss(d, aq + off, bk + off, kIdescQK, k != 0 ? 1u : 0u);
+                        if (leader) ptx::mma_f16_ss(d, aq + off, bk + off, kIdescQK, k != 0 ? 1u : 0u);
                     }
-                    ptx::tc_commit(bar(bSF + t));
+                    if (leader) ptx::tc_commit(bar(bSF + t));
                 };
                 auto issue_pv = [&](int t, int j, int part) {
                     // V tile: D/64 spans of [128 keys x 128 B]; 16 keys per MMA step = 2048 B; `part` selects BN / kPParts keys
                     const uint64_t bv = (j & 1) ? dV1 : dV0;
                     const uint32_t d = tmem + kColO + t * D, a = tmem + kColS + t * BN;
 #pragma unroll
-                    for (int k = part * (8 / kPParts); k < (part + 1) * (8 / kPParts); ++k) ptx::mma_f16_ts(d, a + k * 8, bv + (uint64_t) (k * 128), kIdescPV, (j | k) != 0 ? 1u : 0u);
+                    for (int k = part * (8 / kPParts); k < (part + 1) * (8 / kPParts); ++k)
+                        if (leader) ptx::mma_f16_ts(d, a + k * 8, bv + (uint64_t) (k * 128), kIdescPV, (j | k) != 0 ? 1u : 0u);
                 };
-                bool ok = ptx::mbar_wait(bar(bQ), 0, ctl + 1, p.dev_err);
-                ok      = ok && ptx::mbar_wait(bar(bKF + 0), 0, ctl + 1, p.dev_err);
+                bool ok = wait(bQ, 0) && wait(bKF + 0, 0);
                 if (ok) {
                     ptx::tc_fence_after();
 #pragma unroll
                     for (int t = 0; t < kQTiles; ++t)
                         if (n_t[t] > 0) issue_qk(t, 0);
-                    ptx::tc_commit(bar(bKE + 0));
+                    if (leader) ptx::tc_commit(bar(bKE + 0));
                 }
                 for (int j = 0; j < n_max && ok; ++j) {
                     const int vs = j % VS;
-                    ok = ptx::mbar_wait(bar(bVF + vs), (j / VS) & 1, ctl + 1, p.dev_err);
+                    ok = wait(bVF + vs, (j / VS) & 1);
                     const bool more = j + 1 < n_max;
 #pragma unroll
                     for (int t = 0; t < kQTiles && ok; ++t) {
                         if (j < n_t[t]) {
-                            ok = ptx::mbar_wait(bar(bPF + kPParts * t), j & 1, ctl + 1, p.dev_err);
+                            ok = wait(bPF + kPParts * t, j & 1);
                             if (!ok) break;
-                            long long *tl = (p.timeline && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (j == kTlTile || j == kTlTile + 1))
-                                                ? p.timeline + (j - kTlTile) * 16 + 10 + t * 2 : nullptr;
-                            if (tl) tl[0] = clock64();
+                            if (tlm && (j == kTlTile || j == kTlTile + 1)) tlm[(j - kTlTile) * 16 + 10 + t * 2] = clock64();
                             ptx::tc_fence_after();
                             issue_pv(t, j, 0);
 #pragma unroll
                             for (int part = 1; part < kPParts && ok; ++part) {
-                                ok = ptx::mbar_wait(bar(bPF + kPParts * t + part), j & 1, ctl + 1, p.dev_err);
+                                ok = wait(bPF + kPParts * t + part, j & 1);
                                 if (ok) {
                                     ptx::tc_fence_after();
                                     issue_pv(t, j, part);
@@ -303,19 +308,21 @@ namespace {
                             }
                             if (!ok) break;
                             if (j + 1 < n_t[t]) {
-                                ok = ptx::mbar_wait(bar(bKF + (j + 1) % KS), ((j + 1) / KS) & 1, ctl + 1, p.dev_err);
+                                ok = wait(bKF + (j + 1) % KS, ((j + 1) / KS) & 1);
                                 if (!ok) break;
                                 ptx::tc_fence_after();
                                 issue_qk(t, j + 1);
-                                if (tl) tl[1] = clock64();
-                            } else {
+                                if (tlm && (j == kTlTile || j == kTlTile + 1)) tlm[(j - kTlTile) * 16 + 11 + t * 2] = clock64();
+                            } else if (leader) {
                                 ptx::tc_commit(bar(bOF + t)); // O_t complete
                             }
                         }
                     }
                     if (!ok) break;
-                    ptx::tc_commit(bar(bVE + vs));
-                    if (more) ptx::tc_commit(bar(bKE + (j + 1) % KS));
+                    if (leader) {
+                        ptx::tc_commit(bar(bVE + vs));
+                        if (more) ptx::tc_commit(bar(bKE + (j + 1) % KS));
+                    }
                 }
             }
           }

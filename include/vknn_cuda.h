@@ -157,8 +157,10 @@ VKC_API int vkc_layernorm(vkc_ctx *ctx, const void *X, const float *gamma, const
 /* ---- K5: generic per-element step program. Reference: applyPwEpilogue / FusedPointwiseCpu
  * src/backend/cpu/ops/fused_pointwise.cpp:107-185, BinaryCpu ops/binary.cpp:31-140, UnaryCpu ops/unary.cpp:10-69,
  * AddCpu ops/add.cpp:14-125; device path replaced: shaders/fused_pw_flat.comp + pw_epilogue.glsl:10-39.
- *   Y = program(X); steps: 4 ints per step {kind 0 binary/1 unary/2 act, code, operand index (1-based into
- *   operands[]), unused}; params: 2 floats per step; operand i has element strides op_strides[i*rank .. +rank)
+ *   Y = program(X); steps: 4 ints per step {kind 0 binary/1 unary/2 act/3 select, code, operand index (1-based into
+ *   operands[]), unused}; binary codes 16/17/18 are Equal/Greater/GreaterEqual (1.0 / 0.0 results, EqualCpu ops/equal.cpp,
+ *   ops/greater.cpp, ops/greaterequal.cpp); a select step (WhereCpu ops/where.cpp:17-80) treats the running value as the
+ *   condition and replaces it by operand[index] when non-zero, else by operand[code]; params: 2 floats per step; operand i has element strides op_strides[i*rank .. +rank)
  *   against the output shape (0 on broadcast dims). At most 8 steps, 6 operands, rank 8
  *   (include/vknn/op_type.h:65-67). Operands share the storage dtype. ---- */
 VKC_API int vkc_pointwise(vkc_ctx *ctx, const void *X, void *Y, const int64_t *shape, int rank, int nsteps, const int32_t *steps,
@@ -168,6 +170,11 @@ VKC_API int vkc_pointwise(vkc_ctx *ctx, const void *X, void *Y, const int64_t *s
 /* ---- standalone Softmax over rows of `inner` contiguous elements, for Softmax nodes outside an attention
  * pattern. Reference: SoftmaxCpu::run src/backend/cpu/ops/softmax.cpp:9-47; shaders/flat_softmax.comp:9-50. ---- */
 VKC_API int vkc_softmax(vkc_ctx *ctx, const void *X, void *Y, int64_t outer, int64_t inner, int dtype, vkc_stream stream);
+
+/* ---- Reduce family over the trailing `n` contiguous elements of each of `rows` rows (the caller moves the reduced axes
+ * last): op 0 mean, 1 sum, 2 max, 3 min, 4 product, 5 L2 norm; fp32 accumulation. Reference: ReduceCpu::run
+ * src/backend/cpu/ops/reduce.cpp:11-108 (ReduceType include/vknn/reduce_type.h:8). ---- */
+VKC_API int vkc_reduce_rows(vkc_ctx *ctx, const void *X, void *Y, int64_t rows, int64_t n, int op, int dtype, vkc_stream stream);
 
 /* ---- strided gather copy Y[i] = X[sum_d idx_d(i) * in_strides[d]] over an output of `shape`, for Transpose /
  * Gather / Slice nodes that cannot be absorbed as strides. Reference: TransposeCpu::run ops/transpose.cpp:8-63;

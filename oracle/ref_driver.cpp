@@ -71,6 +71,8 @@ namespace {
             {"Conv", OpType::Conv},           {"Slice", OpType::Slice},         {"Split", OpType::Split},
             {"Expand", OpType::Expand},       {"Tile", OpType::Tile},           {"Concat", OpType::Concat},
             {"Squeeze", OpType::Squeeze},     {"Unsqueeze", OpType::Unsqueeze},
+            {"Reduce", OpType::Reduce},       {"Where", OpType::Where},         {"Equal", OpType::Equal},
+            {"Greater", OpType::Greater},     {"GreaterEqual", OpType::GreaterEqual},
         };
         auto it = m.find(n);
         if (it == m.end()) {

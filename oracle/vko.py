@@ -435,3 +435,35 @@ def vit_frontend_graph(img, wconv, bconv, cls, pos, cos, sin):
     g.node("Slice", "every_other", ["seqpos"], ["strided"], starts=[0, 0], ends=[N + 1, O // 2], axes=[1, 2], steps=[2, 1])
     g.node("Tile", "tile", ["strided", "reps"], ["tiled"])
     return g
+
+
+def masked_pool_graph(x, thr):
+    """Token selection and pooling as an exporter emits them: Greater / GreaterEqual / Equal -> Where -> Reduce{Sum, Mean, Max,
+    Min, L2} over different axis sets, with and without keepdims. x [B,T,d]; thr [1,1,d] threshold initializer."""
+    B, T, d = x.shape
+    g = RefGraph()
+    g.input("x", x)
+    g.init("thr", thr)
+    g.init("zero", np.zeros((1,), dtype=np.float32))
+    g.init("axes_t", np.array([1], dtype=np.int64))
+    for n in ("gt", "kept", "mx", "eq", "rowmean", "ge"):
+        g.inter(n)
+    g.output("pooled", (B, d))
+    g.output("count", (B, 1, d))
+    g.output("argmax_mask_sum", (T,))
+    g.output("l2", (B, T))
+    g.output("minv", (1, 1, d))
+    g.output("ge_mean", (B, T, 1))
+    g.node("Greater", "gt", ["x", "thr"], ["gt"])
+    g.node("Where", "keep", ["gt", "x", "zero"], ["kept"])
+    g.node("Reduce", "pool", ["kept", "axes_t"], ["pooled"], subop=1, keepdims=0)
+    g.node("Reduce", "count", ["gt"], ["count"], subop=1, axes=[1], keepdims=1)
+    g.node("Reduce", "mx", ["x"], ["mx"], subop=2, axes=[0, 2], keepdims=1)
+    g.node("Equal", "eq", ["x", "mx"], ["eq"])
+    g.node("Reduce", "eqsum", ["eq"], ["argmax_mask_sum"], subop=1, axes=[0, 2], keepdims=0)
+    g.node("Reduce", "l2", ["x"], ["l2"], subop=5, axes=[-1], keepdims=0)
+    g.node("Reduce", "minv", ["x"], ["minv"], subop=3, axes=[0, 1], keepdims=1)
+    g.node("Reduce", "rowmean", ["x"], ["rowmean"], subop=0, axes=[2], keepdims=1)
+    g.node("GreaterEqual", "ge", ["x", "rowmean"], ["ge"])
+    g.node("Reduce", "ge_mean", ["ge"], ["ge_mean"], subop=0, axes=[2], keepdims=1)
+    return g

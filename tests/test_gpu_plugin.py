@@ -156,3 +156,27 @@ def test_vit_frontend_ops_run_on_the_cuda_backend(precision):
             assert np.abs(a - b).max() <= 1e-4 * max(1.0, np.abs(b).max()), what
         else:
             assert_low(a, b, what)
+
+
+@pytest.mark.parametrize("precision", ["low", "high"])
+def test_selection_and_reduce_ops_run_on_the_cuda_backend(precision):
+    """Greater / GreaterEqual / Equal, Where and the Reduce family (sum, mean, max, min, L2; leading, middle, trailing and
+    mixed axes; keepdims on and off) plan into one CUDA segment and match the reference CPU backend. Inputs are exactly
+    representable in fp16, so the comparisons see the same values at both storage precisions."""
+    rng = np.random.default_rng(7)
+    B, T, d = 3, 37, 48
+    x = rng.standard_normal((B, T, d)).astype(np.float16).astype(np.float32)
+    thr = (0.3 * rng.standard_normal((1, 1, d))).astype(np.float16).astype(np.float32)
+    ref, _ = vko.masked_pool_graph(x, thr).run(backend="cpu")
+    got, info = vko.masked_pool_graph(x, thr).run(backend="cuda", precision=precision, iters=2)
+    kinds = [n[0] for n in info["nodes"]]
+    for op in ("Greater", "GreaterEqual", "Equal", "Where", "Reduce"):
+        assert op in kinds, kinds
+    assert all(n[1] == CUDA_KIND for n in info["nodes"]), info["nodes"]
+    names = ("pooled", "count", "argmax_mask_sum", "l2", "minv", "ge_mean")
+    for a, b, what in zip(got, ref, names):
+        assert a.shape == b.shape, what
+        tol = 1e-4 * max(1.0, np.abs(b).max()) if precision == "high" else 1e-2 * max(1.0, np.abs(b).max())
+        assert np.abs(a - b).max() <= tol, (what, float(np.abs(a - b).max()))
+    # counts and masks are exact integers in either precision
+    assert np.array_equal(got[1], ref[1]) and np.array_equal(got[2], ref[2])

@@ -140,3 +140,37 @@ def test_live_pin_against_reference_engine():
         q, k, v = (rng.standard_normal(s).astype(np.float32) for s in ((B, H, Sq, D), (B, H, Skv, D), (B, H, Skv, D)))
         (o,), _ = vko.attention_graph(q, k, v, 0.3).run()
         eq(vko.attention(q, k, v, 0.3), o)
+
+
+@pytest.mark.skipif(not vko.have_ref(), reason="reference driver not built")
+def test_frontend_and_pooling_graphs_on_the_reference_cpu_backend():
+    """The graph builders the plug-in tests use for the ops around the encoder blocks (patch-embedding Conv, Expand, Concat,
+    Slice, Split, Tile, Where, comparisons, Reduce) are pinned here: the reference CPU backend must reproduce a plain numpy
+    statement of the same computation."""
+    rng = np.random.default_rng(5)
+    B, C, H, W, p, O = 2, 3, 64, 48, 16, 64
+    N = (H // p) * (W // p)
+    img = rng.standard_normal((B, C, H, W)).astype(np.float32)
+    wc = (0.05 * rng.standard_normal((O, C, p, p))).astype(np.float32)
+    bc = (0.1 * rng.standard_normal(O)).astype(np.float32)
+    cls = rng.standard_normal((1, 1, O)).astype(np.float32)
+    pos = rng.standard_normal((1, N + 1, O)).astype(np.float32)
+    cos = np.cos(rng.standard_normal((N, O))).astype(np.float32)
+    sin = np.sin(rng.standard_normal((N, O))).astype(np.float32)
+    outs, info = vko.vit_frontend_graph(img, wc, bc, cls, pos, cos, sin).run(backend="cpu")
+    pat = img.reshape(B, C, H // p, p, W // p, p).transpose(0, 2, 4, 1, 3, 5).reshape(B, N, C * p * p)
+    seq = np.concatenate([np.broadcast_to(cls, (B, 1, O)), pat @ wc.reshape(O, -1).T + bc], 1) + pos
+    pa = seq[:, 1:]
+    rope = pa * cos + np.concatenate([-pa[..., O // 2:], pa[..., :O // 2]], -1) * sin
+    tiled = np.tile(seq[:, 0:N + 1:2, :O // 2], (1, 2, 3))
+    for a, b in zip(outs, (seq, rope, tiled)):
+        assert a.shape == b.shape and np.abs(a - b).max() <= 1e-4
+
+    x = rng.standard_normal((3, 37, 48)).astype(np.float16).astype(np.float32)
+    thr = (0.3 * rng.standard_normal((1, 1, 48))).astype(np.float16).astype(np.float32)
+    outs, _ = vko.masked_pool_graph(x, thr).run(backend="cpu")
+    gt = x > thr
+    exp = [np.where(gt, x, 0).sum(1), gt.sum(1, keepdims=True), (x == x.max((0, 2), keepdims=True)).sum((0, 2)), np.sqrt((x * x).sum(-1)),
+           x.min((0, 1), keepdims=True), (x >= x.mean(2, keepdims=True)).mean(2, keepdims=True)]
+    for a, b in zip(outs, exp):
+        assert a.shape == b.shape and np.abs(a - b).max() <= 1e-4

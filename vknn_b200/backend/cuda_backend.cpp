@@ -101,7 +101,8 @@ namespace vknn {
         };
 
         struct Step {
-            enum Kind { Gemm, Attn, LayerNorm, Pointwise, Softmax, Copy } kind;
+            enum Kind { Gemm, Attn, LayerNorm, Pointwise, Softmax, Copy, Reduce } kind;
+            int reduceOp = 0;
             // generic operands (device pointers resolved at plan time)
             const void *a = nullptr, *b = nullptr, *c = nullptr;
             void       *d = nullptr;
@@ -223,7 +224,12 @@ namespace vknn {
                 case OpType::Expand:
                 case OpType::Tile:
                 case OpType::Concat:
-                case OpType::Conv: return true;
+                case OpType::Conv:
+                case OpType::Reduce:
+                case OpType::Where:
+                case OpType::Equal:
+                case OpType::Greater:
+                case OpType::GreaterEqual: return true;
                 default: return false;
             }
         }
@@ -273,6 +279,20 @@ namespace vknn {
                     return b && commutative;
                 }
                 case OpType::FusedPointwise: return !g.isInitializer(nd.inputs[0]);
+                case OpType::Equal:
+                case OpType::Greater:
+                case OpType::GreaterEqual: {
+                    // like Binary: one runtime operand must already have the output shape (the other may broadcast)
+                    const Shape &o = g.desc(nd.outputs[0]).shape;
+                    return (g.desc(nd.inputs[0]).shape == o && !g.isInitializer(nd.inputs[0])) || (g.desc(nd.inputs[1]).shape == o && !g.isInitializer(nd.inputs[1]));
+                }
+                case OpType::Where: // the condition drives the step program: it must be a runtime tensor of the output shape
+                    return nd.inputs.size() == 3 && g.desc(nd.inputs[0]).shape == g.desc(nd.outputs[0]).shape && !g.isInitializer(nd.inputs[0]) &&
+                           g.desc(nd.inputs[0]).dtype != DType::Int64;
+                case OpType::Reduce: {
+                    if (nd.inputs.size() > 1 && nd.inputs[1] != kNoTensor && !g.isInitializer(nd.inputs[1])) return false;
+                    return nd.subOp >= 0 && nd.subOp <= 5 && !g.isInitializer(nd.inputs[0]);
+                }
                 case OpType::Slice:
                 case OpType::Expand:
                 case OpType::Tile: {
@@ -770,6 +790,21 @@ namespace vknn {
                 s.pwSteps.insert(s.pwSteps.end(), {2, (int) n.fusedAct, -1, 0});
                 s.pwParams.insert(s.pwParams.end(), {n.actLo, n.actHi});
             }
+        } else if (n.type == OpType::Equal || n.type == OpType::Greater || n.type == OpType::GreaterEqual) {
+            // comparison codes of the step program: 16 ==, 17 >, 18 >=; with the operands swapped 19 <, 20 <=
+            int      code  = n.type == OpType::Equal ? 16 : (n.type == OpType::Greater ? 17 : 18);
+            TensorId other = n.inputs[1];
+            if (!(g.desc(primary).shape == oshape && !initIds_.count(primary))) {
+                std::swap(primary, other);
+                code = code == 16 ? 16 : (code == 17 ? 19 : 20);
+            }
+            const int oi = addOperand(other);
+            s.pwSteps  = {0, code, oi, 0};
+            s.pwParams = {0.f, 0.f};
+        } else if (n.type == OpType::Where) {
+            const int ix = addOperand(n.inputs[1]), iy = addOperand(n.inputs[2]);
+            s.pwSteps  = {3, iy, ix, 0};
+            s.pwParams = {0.f, 0.f};
         } else if (n.type == OpType::Unary) {
             s.pwSteps  = {1, n.subOp, -1, 0};
             s.pwParams = {n.actLo, n.actHi};
@@ -1035,9 +1070,42 @@ namespace vknn {
                     steps_.push_back(s);
                     break;
                 }
+                case OpType::Reduce: {
+                    // move the reduced axes last (one strided copy), then one warp per output element
+                    // (src/backend/cpu/ops/reduce.cpp:11-108)
+                    const View &x = views_.at(n.inputs[0]);
+                    const int   r = (int) x.shape.size();
+                    std::vector<int64_t> axes = n.attr.getints("axes");
+                    if (axes.empty() && n.inputs.size() > 1 && n.inputs[1] != kNoTensor) axes = i64Inits_.at(n.inputs[1]);
+                    std::set<int> ax;
+                    for (int64_t a : axes) ax.insert((int) (a < 0 ? a + r : a));
+                    if (axes.empty())
+                        for (int i = 0; i < r; ++i) ax.insert(i);
+                    View    v2 = x;
+                    int64_t rows = 1, red = 1;
+                    v2.shape.clear(), v2.strides.clear();
+                    for (int i = 0; i < r; ++i)
+                        if (!ax.count(i)) v2.shape.push_back(x.shape[i]), v2.strides.push_back(x.strides[i]), rows *= x.shape[i];
+                    for (int i = 0; i < r; ++i)
+                        if (ax.count(i)) v2.shape.push_back(x.shape[i]), v2.strides.push_back(x.strides[i]), red *= x.shape[i];
+                    View a = materialize(v2, "reduce");
+                    View y = newTensor(n.outputs[0], g.desc(n.outputs[0]).shape);
+                    if (prod(y.shape) != rows) fail(Status::RuntimeError, "Reduce: planned size differs from the inferred one");
+                    Step s;
+                    s.kind = Step::Reduce;
+                    s.a = ptrOf(a), s.d = ptrOf(y);
+                    s.rows = rows, s.norm = red, s.reduceOp = n.subOp;
+                    s.label = "reduce";
+                    steps_.push_back(s);
+                    break;
+                }
                 case OpType::Binary:
                 case OpType::Add:
                 case OpType::Unary:
+                case OpType::Where:
+                case OpType::Equal:
+                case OpType::Greater:
+                case OpType::GreaterEqual:
                 case OpType::FusedPointwise: planPointwise(n); break;
                 default: fail(Status::Unsupported, std::string("node type ") + opTypeName(n.type));
             }
@@ -1113,6 +1181,9 @@ namespace vknn {
                 check(ctx_, vkc_pointwise(ctx_, s.a, s.d, s.shape.data(), (int) s.shape.size(), (int) s.pwSteps.size() / 4, s.pwSteps.data(),
                                           s.pwParams.data(), (int) s.operands.size(), s.operands.data(), s.opStrides.data(), dtype_, nullptr),
                       "vkc_pointwise");
+                break;
+            case Step::Reduce:
+                check(ctx_, vkc_reduce_rows(ctx_, s.a, s.d, s.rows, s.norm, s.reduceOp, dtype_, nullptr), "vkc_reduce_rows");
                 break;
             case Step::Copy:
                 if (s.outStrides.empty())

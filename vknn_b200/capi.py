@@ -80,6 +80,7 @@ def load_library():
     L.vkc_pointwise.argtypes = [vp, vp, vp, vp, i32, i32, vp, vp, i32, vp, vp, i32, vp]
     L.vkc_softmax.argtypes = [vp, vp, vp, i64, i64, i32, vp]
     L.vkc_strided_copy.argtypes = [vp, vp, vp, vp, vp, i32, i64, i32, vp]
+    L.vkc_reduce_rows.argtypes = [vp, vp, vp, i64, i64, i32, i32, vp]
     L.vkc_strided_copy2.argtypes = [vp, vp, vp, vp, vp, vp, i32, i64, i32, vp]
     L.vkc_graph_begin.argtypes = [vp]
     L.vkc_graph_end.argtypes = [vp, C.POINTER(vp)]

@@ -25,6 +25,11 @@ namespace {
             case 3: return fmaxf(a, b);
             case 4: return fminf(a, b);
             case 5: return powf(a, b);
+            case 16: return a == b ? 1.f : 0.f; // Equal / Greater / GreaterEqual nodes: 1.0 / 0.0 like the reference
+            case 17: return a > b ? 1.f : 0.f;
+            case 18: return a >= b ? 1.f : 0.f;
+            case 19: return a < b ? 1.f : 0.f; // the two above with the operands swapped
+            case 20: return a <= b ? 1.f : 0.f;
             default: return a + b;
         }
     }
@@ -84,6 +89,21 @@ namespace {
                         }
                     }
                     acc = pw_binary(acc, St<T>::ld((const T *) pg.operand[oi] + io), pg.code[s]);
+                } else if (pg.kind[s] == 3) {
+                    // select (Where): acc is the condition; operands opidx / code are the "true" / "false" values
+                    const int oi = acc != 0.f ? pg.opidx[s] : pg.code[s];
+                    int64_t   io = 0;
+                    if (pg.same_shape[oi]) {
+                        io = i;
+                    } else {
+                        int64_t rem = i;
+                        for (int d = pg.rank - 1; d >= 0; --d) {
+                            const int64_t c = rem % pg.shape[d];
+                            rem /= pg.shape[d];
+                            io += c * pg.ostride[oi][d];
+                        }
+                    }
+                    acc = St<T>::ld((const T *) pg.operand[oi] + io);
                 } else if (pg.kind[s] == 1) {
                     acc = pw_unary(acc, pg.code[s], pg.p0[s], pg.p1[s]);
                 } else {
@@ -110,6 +130,26 @@ namespace {
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
         for (int64_t j = lane; j < inner; j += 32) St<T>::st(yr + j, expf(St<T>::ld(xr + j) - mx) / s);
+    }
+
+    // One warp per output element: `n` contiguous values reduced in fp32 (the caller has moved the reduced axes last).
+    // op: 0 mean, 1 sum, 2 max, 3 min, 4 product, 5 L2 norm (the reference's ReduceType).
+    template <typename T> __global__ void __launch_bounds__(256) reduce_rows_kernel(const T *__restrict__ X, T *__restrict__ Y, int64_t rows, int64_t n, int op) {
+        const int     lane = threadIdx.x & 31;
+        const int64_t row  = (int64_t) blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+        if (row >= rows) return;
+        const T *xr  = X + row * n;
+        float    acc = op == 2 ? -INFINITY : (op == 3 ? INFINITY : (op == 4 ? 1.f : 0.f));
+        for (int64_t j = lane; j < n; j += 32) {
+            const float v = St<T>::ld(xr + j);
+            acc           = op == 2 ? fmaxf(acc, v) : (op == 3 ? fminf(acc, v) : (op == 4 ? acc * v : (op == 5 ? acc + v * v : acc + v)));
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float w = __shfl_xor_sync(0xffffffffu, acc, o);
+            acc           = op == 2 ? fmaxf(acc, w) : (op == 3 ? fminf(acc, w) : (op == 4 ? acc * w : acc + w));
+        }
+        if (lane == 0) St<T>::st(Y + row, op == 0 ? acc / (float) n : (op == 5 ? sqrtf(acc) : acc));
     }
 
     struct CopyDesc {
@@ -177,10 +217,12 @@ int vkc_pointwise(vkc_ctx *ctx, const void *X, void *Y, const int64_t *shape, in
         pg.kind[s]  = steps[s * 4 + 0];
         pg.code[s]  = steps[s * 4 + 1];
         pg.opidx[s] = steps[s * 4 + 2] - 1; // the reference numbers operands from 1 (0 is the primary)
+        if (pg.kind[s] == 3) pg.code[s] -= 1; // select: the "false" operand, numbered the same way
         pg.p0[s]    = params ? params[s * 2 + 0] : 0.f;
         pg.p1[s]    = params ? params[s * 2 + 1] : 0.f;
-        VKC_REQUIRE(ctx, pg.kind[s] >= 0 && pg.kind[s] <= 2, "pointwise: bad step kind %d", pg.kind[s]);
-        if (pg.kind[s] == 0) VKC_REQUIRE(ctx, pg.opidx[s] >= 0 && pg.opidx[s] < noperands, "pointwise: step %d names operand %d of %d", s, pg.opidx[s] + 1, noperands);
+        VKC_REQUIRE(ctx, pg.kind[s] >= 0 && pg.kind[s] <= 3, "pointwise: bad step kind %d", pg.kind[s]);
+        if (pg.kind[s] == 3) VKC_REQUIRE(ctx, pg.code[s] >= 0 && pg.code[s] < noperands, "pointwise: select step %d names operand %d of %d", s, pg.code[s] + 1, noperands);
+        if (pg.kind[s] == 0 || pg.kind[s] == 3) VKC_REQUIRE(ctx, pg.opidx[s] >= 0 && pg.opidx[s] < noperands, "pointwise: step %d names operand %d of %d", s, pg.opidx[s] + 1, noperands);
     }
     if (n == 0) return VKC_OK;
     VKC_REQUIRE(ctx, X && Y, "pointwise: null tensor");
@@ -209,6 +251,24 @@ int vkc_softmax(vkc_ctx *ctx, const void *X, void *Y, int64_t outer, int64_t inn
         default: softmax_kernel<__nv_bfloat16><<<(unsigned) blocks, 256, 0, st>>>((const __nv_bfloat16 *) X, (__nv_bfloat16 *) Y, outer, inner); break;
     }
     return vkc_post_launch(ctx, "softmax");
+}
+
+int vkc_reduce_rows(vkc_ctx *ctx, const void *X, void *Y, int64_t rows, int64_t n, int op, int dtype, vkc_stream stream) {
+    if (!ctx) return VKC_ERR_INVALID;
+    VKC_REQUIRE(ctx, rows >= 0 && n >= 1, "reduce: bad extents");
+    VKC_REQUIRE(ctx, op >= 0 && op <= 5, "reduce: bad op %d", op);
+    VKC_REQUIRE(ctx, dtype == VKC_F32 || dtype == VKC_F16 || dtype == VKC_BF16, "reduce: bad dtype %d", dtype);
+    if (rows == 0) return VKC_OK;
+    VKC_REQUIRE(ctx, X && Y, "reduce: null tensor");
+    cudaStream_t  st     = vkc_pick_stream(ctx, stream);
+    const int64_t blocks = (rows + 7) / 8;
+    VKC_REQUIRE(ctx, blocks <= INT32_MAX, "reduce: too many rows");
+    switch (dtype) {
+        case VKC_F32: reduce_rows_kernel<float><<<(unsigned) blocks, 256, 0, st>>>((const float *) X, (float *) Y, rows, n, op); break;
+        case VKC_F16: reduce_rows_kernel<__half><<<(unsigned) blocks, 256, 0, st>>>((const __half *) X, (__half *) Y, rows, n, op); break;
+        default: reduce_rows_kernel<__nv_bfloat16><<<(unsigned) blocks, 256, 0, st>>>((const __nv_bfloat16 *) X, (__nv_bfloat16 *) Y, rows, n, op); break;
+    }
+    return vkc_post_launch(ctx, "reduce_rows");
 }
 
 int vkc_strided_copy2(vkc_ctx *ctx, const void *X, void *Y, const int64_t *shape, const int64_t *in_strides, const int64_t *out_strides, int rank,

@@ -351,6 +351,23 @@ def bench_layernorm(ctx, cfg, steps, warmup, rank, world):
     return dict(total_ms=total_ms, per_launch_ms=per_ms, bytes_step_rank=bytes_rank, gbs=bytes_rank * world * steps / (total_ms * 1e-3) / 1e9)
 
 
+def bench_raster(ctx, steps, warmup, rank, world):
+    """The reference's renderer size: 100352 gaussians, one 224 x 224 view (seeded synthetic splats stand in for the
+    encoder's outputs). One step = project + depth sort + composite; double (specification-exact) and float arithmetic."""
+    import torch
+    from vknn_b200.synthetic import splat_scene
+    H = W = 224
+    means, covs, colors, opac, w2c, K = splat_scene(1006 + rank, 100352, H, W)
+    dev = [torch.from_numpy(a).cuda() for a in (means, covs, colors, opac)]
+    out = {}
+    for name, precise in (("f64", True), ("f32", False)):
+        total_ms, _ = timed_loop(lambda i: ctx.raster_gaussians(*dev, w2c, K, H, W, near=0.2, precise=precise), steps, warmup, world)
+        ctx.sync()
+        out["ms_per_view_" + name] = total_ms / steps
+    out["workload"] = "3D Gaussian splatting: 100352 gaussians, one 224 x 224 view per rank"
+    return out
+
+
 # ---------------------------------------------------------------------------------------------------------------
 def cpu_baseline_prefill(cfg, budget_rows=256):
     """Times the reference's own CPU backend (oracle/_ref, one core) on a bounded sample of the headline workload:
@@ -494,6 +511,8 @@ def main():
             extra["layernorm"] = {"workload": "LayerNorm over 131072 rows x 1024 (config 3 width), fp16, replicated per rank",
                                   "GB/s_per_gpu": ln["bytes_step_rank"] / (ln["per_launch_ms"] * 1e-3) / 1e9,
                                   "frac_hbm_per_gpu": ln["bytes_step_rank"] / (ln["per_launch_ms"] * 1e-3) / 1e9 / pk["hbm_gbs"]}
+        if args.workload == "prefill" and not args.seq:
+            extra["raster"] = bench_raster(ctx, max(3, k // 2), 3, rank, world)
         if args.workload == "prefill" and not args.seq:
             sweep = {}
             for S, causal in ((4096, False), (16384, False), (8192, True), (16384, True)):

@@ -186,6 +186,19 @@ VKC_API int vkc_strided_copy(vkc_ctx *ctx, const void *X, void *Y, const int64_t
 VKC_API int vkc_strided_copy2(vkc_ctx *ctx, const void *X, void *Y, const int64_t *shape, const int64_t *in_strides, const int64_t *out_strides,
                               int rank, int64_t in_offset, int dtype, vkc_stream stream);
 
+/* ---- K6: 3D Gaussian-splatting rasterizer, the step after the encoder. Reference: the renderer specified by
+ * scripts/yonosplat/ref_rasterizer.py:22-75 (render_view) and implemented for the reference's device by
+ * shaders/raster_{preprocess,duplicate,bitonic,ranges,composite,fill}.comp with the host driver examples/yonosplat.cpp.
+ *   means [n,3], covs [n,3,3], colors [n,3], opacities [n]: fp32 device arrays (world space; colors already RGB);
+ *   w2c: host 4x4 row-major world-to-camera matrix; K: host 3x3 pixel intrinsics; znear: near plane (reference 0.2);
+ *   rgb [H,W,3] and alpha [H,W] (may be NULL): fp32 device outputs; precise != 0 computes in double like the float64
+ *   specification (bit-comparable decisions), 0 in float. workspace: device memory of vkc_raster_workspace_bytes(n,
+ *   precise) bytes, 256-byte aligned. ---- */
+VKC_API size_t vkc_raster_workspace_bytes(int64_t n, int precise);
+VKC_API int    vkc_raster_gaussians(vkc_ctx *ctx, const float *means, const float *covs, const float *colors, const float *opacities, int64_t n,
+                                    const double *w2c, const double *K, int H, int W, double znear, int precise, float *rgb, float *alpha,
+                                    void *workspace, size_t workspace_bytes, vkc_stream stream);
+
 /* ---- segment replay. Reference: the pre-recorded command buffer of a device segment,
  * src/backend/vulkan/vk_backend.cpp:1009-1210 (record) and :1353-1357 (submit). Calls made between begin and
  * end on the context's own stream are captured into a CUDA graph; launch replays it. ---- */

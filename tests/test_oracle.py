@@ -174,3 +174,16 @@ def test_frontend_and_pooling_graphs_on_the_reference_cpu_backend():
            x.min((0, 1), keepdims=True), (x >= x.mean(2, keepdims=True)).mean(2, keepdims=True)]
     for a, b in zip(outs, exp):
         assert a.shape == b.shape and np.abs(a - b).max() <= 1e-4
+
+
+def test_rasterizer_oracle_matches_the_reference_renderer():
+    """oracle/rasterizer.py against images rendered by the reference's own scripts/yonosplat/ref_rasterizer.py
+    (tests/golden/raster_golden.npz, written by tests/golden/make_raster_golden.py)."""
+    from oracle import rasterizer
+    g = np.load(os.path.join(os.path.dirname(__file__), "golden", "raster_golden.npz"))
+    for seed in (11, 12):
+        _, n, H, W = (int(v) for v in g["case_%d" % seed])
+        img, alpha = rasterizer.render_view(*rasterizer.scene(seed, n, H, W), H, W)
+        assert np.abs(img - g["rgb_%d" % seed]).max() <= 1e-6
+        assert np.abs(alpha - g["alpha_%d" % seed]).max() <= 1e-6
+        assert img.mean() > 0.1 and (alpha > 0.5).mean() > 0.5  # the scene actually covers the image

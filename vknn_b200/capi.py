@@ -86,6 +86,9 @@ def load_library():
     L.vkc_graph_end.argtypes = [vp, C.POINTER(vp)]
     L.vkc_graph_launch.argtypes = [vp, vp]
     L.vkc_graph_destroy.argtypes = [vp, vp]
+    L.vkc_raster_workspace_bytes.argtypes = [i64, i32]
+    L.vkc_raster_workspace_bytes.restype = sz
+    L.vkc_raster_gaussians.argtypes = [vp, vp, vp, vp, vp, i64, C.POINTER(C.c_double), C.POINTER(C.c_double), i32, i32, C.c_double, i32, vp, vp, vp, sz, vp]
     L.vkc_timer_start.argtypes = [vp, vp]
     L.vkc_timer_stop.argtypes = [vp, vp, C.POINTER(C.c_float)]
     _lib = L
@@ -263,6 +266,28 @@ class Context:
         inner = X.shape[-1]
         assert X.is_contiguous() and Y.is_contiguous()
         self._check(self.lib.vkc_softmax(self.h, X.data_ptr(), Y.data_ptr(), X.numel() // inner, inner, _dtype_code(X), self._stream(stream)))
+
+    def raster_gaussians(self, means, covs, colors, opacities, w2c, K, H, W, near=0.2, precise=True, stream=None):
+        """3D Gaussian-splatting render of one view. means [n,3], covs [n,3,3], colors [n,3], opacities [n]: fp32 CUDA tensors;
+        w2c 4x4 and K 3x3 host arrays (float64). Returns (rgb [H,W,3], alpha [H,W]) fp32 CUDA tensors."""
+        import numpy as np
+        import torch
+        n = int(means.shape[0])
+        for t in (means, covs, colors, opacities):
+            assert t.dtype == torch.float32 and t.is_contiguous() and t.is_cuda
+        w = np.ascontiguousarray(w2c, dtype=np.float64).reshape(16)
+        k = np.ascontiguousarray(K, dtype=np.float64).reshape(9)
+        rgb = torch.empty(H, W, 3, dtype=torch.float32, device=means.device)
+        alpha = torch.empty(H, W, dtype=torch.float32, device=means.device)
+        nbytes = int(self.lib.vkc_raster_workspace_bytes(n, int(bool(precise))))
+        ws = torch.empty(nbytes + 256, dtype=torch.uint8, device=means.device)
+        off = (-ws.data_ptr()) % 256
+        self._check(self.lib.vkc_raster_gaussians(self.h, means.data_ptr(), covs.data_ptr(), colors.data_ptr(), opacities.data_ptr(), n,
+                                                  w.ctypes.data_as(C.POINTER(C.c_double)), k.ctypes.data_as(C.POINTER(C.c_double)), int(H), int(W),
+                                                  float(near), int(bool(precise)), rgb.data_ptr(), alpha.data_ptr(), ws.data_ptr() + off, nbytes,
+                                                  self._stream(stream)))
+        self._keepalive = ws  # the workspace must outlive the asynchronous launches
+        return rgb, alpha
 
     def strided_copy(self, X, Y, shape, in_strides, in_offset=0, stream=None):
         self._check(self.lib.vkc_strided_copy(self.h, X.data_ptr(), Y.data_ptr(), _i64arr(shape), _i64arr(in_strides), len(shape), in_offset,

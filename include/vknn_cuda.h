@@ -193,8 +193,8 @@ VKC_API int vkc_strided_copy2(vkc_ctx *ctx, const void *X, void *Y, const int64_
  *   w2c: host 4x4 row-major world-to-camera matrix; K: host 3x3 pixel intrinsics; znear: near plane (reference 0.2);
  *   rgb [H,W,3] and alpha [H,W] (may be NULL): fp32 device outputs; precise != 0 computes in double like the float64
  *   specification (bit-comparable decisions), 0 in float. workspace: device memory of vkc_raster_workspace_bytes(n,
- *   precise) bytes, 256-byte aligned. ---- */
-VKC_API size_t vkc_raster_workspace_bytes(int64_t n, int precise);
+ *   H, W, precise) bytes, 256-byte aligned. ---- */
+VKC_API size_t vkc_raster_workspace_bytes(int64_t n, int H, int W, int precise);
 VKC_API int    vkc_raster_gaussians(vkc_ctx *ctx, const float *means, const float *covs, const float *colors, const float *opacities, int64_t n,
                                     const double *w2c, const double *K, int H, int W, double znear, int precise, float *rgb, float *alpha,
                                     void *workspace, size_t workspace_bytes, vkc_stream stream);

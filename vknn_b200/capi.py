@@ -86,7 +86,7 @@ def load_library():
     L.vkc_graph_end.argtypes = [vp, C.POINTER(vp)]
     L.vkc_graph_launch.argtypes = [vp, vp]
     L.vkc_graph_destroy.argtypes = [vp, vp]
-    L.vkc_raster_workspace_bytes.argtypes = [i64, i32]
+    L.vkc_raster_workspace_bytes.argtypes = [i64, i32, i32, i32]
     L.vkc_raster_workspace_bytes.restype = sz
     L.vkc_raster_gaussians.argtypes = [vp, vp, vp, vp, vp, i64, C.POINTER(C.c_double), C.POINTER(C.c_double), i32, i32, C.c_double, i32, vp, vp, vp, sz, vp]
     L.vkc_timer_start.argtypes = [vp, vp]
@@ -279,7 +279,7 @@ class Context:
         k = np.ascontiguousarray(K, dtype=np.float64).reshape(9)
         rgb = torch.empty(H, W, 3, dtype=torch.float32, device=means.device)
         alpha = torch.empty(H, W, dtype=torch.float32, device=means.device)
-        nbytes = int(self.lib.vkc_raster_workspace_bytes(n, int(bool(precise))))
+        nbytes = int(self.lib.vkc_raster_workspace_bytes(n, int(H), int(W), int(bool(precise))))
         ws = torch.empty(nbytes + 256, dtype=torch.uint8, device=means.device)
         off = (-ws.data_ptr()) % 256
         self._check(self.lib.vkc_raster_gaussians(self.h, means.data_ptr(), covs.data_ptr(), colors.data_ptr(), opacities.data_ptr(), n,

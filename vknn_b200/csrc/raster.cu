@@ -16,7 +16,9 @@
 //                             compacted in order into shared memory (ballot prefix), then every pixel thread composites
 //                             the compacted records: alpha = min(0.99, opacity * exp(min(power, 0))), gated at 1/255,
 //                             C += alpha * T * colour, T *= 1 - alpha. No binning pass and no duplicated keys: the
-//                             records (a few MB) stay in L2 and each tile streams them once.
+//                             records (a few MB) stay in L2 and each tile streams them once. When the image has few tiles
+//                             the depth order is cut into segments, one CTA per (tile, segment), and a combine kernel
+//                             joins the segments' (C, T) pairs in order, so that the whole GPU is busy.
 // Arithmetic is templated: double (default: decisions such as the radius ceiling and the 1/255 gate fall exactly as in
 // the float64 specification) or float.
 #include "common.cuh"
@@ -165,7 +167,7 @@ namespace {
 
     template <typename F>
     __global__ void __launch_bounds__(kTile *kTile) raster_composite_kernel(const Rec<F> *__restrict__ sorted, const int *__restrict__ nvalid, int H, int W,
-                                                                            float *__restrict__ rgb, float *__restrict__ alpha) {
+                                                                            float *__restrict__ rgb, float *__restrict__ alpha, F *__restrict__ partial) {
         __shared__ Rec<F> hit[kTile * kTile];
         __shared__ int    warp_count[8];
         const int tid = threadIdx.y * kTile + threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -173,12 +175,17 @@ namespace {
         const int px = tx0 + threadIdx.x, py = ty0 + threadIdx.y;
         const int n  = *nvalid;
         F         C0 = 0, C1 = 0, C2 = 0, T = 1;
-        for (int base = 0; base < n; base += kTile * kTile) {
+        // gridDim.z > 1: this CTA composites only its depth segment of the sorted records (whole chunks of 256) and leaves
+        // (C, T) of the segment for the combine kernel: front-to-back compositing is associative in that pair
+        const int chunks = (n + kTile * kTile - 1) / (kTile * kTile), per = (chunks + (int) gridDim.z - 1) / (int) gridDim.z;
+        const int first = (int) blockIdx.z * per * kTile * kTile;
+        const int last  = min(n, first + per * kTile * kTile);
+        for (int base = first; base < last; base += kTile * kTile) {
             // each thread tests one record of the chunk against the tile; hits keep their depth order
             Rec<F>    mine;
             bool      take = false;
             const int k    = base + tid;
-            if (k < n) {
+            if (k < last) {
                 mine = sorted[k];
                 take = mine.x0 < tx0 + kTile && mine.x1 > tx0 && mine.y0 < ty0 + kTile && mine.y1 > ty0;
             }
@@ -208,6 +215,13 @@ namespace {
             }
             __syncthreads();
         }
+        if (gridDim.z > 1) {
+            if (px < W && py < H) {
+                F *o = partial + (((int64_t) blockIdx.z * H + py) * W + px) * 4;
+                o[0] = C0, o[1] = C1, o[2] = C2, o[3] = T;
+            }
+            return;
+        }
         if (px < W && py < H) {
             const int64_t o = ((int64_t) py * W + px) * 3;
             rgb[o]     = (float) fmin((F) 1, fmax((F) 0, C0));
@@ -215,6 +229,31 @@ namespace {
             rgb[o + 2] = (float) fmin((F) 1, fmax((F) 0, C2));
             if (alpha) alpha[(int64_t) py * W + px] = (float) ((F) 1 - T);
         }
+    }
+
+    // Joins the depth segments of a pixel in order: C = C_0 + T_0 C_1 + T_0 T_1 C_2 + ..., T = T_0 T_1 ...
+    template <typename F>
+    __global__ void __launch_bounds__(256) raster_combine_kernel(const F *__restrict__ partial, int segs, int H, int W, float *__restrict__ rgb,
+                                                                 float *__restrict__ alpha) {
+        const int64_t i = (int64_t) blockIdx.x * blockDim.x + threadIdx.x;
+        if (i >= (int64_t) H * W) return;
+        F C0 = 0, C1 = 0, C2 = 0, T = 1;
+        for (int s = 0; s < segs; ++s) {
+            const F *p = partial + ((int64_t) s * H * W + i) * 4;
+            C0 += T * p[0], C1 += T * p[1], C2 += T * p[2];
+            T *= p[3];
+        }
+        rgb[i * 3]     = (float) fmin((F) 1, fmax((F) 0, C0));
+        rgb[i * 3 + 1] = (float) fmin((F) 1, fmax((F) 0, C1));
+        rgb[i * 3 + 2] = (float) fmin((F) 1, fmax((F) 0, C2));
+        if (alpha) alpha[i] = (float) ((F) 1 - T);
+    }
+
+    // Depth segments per tile: enough CTAs to fill the SMs several times over when the image has few tiles.
+    int raster_segments(int H, int W, int sms) {
+        const int64_t tiles = (int64_t) ((W + kTile - 1) / kTile) * ((H + kTile - 1) / kTile);
+        int64_t       s     = (8 * (int64_t) sms + tiles - 1) / tiles;
+        return (int) (s < 1 ? 1 : (s > 32 ? 32 : s));
     }
 
     int64_t pad_pow2(int64_t n) {
@@ -237,6 +276,9 @@ namespace {
         auto *rec = (Rec<F> *) w;
         w += npad * sizeof(Rec<F>);
         auto *sorted = (Rec<F> *) w;
+        w += npad * sizeof(Rec<F>);
+        auto     *partial = (F *) w;
+        const int segs    = raster_segments(cam.H, cam.W, ctx->sm_count);
         raster_preprocess_kernel<F><<<(unsigned) ((npad + 255) / 256), 256, 0, st>>>(means, covs, colors, opac, n, npad, cam, rec, keys, idx);
         if (int rc = vkc_post_launch(ctx, "raster_preprocess")) return rc;
         const unsigned blocks = (unsigned) (npad / kSortBlock);
@@ -252,18 +294,22 @@ namespace {
         }
         raster_gather_kernel<F><<<(unsigned) ((npad + 255) / 256), 256, 0, st>>>(rec, keys, idx, npad, sorted, nvalid);
         if (int rc = vkc_post_launch(ctx, "raster_gather")) return rc;
-        dim3 grid((unsigned) ((cam.W + kTile - 1) / kTile), (unsigned) ((cam.H + kTile - 1) / kTile));
-        raster_composite_kernel<F><<<grid, dim3(kTile, kTile), 0, st>>>(sorted, nvalid, cam.H, cam.W, rgb, alpha);
-        return vkc_post_launch(ctx, "raster_composite");
+        dim3 grid((unsigned) ((cam.W + kTile - 1) / kTile), (unsigned) ((cam.H + kTile - 1) / kTile), (unsigned) segs);
+        raster_composite_kernel<F><<<grid, dim3(kTile, kTile), 0, st>>>(sorted, nvalid, cam.H, cam.W, rgb, alpha, partial);
+        if (int rc = vkc_post_launch(ctx, "raster_composite")) return rc;
+        if (segs == 1) return VKC_OK;
+        raster_combine_kernel<F><<<(unsigned) (((int64_t) cam.H * cam.W + 255) / 256), 256, 0, st>>>(partial, segs, cam.H, cam.W, rgb, alpha);
+        return vkc_post_launch(ctx, "raster_combine");
     }
 
 } // namespace
 
-extern "C" size_t vkc_raster_workspace_bytes(int64_t n, int precise) {
-    if (n < 0) return 0;
+extern "C" size_t vkc_raster_workspace_bytes(int64_t n, int H, int W, int precise) {
+    if (n < 0 || H < 1 || W < 1) return 0;
     const int64_t npad = pad_pow2(n);
     const size_t  rec  = precise ? sizeof(Rec<double>) : sizeof(Rec<float>);
-    return (size_t) npad * (8 + 4 + 2 * rec) + 256;
+    // keys, indices, counter, records, sorted records, and up to 32 depth segments of (C, T) per pixel
+    return (size_t) npad * (8 + 4 + 2 * rec) + 256 + (size_t) 32 * H * W * 4 * (precise ? 8 : 4);
 }
 
 extern "C" int vkc_raster_gaussians(vkc_ctx *ctx, const float *means, const float *covs, const float *colors, const float *opacities, int64_t n,
@@ -274,7 +320,7 @@ extern "C" int vkc_raster_gaussians(vkc_ctx *ctx, const float *means, const floa
     VKC_REQUIRE(ctx, H >= 1 && W >= 1 && H <= 16384 && W <= 16384, "raster: bad image size %d x %d", H, W);
     VKC_REQUIRE(ctx, w2c && K && rgb, "raster: null camera or output");
     VKC_REQUIRE(ctx, n == 0 || (means && covs && colors && opacities), "raster: null gaussian attribute");
-    VKC_REQUIRE(ctx, workspace && workspace_bytes >= vkc_raster_workspace_bytes(n, precise), "raster: workspace smaller than vkc_raster_workspace_bytes");
+    VKC_REQUIRE(ctx, workspace && workspace_bytes >= vkc_raster_workspace_bytes(n, H, W, precise), "raster: workspace smaller than vkc_raster_workspace_bytes");
     VKC_REQUIRE(ctx, ((uintptr_t) workspace & 255) == 0, "raster: workspace must be 256-byte aligned");
     Cam cam;
     for (int a = 0; a < 3; ++a) {

@@ -180,3 +180,19 @@ def test_selection_and_reduce_ops_run_on_the_cuda_backend(precision):
         assert np.abs(a - b).max() <= tol, (what, float(np.abs(a - b).max()))
     # counts and masks are exact integers in either precision
     assert np.array_equal(got[1], ref[1]) and np.array_equal(got[2], ref[2])
+
+
+def test_tuning_table_from_another_device_is_ignored(tmp_path):
+    """A cache file whose header names another GPU / configuration set must not be trusted: the session measures again and
+    rewrites it."""
+    rng = np.random.default_rng(14)
+    w = encoder_weights(rng, 256, 512, bias_scale=0.01)
+    x = rng.standard_normal((2, 130, 256)).astype(np.float32)
+    cache = str(tmp_path / "m.cache")
+    table = tmp_path / "m.cache.cuda"
+    table.write_text("VKNNCUDA-TUNE-1\nsome-other-gpu/configs=3\ngemm:1:260x768x256x1:0:1:111 2\n")
+    (ref,), _ = vko.encoder_layer_graph(x, w, 4).run(backend="cpu")
+    (got,), _ = vko.encoder_layer_graph(x, w, 4).run(backend="cuda", precision="low", cache_file=cache, tuning="fast")
+    assert_low(got, ref, "encoder layer with a foreign tuning table")
+    lines = table.read_text().splitlines()
+    assert lines[1] != "some-other-gpu/configs=3" and len(lines) >= 2 + 4

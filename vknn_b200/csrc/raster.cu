@@ -168,8 +168,12 @@ namespace {
     template <typename F>
     __global__ void __launch_bounds__(kTile *kTile) raster_composite_kernel(const Rec<F> *__restrict__ sorted, const int *__restrict__ nvalid, int H, int W,
                                                                             float *__restrict__ rgb, float *__restrict__ alpha, F *__restrict__ partial) {
-        __shared__ Rec<F> hit[kTile * kTile];
-        __shared__ int    warp_count[8];
+        // hits of the current chunk, split so that the compositing loop reads them with 16-byte shared-memory loads (the
+        // loop is bound by those broadcast loads, not by arithmetic): the pixel box, then the nine values padded to VN
+        constexpr int VN = sizeof(F) == 4 ? 12 : 10;
+        __shared__ __align__(16) int hbox[kTile * kTile][4];
+        __shared__ __align__(16) F   hval[kTile * kTile][VN];
+        __shared__ int               warp_count[8];
         const int tid = threadIdx.y * kTile + threadIdx.x, lane = tid & 31, warp = tid >> 5;
         const int tx0 = blockIdx.x * kTile, ty0 = blockIdx.y * kTile;
         const int px = tx0 + threadIdx.x, py = ty0 + threadIdx.y;
@@ -198,17 +202,31 @@ namespace {
                 if (w < warp) before += warp_count[w];
                 total += warp_count[w];
             }
-            if (take) hit[before + __popc(bal & ((1u << lane) - 1u))] = mine;
+            if (take) {
+                const int pos = before + __popc(bal & ((1u << lane) - 1u));
+                *reinterpret_cast<int4 *>(hbox[pos]) = make_int4(mine.x0, mine.x1, mine.y0, mine.y1);
+                F *hv = hval[pos];
+                hv[0] = mine.u, hv[1] = mine.v, hv[2] = mine.a, hv[3] = mine.b, hv[4] = mine.c, hv[5] = mine.opac, hv[6] = mine.r, hv[7] = mine.g,
+                hv[8] = mine.bl;
+            }
             __syncthreads();
             for (int e = 0; e < total; ++e) {
-                const Rec<F> &gq = hit[e];
-                if (px >= gq.x0 && px < gq.x1 && py >= gq.y0 && py < gq.y1) {
-                    const F dx = (F) px - gq.u, dy = (F) py - gq.v;
-                    const F power = (F) -0.5 * (gq.a * dx * dx + gq.c * dy * dy) - gq.b * dx * dy;
-                    const F al    = fmin((F) 0.99, gq.opac * exp(fmin(power, (F) 0)));
+                const int4 bx = *reinterpret_cast<const int4 *>(hbox[e]);
+                if (px >= bx.x && px < bx.y && py >= bx.z && py < bx.w) {
+                    F gv[VN];
+                    if (sizeof(F) == 4) {
+#pragma unroll
+                        for (int v4 = 0; v4 < 3; ++v4) *reinterpret_cast<float4 *>(&gv[4 * v4]) = *reinterpret_cast<const float4 *>(&hval[e][4 * v4]);
+                    } else {
+#pragma unroll
+                        for (int v2 = 0; v2 < 5; ++v2) *reinterpret_cast<double2 *>(&gv[2 * v2]) = *reinterpret_cast<const double2 *>(&hval[e][2 * v2]);
+                    }
+                    const F dx = (F) px - gv[0], dy = (F) py - gv[1];
+                    const F power = (F) -0.5 * (gv[2] * dx * dx + gv[4] * dy * dy) - gv[3] * dx * dy;
+                    const F al    = fmin((F) 0.99, gv[5] * exp(fmin(power, (F) 0)));
                     if (al > (F) (1.0 / 255.0)) {
                         const F w = al * T;
-                        C0 += w * gq.r, C1 += w * gq.g, C2 += w * gq.bl;
+                        C0 += w * gv[6], C1 += w * gv[7], C2 += w * gv[8];
                         T *= (F) 1 - al;
                     }
                 }

@@ -1,6 +1,6 @@
 """Generates tests/golden/raster_golden.npz: outputs of the reference's own renderer on seeded scenes.
 
-Run where the reference tree is present:  python tests/golden/make_raster_golden.py /root/reference
+Run where the reference tree is present:  python tests/golden/make_raster_golden.py <path of the reference tree>
 It imports scripts/yonosplat/ref_rasterizer.py from that tree (nothing is copied), renders the scenes of
 oracle.rasterizer.scene and stores the images; the scene inputs are regenerated from their seeds by the tests."""
 import importlib.util

@@ -185,6 +185,23 @@ def test_attention_shapes(ctx, impl, causal, B, Hq, Hkv, Sq, Skv, D):
     assert_low(run_attn(ctx, q, k, v, scale, "bf16", causal=causal, impl=impl), ref, "attn")
 
 
+@pytest.mark.parametrize("dt", ["f16", "bf16"])
+@pytest.mark.parametrize("B,Hq,Hkv,Sq,Skv", [(1, 2, 2, 1100, 1100), (2, 4, 2, 777, 1303), (1, 16, 16, 300, 2738)])
+def test_attention_head64_key_range_split(ctx, dt, B, Hq, Hkv, Sq, Skv):
+    """Head size 64, no mask, at least eight key tiles and a shallow grid: the tensor-core path cuts the key range in two
+    and merges the halves (ragged last key tile, GQA, ragged query tiles, Sq != Skv)."""
+    tdt = torch.float16 if dt == "f16" else torch.bfloat16
+    rng = np.random.default_rng(B + Sq + Skv)
+    q = round_to(rng.standard_normal((B, Hq, Sq, 64)), tdt)
+    k = round_to(rng.standard_normal((B, Hkv, Skv, 64)), tdt)
+    v = round_to(rng.standard_normal((B, Hkv, Skv, 64)), tdt)
+    ref = vko.attention(q, k, v, 0.125)
+    n0 = ctx.launch_count()
+    got = run_attn(ctx, q, k, v, 0.125, dt, impl=vknn_b200.IMPL_TCGEN05)
+    assert ctx.launch_count() - n0 == 2  # the attention kernel and the merge of the two key ranges
+    assert_low(got, ref, "attn split")
+
+
 @pytest.mark.parametrize("impl", [vknn_b200.IMPL_SIMT, vknn_b200.IMPL_TCGEN05], ids=["simt", "tc"])
 def test_attention_kv_len(ctx, impl):
     rng = np.random.default_rng(77)

@@ -2,7 +2,9 @@
 // the SM). One CTA owns TWO 128-row query tiles (A and B) of one (batch, head) and walks the key/value
 // sequence in tiles of 128 keys; while the softmax warps of one query tile work, the tensor core runs the
 // MMAs of the other. For head size 64 and grids of only a few rounds a one-tile form runs instead, two CTAs per SM:
-// the same overlap happens between the co-resident CTAs and single tiles balance better over the 148 SMs.
+// the same overlap happens between the co-resident CTAs and single tiles balance better over the 148 SMs; when even those
+// do not fill a few rounds of the SMs and the key sequence is long, each CTA takes half of the key tiles and a merge kernel
+// joins the two normalised partial outputs with their (maximum, sum) weights.
 // Warp numbers below are those of the two-tile form.
 //
 //   warp 8     TMA producer: both Q tiles once, then K and V tiles through two independent 2-stage
@@ -53,6 +55,11 @@ namespace {
         const int32_t *kv_len;
         int           *dev_err;
         long long     *timeline; // optional clock64 stamps of CTA (0,0,0): key tiles kTlTile and kTlTile + 1
+        // key-range splitting (shallow grids): CTA blockIdx.x % kv_splits handles its share of the key tiles and leaves a
+        // partial per row — the normalised output in the storage type and (running maximum, row sum) — for the merge kernel
+        int    kv_splits;
+        void  *part_o;  // [kv_splits][B][Hq][Sq][D] storage type
+        float *part_ml; // [kv_splits][B][Hq][Sq][2]
     };
     constexpr int kTlTile = 20;
 
@@ -178,7 +185,8 @@ namespace {
         const int b = blockIdx.z, h = blockIdx.y;
         const int hk = h / (int) (p.Hq / p.Hkv);
         // heavy (late) query tiles first when causal
-        const int     mt = p.causal ? (int) gridDim.x - 1 - (int) blockIdx.x : (int) blockIdx.x;
+        const int     split = (int) blockIdx.x % p.kv_splits, bx = (int) blockIdx.x / p.kv_splits, nbx = (int) gridDim.x / p.kv_splits;
+        const int     mt = p.causal ? nbx - 1 - bx : bx;
         const int64_t m0 = (int64_t) mt * (kQTiles * BM);
 
         int64_t len = p.kv_len ? (int64_t) p.kv_len[b] : p.Skv;
@@ -203,6 +211,18 @@ namespace {
         int n_max = 0;
 #pragma unroll
         for (int t = 0; t < kQTiles; ++t) n_max = n_t[t] > n_max ? n_t[t] : n_max;
+        // this CTA's share of the key tiles: [jb, jb + per); from here on tile counts and loop indices are local to it
+        int jb = 0;
+        if (p.kv_splits > 1) {
+            const int per = (n_max + p.kv_splits - 1) / p.kv_splits;
+            jb            = split * per;
+            n_max         = 0;
+#pragma unroll
+            for (int t = 0; t < kQTiles; ++t) {
+                n_t[t] = n_t[t] - jb < 0 ? 0 : (n_t[t] - jb > per ? per : n_t[t] - jb);
+                n_max  = n_t[t] > n_max ? n_t[t] : n_max;
+            }
+        }
 
         if (threadIdx.x == 0) {
             for (int i = 0; i < L::nBar; ++i) ptx::mbar_init(bar(i), (i >= bPF && i < bOF) ? 4 : 1); // p_full: one arrival per softmax warp
@@ -239,11 +259,11 @@ namespace {
                     if (!ptx::mbar_wait(bar(bKE + ks), ((j / KS) & 1) ^ 1, ctl + 1, p.dev_err)) break;
                     ptx::mbar_expect_tx(bar(bKF + ks), L::KV_BYTES);
 #pragma unroll
-                    for (int c = 0; c < DCH; ++c) ptx::tma_load_4d(sK + ks * L::KV_BYTES + c * (BN * 128), &tmK, c * 64, j * BN, hk, b, bar(bKF + ks));
+                    for (int c = 0; c < DCH; ++c) ptx::tma_load_4d(sK + ks * L::KV_BYTES + c * (BN * 128), &tmK, c * 64, (jb + j) * BN, hk, b, bar(bKF + ks));
                     if (!ptx::mbar_wait(bar(bVE + vs), ((j / VS) & 1) ^ 1, ctl + 1, p.dev_err)) break;
                     ptx::mbar_expect_tx(bar(bVF + vs), L::KV_BYTES);
 #pragma unroll
-                    for (int c = 0; c < DCH; ++c) ptx::tma_load_4d(sV + vs * L::KV_BYTES + c * (BN * 128), &tmV, c * 64, j * BN, hk, b, bar(bVF + vs));
+                    for (int c = 0; c < DCH; ++c) ptx::tma_load_4d(sV + vs * L::KV_BYTES + c * (BN * 128), &tmV, c * 64, (jb + j) * BN, hk, b, bar(bVF + vs));
                 }
             }
           } else if (warp == kWarpMma) {
@@ -344,7 +364,7 @@ namespace {
             // straddle kv_len or the causal diagonal take it, every other tile runs free of any mask arithmetic).
             auto tile = [&](auto mask_tag, int j) -> bool {
                 constexpr bool kMask = decltype(mask_tag)::value;
-                const int64_t  kv0   = (int64_t) j * BN;
+                const int64_t  kv0   = (int64_t) (jb + j) * BN;
                 ok = ptx::mbar_wait(bar(bSF + t), j & 1, ctl + 1, p.dev_err);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) return false;
@@ -515,7 +535,7 @@ namespace {
                 return true;
             };
             for (int j = 0; j < n; ++j) {
-                const int64_t kv0       = (int64_t) j * BN;
+                const int64_t kv0       = (int64_t) (jb + j) * BN;
                 const bool    need_mask = (kv0 + BN > len) || (p.causal && kv0 + BN - 1 > m0 + (int64_t) t * BM + (p.Skv - p.Sq));
                 if (!(need_mask ? tile(std::true_type{}, j) : tile(std::false_type{}, j))) break;
             }
@@ -527,9 +547,22 @@ namespace {
             if (ok) {
                 ptx::tc_fence_after();
                 // a row with no visible key stores NaN like the reference's 0/0
-                const float inv = (n > 0 && m_used == -INFINITY) ? __int_as_float(0x7fc00000) : 1.0f / l;
-                T          *orow = (T *) p.O + (int64_t) b * p.os[0] + (int64_t) h * p.os[1] + row * p.os[2];
-                const bool  vec_ok = (p.os[0] % 8 == 0) && (p.os[1] % 8 == 0) && (p.os[2] % 8 == 0) && (((uintptr_t) p.O & 15) == 0);
+                float       inv    = (n > 0 && m_used == -INFINITY) ? __int_as_float(0x7fc00000) : 1.0f / l;
+                T          *orow   = (T *) p.O + (int64_t) b * p.os[0] + (int64_t) h * p.os[1] + row * p.os[2];
+                bool        vec_ok = (p.os[0] % 8 == 0) && (p.os[1] % 8 == 0) && (p.os[2] % 8 == 0) && (((uintptr_t) p.O & 15) == 0);
+                if (p.kv_splits > 1) {
+                    // partial of this key range: O / l in the storage type (bounded by max |v|, so 16 bits do not overflow),
+                    // weight data (m, l) in fp32; a range without a visible key for this row has weight 0
+                    const int64_t prow = (((int64_t) split * gridDim.z + b) * p.Hq + h) * p.Sq + row;
+                    const bool    none = n == 0 || m_used == -INFINITY;
+                    inv    = none ? 0.f : 1.0f / l;
+                    orow   = (T *) p.part_o + prow * D;
+                    vec_ok = true;
+                    if (row < p.Sq) {
+                        p.part_ml[prow * 2]     = none ? -INFINITY : m_used;
+                        p.part_ml[prow * 2 + 1] = none ? 0.f : l;
+                    }
+                }
 #pragma unroll 1
                 for (int c = 0; c < D / 32; ++c) {
                     uint32_t v[32];
@@ -567,22 +600,74 @@ namespace {
         if (warp == kWarpMma) ptx::tmem_dealloc(tmem, kTmemCols);
     }
 
+    // Merge of the key-range partials of one query row: weights l_s * 2^(m_s - m) over their sum (m_s are in the log2
+    // domain the kernel works in); a row without any visible key gets NaN like the reference's 0/0.
+    template <typename T, int D>
+    __global__ void __launch_bounds__(256) attn_prefill_merge_kernel(const T *__restrict__ part_o, const float *__restrict__ part_ml, T *__restrict__ O,
+                                                                     int64_t B, int64_t Hq, int64_t Sq, int splits, int64_t os0, int64_t os1, int64_t os2) {
+        constexpr int TPRW = D / 8; // threads per row, 8 elements each
+        const int64_t gid = (int64_t) blockIdx.x * blockDim.x + threadIdx.x;
+        const int64_t row = gid / TPRW, rows = B * Hq * Sq;
+        const int     c   = (int) (gid % TPRW) * 8;
+        vkc_grid_dep_wait(); // launched with programmatic serialization: the partials are complete only after this
+        vkc_grid_dep_launch();
+        if (row >= rows) return;
+        float m = -INFINITY;
+        for (int s = 0; s < splits; ++s) m = fmaxf(m, part_ml[((int64_t) s * rows + row) * 2]);
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, wsum = 0.f;
+        for (int s = 0; s < splits; ++s) {
+            const float ms = part_ml[((int64_t) s * rows + row) * 2], ls = part_ml[((int64_t) s * rows + row) * 2 + 1];
+            const float w  = ms == -INFINITY ? 0.f : ls * exp2f(ms - m);
+            wsum += w;
+            const uint4 pv = *reinterpret_cast<const uint4 *>(part_o + ((int64_t) s * rows + row) * D + c);
+            const T    *pt = reinterpret_cast<const T *>(&pv);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[i] += w * St<T>::ld(pt + i);
+        }
+        const float inv = 1.0f / wsum; // 0/0 -> NaN for a row with no visible key
+        const int64_t b = row / (Hq * Sq), h = (row / Sq) % Hq, r = row % Sq;
+        T *orow = O + b * os0 + h * os1 + r * os2 + c;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) St<T>::st(orow + i, acc[i] * inv);
+    }
+
     template <typename T, int D, int QT>
     int launch_attn_qt(vkc_ctx *ctx, const CUtensorMap &tq, const CUtensorMap &tk, const CUtensorMap &tv, const AttnParams &p, int64_t B, cudaStream_t st) {
         auto          kern = attn_prefill_kernel<T, D, 2, QT>;
         constexpr int smem = (int) Smem<D, 2, 2, QT>::total;
         static_assert(smem * (QT == 1 && D == 64 ? 2 : 1) <= 227 * 1024, "shared memory budget");
         if (int rc = vkc_configure_smem(ctx, kern, smem)) return rc;
-        dim3 grid((unsigned) ((p.Sq + QT * BM - 1) / (QT * BM)), (unsigned) p.Hq, (unsigned) B);
+        dim3 grid((unsigned) ((p.Sq + QT * BM - 1) / (QT * BM)) * (unsigned) p.kv_splits, (unsigned) p.Hq, (unsigned) B);
         vkc_launch(ctx, kern, grid, dim3(threads_for(QT)), smem, st, tq, tk, tv, p);
-        return vkc_post_launch(ctx, "attn_prefill_tcgen05");
+        if (int rc = vkc_post_launch(ctx, "attn_prefill_tcgen05")) return rc;
+        if (p.kv_splits == 1) return VKC_OK;
+        const int64_t threads = B * p.Hq * p.Sq * (D / 8);
+        vkc_launch(ctx, attn_prefill_merge_kernel<T, D>, dim3((unsigned) ((threads + 255) / 256)), dim3(256), 0, st, (const T *) p.part_o,
+                   (const float *) p.part_ml, (T *) p.O, B, p.Hq, p.Sq, p.kv_splits, p.os[0], p.os[1], p.os[2]);
+        return vkc_post_launch(ctx, "attn_prefill_merge");
     }
     template <typename T, int D>
-    int launch_attn(vkc_ctx *ctx, const CUtensorMap &tq, const CUtensorMap &tk, const CUtensorMap &tv, const AttnParams &p, int64_t B, cudaStream_t st) {
+    int launch_attn(vkc_ctx *ctx, const CUtensorMap &tq, const CUtensorMap &tk, const CUtensorMap &tv, AttnParams &p, int64_t B, cudaStream_t st) {
         if (D == 64) {
             // two one-tile CTAs per SM unless the grid is many rounds deep anyway (then sharing K/V between two tiles wins)
             const int64_t pairs = ((p.Sq + 2 * BM - 1) / (2 * BM)) * p.Hq * B;
-            if (pairs < 6 * (int64_t) ctx->sm_count) return launch_attn_qt<T, 64, 1>(ctx, tq, tk, tv, p, B, st);
+            if (pairs < 6 * (int64_t) ctx->sm_count) {
+                // One-tile CTAs, two per SM. When they do not even fill a few rounds of the 2 x SMs slots and the key sequence
+                // is long, the key range is also cut in two: the hardware block scheduler balances the finer units better
+                // (352 CTAs of 22 key tiles on 296 slots -> 704 CTAs of 11), at the price of a small merge pass.
+                const int64_t ctas = ((p.Sq + BM - 1) / BM) * p.Hq * B, slots = 2 * (int64_t) ctx->sm_count, ntiles = (p.Skv + BN - 1) / BN;
+                const int64_t rounds1 = (ctas + slots - 1) / slots, rounds2 = (2 * ctas + slots - 1) / slots;
+                if (!p.causal && !p.kv_len && ntiles >= 8 && ctas < 3 * slots && rounds2 < 2 * rounds1) {
+                    const size_t rows = (size_t) B * p.Hq * p.Sq;
+                    const size_t need = 2 * rows * (64 * 2 + 2 * 4) + 256;
+                    if (vkc_ensure_scratch(ctx, need) == VKC_OK) {
+                        p.kv_splits = 2;
+                        p.part_ml   = (float *) ctx->scratch;
+                        p.part_o    = (char *) ctx->scratch + ((2 * rows * 2 * 4 + 255) & ~(size_t) 255);
+                    }
+                }
+                return launch_attn_qt<T, 64, 1>(ctx, tq, tk, tv, p, B, st);
+            }
         }
         return launch_attn_qt<T, D, 2>(ctx, tq, tk, tv, p, B, st);
     }
@@ -627,6 +712,9 @@ int vkc_attn_prefill_tcgen05(vkc_ctx *ctx, const void *Q, const void *K, const v
     p.kv_len     = kv_len;
     p.dev_err    = ctx->dev_err;
     p.timeline   = ctx->timeline;
+    p.kv_splits  = 1;
+    p.part_o     = nullptr;
+    p.part_ml    = nullptr;
     if (dtype == VKC_F16) return D == 64 ? launch_attn<__half, 64>(ctx, tq, tk, tv, p, B, st) : launch_attn<__half, 128>(ctx, tq, tk, tv, p, B, st);
     return D == 64 ? launch_attn<__nv_bfloat16, 64>(ctx, tq, tk, tv, p, B, st) : launch_attn<__nv_bfloat16, 128>(ctx, tq, tk, tv, p, B, st);
 }

@@ -76,7 +76,7 @@ inline int vkc_post_launch(vkc_ctx *ctx, const char *what) {
     return VKC_OK;
 }
 
-// Launch with programmatic stream serialization: the kernel may start (set up shared memory, barriers, tensor
+// Launch with programmatic stream serialization — ONLY for kernels that execute vkc_grid_dep_wait(): the kernel may start (set up shared memory, barriers, tensor
 // memory) while the previous kernel of the stream is still draining; it must execute griddepcontrol.wait
 // (vkc_grid_dep_wait) before its first access to global memory, which returns once the previous kernel has completed
 // and its writes are visible. Inside a stream capture the dependency becomes a programmatic graph edge.

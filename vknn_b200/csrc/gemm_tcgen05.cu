@@ -423,6 +423,281 @@ namespace {
         return vkc_post_launch(ctx, "gemm_tcgen05");
     }
 
+    // ---------------------------------------------------------------------------------------------------------------
+    // Persistent form: one CTA per SM walks over output tiles (tile t, t + gridDim.x, ...). The accumulator is double
+    // buffered in tensor memory, so the epilogue of tile i runs while the tensor pipe already works on tile i + 1, and
+    // the operand ring keeps streaming across tile boundaries. The epilogue therefore cannot borrow the operand ring:
+    // every epilogue warp owns three 32 x 128 B staging blocks that rotate over its 64-column slabs (residual slab
+    // TMA-loaded into the block one slab ahead, result written over it, one TMA store per slab).
+    constexpr int kPBlocks = 3; // staging blocks per epilogue warp
+    template <int BN, int kStages> constexpr int smem_bytes_persistent() {
+        return kStages * (BM * BK * 2 + BN * BK * 2) + 4 * kPBlocks * 4096 + 1024 /*align*/ + 512 /*barriers*/ + 4 * BN * 4 /*bias, per warp*/;
+    }
+    __host__ __device__ constexpr int acc_stride(int bn) { return bn <= 128 ? 128 : 256; } // TMEM columns between the two accumulators
+
+    template <int BN, int kStages, typename T, bool B_KN>
+    __global__ void __launch_bounds__(kThreads, 1)
+        gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                                       const __grid_constant__ CUtensorMap tmD, const __grid_constant__ CUtensorMap tmR, GemmParams p, int m_tiles,
+                                       int n_tiles, int total_tiles) {
+        constexpr uint32_t A_BYTES = BM * BK * 2;
+        constexpr uint32_t B_BYTES = BN * BK * 2;
+        constexpr bool     kBf16   = std::is_same<T, __nv_bfloat16>::value;
+        constexpr uint32_t kIdesc  = ptx::idesc_f16(BM, BN, kBf16, false, B_KN);
+        constexpr int      kSlabs  = (BN + 63) / 64;
+        constexpr uint32_t kRing   = kStages * (A_BYTES + B_BYTES);
+        constexpr uint32_t kStage  = 4 * kPBlocks * 4096;
+
+        extern __shared__ uint8_t smem_raw[];
+        const uint32_t raw   = ptx::smem_u32(smem_raw);
+        const uint32_t base  = (raw + 1023u) & ~1023u;
+        uint8_t       *gbase = smem_raw + (base - raw);
+        const uint32_t sA    = base;
+        const uint32_t sB    = base + kStages * A_BYTES;
+        const uint32_t sOut  = base + kRing;          // staging blocks: warp q, block b at (q * kPBlocks + b) * 4096
+        const uint32_t sBar  = base + kRing + kStage; // full[kStages], empty[kStages], accFull[2], accEmpty[2], resid[4][kPBlocks]
+        const uint32_t bAccF = sBar + 8 * (2 * kStages), bAccE = bAccF + 16, bRes = bAccE + 16;
+        volatile int  *ctl   = (volatile int *) (gbase + kRing + kStage + 8 * (2 * kStages + 4 + 4 * kPBlocks)); // [0] tmem base, [1] abort
+        const uint32_t sSlot = sBar + 8 * (2 * kStages + 4 + 4 * kPBlocks);
+        float         *sbias = (float *) (gbase + kRing + kStage + 512); // [4 warps][BN]
+        static_assert(8 * (2 * kStages + 4 + 4 * kPBlocks) + 16 <= 512, "barrier area");
+
+        const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+        const int num_kb = (int) ((p.K + BK - 1) / BK);
+
+        if (threadIdx.x == 0) {
+            for (int s = 0; s < kStages; ++s) {
+                ptx::mbar_init(sBar + 8 * s, 1);
+                ptx::mbar_init(sBar + 8 * (kStages + s), 1);
+            }
+            for (int b = 0; b < 2; ++b) {
+                ptx::mbar_init(bAccF + 8 * b, 1);
+                ptx::mbar_init(bAccE + 8 * b, 4); // one arrival per epilogue warp
+            }
+            for (int w = 0; w < 4 * kPBlocks; ++w) ptx::mbar_init(bRes + 8 * w, 1);
+            ctl[1] = 0;
+            ptx::fence_mbar_init();
+            ptx::prefetch_tmap(&tmA);
+            ptx::prefetch_tmap(&tmB);
+            ptx::prefetch_tmap(&tmD);
+        }
+        if (warp == 1) {
+            ptx::tmem_alloc(sSlot, 2 * acc_stride(BN));
+            ptx::tmem_relinquish();
+        }
+        vkc_grid_dep_wait();
+        vkc_grid_dep_launch();
+        ptx::tc_fence_before();
+        __syncthreads();
+        ptx::tc_fence_after();
+        const uint32_t tmem = (uint32_t) ctl[0];
+
+        // tile t -> (row tile fastest, then column tile, then batch): concurrently running CTAs share few B tiles
+        auto tile_of = [&](int t, int &m0, int &n0, int &bz) {
+            m0 = (t % m_tiles) * BM;
+            n0 = ((t / m_tiles) % n_tiles) * BN;
+            bz = t / (m_tiles * n_tiles);
+        };
+
+        if (warp == 0) {
+            if (ptx::elect_one()) {
+                int  it = 0;
+                bool ok = true;
+                for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+                    int m0, n0, bz;
+                    tile_of(t, m0, n0, bz);
+                    const int za = p.a_bcast ? 0 : bz, zb = p.b_bcast ? 0 : bz;
+                    for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                        const int      s  = it % kStages;
+                        const uint32_t ph = (it / kStages) & 1;
+                        const int      kx = kb * BK;
+                        if (!ptx::mbar_wait(sBar + 8 * (kStages + s), ph ^ 1, ctl + 1, p.dev_err)) {
+                            ok = false;
+                            break;
+                        }
+                        const uint32_t full = sBar + 8 * s;
+                        ptx::mbar_expect_tx(full, A_BYTES + B_BYTES);
+                        ptx::tma_load_3d(sA + s * A_BYTES, &tmA, kx, m0, za, full);
+                        if (!B_KN) {
+                            ptx::tma_load_3d(sB + s * B_BYTES, &tmB, kx, n0, zb, full);
+                        } else {
+#pragma unroll
+                            for (int c = 0; c < BN / 64; ++c) ptx::tma_load_3d(sB + s * B_BYTES + c * (BK * 128), &tmB, n0 + c * 64, kx, zb, full);
+                        }
+                    }
+                }
+            }
+        } else if (warp == 1) {
+            if (ptx::elect_one()) {
+                int  it = 0, i = 0;
+                bool ok = true;
+                for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++i) {
+                    const int      buf = i & 1;
+                    const uint32_t acc = tmem + (uint32_t) (buf * acc_stride(BN));
+                    // the epilogue warps have drained this accumulator (two tiles ago)
+                    ok = ptx::mbar_wait(bAccE + 8 * buf, ((i >> 1) & 1) ^ 1, ctl + 1, p.dev_err);
+                    if (!ok) break;
+                    ptx::tc_fence_after();
+                    for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                        const int      s  = it % kStages;
+                        const uint32_t ph = (it / kStages) & 1;
+                        ok                = ptx::mbar_wait(sBar + 8 * s, ph, ctl + 1, p.dev_err);
+                        if (!ok) break;
+                        ptx::tc_fence_after();
+#pragma unroll
+                        for (int k = 0; k < BK / 16; ++k) {
+                            const uint64_t ad = ptx::smem_desc_sw128(sA + s * A_BYTES + k * 32, 16, 1024);
+                            const uint64_t bd = B_KN ? ptx::smem_desc_sw128(sB + s * B_BYTES + k * (16 * 128), BK * 128, 1024)
+                                                     : ptx::smem_desc_sw128(sB + s * B_BYTES + k * 32, 16, 1024);
+                            ptx::mma_f16_ss(acc, ad, bd, kIdesc, (kb | k) != 0 ? 1u : 0u);
+                        }
+                        ptx::tc_commit(sBar + 8 * (kStages + s));
+                    }
+                    if (ok) ptx::tc_commit(bAccF + 8 * buf);
+                }
+            }
+        } else {
+            const int      q      = warp & 3; // the TMEM lane quarter this warp may address
+            float         *wbias  = sbias + q * BN;
+            const uint32_t wOut   = sOut + (uint32_t) (q * kPBlocks) * 4096u;
+            uint8_t       *gOut   = gbase + kRing + (q * kPBlocks) * 4096;
+            const uint32_t wRes   = bRes + 8 * (q * kPBlocks);
+            const bool     resid  = (p.epilogue & VKC_EPI_RESIDUAL) != 0;
+            auto           nslabs = [&](int n0) {
+                int n = 0;
+                for (int sl = 0; sl < kSlabs; ++sl)
+                    if ((int64_t) n0 + sl * 64 < p.N) n = sl + 1;
+                return n;
+            };
+            int  g  = 0; // running slab number of this warp: staging block g % kPBlocks, use (g / kPBlocks) of that block
+            bool ok = true;
+            if (resid && blockIdx.x < total_tiles && lane == 0) {
+                int m0, n0, bz;
+                tile_of(blockIdx.x, m0, n0, bz);
+                ptx::mbar_expect_tx(wRes, 4096u);
+                ptx::tma_load_3d(wOut, &tmR, n0, m0 + q * 32, bz, wRes);
+            }
+            int i = 0;
+            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++i) {
+                int m0, n0, bz;
+                tile_of(t, m0, n0, bz);
+                const int  buf = i & 1, nslab = nslabs(n0), row0 = m0 + q * 32;
+                const bool rows_in = row0 < p.M; // warp-uniform
+                __syncwarp();
+                if (p.epilogue & VKC_EPI_BIAS)
+                    for (int j = lane; j < BN; j += 32) wbias[j] = (int64_t) n0 + j < p.N ? __ldg(p.bias + n0 + j) : 0.f;
+                __syncwarp();
+                ok = ptx::mbar_wait(bAccF + 8 * buf, (i >> 1) & 1, ctl + 1, p.dev_err);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                ptx::tc_fence_after();
+                const uint32_t acc = tmem + ((uint32_t) (q * 32) << 16) + (uint32_t) (buf * acc_stride(BN));
+#pragma unroll 1
+                for (int sl = 0; sl < nslab; ++sl, ++g) {
+                    const int blk = g % kPBlocks;
+                    // The block after this one is free once the store issued two slabs ago has read it; fetch the next
+                    // slab's residual (this tile's or the next tile's first) into it.
+                    if (lane == 0) {
+                        ptx::bulk_wait_group_read_1();
+                        if (resid) {
+                            int  tm0 = m0, tn0 = n0 + (sl + 1) * 64, tbz = bz;
+                            bool more = sl + 1 < nslab;
+                            if (!more && t + (int) gridDim.x < total_tiles) {
+                                tile_of(t + gridDim.x, tm0, tn0, tbz);
+                                more = true;
+                            }
+                            if (more) {
+                                const int nb = (g + 1) % kPBlocks;
+                                ptx::mbar_expect_tx(wRes + 8 * nb, 4096u);
+                                ptx::tma_load_3d(wOut + nb * 4096, &tmR, tn0, tm0 + q * 32, tbz, wRes + 8 * nb);
+                            }
+                        }
+                    }
+                    __syncwarp();
+                    uint32_t r2[2][32];
+                    ptx::tmem_ld_x32(acc + (uint32_t) (sl * 64), r2[0]);
+                    ptx::tmem_ld_x32(acc + (uint32_t) (sl * 64 + 32), r2[1]);
+                    ptx::tc_wait_ld();
+                    if (sl == nslab - 1) { // accumulator drained: the tensor pipe may overwrite it
+                        ptx::tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) ptx::mbar_arrive(bAccE + 8 * buf);
+                    }
+                    if (resid) {
+                        ok = ptx::mbar_wait(wRes + 8 * blk, (g / kPBlocks) & 1, ctl + 1, p.dev_err);
+                        ok = __all_sync(0xffffffffu, ok);
+                        if (!ok) break;
+                    }
+                    uint8_t *blkp = gOut + blk * 4096 + lane * 128;
+#pragma unroll
+                    for (int hf = 0; hf < 2; ++hf) {
+                        float v[32];
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r2[hf][j]);
+                        if (p.epilogue & VKC_EPI_BIAS) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 4) {
+                                const float4 bv = *reinterpret_cast<const float4 *>(wbias + sl * 64 + hf * 32 + j);
+                                v[j] += bv.x, v[j + 1] += bv.y, v[j + 2] += bv.z, v[j + 3] += bv.w;
+                            }
+                        }
+                        if (p.epilogue & VKC_EPI_GELU_ERF) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 2) {
+                                const float2 g2 = gelu_erf_pair(make_float2(v[j], v[j + 1]));
+                                v[j] = g2.x, v[j + 1] = g2.y;
+                            }
+                        }
+#pragma unroll
+                        for (int u = 0; u < 4; ++u) {
+                            uint4 *slot = reinterpret_cast<uint4 *>(blkp + (((hf * 4 + u) ^ (lane & 7)) << 4));
+                            if (resid) {
+                                const uint4 rv = *slot;
+                                const T    *rt = reinterpret_cast<const T *>(&rv);
+#pragma unroll
+                                for (int j = 0; j < 8; ++j) v[u * 8 + j] += St<T>::ld(rt + j);
+                            }
+                            uint4 ov;
+                            T    *ot = reinterpret_cast<T *>(&ov);
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) St<T>::st(ot + j, v[u * 8 + j]);
+                            *slot = ov;
+                        }
+                    }
+                    ptx::fence_proxy_async();
+                    __syncwarp();
+                    if (lane == 0) {
+                        if (rows_in) ptx::tma_store_3d(&tmD, wOut + blk * 4096, n0 + sl * 64, row0, bz);
+                        ptx::bulk_commit_group(); // committed even when empty: the rotation counts groups
+                    }
+                }
+            }
+            if (lane == 0) ptx::bulk_wait_group_read_0();
+            __syncwarp();
+        }
+        if (ctl[1]) {
+            // aborted: give copies still in flight time to land before the CTA releases its shared memory
+            for (int i = 0; i < 50; ++i) __nanosleep(20000);
+        }
+        ptx::tc_fence_before();
+        __syncthreads();
+        if (warp == 1) ptx::tmem_dealloc(tmem, 2 * acc_stride(BN));
+    }
+
+    template <int BN, int kStages, typename T, bool B_KN>
+    int launch_persistent(vkc_ctx *ctx, const CUtensorMap &tmA, const CUtensorMap &tmB, const CUtensorMap &tmD, const CUtensorMap &tmR,
+                          const GemmParams &p, int64_t batch, cudaStream_t st) {
+        auto          kern = gemm_tcgen05_persistent_kernel<BN, kStages, T, B_KN>;
+        constexpr int smem = smem_bytes_persistent<BN, kStages>();
+        static_assert(smem <= 227 * 1024, "shared memory budget");
+        if (int rc = vkc_configure_smem(ctx, kern, smem)) return rc;
+        const int64_t mt = (p.M + BM - 1) / BM, nt = (p.N + BN - 1) / BN, total = mt * nt * batch;
+        if (total > INT32_MAX) return vkc_fail(ctx, VKC_ERR_UNSUPPORTED, "gemm_tcgen05: too many tiles");
+        const int64_t ctas = total < ctx->sm_count ? total : ctx->sm_count;
+        vkc_launch(ctx, kern, dim3((unsigned) ctas), dim3(kThreads), smem, st, tmA, tmB, tmD, tmR, p, (int) mt, (int) nt, (int) total);
+        return vkc_post_launch(ctx, "gemm_tcgen05_persistent");
+    }
+
     // Tile width: fewest waves over the SMs first, then the least padded work. Wide tiles re-read A less often.
     // Configurations the launcher can pick: tile width, ring depth, CTAs per SM, split-K factor.
     enum TileConfig {
@@ -436,6 +711,9 @@ namespace {
         kCfg192x4x1s2, // split-K over a cluster of two CTAs
         kCfg256x3x1s2,
         kCfg128x5x1s2,
+        kCfgP256x3, // persistent, double-buffered accumulator: the epilogue overlaps the next tile's K loop
+        kCfgP192x4,
+        kCfgP128x5,
         kNumConfigs
     };
     struct TileChoice {
@@ -446,11 +724,14 @@ namespace {
     // problems that fit one wave want the deepest ring that fits (one CTA per SM); when even the widest tiles leave most
     // SMs idle, splitting K over a cluster of two fills them; short-K problems are dominated by prologue and epilogue
     // and run best as two co-resident CTAs per SM.
-    TileChoice choose_tile(int64_t M, int64_t N, int64_t K, int64_t batch, int sms, bool can_split) {
+    // A GELU epilogue is arithmetic-bound (about as long as a short K loop); with several tiles per SM the persistent form
+    // hides it behind the next tile's K loop.
+    TileChoice choose_tile(int64_t M, int64_t N, int64_t K, int64_t batch, int sms, bool staged, int epilogue) {
         const int64_t mt     = (M + BM - 1) / BM;
         auto          tiles  = [&](int bn) { return mt * ((N + bn - 1) / bn) * batch; };
         const int64_t num_kb = (K + BK - 1) / BK;
         if (tiles(256) >= 4 * (int64_t) sms) return {kCfg256x4x1, 256};
+        if (staged && (epilogue & VKC_EPI_GELU_ERF) && tiles(128) >= 2 * (int64_t) sms) return {kCfgP128x5, 128};
         if (num_kb >= 16) {
             // one-wave candidates, scored by busy SMs (ties: wider tile = less operand traffic)
             struct Cand {
@@ -461,7 +742,7 @@ namespace {
             int64_t    best_ctas = 0;
             int        best      = -1;
             for (int i = 0; i < 5; ++i) {
-                if (cands[i].split > 1 && (!can_split || num_kb < 8 * cands[i].split)) continue;
+                if (cands[i].split > 1 && (!staged || num_kb < 8 * cands[i].split)) continue;
                 const int64_t ctas = tiles(cands[i].bn) * cands[i].split;
                 if (ctas > sms) continue;
                 if (ctas > best_ctas) best_ctas = ctas, best = i;
@@ -524,10 +805,12 @@ int vkc_gemm_tcgen05(vkc_ctx *ctx, const void *A, const void *B, const float *bi
         tma_out = rc == VKC_OK;
     }
 
-    TileChoice tc = choose_tile(M, N, K, batch, ctx->sm_count, tma_out);
+    TileChoice tc = choose_tile(M, N, K, batch, ctx->sm_count, tma_out, epilogue);
     if (config >= 0) { // caller-chosen configuration (autotuning); refuse what this problem cannot run
-        const int  bns[kNumConfigs] = {256, 256, 192, 128, 64, 192, 128, 192, 256, 128};
-        const bool split            = config >= kCfg192x4x1s2;
+        const int  bns[kNumConfigs] = {256, 256, 192, 128, 64, 192, 128, 192, 256, 128, 256, 192, 128};
+        const bool split            = config >= kCfg192x4x1s2 && config <= kCfg128x5x1s2;
+        if (config >= kCfgP256x3 && !tma_out)
+            return vkc_fail(ctx, VKC_ERR_UNSUPPORTED, "gemm_tcgen05: persistent configuration %d needs a TMA-storable output", config);
         if (split && (!tma_out || (K + BK - 1) / BK < 4))
             return vkc_fail(ctx, VKC_ERR_UNSUPPORTED, "gemm_tcgen05: split-K configuration %d needs a TMA-storable output and at least 4 k-steps", config);
         tc = {(TileConfig) config, bns[config]};
@@ -576,6 +859,9 @@ int vkc_gemm_tcgen05(vkc_ctx *ctx, const void *A, const void *B, const float *bi
 #define VKC_GEMM_LAUNCH_S(BN_, ST_, C_, T_, S_)                                                                    \
     (b_layout == VKC_B_KN ? launch<BN_, ST_, C_, T_, true, S_>(ctx, tmA, tmB, tmD, tmR, p, batch, st) \
                           : launch<BN_, ST_, C_, T_, false, S_>(ctx, tmA, tmB, tmD, tmR, p, batch, st))
+#define VKC_GEMM_LAUNCH_P(BN_, ST_, T_)                                                                      \
+    (b_layout == VKC_B_KN ? launch_persistent<BN_, ST_, T_, true>(ctx, tmA, tmB, tmD, tmR, p, batch, st) \
+                          : launch_persistent<BN_, ST_, T_, false>(ctx, tmA, tmB, tmD, tmR, p, batch, st))
 #define VKC_GEMM_BY_TILE(T_)                                                         \
     do {                                                                             \
         switch (tc.cfg) {                                                            \
@@ -588,6 +874,9 @@ int vkc_gemm_tcgen05(vkc_ctx *ctx, const void *A, const void *B, const float *bi
             case kCfg128x6x1: return VKC_GEMM_LAUNCH(128, 6, 1, T_);                 \
             case kCfg192x4x1s2: return VKC_GEMM_LAUNCH_S(192, 4, 1, T_, 2);          \
             case kCfg256x3x1s2: return VKC_GEMM_LAUNCH_S(256, 3, 1, T_, 2);          \
+            case kCfgP256x3: return VKC_GEMM_LAUNCH_P(256, 3, T_);                   \
+            case kCfgP192x4: return VKC_GEMM_LAUNCH_P(192, 4, T_);                   \
+            case kCfgP128x5: return VKC_GEMM_LAUNCH_P(128, 5, T_);                   \
             default: return VKC_GEMM_LAUNCH_S(128, 5, 1, T_, 2);                     \
         }                                                                            \
     } while (0)
@@ -596,4 +885,5 @@ int vkc_gemm_tcgen05(vkc_ctx *ctx, const void *A, const void *B, const float *bi
 #undef VKC_GEMM_BY_TILE
 #undef VKC_GEMM_LAUNCH
 #undef VKC_GEMM_LAUNCH_S
+#undef VKC_GEMM_LAUNCH_P
 }

@@ -95,6 +95,8 @@ namespace ptx {
     // Waits only until the committed bulk stores have read their shared-memory source (enough before the CTA exits or
     // reuses the staging area; the global writes complete on their own).
     __device__ __forceinline__ void bulk_wait_group_read_0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+    // Same, but leaves the most recently committed group in flight.
+    __device__ __forceinline__ void bulk_wait_group_read_1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
     // Untiled bulk copy of `bytes` contiguous bytes (both addresses 16-byte aligned, size a multiple of 16).
     __device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
         asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src), "r"(bytes),

@@ -186,6 +186,21 @@ VKC_API int vkc_strided_copy(vkc_ctx *ctx, const void *X, void *Y, const int64_t
 VKC_API int vkc_strided_copy2(vkc_ctx *ctx, const void *X, void *Y, const int64_t *shape, const int64_t *in_strides, const int64_t *out_strides,
                               int rank, int64_t in_offset, int dtype, vkc_stream stream);
 
+/* ---- row moves through offset tables: for r in [0, nrows) copy row_elems contiguous elements from src + src_off[r] to
+ * dst + dst_off[r] (offsets in elements, int64 arrays in DEVICE memory; a null table stands for r * row_elems).
+ * Destination rows must not overlap. Serves Gather with a constant index list (GatherCpu::run
+ * src/backend/cpu/ops/gather.cpp:12-99: the table holds (o * axisSize + idx[k]) * inner) and the update loop of ScatterND
+ * (ScatterNDCpu::run src/backend/cpu/ops/scatternd.cpp:49-84; later rows win there, so the caller drops every row whose
+ * destination a later row overwrites). ---- */
+VKC_API int vkc_copy_rows(vkc_ctx *ctx, const void *src, void *dst, const int64_t *src_off, const int64_t *dst_off, int64_t nrows,
+                          int64_t row_elems, int dtype, vkc_stream stream);
+/* Gather along an axis with indices produced at run time: out[o, k, :] = data[o, index[k], :] for data
+ * [outer, axis_size, inner]. `index` is a device tensor of nidx values of index_dtype: a floating type is truncated toward
+ * zero like the reference's cast (gather.cpp:27-30; exact integers reach 2048 in fp16 and 256 in bf16), VKC_I32 is read
+ * as is. Negative values count from the end; a value outside the axis is clamped to it. */
+VKC_API int vkc_gather_rows(vkc_ctx *ctx, const void *data, const void *index, void *out, int64_t outer, int64_t axis_size, int64_t nidx,
+                            int64_t inner, int dtype, int index_dtype, vkc_stream stream);
+
 /* ---- K6: 3D Gaussian-splatting rasterizer, the step after the encoder. Reference: the renderer specified by
  * scripts/yonosplat/ref_rasterizer.py:22-75 (render_view) and implemented for the reference's device by
  * shaders/raster_{preprocess,duplicate,bitonic,ranges,composite,fill}.comp with the host driver examples/yonosplat.cpp.

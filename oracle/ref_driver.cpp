@@ -72,7 +72,7 @@ namespace {
             {"Expand", OpType::Expand},       {"Tile", OpType::Tile},           {"Concat", OpType::Concat},
             {"Squeeze", OpType::Squeeze},     {"Unsqueeze", OpType::Unsqueeze},
             {"Reduce", OpType::Reduce},       {"Where", OpType::Where},         {"Equal", OpType::Equal},
-            {"Greater", OpType::Greater},     {"GreaterEqual", OpType::GreaterEqual},
+            {"Greater", OpType::Greater},     {"GreaterEqual", OpType::GreaterEqual}, {"ScatterND", OpType::ScatterND},
         };
         auto it = m.find(n);
         if (it == m.end()) {

@@ -34,6 +34,9 @@ def build():
     """Compile the C restatement (and, where the reference sources are present, oracle/_ref)."""
     subprocess.check_call(["make", "-s", "-C", HERE, "oracle"])
     subprocess.check_call(["make", "-s", "-C", HERE, "ref"])
+    # the same driver linked with the CUDA plug-in (the GPU plug-in tests run it); needs the built kernel library
+    if os.path.exists(os.path.join(HERE, "..", "vknn_b200", "libvknn_cuda.so")):
+        subprocess.check_call(["make", "-s", "-C", HERE, "ref-cuda"])
 
 
 def lib():
@@ -466,4 +469,36 @@ def masked_pool_graph(x, thr):
     g.node("Reduce", "rowmean", ["x"], ["rowmean"], subop=0, axes=[2], keepdims=1)
     g.node("GreaterEqual", "ge", ["x", "rowmean"], ["ge"])
     g.node("Reduce", "ge_mean", ["ge"], ["ge_mean"], subop=0, axes=[2], keepdims=1)
+    return g
+
+
+def token_lookup_graph(x, table, pos, keep, upd, scat_idx, mask):
+    """Index-driven data movement as an exported encoder uses it around its blocks: a rotary table looked up with positions
+    computed at run time (Gather with a floating index tensor), a constant token selection (Gather with an int64 index list,
+    one with a 2-D index shape), ScatterND writing update rows back at constant (batch, token) positions, later rows winning,
+    and Where with a condition that broadcasts over the batch and feature axes.
+    x [B,T,d]; table [P,d]; pos [T] (integral values); keep int64 [K]; upd [R,d]; scat_idx int64 [R,2]; mask [T,1]."""
+    B, T, d = x.shape
+    K, R = keep.shape[0], upd.shape[0]
+    g = RefGraph()
+    g.input("x", x)
+    g.input("pos", pos)
+    g.input("upd", upd)
+    g.input("mask", mask)
+    g.init("table", table)
+    g.init("keep", keep.astype(np.int64))
+    g.init("keep2d", np.array([[0, -1, 2], [T - 1, 1, 0]], dtype=np.int64))
+    g.init("scat_idx", scat_idx.astype(np.int64))
+    for n in ("rot", "xr"):
+        g.inter(n)
+    g.output("rotated_kept", (B, K, d))
+    g.output("picked2d", (B, 2, 3, d))
+    g.output("scattered", (B, T, d))
+    g.output("chosen", (B, T, d))
+    g.node("Gather", "lookup", ["table", "pos"], ["rot"], axis=0)
+    g.node("Binary", "rotate", ["x", "rot"], ["xr"], subop=0)
+    g.node("Gather", "select", ["xr", "keep"], ["rotated_kept"], axis=1)
+    g.node("Gather", "select2d", ["x", "keep2d"], ["picked2d"], axis=-2)
+    g.node("ScatterND", "writeback", ["xr", "scat_idx", "upd"], ["scattered"])
+    g.node("Where", "choose", ["mask", "x", "xr"], ["chosen"])
     return g

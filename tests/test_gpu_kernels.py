@@ -364,6 +364,57 @@ def test_strided_copy_transpose(ctx):
     assert np.array_equal(host(Y), ref)
 
 
+@pytest.mark.parametrize("dt", [torch.float32, torch.float16])
+@pytest.mark.parametrize("inner", [1, 7, 8, 200])
+def test_gather_rows_runtime_index(ctx, dt, inner):
+    """out[o, k, :] = data[o, idx[k], :] with the index tensor on the device (float, half or int32), rows of odd and
+    16-byte-multiple lengths, negative indices counted from the end; numpy indexing is the reference
+    (GatherCpu::run src/backend/cpu/ops/gather.cpp:12-99)."""
+    rng = np.random.default_rng(40 + inner)
+    outer, axis = 3, 19
+    data = rng.standard_normal((outer, axis, inner)).astype(np.float16).astype(np.float32)
+    idx = np.array([0, 18, -1, 5, 5, -19, 7.9, 3], dtype=np.float32)  # 7.9 truncates to 7 like the reference's cast
+    want = data[:, idx.astype(np.int64)]
+    D = dev(data, dt)
+    for I in (torch.from_numpy(idx).cuda(), torch.from_numpy(idx).cuda().to(torch.float16), torch.from_numpy(idx.astype(np.int32)).cuda()):
+        Y = torch.zeros(want.shape, dtype=dt, device="cuda")
+        ctx.gather_rows(D, I, Y, outer, axis, inner)
+        ctx.sync()
+        assert np.array_equal(host(Y), want), str(I.dtype)
+    # an index outside the axis is clamped to it, never read from stray memory
+    Y = torch.zeros((outer, 2, inner), dtype=dt, device="cuda")
+    ctx.gather_rows(D, torch.tensor([1000.0, -1000.0], device="cuda"), Y, outer, axis, inner)
+    ctx.sync()
+    assert np.array_equal(host(Y), data[:, [axis - 1, 0]])
+
+
+def test_copy_rows_offset_tables(ctx):
+    """Row moves through device offset tables: a gather (source table), a scatter (destination table) and both at once."""
+    rng = np.random.default_rng(44)
+    src = rng.standard_normal((13, 24)).astype(np.float16).astype(np.float32)
+    S = dev(src, torch.float16)
+    pick = np.array([12, 0, 5, 5, 3], dtype=np.int64)
+    Y = torch.zeros((5, 24), dtype=torch.float16, device="cuda")
+    ctx.copy_rows(S, Y, torch.from_numpy(pick * 24).cuda(), None, 24)
+    ctx.sync()
+    assert np.array_equal(host(Y), src[pick])
+    dst_rows = np.array([7, 1, 9], dtype=np.int64)
+    Z = torch.zeros((10, 24), dtype=torch.float16, device="cuda")
+    ctx.copy_rows(S, Z, None, torch.from_numpy(dst_rows * 24).cuda(), 24)
+    ctx.sync()
+    want = np.zeros((10, 24), np.float32)
+    want[dst_rows] = src[:3]
+    assert np.array_equal(host(Z), want)
+    # 6-element rows at odd element offsets: the element-wise path
+    Z2 = torch.zeros(100, dtype=torch.float16, device="cuda")
+    ctx.copy_rows(S, Z2, torch.tensor([3, 51], device="cuda"), torch.tensor([1, 77], device="cuda"), 6)
+    ctx.sync()
+    want2 = np.zeros(100, np.float32)
+    want2[1:7] = src.ravel()[3:9]
+    want2[77:83] = src.ravel()[51:57]
+    assert np.array_equal(host(Z2), want2)
+
+
 def test_upload_download_roundtrip(ctx):
     rng = np.random.default_rng(1)
     x = rng.standard_normal(10007).astype(np.float32)

@@ -182,6 +182,44 @@ def test_selection_and_reduce_ops_run_on_the_cuda_backend(precision):
     assert np.array_equal(got[1], ref[1]) and np.array_equal(got[2], ref[2])
 
 
+@pytest.mark.parametrize("precision", ["low", "high"])
+def test_index_driven_ops_run_on_the_cuda_backend(precision):
+    """Gather with an index tensor computed at run time and with constant index lists (rank 1 and 2), ScatterND with constant
+    indices (duplicates: the later row wins; negative indices) and Where with a broadcasting condition plan into one CUDA
+    segment and match the reference CPU backend. Values are exactly representable in fp16 and the only arithmetic is one
+    multiplication, so the moved rows are compared exactly against what the multiplication produced."""
+    rng = np.random.default_rng(32)
+    B, T, d, P = 3, 50, 72, 64
+    f16 = lambda a: a.astype(np.float16).astype(np.float32)
+    x = f16(rng.standard_normal((B, T, d)))
+    table = f16(rng.standard_normal((P, d)))
+    pos = rng.integers(0, P, size=T).astype(np.float32)
+    keep = np.array([4, 0, -1, 4, 17, 33, 2], dtype=np.int64)
+    R = 11
+    upd = f16(rng.standard_normal((R, d)))
+    scat_idx = np.stack([rng.integers(-B, B, size=R), rng.integers(-T, T, size=R)], axis=1).astype(np.int64)
+    scat_idx[5] = scat_idx[1]          # a duplicate destination: row 5 must win over row 1
+    scat_idx[9] = [scat_idx[2][0] % B - B, scat_idx[2][1] % T]  # the same destination through a negative batch index
+    mask = (rng.random((T, 1)) > 0.5).astype(np.float32)
+    graph = lambda: vko.token_lookup_graph(x, table, pos, keep, upd, scat_idx, mask)
+    ref, _ = graph().run(backend="cpu")
+    got, info = graph().run(backend="cuda", precision=precision, iters=2)
+    kinds = [n[0] for n in info["nodes"]]
+    for op in ("Gather", "ScatterND", "Where"):
+        assert op in kinds, kinds
+    assert all(n[1] == CUDA_KIND for n in info["nodes"]), info["nodes"]
+    for a, b, what in zip(got, ref, ("rotated_kept", "picked2d", "scattered", "chosen")):
+        assert a.shape == b.shape, what
+        tol = 1e-4 * max(1.0, np.abs(b).max()) if precision == "high" else 1e-2 * max(1.0, np.abs(b).max())
+        assert np.abs(a - b).max() <= tol, (what, float(np.abs(a - b).max()))
+    # pure moves of input values are exact at either precision
+    assert np.array_equal(got[1], ref[1])
+    wrote = np.zeros((B, T), bool)
+    for b, t in scat_idx:
+        wrote[b, t] = True
+    assert np.array_equal(got[2][wrote], ref[2][wrote])
+
+
 def test_tuning_table_from_another_device_is_ignored(tmp_path):
     """A cache file whose header names another GPU / configuration set must not be trusted: the session measures again and
     rewrites it."""

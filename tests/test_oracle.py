@@ -187,3 +187,28 @@ def test_rasterizer_oracle_matches_the_reference_renderer():
         assert np.abs(img - g["rgb_%d" % seed]).max() <= 1e-6
         assert np.abs(alpha - g["alpha_%d" % seed]).max() <= 1e-6
         assert img.mean() > 0.1 and (alpha > 0.5).mean() > 0.5  # the scene actually covers the image
+
+
+def test_token_lookup_graph_matches_numpy():
+    """Gather (run-time floating index, constant index lists of rank 1 and 2), ScatterND (later rows win, negative indices) and
+    Where with a broadcasting condition, run by the reference CPU backend, against plain numpy indexing."""
+    if not os.path.exists(vko.REF_DRIVER):
+        pytest.skip("reference driver not built")
+    rng = np.random.default_rng(31)
+    B, T, d, P = 2, 9, 8, 16
+    x = rng.standard_normal((B, T, d)).astype(np.float32)
+    table = rng.standard_normal((P, d)).astype(np.float32)
+    pos = np.array([3, 0, 15, 7, 7, 1, 2, 14, 5], dtype=np.float32)
+    keep = np.array([4, 0, -1, 4], dtype=np.int64)
+    upd = rng.standard_normal((4, d)).astype(np.float32)
+    scat_idx = np.array([[0, 1], [1, -1], [0, 1], [-1, 0]], dtype=np.int64)
+    mask = (rng.random((T, 1)) > 0.5).astype(np.float32)
+    outs, _ = vko.token_lookup_graph(x, table, pos, keep, upd, scat_idx, mask).run(backend="cpu")
+    xr = x * table[pos.astype(np.int64)][None]
+    want_sc = xr.copy()
+    for r, (b, t) in enumerate(scat_idx):
+        want_sc[b, t] = upd[r]
+    np.testing.assert_array_equal(outs[0], xr[:, keep])
+    np.testing.assert_array_equal(outs[1], x[:, np.array([[0, -1, 2], [T - 1, 1, 0]])])
+    np.testing.assert_array_equal(outs[2], want_sc)
+    np.testing.assert_array_equal(outs[3], np.where(mask[None] != 0, x, xr))

@@ -101,7 +101,9 @@ namespace vknn {
         };
 
         struct Step {
-            enum Kind { Gemm, Attn, LayerNorm, Pointwise, Softmax, Copy, Reduce } kind;
+            enum Kind { Gemm, Attn, LayerNorm, Pointwise, Softmax, Copy, Reduce, Rows, GatherRt } kind;
+            // Rows: a -> d through the offset tables b (source) / c (destination), `rows` rows of `norm` elements.
+            // GatherRt: data a, index tensor b, M = outer, N = axis size, K = index count, norm = inner elements.
             int reduceOp = 0;
             // generic operands (device pointers resolved at plan time)
             const void *a = nullptr, *b = nullptr, *c = nullptr;
@@ -227,6 +229,7 @@ namespace vknn {
                 case OpType::Conv:
                 case OpType::Reduce:
                 case OpType::Where:
+                case OpType::ScatterND:
                 case OpType::Equal:
                 case OpType::Greater:
                 case OpType::GreaterEqual: return true;
@@ -254,9 +257,20 @@ namespace vknn {
                     return axis == -1 || axis == r - 1;
                 }
                 case OpType::Gather: {
-                    if (!g.isInitializer(nd.inputs[1])) return false;
+                    // constant int64 indices (one: a view; several: a row table built at plan time) or a floating
+                    // index tensor computed inside the segment (src/backend/cpu/ops/gather.cpp:27-30)
                     const TensorDesc &d = g.desc(nd.inputs[1]);
-                    return d.dtype == DType::Int64 && prod(d.shape) == 1;
+                    if (g.desc(nd.inputs[0]).dtype == DType::Int64) return false;
+                    if (g.isInitializer(nd.inputs[1])) return d.dtype == DType::Int64 && prod(d.shape) >= 1;
+                    return d.dtype == DType::Float32 || d.dtype == DType::Float16;
+                }
+                case OpType::ScatterND: {
+                    // constant int64 indices: destinations (and which duplicate wins) are resolved at plan time
+                    if (nd.inputs.size() != 3 || !g.isInitializer(nd.inputs[1]) || g.desc(nd.inputs[1]).dtype != DType::Int64) return false;
+                    const TensorDesc &dd = g.desc(nd.inputs[0]), &ud = g.desc(nd.inputs[2]);
+                    if (dd.dtype == DType::Int64 || ud.dtype == DType::Int64 || dd.shape.empty()) return false;
+                    const Shape &is = g.desc(nd.inputs[1]).shape;
+                    return !is.empty() && is.back() >= 1 && is.back() <= (int64_t) dd.shape.size();
                 }
                 case OpType::MatMul: {
                     const Shape &a = g.desc(nd.inputs[0]).shape, &b = g.desc(nd.inputs[1]).shape;
@@ -286,9 +300,18 @@ namespace vknn {
                     const Shape &o = g.desc(nd.outputs[0]).shape;
                     return (g.desc(nd.inputs[0]).shape == o && !g.isInitializer(nd.inputs[0])) || (g.desc(nd.inputs[1]).shape == o && !g.isInitializer(nd.inputs[1]));
                 }
-                case OpType::Where: // the condition drives the step program: it must be a runtime tensor of the output shape
-                    return nd.inputs.size() == 3 && g.desc(nd.inputs[0]).shape == g.desc(nd.outputs[0]).shape && !g.isInitializer(nd.inputs[0]) &&
-                           g.desc(nd.inputs[0]).dtype != DType::Int64;
+                case OpType::Where: { // the condition drives the step program; one that broadcasts is expanded to the output shape first
+                    if (nd.inputs.size() != 3) return false;
+                    for (TensorId in : nd.inputs)
+                        if (g.desc(in).dtype != DType::Float32 && g.desc(in).dtype != DType::Float16) return false;
+                    const Shape &c = g.desc(nd.inputs[0]).shape, &o = g.desc(nd.outputs[0]).shape;
+                    if (c.size() > o.size()) return false;
+                    for (size_t i = 0; i < c.size(); ++i) {
+                        const int64_t cd = c[c.size() - 1 - i], od = o[o.size() - 1 - i];
+                        if (cd != od && cd != 1) return false;
+                    }
+                    return true;
+                }
                 case OpType::Reduce: {
                     if (nd.inputs.size() > 1 && nd.inputs[1] != kNoTensor && !g.isInitializer(nd.inputs[1])) return false;
                     return nd.subOp >= 0 && nd.subOp <= 5 && !g.isInitializer(nd.inputs[0]);
@@ -824,7 +847,17 @@ namespace vknn {
             s.pwParams.assign(pr.begin(), pr.end());
             s.pwParams.resize(s.pwSteps.size() / 2, 0.f);
         }
-        View x = materialize(views_.at(primary), "pointwise primary");
+        View px = views_.at(primary);
+        if (n.type == OpType::Where && px.shape != oshape) {
+            // a broadcasting condition: read it through stride-0 axes, written out once at the output shape
+            View      e   = px;
+            const int off = rank - (int) px.shape.size();
+            e.shape = oshape;
+            e.strides.assign((size_t) rank, 0);
+            for (int d = off; d < rank; ++d) e.strides[(size_t) d] = px.shape[(size_t) (d - off)] == 1 ? 0 : px.strides[(size_t) (d - off)];
+            px = e;
+        }
+        View x = materialize(px, "pointwise primary");
         View y = newTensor(n.outputs[0], oshape);
         s.a = ptrOf(x);
         s.d = ptrOf(y);
@@ -912,23 +945,123 @@ namespace vknn {
                     int64_t     axis = n.attr.geti("axis", 0);
                     const int   r    = (int) x.shape.size();
                     if (axis < 0) axis += r;
-                    int64_t idx = i64Inits_.at(n.inputs[1])[0];
-                    if (idx < 0) idx += x.shape[axis];
-                    View y = x;
-                    y.offset += idx * x.strides[axis];
                     const TensorDesc &id = g.desc(n.inputs[1]);
-                    const bool scalar    = id.shape.empty() || (id.shape.size() == 1 && id.shape[0] == 1);
-                    if (scalar) {
-                        y.shape.erase(y.shape.begin() + axis);
-                        y.strides.erase(y.strides.begin() + axis);
-                        if (y.shape.empty()) {
-                            y.shape   = {1};
-                            y.strides = {1};
+                    const bool constIdx  = i64Inits_.count(n.inputs[1]) != 0;
+                    if (constIdx && i64Inits_.at(n.inputs[1]).size() == 1) {
+                        // one constant index: a view
+                        int64_t idx = i64Inits_.at(n.inputs[1])[0];
+                        if (idx < 0) idx += x.shape[axis];
+                        View y = x;
+                        y.offset += idx * x.strides[axis];
+                        const bool scalar = id.shape.empty() || (id.shape.size() == 1 && id.shape[0] == 1);
+                        if (scalar) {
+                            y.shape.erase(y.shape.begin() + axis);
+                            y.strides.erase(y.strides.begin() + axis);
+                            if (y.shape.empty()) {
+                                y.shape   = {1};
+                                y.strides = {1};
+                            }
+                        } else {
+                            y.shape[axis] = 1;
                         }
-                    } else {
-                        y.shape[axis] = 1;
+                        views_[n.outputs[0]] = y;
+                        break;
                     }
-                    views_[n.outputs[0]] = y;
+                    // several indices: rows of `inner` elements move from a dense copy of the data
+                    // (src/backend/cpu/ops/gather.cpp:31-76: out = data[:axis] + indices.shape + data[axis+1:])
+                    View    xd    = materialize(x, "gather data");
+                    int64_t outer = 1, inner = 1;
+                    for (int i = 0; i < axis; ++i) outer *= x.shape[i];
+                    for (int i = (int) axis + 1; i < r; ++i) inner *= x.shape[i];
+                    const int64_t axisSize = x.shape[axis];
+                    View          y        = newTensor(n.outputs[0], g.desc(n.outputs[0]).shape);
+                    Step          s;
+                    s.a    = ptrOf(xd);
+                    s.d    = ptrOf(y);
+                    s.norm = inner;
+                    if (constIdx) {
+                        const std::vector<int64_t> &ix = i64Inits_.at(n.inputs[1]);
+                        const int64_t               nidx = (int64_t) ix.size();
+                        std::vector<int64_t>        table((size_t) (outer * nidx));
+                        for (int64_t o = 0; o < outer; ++o)
+                            for (int64_t k = 0; k < nidx; ++k) {
+                                int64_t v = ix[(size_t) k] < 0 ? ix[(size_t) k] + axisSize : ix[(size_t) k];
+                                if (v < 0 || v >= axisSize) fail(Status::InvalidArgument, "Gather index out of range in " + n.name);
+                                table[(size_t) (o * nidx + k)] = (o * axisSize + v) * inner;
+                            }
+                        const int tb = newBuffer(table.size() * 8);
+                        check(ctx_, vkc_upload(ctx_, bufs_[tb].ptr, VKC_I32, table.data(), VKC_I32, (int64_t) table.size() * 2, nullptr), "vkc_upload");
+                        s.kind  = Step::Rows;
+                        s.b     = bufs_[tb].ptr;
+                        s.rows  = outer * nidx;
+                        s.label = "gather(rows)";
+                    } else {
+                        View iv = materialize(views_.at(n.inputs[1]), "gather index");
+                        s.kind  = Step::GatherRt;
+                        s.b     = ptrOf(iv);
+                        s.M     = outer;
+                        s.N     = axisSize;
+                        s.K     = prod(iv.shape);
+                        s.label = "gather(runtime index)";
+                    }
+                    steps_.push_back(s);
+                    break;
+                }
+                case OpType::ScatterND: {
+                    // out = data, then every index row overwrites one slice (src/backend/cpu/ops/scatternd.cpp:13-84). The
+                    // indices are constants: destinations are computed here, and of several rows aimed at one slice only the
+                    // last survives, which is what the reference's sequential loop leaves behind.
+                    const View                 &x  = views_.at(n.inputs[0]);
+                    const std::vector<int64_t> &ix = i64Inits_.at(n.inputs[1]);
+                    const Shape                &is = g.desc(n.inputs[1]).shape;
+                    const int                   r  = (int) x.shape.size();
+                    const int                   q  = (int) is.back();
+                    const int64_t               nrows = (int64_t) ix.size() / q;
+                    std::vector<int64_t>        stride((size_t) r, 1);
+                    for (int k = r - 2; k >= 0; --k) stride[(size_t) k] = stride[(size_t) k + 1] * x.shape[(size_t) k + 1];
+                    int64_t slice = 1;
+                    for (int k = q; k < r; ++k) slice *= x.shape[(size_t) k];
+                    View y = newTensor(n.outputs[0], x.shape);
+                    {
+                        Step c;
+                        c.kind      = Step::Copy;
+                        c.a         = bufs_[x.buf].ptr;
+                        c.d         = ptrOf(y);
+                        c.shape     = x.shape;
+                        c.inStrides = x.strides;
+                        c.inOffset  = x.offset;
+                        c.label     = "copy(scatter data)";
+                        steps_.push_back(c);
+                    }
+                    std::map<int64_t, int64_t> last; // destination offset -> the row that writes it last
+                    for (int64_t rr = 0; rr < nrows; ++rr) {
+                        int64_t off = 0;
+                        for (int c = 0; c < q; ++c) {
+                            int64_t v = ix[(size_t) (rr * q + c)];
+                            if (v < 0) v += x.shape[(size_t) c];
+                            if (v < 0 || v >= x.shape[(size_t) c]) fail(Status::InvalidArgument, "ScatterND index out of range in " + n.name);
+                            off += v * stride[(size_t) c];
+                        }
+                        last[off] = rr;
+                    }
+                    std::vector<int64_t> table;
+                    for (const auto &kv : last) table.push_back(kv.second * slice);
+                    for (const auto &kv : last) table.push_back(kv.first);
+                    if (!last.empty()) {
+                        View      u  = materialize(views_.at(n.inputs[2]), "scatter updates");
+                        const int tb = newBuffer(table.size() * 8);
+                        check(ctx_, vkc_upload(ctx_, bufs_[tb].ptr, VKC_I32, table.data(), VKC_I32, (int64_t) table.size() * 2, nullptr), "vkc_upload");
+                        Step s;
+                        s.kind  = Step::Rows;
+                        s.a     = ptrOf(u);
+                        s.d     = ptrOf(y);
+                        s.b     = bufs_[tb].ptr;
+                        s.c     = static_cast<const int64_t *>(bufs_[tb].ptr) + last.size();
+                        s.rows  = (int64_t) last.size();
+                        s.norm  = slice;
+                        s.label = "scatter(rows)";
+                        steps_.push_back(s);
+                    }
                     break;
                 }
                 case OpType::Slice: {
@@ -1184,6 +1317,13 @@ namespace vknn {
                 break;
             case Step::Reduce:
                 check(ctx_, vkc_reduce_rows(ctx_, s.a, s.d, s.rows, s.norm, s.reduceOp, dtype_, nullptr), "vkc_reduce_rows");
+                break;
+            case Step::Rows:
+                check(ctx_, vkc_copy_rows(ctx_, s.a, s.d, static_cast<const int64_t *>(s.b), static_cast<const int64_t *>(s.c), s.rows, s.norm, dtype_, nullptr),
+                      "vkc_copy_rows");
+                break;
+            case Step::GatherRt:
+                check(ctx_, vkc_gather_rows(ctx_, s.a, s.b, s.d, s.M, s.N, s.K, s.norm, dtype_, dtype_, nullptr), "vkc_gather_rows");
                 break;
             case Step::Copy:
                 if (s.outStrides.empty())

@@ -9,7 +9,7 @@ import re
 HERE = os.path.dirname(os.path.abspath(__file__))
 HEADER = os.path.join(os.path.dirname(HERE), "include", "vknn_cuda.h")
 
-F32, F16, BF16 = 0, 1, 2
+F32, F16, BF16, I32 = 0, 1, 2, 3
 EPI_NONE, EPI_BIAS, EPI_GELU_ERF, EPI_RESIDUAL = 0, 1, 2, 4
 B_KN, B_NK = 0, 1
 IMPL_AUTO, IMPL_SIMT, IMPL_TCGEN05 = 0, 1, 2
@@ -82,6 +82,8 @@ def load_library():
     L.vkc_strided_copy.argtypes = [vp, vp, vp, vp, vp, i32, i64, i32, vp]
     L.vkc_reduce_rows.argtypes = [vp, vp, vp, i64, i64, i32, i32, vp]
     L.vkc_strided_copy2.argtypes = [vp, vp, vp, vp, vp, vp, i32, i64, i32, vp]
+    L.vkc_copy_rows.argtypes = [vp, vp, vp, vp, vp, i64, i64, i32, vp]
+    L.vkc_gather_rows.argtypes = [vp, vp, vp, vp, i64, i64, i64, i64, i32, i32, vp]
     L.vkc_graph_begin.argtypes = [vp]
     L.vkc_graph_end.argtypes = [vp, C.POINTER(vp)]
     L.vkc_graph_launch.argtypes = [vp, vp]
@@ -288,6 +290,19 @@ class Context:
                                                   self._stream(stream)))
         self._keepalive = ws  # the workspace must outlive the asynchronous launches
         return rgb, alpha
+
+    def copy_rows(self, src, dst, src_off, dst_off, row_elems, stream=None):
+        """dst[dst_off[r] + j] = src[src_off[r] + j] for every row r; the offset tables are int64 device tensors (None: r * row_elems)."""
+        nrows = (src_off if src_off is not None else dst_off).numel() if (src_off is not None or dst_off is not None) else src.numel() // max(row_elems, 1)
+        self._check(self.lib.vkc_copy_rows(self.h, src.data_ptr(), dst.data_ptr(), src_off.data_ptr() if src_off is not None else None,
+                                           dst_off.data_ptr() if dst_off is not None else None, nrows, row_elems, _dtype_code(src), self._stream(stream)))
+
+    def gather_rows(self, data, index, out, outer, axis_size, inner, stream=None):
+        """out[o, k, :] = data[o, index[k], :] with a device-resident index tensor (float32 / float16 / bfloat16 / int32)."""
+        import torch
+        icode = I32 if index.dtype == torch.int32 else _dtype_code(index)
+        self._check(self.lib.vkc_gather_rows(self.h, data.data_ptr(), index.data_ptr(), out.data_ptr(), outer, axis_size, index.numel(), inner,
+                                             _dtype_code(data), icode, self._stream(stream)))
 
     def strided_copy(self, X, Y, shape, in_strides, in_offset=0, stream=None):
         self._check(self.lib.vkc_strided_copy(self.h, X.data_ptr(), Y.data_ptr(), _i64arr(shape), _i64arr(in_strides), len(shape), in_offset,

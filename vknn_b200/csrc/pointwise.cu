@@ -179,6 +179,52 @@ namespace {
         return (int) (blocks < cap ? (blocks > 0 ? blocks : 1) : cap);
     }
 
+    // Row moves for Gather and ScatterND: row r of `rows` copies row_elems contiguous elements from src_off(r) to
+    // dst_off(r). One warp walks a row in 16-byte pieces when both ends allow it, else element by element; rows are
+    // spread over warps grid-stride. W is the storage word (2 or 4 bytes).
+    template <typename W> __device__ __forceinline__ void move_row(const W *__restrict__ s, W *__restrict__ d, int64_t n, int lane) {
+        constexpr int kPer = 16 / (int) sizeof(W);
+        if ((((uintptr_t) s | (uintptr_t) d) & 15) == 0 && n % kPer == 0) {
+            const uint4 *s4 = reinterpret_cast<const uint4 *>(s);
+            uint4       *d4 = reinterpret_cast<uint4 *>(d);
+            for (int64_t j = lane; j < n / kPer; j += 32) d4[j] = s4[j];
+        } else {
+            for (int64_t j = lane; j < n; j += 32) d[j] = s[j];
+        }
+    }
+
+    template <typename W>
+    __global__ void __launch_bounds__(256) copy_rows_kernel(const W *__restrict__ src, W *__restrict__ dst, const int64_t *__restrict__ src_off,
+                                                            const int64_t *__restrict__ dst_off, int64_t nrows, int64_t row_elems) {
+        const int     lane  = threadIdx.x & 31;
+        const int64_t warp0 = (int64_t) blockIdx.x * 8 + (threadIdx.x >> 5), nwarps = (int64_t) gridDim.x * 8;
+        for (int64_t r = warp0; r < nrows; r += nwarps) {
+            const int64_t so = src_off ? __ldg(src_off + r) : r * row_elems, dofs = dst_off ? __ldg(dst_off + r) : r * row_elems;
+            move_row(src + so, dst + dofs, row_elems, lane);
+        }
+    }
+
+    template <typename I> __device__ __forceinline__ int64_t index_value(const I *p, int64_t k);
+    template <> __device__ __forceinline__ int64_t index_value<float>(const float *p, int64_t k) { return (int64_t) p[k]; }
+    template <> __device__ __forceinline__ int64_t index_value<__half>(const __half *p, int64_t k) { return (int64_t) __half2float(p[k]); }
+    template <> __device__ __forceinline__ int64_t index_value<__nv_bfloat16>(const __nv_bfloat16 *p, int64_t k) { return (int64_t) __bfloat162float(p[k]); }
+    template <> __device__ __forceinline__ int64_t index_value<int32_t>(const int32_t *p, int64_t k) { return p[k]; }
+
+    // Gather along an axis with indices that are themselves device data: out[o, k, :] = data[o, idx[k], :].
+    template <typename W, typename I>
+    __global__ void __launch_bounds__(256) gather_rows_kernel(const W *__restrict__ data, const I *__restrict__ idx, W *__restrict__ out, int64_t outer,
+                                                              int64_t axis_size, int64_t nidx, int64_t inner) {
+        const int     lane  = threadIdx.x & 31;
+        const int64_t warp0 = (int64_t) blockIdx.x * 8 + (threadIdx.x >> 5), nwarps = (int64_t) gridDim.x * 8;
+        for (int64_t r = warp0; r < outer * nidx; r += nwarps) {
+            const int64_t o = r / nidx, k = r - o * nidx;
+            int64_t       i = index_value<I>(idx, k);
+            if (i < 0) i += axis_size;
+            i = i < 0 ? 0 : (i >= axis_size ? axis_size - 1 : i); // an index outside the axis reads the nearest row instead of stray memory
+            move_row(data + (o * axis_size + i) * inner, out + r * inner, inner, lane);
+        }
+    }
+
 } // namespace
 
 extern "C" {
@@ -300,6 +346,51 @@ int vkc_strided_copy2(vkc_ctx *ctx, const void *X, void *Y, const int64_t *shape
 int vkc_strided_copy(vkc_ctx *ctx, const void *X, void *Y, const int64_t *shape, const int64_t *in_strides, int rank, int64_t in_offset, int dtype,
                      vkc_stream stream) {
     return vkc_strided_copy2(ctx, X, Y, shape, in_strides, nullptr, rank, in_offset, dtype, stream);
+}
+
+int vkc_copy_rows(vkc_ctx *ctx, const void *src, void *dst, const int64_t *src_off, const int64_t *dst_off, int64_t nrows, int64_t row_elems, int dtype,
+                  vkc_stream stream) {
+    if (!ctx) return VKC_ERR_INVALID;
+    VKC_REQUIRE(ctx, nrows >= 0 && row_elems >= 0, "copy_rows: bad extents");
+    VKC_REQUIRE(ctx, dtype == VKC_F32 || dtype == VKC_F16 || dtype == VKC_BF16, "copy_rows: bad dtype %d", dtype);
+    if (nrows == 0 || row_elems == 0) return VKC_OK;
+    VKC_REQUIRE(ctx, src && dst, "copy_rows: null tensor");
+    cudaStream_t  st     = vkc_pick_stream(ctx, stream);
+    const int64_t want   = (nrows + 7) / 8, cap = (int64_t) ctx->sm_count * 16;
+    const unsigned blocks = (unsigned) (want < cap ? want : cap);
+    if (vkc_dtype_size(dtype) == 4)
+        copy_rows_kernel<uint32_t><<<blocks, 256, 0, st>>>((const uint32_t *) src, (uint32_t *) dst, src_off, dst_off, nrows, row_elems);
+    else
+        copy_rows_kernel<uint16_t><<<blocks, 256, 0, st>>>((const uint16_t *) src, (uint16_t *) dst, src_off, dst_off, nrows, row_elems);
+    return vkc_post_launch(ctx, "copy_rows");
+}
+
+int vkc_gather_rows(vkc_ctx *ctx, const void *data, const void *index, void *out, int64_t outer, int64_t axis_size, int64_t nidx, int64_t inner,
+                    int dtype, int index_dtype, vkc_stream stream) {
+    if (!ctx) return VKC_ERR_INVALID;
+    VKC_REQUIRE(ctx, outer >= 0 && axis_size >= 1 && nidx >= 0 && inner >= 0, "gather_rows: bad extents");
+    VKC_REQUIRE(ctx, dtype == VKC_F32 || dtype == VKC_F16 || dtype == VKC_BF16, "gather_rows: bad dtype %d", dtype);
+    VKC_REQUIRE(ctx, index_dtype == VKC_F32 || index_dtype == VKC_F16 || index_dtype == VKC_BF16 || index_dtype == VKC_I32,
+                "gather_rows: bad index dtype %d", index_dtype);
+    if (outer * nidx == 0 || inner == 0) return VKC_OK;
+    VKC_REQUIRE(ctx, data && index && out, "gather_rows: null tensor");
+    cudaStream_t  st     = vkc_pick_stream(ctx, stream);
+    const int64_t want   = (outer * nidx + 7) / 8, cap = (int64_t) ctx->sm_count * 16;
+    const unsigned blocks = (unsigned) (want < cap ? want : cap);
+#define VKC_GATHER(W_)                                                                                                                            \
+    switch (index_dtype) {                                                                                                                        \
+        case VKC_F32: gather_rows_kernel<W_, float><<<blocks, 256, 0, st>>>((const W_ *) data, (const float *) index, (W_ *) out, outer, axis_size, nidx, inner); break; \
+        case VKC_F16: gather_rows_kernel<W_, __half><<<blocks, 256, 0, st>>>((const W_ *) data, (const __half *) index, (W_ *) out, outer, axis_size, nidx, inner); break; \
+        case VKC_BF16: gather_rows_kernel<W_, __nv_bfloat16><<<blocks, 256, 0, st>>>((const W_ *) data, (const __nv_bfloat16 *) index, (W_ *) out, outer, axis_size, nidx, inner); break; \
+        default: gather_rows_kernel<W_, int32_t><<<blocks, 256, 0, st>>>((const W_ *) data, (const int32_t *) index, (W_ *) out, outer, axis_size, nidx, inner); break; \
+    }
+    if (vkc_dtype_size(dtype) == 4) {
+        VKC_GATHER(uint32_t)
+    } else {
+        VKC_GATHER(uint16_t)
+    }
+#undef VKC_GATHER
+    return vkc_post_launch(ctx, "gather_rows");
 }
 
 } // extern "C"

@@ -60,6 +60,11 @@ namespace {
         int    kv_splits;
         void  *part_o;  // [kv_splits][B][Hq][Sq][D] storage type
         float *part_ml; // [kv_splits][B][Hq][Sq][2]
+        // causal launch order (0: off). Blocks start in linear grid order, so the grid is re-read as groups of head_group
+        // (batch, head) pairs; inside a group the query tiles run from the heaviest to the lightest with the pairs of the
+        // group side by side. The last blocks to start are then the lightest ones (no long tail behind a late heavy tile),
+        // while the K/V of the pairs in flight still fit in L2.
+        int head_group;
     };
     constexpr int kTlTile = 20;
 
@@ -182,10 +187,19 @@ namespace {
                       bOF = bPF + QT * kPParts;
 
         const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-        const int b = blockIdx.z, h = blockIdx.y;
+        int       b = blockIdx.z, h = blockIdx.y, bx = (int) blockIdx.x / p.kv_splits;
+        const int split = (int) blockIdx.x % p.kv_splits, nbx = (int) gridDim.x / p.kv_splits;
+        if (p.head_group > 0) { // kv_splits == 1 here
+            const int pairs = (int) (gridDim.y * gridDim.z), lin = (int) (blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z));
+            const int grp = lin / (p.head_group * nbx), r = lin - grp * p.head_group * nbx; // every group before the last is full
+            const int gsz = min(p.head_group, pairs - grp * p.head_group);
+            const int hb  = grp * p.head_group + r % gsz;
+            bx            = r / gsz;
+            h             = hb % (int) gridDim.y;
+            b             = hb / (int) gridDim.y;
+        }
         const int hk = h / (int) (p.Hq / p.Hkv);
         // heavy (late) query tiles first when causal
-        const int     split = (int) blockIdx.x % p.kv_splits, bx = (int) blockIdx.x / p.kv_splits, nbx = (int) gridDim.x / p.kv_splits;
         const int     mt = p.causal ? nbx - 1 - bx : bx;
         const int64_t m0 = (int64_t) mt * (kQTiles * BM);
 
@@ -672,6 +686,15 @@ namespace {
         return launch_attn_qt<T, D, 2>(ctx, tq, tk, tv, p, B, st);
     }
 
+    // (batch, head) pairs whose K and V (all Skv keys) together stay within about half of L2
+    int causal_head_group(const vkc_ctx *ctx, int64_t pairs, int64_t Skv, int64_t D) {
+        const int64_t per_pair = 2 * Skv * D * 2, budget = (int64_t) ctx->l2_bytes / 2;
+        int64_t       g        = budget / (per_pair > 0 ? per_pair : 1);
+        if (g < 1) g = 1;
+        if (g > pairs) g = pairs;
+        return (int) g;
+    }
+
     int make_qkv_map(vkc_ctx *ctx, CUtensorMap *map, int dtype, const void *base, int64_t B, int64_t H, int64_t S, int64_t D, const int64_t *str) {
         // dims innermost first: {D, S, H, B}; element strides {1, str[2], str[1], str[0]}
         uint64_t dims[4] = {(uint64_t) D, (uint64_t) S, (uint64_t) H, (uint64_t) B};
@@ -713,6 +736,7 @@ int vkc_attn_prefill_tcgen05(vkc_ctx *ctx, const void *Q, const void *K, const v
     p.dev_err    = ctx->dev_err;
     p.timeline   = ctx->timeline;
     p.kv_splits  = 1;
+    p.head_group = causal ? causal_head_group(ctx, B * Hq, Skv, D) : 0;
     p.part_o     = nullptr;
     p.part_ml    = nullptr;
     if (dtype == VKC_F16) return D == 64 ? launch_attn<__half, 64>(ctx, tq, tk, tv, p, B, st) : launch_attn<__half, 128>(ctx, tq, tk, tv, p, B, st);

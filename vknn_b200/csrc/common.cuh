@@ -23,6 +23,7 @@ enum : int {
 struct vkc_ctx {
     int          device     = 0;
     int          sm_count   = 0;
+    size_t       l2_bytes   = 0;
     int          cc_major   = 0;
     int          impl       = VKC_IMPL_AUTO;
     cudaStream_t stream     = nullptr;

@@ -77,6 +77,7 @@ int vkc_ctx_create(int device_ordinal, vkc_ctx **out) {
     vkc_ctx *ctx  = new vkc_ctx();
     ctx->device   = device_ordinal;
     ctx->sm_count = prop.multiProcessorCount;
+    ctx->l2_bytes = (size_t) prop.l2CacheSize;
     if (const char *e = getenv("VKNN_PDL")) ctx->dep_launch = atoi(e) != 0;
     ctx->cc_major = prop.major;
     if (cudaSetDevice(device_ordinal) != cudaSuccess || cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking) != cudaSuccess ||

@@ -119,6 +119,40 @@ VKC_API int vkc_attn_prefill(vkc_ctx *ctx, const void *Q, const void *K, const v
                              const int64_t *v_strides, const int64_t *o_strides, float scale, int causal, const float *mask,
                              const int32_t *kv_len, int dtype, vkc_stream stream);
 
+/* ---- prefill attention with its output fanned out to several GPUs (the all-gather at the attention-output boundary of a
+ * head-sharded encoder, done by the kernel that produces the tiles instead of a collective after it). The reference has no
+ * multi-device path (docs/LIMITATIONS.md:15-32); the arithmetic is vkc_attn_prefill's (MatMulCpu / SoftmaxCpu chain,
+ * src/backend/cpu/ops/matmul.cpp:14-116, softmax.cpp:9-51).
+ *   dest[0..n_dest): output buffers addressed with o_strides, all mapped on THIS GPU: its own gather buffer and the peers'
+ *     (vkc_peer_open); the kernel stores every output row into each of them (plain peer stores over NVLink).
+ *   flag[p]: a 32-bit word in destination p's memory that belongs to this rank. When the last block has stored its rows the
+ *     kernel publishes (release, system scope) the number of fan-outs this rank has completed so far. NULL: no signal.
+ *   state: two zero-initialised 32-bit words in this GPU's memory (block counter, completed fan-outs); the caller keeps
+ *     them for the lifetime of the flags.
+ * The consumer calls vkc_peer_wait on its own flag array before reading its buffer. Needs the tensor-core kernel
+ * (16-bit storage, D in {64,128}, no additive mask): VKC_ERR_UNSUPPORTED otherwise. ---- */
+typedef struct vkc_fanout {
+    int       n_dest;
+    void     *dest[8];
+    uint32_t *flag[8];
+    uint32_t *state;
+} vkc_fanout;
+VKC_API int vkc_attn_prefill_fanout(vkc_ctx *ctx, const void *Q, const void *K, const void *V, int64_t B, int64_t Hq, int64_t Hkv, int64_t Sq,
+                                    int64_t Skv, int64_t D, const int64_t *q_strides, const int64_t *k_strides, const int64_t *v_strides,
+                                    const int64_t *o_strides, float scale, int causal, const int32_t *kv_len, int dtype, const vkc_fanout *fan,
+                                    vkc_stream stream);
+/* Waits (on the stream, in a one-block kernel) until each of the n flags has reached *expected + 1, then stores that value
+ * to *expected (a 32-bit device word, zero-initialised once). The wait is bounded (about two seconds): on expiry the
+ * kernel sets the context's device error word, which the next vkc_sync reports as VKC_ERR_DEVICE, and returns, so a
+ * missing peer never hangs the GPU. */
+VKC_API int vkc_peer_wait(vkc_ctx *ctx, const uint32_t *flags, int n, uint32_t *expected, vkc_stream stream);
+/* Sharing a vkc_alloc'ed buffer with the other processes of the node: export gives 64 opaque bytes to hand to a peer
+ * process (any transport), open maps that buffer into this process (peer access over NVLink), close unmaps it. */
+#define VKC_PEER_HANDLE_BYTES 64
+VKC_API int vkc_peer_export(vkc_ctx *ctx, void *dptr, unsigned char *handle);
+VKC_API int vkc_peer_open(vkc_ctx *ctx, const unsigned char *handle, void **dptr);
+VKC_API int vkc_peer_close(vkc_ctx *ctx, void *dptr);
+
 /* ---- K3: single-query (decode) attention over a KV cache, split along the cache length. Reference: the same
  * node run as K2 in its decode shape, which the reference executes as naive MatMul (M < 32 path,
  * src/backend/vulkan/ops/matmul.cpp:137-141, shaders/matmul.comp:15-29) -> scale+mask -> flat_softmax -> MatMul.

@@ -415,6 +415,52 @@ def test_copy_rows_offset_tables(ctx):
     assert np.array_equal(host(Z2), want2)
 
 
+@pytest.mark.parametrize("H,T,D", [(2, 700, 64), (4, 300, 128), (12, 1500, 64), (2, 2738, 64)])
+def test_attention_fanout_stores_and_signals(ctx, H, T, D):
+    """vkc_attn_prefill_fanout on one GPU: the same rows as vkc_attn_prefill land in every destination (here two local
+    [T, H*D] buffers at a column offset, the merged-head layout a head-sharded encoder gathers into), through the direct
+    epilogue (D = 128), the key-range-split merge pass (few heads at D = 64) and the unsplit one-tile form; each call raises
+    this rank's flag in every destination by one, and vkc_peer_wait consumes exactly one step per call."""
+    g = torch.Generator(device="cuda").manual_seed(70 + H)
+    qkv = torch.randn(T, 3, H, D, generator=g, device="cuda").half()
+    q, k, v = (qkv[:, i].permute(1, 0, 2).unsqueeze(0) for i in range(3))
+    ref = torch.zeros(1, H, T, D, dtype=torch.float16, device="cuda")
+    ctx.attn_prefill(q, k, v, ref, scale=D ** -0.5)
+    width, off = H * D + 64, 64
+    bufs = [torch.zeros(T, width, dtype=torch.float16, device="cuda") for _ in range(2)]
+    flags = torch.zeros(2, 4, dtype=torch.int32, device="cuda")  # destination d: this rank owns word 1 of its flag row
+    state = torch.zeros(2, dtype=torch.int32, device="cuda")
+    expected = torch.zeros(1, dtype=torch.int32, device="cuda")
+    for call in (1, 2):
+        ctx.attn_prefill_fanout(q, k, v, [b.data_ptr() + off * 2 for b in bufs], [flags[d, 1:].data_ptr() for d in range(2)], state,
+                                (T * width, D, width), scale=D ** -0.5)
+        ctx.peer_wait(flags[0, 1:].data_ptr(), 1, expected)
+        ctx.sync()
+        want = ref[0].permute(1, 0, 2).reshape(T, H * D)
+        for b in bufs:
+            assert torch.equal(b[:, off:], want)
+            assert not b[:, :off].any()
+        assert flags[:, 1].tolist() == [call, call] and not flags[:, 0].any() and expected.item() == call
+        assert state.tolist() == [0, call]
+
+
+def test_peer_wait_runs_out_instead_of_hanging(ctx):
+    """A flag that nobody raises: the wait kernel gives up after its limit and the next sync reports a device error; the
+    context stays usable."""
+    flags = torch.zeros(2, dtype=torch.int32, device="cuda")
+    expected = torch.zeros(1, dtype=torch.int32, device="cuda")
+    ctx.peer_wait(flags.data_ptr(), 2, expected)
+    with pytest.raises(vknn_b200.VkcError) as e:
+        ctx.sync()
+    assert e.value.code == -5
+    ctx.sync()
+    x = torch.randn(64, 256, device="cuda").half()
+    y = torch.empty_like(x)
+    ctx.layernorm(x, torch.ones(256, device="cuda"), torch.zeros(256, device="cuda"), y, 1e-5)
+    ctx.sync()
+    assert torch.isfinite(y.float()).all()
+
+
 def test_upload_download_roundtrip(ctx):
     rng = np.random.default_rng(1)
     x = rng.standard_normal(10007).astype(np.float32)

@@ -1,5 +1,6 @@
-"""Multi-GPU path on real devices (skipped with fewer than two GPUs): a head-sharded encoder layer, with its one
-NCCL all-gather at the attention-output boundary, must reproduce the single-GPU layer."""
+"""Multi-GPU path on real devices (skipped with fewer than two GPUs): a head-sharded encoder layer must reproduce the
+single-GPU layer, both with the NCCL all-gather at the attention-output boundary and with the attention kernel storing its
+tiles into every rank's gather buffer over peer memory (no collective, captured as a CUDA graph)."""
 import os
 import socket
 
@@ -30,6 +31,27 @@ def _worker(rank, world, port, ret):
         got = layer.forward_head_sharded(x)
         ctx.sync()
         ret[rank] = float((got.float() - ref.float()).abs().max())
+        # the same through peer memory: two layers (the two gather buffers alternate), eager and as a replayed graph
+        from vknn_b200.encoder import EncoderStack
+        from vknn_b200.sharding import PeerGather
+        rng = np.random.default_rng(6)
+        stack = EncoderStack(ctx, [encoder_weights(rng, 256, 512, bias_scale=0.01) for _ in range(2)], 8, dtype=torch.float16)
+        ref2 = stack.forward(x).clone()
+        stack.shard_heads(rank, world)
+        gather = PeerGather(ctx, 333, 256, torch.float16)
+        got2 = stack.forward_head_sharded_fused(x, gather).clone()
+        ctx.sync()
+        err = float((got2.float() - ref2.float()).abs().max())
+        torch.cuda.synchronize()
+        dist.barrier()
+        graph, y = stack.capture_head_sharded_fused(x, gather)
+        for _ in range(3):
+            graph.replay()
+        ctx.sync()
+        err = max(err, float((y.float() - ref2.float()).abs().max()))
+        ret["fused%d" % rank] = err
+        dist.barrier()
+        gather.close()
         ctx.close()
     finally:
         dist.destroy_process_group()
@@ -45,3 +67,4 @@ def test_head_sharded_layer_matches_single_gpu():
     mp.spawn(_worker, args=(2, port, ret), nprocs=2, join=True)
     # same kernels on the same values; only the GEMM tile shapes differ between the sharded and the full QKV projection
     assert all(ret[r] <= 2e-3 for r in range(2)), dict(ret)
+    assert all(ret["fused%d" % r] <= 4e-3 for r in range(2)), dict(ret)

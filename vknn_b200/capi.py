@@ -70,6 +70,11 @@ def load_library():
     L.vkc_gemm_ex.argtypes = [vp, vp, vp, vp, vp, vp] + [i64] * 10 + [i32, i32, i32, i32, vp]
     L.vkc_gemm_config_count.argtypes = []
     L.vkc_attn_prefill.argtypes = [vp, vp, vp, vp, vp] + [i64] * 6 + [vp, vp, vp, vp, f32, i32, vp, vp, i32, vp]
+    L.vkc_attn_prefill_fanout.argtypes = [vp, vp, vp, vp] + [i64] * 6 + [vp, vp, vp, vp, f32, i32, vp, i32, C.POINTER(Fanout), vp]
+    L.vkc_peer_wait.argtypes = [vp, vp, i32, vp, vp]
+    L.vkc_peer_export.argtypes = [vp, vp, C.c_char_p]
+    L.vkc_peer_open.argtypes = [vp, C.c_char_p, C.POINTER(vp)]
+    L.vkc_peer_close.argtypes = [vp, vp]
     L.vkc_attn_decode_workspace_bytes.argtypes = [i64] * 5
     L.vkc_attn_decode_workspace_bytes.restype = sz
     L.vkc_attn_decode.argtypes = [vp, vp, vp, vp, vp] + [i64] * 5 + [vp, f32, vp, sz, i32, vp]
@@ -109,6 +114,14 @@ def _np_dtype_code(a):
     if a.dtype == np.float16:
         return F16
     raise TypeError("host arrays must be float32 or float16")
+
+
+class Fanout(C.Structure):
+    """Mirror of struct vkc_fanout (include/vknn_cuda.h)."""
+    _fields_ = [("n_dest", C.c_int), ("dest", C.c_void_p * 8), ("flag", C.c_void_p * 8), ("state", C.c_void_p)]
+
+
+PEER_HANDLE_BYTES = 64
 
 
 def _i64arr(vals):
@@ -212,6 +225,50 @@ class Context:
                                               st(Q), st(K), st(V), st(O), float(scale), int(bool(causal)),
                                               mask.data_ptr() if mask is not None else None, kv_len.data_ptr() if kv_len is not None else None,
                                               _dtype_code(Q), self._stream(stream)))
+
+    def attn_prefill_fanout(self, Q, K, V, dests, flags, state, o_strides, scale, causal=False, kv_len=None, stream=None):
+        """attn_prefill whose output rows are stored into every buffer of `dests` (raw device pointers mapped on this GPU,
+        addressed with o_strides = (batch, head, row) element strides); `flags[d]` (pointer or None) receives this rank's
+        completion count when the last block has stored; `state` is a zeroed 2 x int32 device tensor kept by the caller."""
+        B, Hq, Sq, D = Q.shape
+        _, Hkv, Skv, _ = K.shape
+        for t in (Q, K, V):
+            assert t.stride(-1) == 1
+        f = Fanout()
+        f.n_dest = len(dests)
+        for i, d in enumerate(dests):
+            f.dest[i] = int(d)
+            f.flag[i] = int(flags[i]) if flags is not None and flags[i] else None
+        f.state = state.data_ptr()
+        st = lambda t: _i64arr([t.stride(0), t.stride(1), t.stride(2)])  # noqa: E731
+        self._check(self.lib.vkc_attn_prefill_fanout(self.h, Q.data_ptr(), K.data_ptr(), V.data_ptr(), B, Hq, Hkv, Sq, Skv, D, st(Q), st(K), st(V),
+                                                     _i64arr(list(o_strides)), float(scale), int(bool(causal)),
+                                                     kv_len.data_ptr() if kv_len is not None else None, _dtype_code(Q), C.byref(f), self._stream(stream)))
+
+    def peer_wait(self, flags_ptr, n, expected, stream=None):
+        """Stream-ordered bounded wait until each of the n flag words at flags_ptr has reached expected[0] + 1."""
+        self._check(self.lib.vkc_peer_wait(self.h, int(flags_ptr), n, expected.data_ptr(), self._stream(stream)))
+
+    def raw_alloc(self, nbytes):
+        p = C.c_void_p()
+        self._check(self.lib.vkc_alloc(self.h, nbytes, C.byref(p)))
+        return int(p.value)
+
+    def raw_free(self, ptr):
+        self._check(self.lib.vkc_free(self.h, int(ptr)))
+
+    def peer_export(self, ptr):
+        buf = C.create_string_buffer(PEER_HANDLE_BYTES)
+        self._check(self.lib.vkc_peer_export(self.h, int(ptr), buf))
+        return bytes(buf.raw)
+
+    def peer_open(self, handle):
+        p = C.c_void_p()
+        self._check(self.lib.vkc_peer_open(self.h, C.c_char_p(handle), C.byref(p)))
+        return int(p.value)
+
+    def peer_close(self, ptr):
+        self._check(self.lib.vkc_peer_close(self.h, int(ptr)))
 
     def attn_decode_workspace_bytes(self, B, Hq, Hkv, Lmax, D):
         return int(self.lib.vkc_attn_decode_workspace_bytes(B, Hq, Hkv, Lmax, D))

@@ -46,6 +46,29 @@ namespace {
     constexpr float kRescaleThreshold = 8.0f;
     constexpr int   kPParts = 2; // P_t is handed to the MMA issuer in this many column groups (BN / kPParts keys each)
 
+    struct FanOut {
+        int       n_dest;
+        void     *dest[8];
+        unsigned *flag[8];
+        unsigned *state; // [0] blocks that have stored, [1] fan-outs completed
+    };
+    // Called by every thread of a block after its last output store; `total` blocks take part. The stores of all blocks
+    // are ordered before the flag values by the fences around the block counter (the last block to arrive publishes).
+    __device__ __forceinline__ void fanout_signal(const FanOut &f, unsigned total) {
+        __threadfence_system();
+        __syncthreads();
+        if (threadIdx.x == 0 && f.state) {
+            if (atomicAdd(f.state, 1u) == total - 1) {
+                __threadfence_system();
+                f.state[0]       = 0;
+                const unsigned e = f.state[1] + 1;
+                f.state[1]       = e;
+                for (int d = 0; d < f.n_dest; ++d)
+                    if (f.flag[d]) asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f.flag[d]), "r"(e) : "memory");
+            }
+        }
+    }
+
     struct AttnParams {
         void          *O;
         int64_t        os[3];
@@ -65,6 +88,9 @@ namespace {
         // group side by side. The last blocks to start are then the lightest ones (no long tail behind a late heavy tile),
         // while the K/V of the pairs in flight still fit in L2.
         int head_group;
+        // output fan-out (n_dest > 0): every output row goes to dest[0..n_dest) instead of O; when the grid's last block has
+        // stored, flag[d] (a word in destination d's memory) receives this rank's count of completed fan-outs
+        FanOut fan;
     };
     constexpr int kTlTile = 20;
 
@@ -562,8 +588,10 @@ namespace {
                 ptx::tc_fence_after();
                 // a row with no visible key stores NaN like the reference's 0/0
                 float       inv    = (n > 0 && m_used == -INFINITY) ? __int_as_float(0x7fc00000) : 1.0f / l;
-                T          *orow   = (T *) p.O + (int64_t) b * p.os[0] + (int64_t) h * p.os[1] + row * p.os[2];
+                const int64_t ooff  = (int64_t) b * p.os[0] + (int64_t) h * p.os[1] + row * p.os[2];
+                T          *orow   = (T *) p.O + ooff;
                 bool        vec_ok = (p.os[0] % 8 == 0) && (p.os[1] % 8 == 0) && (p.os[2] % 8 == 0) && (((uintptr_t) p.O & 15) == 0);
+                const int   ndest  = p.kv_splits > 1 ? 0 : p.fan.n_dest; // fan-out of final rows only (the launcher checked alignment)
                 if (p.kv_splits > 1) {
                     // partial of this key range: O / l in the storage type (bounded by max |v|, so 16 bits do not overflow),
                     // weight data (m, l) in fp32; a range without a visible key for this row has weight 0
@@ -596,7 +624,11 @@ namespace {
 #pragma unroll
                                 for (int i = 0; i < 4; ++i)
                                     o32[i] = pack2<T>(__uint_as_float(v[g * 8 + 2 * i]) * inv, __uint_as_float(v[g * 8 + 2 * i + 1]) * inv);
-                                *reinterpret_cast<uint4 *>(orow + c * 32 + g * 8) = ov;
+                                if (ndest == 0) {
+                                    *reinterpret_cast<uint4 *>(orow + c * 32 + g * 8) = ov;
+                                } else {
+                                    for (int dd = 0; dd < ndest; ++dd) *reinterpret_cast<uint4 *>((T *) p.fan.dest[dd] + ooff + c * 32 + g * 8) = ov;
+                                }
                             }
                         } else {
 #pragma unroll
@@ -612,37 +644,50 @@ namespace {
         ptx::tc_fence_before();
         __syncthreads();
         if (warp == kWarpMma) ptx::tmem_dealloc(tmem, kTmemCols);
+        if (p.kv_splits == 1 && p.fan.n_dest > 0) fanout_signal(p.fan, gridDim.x * gridDim.y * gridDim.z);
     }
 
     // Merge of the key-range partials of one query row: weights l_s * 2^(m_s - m) over their sum (m_s are in the log2
     // domain the kernel works in); a row without any visible key gets NaN like the reference's 0/0.
     template <typename T, int D>
     __global__ void __launch_bounds__(256) attn_prefill_merge_kernel(const T *__restrict__ part_o, const float *__restrict__ part_ml, T *__restrict__ O,
-                                                                     int64_t B, int64_t Hq, int64_t Sq, int splits, int64_t os0, int64_t os1, int64_t os2) {
+                                                                     int64_t B, int64_t Hq, int64_t Sq, int splits, int64_t os0, int64_t os1, int64_t os2,
+                                                                     const FanOut fan) {
         constexpr int TPRW = D / 8; // threads per row, 8 elements each
         const int64_t gid = (int64_t) blockIdx.x * blockDim.x + threadIdx.x;
         const int64_t row = gid / TPRW, rows = B * Hq * Sq;
         const int     c   = (int) (gid % TPRW) * 8;
         vkc_grid_dep_wait(); // launched with programmatic serialization: the partials are complete only after this
         vkc_grid_dep_launch();
-        if (row >= rows) return;
-        float m = -INFINITY;
-        for (int s = 0; s < splits; ++s) m = fmaxf(m, part_ml[((int64_t) s * rows + row) * 2]);
-        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, wsum = 0.f;
-        for (int s = 0; s < splits; ++s) {
-            const float ms = part_ml[((int64_t) s * rows + row) * 2], ls = part_ml[((int64_t) s * rows + row) * 2 + 1];
-            const float w  = ms == -INFINITY ? 0.f : ls * exp2f(ms - m);
-            wsum += w;
-            const uint4 pv = *reinterpret_cast<const uint4 *>(part_o + ((int64_t) s * rows + row) * D + c);
-            const T    *pt = reinterpret_cast<const T *>(&pv);
+        if (row < rows) {
+            float m = -INFINITY;
+            for (int s = 0; s < splits; ++s) m = fmaxf(m, part_ml[((int64_t) s * rows + row) * 2]);
+            float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, wsum = 0.f;
+            for (int s = 0; s < splits; ++s) {
+                const float ms = part_ml[((int64_t) s * rows + row) * 2], ls = part_ml[((int64_t) s * rows + row) * 2 + 1];
+                const float w  = ms == -INFINITY ? 0.f : ls * exp2f(ms - m);
+                wsum += w;
+                const uint4 pv = *reinterpret_cast<const uint4 *>(part_o + ((int64_t) s * rows + row) * D + c);
+                const T    *pt = reinterpret_cast<const T *>(&pv);
 #pragma unroll
-            for (int i = 0; i < 8; ++i) acc[i] += w * St<T>::ld(pt + i);
+                for (int i = 0; i < 8; ++i) acc[i] += w * St<T>::ld(pt + i);
+            }
+            const float inv = 1.0f / wsum; // 0/0 -> NaN for a row with no visible key
+            const int64_t b = row / (Hq * Sq), h = (row / Sq) % Hq, r = row % Sq;
+            const int64_t ooff = b * os0 + h * os1 + r * os2 + c;
+            if (fan.n_dest == 0) {
+                T *orow = O + ooff;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) St<T>::st(orow + i, acc[i] * inv);
+            } else {
+                uint4 ov; // the launcher checked that every destination takes 16-byte stores
+                T    *ot = reinterpret_cast<T *>(&ov);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) St<T>::st(ot + i, acc[i] * inv);
+                for (int dd = 0; dd < fan.n_dest; ++dd) *reinterpret_cast<uint4 *>((T *) fan.dest[dd] + ooff) = ov;
+            }
         }
-        const float inv = 1.0f / wsum; // 0/0 -> NaN for a row with no visible key
-        const int64_t b = row / (Hq * Sq), h = (row / Sq) % Hq, r = row % Sq;
-        T *orow = O + b * os0 + h * os1 + r * os2 + c;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) St<T>::st(orow + i, acc[i] * inv);
+        if (fan.n_dest > 0) fanout_signal(fan, gridDim.x); // every thread of the block, also the ones past the last row
     }
 
     template <typename T, int D, int QT>
@@ -657,7 +702,7 @@ namespace {
         if (p.kv_splits == 1) return VKC_OK;
         const int64_t threads = B * p.Hq * p.Sq * (D / 8);
         vkc_launch(ctx, attn_prefill_merge_kernel<T, D>, dim3((unsigned) ((threads + 255) / 256)), dim3(256), 0, st, (const T *) p.part_o,
-                   (const float *) p.part_ml, (T *) p.O, B, p.Hq, p.Sq, p.kv_splits, p.os[0], p.os[1], p.os[2]);
+                   (const float *) p.part_ml, (T *) p.O, B, p.Hq, p.Sq, p.kv_splits, p.os[0], p.os[1], p.os[2], p.fan);
         return vkc_post_launch(ctx, "attn_prefill_merge");
     }
     template <typename T, int D>
@@ -670,14 +715,23 @@ namespace {
                 // is long, the key range is also cut in two: the hardware block scheduler balances the finer units better
                 // (352 CTAs of 22 key tiles on 296 slots -> 704 CTAs of 11), at the price of a small merge pass.
                 const int64_t ctas = ((p.Sq + BM - 1) / BM) * p.Hq * B, slots = 2 * (int64_t) ctx->sm_count, ntiles = (p.Skv + BN - 1) / BN;
-                const int64_t rounds1 = (ctas + slots - 1) / slots, rounds2 = (2 * ctas + slots - 1) / slots;
-                if (!p.causal && !p.kv_len && ntiles >= 8 && ctas < 3 * slots && rounds2 < 2 * rounds1) {
+                // Cost of a split factor: rounds over the slots x (key tiles per CTA + about 1.5 tiles of prologue and epilogue),
+                // plus a quarter tile per partial for the merge pass; 44 CTAs of 22 tiles (two heads of a head-sharded encoder)
+                // run as 264 CTAs of 4.
+                if (!p.causal && !p.kv_len && ntiles >= 8 && ctas < 3 * slots) {
+                    int    best = 1;
+                    double best_cost = (double) ((ctas + slots - 1) / slots) * ((double) ntiles + 1.5);
+                    for (int sf = 2; sf <= 8 && ntiles / sf >= 2; ++sf) {
+                        if ((sf - 1) * ((ntiles + sf - 1) / sf) >= ntiles) continue; // the last range would be empty
+                        const double cost = (double) ((sf * ctas + slots - 1) / slots) * ((double) ((ntiles + sf - 1) / sf) + 1.5) + 0.25 * sf;
+                        if (cost < best_cost - 1e-9) best_cost = cost, best = sf;
+                    }
                     const size_t rows = (size_t) B * p.Hq * p.Sq;
-                    const size_t need = 2 * rows * (64 * 2 + 2 * 4) + 256;
-                    if (vkc_ensure_scratch(ctx, need) == VKC_OK) {
-                        p.kv_splits = 2;
+                    const size_t need = (size_t) best * rows * (64 * 2 + 2 * 4) + 256;
+                    if (best > 1 && vkc_ensure_scratch(ctx, need) == VKC_OK) {
+                        p.kv_splits = best;
                         p.part_ml   = (float *) ctx->scratch;
-                        p.part_o    = (char *) ctx->scratch + ((2 * rows * 2 * 4 + 255) & ~(size_t) 255);
+                        p.part_o    = (char *) ctx->scratch + (((size_t) best * rows * 2 * 4 + 255) & ~(size_t) 255);
                     }
                 }
                 return launch_attn_qt<T, 64, 1>(ctx, tq, tk, tv, p, B, st);
@@ -710,7 +764,7 @@ namespace {
 
 int vkc_attn_prefill_tcgen05(vkc_ctx *ctx, const void *Q, const void *K, const void *V, void *O, int64_t B, int64_t Hq, int64_t Hkv, int64_t Sq,
                              int64_t Skv, int64_t D, const int64_t *qs, const int64_t *ks, const int64_t *vs, const int64_t *os, float scale,
-                             int causal, const int32_t *kv_len, int dtype, cudaStream_t st) {
+                             int causal, const int32_t *kv_len, int dtype, const vkc_fanout *fan, cudaStream_t st) {
     if (dtype != VKC_F16 && dtype != VKC_BF16) return vkc_fail(ctx, VKC_ERR_UNSUPPORTED, "attn_prefill_tcgen05: 16-bit storage only");
     if (D != 64 && D != 128) return vkc_fail(ctx, VKC_ERR_UNSUPPORTED, "attn_prefill_tcgen05: head dim must be 64 or 128");
     if (!(scale > 0.f)) return vkc_fail(ctx, VKC_ERR_UNSUPPORTED, "attn_prefill_tcgen05: scale must be positive");
@@ -737,6 +791,19 @@ int vkc_attn_prefill_tcgen05(vkc_ctx *ctx, const void *Q, const void *K, const v
     p.timeline   = ctx->timeline;
     p.kv_splits  = 1;
     p.head_group = causal ? causal_head_group(ctx, B * Hq, Skv, D) : 0;
+    memset(&p.fan, 0, sizeof p.fan);
+    if (fan) {
+        if (fan->n_dest < 1 || fan->n_dest > 8 || !fan->state) return vkc_fail(ctx, VKC_ERR_INVALID, "attn_prefill_fanout: 1..8 destinations and a state buffer are required");
+        if ((os[0] % 8) || (os[1] % 8) || (os[2] % 8)) return vkc_fail(ctx, VKC_ERR_UNSUPPORTED, "attn_prefill_fanout: output strides must be multiples of 16 bytes");
+        p.fan.n_dest = fan->n_dest;
+        p.fan.state  = fan->state;
+        for (int d = 0; d < fan->n_dest; ++d) {
+            if (!fan->dest[d] || ((uintptr_t) fan->dest[d] & 15)) return vkc_fail(ctx, VKC_ERR_INVALID, "attn_prefill_fanout: destination %d is null or not 16-byte aligned", d);
+            p.fan.dest[d] = fan->dest[d];
+            p.fan.flag[d] = fan->flag[d];
+        }
+        p.O = fan->dest[0];
+    }
     p.part_o     = nullptr;
     p.part_ml    = nullptr;
     if (dtype == VKC_F16) return D == 64 ? launch_attn<__half, 64>(ctx, tq, tk, tv, p, B, st) : launch_attn<__half, 128>(ctx, tq, tk, tv, p, B, st);

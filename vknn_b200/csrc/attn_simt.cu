@@ -7,7 +7,7 @@
 
 int vkc_attn_prefill_tcgen05(vkc_ctx *ctx, const void *Q, const void *K, const void *V, void *O, int64_t B, int64_t Hq, int64_t Hkv, int64_t Sq,
                              int64_t Skv, int64_t D, const int64_t *qs, const int64_t *ks, const int64_t *vs, const int64_t *os, float scale,
-                             int causal, const int32_t *kv_len, int dtype, cudaStream_t st);
+                             int causal, const int32_t *kv_len, int dtype, const vkc_fanout *fan, cudaStream_t st);
 
 namespace {
 
@@ -153,7 +153,7 @@ extern "C" int vkc_attn_prefill(vkc_ctx *ctx, const void *Q, const void *K, cons
 
     const bool tc_shape = dtype != VKC_F32 && !mask && (D == 64 || D == 128);
     if (tc_shape && ctx->impl != VKC_IMPL_SIMT) {
-        int rc = vkc_attn_prefill_tcgen05(ctx, Q, K, V, O, B, Hq, Hkv, Sq, Skv, D, p.qs, p.ks, p.vs, p.os, scale, p.causal, kv_len, dtype, st);
+        int rc = vkc_attn_prefill_tcgen05(ctx, Q, K, V, O, B, Hq, Hkv, Sq, Skv, D, p.qs, p.ks, p.vs, p.os, scale, p.causal, kv_len, dtype, nullptr, st);
         if (rc != VKC_ERR_UNSUPPORTED || ctx->impl == VKC_IMPL_TCGEN05) return rc;
     } else if (ctx->impl == VKC_IMPL_TCGEN05) {
         return vkc_fail(ctx, VKC_ERR_UNSUPPORTED, "attn_prefill: the tensor-core kernel needs 16-bit storage, no additive mask and D in {64,128}");
@@ -163,4 +163,28 @@ extern "C" int vkc_attn_prefill(vkc_ctx *ctx, const void *Q, const void *K, cons
         case VKC_F16: return launch_attn_simt<__half>(ctx, Q, K, V, O, p, st);
         default: return launch_attn_simt<__nv_bfloat16>(ctx, Q, K, V, O, p, st);
     }
+}
+
+extern "C" int vkc_attn_prefill_fanout(vkc_ctx *ctx, const void *Q, const void *K, const void *V, int64_t B, int64_t Hq, int64_t Hkv, int64_t Sq,
+                                       int64_t Skv, int64_t D, const int64_t *q_strides, const int64_t *k_strides, const int64_t *v_strides,
+                                       const int64_t *o_strides, float scale, int causal, const int32_t *kv_len, int dtype, const vkc_fanout *fan,
+                                       vkc_stream stream) {
+    if (!ctx) return VKC_ERR_INVALID;
+    VKC_REQUIRE(ctx, fan, "attn_prefill_fanout: null fan-out description");
+    VKC_REQUIRE(ctx, B >= 1 && Hq >= 1 && Hkv >= 1 && Sq >= 1 && Skv >= 1 && D >= 1, "attn_prefill_fanout: bad extents");
+    VKC_REQUIRE(ctx, Hq % Hkv == 0, "attn_prefill_fanout: Hq=%lld is not a multiple of Hkv=%lld", (long long) Hq, (long long) Hkv);
+    VKC_REQUIRE(ctx, Q && K && V, "attn_prefill_fanout: null tensor");
+    VKC_REQUIRE(ctx, Hq <= 65535 && B <= 65535, "attn_prefill_fanout: grid too large");
+    if ((dtype != VKC_F16 && dtype != VKC_BF16) || (D != 64 && D != 128))
+        return vkc_fail(ctx, VKC_ERR_UNSUPPORTED, "attn_prefill_fanout: needs the tensor-core kernel (16-bit storage, D in {64,128})");
+    int64_t       qs[3], ks[3], vs[3], os[3];
+    const int64_t dq[3] = {Hq * Sq * D, Sq * D, D}, dk[3] = {Hkv * Skv * D, Skv * D, D};
+    for (int i = 0; i < 3; ++i) {
+        qs[i] = q_strides ? q_strides[i] : dq[i];
+        ks[i] = k_strides ? k_strides[i] : dk[i];
+        vs[i] = v_strides ? v_strides[i] : dk[i];
+        os[i] = o_strides ? o_strides[i] : dq[i];
+    }
+    return vkc_attn_prefill_tcgen05(ctx, Q, K, V, nullptr, B, Hq, Hkv, Sq, Skv, D, qs, ks, vs, os, scale, causal ? 1 : 0, kv_len, dtype, fan,
+                                    vkc_pick_stream(ctx, stream));
 }

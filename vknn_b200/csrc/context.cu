@@ -127,7 +127,7 @@ int vkc_sync(vkc_ctx *ctx, vkc_stream stream) {
     VKC_CUDA(ctx, cudaMemcpy(&code, ctx->dev_err, sizeof(int), cudaMemcpyDeviceToHost));
     if (code != 0) {
         cudaMemset(ctx->dev_err, 0, sizeof(int));
-        return vkc_fail(ctx, VKC_ERR_DEVICE, "device-side error word %d (1 = bounded wait ran out, 2 = tensor-memory allocation)", code);
+        return vkc_fail(ctx, VKC_ERR_DEVICE, "device-side error word %d (1 = bounded wait ran out, 2 = tensor-memory allocation, 3 = a peer's flag did not arrive)", code);
     }
     return VKC_OK;
 }
@@ -303,3 +303,61 @@ int vkc_timer_stop(vkc_ctx *ctx, vkc_stream stream, float *ms) {
 }
 
 } // extern "C"
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Peer memory: buffers shared between the processes of one node, and the bounded wait on flags that peers write.
+namespace {
+    __global__ void peer_wait_kernel(const uint32_t *flags, int n, uint32_t *expected, int *dev_err) {
+        const uint32_t want = *expected + 1;
+        bool           ok   = true;
+        if ((int) threadIdx.x < n) {
+            const long long t0 = clock64();
+            for (;;) {
+                uint32_t v;
+                asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flags + threadIdx.x) : "memory");
+                if ((int32_t) (v - want) >= 0) break;
+                if (clock64() - t0 > 4000000000LL) { // about two seconds: the peer is not coming
+                    ok = false;
+                    break;
+                }
+                __nanosleep(200);
+            }
+        }
+        if (!ok) atomicExch(dev_err, 3);
+        __syncthreads();
+        if (threadIdx.x == 0) *expected = want;
+    }
+} // namespace
+
+extern "C" int vkc_peer_wait(vkc_ctx *ctx, const uint32_t *flags, int n, uint32_t *expected, vkc_stream stream) {
+    if (!ctx) return VKC_ERR_INVALID;
+    VKC_REQUIRE(ctx, flags && expected && n >= 1 && n <= 32, "peer_wait: 1..32 flags and an expected-count word are required");
+    peer_wait_kernel<<<1, 32, 0, vkc_pick_stream(ctx, stream)>>>(flags, n, expected, ctx->dev_err);
+    return vkc_post_launch(ctx, "peer_wait");
+}
+
+extern "C" int vkc_peer_export(vkc_ctx *ctx, void *dptr, unsigned char *handle) {
+    if (!ctx) return VKC_ERR_INVALID;
+    VKC_REQUIRE(ctx, dptr && handle, "peer_export: null argument");
+    static_assert(sizeof(cudaIpcMemHandle_t) == VKC_PEER_HANDLE_BYTES, "handle size");
+    cudaIpcMemHandle_t h;
+    VKC_CUDA(ctx, cudaIpcGetMemHandle(&h, dptr));
+    memcpy(handle, &h, sizeof h);
+    return VKC_OK;
+}
+
+extern "C" int vkc_peer_open(vkc_ctx *ctx, const unsigned char *handle, void **dptr) {
+    if (!ctx) return VKC_ERR_INVALID;
+    VKC_REQUIRE(ctx, dptr && handle, "peer_open: null argument");
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle, sizeof h);
+    *dptr = nullptr;
+    VKC_CUDA(ctx, cudaIpcOpenMemHandle(dptr, h, cudaIpcMemLazyEnablePeerAccess));
+    return VKC_OK;
+}
+
+extern "C" int vkc_peer_close(vkc_ctx *ctx, void *dptr) {
+    if (!ctx) return VKC_ERR_INVALID;
+    if (dptr) VKC_CUDA(ctx, cudaIpcCloseMemHandle(dptr));
+    return VKC_OK;
+}

@@ -156,6 +156,35 @@ class EncoderLayer:
         c.gemm(buf["f"], w["w2"], y.view(T, d), bias=w["b2"], residual=buf["x1"])
         return y
 
+    def forward_head_sharded_fused(self, x, gather, out=None):
+        """Like forward_head_sharded, without a collective: the attention kernel stores its output tiles straight into every
+        rank's gather buffer (sharding.PeerGather) and publishes a flag; the out-projection reads this rank's buffer after a
+        bounded device-side wait on the flags. Only this library's kernels run, so the whole stack captures into one CUDA graph."""
+        c, w = self.ctx, self.w
+        B, T, d = x.shape
+        assert B == 1 and gather.rows == T and gather.width == d
+        Hl, D = self.Hl, d // self.H
+        dl = Hl * D
+        buf = self._buffers(B, T, x.device)
+        key = ("hsf", T)
+        if key not in self._buf:
+            self._buf[key] = dict(qkv=torch.empty(T, 3, Hl, D, dtype=self.dtype, device=x.device))
+        hs = self._buf[key]
+        x2 = x.view(T, d)
+        y = out if out is not None else torch.empty_like(x)
+        c.layernorm(x2, w["ln1_g"], w["ln1_b"], buf["h"], self.eps)
+        c.gemm(buf["h"], w["wqkv_local"], hs["qkv"].view(T, 3 * dl), bias=w["bqkv_local"])
+        q, k, v = (hs["qkv"][:, i].permute(1, 0, 2).unsqueeze(0) for i in range(3))      # [1,Hl,T,D] views
+        kbuf = gather.next_buffer()
+        # output element (head h, row t, :) of this rank lands at [t, (rank*Hl + h)*D : ...] of every rank's [T, d] buffer
+        c.attn_prefill_fanout(q, k, v, gather.dests(kbuf, self.rank * dl), gather.flags(), gather.state, (T * d, D, d), scale=1.0 / (D ** 0.5))
+        gather.wait()
+        c.gemm(gather.buffers[kbuf], w["wo"], buf["x1"], bias=w["bo"], residual=x2)
+        c.layernorm(buf["x1"], w["ln2_g"], w["ln2_b"], buf["h"], self.eps)
+        c.gemm(buf["h"], w["w1"], buf["f"], bias=w["b1"], epilogue=capi.EPI_BIAS | capi.EPI_GELU_ERF)
+        c.gemm(buf["f"], w["w2"], y.view(T, d), bias=w["b2"], residual=buf["x1"])
+        return y
+
     def flops(self, B, T):
         d, dm, H = self.d, self.dmlp, self.H
         M = B * T
@@ -197,6 +226,22 @@ class EncoderStack:
         for i, layer in enumerate(self.layers):
             cur = layer.forward_head_sharded(cur, group=group, out=bufs[i % 2])
         return cur
+
+    def forward_head_sharded_fused(self, x, gather):
+        """All layers with the attention output fanned out by the attention kernel (no collective). The two gather buffers
+        alternate per layer, so an even number of layers keeps the alternation intact from one forward to the next."""
+        assert len(self.layers) % 2 == 0, "an odd layer count would reuse a gather buffer that a slower rank may still read"
+        cur, bufs = x, self._pingpong(x)
+        for i, layer in enumerate(self.layers):
+            cur = layer.forward_head_sharded_fused(cur, gather, out=bufs[i % 2])
+        return cur
+
+    def capture_head_sharded_fused(self, x, gather):
+        """CUDA graph of forward_head_sharded_fused; needs one eager call on every rank beforehand."""
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            y = self.forward_head_sharded_fused(x, gather)
+        return g, y
 
     def capture(self, x):
         """CUDA graph of forward(x); returns (graph, output tensor). Needs one eager forward beforehand."""

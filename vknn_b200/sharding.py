@@ -40,3 +40,78 @@ def gather_dim(local, dim, n_total, group=None):
     dist.all_gather(out, moved, group=group)
     full = torch.cat([o[: hi - lo] for o, (lo, hi) in zip(out, sizes)], 0)
     return full.movedim(0, dim).contiguous()
+
+
+class _RawCuda:
+    """Zero-copy torch view of a raw device pointer (through __cuda_array_interface__)."""
+
+    def __init__(self, ptr, nbytes):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (int(ptr), False), "version": 2}
+
+
+def tensor_at(ptr, nbytes, dtype, shape, device):
+    import torch
+    return torch.as_tensor(_RawCuda(ptr, nbytes), device=device).view(dtype).view(*shape)
+
+
+class PeerGather:
+    """The gather buffers of a head-sharded encoder, shared between the ranks of one node so that the attention kernel
+    itself can store its output tiles into every rank's buffer (vkc_attn_prefill_fanout) instead of an all-gather after it.
+
+    Every rank allocates one block: two [rows, width] buffers (consecutive fan-outs alternate between them: a rank can be at
+    most one fan-out ahead of a peer that still reads the other buffer) and one 32-bit flag per rank. The blocks are
+    exchanged as 64-byte handles over the process group and mapped into every process; data then moves by plain peer stores
+    over NVLink, and completion by one flag word per (writer, reader) pair. Waiting is bounded on the device
+    (vkc_peer_wait): a rank that never arrives shows up as an error of the next sync, not as a hang."""
+
+    FLAG_BYTES = 256
+
+    def __init__(self, ctx, rows, width, dtype, group=None):
+        import torch
+        import torch.distributed as dist
+        self.ctx, self.rows, self.width, self.dtype = ctx, rows, width, dtype
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        if self.world > 8:
+            raise ValueError("PeerGather covers the GPUs of one node (at most 8 ranks)")
+        esize = torch.empty((), dtype=dtype).element_size()
+        self.buf_bytes = (rows * width * esize + 255) // 256 * 256
+        self.block_bytes = 2 * self.buf_bytes + self.FLAG_BYTES
+        self.device = torch.device("cuda", torch.cuda.current_device())
+        self.local = ctx.raw_alloc(self.block_bytes)
+        tensor_at(self.local, self.block_bytes, torch.uint8, (self.block_bytes,), self.device).zero_()
+        torch.cuda.synchronize()
+        handles = [None] * self.world
+        dist.all_gather_object(handles, ctx.peer_export(self.local), group=group)
+        self.base = [self.local if r == self.rank else ctx.peer_open(handles[r]) for r in range(self.world)]
+        dist.barrier(group=group)  # every block is zeroed and mapped before anyone stores into it
+        self.state = torch.zeros(2, dtype=torch.int32, device=self.device)
+        self.expected = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.calls = 0
+        self.buffers = [tensor_at(self.local + k * self.buf_bytes, rows * width * esize, dtype, (rows, width), self.device) for k in range(2)]
+        self._esize = esize
+
+    def next_buffer(self):
+        """Index of the buffer the next fan-out writes (and the next wait makes readable)."""
+        k = self.calls % 2
+        self.calls += 1
+        return k
+
+    def dests(self, k, col_offset):
+        """Where this rank's columns start in buffer k of every rank."""
+        return [b + k * self.buf_bytes + col_offset * self._esize for b in self.base]
+
+    def flags(self):
+        """The word this rank owns in every rank's flag array."""
+        return [b + 2 * self.buf_bytes + 4 * self.rank for b in self.base]
+
+    def wait(self, stream=None):
+        self.ctx.peer_wait(self.local + 2 * self.buf_bytes, self.world, self.expected, stream=stream)
+
+    def close(self):
+        import torch
+        torch.cuda.synchronize()
+        for r, b in enumerate(self.base):
+            if r != self.rank:
+                self.ctx.peer_close(b)
+        self.ctx.raw_free(self.local)
+        self.base = []

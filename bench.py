@@ -371,6 +371,22 @@ def bench_stack(ctx, cfg, steps, warmup, rank, world):
         res["head_sharded_one_sequence"] = dict(tok_s=T * steps / (t_ms * 1e-3), ms_per_forward=t_ms / steps,
                                                 note="strong scaling of a single sequence: QKV+attention sharded by head, all-gather per layer, "
                                                      "out-projection and MLP replicated (about half of the flops do not shard)")
+        if world <= 8 and L % 2 == 0:
+            # the same without a collective: the attention kernel stores its tiles into every rank's gather buffer over peer
+            # memory and raises a flag; the whole forward is one CUDA graph per rank
+            from vknn_b200.sharding import PeerGather
+            gather = PeerGather(ctx, T, d, torch.float16)
+            stack.forward_head_sharded_fused(xs, gather)
+            ctx.sync()
+            dist.barrier()
+            fgraph, _ = stack.capture_head_sharded_fused(xs, gather)
+            f_ms, _ = timed_loop(lambda i: fgraph.replay(), steps, warmup, world)
+            ctx.sync()
+            res["head_sharded_one_sequence_fused"] = dict(tok_s=T * steps / (f_ms * 1e-3), ms_per_forward=f_ms / steps,
+                                                          note="attention output fanned out by the attention kernel over peer memory "
+                                                               "(no NCCL call in the forward), graph replay")
+            dist.barrier()
+            gather.close()
     return res
 
 

@@ -35,10 +35,11 @@ def _worker(rank, world, port, ret):
         from vknn_b200.encoder import EncoderStack
         from vknn_b200.sharding import PeerGather
         rng = np.random.default_rng(6)
-        stack = EncoderStack(ctx, [encoder_weights(rng, 256, 512, bias_scale=0.01) for _ in range(2)], 8, dtype=torch.float16)
+        x = torch.randn(1, 333, 512, generator=torch.Generator().manual_seed(2)).cuda().half()  # head size 64: the tensor-core kernel
+        stack = EncoderStack(ctx, [encoder_weights(rng, 512, 1024, bias_scale=0.01) for _ in range(2)], 8, dtype=torch.float16)
         ref2 = stack.forward(x).clone()
         stack.shard_heads(rank, world)
-        gather = PeerGather(ctx, 333, 256, torch.float16)
+        gather = PeerGather(ctx, 333, 512, torch.float16)
         got2 = stack.forward_head_sharded_fused(x, gather).clone()
         ctx.sync()
         err = float((got2.float() - ref2.float()).abs().max())

@@ -386,6 +386,20 @@ def bench_stack(ctx, cfg, steps, warmup, rank, world):
                                                           note="attention output fanned out by the attention kernel over peer memory "
                                                                "(no NCCL call in the forward), graph replay")
             dist.barrier()
+            # tokens sharded too (out-projection and MLP on T/world rows per rank): LayerNorm 1 and the attention kernel each
+            # fan their output out to every rank, two flag waits per layer, still no collective call and one graph per rank
+            gh = PeerGather(ctx, T, d, torch.float16)
+            stack.forward_token_sharded(xs, gh, gather)
+            ctx.sync()
+            dist.barrier()
+            tgraph, _ = stack.capture_token_sharded(xs, gh, gather)
+            t2_ms, _ = timed_loop(lambda i: tgraph.replay(), steps, warmup, world)
+            ctx.sync()
+            res["token_and_head_sharded_one_sequence"] = dict(tok_s=T * steps / (t2_ms * 1e-3), ms_per_forward=t2_ms / steps,
+                                                              note="every GEMM, LayerNorm and the attention sharded; the two gathers per layer "
+                                                                   "are stores of the producing kernels over peer memory; output left sharded by rows")
+            dist.barrier()
+            gh.close()
             gather.close()
     return res
 

@@ -141,6 +141,12 @@ VKC_API int vkc_attn_prefill_fanout(vkc_ctx *ctx, const void *Q, const void *K, 
                                     int64_t Skv, int64_t D, const int64_t *q_strides, const int64_t *k_strides, const int64_t *v_strides,
                                     const int64_t *o_strides, float scale, int causal, const int32_t *kv_len, int dtype, const vkc_fanout *fan,
                                     vkc_stream stream);
+/* LayerNorm whose output rows go to every destination of `fan` (same description as above; dest[d] points at the first of
+ * the `rows` rows in destination d): the all-gather of a token-sharded activation done by the kernel that produces it.
+ * Arithmetic of vkc_layernorm (LayerNormCpu::run src/backend/cpu/ops/layernorm.cpp:12-79). Rows must be 16-byte aligned
+ * and at most 8 * 32 * (16 / element size) elements long: VKC_ERR_UNSUPPORTED otherwise. */
+VKC_API int vkc_layernorm_fanout(vkc_ctx *ctx, const void *X, const float *gamma, const float *beta, int64_t rows, int64_t norm, float eps,
+                                 int dtype, const vkc_fanout *fan, vkc_stream stream);
 /* Waits (on the stream, in a one-block kernel) until each of the n flags has reached *expected + 1, then stores that value
  * to *expected (a 32-bit device word, zero-initialised once). The wait is bounded (about two seconds): on expiry the
  * kernel sets the context's device error word, which the next vkc_sync reports as VKC_ERR_DEVICE, and returns, so a

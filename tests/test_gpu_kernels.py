@@ -444,6 +444,29 @@ def test_attention_fanout_stores_and_signals(ctx, H, T, D):
         assert state.tolist() == [0, call]
 
 
+@pytest.mark.parametrize("dt", [torch.float16, torch.float32])
+def test_layernorm_fanout_stores_and_signals(ctx, dt):
+    """vkc_layernorm_fanout: the rows vkc_layernorm produces, stored at a row offset into two destinations, and the flag raised
+    once per call (a grid with idle warps in its last block included)."""
+    g = torch.Generator(device="cuda").manual_seed(9)
+    rows, norm, at = 1003, 1024, 17
+    x = torch.randn(rows, norm, generator=g, device="cuda").to(dt)
+    gamma = torch.randn(norm, generator=g, device="cuda")
+    beta = torch.randn(norm, generator=g, device="cuda")
+    ref = torch.empty_like(x)
+    ctx.layernorm(x, gamma, beta, ref, 1e-6)
+    bufs = [torch.zeros(rows + 40, norm, dtype=dt, device="cuda") for _ in range(2)]
+    flags = torch.zeros(2, dtype=torch.int32, device="cuda")
+    state = torch.zeros(2, dtype=torch.int32, device="cuda")
+    expected = torch.zeros(1, dtype=torch.int32, device="cuda")
+    ctx.layernorm_fanout(x, gamma, beta, [b[at:].data_ptr() for b in bufs], [flags[d:].data_ptr() for d in range(2)], state, 1e-6)
+    ctx.peer_wait(flags.data_ptr(), 2, expected)
+    ctx.sync()
+    for b in bufs:
+        assert torch.equal(b[at:at + rows], ref) and not b[:at].any() and not b[at + rows:].any()
+    assert flags.tolist() == [1, 1] and state.tolist() == [0, 1] and expected.item() == 1
+
+
 def test_peer_wait_runs_out_instead_of_hanging(ctx):
     """A flag that nobody raises: the wait kernel gives up after its limit and the next sync reports a device error; the
     context stays usable."""

@@ -52,6 +52,22 @@ def _worker(rank, world, port, ret):
         err = max(err, float((y.float() - ref2.float()).abs().max()))
         ret["fused%d" % rank] = err
         dist.barrier()
+        # tokens sharded as well: LayerNorm and attention both fan their output out, no collective inside the forward
+        from vknn_b200.sharding import gather_dim
+        gh = PeerGather(ctx, 333, 512, torch.float16)
+        mine = stack.forward_token_sharded(x, gh, gather)
+        ctx.sync()
+        full = gather_dim(mine.clone(), 0, 333)
+        err = float((full.float() - ref2[0].float()).abs().max())
+        dist.barrier()
+        graph, y = stack.capture_token_sharded(x, gh, gather)
+        for _ in range(3):
+            graph.replay()
+        ctx.sync()
+        full = gather_dim(y.clone(), 0, 333)
+        ret["tokens%d" % rank] = max(err, float((full.float() - ref2[0].float()).abs().max()))
+        dist.barrier()
+        gh.close()
         gather.close()
         ctx.close()
     finally:
@@ -69,3 +85,4 @@ def test_head_sharded_layer_matches_single_gpu():
     # same kernels on the same values; only the GEMM tile shapes differ between the sharded and the full QKV projection
     assert all(ret[r] <= 2e-3 for r in range(2)), dict(ret)
     assert all(ret["fused%d" % r] <= 4e-3 for r in range(2)), dict(ret)
+    assert all(ret["tokens%d" % r] <= 4e-3 for r in range(2)), dict(ret)

@@ -72,6 +72,7 @@ def load_library():
     L.vkc_attn_prefill.argtypes = [vp, vp, vp, vp, vp] + [i64] * 6 + [vp, vp, vp, vp, f32, i32, vp, vp, i32, vp]
     L.vkc_attn_prefill_fanout.argtypes = [vp, vp, vp, vp] + [i64] * 6 + [vp, vp, vp, vp, f32, i32, vp, i32, C.POINTER(Fanout), vp]
     L.vkc_peer_wait.argtypes = [vp, vp, i32, vp, vp]
+    L.vkc_layernorm_fanout.argtypes = [vp, vp, vp, vp, i64, i64, f32, i32, C.POINTER(Fanout), vp]
     L.vkc_peer_export.argtypes = [vp, vp, C.c_char_p]
     L.vkc_peer_open.argtypes = [vp, C.c_char_p, C.POINTER(vp)]
     L.vkc_peer_close.argtypes = [vp, vp]
@@ -244,6 +245,23 @@ class Context:
         self._check(self.lib.vkc_attn_prefill_fanout(self.h, Q.data_ptr(), K.data_ptr(), V.data_ptr(), B, Hq, Hkv, Sq, Skv, D, st(Q), st(K), st(V),
                                                      _i64arr(list(o_strides)), float(scale), int(bool(causal)),
                                                      kv_len.data_ptr() if kv_len is not None else None, _dtype_code(Q), C.byref(f), self._stream(stream)))
+
+    def _fanout(self, dests, flags, state):
+        f = Fanout()
+        f.n_dest = len(dests)
+        for i, d in enumerate(dests):
+            f.dest[i] = int(d)
+            f.flag[i] = int(flags[i]) if flags is not None and flags[i] else None
+        f.state = state.data_ptr()
+        return f
+
+    def layernorm_fanout(self, X, gamma, beta, dests, flags, state, eps, stream=None):
+        """LayerNorm of X [rows, norm] whose output rows are stored at each pointer of `dests` (see attn_prefill_fanout)."""
+        rows, norm = X.shape
+        assert X.is_contiguous()
+        f = self._fanout(dests, flags, state)
+        self._check(self.lib.vkc_layernorm_fanout(self.h, X.data_ptr(), gamma.data_ptr(), beta.data_ptr() if beta is not None else None, rows, norm,
+                                                  float(eps), _dtype_code(X), C.byref(f), self._stream(stream)))
 
     def peer_wait(self, flags_ptr, n, expected, stream=None):
         """Stream-ordered bounded wait until each of the n flag words at flags_ptr has reached expected[0] + 1."""

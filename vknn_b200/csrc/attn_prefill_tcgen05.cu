@@ -46,28 +46,8 @@ namespace {
     constexpr float kRescaleThreshold = 8.0f;
     constexpr int   kPParts = 2; // P_t is handed to the MMA issuer in this many column groups (BN / kPParts keys each)
 
-    struct FanOut {
-        int       n_dest;
-        void     *dest[8];
-        unsigned *flag[8];
-        unsigned *state; // [0] blocks that have stored, [1] fan-outs completed
-    };
-    // Called by every thread of a block after its last output store; `total` blocks take part. The stores of all blocks
-    // are ordered before the flag values by the fences around the block counter (the last block to arrive publishes).
-    __device__ __forceinline__ void fanout_signal(const FanOut &f, unsigned total) {
-        __threadfence_system();
-        __syncthreads();
-        if (threadIdx.x == 0 && f.state) {
-            if (atomicAdd(f.state, 1u) == total - 1) {
-                __threadfence_system();
-                f.state[0]       = 0;
-                const unsigned e = f.state[1] + 1;
-                f.state[1]       = e;
-                for (int d = 0; d < f.n_dest; ++d)
-                    if (f.flag[d]) asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f.flag[d]), "r"(e) : "memory");
-            }
-        }
-    }
+    using FanOut = VkcFanDev;
+    __device__ __forceinline__ void fanout_signal(const FanOut &f, unsigned total) { vkc_fanout_signal(f, total); }
 
     struct AttnParams {
         void          *O;
@@ -791,17 +771,9 @@ int vkc_attn_prefill_tcgen05(vkc_ctx *ctx, const void *Q, const void *K, const v
     p.timeline   = ctx->timeline;
     p.kv_splits  = 1;
     p.head_group = causal ? causal_head_group(ctx, B * Hq, Skv, D) : 0;
-    memset(&p.fan, 0, sizeof p.fan);
+    if (int frc = vkc_fan_to_dev(ctx, fan, &p.fan, "attn_prefill_fanout")) return frc;
     if (fan) {
-        if (fan->n_dest < 1 || fan->n_dest > 8 || !fan->state) return vkc_fail(ctx, VKC_ERR_INVALID, "attn_prefill_fanout: 1..8 destinations and a state buffer are required");
         if ((os[0] % 8) || (os[1] % 8) || (os[2] % 8)) return vkc_fail(ctx, VKC_ERR_UNSUPPORTED, "attn_prefill_fanout: output strides must be multiples of 16 bytes");
-        p.fan.n_dest = fan->n_dest;
-        p.fan.state  = fan->state;
-        for (int d = 0; d < fan->n_dest; ++d) {
-            if (!fan->dest[d] || ((uintptr_t) fan->dest[d] & 15)) return vkc_fail(ctx, VKC_ERR_INVALID, "attn_prefill_fanout: destination %d is null or not 16-byte aligned", d);
-            p.fan.dest[d] = fan->dest[d];
-            p.fan.flag[d] = fan->flag[d];
-        }
         p.O = fan->dest[0];
     }
     p.part_o     = nullptr;

@@ -185,3 +185,50 @@ __device__ __forceinline__ float vkc_gelu_erf_fast(float h) {
         case VKC_BF16: { using T = __nv_bfloat16; __VA_ARGS__; } break; \
         default: break;                                    \
     }
+
+// Output fan-out to several GPUs (device-side copy of vkc_fanout): a kernel stores each output row into dest[0..n_dest) and,
+// when the grid's last block has stored, publishes this rank's count of completed fan-outs in flag[d] (a word in
+// destination d's memory).
+struct VkcFanDev {
+    int       n_dest;
+    void     *dest[8];
+    unsigned *flag[8];
+    unsigned *state; // [0] blocks that have stored, [1] fan-outs completed
+};
+#ifdef __CUDACC__
+// Called by every thread of a block after its last output store; `total` blocks take part. The stores of all blocks are
+// ordered before the flag values by the barrier, the fences around the block counter and the release stores (the last block
+// to arrive publishes).
+__device__ __forceinline__ void vkc_fanout_signal(const VkcFanDev &f, unsigned total) {
+    // The block's stores are ordered before thread 0's device-scope fence by the barrier, the blocks' fences before the last
+    // block's system-scope fence by the counter, and that fence before the flag stores (fence + relaxed store = release): causality order is
+    // transitive over the scopes, and only ONE system-scope fence runs per kernel (they serialise GPU-wide: one per block
+    // cost 10 us per kernel).
+    __syncthreads();
+    if (threadIdx.x == 0 && f.state) {
+        __threadfence();
+        if (atomicAdd(f.state, 1u) == total - 1) {
+            __threadfence_system();
+            f.state[0]       = 0;
+            const unsigned e = f.state[1] + 1;
+            f.state[1]       = e;
+            for (int d = 0; d < f.n_dest; ++d)
+                if (f.flag[d]) asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(f.flag[d]), "r"(e) : "memory"); // released by the fence above
+        }
+    }
+}
+#endif
+// Validates a caller's fan-out description (destinations 16-byte aligned) and copies it; returns VKC_OK or fails the context.
+inline int vkc_fan_to_dev(vkc_ctx *ctx, const vkc_fanout *fan, VkcFanDev *out, const char *who) {
+    memset(out, 0, sizeof *out);
+    if (!fan) return VKC_OK;
+    if (fan->n_dest < 1 || fan->n_dest > 8 || !fan->state) return vkc_fail(ctx, VKC_ERR_INVALID, "%s: 1..8 destinations and a state buffer are required", who);
+    out->n_dest = fan->n_dest;
+    out->state  = fan->state;
+    for (int d = 0; d < fan->n_dest; ++d) {
+        if (!fan->dest[d] || ((uintptr_t) fan->dest[d] & 15)) return vkc_fail(ctx, VKC_ERR_INVALID, "%s: destination %d is null or not 16-byte aligned", who, d);
+        out->dest[d] = fan->dest[d];
+        out->flag[d] = fan->flag[d];
+    }
+    return VKC_OK;
+}

@@ -23,15 +23,17 @@ namespace {
     // storage the next row's loads are issued before the current row is reduced (more bytes in flight per SM).
     template <typename T, int CHUNKS>
     __global__ void __launch_bounds__(256, 2) layernorm_kernel(const T *__restrict__ X, const float *__restrict__ gamma,
-                                                               const float *__restrict__ beta, T *__restrict__ Y, int64_t rows, int norm, float eps) {
+                                                               const float *__restrict__ beta, T *__restrict__ Y, int64_t rows, int norm, float eps,
+                                                               const VkcFanDev fan) {
         constexpr int  VN       = Vec16<T>::N;
         constexpr bool PREFETCH = sizeof(T) == 2;
         const int      lane     = threadIdx.x & 31;
         const int64_t  nwarps   = (int64_t) gridDim.x * (blockDim.x >> 5);
         int64_t        row      = (int64_t) blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-        if (row >= rows) return;
+        if (row >= rows && fan.n_dest == 0) return;
         vkc_grid_dep_wait();
         vkc_grid_dep_launch();
+        if (row < rows) {
 
         float g[CHUNKS][VN], bt[CHUNKS][VN];
 #pragma unroll
@@ -98,7 +100,11 @@ namespace {
                         if (beta) o += bt[c][j];
                         St<T>::st(t + j, o);
                     }
-                    *reinterpret_cast<uint4 *>(yr + e) = out;
+                    if (fan.n_dest == 0) {
+                        *reinterpret_cast<uint4 *>(yr + e) = out;
+                    } else { // the row goes to every destination (this GPU's and the peers' buffers)
+                        for (int d = 0; d < fan.n_dest; ++d) *reinterpret_cast<uint4 *>((T *) fan.dest[d] + row * norm + e) = out;
+                    }
                 }
             }
             if (PREFETCH) {
@@ -108,6 +114,8 @@ namespace {
                 load_row(row + nwarps, cur);
             }
         }
+        }
+        if (fan.n_dest > 0) vkc_fanout_signal(fan, gridDim.x); // every thread of the block, warps without a row included
     }
 
     // Any norm / alignment: one warp per row, three passes over global memory (rows stay L1/L2 resident).
@@ -139,16 +147,18 @@ namespace {
     }
 
     template <typename T>
-    int launch_ln(vkc_ctx *ctx, const void *X, const float *gamma, const float *beta, void *Y, int64_t rows, int64_t norm, float eps, cudaStream_t st) {
+    int launch_ln(vkc_ctx *ctx, const void *X, const float *gamma, const float *beta, void *Y, int64_t rows, int64_t norm, float eps, cudaStream_t st,
+                  const VkcFanDev &fan) {
         constexpr int VN      = Vec16<T>::N;
         const int     wpb     = 8; // warps (= rows) per block
         const int64_t blocks  = (rows + wpb - 1) / wpb;
         const int64_t pblocks = std::min<int64_t>(blocks, (int64_t) ctx->sm_count * 2); // persistent warps: two 256-thread blocks per SM
+        if (fan.n_dest > 0) Y = fan.dest[0];
         const bool    aligned = (norm % VN == 0) && (((uintptr_t) X & 15) == 0) && (((uintptr_t) Y & 15) == 0) && (((uintptr_t) gamma & 15) == 0) &&
                                 (!beta || ((uintptr_t) beta & 15) == 0);
         const int64_t chunks  = (norm + 32 * VN - 1) / (32 * VN);
         if (blocks > INT32_MAX) return vkc_fail(ctx, VKC_ERR_UNSUPPORTED, "layernorm: too many rows");
-#define VKC_LN(C) vkc_launch(ctx, layernorm_kernel<T, C>, dim3((unsigned) pblocks), dim3(wpb * 32), 0, st, (const T *) X, gamma, beta, (T *) Y, rows, (int) norm, eps)
+#define VKC_LN(C) vkc_launch(ctx, layernorm_kernel<T, C>, dim3((unsigned) pblocks), dim3(wpb * 32), 0, st, (const T *) X, gamma, beta, (T *) Y, rows, (int) norm, eps, fan)
         if (aligned && chunks <= 8) {
             switch (chunks) {
                 case 1: VKC_LN(1); break;
@@ -160,6 +170,8 @@ namespace {
                 case 7: VKC_LN(7); break;
                 default: VKC_LN(8); break;
             }
+        } else if (fan.n_dest > 0) {
+            return vkc_fail(ctx, VKC_ERR_UNSUPPORTED, "layernorm_fanout: needs 16-byte aligned rows of at most %d elements", 8 * 32 * VN);
         } else {
             vkc_launch(ctx, layernorm_generic_kernel<T>, dim3((unsigned) blocks), dim3(wpb * 32), 0, st, (const T *) X, gamma, beta, (T *) Y, rows, norm, eps);
         }
@@ -177,9 +189,27 @@ extern "C" int vkc_layernorm(vkc_ctx *ctx, const void *X, const float *gamma, co
     if (rows == 0) return VKC_OK;
     VKC_REQUIRE(ctx, X && Y && gamma, "layernorm: null operand");
     cudaStream_t st = vkc_pick_stream(ctx, stream);
+    VkcFanDev    fd;
+    memset(&fd, 0, sizeof fd);
     switch (dtype) {
-        case VKC_F32: return launch_ln<float>(ctx, X, gamma, beta, Y, rows, norm, eps, st);
-        case VKC_F16: return launch_ln<__half>(ctx, X, gamma, beta, Y, rows, norm, eps, st);
-        default: return launch_ln<__nv_bfloat16>(ctx, X, gamma, beta, Y, rows, norm, eps, st);
+        case VKC_F32: return launch_ln<float>(ctx, X, gamma, beta, Y, rows, norm, eps, st, fd);
+        case VKC_F16: return launch_ln<__half>(ctx, X, gamma, beta, Y, rows, norm, eps, st, fd);
+        default: return launch_ln<__nv_bfloat16>(ctx, X, gamma, beta, Y, rows, norm, eps, st, fd);
+    }
+}
+
+extern "C" int vkc_layernorm_fanout(vkc_ctx *ctx, const void *X, const float *gamma, const float *beta, int64_t rows, int64_t norm, float eps,
+                                    int dtype, const vkc_fanout *fan, vkc_stream stream) {
+    if (!ctx) return VKC_ERR_INVALID;
+    VKC_REQUIRE(ctx, rows >= 1 && norm >= 1, "layernorm_fanout: bad extents rows=%lld norm=%lld", (long long) rows, (long long) norm);
+    VKC_REQUIRE(ctx, dtype == VKC_F32 || dtype == VKC_F16 || dtype == VKC_BF16, "layernorm_fanout: bad dtype %d", dtype);
+    VKC_REQUIRE(ctx, X && gamma && fan, "layernorm_fanout: null operand");
+    VkcFanDev fd;
+    if (int rc = vkc_fan_to_dev(ctx, fan, &fd, "layernorm_fanout")) return rc;
+    cudaStream_t st = vkc_pick_stream(ctx, stream);
+    switch (dtype) {
+        case VKC_F32: return launch_ln<float>(ctx, X, gamma, beta, nullptr, rows, norm, eps, st, fd);
+        case VKC_F16: return launch_ln<__half>(ctx, X, gamma, beta, nullptr, rows, norm, eps, st, fd);
+        default: return launch_ln<__nv_bfloat16>(ctx, X, gamma, beta, nullptr, rows, norm, eps, st, fd);
     }
 }

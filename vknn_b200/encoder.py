@@ -185,6 +185,39 @@ class EncoderLayer:
         c.gemm(buf["f"], w["w2"], y.view(T, d), bias=w["b2"], residual=buf["x1"])
         return y
 
+    def forward_token_sharded(self, x_loc, rows, T, gather_h, gather_att, out=None):
+        """One block with EVERYTHING sharded and no collective call: this rank holds rows [rows[0], rows[1]) of the residual
+        stream (x_loc [Tl, d]) and heads [rank*Hl, (rank+1)*Hl). LayerNorm 1 stores its normalised rows into every rank's
+        `gather_h` buffer (each rank's QKV projection needs all tokens for its own heads); the attention kernel stores its
+        heads' output for all tokens into every rank's `gather_att` buffer; out-projection, LayerNorm 2 and the MLP then run on
+        this rank's rows only. Returns the rank's rows of the block output."""
+        c, w = self.ctx, self.w
+        lo, hi = rows
+        Tl, d = x_loc.shape
+        assert Tl == hi - lo
+        Hl, D, dm = self.Hl, d // self.H, self.dmlp
+        dl = Hl * D
+        key = ("ts", T, Tl)
+        if key not in self._buf:
+            mk = lambda *s_: torch.empty(*s_, dtype=self.dtype, device=x_loc.device)  # noqa: E731
+            self._buf[key] = dict(qkv=mk(T, 3, Hl, D), x1=mk(Tl, d), h=mk(Tl, d), f=mk(Tl, dm))
+        b = self._buf[key]
+        y = out if out is not None else torch.empty_like(x_loc)
+        kh = gather_h.next_buffer()
+        c.layernorm_fanout(x_loc, w["ln1_g"], w["ln1_b"], gather_h.dests(kh, lo * d), gather_h.flags(), gather_h.state, self.eps)
+        gather_h.wait()
+        c.gemm(gather_h.buffers[kh], w["wqkv_local"], b["qkv"].view(T, 3 * dl), bias=w["bqkv_local"])
+        q, k, v = (b["qkv"][:, i].permute(1, 0, 2).unsqueeze(0) for i in range(3))
+        ka = gather_att.next_buffer()
+        c.attn_prefill_fanout(q, k, v, gather_att.dests(ka, self.rank * dl), gather_att.flags(), gather_att.state, (T * d, D, d),
+                              scale=1.0 / (D ** 0.5))
+        gather_att.wait()
+        c.gemm(gather_att.buffers[ka][lo:hi], w["wo"], b["x1"], bias=w["bo"], residual=x_loc)
+        c.layernorm(b["x1"], w["ln2_g"], w["ln2_b"], b["h"], self.eps)
+        c.gemm(b["h"], w["w1"], b["f"], bias=w["b1"], epilogue=capi.EPI_BIAS | capi.EPI_GELU_ERF)
+        c.gemm(b["f"], w["w2"], y, bias=w["b2"], residual=b["x1"])
+        return y
+
     def flops(self, B, T):
         d, dm, H = self.d, self.dmlp, self.H
         M = B * T
@@ -235,6 +268,29 @@ class EncoderStack:
         for i, layer in enumerate(self.layers):
             cur = layer.forward_head_sharded_fused(cur, gather, out=bufs[i % 2])
         return cur
+
+    def forward_token_sharded(self, x, gather_h, gather_att):
+        """x [1,T,d] replicated; returns this rank's rows [Tl, d] of the stack output (sharding.shard_range(T, rank, world)).
+        Heads and tokens are both sharded; the two all-gathers per layer are done by the LayerNorm and attention kernels
+        themselves over peer memory. Needs shard_heads() first and an even layer count (the gather buffers alternate)."""
+        from .sharding import shard_range
+        assert len(self.layers) % 2 == 0, "an odd layer count would reuse a gather buffer that a slower rank may still read"
+        T, d = x.shape[1], x.shape[2]
+        rank, world = self.layers[0].rank, self.layers[0].world
+        lo, hi = shard_range(T, rank, world)
+        key = ("ts", T, hi - lo)
+        if key not in self._pp:
+            self._pp[key] = [torch.empty(hi - lo, d, dtype=x.dtype, device=x.device) for _ in range(2)]
+        cur = x.view(T, d)[lo:hi]
+        for i, layer in enumerate(self.layers):
+            cur = layer.forward_token_sharded(cur, (lo, hi), T, gather_h, gather_att, out=self._pp[key][i % 2])
+        return cur
+
+    def capture_token_sharded(self, x, gather_h, gather_att):
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            y = self.forward_token_sharded(x, gather_h, gather_att)
+        return g, y
 
     def capture_head_sharded_fused(self, x, gather):
         """CUDA graph of forward_head_sharded_fused; needs one eager call on every rank beforehand."""

@@ -32,6 +32,7 @@
 // entirely above a query tile's diagonal are skipped for that tile.
 #include <type_traits>
 #include "common.cuh"
+#include <cstdlib>
 #include "ptx.cuh"
 #include "tensormap.cuh"
 
@@ -771,6 +772,9 @@ int vkc_attn_prefill_tcgen05(vkc_ctx *ctx, const void *Q, const void *K, const v
     p.timeline   = ctx->timeline;
     p.kv_splits  = 1;
     p.head_group = causal ? causal_head_group(ctx, B * Hq, Skv, D) : 0;
+    if (const char *e = getenv("VKNN_CAUSAL_ORDER")) { // 0: plain grid order (heaviest query tile first inside each head)
+        if (atoi(e) == 0) p.head_group = 0;
+    }
     if (int frc = vkc_fan_to_dev(ctx, fan, &p.fan, "attn_prefill_fanout")) return frc;
     if (fan) {
         if ((os[0] % 8) || (os[1] % 8) || (os[2] % 8)) return vkc_fail(ctx, VKC_ERR_UNSUPPORTED, "attn_prefill_fanout: output strides must be multiples of 16 bytes");

@@ -77,13 +77,30 @@ class PeerGather:
         self.buf_bytes = (rows * width * esize + 255) // 256 * 256
         self.block_bytes = 2 * self.buf_bytes + self.FLAG_BYTES
         self.device = torch.device("cuda", torch.cuda.current_device())
-        self.local = ctx.raw_alloc(self.block_bytes)
-        tensor_at(self.local, self.block_bytes, torch.uint8, (self.block_bytes,), self.device).zero_()
-        torch.cuda.synchronize()
+        # Every rank takes part in both exchanges whatever happened locally, and all ranks then fail together: a rank that
+        # raised on its own would leave the others waiting in a collective.
+        self.local, self.base, handle, err = None, [], None, None
+        try:
+            self.local = ctx.raw_alloc(self.block_bytes)
+            tensor_at(self.local, self.block_bytes, torch.uint8, (self.block_bytes,), self.device).zero_()
+            torch.cuda.synchronize()
+            handle = ctx.peer_export(self.local)
+        except Exception as e:  # noqa: BLE001
+            err = e
         handles = [None] * self.world
-        dist.all_gather_object(handles, ctx.peer_export(self.local), group=group)
-        self.base = [self.local if r == self.rank else ctx.peer_open(handles[r]) for r in range(self.world)]
-        dist.barrier(group=group)  # every block is zeroed and mapped before anyone stores into it
+        dist.all_gather_object(handles, handle, group=group)
+        if err is None and all(h is not None for h in handles):
+            try:
+                self.base = [self.local if r == self.rank else ctx.peer_open(handles[r]) for r in range(self.world)]
+            except Exception as e:  # noqa: BLE001
+                err = e
+        oks = [None] * self.world
+        dist.all_gather_object(oks, err is None and len(self.base) == self.world, group=group)  # also: every block is zeroed and mapped
+        if not all(oks):
+            if self.local is not None:
+                ctx.raw_free(self.local)
+            raise RuntimeError("PeerGather: sharing the gather buffers failed on rank(s) %s%s"
+                               % ([r for r, ok in enumerate(oks) if not ok], (": %s" % err) if err is not None else ""))
         self.state = torch.zeros(2, dtype=torch.int32, device=self.device)
         self.expected = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.calls = 0

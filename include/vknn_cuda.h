@@ -148,7 +148,7 @@ VKC_API int vkc_attn_prefill_fanout(vkc_ctx *ctx, const void *Q, const void *K, 
 VKC_API int vkc_layernorm_fanout(vkc_ctx *ctx, const void *X, const float *gamma, const float *beta, int64_t rows, int64_t norm, float eps,
                                  int dtype, const vkc_fanout *fan, vkc_stream stream);
 /* Waits (on the stream, in a one-block kernel) until each of the n flags has reached *expected + 1, then stores that value
- * to *expected (a 32-bit device word, zero-initialised once). The wait is bounded (about two seconds): on expiry the
+ * to *expected (a 32-bit device word, zero-initialised once). The wait is bounded (about five seconds): on expiry the
  * kernel sets the context's device error word, which the next vkc_sync reports as VKC_ERR_DEVICE, and returns, so a
  * missing peer never hangs the GPU. */
 VKC_API int vkc_peer_wait(vkc_ctx *ctx, const uint32_t *flags, int n, uint32_t *expected, vkc_stream stream);

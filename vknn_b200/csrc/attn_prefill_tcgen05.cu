@@ -64,11 +64,6 @@ namespace {
         int    kv_splits;
         void  *part_o;  // [kv_splits][B][Hq][Sq][D] storage type
         float *part_ml; // [kv_splits][B][Hq][Sq][2]
-        // causal launch order (0: off). Blocks start in linear grid order, so the grid is re-read as groups of head_group
-        // (batch, head) pairs; inside a group the query tiles run from the heaviest to the lightest with the pairs of the
-        // group side by side. The last blocks to start are then the lightest ones (no long tail behind a late heavy tile),
-        // while the K/V of the pairs in flight still fit in L2.
-        int head_group;
         // output fan-out (n_dest > 0): every output row goes to dest[0..n_dest) instead of O; when the grid's last block has
         // stored, flag[d] (a word in destination d's memory) receives this rank's count of completed fan-outs
         FanOut fan;
@@ -194,17 +189,8 @@ namespace {
                       bOF = bPF + QT * kPParts;
 
         const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-        int       b = blockIdx.z, h = blockIdx.y, bx = (int) blockIdx.x / p.kv_splits;
+        const int b = blockIdx.z, h = blockIdx.y, bx = (int) blockIdx.x / p.kv_splits;
         const int split = (int) blockIdx.x % p.kv_splits, nbx = (int) gridDim.x / p.kv_splits;
-        if (p.head_group > 0) { // kv_splits == 1 here
-            const int pairs = (int) (gridDim.y * gridDim.z), lin = (int) (blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z));
-            const int grp = lin / (p.head_group * nbx), r = lin - grp * p.head_group * nbx; // every group before the last is full
-            const int gsz = min(p.head_group, pairs - grp * p.head_group);
-            const int hb  = grp * p.head_group + r % gsz;
-            bx            = r / gsz;
-            h             = hb % (int) gridDim.y;
-            b             = hb / (int) gridDim.y;
-        }
         const int hk = h / (int) (p.Hq / p.Hkv);
         // heavy (late) query tiles first when causal
         const int     mt = p.causal ? nbx - 1 - bx : bx;
@@ -721,15 +707,6 @@ namespace {
         return launch_attn_qt<T, D, 2>(ctx, tq, tk, tv, p, B, st);
     }
 
-    // (batch, head) pairs whose K and V (all Skv keys) together stay within about half of L2
-    int causal_head_group(const vkc_ctx *ctx, int64_t pairs, int64_t Skv, int64_t D) {
-        const int64_t per_pair = 2 * Skv * D * 2, budget = (int64_t) ctx->l2_bytes / 2;
-        int64_t       g        = budget / (per_pair > 0 ? per_pair : 1);
-        if (g < 1) g = 1;
-        if (g > pairs) g = pairs;
-        return (int) g;
-    }
-
     int make_qkv_map(vkc_ctx *ctx, CUtensorMap *map, int dtype, const void *base, int64_t B, int64_t H, int64_t S, int64_t D, const int64_t *str) {
         // dims innermost first: {D, S, H, B}; element strides {1, str[2], str[1], str[0]}
         uint64_t dims[4] = {(uint64_t) D, (uint64_t) S, (uint64_t) H, (uint64_t) B};
@@ -771,10 +748,6 @@ int vkc_attn_prefill_tcgen05(vkc_ctx *ctx, const void *Q, const void *K, const v
     p.dev_err    = ctx->dev_err;
     p.timeline   = ctx->timeline;
     p.kv_splits  = 1;
-    p.head_group = causal ? causal_head_group(ctx, B * Hq, Skv, D) : 0;
-    if (const char *e = getenv("VKNN_CAUSAL_ORDER")) { // 0: plain grid order (heaviest query tile first inside each head)
-        if (atoi(e) == 0) p.head_group = 0;
-    }
     if (int frc = vkc_fan_to_dev(ctx, fan, &p.fan, "attn_prefill_fanout")) return frc;
     if (fan) {
         if ((os[0] % 8) || (os[1] % 8) || (os[2] % 8)) return vkc_fail(ctx, VKC_ERR_UNSUPPORTED, "attn_prefill_fanout: output strides must be multiples of 16 bytes");

@@ -316,7 +316,7 @@ namespace {
                 uint32_t v;
                 asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flags + threadIdx.x) : "memory");
                 if ((int32_t) (v - want) >= 0) break;
-                if (clock64() - t0 > 4000000000LL) { // about two seconds: the peer is not coming
+                if (clock64() - t0 > 10000000000LL) { // about five seconds: the peer is not coming
                     ok = false;
                     break;
                 }

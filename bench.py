@@ -341,7 +341,9 @@ def bench_encoder(ctx, cfg, steps, warmup, rank, world):
 def bench_stack(ctx, cfg, steps, warmup, rank, world):
     """Config 3: 24 pre-LN blocks, d=1024, 16 heads, MLP 4096, 2738 tokens, batch 1. Weak scaling runs one sequence
     per rank (graph replay); with more than one rank the same stack is also run head-sharded on ONE shared sequence
-    (QKV + attention sharded by head, one NCCL all-gather per layer at the attention output, the rest replicated)."""
+    (QKV + attention sharded by head, one NCCL all-gather per layer at the attention output, the rest replicated), and then
+    twice more without any collective call: with the attention kernel storing its tiles into every rank's gather buffer
+    over peer memory, and with the tokens sharded as well (LayerNorm 1 fans its rows out the same way)."""
     import torch
     from vknn_b200.encoder import EncoderStack
     from vknn_b200.synthetic import encoder_weights

@@ -118,13 +118,10 @@ class EncoderLayer:
     def shard_heads(self, rank, world):
         """Keeps only this rank's heads of the QKV projection (columns of Wqkv / entries of bqkv). Attention then runs
         on H/world heads per rank; the attention output is all-gathered before the replicated out-projection + MLP."""
+        from .sharding import qkv_head_slice
         assert self.H % world == 0
-        H, d = self.H, self.d
-        D, Hl = d // H, H // world
-        wq = self.w["wqkv"].view(d, 3, H, D)[:, :, rank * Hl:(rank + 1) * Hl].reshape(d, 3 * Hl * D).contiguous()
-        bq = self.w["bqkv"].view(3, H, D)[:, rank * Hl:(rank + 1) * Hl].reshape(3 * Hl * D).contiguous()
-        self.w["wqkv_local"], self.w["bqkv_local"] = wq, bq
-        self.rank, self.world, self.Hl = rank, world, Hl
+        self.w["wqkv_local"], self.w["bqkv_local"] = qkv_head_slice(self.w["wqkv"], self.w["bqkv"], self.H, rank, world)
+        self.rank, self.world, self.Hl = rank, world, self.H // world
 
     def forward_head_sharded(self, x, group=None, out=None):
         """x [1,T,d] replicated on every rank. One NCCL all-gather per layer, at the attention-output boundary."""

@@ -42,6 +42,19 @@ def gather_dim(local, dim, n_total, group=None):
     return full.movedim(0, dim).contiguous()
 
 
+def qkv_head_slice(wqkv, bqkv, heads, rank, world):
+    """This rank's heads of a packed QKV projection: Wqkv [d, 3*d] is read as [d, 3, heads, D] and bqkv [3*d] as
+    [3, heads, D]; the slice keeps heads [rank*heads/world, (rank+1)*heads/world) of each of Q, K and V, packed the same way
+    ([d, 3*Hl*D] and [3*Hl*D]). Torch tensors on any device."""
+    if heads % world:
+        raise ValueError("%d heads do not divide over %d ranks" % (heads, world))
+    d = wqkv.shape[0]
+    D, Hl = d // heads, heads // world
+    wq = wqkv.view(d, 3, heads, D)[:, :, rank * Hl:(rank + 1) * Hl].reshape(d, 3 * Hl * D).contiguous()
+    bq = bqkv.view(3, heads, D)[:, rank * Hl:(rank + 1) * Hl].reshape(3 * Hl * D).contiguous()
+    return wq, bq
+
+
 class _RawCuda:
     """Zero-copy torch view of a raw device pointer (through __cuda_array_interface__)."""
 

@@ -52,18 +52,15 @@ enum { VKC_IMPL_AUTO = 0, VKC_IMPL_SIMT = 1, VKC_IMPL_TCGEN05 = 2 };
 VKC_API int         vkc_device_count(int *count);
 VKC_API int         vkc_ctx_create(int device_ordinal, vkc_ctx **out);
 VKC_API int         vkc_ctx_destroy(vkc_ctx *ctx);
+/* Name, SM count and maximum SM clock (MHz) of the context's device: what a measured table has to be keyed by
+ * (the reference keys its caches by the Vulkan device identity, src/backend/vulkan/vk_backend.cpp:445-470). */
+VKC_API int         vkc_device_info(const vkc_ctx *ctx, char *name, size_t name_cap, int *sm_count, int *sm_clock_mhz);
 VKC_API const char *vkc_last_error(const vkc_ctx *ctx);
 VKC_API int         vkc_ctx_set_impl(vkc_ctx *ctx, int impl);
 /* Blocks until `stream` is idle, then reports (and clears) any device-side error word the kernels wrote. */
 VKC_API int vkc_sync(vkc_ctx *ctx, vkc_stream stream);
 /* Number of kernels of this library launched through `ctx` since it was created. */
 VKC_API int64_t vkc_launch_count(const vkc_ctx *ctx);
-
-/* Development aid (no reference counterpart): the first call arms a 64-slot device buffer in which GEMM launches record
- * clock64 stamps of their first CTA (slots 0-8: entry, set-up done, first operands landed, MMAs issued, accumulator
- * ready, epilogue done, exit, split-K partials sent, split-K partials received) and tensor-core prefill launches record two steady-state key tiles of their first CTA
- * (slots 0-31); a later call with host64 != NULL copies the 64 slots of the last launch back. */
-VKC_API int vkc_debug_timeline(vkc_ctx *ctx, long long *host64);
 
 /* ---- memory and boundary transfers. Reference: boundary pack/unpack of a device segment, host fp32 <->
  * device storage precision, src/backend/vulkan/vk_backend.cpp:558-696,1324-1382; weight upload helpers
@@ -148,9 +145,10 @@ VKC_API int vkc_attn_prefill_fanout(vkc_ctx *ctx, const void *Q, const void *K, 
 VKC_API int vkc_layernorm_fanout(vkc_ctx *ctx, const void *X, const float *gamma, const float *beta, int64_t rows, int64_t norm, float eps,
                                  int dtype, const vkc_fanout *fan, vkc_stream stream);
 /* Waits (on the stream, in a one-block kernel) until each of the n flags has reached *expected + 1, then stores that value
- * to *expected (a 32-bit device word, zero-initialised once). The wait is bounded (about five seconds): on expiry the
- * kernel sets the context's device error word, which the next vkc_sync reports as VKC_ERR_DEVICE, and returns, so a
- * missing peer never hangs the GPU. */
+ * to *expected (a 32-bit device word, zero-initialised once). The wait is bounded (about two seconds): on expiry the
+ * kernel sets the context's device error word, which the next vkc_sync reports as VKC_ERR_DEVICE, leaves *expected as it
+ * was and returns, so a missing peer never hangs the GPU. While the error word is set, later waits on the same context
+ * return at once without polling (a captured forward with dozens of waits does not spend the limit dozens of times). */
 VKC_API int vkc_peer_wait(vkc_ctx *ctx, const uint32_t *flags, int n, uint32_t *expected, vkc_stream stream);
 /* Sharing a vkc_alloc'ed buffer with the other processes of the node: export gives 64 opaque bytes to hand to a peer
  * process (any transport), open maps that buffer into this process (peer access over NVLink), close unmaps it. */
@@ -176,11 +174,13 @@ VKC_API int    vkc_attn_decode(vkc_ctx *ctx, const void *Q, const void *Kc, cons
  * cudaMalloc is forbidden or would stall the device (allocation synchronises). This entry point does the same
  * work as vkc_attn_decode but keeps the per-split partial results in a fixed area compiled into the library
  * (vkc_attn_decode_noalloc_max_bytes() = 16 MiB, resident on every GPU that loads the library until the process
- * ends) and performs no cudaMalloc / cudaFree or any other allocating call. The caller still passes Q, the cache
- * and O. Shapes whose partials need more than the fixed area (B*Hq*ceil(Lmax/chunk)*(D+2)*4 bytes, see
- * vkc_attn_decode_workspace_bytes) are refused with VKC_ERR_INVALID and a message; nothing is launched.
+ * ends) and calls no cudaMalloc / cudaFree or any other allocating routine. The caller still passes Q, the cache
+ * and O. Shapes whose partials need more than the fixed area (the figure vkc_attn_decode_workspace_bytes returns
+ * for the shape) are refused with VKC_ERR_INVALID and a message; nothing is launched.
  * The first call on a device resolves the area's device address (cudaGetSymbolAddress, with that device made
- * current for the lookup); make that first call before starting any stream capture. All calls on a device share
+ * current for the lookup); under CUDA's lazy module loading that is also when the driver places the library's code
+ * and the area itself on the device, so make that first call at start-up and before any stream capture: only
+ * calls after it are free of driver-side allocation. All calls on a device share
  * the one area and it keeps whatever the last call left there: nothing in it needs clearing between calls, but
  * two calls that run concurrently on the same GPU (different streams or contexts) race on it. ---- */
 VKC_API size_t vkc_attn_decode_noalloc_max_bytes(void);

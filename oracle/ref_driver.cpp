@@ -11,13 +11,15 @@
 //
 //   tensor <name> <input|init|inter|output> <f32|i64> <rank> <d0> <d1> ...
 //   node <OpType> <name> subop=<int> in=<a,b,c> out=<y> [fusedbias=<name>] [i:<k>=<int>] [f:<k>=<float>]
-//        [ints:<k>=<a,b,c>] [floats:<k>=<a,b,c>]
+//        [ints:<k>=<a,b,c>] [floats:<k>=<a,b,c>] [s:<k>=<string without blanks>]
 //
 // Tensor payloads of inputs and initializers are raw little-endian values concatenated in spec order
 // in <data.bin>; outputs are written concatenated in graph-output order to <out.bin> as fp32.
 //
 // usage: vknn_ref_driver <spec.txt> <data.bin> <out.bin> [--backend cpu|cuda] [--precision low|high]
-//                        [--iters N] [--warmup W] [--quiet] [--vxm-fp16 <file.vxm>]
+//                        [--iters N] [--warmup W] [--quiet] [--vxm-fp16 <file.vxm>] [--device N] [--profile]
+// --device N selects the CUDA device through the plug-in's spare Config::hints slot; --profile turns Config::profile on and
+// adds the Session profiler's records of the last run to the JSON line.
 // --vxm-fp16 takes the route of the reference's model compiler (convert/compile.cpp:36-96): run the standard
 // passes, store every fp32 initializer as fp16, write the ".vxm" file, and create the Session from that file
 // (Session::createFromVxm, include/vknn/session_class.h:24), so the backend sees fp16 weights.
@@ -73,6 +75,7 @@ namespace {
             {"Squeeze", OpType::Squeeze},     {"Unsqueeze", OpType::Unsqueeze},
             {"Reduce", OpType::Reduce},       {"Where", OpType::Where},         {"Equal", OpType::Equal},
             {"Greater", OpType::Greater},     {"GreaterEqual", OpType::GreaterEqual}, {"ScatterND", OpType::ScatterND},
+            {"Einsum", OpType::Einsum},
         };
         auto it = m.find(n);
         if (it == m.end()) {
@@ -103,6 +106,8 @@ int main(int argc, char **argv) {
     std::string vxmPath;
     bool        deviceIo = false;
     std::string cacheFile, tuning;
+    int         device  = -1;
+    bool        profile = false;
     for (int i = 4; i < argc; ++i) {
         std::string a = argv[i];
         if (a == "--backend" && i + 1 < argc) backend = argv[++i];
@@ -114,6 +119,8 @@ int main(int argc, char **argv) {
         else if (a == "--device-io") deviceIo = true;
         else if (a == "--cache-file" && i + 1 < argc) cacheFile = argv[++i];
         else if (a == "--tuning" && i + 1 < argc) tuning = argv[++i];
+        else if (a == "--device" && i + 1 < argc) device = std::atoi(argv[++i]);
+        else if (a == "--profile") profile = true;
     }
 
     std::ifstream spec(specPath);
@@ -204,6 +211,11 @@ int main(int argc, char **argv) {
                     a.kind = Attr::Ints;
                     for (auto &s : splitc(v, ',')) a.ints.push_back(std::atoll(s.c_str()));
                     n.attr.map[k.substr(5)] = a;
+                } else if (k.rfind("s:", 0) == 0) {
+                    Attr a;
+                    a.kind = Attr::String;
+                    a.str  = v;
+                    n.attr.map[k.substr(2)] = a;
                 } else if (k.rfind("floats:", 0) == 0) {
                     Attr a;
                     a.kind = Attr::Floats;
@@ -228,6 +240,8 @@ int main(int argc, char **argv) {
         cfg.backend  = BackendKind::Cpu;
         cfg.fallback = {};
     }
+    if (device >= 0) cfg.setHint(static_cast<Hint>(8), device + 1); // the CUDA plug-in's device slot: ordinal + 1, 0 = unset
+    cfg.profile   = profile;
     cfg.cacheFile = cacheFile; // empty: no cache file (the default of a session built from an in-memory graph)
     if (!tuning.empty()) cfg.setHint(Hint::Tuning, tuning == "off" ? Mode::NoTune : tuning == "thorough" ? Mode::Thorough : Mode::Fast);
     cfg.applyLogLevel();
@@ -272,7 +286,7 @@ int main(int argc, char **argv) {
     std::vector<int>    outHandle;
     std::vector<int64_t> outElems;
     if (deviceIo) {
-        if (backend != "cuda" || vkc_ctx_create(0, &ioCtx) != VKC_OK) {
+        if (backend != "cuda" || vkc_ctx_create(device >= 0 ? device : 0, &ioCtx) != VKC_OK) {
             std::printf("{\"ok\": false, \"error\": \"--device-io needs the cuda backend and a device\"}\n");
             return 1;
         }
@@ -370,6 +384,12 @@ int main(int argc, char **argv) {
     for (size_t i = 0; i < nodes.size(); ++i) {
         js << (i ? ", " : "") << "[\"" << opTypeName(nodes[i].type) << "\", " << (i < nb.size() ? (int) nb[i] : -1) << ", " << nodes[i].subOp
            << ", " << (nodes[i].fusedBias != kNoTensor ? 1 : 0) << "]";
+    }
+    js << "], \"profile\": [";
+    {
+        const auto &recs = sess->profiler().records();
+        for (size_t i = 0; i < recs.size(); ++i)
+            js << (i ? ", " : "") << "[\"" << recs[i].name << "\", \"" << opTypeName(recs[i].type) << "\", \"" << recs[i].backend << "\", " << recs[i].gpuMs << "]";
     }
     js << "], \"outputs\": [";
     for (size_t i = 0; i < outs.size(); ++i) {

@@ -30,13 +30,23 @@ _i64p = C.POINTER(C.c_int64)
 _i32p = C.POINTER(C.c_int32)
 
 
+def reference_dir():
+    """Where the reference tree lies: $VKNN_REFERENCE_DIR, else a `reference` folder beside the repository. None when
+    neither holds the engine's sources (then oracle/_ref is used as prebuilt)."""
+    for cand in (os.environ.get("VKNN_REFERENCE_DIR"), os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")):
+        if cand and os.path.exists(os.path.join(cand, "src", "core", "session.cpp")):
+            return cand
+    return None
+
+
 def build():
     """Compile the C restatement (and, where the reference sources are present, oracle/_ref)."""
     subprocess.check_call(["make", "-s", "-C", HERE, "oracle"])
-    subprocess.check_call(["make", "-s", "-C", HERE, "ref"])
+    ref = ["REF=" + reference_dir()] if reference_dir() else []
+    subprocess.check_call(["make", "-s", "-C", HERE, "ref"] + ref)
     # the same driver linked with the CUDA plug-in (the GPU plug-in tests run it); needs the built kernel library
     if os.path.exists(os.path.join(HERE, "..", "vknn_b200", "libvknn_cuda.so")):
-        subprocess.check_call(["make", "-s", "-C", HERE, "ref-cuda"])
+        subprocess.check_call(["make", "-s", "-C", HERE, "ref-cuda"] + ref)
 
 
 def lib():
@@ -260,7 +270,9 @@ class RefGraph:
         if fusedbias:
             s += " fusedbias=%s" % fusedbias
         for k, v in attrs.items():
-            if isinstance(v, float):
+            if isinstance(v, str):
+                s += " s:%s=%s" % (k, v.replace(" ", ""))
+            elif isinstance(v, float):
                 s += " f:%s=%r" % (k, v)
             elif isinstance(v, int):
                 s += " i:%s=%d" % (k, v)
@@ -270,7 +282,8 @@ class RefGraph:
                 s += " ints:%s=%s" % (k, ",".join(str(int(x)) for x in v))
         self.lines.append(s)
 
-    def run(self, backend="cpu", precision="high", iters=1, warmup=0, timeout=3600, vxm_fp16=False, device_io=False, cache_file=None, tuning=None):
+    def run(self, backend="cpu", precision="high", iters=1, warmup=0, timeout=3600, vxm_fp16=False, device_io=False, cache_file=None, tuning=None,
+            device=None, profile=False):
         exe = REF_DRIVER_CUDA if backend == "cuda" else REF_DRIVER
         if not os.path.exists(exe):
             raise FileNotFoundError(exe)
@@ -290,6 +303,10 @@ class RefGraph:
                 cmd += ["--cache-file", cache_file]
             if tuning:  # Hint::Tuning: off | fast | thorough
                 cmd += ["--tuning", tuning]
+            if device is not None:  # CUDA device ordinal (cuda driver only)
+                cmd += ["--device", str(int(device))]
+            if profile:  # Config::profile: the JSON line then carries the Session profiler's records
+                cmd += ["--profile"]
             r = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout)
             info = None
             for ln in r.stdout.splitlines():
@@ -501,4 +518,31 @@ def token_lookup_graph(x, table, pos, keep, upd, scat_idx, mask):
     g.node("Gather", "select2d", ["x", "keep2d"], ["picked2d"], axis=-2)
     g.node("ScatterND", "writeback", ["xr", "scat_idx", "upd"], ["scattered"])
     g.node("Where", "choose", ["mask", "x", "xr"], ["chosen"])
+    return g
+
+
+def rope_table_graph(x, pos, inv_freq):
+    """Rotary position embedding with its frequency table built in the graph, as the exported encoder does it (one outer
+    product per table): freqs = Einsum("i,j->ij", pos, inv_freq) -> Concat(freqs, freqs) -> Cos / Sin -> x * cos +
+    rotate_half(x) * sin. x [B,T,d]; pos [T] positions (a run-time input); inv_freq [d/2] constant. Outputs: the frequency
+    table [T,d/2], and the rotated tokens [B,T,d]."""
+    B, T, d = x.shape
+    g = RefGraph()
+    g.input("x", x)
+    g.input("pos", pos)
+    g.init("inv_freq", inv_freq)
+    for n in ("emb", "cos", "sin", "x1", "x2", "nx2", "rot", "xc", "rs"):
+        g.inter(n)
+    g.output("freqs", (T, d // 2))
+    g.output("roped", (B, T, d))
+    g.node("Einsum", "freq_table", ["pos", "inv_freq"], ["freqs"], equation="i,j->ij")
+    g.node("Concat", "both_halves", ["freqs", "freqs"], ["emb"], axis=1)
+    g.node("Unary", "cos", ["emb"], ["cos"], subop=16)
+    g.node("Unary", "sin", ["emb"], ["sin"], subop=17)
+    g.node("Split", "halves", ["x"], ["x1", "x2"], axis=2)
+    g.node("Unary", "neg", ["x2"], ["nx2"], subop=7)
+    g.node("Concat", "rotate_half", ["nx2", "x1"], ["rot"], axis=2)
+    g.node("Binary", "x_cos", ["x", "cos"], ["xc"], subop=0)
+    g.node("Binary", "rot_sin", ["rot", "sin"], ["rs"], subop=0)
+    g.node("Add", "rope", ["xc", "rs"], ["roped"])
     return g

@@ -32,4 +32,6 @@ def main(ref_root):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        sys.exit("usage: make_raster_golden.py <path of the reference tree>")
+    main(sys.argv[1])

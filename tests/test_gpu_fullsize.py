@@ -6,7 +6,7 @@ import torch
 
 import vknn_b200
 from oracle import vko
-from tests.util import assert_low, metrics
+from tests.util import assert_low, assert_storage, metrics
 
 pytestmark = pytest.mark.gpu
 
@@ -57,6 +57,49 @@ def test_prefill_config4_s16384_properties(ctx):
     assert_low(o[0, 0, rows].float().cpu().numpy(), ref[0, 0], "oracle rows at S=16384")
 
 
+def test_prefill_config4_s8192_oracle_rows(ctx):
+    """The benchmark's headline shape (config 4 at seq 8192: batch 4 x 16 heads, head_dim 128, bf16), without and with the
+    causal mask, against the oracle on 18 query rows of each of three (batch, head) units: the first and last rows of the
+    sequence, both sides of the 128-row tile edges and of the 256-row edge between two CTAs, and rows inside tiles. The
+    oracle computes row slices in seconds (all 8192 keys per row); for the causal case the slice's mask is passed as the
+    additive -inf tensor the reference's graph would carry."""
+    B, H, S, D = 4, 16, 8192, 128
+    g = torch.Generator(device="cuda").manual_seed(1005)
+    q, k, v = (torch.randn(B, H, S, D, generator=g, device="cuda").bfloat16() for _ in range(3))
+    o = torch.empty_like(q)
+    scale = D ** -0.5
+    rows = [0, 1, 63, 127, 128, 129, 255, 256, 257, 1000, 4095, 4096, 4097, 7935, 7936, 8063, 8064, 8191]
+    units = [(0, 0), (1, 7), (3, 15)]
+    for causal in (False, True):
+        ctx.attn_prefill(q, k, v, o, scale, causal=causal)
+        ctx.sync()
+        mask = None
+        if causal:
+            mask = np.zeros((len(rows), S), np.float32)
+            for i, r in enumerate(rows):
+                mask[i, r + 1:] = -np.inf
+        for b, h in units:
+            qh = q[b, h, rows].float().cpu().numpy()[None, None]
+            ref = vko.attention(qh, k[b, h].float().cpu().numpy()[None, None], v[b, h].float().cpu().numpy()[None, None], scale, mask=mask)
+            assert_low(o[b, h, rows].float().cpu().numpy(), ref[0, 0], "config 4, S=8192, causal=%s, unit %s" % (causal, (b, h)))
+
+
+def test_encoder_layer_config2_batch8_full_images(ctx):
+    """Config 2 at its named batch (8 images x 197 tokens, d=768, 12 heads, MLP 3072, fp16): the layer runs on the whole
+    batch and the first and last image are compared with the oracle's block on that image alone (images are independent, so
+    a per-image oracle run is the full-size answer for that image)."""
+    from vknn_b200.encoder import EncoderLayer
+    from vknn_b200.synthetic import encoder_weights
+    rng = np.random.default_rng(1002)
+    w = encoder_weights(rng, 768, 3072)
+    x = rng.standard_normal((8, 197, 768)).astype(np.float32).astype(np.float16).astype(np.float32)
+    y = EncoderLayer(ctx, w, 12, dtype=torch.float16).forward(torch.from_numpy(x).cuda().half())
+    ctx.sync()
+    for img in (0, 7):
+        ref = vko.encoder_layer(x[img:img + 1], w, 12, eps=1e-6)
+        assert_storage(y[img:img + 1].float().cpu().numpy(), ref, "f16", "config 2, image %d of 8" % img, ulps=3)
+
+
 def test_decode_config5_full_size_properties(ctx):
     """Config 5 at full size (batch 32, 32 q / 8 kv heads, cache 8192, valid lengths 1024..8192): constant V gives the
     constant; the tensor-core and SIMT forms agree; the oracle agrees on the two shortest sequences."""
@@ -100,9 +143,10 @@ def test_encoder_stack_config3_width_two_layers(ctx):
         ref = vko.encoder_layer(ref, w, 16, eps=1e-6)
     y = EncoderStack(ctx, ws, 16).forward(torch.from_numpy(x).cuda().half())
     ctx.sync()
-    m = metrics(y.float().cpu().numpy(), ref)
-    # activations grow to O(10) over the residual stream; the storage rounding of fp16 at that magnitude is 8e-3
-    assert m["cosine"] >= 0.9999 and m["max_abs"] <= 4e-2, m
+    # The residual stream grows to O(10), where one fp16 ulp is 7.8e-3, and the 14 kernels of the two blocks each round
+    # their output to fp16 where the reference keeps fp32: the chain is held to 6 ulps of the rounded oracle output and to
+    # the stated 1e-2 wherever |y| <= 2.
+    assert_storage(y.float().cpu().numpy(), ref, "f16", "two blocks at config-3 width", ulps=6)
 
 
 def test_empty_and_degenerate_inputs(ctx):

@@ -234,3 +234,91 @@ def test_tuning_table_from_another_device_is_ignored(tmp_path):
     assert_low(got, ref, "encoder layer with a foreign tuning table")
     lines = table.read_text().splitlines()
     assert lines[1] != "some-other-gpu/configs=3" and len(lines) >= 2 + 4
+
+
+@pytest.mark.parametrize("precision", ["low", "high"])
+def test_rope_frequency_table_einsum_runs_on_the_cuda_backend(precision):
+    """Einsum "i,j->ij" (the rotary frequency tables of the exported encoder; the passes do not lower it) with the Cos / Sin /
+    rotation around it plans on the CUDA backend with no CPU backend active and matches the reference CPU backend. Positions
+    and inverse frequencies are exactly representable in fp16 and their products stay below 2048, so the table itself is
+    compared at storage precision."""
+    rng = np.random.default_rng(34)
+    B, T, d = 2, 74, 64
+    x = rng.standard_normal((B, T, d)).astype(np.float16).astype(np.float32)
+    pos = np.arange(T, dtype=np.float32)
+    inv_freq = (2.0 ** -np.arange(d // 2, dtype=np.float32) * 4).astype(np.float32)  # powers of two: exact in fp16
+    graph = lambda: vko.rope_table_graph(x, pos, inv_freq)
+    ref, info_cpu = graph().run(backend="cpu")
+    got, info = graph().run(backend="cuda", precision=precision, iters=2)
+    assert "Einsum" in [n[0] for n in info["nodes"]]
+    assert all(n[1] == CUDA_KIND for n in info["nodes"]), info["nodes"]
+    assert got[0].shape == ref[0].shape == (T, d // 2)
+    if precision == "high":
+        assert np.array_equal(got[0], ref[0])
+        assert_high(got[1], ref[1], "rope through the plug-in, fp32")
+    else:
+        normal = ref[0] >= 2.0 ** -14  # below that fp16 is subnormal
+        assert np.array_equal(got[0][normal], ref[0][normal])
+        # sin / cos of an argument stored in fp16 differ from fp32 by up to the argument's rounding (ulp/2 of values up to 292)
+        small = np.broadcast_to(np.concatenate([ref[0], ref[0]], axis=1) <= 8.0, ref[1].shape)
+        assert np.abs(got[1] - ref[1])[small].max() <= 1e-2
+
+
+def test_profiler_gets_one_record_per_launch():
+    """Config::profile: the Session's profiler receives a record per kernel launch of the CUDA segment, tagged with the node
+    it was planned for and a device time, like the per-node records of the reference's own backends."""
+    rng = np.random.default_rng(35)
+    w = encoder_weights(rng, 256, 512, bias_scale=0.01)
+    x = rng.standard_normal((2, 130, 256)).astype(np.float32)
+    (ref,), _ = vko.encoder_layer_graph(x, w, 4).run(backend="cpu")
+    (got,), info = vko.encoder_layer_graph(x, w, 4).run(backend="cuda", precision="low", iters=2, profile=True)
+    assert_low(got, ref, "profiled encoder layer")
+    recs = info["profile"]
+    assert len(recs) == 7, recs  # LayerNorm, QKV GEMM, attention, out-projection, LayerNorm, fc1 + GELU, fc2 + residual
+    assert all(r[2] == "CUDA" and r[3] >= 0 for r in recs), recs
+    assert [r[1] for r in recs] == ["LayerNorm", "MatMul", "MatMul", "MatMul", "LayerNorm", "MatMul", "MatMul"], recs
+
+
+def test_runtime_gather_over_a_long_axis_is_left_to_another_backend():
+    """An index tensor computed at run time lives in the segment's storage type; fp16 holds integers exactly only up to 2048,
+    so with fp16 storage a Gather over a longer axis is declined at plan time (no CPU backend is active here: the plan
+    fails) instead of fetching wrong rows. With fp32 storage the same graph runs."""
+    rng = np.random.default_rng(36)
+    P, T, d = 2738, 40, 8
+    table = rng.standard_normal((P, d)).astype(np.float32)
+    pos = rng.integers(2049, P, size=T).astype(np.float32)
+
+    def graph():
+        g = vko.RefGraph()
+        g.input("pos", pos)
+        g.input("x", np.ones((T, d), np.float32))
+        g.init("table", table)
+        g.inter("rows")
+        g.output("y", (T, d))
+        g.node("Gather", "lookup", ["table", "pos"], ["rows"], axis=0)
+        g.node("Binary", "use", ["x", "rows"], ["y"], subop=0)
+        return g
+
+    with pytest.raises(RuntimeError) as e:
+        graph().run(backend="cuda", precision="low")
+    assert "plan" in str(e.value)
+    (got,), _ = graph().run(backend="cuda", precision="high")
+    assert np.array_equal(got, table[pos.astype(np.int64)])
+
+
+def test_device_ordinal_from_the_config():
+    """The plug-in takes its device from a spare Config::hints slot: the same graph gives the same result on every visible
+    GPU, and an ordinal that does not exist is refused when the session is planned."""
+    import torch
+    rng = np.random.default_rng(37)
+    q, k, v = (rng.standard_normal((1, 4, 150, 64)).astype(np.float32) for _ in range(3))
+    outs = []
+    for dev_i in range(min(torch.cuda.device_count(), 2)):
+        (got,), _ = vko.attention_graph(q, k, v, 0.125).run(backend="cuda", precision="low", device=dev_i)
+        outs.append(got)
+    (ref,), _ = vko.attention_graph(q, k, v, 0.125).run(backend="cpu")
+    for got in outs:
+        assert_low(got, ref, "attention on a chosen device")
+        assert np.array_equal(got, outs[0])
+    with pytest.raises(RuntimeError):
+        vko.attention_graph(q, k, v, 0.125).run(backend="cuda", precision="low", device=torch.cuda.device_count())

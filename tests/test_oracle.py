@@ -212,3 +212,22 @@ def test_token_lookup_graph_matches_numpy():
     np.testing.assert_array_equal(outs[1], x[:, np.array([[0, -1, 2], [T - 1, 1, 0]])])
     np.testing.assert_array_equal(outs[2], want_sc)
     np.testing.assert_array_equal(outs[3], np.where(mask[None] != 0, x, xr))
+
+
+def test_rope_table_graph_matches_numpy():
+    """The rotary frequency table as the exported encoder builds it (Einsum "i,j->ij", then Concat / Cos / Sin and the
+    rotation), run by the reference CPU backend, against plain numpy (reference arithmetic: src/backend/cpu/ops/einsum.cpp:33-44)."""
+    if not os.path.exists(vko.REF_DRIVER):
+        pytest.skip("reference driver not built")
+    rng = np.random.default_rng(33)
+    B, T, d = 2, 11, 16
+    x = rng.standard_normal((B, T, d)).astype(np.float32)
+    pos = np.arange(T, dtype=np.float32)
+    inv_freq = (1.0 / (100.0 ** (np.arange(0, d, 2, dtype=np.float32) / d))).astype(np.float32)
+    (freqs, roped), info = vko.rope_table_graph(x, pos, inv_freq).run(backend="cpu")
+    assert "Einsum" in [n[0] for n in info["nodes"]]  # the outer product is not lowered to MatMul by the passes
+    want = pos[:, None] * inv_freq[None, :]
+    np.testing.assert_array_equal(freqs, want)
+    emb = np.concatenate([want, want], axis=1)
+    rot = np.concatenate([-x[..., d // 2:], x[..., :d // 2]], axis=-1)
+    np.testing.assert_allclose(roped, x * np.cos(emb) + rot * np.sin(emb), rtol=0, atol=2e-6)

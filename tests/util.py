@@ -32,6 +32,38 @@ def assert_low(got, ref, what=""):
     return m
 
 
+MANT_BITS = {"f16": 10, "bf16": 7}
+
+
+def assert_storage(got, ref, dt, what="", ulps=1):
+    """The 16-bit storage rule for kernels whose output is O(1) or larger (GEMM, LayerNorm, chained blocks), where half an
+    ulp of the storage type alone can exceed 1e-2 (bf16 at |y| >= 2.56, f16 at |y| >= 20.5):
+      * cosine >= 0.9999;
+      * against the oracle output ROUNDED to the storage type, every element is within `ulps` units in the last place of
+        that type, the ulp taken at max(|y|, 1/4) (below 1/4 cancellation noise of the fp32 sums outweighs the spacing);
+      * wherever |y| <= 2 the difference from the UNROUNDED oracle output is <= 1e-2 (the stated tolerance, which half an
+        ulp cannot break in that range).
+    `ulps` is 1 for a single kernel; chained blocks, which store every intermediate in 16 bits where the reference keeps
+    fp32, state their own count."""
+    import torch
+    tdt = {"f16": torch.float16, "bf16": torch.bfloat16}[dt]
+    got = np.asarray(got, dtype=np.float32)
+    ref = np.asarray(ref, dtype=np.float32)
+    m = metrics(got, ref)
+    assert m["nan"] == 0 and m["cosine"] >= TOL_LOW["cosine"], (what, m)
+    ref_r = round_to(ref, tdt)
+    mag = np.maximum(np.abs(ref_r), 0.25).astype(np.float64)
+    ulp = np.exp2(np.floor(np.log2(mag)) - MANT_BITS[dt])
+    worst = float((np.abs(got.astype(np.float64) - ref_r) / ulp).max())
+    assert worst <= ulps + 1e-6, (what, "ulps off the rounded oracle output", worst, m)
+    small = np.abs(ref) <= 2.0
+    if small.any():
+        d = float(np.abs(got[small] - ref[small]).max())
+        assert d <= TOL_LOW["max_abs"], (what, "max|d| where |y| <= 2", d, m)
+    m["ulps"] = worst
+    return m
+
+
 def assert_high(got, ref, what=""):
     m = metrics(got, ref)
     scale = float(np.abs(np.asarray(ref)).max()) + 1e-30

@@ -27,11 +27,13 @@
 #include "vknn/binary_type.h"
 #include "vknn/error.h"
 #include "vknn/logging.h"
+#include "vknn/profiler.h"
 #include "vknn/unary_type.h"
 #include "vknn_cuda.h"
 
 #include <algorithm>
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 #include <fstream>
 #include <sstream>
@@ -53,6 +55,11 @@ namespace vknn {
     namespace {
 
         constexpr BackendKind kCuda = static_cast<BackendKind>(2); // first value after Vulkan = 0, Cpu = 1
+        // Device selection travels in a spare slot of Config::hints (include/vknn/config_struct.h:74-88; the reference's
+        // Hint enum ends at 4, include/vknn/hint.h:9-15): cfg.setHint(static_cast<Hint>(8), ordinal + 1). 0 (the production
+        // default of every hint) means "not set": then the environment variable VKNN_CUDA_DEVICE, else device 0. One
+        // Session drives one device; a multi-GPU application creates one Session per device (per thread or process).
+        constexpr int kHintCudaDevice = 8;
 
         [[noreturn]] void fail(Status s, const std::string &msg) { throw Error(s, "CUDA backend: " + msg); }
 
@@ -122,6 +129,7 @@ namespace vknn {
             std::vector<const void *> operands;
             int64_t                   inOffset = 0;
             std::string               label;
+            int                       node = -1; // graph node this launch was planned for (profiler records)
         };
 
         bool isScalarInit(const Graph &g, TensorId id, float *value) {
@@ -193,16 +201,34 @@ namespace vknn {
     class CudaBackend: public Backend {
       public:
         CudaBackend() {
-            int n = 0;
-            if (vkc_device_count(&n) == VKC_OK && n > 0 && vkc_ctx_create(0, &ctx_) != VKC_OK) ctx_ = nullptr;
+            // The context is created in configure(), which knows the device the Config asks for; available() is asked
+            // before that (src/core/session.cpp:340-348) and only needs to know that a usable GPU exists.
+            if (vkc_device_count(&deviceCount_) != VKC_OK) deviceCount_ = 0;
         }
         ~CudaBackend() override {
             if (ctx_) vkc_ctx_destroy(ctx_);
         }
         BackendKind kind() const override { return kCuda; }
         const char *name() const override { return "CUDA"; }
-        bool        available() const override { return ctx_ != nullptr; }
-        void        configure(const Config &cfg) override { precision_ = cfg.precision; }
+        bool        available() const override { return deviceCount_ > 0; }
+        void        configure(const Config &cfg) override {
+            precision_ = cfg.precision;
+            int want   = cfg.hint(static_cast<Hint>(kHintCudaDevice), 0) - 1;
+            if (want < 0) {
+                const char *e = std::getenv("VKNN_CUDA_DEVICE");
+                want          = e ? std::atoi(e) : 0;
+            }
+            if (ctx_ && want == device_) return;
+            if (want < 0 || want >= deviceCount_) fail(Status::InvalidArgument, "device ordinal " + std::to_string(want) + " does not exist (" + std::to_string(deviceCount_) + " visible)");
+            if (ctx_) vkc_ctx_destroy(ctx_);
+            ctx_ = nullptr;
+            if (vkc_ctx_create(want, &ctx_) != VKC_OK) {
+                ctx_ = nullptr;
+                fail(Status::RuntimeError, "device " + std::to_string(want) + " is not a usable sm_100 GPU");
+            }
+            device_ = want;
+        }
+        int device() const { return device_; }
 
         bool supports(OpType t, DType dt) const override {
             if (dt != DType::Float32 && dt != DType::Float16) return false;
@@ -230,6 +256,7 @@ namespace vknn {
                 case OpType::Reduce:
                 case OpType::Where:
                 case OpType::ScatterND:
+                case OpType::Einsum:
                 case OpType::Equal:
                 case OpType::Greater:
                 case OpType::GreaterEqual: return true;
@@ -262,12 +289,33 @@ namespace vknn {
                     const TensorDesc &d = g.desc(nd.inputs[1]);
                     if (g.desc(nd.inputs[0]).dtype == DType::Int64) return false;
                     if (g.isInitializer(nd.inputs[1])) return d.dtype == DType::Int64 && prod(d.shape) >= 1;
-                    return d.dtype == DType::Float32 || d.dtype == DType::Float16;
+                    if (d.dtype != DType::Float32 && d.dtype != DType::Float16) return false;
+                    // The index tensor lives in the segment's storage type. The reference casts from fp32
+                    // (gather.cpp:27-30); f16 storage holds integers exactly only up to 2048, so a longer axis would
+                    // fetch wrong rows silently: leave such a node to another backend.
+                    const Shape &ds   = g.desc(nd.inputs[0]).shape;
+                    int64_t      axis = nd.attr.geti("axis", 0);
+                    if (axis < 0) axis += (int64_t) ds.size();
+                    if (axis < 0 || axis >= (int64_t) ds.size()) return false;
+                    return precision_ == Precision::High ? ds[(size_t) axis] <= (1 << 24) : ds[(size_t) axis] <= 2048;
+                }
+                case OpType::Einsum: {
+                    // only the outer product (the rotary frequency tables); the two batched equations arrive as MatMul
+                    // (src/import/lower_einsum.cpp:36-110)
+                    std::string eq;
+                    for (char c : nd.attr.gets("equation", ""))
+                        if (c != ' ' && c != '\t') eq += c;
+                    if (eq != "i,j->ij" || nd.inputs.size() != 2) return false;
+                    for (TensorId in : nd.inputs)
+                        if (g.desc(in).dtype != DType::Float32 && g.desc(in).dtype != DType::Float16) return false;
+                    return true;
                 }
                 case OpType::ScatterND: {
                     // constant int64 indices: destinations (and which duplicate wins) are resolved at plan time
                     if (nd.inputs.size() != 3 || !g.isInitializer(nd.inputs[1]) || g.desc(nd.inputs[1]).dtype != DType::Int64) return false;
                     const TensorDesc &dd = g.desc(nd.inputs[0]), &ud = g.desc(nd.inputs[2]);
+                    // int64 data is shape arithmetic: its consumers (Reshape / Expand / Slice parameters) need constants at
+                    // plan time, so such a node is of no use on a device; it stays with the backend that owns the host tensors
                     if (dd.dtype == DType::Int64 || ud.dtype == DType::Int64 || dd.shape.empty()) return false;
                     const Shape &is = g.desc(nd.inputs[1]).shape;
                     return !is.empty() && is.back() >= 1 && is.back() <= (int64_t) dd.shape.size();
@@ -355,7 +403,7 @@ namespace vknn {
         }
 
         std::unique_ptr<Segment> compileSegment(const std::vector<int> &nodeIdx, Graph &g, const Config &cfg) override {
-            if (!ctx_) fail(Status::RuntimeError, "no usable sm_100 device");
+            if (!ctx_) configure(cfg);
             return std::unique_ptr<Segment>(new CudaSegment(this, ctx_, nodeIdx, g, cfg));
         }
 
@@ -401,14 +449,19 @@ namespace vknn {
             tuneDirty_ = false;
         }
         std::string gpuTag() const {
-            int n = 0;
-            vkc_device_count(&n);
-            return "sm_100a/configs=" + std::to_string(vkc_gemm_config_count());
+            char name[128] = "unknown";
+            int  sms = 0, mhz = 0;
+            if (ctx_) vkc_device_info(ctx_, name, sizeof name, &sms, &mhz);
+            std::string tag = name;
+            for (char &c : tag)
+                if (c == ' ') c = '_';
+            return tag + "/sms=" + std::to_string(sms) + "/mhz=" + std::to_string(mhz) + "/configs=" + std::to_string(vkc_gemm_config_count());
         }
 
       private:
-        vkc_ctx  *ctx_       = nullptr;
-        Precision precision_ = Precision::Low;
+        vkc_ctx  *ctx_         = nullptr;
+        int       deviceCount_ = 0, device_ = -1;
+        Precision precision_   = Precision::Low;
         std::map<std::string, int> tune_;
         std::string                tuneFile_;
         bool                       tuneLoaded_ = false, tuneDirty_ = false;
@@ -910,7 +963,17 @@ namespace vknn {
         std::set<int> done;
         for (size_t pos = 0; pos < nodeIdx.size(); ++pos) {
             if (done.count((int) pos)) continue;
-            const Node &n = g.nodes[nodeIdx[pos]];
+            const Node  &n      = g.nodes[nodeIdx[pos]];
+            const size_t first_ = steps_.size();
+            struct TagSteps { // every launch planned for this node carries its index, for the profiler records
+                std::vector<Step> &st;
+                size_t             from;
+                int                node;
+                ~TagSteps() {
+                    for (size_t i = from; i < st.size(); ++i)
+                        if (st[i].node < 0) st[i].node = node;
+                }
+            } tag_ {steps_, first_, nodeIdx[pos]};
             switch (n.type) {
                 case OpType::Reshape:
                 case OpType::Squeeze:
@@ -1170,6 +1233,28 @@ namespace vknn {
                     }
                     break;
                 }
+                case OpType::Einsum: {
+                    // "i,j->ij" (src/backend/cpu/ops/einsum.cpp:33-44): y[i,j] = a[i] * b[j]. a is read through a stride-0
+                    // column axis and written out once at [I,J]; b joins as a broadcast operand of a one-step Mul program.
+                    View a = materialize(views_.at(n.inputs[0]), "einsum a"), b = materialize(views_.at(n.inputs[1]), "einsum b");
+                    const int64_t I = prod(a.shape), J = prod(b.shape);
+                    View          e = a;
+                    e.shape   = {I, J};
+                    e.strides = {1, 0};
+                    View x = materialize(e, "einsum a rows");
+                    View y = newTensor(n.outputs[0], Shape {I, J});
+                    Step s;
+                    s.kind      = Step::Pointwise;
+                    s.shape     = {I, J};
+                    s.operands  = {ptrOf(b)};
+                    s.opStrides = {0, 1};
+                    s.pwSteps   = {0, (int) BinaryType::Mul, 1, 0};
+                    s.pwParams  = {0.f, 0.f};
+                    s.a = ptrOf(x), s.d = ptrOf(y);
+                    s.label = "einsum(outer)";
+                    steps_.push_back(s);
+                    break;
+                }
                 case OpType::Conv: planPatchConv(n); break;
                 case OpType::MatMul:
                     if (!tryAttention(pos, done)) planMatMul(pos, done);
@@ -1361,7 +1446,26 @@ namespace vknn {
             if (rt.elems() != prod(v.shape)) fail(Status::InvalidArgument, "boundary input " + g.desc(id).name + " has an unexpected size");
             check(ctx_, vkc_upload(ctx_, ptrOf(v), dtype_, rt.host.bytes.data(), VKC_F32, rt.elems(), nullptr), "vkc_upload");
         }
-        if (graph_) {
+        if (ctx.profiler && ctx.profiler->enabled()) {
+            // Profiled run: launches go out one by one between device timers and every launch leaves an OpRecord under the
+            // node it was planned for (the counterpart of the per-node records of src/backend/cpu/cpu_backend.cpp:133-142 and
+            // the timestamp records of src/backend/vulkan/vk_backend.cpp:1436-1457). Nodes folded into a neighbour's launch
+            // (views, fused attention, GEMM epilogues) have no record of their own.
+            for (const Step &s : steps_) {
+                float ms = -1.f;
+                check(ctx_, vkc_timer_start(ctx_, nullptr), "vkc_timer_start");
+                launch(s);
+                check(ctx_, vkc_timer_stop(ctx_, nullptr, &ms), "vkc_timer_stop");
+                OpRecord r;
+                r.name     = (s.node >= 0 ? g.nodes[(size_t) s.node].name : std::string()) + " [" + s.label + "]";
+                r.type     = s.node >= 0 ? g.nodes[(size_t) s.node].type : OpType::Unknown;
+                r.backend  = "CUDA";
+                r.cpuMs    = ms;
+                r.gpuMs    = ms;
+                r.fellBack = false;
+                ctx.profiler->add(r);
+            }
+        } else if (graph_) {
             check(ctx_, vkc_graph_launch(ctx_, graph_), "vkc_graph_launch");
         } else if (useGraph_ && runs_ == 1) {
             // the eager first run sized every scratch buffer; record the launch list once and replay it from now on

@@ -51,13 +51,13 @@ def load_library():
     L.vkc_device_count.argtypes = [C.POINTER(C.c_int)]
     L.vkc_ctx_create.argtypes = [i32, C.POINTER(vp)]
     L.vkc_ctx_destroy.argtypes = [vp]
+    L.vkc_device_info.argtypes = [vp, C.c_char_p, sz, C.POINTER(C.c_int), C.POINTER(C.c_int)]
     L.vkc_last_error.argtypes = [vp]
     L.vkc_last_error.restype = C.c_char_p
     L.vkc_ctx_set_impl.argtypes = [vp, i32]
     L.vkc_sync.argtypes = [vp, vp]
     L.vkc_launch_count.argtypes = [vp]
     L.vkc_launch_count.restype = i64
-    L.vkc_debug_timeline.argtypes = [vp, C.POINTER(C.c_longlong)]
     L.vkc_extbuf_register.argtypes = [vp, C.c_size_t, C.POINTER(C.c_int)]
     L.vkc_extbuf_unregister.argtypes = [C.c_int]
     L.vkc_extbuf_lookup.argtypes = [C.c_int, C.POINTER(vp), C.POINTER(C.c_size_t)]
@@ -165,6 +165,13 @@ class Context:
         # torch's default stream is the legacy NULL stream; NULL means "the context's own stream" in the C-ABI,
         # so name the legacy stream by its explicit handle (cudaStreamLegacy == 0x1) to keep torch ordering.
         return C.c_void_p(h if h else 1)
+
+    def device_info(self):
+        """(name, SM count, maximum SM clock in MHz) of the context's device."""
+        name = C.create_string_buffer(128)
+        sms, mhz = C.c_int(0), C.c_int(0)
+        self._check(self.lib.vkc_device_info(self.h, name, 128, C.byref(sms), C.byref(mhz)))
+        return name.value.decode(), sms.value, mhz.value
 
     def set_impl(self, impl):
         self._check(self.lib.vkc_ctx_set_impl(self.h, impl))

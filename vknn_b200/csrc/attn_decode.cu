@@ -10,6 +10,7 @@
 //
 // Algorithmic bytes per call: sum_b 2 * Hkv * kv_len[b] * D * sizeof(T)  (+ Q and O).
 #include "common.cuh"
+#include <mutex>
 
 int vkc_attn_decode_tcgen05(vkc_ctx *ctx, const void *Q, const void *Kc, const void *Vc, int64_t B, int64_t Hq, int64_t Hkv, int64_t Lmax, int64_t D,
                             const int32_t *kv_len, float scale, float *part_ml, float *part_o, int chunk, int parts_stride, int dtype, cudaStream_t st);
@@ -298,7 +299,8 @@ namespace {
 constexpr size_t kStaticScratchBytes = (size_t) 16 << 20;
 static __device__ __align__(256) unsigned char g_decode_static_scratch[kStaticScratchBytes];
 constexpr int kMaxDevices = 64;
-static void *g_decode_static_ptr[kMaxDevices] = {nullptr};
+static void      *g_decode_static_ptr[kMaxDevices] = {nullptr};
+static std::mutex g_decode_static_mu; // guards the one-time address lookup (host threads may make their first calls together)
 
 extern "C" size_t vkc_attn_decode_workspace_bytes(int64_t B, int64_t Hq, int64_t Hkv, int64_t Lmax, int64_t D) {
     if (B <= 0 || Hq <= 0 || Hkv <= 0 || Lmax <= 0 || D <= 0) return 0;
@@ -321,14 +323,14 @@ extern "C" int vkc_attn_decode(vkc_ctx *ctx, const void *Q, const void *Kc, cons
     VKC_REQUIRE(ctx, !(((uintptr_t) Q | (uintptr_t) Kc | (uintptr_t) Vc) & 15), "attn_decode: Q/K/V must be 16-byte aligned");
     const size_t need = vkc_attn_decode_workspace_bytes(B, Hq, Hkv, Lmax, D);
     float       *ws   = (float *) workspace;
+    cudaStream_t st = vkc_pick_stream(ctx, stream);
     if (!ws) {
-        int rc = vkc_ensure_scratch(ctx, need);
+        int rc = vkc_ensure_scratch(ctx, need, st);
         if (rc) return rc;
         ws = (float *) ctx->scratch;
     } else {
         VKC_REQUIRE(ctx, workspace_bytes >= need, "attn_decode: workspace of %zu bytes is smaller than the %zu required", workspace_bytes, need);
     }
-    cudaStream_t st = vkc_pick_stream(ctx, stream);
 #define VKC_DEC_T(T)                                                                                         \
     (D == 64 ? launch_decode<T, 1>(ctx, Q, Kc, Vc, O, B, Hq, Hkv, Lmax, kv_len, scale, ws, st)                \
              : D == 128 ? launch_decode<T, 2>(ctx, Q, Kc, Vc, O, B, Hq, Hkv, Lmax, kv_len, scale, ws, st)     \
@@ -350,8 +352,15 @@ extern "C" int vkc_attn_decode_noalloc(vkc_ctx *ctx, const void *Q, const void *
                         "attn_decode_noalloc: this shape needs %zu bytes of partial-result scratch, more than the fixed %zu-byte area; "
                         "use vkc_attn_decode with a caller workspace instead",
                         need, kStaticScratchBytes);
-    if (!g_decode_static_ptr[ctx->device]) {
-        // one-time set-up for this device: resolve the device address of the file-scope array
+    void *area = nullptr;
+    {
+        std::lock_guard<std::mutex> lk(g_decode_static_mu);
+        area = g_decode_static_ptr[ctx->device];
+    }
+    if (!area) {
+        // one-time set-up for this device: resolve the device address of the file-scope array. With lazy module loading this
+        // is also the moment the driver places the library's code and the array itself on the device.
+        std::lock_guard<std::mutex> lk(g_decode_static_mu);
         int cur = -1;
         VKC_CUDA(ctx, cudaGetDevice(&cur));
         if (cur != ctx->device) VKC_CUDA(ctx, cudaSetDevice(ctx->device));
@@ -360,9 +369,10 @@ extern "C" int vkc_attn_decode_noalloc(vkc_ctx *ctx, const void *Q, const void *
         if (cur != ctx->device) cudaSetDevice(cur);
         if (e != cudaSuccess || !ptr) return vkc_fail(ctx, VKC_ERR_CUDA, "cudaGetSymbolAddress(decode scratch): %s", cudaGetErrorString(e));
         g_decode_static_ptr[ctx->device] = ptr;
+        area                             = ptr;
     }
     // Nothing in the area has to start at zero: the split kernel writes every (row, split) partial that the merge
     // kernel reads for this call, and stale contents beyond them are never read.
-    return vkc_attn_decode(ctx, Q, Kc, Vc, O, B, Hq, Hkv, Lmax, D, kv_len, scale, g_decode_static_ptr[ctx->device], kStaticScratchBytes, dtype,
+    return vkc_attn_decode(ctx, Q, Kc, Vc, O, B, Hq, Hkv, Lmax, D, kv_len, scale, area, kStaticScratchBytes, dtype,
                            stream);
 }

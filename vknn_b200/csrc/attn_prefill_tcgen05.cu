@@ -58,7 +58,6 @@ namespace {
         int            causal;
         const int32_t *kv_len;
         int           *dev_err;
-        long long     *timeline; // optional clock64 stamps of CTA (0,0,0): key tiles kTlTile and kTlTile + 1
         // key-range splitting (shallow grids): CTA blockIdx.x % kv_splits handles its share of the key tiles and leaves a
         // partial per row — the normalised output in the storage type and (running maximum, row sum) — for the merge kernel
         int    kv_splits;
@@ -68,7 +67,6 @@ namespace {
         // stored, flag[d] (a word in destination d's memory) receives this rank's count of completed fan-outs
         FanOut fan;
     };
-    constexpr int kTlTile = 20;
 
     template <int D, int KS, int VS, int QT> struct Smem {
         static constexpr uint32_t Q_BYTES  = BM * D * 2; // per query tile
@@ -285,7 +283,6 @@ namespace {
                 const uint64_t dQ0 = ptx::smem_desc_sw128(sQ, 16, 1024), dQ1 = ptx::smem_desc_sw128(sQ + L::Q_BYTES, 16, 1024);
                 const uint64_t dK0 = ptx::smem_desc_sw128(sK, 16, 1024), dK1 = ptx::smem_desc_sw128(sK + L::KV_BYTES, 16, 1024);
                 const uint64_t dV0 = ptx::smem_desc_sw128(sV, BN * 128, 1024), dV1 = ptx::smem_desc_sw128(sV + L::KV_BYTES, BN * 128, 1024);
-                long long *tlm = (p.timeline && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && leader) ? p.timeline : nullptr;
                 auto wait = [&](int barIdx, uint32_t parity) { return __all_sync(0xffffffffu, ptx::mbar_wait(bar(barIdx), parity, ctl + 1, p.dev_err)); };
                 auto issue_qk = [&](int t, int j) {
                     const uint64_t aq = t ? dQ1 : dQ0, bk = (j & 1) ? dK1 : dK0;
@@ -322,7 +319,6 @@ namespace {
                         if (j < n_t[t]) {
                             ok = wait(bPF + kPParts * t, j & 1);
                             if (!ok) break;
-                            if (tlm && (j == kTlTile || j == kTlTile + 1)) tlm[(j - kTlTile) * 16 + 10 + t * 2] = clock64();
                             ptx::tc_fence_after();
                             issue_pv(t, j, 0);
 #pragma unroll
@@ -339,7 +335,6 @@ namespace {
                                 if (!ok) break;
                                 ptx::tc_fence_after();
                                 issue_qk(t, j + 1);
-                                if (tlm && (j == kTlTile || j == kTlTile + 1)) tlm[(j - kTlTile) * 16 + 11 + t * 2] = clock64();
                             } else if (leader) {
                                 ptx::tc_commit(bar(bOF + t)); // O_t complete
                             }
@@ -364,7 +359,6 @@ namespace {
             const uint32_t tO     = tmem + ((uint32_t) (q * 32) << 16) + kColO + t * D;
             const int64_t  my_lim = p.causal ? row + (p.Skv - p.Sq) : p.Skv; // keys <= my_lim visible
             const int      n      = n_t[t];
-            long long     *tl0    = (p.timeline && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) ? p.timeline : nullptr;
             float          m_used = -INFINITY, l = 0.f;
             bool           ok     = true;
             // One key tile; kMask selects the body that replaces invisible scores by -inf (only the tiles that
@@ -375,14 +369,11 @@ namespace {
                 ok = ptx::mbar_wait(bar(bSF + t), j & 1, ctl + 1, p.dev_err);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) return false;
-                long long *tl = (tl0 && lane == 0 && q == 0 && (j == kTlTile || j == kTlTile + 1)) ? tl0 + (j - kTlTile) * 16 + t * 5 : nullptr;
-                if (tl) tl[0] = clock64();
                 ptx::tc_fence_after();
                 uint32_t s[4][32];
 #pragma unroll
                 for (int c = 0; c < 4; ++c) ptx::tmem_ld_x32(tS + c * 32, s[c]);
                 ptx::tc_wait_ld();
-                if (tl) tl[1] = clock64();
                 if (kMask) {
                     // visible columns of this row in this tile: [0, nvis)
                     int64_t lim = len < my_lim + 1 ? len : my_lim + 1;
@@ -434,7 +425,6 @@ namespace {
                     }
                 }
                 const float neg_m = m_used == -INFINITY ? 0.f : -m_used;
-                if (tl) tl[2] = clock64();
                 const float2 sc2 = make_float2(p.scale_log2, p.scale_log2), nm2 = make_float2(neg_m, neg_m);
                 float2       ls  = make_float2(0.f, 0.f);
                 // P for column group `part` of this row is in TMEM: one arrival per warp on that group's barrier
@@ -536,9 +526,7 @@ namespace {
                     S2(60), S2(61), S2(62), S2(63);
                 }
                 l += ls.x + ls.y;
-                if (tl) tl[3] = clock64();
                 p_ready(kPParts - 1);
-                if (tl) tl[4] = clock64();
                 return true;
             };
             for (int j = 0; j < n; ++j) {
@@ -695,7 +683,7 @@ namespace {
                     }
                     const size_t rows = (size_t) B * p.Hq * p.Sq;
                     const size_t need = (size_t) best * rows * (64 * 2 + 2 * 4) + 256;
-                    if (best > 1 && vkc_ensure_scratch(ctx, need) == VKC_OK) {
+                    if (best > 1 && vkc_ensure_scratch(ctx, need, st) == VKC_OK) {
                         p.kv_splits = best;
                         p.part_ml   = (float *) ctx->scratch;
                         p.part_o    = (char *) ctx->scratch + (((size_t) best * rows * 2 * 4 + 255) & ~(size_t) 255);
@@ -746,7 +734,6 @@ int vkc_attn_prefill_tcgen05(vkc_ctx *ctx, const void *Q, const void *K, const v
     p.causal     = causal;
     p.kv_len     = kv_len;
     p.dev_err    = ctx->dev_err;
-    p.timeline   = ctx->timeline;
     p.kv_splits  = 1;
     if (int frc = vkc_fan_to_dev(ctx, fan, &p.fan, "attn_prefill_fanout")) return frc;
     if (fan) {

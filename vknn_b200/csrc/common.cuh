@@ -10,6 +10,7 @@
 #include <cstring>
 #include <set>
 #include <string>
+#include <vector>
 #include <utility>
 #include <type_traits>
 
@@ -28,8 +29,11 @@ struct vkc_ctx {
     int          impl       = VKC_IMPL_AUTO;
     cudaStream_t stream     = nullptr;
     int         *dev_err    = nullptr; // device word; 0 = ok
-    void        *scratch    = nullptr; // grown on demand: decode partials, upload staging
+    void        *scratch    = nullptr; // grown on demand: decode and prefill partials, boundary staging
     size_t       scratch_sz = 0;
+    std::vector<void *> retired_scratch;      // outgrown blocks, kept until the context is destroyed (graphs may point at them)
+    cudaStream_t scratch_user = nullptr;      // stream of the last launch that used the scratch
+    cudaEvent_t  scratch_ev   = nullptr;
     cudaEvent_t  ev0 = nullptr, ev1 = nullptr;
     int64_t      launches = 0;
     bool         capturing = false;
@@ -37,7 +41,6 @@ struct vkc_ctx {
     std::string  err;
     // driver entry point for tensor-map encoding (resolved once; no link-time dependency on libcuda)
     void *encode_tiled = nullptr;
-    long long *timeline = nullptr; // optional 64-slot device buffer: clock64 stamps of CTA (0,0,0) of the last GEMM or prefill launch
     // kernels whose dynamic shared-memory limit has been raised on this context's device
     std::set<const void *> smem_configured;
 };
@@ -121,7 +124,7 @@ __device__ __forceinline__ void vkc_grid_dep_launch() { asm volatile("griddepcon
 
 inline size_t vkc_dtype_size(int dt) { return dt == VKC_F32 || dt == VKC_I32 ? 4 : 2; }
 
-int vkc_ensure_scratch(vkc_ctx *ctx, size_t bytes);
+int vkc_ensure_scratch(vkc_ctx *ctx, size_t bytes, cudaStream_t st);
 
 // Opt a kernel into more than 48 KB of dynamic shared memory, once per context (the attribute is per device).
 template <typename Kernel> inline int vkc_configure_smem(vkc_ctx *ctx, Kernel kern, int bytes) {

@@ -30,21 +30,43 @@ namespace {
 
 } // namespace
 
-int vkc_ensure_scratch(vkc_ctx *ctx, size_t bytes) {
-    if (bytes <= ctx->scratch_sz) return VKC_OK;
-    if (ctx->capturing) return vkc_fail(ctx, VKC_ERR_INVALID, "context scratch cannot grow during graph capture; run the segment once first");
-    if (ctx->scratch) {
-        VKC_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
-        VKC_CUDA(ctx, cudaFree(ctx->scratch));
-        ctx->scratch    = nullptr;
-        ctx->scratch_sz = 0;
-    }
-    size_t want = (bytes + ((size_t) 1 << 20) - 1) & ~(((size_t) 1 << 20) - 1);
-    if (cudaMalloc(&ctx->scratch, want) != cudaSuccess) {
+// The context's scratch block only ever grows, and a block that has been handed out is never freed before the context is
+// destroyed: its address may be baked into CUDA graphs the caller captured (key-range partials of prefill attention, decode
+// partials, boundary staging), and those graphs must stay replayable after a later, larger call. A block that is outgrown is
+// retired to a list that vkc_ctx_destroy frees. Growth is refused while `st` (or the context's own stream) is being
+// captured, because an allocation is not a capturable operation: run the shape once outside the capture first.
+// All users of the scratch are expected on one stream; when the using stream changes, the new stream is made to wait for
+// everything enqueued so far on the previous one (not possible, and skipped, while either is being captured).
+int vkc_ensure_scratch(vkc_ctx *ctx, size_t bytes, cudaStream_t st) {
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(st, &cap) != cudaSuccess) {
         cudaGetLastError();
-        return vkc_fail(ctx, VKC_ERR_OOM, "scratch allocation of %zu bytes failed", want);
+        cap = cudaStreamCaptureStatusActive; // the stream is in a broken capture: do nothing that could make it worse
     }
-    ctx->scratch_sz = want;
+    const bool capturing = ctx->capturing || cap != cudaStreamCaptureStatusNone;
+    if (bytes > ctx->scratch_sz) {
+        if (capturing)
+            return vkc_fail(ctx, VKC_ERR_INVALID, "context scratch cannot grow to %zu bytes during graph capture; run the shape once outside the capture first", bytes);
+        size_t want = (bytes + ((size_t) 1 << 20) - 1) & ~(((size_t) 1 << 20) - 1);
+        void  *blk  = nullptr;
+        if (cudaMalloc(&blk, want) != cudaSuccess) {
+            cudaGetLastError();
+            return vkc_fail(ctx, VKC_ERR_OOM, "scratch allocation of %zu bytes failed", want);
+        }
+        if (ctx->scratch) ctx->retired_scratch.push_back(ctx->scratch); // still referenced by earlier launches and graphs
+        ctx->scratch    = blk;
+        ctx->scratch_sz = want;
+    }
+    if (ctx->scratch_user && ctx->scratch_user != st && !capturing) {
+        cudaStreamCaptureStatus prev = cudaStreamCaptureStatusNone;
+        if (cudaStreamIsCapturing(ctx->scratch_user, &prev) == cudaSuccess && prev == cudaStreamCaptureStatusNone) {
+            VKC_CUDA(ctx, cudaEventRecord(ctx->scratch_ev, ctx->scratch_user));
+            VKC_CUDA(ctx, cudaStreamWaitEvent(st, ctx->scratch_ev, 0));
+        } else {
+            cudaGetLastError();
+        }
+    }
+    if (!capturing) ctx->scratch_user = st;
     return VKC_OK;
 }
 
@@ -82,7 +104,8 @@ int vkc_ctx_create(int device_ordinal, vkc_ctx **out) {
     ctx->cc_major = prop.major;
     if (cudaSetDevice(device_ordinal) != cudaSuccess || cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking) != cudaSuccess ||
         cudaMalloc(&ctx->dev_err, sizeof(int)) != cudaSuccess || cudaMemset(ctx->dev_err, 0, sizeof(int)) != cudaSuccess ||
-        cudaEventCreate(&ctx->ev0) != cudaSuccess || cudaEventCreate(&ctx->ev1) != cudaSuccess) {
+        cudaEventCreate(&ctx->ev0) != cudaSuccess || cudaEventCreate(&ctx->ev1) != cudaSuccess ||
+        cudaEventCreateWithFlags(&ctx->scratch_ev, cudaEventDisableTiming) != cudaSuccess) {
         delete ctx;
         return VKC_ERR_CUDA;
     }
@@ -101,12 +124,30 @@ int vkc_ctx_destroy(vkc_ctx *ctx) {
     cudaSetDevice(ctx->device);
     if (ctx->stream) cudaStreamSynchronize(ctx->stream);
     if (ctx->scratch) cudaFree(ctx->scratch);
+    for (void *blk : ctx->retired_scratch) cudaFree(blk);
+    if (ctx->scratch_ev) cudaEventDestroy(ctx->scratch_ev);
     if (ctx->dev_err) cudaFree(ctx->dev_err);
-    if (ctx->timeline) cudaFree(ctx->timeline);
     if (ctx->ev0) cudaEventDestroy(ctx->ev0);
     if (ctx->ev1) cudaEventDestroy(ctx->ev1);
     if (ctx->stream) cudaStreamDestroy(ctx->stream);
     delete ctx;
+    return VKC_OK;
+}
+
+int vkc_device_info(const vkc_ctx *ctx, char *name, size_t name_cap, int *sm_count, int *sm_clock_mhz) {
+    if (!ctx) return VKC_ERR_INVALID;
+    cudaDeviceProp prop;
+    if (cudaGetDeviceProperties(&prop, ctx->device) != cudaSuccess) {
+        cudaGetLastError();
+        return VKC_ERR_CUDA;
+    }
+    if (name && name_cap) snprintf(name, name_cap, "%s", prop.name);
+    if (sm_count) *sm_count = prop.multiProcessorCount;
+    if (sm_clock_mhz) {
+        int khz = 0;
+        if (cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, ctx->device) != cudaSuccess) cudaGetLastError();
+        *sm_clock_mhz = khz / 1000;
+    }
     return VKC_OK;
 }
 
@@ -133,17 +174,6 @@ int vkc_sync(vkc_ctx *ctx, vkc_stream stream) {
 }
 
 int64_t vkc_launch_count(const vkc_ctx *ctx) { return ctx ? ctx->launches : 0; }
-
-// Development aid: after this call, GEMM and prefill-attention launches record clock64 stamps of their first CTA; read them back with a second call.
-int vkc_debug_timeline(vkc_ctx *ctx, long long *host64) {
-    if (!ctx) return VKC_ERR_INVALID;
-    if (!ctx->timeline) {
-        VKC_CUDA(ctx, cudaMalloc(&ctx->timeline, 64 * sizeof(long long)));
-        VKC_CUDA(ctx, cudaMemset(ctx->timeline, 0, 64 * sizeof(long long)));
-    }
-    if (host64) VKC_CUDA(ctx, cudaMemcpy(host64, ctx->timeline, 64 * sizeof(long long), cudaMemcpyDeviceToHost));
-    return VKC_OK;
-}
 
 int vkc_alloc(vkc_ctx *ctx, size_t bytes, void **dptr) {
     if (!ctx || !dptr) return VKC_ERR_INVALID;
@@ -222,7 +252,7 @@ int vkc_upload(vkc_ctx *ctx, void *dst_dev, int dst_dtype, const void *src_host,
     }
     // stage in the source type on the device, then convert there (the reference converts on the host)
     size_t bytes = (size_t) n * vkc_dtype_size(src_dtype);
-    int    rc    = vkc_ensure_scratch(ctx, bytes);
+    int    rc    = vkc_ensure_scratch(ctx, bytes, st);
     if (rc) return rc;
     VKC_CUDA(ctx, cudaMemcpyAsync(ctx->scratch, src_host, bytes, cudaMemcpyHostToDevice, st));
     return vkc_convert(ctx, dst_dev, dst_dtype, ctx->scratch, src_dtype, n, stream);
@@ -238,7 +268,7 @@ int vkc_download(vkc_ctx *ctx, void *dst_host, int dst_dtype, const void *src_de
         return VKC_OK;
     }
     size_t bytes = (size_t) n * vkc_dtype_size(dst_dtype);
-    int    rc    = vkc_ensure_scratch(ctx, bytes);
+    int    rc    = vkc_ensure_scratch(ctx, bytes, st);
     if (rc) return rc;
     rc = vkc_convert(ctx, ctx->scratch, dst_dtype, src_dev, src_dtype, n, stream);
     if (rc) return rc;
@@ -307,25 +337,28 @@ int vkc_timer_stop(vkc_ctx *ctx, vkc_stream stream, float *ms) {
 // ---------------------------------------------------------------------------------------------------------------------
 // Peer memory: buffers shared between the processes of one node, and the bounded wait on flags that peers write.
 namespace {
+    // One warp; lane i polls flag i. A context whose device error word is already set (an earlier wait ran out, a peer is gone)
+    // returns at once instead of spinning through its own limit again, and the expected count only advances when every flag
+    // arrived, so that flags and count stay in step for a retry.
     __global__ void peer_wait_kernel(const uint32_t *flags, int n, uint32_t *expected, int *dev_err) {
         const uint32_t want = *expected + 1;
-        bool           ok   = true;
-        if ((int) threadIdx.x < n) {
+        bool           ok   = *reinterpret_cast<volatile int *>(dev_err) == 0;
+        if (ok && (int) threadIdx.x < n) {
             const long long t0 = clock64();
             for (;;) {
                 uint32_t v;
                 asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flags + threadIdx.x) : "memory");
                 if ((int32_t) (v - want) >= 0) break;
-                if (clock64() - t0 > 10000000000LL) { // about five seconds: the peer is not coming
+                if (clock64() - t0 > 4000000000LL) { // about two seconds: the peer is not coming
                     ok = false;
+                    atomicCAS(dev_err, 0, 3);
                     break;
                 }
                 __nanosleep(200);
             }
         }
-        if (!ok) atomicExch(dev_err, 3);
-        __syncthreads();
-        if (threadIdx.x == 0) *expected = want;
+        ok = __all_sync(0xffffffffu, ok);
+        if (ok && threadIdx.x == 0) *expected = want;
     }
 } // namespace
 

@@ -30,10 +30,6 @@
 #include <cmath>
 #include <cstdlib>
 
-int vkc_gemm_tcgen05_pair(vkc_ctx *ctx, const void *A, const void *B, const float *bias, const void *residual, void *D, int64_t M, int64_t N,
-                          int64_t K, int64_t batch, int64_t stride_a, int64_t stride_b, int64_t stride_d, int64_t lda, int64_t ldb, int64_t ldd,
-                          int b_layout, int epilogue, int dtype, int bn, cudaStream_t st);
-
 namespace {
 
     constexpr int BM       = 128;
@@ -49,7 +45,6 @@ namespace {
         int          epilogue;
         int          a_bcast, b_bcast; // batch stride 0: always read batch slice 0
         int         *dev_err;
-        long long   *timeline; // optional clock64 stamps of CTA (0,0,0)
         int          tma_out;  // D (and the residual) meet the TMA alignment rules: staged, coalesced epilogue
     };
 
@@ -120,8 +115,6 @@ namespace {
         const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
         const int krank = kSplit > 1 ? (int) ptx::cluster_ctarank() : 0; // = blockIdx.x % kSplit
         const int m0 = (blockIdx.x / kSplit) * BM, n0 = blockIdx.y * BN, bz = blockIdx.z;
-        long long *tl = (p.timeline && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) ? p.timeline : nullptr;
-        if (tl && threadIdx.x == 0) tl[0] = clock64();
         const int num_kb_all = (int) ((p.K + BK - 1) / BK);
         const int kb_per     = (num_kb_all + kSplit - 1) / kSplit; // the launcher guarantees every rank a non-empty range
         const int kb0        = krank * kb_per;
@@ -162,7 +155,6 @@ namespace {
         __syncthreads();
         ptx::tc_fence_after();
         const uint32_t tmem = (uint32_t) ctl[0];
-        if (tl && threadIdx.x == 0) tl[1] = clock64();
 
         if (warp == 0) {
             if (ptx::elect_one()) {
@@ -192,7 +184,6 @@ namespace {
                     const uint32_t ph = (kb / kStages) & 1;
                     ok                = ptx::mbar_wait(sBar + 8 * s, ph, ctl + 1, p.dev_err);
                     if (!ok) break;
-                    if (tl && kb == 0) tl[2] = clock64();
                     ptx::tc_fence_after();
 #pragma unroll
                     for (int k = 0; k < BK / 16; ++k) {
@@ -204,13 +195,11 @@ namespace {
                     ptx::tc_commit(sBar + 8 * (kStages + s)); // frees the stage once these MMAs have read it
                 }
                 if (ok) ptx::tc_commit(sBar + 8 * 2 * kStages); // accumulator complete
-                if (tl) tl[3] = clock64();
             }
             if (kSplit > 1) ptx::cluster_wait();
         } else {
             const bool ok = ptx::mbar_wait(sBar + 8 * 2 * kStages, 0, ctl + 1, p.dev_err);
             ptx::tc_fence_after();
-            if (tl && threadIdx.x == 64) tl[4] = clock64();
             bool recv_ok = true;
             if (kSplit > 1) {
                 // Send this CTA's partial of every slab it does not own to the owner: each warp stages its 32 rows of the
@@ -245,10 +234,8 @@ namespace {
                         if (lane == 0) ptx::bulk_copy_to_peer(ptx::mapa(dst, (uint32_t) owner), stage, 8192u, ptx::mapa(sRecvBar, (uint32_t) owner));
                     }
                 }
-                if (tl && threadIdx.x == 64) tl[7] = clock64();
                 recv_ok = ptx::mbar_wait_cluster(sRecvBar, 0, ctl + 1, p.dev_err);
                 recv_ok = __all_sync(0xffffffffu, recv_ok);
-                if (tl && threadIdx.x == 64) tl[8] = clock64();
             }
             if (ok && recv_ok) {
                 const int     q   = warp & 3; // the TMEM lane quarter this warp may address
@@ -398,7 +385,6 @@ namespace {
                 }
             }
         }
-        if (tl && threadIdx.x == 64) tl[5] = clock64();
         if (ctl[1]) {
             // aborted: give copies still in flight time to land before the CTA releases its shared memory
             for (int i = 0; i < 50; ++i) __nanosleep(20000);
@@ -407,7 +393,6 @@ namespace {
         __syncthreads();
         if (warp == 1) ptx::tmem_dealloc(tmem, tmem_cols(BN));
         if (kSplit > 1) ptx::cluster_sync(); // no CTA releases its shared memory while another may still write into it
-        if (tl && threadIdx.x == 0) tl[6] = clock64();
     }
 
     template <int BN, int kStages, int kCtasPerSm, typename T, bool B_KN, int kSplit = 1>
@@ -779,14 +764,6 @@ int vkc_gemm_tcgen05(vkc_ctx *ctx, const void *A, const void *B, const float *bi
         return vkc_fail(ctx, VKC_ERR_UNSUPPORTED, "gemm_tcgen05: operand strides/bases must be multiples of 16 bytes");
     if (M > INT32_MAX || N > INT32_MAX || K > INT32_MAX || batch > 65535) return vkc_fail(ctx, VKC_ERR_UNSUPPORTED, "gemm_tcgen05: extent too large");
 
-    {
-        // CTA-pair form (256-row tiles over two SMs); selection heuristics live here
-        static const char *force = getenv("VKNN_GEMM_PAIR");
-        const int          bn    = force ? atoi(force) : 0;
-        if ((bn == 128 || bn == 256) && M > 128)
-            return vkc_gemm_tcgen05_pair(ctx, A, B, bias, residual, D, M, N, K, batch, stride_a, stride_b, stride_d, lda, ldb, ldd, b_layout, epilogue,
-                                         dtype, bn, st);
-    }
     const bool a_bcast = stride_a == 0 || batch == 1, b_bcast = stride_b == 0 || batch == 1;
     // split-K needs the staged (TMA) epilogue; its alignment conditions are the ones checked for tma_out below
     const bool can_stage = (ldd % 8 == 0) && (stride_d % 8 == 0) && (((uintptr_t) D & 15) == 0) &&
@@ -851,7 +828,6 @@ int vkc_gemm_tcgen05(vkc_ctx *ctx, const void *A, const void *B, const float *bi
     p.a_bcast  = a_bcast;
     p.b_bcast  = b_bcast;
     p.dev_err  = ctx->dev_err;
-    p.timeline = ctx->timeline;
     p.tma_out  = tma_out ? 1 : 0;
 #define VKC_GEMM_LAUNCH(BN_, ST_, C_, T_)                                                                       \
     (b_layout == VKC_B_KN ? launch<BN_, ST_, C_, T_, true>(ctx, tmA, tmB, tmD, tmR, p, batch, st) \

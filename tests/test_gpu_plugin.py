@@ -274,9 +274,11 @@ def test_profiler_gets_one_record_per_launch():
     (got,), info = vko.encoder_layer_graph(x, w, 4).run(backend="cuda", precision="low", iters=2, profile=True)
     assert_low(got, ref, "profiled encoder layer")
     recs = info["profile"]
-    assert len(recs) == 7, recs  # LayerNorm, QKV GEMM, attention, out-projection, LayerNorm, fc1 + GELU, fc2 + residual
     assert all(r[2] == "CUDA" and r[3] >= 0 for r in recs), recs
-    assert [r[1] for r in recs] == ["LayerNorm", "MatMul", "MatMul", "MatMul", "LayerNorm", "MatMul", "MatMul"], recs
+    labels = [r[0].split("[")[-1].rstrip("]") for r in recs]
+    # LayerNorm, QKV GEMM, attention, out-projection, LayerNorm, fc1 + GELU, fc2 + residual, plus whatever copies the views needed
+    assert labels.count("layernorm") == 2 and labels.count("matmul") == 4 and labels.count("attention") == 1, recs
+    assert recs[0][0].startswith("ln1 ") and any(r[0].startswith("qk ") for r in recs), recs
 
 
 def test_runtime_gather_over_a_long_axis_is_left_to_another_backend():

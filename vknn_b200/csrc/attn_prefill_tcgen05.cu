@@ -560,32 +560,65 @@ namespace {
                         p.part_ml[prow * 2 + 1] = none ? 0.f : l;
                     }
                 }
+                if (vec_ok) {
+                    // Coalesced stores. Thread = row would write 16 bytes per row and instruction (32 scattered segments per
+                    // warp store: harmless in local memory, where L2 merges them, but every segment is its own NVLink packet
+                    // when the destination is a peer). The warp therefore stages its 32 rows in this tile's Q area, which is
+                    // idle once O is final (every MMA that read Q has completed), in 16-byte chunks XOR-swizzled by the row,
+                    // and then writes whole rows: 32 / CH rows of CH contiguous chunks per instruction.
+                    constexpr int  CH     = D / 8; // 16-byte chunks per row
+                    const uint32_t sStage = sQ + (uint32_t) t * L::Q_BYTES + (uint32_t) (q * 32) * (D * 2);
 #pragma unroll 1
-                for (int c = 0; c < D / 32; ++c) {
-                    uint32_t v[32];
-                    if (n > 0) {
-                        ptx::tmem_ld_x32(tO + c * 32, v);
-                        ptx::tc_wait_ld();
-                    } else {
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) v[i] = 0u;
-                    }
-                    if (row < p.Sq) {
-                        if (vec_ok) {
-#pragma unroll
-                            for (int g = 0; g < 4; ++g) {
-                                uint4     ov;
-                                uint32_t *o32 = reinterpret_cast<uint32_t *>(&ov);
-#pragma unroll
-                                for (int i = 0; i < 4; ++i)
-                                    o32[i] = pack2<T>(__uint_as_float(v[g * 8 + 2 * i]) * inv, __uint_as_float(v[g * 8 + 2 * i + 1]) * inv);
-                                if (ndest == 0) {
-                                    *reinterpret_cast<uint4 *>(orow + c * 32 + g * 8) = ov;
-                                } else {
-                                    for (int dd = 0; dd < ndest; ++dd) *reinterpret_cast<uint4 *>((T *) p.fan.dest[dd] + ooff + c * 32 + g * 8) = ov;
-                                }
-                            }
+                    for (int c = 0; c < D / 32; ++c) {
+                        uint32_t v[32];
+                        if (n > 0) {
+                            ptx::tmem_ld_x32(tO + c * 32, v);
+                            ptx::tc_wait_ld();
                         } else {
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) v[i] = 0u;
+                        }
+#pragma unroll
+                        for (int g = 0; g < 4; ++g) {
+                            uint32_t o32[4];
+#pragma unroll
+                            for (int i = 0; i < 4; ++i)
+                                o32[i] = pack2<T>(__uint_as_float(v[g * 8 + 2 * i]) * inv, __uint_as_float(v[g * 8 + 2 * i + 1]) * inv);
+                            ptx::st_shared_v4(sStage + (uint32_t) lane * (D * 2) + (uint32_t) (((c * 4 + g) ^ (lane & (CH - 1))) << 4), o32[0], o32[1], o32[2], o32[3]);
+                        }
+                    }
+                    __syncwarp();
+                    // partial rows are dense [.., Sq, D]; final rows follow the caller's output strides
+                    const int64_t row_stride = p.kv_splits > 1 ? (int64_t) D : p.os[2];
+                    const int64_t base_off   = p.kv_splits > 1 ? ((((int64_t) split * gridDim.z + b) * p.Hq + h) * p.Sq) * D
+                                                               : (int64_t) b * p.os[0] + (int64_t) h * p.os[1];
+                    T *const obase = p.kv_splits > 1 ? (T *) p.part_o : (T *) p.O;
+#pragma unroll 1
+                    for (int i = 0; i < CH; ++i) {
+                        const int     rr   = i * (32 / CH) + lane / CH, ch = lane % CH;
+                        const int64_t grow = m0 + (int64_t) t * BM + q * 32 + rr;
+                        const uint4   ov   = ptx::ld_shared_v4(sStage + (uint32_t) rr * (D * 2) + (uint32_t) ((ch ^ (rr & (CH - 1))) << 4));
+                        if (grow < p.Sq) {
+                            const int64_t off = base_off + grow * row_stride + ch * 8;
+                            if (ndest == 0) {
+                                *reinterpret_cast<uint4 *>(obase + off) = ov;
+                            } else {
+                                for (int dd = 0; dd < ndest; ++dd) *reinterpret_cast<uint4 *>((T *) p.fan.dest[dd] + off) = ov;
+                            }
+                        }
+                    }
+                } else {
+#pragma unroll 1
+                    for (int c = 0; c < D / 32; ++c) {
+                        uint32_t v[32];
+                        if (n > 0) {
+                            ptx::tmem_ld_x32(tO + c * 32, v);
+                            ptx::tc_wait_ld();
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) v[i] = 0u;
+                        }
+                        if (row < p.Sq) {
 #pragma unroll
                             for (int i = 0; i < 32; ++i) St<T>::st(orow + c * 32 + i, __uint_as_float(v[i]) * inv);
                         }

@@ -150,6 +150,20 @@ VKC_API int vkc_layernorm_fanout(vkc_ctx *ctx, const void *X, const float *gamma
  * was and returns, so a missing peer never hangs the GPU. While the error word is set, later waits on the same context
  * return at once without polling (a captured forward with dozens of waits does not spend the limit dozens of times). */
 VKC_API int vkc_peer_wait(vkc_ctx *ctx, const uint32_t *flags, int n, uint32_t *expected, vkc_stream stream);
+/* The same wait folded into the consuming GEMM (no separate launch between the producers' signal and the consumer): the
+ * kernel's TMA-producer thread of every CTA polls the gate's flags, bounded like vkc_peer_wait (device error 3 on expiry; the
+ * kernel then leaves through its own bounded barrier waits without reading A), before its first load. state: two 32-bit
+ * device words, zero-initialised once, {expected count, CTAs that have passed}; the last CTA to pass advances the count.
+ * A gate state is used either by vkc_peer_wait (its first word) or by gated kernels, not by both in one step. The
+ * arithmetic is vkc_gemm_ex's. The reference has no multi-device path (docs/LIMITATIONS.md:15-32). */
+typedef struct vkc_gate {
+    const uint32_t *flags;
+    int             n;
+    uint32_t       *state;
+} vkc_gate;
+VKC_API int vkc_gemm_gated(vkc_ctx *ctx, const void *A, const void *B, const float *bias, const void *residual, void *D, int64_t M, int64_t N,
+                           int64_t K, int64_t batch, int64_t stride_a, int64_t stride_b, int64_t stride_d, int64_t lda, int64_t ldb,
+                           int64_t ldd, int b_layout, int epilogue, int dtype, int config, const vkc_gate *gate, vkc_stream stream);
 /* Sharing a vkc_alloc'ed buffer with the other processes of the node: export gives 64 opaque bytes to hand to a peer
  * process (any transport), open maps that buffer into this process (peer access over NVLink), close unmaps it. */
 #define VKC_PEER_HANDLE_BYTES 64

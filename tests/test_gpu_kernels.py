@@ -561,6 +561,53 @@ def test_peer_wait_runs_out_instead_of_hanging(ctx):
     assert torch.isfinite(y.float()).all()
 
 
+def test_gemm_gate_waits_for_flags_inside_the_kernel():
+    """A GEMM whose A operand other GPUs produce polls their flags from its own producer warp. With the flags already raised
+    the gated kernel equals the plain one and advances the expected count once (every CTA passed); with a flag that nobody
+    raises it gives up after its limit, reports a device error through the next sync, leaves the count alone, and the
+    context stays usable. Every tensor-core configuration family is covered: one-tile CTAs, split-K clusters, persistent."""
+    c = vknn_b200.Context(0)
+    try:
+        M, N, K = 342, 1024, 1024
+        a = torch.randn(M, K, device="cuda").half()
+        b = (0.05 * torch.randn(K, N, device="cuda")).half()
+        want = torch.empty(M, N, device="cuda", dtype=torch.float16)
+        c.gemm(a, b, want)
+        c.sync()
+        flags = torch.zeros(4, dtype=torch.int32, device="cuda")
+        state = torch.zeros(2, dtype=torch.int32, device="cuda")
+        rounds = 0
+        for cfg in [-1] + list(range(c.gemm_config_count())):
+            got = torch.zeros_like(want)
+            flags.fill_(rounds + 1)
+            try:
+                c.gemm(a, b, got, config=cfg, gate=(flags.data_ptr(), 4, state))
+            except vknn_b200.VkcError as e:
+                assert e.code == -2  # a configuration this shape cannot run
+                continue
+            c.sync()
+            rounds += 1
+            assert torch.equal(got, want) or float((got.float() - want.float()).abs().max()) <= 2e-3, cfg  # split-K sums in another order
+            assert state.tolist() == [rounds, 0], (cfg, state.tolist())
+        assert rounds >= 6
+        # nobody raises the flags for the next round
+        got = torch.full_like(want, 7.0)
+        c.gemm(a, b, got, gate=(flags.data_ptr(), 4, state))
+        with pytest.raises(vknn_b200.VkcError) as e:
+            c.sync()
+        assert e.value.code == -5
+        assert state.tolist() == [rounds, 0]
+        c.gemm(a, b, got)
+        c.sync()
+        assert torch.equal(got, want)
+    finally:
+        try:
+            c.sync()
+        except vknn_b200.VkcError:
+            pass
+        c.close()
+
+
 def test_upload_download_roundtrip(ctx):
     rng = np.random.default_rng(1)
     x = rng.standard_normal(10007).astype(np.float32)

@@ -68,6 +68,7 @@ def load_library():
     L.vkc_convert.argtypes = [vp, vp, i32, vp, i32, i64, vp]
     L.vkc_gemm.argtypes = [vp, vp, vp, vp, vp, vp] + [i64] * 10 + [i32, i32, i32, vp]
     L.vkc_gemm_ex.argtypes = [vp, vp, vp, vp, vp, vp] + [i64] * 10 + [i32, i32, i32, i32, vp]
+    L.vkc_gemm_gated.argtypes = [vp, vp, vp, vp, vp, vp] + [i64] * 10 + [i32, i32, i32, i32, C.POINTER(Gate), vp]
     L.vkc_gemm_config_count.argtypes = []
     L.vkc_attn_prefill.argtypes = [vp, vp, vp, vp, vp] + [i64] * 6 + [vp, vp, vp, vp, f32, i32, vp, vp, i32, vp]
     L.vkc_attn_prefill_fanout.argtypes = [vp, vp, vp, vp] + [i64] * 6 + [vp, vp, vp, vp, f32, i32, vp, i32, C.POINTER(Fanout), vp]
@@ -120,6 +121,11 @@ def _np_dtype_code(a):
 class Fanout(C.Structure):
     """Mirror of struct vkc_fanout (include/vknn_cuda.h)."""
     _fields_ = [("n_dest", C.c_int), ("dest", C.c_void_p * 8), ("flag", C.c_void_p * 8), ("state", C.c_void_p)]
+
+
+class Gate(C.Structure):
+    """Mirror of struct vkc_gate (include/vknn_cuda.h)."""
+    _fields_ = [("flags", C.c_void_p), ("n", C.c_int), ("state", C.c_void_p)]
 
 
 PEER_HANDLE_BYTES = 64
@@ -203,9 +209,10 @@ class Context:
         self._check(self.lib.vkc_convert(self.h, dst.data_ptr(), _dtype_code(dst), src.data_ptr(), _dtype_code(src), src.numel(), self._stream(stream)))
 
     # ---- kernels ----
-    def gemm(self, A, B, D, bias=None, residual=None, b_layout=B_KN, epilogue=None, stream=None, config=-1):
+    def gemm(self, A, B, D, bias=None, residual=None, b_layout=B_KN, epilogue=None, stream=None, config=-1, gate=None):
         """A [batch?,M,K], B [batch?,K,N] (B_KN) or [batch?,N,K] (B_NK), D [batch?,M,N]; a 2-D operand broadcasts.
-        config >= 0 forces one of the tensor-core kernel's configurations (see gemm_config_count)."""
+        config >= 0 forces one of the tensor-core kernel's configurations (see gemm_config_count).
+        gate = (flags pointer, n, state tensor of two int32): A is produced by other GPUs; the kernel waits for their flags."""
         M, K = A.shape[-2:]
         N = D.shape[-1]
         batch = D.shape[0] if D.dim() == 3 else 1
@@ -214,10 +221,14 @@ class Context:
         sd = D.stride(0) if D.dim() == 3 else 0
         if epilogue is None:
             epilogue = (EPI_BIAS if bias is not None else 0) | (EPI_RESIDUAL if residual is not None else 0)
-        self._check(self.lib.vkc_gemm_ex(self.h, A.data_ptr(), B.data_ptr(), bias.data_ptr() if bias is not None else None,
-                                         residual.data_ptr() if residual is not None else None, D.data_ptr(), M, N, K, batch, sa, sb, sd,
-                                         A.stride(-2), B.stride(-2), D.stride(-2), b_layout, epilogue, _dtype_code(A), int(config),
-                                         self._stream(stream)))
+        args = (self.h, A.data_ptr(), B.data_ptr(), bias.data_ptr() if bias is not None else None,
+                residual.data_ptr() if residual is not None else None, D.data_ptr(), M, N, K, batch, sa, sb, sd,
+                A.stride(-2), B.stride(-2), D.stride(-2), b_layout, epilogue, _dtype_code(A), int(config))
+        if gate is None:
+            self._check(self.lib.vkc_gemm_ex(*args, self._stream(stream)))
+        else:
+            g = Gate(int(gate[0]), int(gate[1]), gate[2].data_ptr())
+            self._check(self.lib.vkc_gemm_gated(*args, C.byref(g), self._stream(stream)))
 
     def gemm_config_count(self):
         return int(self.lib.vkc_gemm_config_count())

@@ -221,6 +221,42 @@ __device__ __forceinline__ void vkc_fanout_signal(const VkcFanDev &f, unsigned t
     }
 }
 #endif
+#ifdef __CUDACC__
+// Gate of a kernel whose input other GPUs produce (the consumer side of the fan-out above, folded into the consuming kernel
+// instead of a separate wait kernel). ONE thread per CTA calls this before the CTA's first load of the gated data: it polls
+// the `n` flag words (system-scope acquire loads) until each has reached state[0] + 1, for at most about half a second —
+// shorter than the kernels' own barrier waits, so that a missing peer is reported as such. On expiry, or when the context's
+// error word is already set, it records device error 3 and returns false; the caller then raises the CTA's abort flag so
+// that the other roles leave through their bounded waits. The last of `total_ctas` callers advances state[0] (only when no
+// error is pending, so that flags and count stay in step) and clears the caller counter state[1]. The cross-proxy fence
+// orders the acquire before the CTA's bulk-tensor loads of what the peers wrote.
+__device__ __forceinline__ bool vkc_gate_wait(const unsigned *flags, int n, unsigned *state, unsigned total_ctas, int *dev_err) {
+    const unsigned  want = *reinterpret_cast<volatile unsigned *>(state) + 1;
+    bool            ok   = *reinterpret_cast<volatile int *>(dev_err) == 0;
+    const long long t0   = clock64();
+    for (int f = 0; f < n && ok; ++f) {
+        for (;;) {
+            unsigned v;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flags + f) : "memory");
+            if ((int) (v - want) >= 0) break;
+            if (clock64() - t0 > 1000000000LL) {
+                ok = false;
+                atomicCAS(dev_err, 0, 3);
+                break;
+            }
+            __nanosleep(64);
+        }
+    }
+    asm volatile("fence.proxy.async.global;" ::: "memory");
+    __threadfence();
+    if (atomicAdd(state + 1, 1u) == total_ctas - 1) {
+        state[1] = 0;
+        if (ok && *reinterpret_cast<volatile int *>(dev_err) == 0) state[0] = want;
+        __threadfence();
+    }
+    return ok;
+}
+#endif
 // Validates a caller's fan-out description (destinations 16-byte aligned) and copies it; returns VKC_OK or fails the context.
 inline int vkc_fan_to_dev(vkc_ctx *ctx, const vkc_fanout *fan, VkcFanDev *out, const char *who) {
     memset(out, 0, sizeof *out);

@@ -6,7 +6,7 @@
 
 int vkc_gemm_tcgen05(vkc_ctx *ctx, const void *A, const void *B, const float *bias, const void *residual, void *D, int64_t M, int64_t N,
                      int64_t K, int64_t batch, int64_t stride_a, int64_t stride_b, int64_t stride_d, int64_t lda, int64_t ldb, int64_t ldd,
-                     int b_layout, int epilogue, int dtype, int config, cudaStream_t st);
+                     int b_layout, int epilogue, int dtype, int config, const vkc_gate *gate, cudaStream_t st);
 
 namespace {
 
@@ -106,9 +106,9 @@ extern "C" int vkc_gemm(vkc_ctx *ctx, const void *A, const void *B, const float 
     return vkc_gemm_ex(ctx, A, B, bias, residual, D, M, N, K, batch, stride_a, stride_b, stride_d, lda, ldb, ldd, b_layout, epilogue, dtype, -1, stream);
 }
 
-extern "C" int vkc_gemm_ex(vkc_ctx *ctx, const void *A, const void *B, const float *bias, const void *residual, void *D, int64_t M, int64_t N,
+static int gemm_dispatch(vkc_ctx *ctx, const void *A, const void *B, const float *bias, const void *residual, void *D, int64_t M, int64_t N,
                            int64_t K, int64_t batch, int64_t stride_a, int64_t stride_b, int64_t stride_d, int64_t lda, int64_t ldb, int64_t ldd,
-                           int b_layout, int epilogue, int dtype, int config, vkc_stream stream) {
+                           int b_layout, int epilogue, int dtype, int config, const vkc_gate *gate, vkc_stream stream) {
     if (!ctx) return VKC_ERR_INVALID;
     VKC_REQUIRE(ctx, config >= -1 && config < vkc_gemm_config_count(), "gemm: bad configuration index %d", config);
     VKC_REQUIRE(ctx, M >= 0 && N >= 0 && K >= 0 && batch >= 0, "gemm: negative extent");
@@ -127,10 +127,14 @@ extern "C" int vkc_gemm_ex(vkc_ctx *ctx, const void *A, const void *B, const flo
     if (ctx->impl == VKC_IMPL_AUTO) want_tc = want_tc && M >= 32 && N >= 32 && K >= 32; // the reference's tiled-path rule (ops/matmul.cpp:141)
     if (want_tc) {
         int rc = vkc_gemm_tcgen05(ctx, A, B, bias, residual, D, M, N, K, batch, stride_a, stride_b, stride_d, lda, ldb, ldd, b_layout, epilogue,
-                                  dtype, config, st);
+                                  dtype, config, gate, st);
         if (rc != VKC_ERR_UNSUPPORTED || ctx->impl == VKC_IMPL_TCGEN05 || config >= 0) return rc;
     } else if (config >= 0) {
         return vkc_fail(ctx, VKC_ERR_UNSUPPORTED, "gemm: a tensor-core configuration was requested for a problem the tensor-core kernel does not take");
+    }
+    if (gate) { // the fp32-pipe kernel has no gate of its own: a one-warp wait kernel in front of it
+        int rc = vkc_peer_wait(ctx, gate->flags, gate->n, gate->state, stream);
+        if (rc) return rc;
     }
     switch (dtype) {
         case VKC_F32:
@@ -141,4 +145,20 @@ extern "C" int vkc_gemm_ex(vkc_ctx *ctx, const void *A, const void *B, const flo
             return launch_simt<__nv_bfloat16>(ctx, A, B, bias, residual, D, M, N, K, batch, stride_a, stride_b, stride_d, lda, ldb, ldd, b_layout,
                                               epilogue, st);
     }
+}
+
+extern "C" int vkc_gemm_ex(vkc_ctx *ctx, const void *A, const void *B, const float *bias, const void *residual, void *D, int64_t M, int64_t N,
+                           int64_t K, int64_t batch, int64_t stride_a, int64_t stride_b, int64_t stride_d, int64_t lda, int64_t ldb, int64_t ldd,
+                           int b_layout, int epilogue, int dtype, int config, vkc_stream stream) {
+    return gemm_dispatch(ctx, A, B, bias, residual, D, M, N, K, batch, stride_a, stride_b, stride_d, lda, ldb, ldd, b_layout, epilogue, dtype, config,
+                         nullptr, stream);
+}
+
+extern "C" int vkc_gemm_gated(vkc_ctx *ctx, const void *A, const void *B, const float *bias, const void *residual, void *D, int64_t M, int64_t N,
+                              int64_t K, int64_t batch, int64_t stride_a, int64_t stride_b, int64_t stride_d, int64_t lda, int64_t ldb, int64_t ldd,
+                              int b_layout, int epilogue, int dtype, int config, const vkc_gate *gate, vkc_stream stream) {
+    if (!ctx) return VKC_ERR_INVALID;
+    VKC_REQUIRE(ctx, gate && gate->flags && gate->state && gate->n >= 1 && gate->n <= 32, "gemm_gated: a gate with 1..32 flags and a state buffer is required");
+    return gemm_dispatch(ctx, A, B, bias, residual, D, M, N, K, batch, stride_a, stride_b, stride_d, lda, ldb, ldd, b_layout, epilogue, dtype, config, gate,
+                         stream);
 }

@@ -46,6 +46,10 @@ namespace {
         int          a_bcast, b_bcast; // batch stride 0: always read batch slice 0
         int         *dev_err;
         int          tma_out;  // D (and the residual) meet the TMA alignment rules: staged, coalesced epilogue
+        // optional gate: A is produced by other GPUs; the TMA producer polls their flags before its first load (vkc_gate_wait)
+        const unsigned *gate_flags;
+        int             gate_n;
+        unsigned       *gate_state;
     };
 
     // GELU(erf) on two values at once with packed fp32 arithmetic and no special-function unit: erf(x), x = h/sqrt(2)
@@ -159,7 +163,12 @@ namespace {
         if (warp == 0) {
             if (ptx::elect_one()) {
                 const int za = p.a_bcast ? 0 : bz, zb = p.b_bcast ? 0 : bz;
-                for (int kb = 0; kb < num_kb; ++kb) {
+                bool      gate_ok = true;
+                if (p.gate_flags) {
+                    gate_ok = vkc_gate_wait(p.gate_flags, p.gate_n, p.gate_state, gridDim.x * gridDim.y * gridDim.z, p.dev_err);
+                    if (!gate_ok) ctl[1] = 1; // the other roles leave through their bounded waits
+                }
+                for (int kb = 0; kb < num_kb && gate_ok; ++kb) {
                     const int      s  = kb % kStages;
                     const uint32_t ph = (kb / kStages) & 1;
                     const int      kx = (kb0 + kb) * BK; // element offset along K
@@ -488,6 +497,10 @@ namespace {
             if (ptx::elect_one()) {
                 int  it = 0;
                 bool ok = true;
+                if (p.gate_flags) {
+                    ok = vkc_gate_wait(p.gate_flags, p.gate_n, p.gate_state, gridDim.x, p.dev_err);
+                    if (!ok) ctl[1] = 1;
+                }
                 for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
                     int m0, n0, bz;
                     tile_of(t, m0, n0, bz);
@@ -758,7 +771,7 @@ extern "C" int vkc_gemm_config_count(void) { return kNumConfigs; }
 // meet the TMA alignment rules; the caller then uses the SIMT kernel.
 int vkc_gemm_tcgen05(vkc_ctx *ctx, const void *A, const void *B, const float *bias, const void *residual, void *D, int64_t M, int64_t N,
                      int64_t K, int64_t batch, int64_t stride_a, int64_t stride_b, int64_t stride_d, int64_t lda, int64_t ldb, int64_t ldd,
-                     int b_layout, int epilogue, int dtype, int config, cudaStream_t st) {
+                     int b_layout, int epilogue, int dtype, int config, const vkc_gate *gate, cudaStream_t st) {
     if (dtype != VKC_F16 && dtype != VKC_BF16) return vkc_fail(ctx, VKC_ERR_UNSUPPORTED, "gemm_tcgen05: 16-bit storage only");
     if ((lda % 8) || (ldb % 8) || (stride_a % 8) || (stride_b % 8) || ((uintptr_t) A & 15) || ((uintptr_t) B & 15))
         return vkc_fail(ctx, VKC_ERR_UNSUPPORTED, "gemm_tcgen05: operand strides/bases must be multiples of 16 bytes");
@@ -829,6 +842,9 @@ int vkc_gemm_tcgen05(vkc_ctx *ctx, const void *A, const void *B, const float *bi
     p.b_bcast  = b_bcast;
     p.dev_err  = ctx->dev_err;
     p.tma_out  = tma_out ? 1 : 0;
+    p.gate_flags = gate ? gate->flags : nullptr;
+    p.gate_n     = gate ? gate->n : 0;
+    p.gate_state = gate ? gate->state : nullptr;
 #define VKC_GEMM_LAUNCH(BN_, ST_, C_, T_)                                                                       \
     (b_layout == VKC_B_KN ? launch<BN_, ST_, C_, T_, true>(ctx, tmA, tmB, tmD, tmR, p, batch, st) \
                           : launch<BN_, ST_, C_, T_, false>(ctx, tmA, tmB, tmD, tmR, p, batch, st))

@@ -175,8 +175,8 @@ class EncoderLayer:
         kbuf = gather.next_buffer()
         # output element (head h, row t, :) of this rank lands at [t, (rank*Hl + h)*D : ...] of every rank's [T, d] buffer
         c.attn_prefill_fanout(q, k, v, gather.dests(kbuf, self.rank * dl), gather.flags(), gather.state, (T * d, D, d), scale=1.0 / (D ** 0.5))
-        gather.wait()
-        c.gemm(gather.buffers[kbuf], w["wo"], buf["x1"], bias=w["bo"], residual=x2)
+        # the out-projection's own producer warp waits for the ranks' flags (no wait kernel between the two launches)
+        c.gemm(gather.buffers[kbuf], w["wo"], buf["x1"], bias=w["bo"], residual=x2, gate=gather.gate())
         c.layernorm(buf["x1"], w["ln2_g"], w["ln2_b"], buf["h"], self.eps)
         c.gemm(buf["h"], w["w1"], buf["f"], bias=w["b1"], epilogue=capi.EPI_BIAS | capi.EPI_GELU_ERF)
         c.gemm(buf["f"], w["w2"], y.view(T, d), bias=w["b2"], residual=buf["x1"])
@@ -202,14 +202,12 @@ class EncoderLayer:
         y = out if out is not None else torch.empty_like(x_loc)
         kh = gather_h.next_buffer()
         c.layernorm_fanout(x_loc, w["ln1_g"], w["ln1_b"], gather_h.dests(kh, lo * d), gather_h.flags(), gather_h.state, self.eps)
-        gather_h.wait()
-        c.gemm(gather_h.buffers[kh], w["wqkv_local"], b["qkv"].view(T, 3 * dl), bias=w["bqkv_local"])
+        c.gemm(gather_h.buffers[kh], w["wqkv_local"], b["qkv"].view(T, 3 * dl), bias=w["bqkv_local"], gate=gather_h.gate())
         q, k, v = (b["qkv"][:, i].permute(1, 0, 2).unsqueeze(0) for i in range(3))
         ka = gather_att.next_buffer()
         c.attn_prefill_fanout(q, k, v, gather_att.dests(ka, self.rank * dl), gather_att.flags(), gather_att.state, (T * d, D, d),
                               scale=1.0 / (D ** 0.5))
-        gather_att.wait()
-        c.gemm(gather_att.buffers[ka][lo:hi], w["wo"], b["x1"], bias=w["bo"], residual=x_loc)
+        c.gemm(gather_att.buffers[ka][lo:hi], w["wo"], b["x1"], bias=w["bo"], residual=x_loc, gate=gather_att.gate())
         c.layernorm(b["x1"], w["ln2_g"], w["ln2_b"], b["h"], self.eps)
         c.gemm(b["h"], w["w1"], b["f"], bias=w["b1"], epilogue=capi.EPI_BIAS | capi.EPI_GELU_ERF)
         c.gemm(b["f"], w["w2"], y, bias=w["b2"], residual=b["x1"])

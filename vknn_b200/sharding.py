@@ -115,7 +115,7 @@ class PeerGather:
             raise RuntimeError("PeerGather: sharing the gather buffers failed on rank(s) %s%s"
                                % ([r for r, ok in enumerate(oks) if not ok], (": %s" % err) if err is not None else ""))
         self.state = torch.zeros(2, dtype=torch.int32, device=self.device)
-        self.expected = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.expected = torch.zeros(2, dtype=torch.int32, device=self.device)  # [0] fan-outs consumed so far, [1] CTA counter of a gated kernel
         self.calls = 0
         self.buffers = [tensor_at(self.local + k * self.buf_bytes, rows * width * esize, dtype, (rows, width), self.device) for k in range(2)]
         self._esize = esize
@@ -136,6 +136,10 @@ class PeerGather:
 
     def wait(self, stream=None):
         self.ctx.peer_wait(self.local + 2 * self.buf_bytes, self.world, self.expected, stream=stream)
+
+    def gate(self):
+        """The same wait as a gate of the consuming GEMM (Context.gemm(..., gate=...)): flag array, flag count, state words."""
+        return (self.local + 2 * self.buf_bytes, self.world, self.expected)
 
     def close(self):
         import torch

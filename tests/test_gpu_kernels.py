@@ -569,8 +569,9 @@ def test_gemm_gate_waits_for_flags_inside_the_kernel():
     c = vknn_b200.Context(0)
     try:
         M, N, K = 342, 1024, 1024
-        a = torch.randn(M, K, device="cuda").half()
-        b = (0.05 * torch.randn(K, N, device="cuda")).half()
+        gen = torch.Generator(device="cuda").manual_seed(41)
+        a = torch.randn(M, K, device="cuda", generator=gen).half()
+        b = (0.05 * torch.randn(K, N, device="cuda", generator=gen)).half()
         want = torch.empty(M, N, device="cuda", dtype=torch.float16)
         c.gemm(a, b, want)
         c.sync()
@@ -587,7 +588,8 @@ def test_gemm_gate_waits_for_flags_inside_the_kernel():
                 continue
             c.sync()
             rounds += 1
-            assert torch.equal(got, want) or float((got.float() - want.float()).abs().max()) <= 2e-3, cfg  # split-K sums in another order
+            # split-K sums in another order: one fp16 ulp of outputs that reach |y| < 8
+            assert torch.equal(got, want) or float((got.float() - want.float()).abs().max()) <= 2.0 ** -8, cfg
             assert state.tolist() == [rounds, 0], (cfg, state.tolist())
         assert rounds >= 6
         # nobody raises the flags for the next round

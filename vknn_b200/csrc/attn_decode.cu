@@ -11,6 +11,7 @@
 // Algorithmic bytes per call: sum_b 2 * Hkv * kv_len[b] * D * sizeof(T)  (+ Q and O).
 #include "common.cuh"
 #include <mutex>
+#include <cstdlib>
 
 int vkc_attn_decode_tcgen05(vkc_ctx *ctx, const void *Q, const void *Kc, const void *Vc, int64_t B, int64_t Hq, int64_t Hkv, int64_t Lmax, int64_t D,
                             const int32_t *kv_len, float scale, float *part_ml, float *part_o, int chunk, int parts_stride, int dtype, cudaStream_t st);

@@ -696,6 +696,306 @@ namespace {
         return vkc_post_launch(ctx, "gemm_tcgen05_persistent");
     }
 
+    // ---------------------------------------------------------------------------------------------------------------
+    // CTA-pair form: two CTAs on two SMs (a cluster of two) drive ONE tcgen05.mma.cta_group::2 stream over a 256 x BN output
+    // tile. Each CTA loads its own 128 rows of A and HALF of the B tile; the tensor cores of both SMs read both halves, so
+    // per k-step a CTA pulls 16 KB + BN x 64 bytes from L2 for 128 x BN x 64 multiply-adds — half the B traffic of the
+    // one-CTA forms, which at 128 x 256 tiles need about 96 bytes per clock and SM and are fed at 55-85. Everything else is the
+    // persistent form above: pairs walk over output tiles, the accumulator is double buffered in tensor memory (each CTA holds
+    // its 128 rows), the operand ring streams across tile boundaries, every epilogue warp owns rotating staging blocks.
+    //   warp 0 (both CTAs): TMA producer; the completion bytes of BOTH CTAs' loads are counted on the LEADER's "full" barrier
+    //   warp 1 (leader):    MMA issuer; commits each stage's "empty" barrier and each tile's "accumulator full" barrier in
+    //                       both CTAs; waits for "accumulator empty" arrivals from the epilogue warps of both CTAs
+    //   warps 2-5:          epilogue over the CTA's own 128 accumulator rows
+    // No load is multicast: each CTA fetches what it keeps.
+    template <int BN, int kStages> constexpr int smem_bytes_pair() {
+        return kStages * (BM * BK * 2 + (BN / 2) * BK * 2) + 4 * kPBlocks * 4096 + 1024 /*align*/ + 512 /*barriers*/ + 4 * BN * 4 /*bias, per warp*/;
+    }
+
+    template <int BN, int kStages, typename T, bool B_KN>
+    __global__ void __launch_bounds__(kThreads, 1)
+        gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                                 const __grid_constant__ CUtensorMap tmD, const __grid_constant__ CUtensorMap tmR, GemmParams p, int m_tiles,
+                                 int n_tiles, int total_tiles) {
+        constexpr uint32_t A_BYTES = BM * BK * 2;
+        constexpr uint32_t B_BYTES = (BN / 2) * BK * 2; // this CTA's half of the B tile
+        constexpr bool     kBf16   = std::is_same<T, __nv_bfloat16>::value;
+        constexpr uint32_t kIdesc  = ptx::idesc_f16(2 * BM, BN, kBf16, false, B_KN);
+        constexpr int      kSlabs  = (BN + 63) / 64;
+        constexpr uint32_t kRing   = kStages * (A_BYTES + B_BYTES);
+        constexpr uint32_t kStage  = 4 * kPBlocks * 4096;
+
+        extern __shared__ uint8_t smem_raw[];
+        const uint32_t raw   = ptx::smem_u32(smem_raw);
+        const uint32_t base  = (raw + 1023u) & ~1023u;
+        uint8_t       *gbase = smem_raw + (base - raw);
+        const uint32_t sA    = base;
+        const uint32_t sB    = base + kStages * A_BYTES;
+        const uint32_t sOut  = base + kRing;
+        const uint32_t sBar  = base + kRing + kStage; // full[kStages], empty[kStages], accFull[2], accEmpty[2], resid[4][kPBlocks]
+        const uint32_t bAccF = sBar + 8 * (2 * kStages), bAccE = bAccF + 16, bRes = bAccE + 16;
+        volatile int  *ctl   = (volatile int *) (gbase + kRing + kStage + 8 * (2 * kStages + 4 + 4 * kPBlocks)); // [0] tmem base, [1] abort
+        const uint32_t sSlot = sBar + 8 * (2 * kStages + 4 + 4 * kPBlocks);
+        float         *sbias = (float *) (gbase + kRing + kStage + 512); // [4 warps][BN]
+        static_assert(8 * (2 * kStages + 4 + 4 * kPBlocks) + 16 <= 512, "barrier area");
+
+        const int      warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+        const uint32_t rank = ptx::cluster_ctarank(); // 0 = leader
+        const int      pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
+        const int      num_kb = (int) ((p.K + BK - 1) / BK);
+
+        if (threadIdx.x == 0) {
+            for (int s = 0; s < kStages; ++s) {
+                ptx::mbar_init(sBar + 8 * s, 1);
+                ptx::mbar_init(sBar + 8 * (kStages + s), 1);
+            }
+            for (int b = 0; b < 2; ++b) {
+                ptx::mbar_init(bAccF + 8 * b, 1);
+                ptx::mbar_init(bAccE + 8 * b, 8); // one arrival per epilogue warp of both CTAs (used in the leader only)
+            }
+            for (int w = 0; w < 4 * kPBlocks; ++w) ptx::mbar_init(bRes + 8 * w, 1);
+            ctl[1] = 0;
+            ptx::fence_mbar_init();
+            ptx::prefetch_tmap(&tmA);
+            ptx::prefetch_tmap(&tmB);
+            ptx::prefetch_tmap(&tmD);
+        }
+        if (warp == 1) {
+            ptx::tmem_alloc_pair(sSlot, 2 * acc_stride(BN));
+            ptx::tmem_relinquish_pair();
+        }
+        vkc_grid_dep_wait();
+        vkc_grid_dep_launch();
+        ptx::tc_fence_before();
+        __syncthreads();
+        ptx::cluster_sync(); // both CTAs' barriers exist before either side signals them
+        ptx::tc_fence_after();
+        const uint32_t tmem = (uint32_t) ctl[0];
+
+        // tile t -> groups of kGroupM pair-row tiles; inside a group the row tile runs fastest, then the column tile; then the
+        // next group, then the batch. The pairs that run at the same time then share a few hundred rows of A and columns of B
+        // (for 8192^3: 8 x 9 tiles, 71 MB of operands) instead of a full column of row tiles, so the operands stay in L2.
+        // m0 is this CTA's first row.
+        constexpr int kGroupM = 8;
+        auto tile_of = [&](int t, int &m0, int &n0, int &bz) {
+            const int per_batch = m_tiles * n_tiles, tb = t % per_batch;
+            const int grp = tb / (kGroupM * n_tiles), first = grp * kGroupM;
+            const int gsz = m_tiles - first < kGroupM ? m_tiles - first : kGroupM;
+            const int in_g = tb - grp * (kGroupM * n_tiles);
+            m0 = (first + in_g % gsz) * (2 * BM) + (int) rank * BM;
+            n0 = (in_g / gsz) * BN;
+            bz = t / per_batch;
+        };
+
+        if (warp == 0) {
+            if (ptx::elect_one()) {
+                int  it = 0;
+                bool ok = true;
+                if (p.gate_flags) {
+                    ok = vkc_gate_wait(p.gate_flags, p.gate_n, p.gate_state, gridDim.x, p.dev_err);
+                    if (!ok) ctl[1] = 1;
+                }
+                for (int t = pair; t < total_tiles && ok; t += npairs) {
+                    int m0, n0, bz;
+                    tile_of(t, m0, n0, bz);
+                    const int za = p.a_bcast ? 0 : bz, zb = p.b_bcast ? 0 : bz;
+                    const int nb = n0 + (int) rank * (BN / 2); // this CTA's half of the tile's columns
+                    for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                        const int      s  = it % kStages;
+                        const uint32_t ph = (it / kStages) & 1;
+                        const int      kx = kb * BK;
+                        if (!ptx::mbar_wait(sBar + 8 * (kStages + s), ph ^ 1, ctl + 1, p.dev_err)) {
+                            ok = false;
+                            break;
+                        }
+                        const uint32_t full = ptx::mapa(sBar + 8 * s, 0);
+                        if (rank == 0) ptx::mbar_expect_tx(sBar + 8 * s, 2 * (A_BYTES + B_BYTES)); // the bytes of both CTAs
+                        ptx::tma_load_3d_pair(sA + s * A_BYTES, &tmA, kx, m0, za, full);
+                        if (!B_KN) {
+                            ptx::tma_load_3d_pair(sB + s * B_BYTES, &tmB, kx, nb, zb, full);
+                        } else {
+#pragma unroll
+                            for (int c = 0; c < BN / 128; ++c) ptx::tma_load_3d_pair(sB + s * B_BYTES + c * (BK * 128), &tmB, nb + c * 64, kx, zb, full);
+                        }
+                    }
+                }
+            }
+        } else if (warp == 1) {
+            if (rank == 0 && ptx::elect_one()) {
+                int  it = 0, i = 0;
+                bool ok = true;
+                for (int t = pair; t < total_tiles && ok; t += npairs, ++i) {
+                    const int      buf = i & 1;
+                    const uint32_t acc = tmem + (uint32_t) (buf * acc_stride(BN));
+                    // the epilogue warps of both CTAs have drained this accumulator (two tiles ago)
+                    ok = ptx::mbar_wait_cluster(bAccE + 8 * buf, ((i >> 1) & 1) ^ 1, ctl + 1, p.dev_err);
+                    if (!ok) break;
+                    ptx::tc_fence_after();
+                    for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                        const int      s  = it % kStages;
+                        const uint32_t ph = (it / kStages) & 1;
+                        ok                = ptx::mbar_wait_cluster(sBar + 8 * s, ph, ctl + 1, p.dev_err);
+                        if (!ok) break;
+                        ptx::tc_fence_after();
+#pragma unroll
+                        for (int k = 0; k < BK / 16; ++k) {
+                            const uint64_t ad = ptx::smem_desc_sw128(sA + s * A_BYTES + k * 32, 16, 1024);
+                            const uint64_t bd = B_KN ? ptx::smem_desc_sw128(sB + s * B_BYTES + k * (16 * 128), BK * 128, 1024)
+                                                     : ptx::smem_desc_sw128(sB + s * B_BYTES + k * 32, 16, 1024);
+                            ptx::mma_f16_ss_pair(acc, ad, bd, kIdesc, (kb | k) != 0 ? 1u : 0u);
+                        }
+                        // the stage is free in BOTH CTAs once these MMAs have read it
+                        ptx::tc_commit_pair(sBar + 8 * (kStages + s));
+                        ptx::tc_commit_pair(ptx::mapa(sBar + 8 * (kStages + s), 1));
+                    }
+                    if (ok) {
+                        ptx::tc_commit_pair(bAccF + 8 * buf);
+                        ptx::tc_commit_pair(ptx::mapa(bAccF + 8 * buf, 1));
+                    }
+                }
+            }
+        } else {
+            const int      q      = warp & 3; // the TMEM lane quarter this warp may address
+            float         *wbias  = sbias + q * BN;
+            const uint32_t wOut   = sOut + (uint32_t) (q * kPBlocks) * 4096u;
+            uint8_t       *gOut   = gbase + kRing + (q * kPBlocks) * 4096;
+            const uint32_t wRes   = bRes + 8 * (q * kPBlocks);
+            const bool     resid  = (p.epilogue & VKC_EPI_RESIDUAL) != 0;
+            const uint32_t accE0  = ptx::mapa(bAccE, 0); // the leader's "accumulator empty" barriers
+            auto           nslabs = [&](int n0) {
+                int n = 0;
+                for (int sl = 0; sl < kSlabs; ++sl)
+                    if ((int64_t) n0 + sl * 64 < p.N) n = sl + 1;
+                return n;
+            };
+            int  g  = 0; // running slab number of this warp: staging block g % kPBlocks, use (g / kPBlocks) of that block
+            bool ok = true;
+            if (resid && pair < total_tiles && lane == 0) {
+                int m0, n0, bz;
+                tile_of(pair, m0, n0, bz);
+                ptx::mbar_expect_tx(wRes, 4096u);
+                ptx::tma_load_3d(wOut, &tmR, n0, m0 + q * 32, bz, wRes);
+            }
+            int i = 0;
+            for (int t = pair; t < total_tiles && ok; t += npairs, ++i) {
+                int m0, n0, bz;
+                tile_of(t, m0, n0, bz);
+                const int  buf = i & 1, nslab = nslabs(n0), row0 = m0 + q * 32;
+                const bool rows_in = row0 < p.M; // warp-uniform
+                __syncwarp();
+                if (p.epilogue & VKC_EPI_BIAS)
+                    for (int j = lane; j < BN; j += 32) wbias[j] = (int64_t) n0 + j < p.N ? __ldg(p.bias + n0 + j) : 0.f;
+                __syncwarp();
+                ok = ptx::mbar_wait(bAccF + 8 * buf, (i >> 1) & 1, ctl + 1, p.dev_err);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                ptx::tc_fence_after();
+                const uint32_t acc = tmem + ((uint32_t) (q * 32) << 16) + (uint32_t) (buf * acc_stride(BN));
+#pragma unroll 1
+                for (int sl = 0; sl < nslab; ++sl, ++g) {
+                    const int blk = g % kPBlocks;
+                    if (lane == 0) {
+                        ptx::bulk_wait_group_read_1();
+                        if (resid) {
+                            int  tm0 = m0, tn0 = n0 + (sl + 1) * 64, tbz = bz;
+                            bool more = sl + 1 < nslab;
+                            if (!more && t + npairs < total_tiles) {
+                                tile_of(t + npairs, tm0, tn0, tbz);
+                                more = true;
+                            }
+                            if (more) {
+                                const int nb = (g + 1) % kPBlocks;
+                                ptx::mbar_expect_tx(wRes + 8 * nb, 4096u);
+                                ptx::tma_load_3d(wOut + nb * 4096, &tmR, tn0, tm0 + q * 32, tbz, wRes + 8 * nb);
+                            }
+                        }
+                    }
+                    __syncwarp();
+                    uint32_t r2[2][32];
+                    ptx::tmem_ld_x32(acc + (uint32_t) (sl * 64), r2[0]);
+                    ptx::tmem_ld_x32(acc + (uint32_t) (sl * 64 + 32), r2[1]);
+                    ptx::tc_wait_ld();
+                    if (sl == nslab - 1) { // accumulator drained: the tensor pipe may overwrite it
+                        ptx::tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) ptx::mbar_arrive_cluster(accE0 + 8 * buf);
+                    }
+                    if (resid) {
+                        ok = ptx::mbar_wait(wRes + 8 * blk, (g / kPBlocks) & 1, ctl + 1, p.dev_err);
+                        ok = __all_sync(0xffffffffu, ok);
+                        if (!ok) break;
+                    }
+                    uint8_t *blkp = gOut + blk * 4096 + lane * 128;
+#pragma unroll
+                    for (int hf = 0; hf < 2; ++hf) {
+                        float v[32];
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r2[hf][j]);
+                        if (p.epilogue & VKC_EPI_BIAS) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 4) {
+                                const float4 bv = *reinterpret_cast<const float4 *>(wbias + sl * 64 + hf * 32 + j);
+                                v[j] += bv.x, v[j + 1] += bv.y, v[j + 2] += bv.z, v[j + 3] += bv.w;
+                            }
+                        }
+                        if (p.epilogue & VKC_EPI_GELU_ERF) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 2) {
+                                const float2 g2 = gelu_erf_pair(make_float2(v[j], v[j + 1]));
+                                v[j] = g2.x, v[j + 1] = g2.y;
+                            }
+                        }
+#pragma unroll
+                        for (int u = 0; u < 4; ++u) {
+                            uint4 *slot = reinterpret_cast<uint4 *>(blkp + (((hf * 4 + u) ^ (lane & 7)) << 4));
+                            if (resid) {
+                                const uint4 rv = *slot;
+                                const T    *rt = reinterpret_cast<const T *>(&rv);
+#pragma unroll
+                                for (int j = 0; j < 8; ++j) v[u * 8 + j] += St<T>::ld(rt + j);
+                            }
+                            uint4 ov;
+                            T    *ot = reinterpret_cast<T *>(&ov);
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) St<T>::st(ot + j, v[u * 8 + j]);
+                            *slot = ov;
+                        }
+                    }
+                    ptx::fence_proxy_async();
+                    __syncwarp();
+                    if (lane == 0) {
+                        if (rows_in) ptx::tma_store_3d(&tmD, wOut + blk * 4096, n0 + sl * 64, row0, bz);
+                        ptx::bulk_commit_group(); // committed even when empty: the rotation counts groups
+                    }
+                }
+            }
+            if (lane == 0) ptx::bulk_wait_group_read_0();
+            __syncwarp();
+        }
+        if (ctl[1]) {
+            // aborted: give copies still in flight time to land before the CTA releases its shared memory
+            for (int i = 0; i < 50; ++i) __nanosleep(20000);
+        }
+        ptx::tc_fence_before();
+        __syncthreads();
+        ptx::cluster_sync(); // neither CTA leaves while the other may still touch its shared memory, barriers or tensor memory
+        if (warp == 1) ptx::tmem_dealloc_pair(tmem, 2 * acc_stride(BN));
+    }
+
+    template <int BN, int kStages, typename T, bool B_KN>
+    int launch_pair(vkc_ctx *ctx, const CUtensorMap &tmA, const CUtensorMap &tmB, const CUtensorMap &tmD, const CUtensorMap &tmR, const GemmParams &p,
+                    int64_t batch, cudaStream_t st) {
+        auto          kern = gemm_tcgen05_pair_kernel<BN, kStages, T, B_KN>;
+        constexpr int smem = smem_bytes_pair<BN, kStages>();
+        static_assert(smem <= 227 * 1024, "shared memory budget");
+        if (int rc = vkc_configure_smem(ctx, kern, smem)) return rc;
+        const int64_t mt = (p.M + 2 * BM - 1) / (2 * BM), nt = (p.N + BN - 1) / BN, total = mt * nt * batch;
+        if (total > INT32_MAX) return vkc_fail(ctx, VKC_ERR_UNSUPPORTED, "gemm_tcgen05: too many tiles");
+        const int64_t pairs = total < ctx->sm_count / 2 ? total : ctx->sm_count / 2;
+        vkc_launch_cluster(ctx, kern, dim3((unsigned) (2 * pairs)), dim3(kThreads), smem, st, 2u, tmA, tmB, tmD, tmR, p, (int) mt, (int) nt, (int) total);
+        return vkc_post_launch(ctx, "gemm_tcgen05_pair");
+    }
+
     // Tile width: fewest waves over the SMs first, then the least padded work. Wide tiles re-read A less often.
     // Configurations the launcher can pick: tile width, ring depth, CTAs per SM, split-K factor.
     enum TileConfig {
@@ -712,6 +1012,8 @@ namespace {
         kCfgP256x3, // persistent, double-buffered accumulator: the epilogue overlaps the next tile's K loop
         kCfgP192x4,
         kCfgP128x5,
+        kCfgPair256x5, // CTA pairs (cta_group::2), 256 x 256 tiles, persistent
+        kCfgPair128x6, // CTA pairs, 256 x 128 tiles
         kNumConfigs
     };
     struct TileChoice {
@@ -728,6 +1030,8 @@ namespace {
         const int64_t mt     = (M + BM - 1) / BM;
         auto          tiles  = [&](int bn) { return mt * ((N + bn - 1) / bn) * batch; };
         const int64_t num_kb = (K + BK - 1) / BK;
+        // large problems in every dimension: CTA pairs halve the B traffic per SM (4096^3: 97.8 us against 109)
+        if (staged && M >= 2048 && N >= 2048 && K >= 2048) return {kCfgPair256x5, 256};
         if (tiles(256) >= 4 * (int64_t) sms) return {kCfg256x4x1, 256};
         if (staged && (epilogue & VKC_EPI_GELU_ERF) && tiles(128) >= 2 * (int64_t) sms) return {kCfgP128x5, 128};
         if (num_kb >= 16) {
@@ -746,6 +1050,9 @@ namespace {
                 if (ctas > best_ctas) best_ctas = ctas, best = i;
             }
             if (best >= 0 && best_ctas * 10 >= (int64_t) sms * 6) return {cands[best].cfg, cands[best].bn};
+            // a few row tiles and a very long K (the row shards of a token-sharded encoder: 342 x 1024 x 4096): half of K per CTA
+            // still beats one narrow tile per CTA over the whole K (10.5 against 13.3 us)
+            if (best >= 0 && cands[best].split == 2 && num_kb >= 32 && best_ctas * 10 >= (int64_t) sms * 3) return {cands[best].cfg, cands[best].bn};
         }
         TileChoice    best {kCfg128x3x2, 128};
         double        best_cost = 1e300;
@@ -797,12 +1104,16 @@ int vkc_gemm_tcgen05(vkc_ctx *ctx, const void *A, const void *B, const float *bi
 
     TileChoice tc = choose_tile(M, N, K, batch, ctx->sm_count, tma_out, epilogue);
     if (config >= 0) { // caller-chosen configuration (autotuning); refuse what this problem cannot run
-        const int  bns[kNumConfigs] = {256, 256, 192, 128, 64, 192, 128, 192, 256, 128, 256, 192, 128};
-        const bool split            = config >= kCfg192x4x1s2 && config <= kCfg128x5x1s2;
-        if (config >= kCfgP256x3 && !tma_out)
+        const int  bns[kNumConfigs] = {256, 256, 192, 128, 64, 192, 128, 192, 256, 128, 256, 192, 128, 256, 128};
+        const int  split            = (config >= kCfg192x4x1s2 && config <= kCfg128x5x1s2) ? 2 : 1;
+        if (((config >= kCfgP256x3 && config <= kCfgP128x5) || config >= kCfgPair256x5) && !tma_out)
             return vkc_fail(ctx, VKC_ERR_UNSUPPORTED, "gemm_tcgen05: persistent configuration %d needs a TMA-storable output", config);
-        if (split && (!tma_out || (K + BK - 1) / BK < 4))
-            return vkc_fail(ctx, VKC_ERR_UNSUPPORTED, "gemm_tcgen05: split-K configuration %d needs a TMA-storable output and at least 4 k-steps", config);
+        if (config >= kCfgPair256x5 && M <= BM)
+            return vkc_fail(ctx, VKC_ERR_UNSUPPORTED, "gemm_tcgen05: CTA-pair configuration %d needs more than one 128-row tile", config);
+        // every CTA of the cluster must get a non-empty K range: ceil(kb / split) * (split - 1) < kb
+        const int64_t nkb = (K + BK - 1) / BK;
+        if (split > 1 && (!tma_out || nkb < 2 * split || ((nkb + split - 1) / split) * (split - 1) >= nkb))
+            return vkc_fail(ctx, VKC_ERR_UNSUPPORTED, "gemm_tcgen05: split-K configuration %d needs a TMA-storable output and at least %d k-steps", config, 2 * split);
         tc = {(TileConfig) config, bns[config]};
     }
     const int        BN = tc.bn;
@@ -818,7 +1129,7 @@ int vkc_gemm_tcgen05(vkc_ctx *ctx, const void *A, const void *B, const float *bi
     if (b_layout == VKC_B_NK) {
         uint64_t dims[3] = {(uint64_t) K, (uint64_t) N, (uint64_t) (b_bcast ? 1 : batch)};
         uint64_t str[2]  = {(uint64_t) ldb * 2, (uint64_t) (b_bcast ? (uint64_t) ldb * 2 * (uint64_t) N : (uint64_t) stride_b * 2)};
-        uint32_t box[3]  = {BK, (uint32_t) BN, 1};
+        uint32_t box[3]  = {BK, (uint32_t) (tc.cfg >= kCfgPair256x5 ? BN / 2 : BN), 1}; // a CTA of a pair loads half of the tile's columns
         int      rc      = vkc_make_tmap(ctx, &tmB, dtype, B, 3, dims, str, box);
         if (rc) return rc;
     } else {
@@ -854,6 +1165,9 @@ int vkc_gemm_tcgen05(vkc_ctx *ctx, const void *A, const void *B, const float *bi
 #define VKC_GEMM_LAUNCH_P(BN_, ST_, T_)                                                                      \
     (b_layout == VKC_B_KN ? launch_persistent<BN_, ST_, T_, true>(ctx, tmA, tmB, tmD, tmR, p, batch, st) \
                           : launch_persistent<BN_, ST_, T_, false>(ctx, tmA, tmB, tmD, tmR, p, batch, st))
+#define VKC_GEMM_LAUNCH_2(BN_, ST_, T_)                                                                \
+    (b_layout == VKC_B_KN ? launch_pair<BN_, ST_, T_, true>(ctx, tmA, tmB, tmD, tmR, p, batch, st) \
+                          : launch_pair<BN_, ST_, T_, false>(ctx, tmA, tmB, tmD, tmR, p, batch, st))
 #define VKC_GEMM_BY_TILE(T_)                                                         \
     do {                                                                             \
         switch (tc.cfg) {                                                            \
@@ -869,6 +1183,8 @@ int vkc_gemm_tcgen05(vkc_ctx *ctx, const void *A, const void *B, const float *bi
             case kCfgP256x3: return VKC_GEMM_LAUNCH_P(256, 3, T_);                   \
             case kCfgP192x4: return VKC_GEMM_LAUNCH_P(192, 4, T_);                   \
             case kCfgP128x5: return VKC_GEMM_LAUNCH_P(128, 5, T_);                   \
+            case kCfgPair256x5: return VKC_GEMM_LAUNCH_2(256, 5, T_);                \
+            case kCfgPair128x6: return VKC_GEMM_LAUNCH_2(128, 6, T_);                \
             default: return VKC_GEMM_LAUNCH_S(128, 5, 1, T_, 2);                     \
         }                                                                            \
     } while (0)
@@ -878,4 +1194,5 @@ int vkc_gemm_tcgen05(vkc_ctx *ctx, const void *A, const void *B, const float *bi
 #undef VKC_GEMM_LAUNCH
 #undef VKC_GEMM_LAUNCH_S
 #undef VKC_GEMM_LAUNCH_P
+#undef VKC_GEMM_LAUNCH_2
 }

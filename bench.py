@@ -409,7 +409,8 @@ def bench_prefill_delivered(ctx, cfg, steps, warmup, rank, world):
         def step_fused(i):
             q, k, v = sets[i % ns]
             kb = gather.next_buffer()
-            ctx.attn_prefill_fanout(q, k, v, gather.dests(kb, rank * Hl * D), gather.flags(), gather.state, o_strides, scale, causal=cfg["causal"])
+            ctx.attn_prefill_fanout(q, k, v, gather.dests(kb, rank * Hl * D), gather.flags(), gather.state, o_strides, scale, causal=cfg["causal"],
+                                    mcast=gather.mcast(kb, rank * Hl * D))
             gather.wait()
             return kb
 
@@ -422,7 +423,8 @@ def bench_prefill_delivered(ctx, cfg, steps, warmup, rank, world):
         dist.barrier()
         f_ms, _ = timed_loop(step_fused, steps, warmup + (warmup % 2), world)
         ctx.sync()
-        out["fused_fanout"] = dict(ms_per_step=f_ms / steps, max_abs_vs_nccl_path=max_over_ranks(err, world))
+        out["fused_fanout"] = dict(ms_per_step=f_ms / steps, max_abs_vs_nccl_path=max_over_ranks(err, world),
+                                   stores="one multimem store per 16 bytes, replicated by the NVSwitch" if gather.mcast_base else "one peer store per destination")
         dist.barrier()
         gather.close()
     except Exception as e:  # noqa: BLE001 - peer memory unavailable on this box: the NCCL figure stands

@@ -133,6 +133,10 @@ typedef struct vkc_fanout {
     void     *dest[8];
     uint32_t *flag[8];
     uint32_t *state;
+    void     *mcast; /* NULL, or the address of the same output buffer in an NVSwitch multicast mapping that covers all n_dest
+                        GPUs (cuMulticast* / a symmetric-memory allocator): the kernel then issues ONE multimem store per 16
+                        bytes, which the switch replicates to every destination, instead of n_dest peer stores. dest[] and
+                        flag[] are still needed (flags are written per destination). */
 } vkc_fanout;
 VKC_API int vkc_attn_prefill_fanout(vkc_ctx *ctx, const void *Q, const void *K, const void *V, int64_t B, int64_t Hq, int64_t Hkv, int64_t Sq,
                                     int64_t Skv, int64_t D, const int64_t *q_strides, const int64_t *k_strides, const int64_t *v_strides,

@@ -43,13 +43,13 @@ def test_header_is_plain_c(tmp_path):
     inc = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "include")
     src = tmp_path / "t.c"
     src.write_text('#include <stdio.h>\n#include <stddef.h>\n#include "vknn_cuda.h"\n'
-                   'int main(void) { printf("%zu %zu %zu %zu\\n", sizeof(vkc_fanout), offsetof(vkc_fanout, dest), '
-                   'offsetof(vkc_fanout, flag), offsetof(vkc_fanout, state)); return 0; }\n')
+                   'int main(void) { printf("%zu %zu %zu %zu %zu\\n", sizeof(vkc_fanout), offsetof(vkc_fanout, dest), '
+                   'offsetof(vkc_fanout, flag), offsetof(vkc_fanout, state), offsetof(vkc_fanout, mcast)); return 0; }\n')
     exe = tmp_path / "t"
     subprocess.check_call(["gcc", "-std=c99", "-Wall", "-Werror", "-pedantic", "-I", inc, str(src), "-o", str(exe)])
-    size, o_dest, o_flag, o_state = (int(v) for v in subprocess.check_output([str(exe)]).split())
+    size, o_dest, o_flag, o_state, o_mcast = (int(v) for v in subprocess.check_output([str(exe)]).split())
     from vknn_b200.capi import Fanout
-    assert (C.sizeof(Fanout), Fanout.dest.offset, Fanout.flag.offset, Fanout.state.offset) == (size, o_dest, o_flag, o_state)
+    assert (C.sizeof(Fanout), Fanout.dest.offset, Fanout.flag.offset, Fanout.state.offset, Fanout.mcast.offset) == (size, o_dest, o_flag, o_state, o_mcast)
 
 
 def test_peer_and_fanout_entry_points_refuse_a_null_context():
@@ -60,3 +60,23 @@ def test_peer_and_fanout_entry_points_refuse_a_null_context():
     assert lib.vkc_layernorm_fanout(None, None, None, None, 1, 1, 1e-5, 1, None, None) == -1
     assert lib.vkc_copy_rows(None, None, None, None, None, 1, 1, 1, None) == -1
     assert lib.vkc_gather_rows(None, None, None, None, 1, 1, 1, 1, 1, 0, None) == -1
+    assert lib.vkc_gemm_gated(None, None, None, None, None, None, 1, 1, 1, 1, 0, 0, 0, 1, 1, 1, 0, 0, 1, -1, None, None) == -1
+    assert lib.vkc_device_info(None, None, 0, None, None) == -1
+
+
+def test_gate_struct_layout(tmp_path):
+    """The Python mirror of struct vkc_gate has the layout the C compiler gives it."""
+    import os
+    import shutil
+    import subprocess
+    if not shutil.which("gcc"):
+        pytest.skip("no C compiler")
+    inc = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "include")
+    src = tmp_path / "g.c"
+    src.write_text('#include <stdio.h>\n#include <stddef.h>\n#include "vknn_cuda.h"\n'
+                   'int main(void) { printf("%zu %zu %zu\\n", sizeof(vkc_gate), offsetof(vkc_gate, n), offsetof(vkc_gate, state)); return 0; }\n')
+    exe = tmp_path / "g"
+    subprocess.check_call(["gcc", "-std=c99", "-Wall", "-Werror", "-pedantic", "-I", inc, str(src), "-o", str(exe)])
+    size, o_n, o_state = (int(v) for v in subprocess.check_output([str(exe)]).split())
+    from vknn_b200.capi import Gate
+    assert (C.sizeof(Gate), Gate.n.offset, Gate.state.offset) == (size, o_n, o_state)

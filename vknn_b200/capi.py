@@ -120,7 +120,7 @@ def _np_dtype_code(a):
 
 class Fanout(C.Structure):
     """Mirror of struct vkc_fanout (include/vknn_cuda.h)."""
-    _fields_ = [("n_dest", C.c_int), ("dest", C.c_void_p * 8), ("flag", C.c_void_p * 8), ("state", C.c_void_p)]
+    _fields_ = [("n_dest", C.c_int), ("dest", C.c_void_p * 8), ("flag", C.c_void_p * 8), ("state", C.c_void_p), ("mcast", C.c_void_p)]
 
 
 class Gate(C.Structure):
@@ -245,39 +245,36 @@ class Context:
                                               mask.data_ptr() if mask is not None else None, kv_len.data_ptr() if kv_len is not None else None,
                                               _dtype_code(Q), self._stream(stream)))
 
-    def attn_prefill_fanout(self, Q, K, V, dests, flags, state, o_strides, scale, causal=False, kv_len=None, stream=None):
+    def attn_prefill_fanout(self, Q, K, V, dests, flags, state, o_strides, scale, causal=False, kv_len=None, stream=None, mcast=None):
         """attn_prefill whose output rows are stored into every buffer of `dests` (raw device pointers mapped on this GPU,
         addressed with o_strides = (batch, head, row) element strides); `flags[d]` (pointer or None) receives this rank's
-        completion count when the last block has stored; `state` is a zeroed 2 x int32 device tensor kept by the caller."""
+        completion count when the last block has stored; `state` is a zeroed 2 x int32 device tensor kept by the caller.
+        mcast: the same buffer's address in an NVSwitch multicast mapping of all destinations (one store reaches them all)."""
         B, Hq, Sq, D = Q.shape
         _, Hkv, Skv, _ = K.shape
         for t in (Q, K, V):
             assert t.stride(-1) == 1
-        f = Fanout()
-        f.n_dest = len(dests)
-        for i, d in enumerate(dests):
-            f.dest[i] = int(d)
-            f.flag[i] = int(flags[i]) if flags is not None and flags[i] else None
-        f.state = state.data_ptr()
+        f = self._fanout(dests, flags, state, mcast)
         st = lambda t: _i64arr([t.stride(0), t.stride(1), t.stride(2)])  # noqa: E731
         self._check(self.lib.vkc_attn_prefill_fanout(self.h, Q.data_ptr(), K.data_ptr(), V.data_ptr(), B, Hq, Hkv, Sq, Skv, D, st(Q), st(K), st(V),
                                                      _i64arr(list(o_strides)), float(scale), int(bool(causal)),
                                                      kv_len.data_ptr() if kv_len is not None else None, _dtype_code(Q), C.byref(f), self._stream(stream)))
 
-    def _fanout(self, dests, flags, state):
+    def _fanout(self, dests, flags, state, mcast=None):
         f = Fanout()
         f.n_dest = len(dests)
         for i, d in enumerate(dests):
             f.dest[i] = int(d)
             f.flag[i] = int(flags[i]) if flags is not None and flags[i] else None
         f.state = state.data_ptr()
+        f.mcast = int(mcast) if mcast else None
         return f
 
-    def layernorm_fanout(self, X, gamma, beta, dests, flags, state, eps, stream=None):
+    def layernorm_fanout(self, X, gamma, beta, dests, flags, state, eps, stream=None, mcast=None):
         """LayerNorm of X [rows, norm] whose output rows are stored at each pointer of `dests` (see attn_prefill_fanout)."""
         rows, norm = X.shape
         assert X.is_contiguous()
-        f = self._fanout(dests, flags, state)
+        f = self._fanout(dests, flags, state, mcast)
         self._check(self.lib.vkc_layernorm_fanout(self.h, X.data_ptr(), gamma.data_ptr(), beta.data_ptr() if beta is not None else None, rows, norm,
                                                   float(eps), _dtype_code(X), C.byref(f), self._stream(stream)))
 

@@ -600,11 +600,8 @@ namespace {
                         const uint4   ov   = ptx::ld_shared_v4(sStage + (uint32_t) rr * (D * 2) + (uint32_t) ((ch ^ (rr & (CH - 1))) << 4));
                         if (grow < p.Sq) {
                             const int64_t off = base_off + grow * row_stride + ch * 8;
-                            if (ndest == 0) {
-                                *reinterpret_cast<uint4 *>(obase + off) = ov;
-                            } else {
-                                for (int dd = 0; dd < ndest; ++dd) *reinterpret_cast<uint4 *>((T *) p.fan.dest[dd] + off) = ov;
-                            }
+                            if (ndest == 0) *reinterpret_cast<uint4 *>(obase + off) = ov;
+                            else vkc_fanout_store16<T>(p.fan, off, ov);
                         }
                     }
                 } else {
@@ -672,7 +669,7 @@ namespace {
                 T    *ot = reinterpret_cast<T *>(&ov);
 #pragma unroll
                 for (int i = 0; i < 8; ++i) St<T>::st(ot + i, acc[i] * inv);
-                for (int dd = 0; dd < fan.n_dest; ++dd) *reinterpret_cast<uint4 *>((T *) fan.dest[dd] + ooff) = ov;
+                vkc_fanout_store16<T>(fan, ooff, ov);
             }
         }
         if (fan.n_dest > 0) fanout_signal(fan, gridDim.x); // every thread of the block, also the ones past the last row

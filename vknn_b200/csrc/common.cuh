@@ -197,8 +197,20 @@ struct VkcFanDev {
     void     *dest[8];
     unsigned *flag[8];
     unsigned *state; // [0] blocks that have stored, [1] fan-outs completed
+    void     *mcast; // multicast mapping of the destinations' buffers, or null
 };
 #ifdef __CUDACC__
+// One 16-byte store to every destination of a fan-out: through the multicast mapping (one multimem store, replicated by the
+// NVSwitch) when there is one, else one peer store per destination. `off` in elements of T.
+template <typename T> __device__ __forceinline__ void vkc_fanout_store16(const VkcFanDev &f, int64_t off, const uint4 &v) {
+    if (f.mcast) {
+        asm volatile("multimem.st.weak.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"((T *) f.mcast + off), "f"(__uint_as_float(v.x)),
+                     "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)), "f"(__uint_as_float(v.w))
+                     : "memory");
+    } else {
+        for (int d = 0; d < f.n_dest; ++d) *reinterpret_cast<uint4 *>((T *) f.dest[d] + off) = v;
+    }
+}
 // Called by every thread of a block after its last output store; `total` blocks take part. The stores of all blocks are
 // ordered before the flag values by the barrier, the fences around the block counter and the release stores (the last block
 // to arrive publishes).
@@ -269,5 +281,7 @@ inline int vkc_fan_to_dev(vkc_ctx *ctx, const vkc_fanout *fan, VkcFanDev *out, c
         out->dest[d] = fan->dest[d];
         out->flag[d] = fan->flag[d];
     }
+    if (fan->mcast && ((uintptr_t) fan->mcast & 15)) return vkc_fail(ctx, VKC_ERR_INVALID, "%s: the multicast address is not 16-byte aligned", who);
+    out->mcast = fan->mcast;
     return VKC_OK;
 }

@@ -707,7 +707,7 @@ namespace {
     //   warp 1 (leader):    MMA issuer; commits each stage's "empty" barrier and each tile's "accumulator full" barrier in
     //                       both CTAs; waits for "accumulator empty" arrivals from the epilogue warps of both CTAs
     //   warps 2-5:          epilogue over the CTA's own 128 accumulator rows
-    // No load is multicast: each CTA fetches what it keeps.
+    // Every CTA fetches what it keeps; no load is shared between the CTAs of a pair.
     template <int BN, int kStages> constexpr int smem_bytes_pair() {
         return kStages * (BM * BK * 2 + (BN / 2) * BK * 2) + 4 * kPBlocks * 4096 + 1024 /*align*/ + 512 /*barriers*/ + 4 * BN * 4 /*bias, per warp*/;
     }

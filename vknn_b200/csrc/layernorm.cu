@@ -103,7 +103,7 @@ namespace {
                     if (fan.n_dest == 0) {
                         *reinterpret_cast<uint4 *>(yr + e) = out;
                     } else { // the row goes to every destination (this GPU's and the peers' buffers)
-                        for (int d = 0; d < fan.n_dest; ++d) *reinterpret_cast<uint4 *>((T *) fan.dest[d] + row * norm + e) = out;
+                        vkc_fanout_store16<T>(fan, row * norm + e, out);
                     }
                 }
             }

@@ -174,7 +174,8 @@ class EncoderLayer:
         q, k, v = (hs["qkv"][:, i].permute(1, 0, 2).unsqueeze(0) for i in range(3))      # [1,Hl,T,D] views
         kbuf = gather.next_buffer()
         # output element (head h, row t, :) of this rank lands at [t, (rank*Hl + h)*D : ...] of every rank's [T, d] buffer
-        c.attn_prefill_fanout(q, k, v, gather.dests(kbuf, self.rank * dl), gather.flags(), gather.state, (T * d, D, d), scale=1.0 / (D ** 0.5))
+        c.attn_prefill_fanout(q, k, v, gather.dests(kbuf, self.rank * dl), gather.flags(), gather.state, (T * d, D, d), scale=1.0 / (D ** 0.5),
+                              mcast=gather.mcast(kbuf, self.rank * dl))
         # the out-projection's own producer warp waits for the ranks' flags (no wait kernel between the two launches)
         c.gemm(gather.buffers[kbuf], w["wo"], buf["x1"], bias=w["bo"], residual=x2, gate=gather.gate())
         c.layernorm(buf["x1"], w["ln2_g"], w["ln2_b"], buf["h"], self.eps)
@@ -201,12 +202,13 @@ class EncoderLayer:
         b = self._buf[key]
         y = out if out is not None else torch.empty_like(x_loc)
         kh = gather_h.next_buffer()
-        c.layernorm_fanout(x_loc, w["ln1_g"], w["ln1_b"], gather_h.dests(kh, lo * d), gather_h.flags(), gather_h.state, self.eps)
+        c.layernorm_fanout(x_loc, w["ln1_g"], w["ln1_b"], gather_h.dests(kh, lo * d), gather_h.flags(), gather_h.state, self.eps,
+                           mcast=gather_h.mcast(kh, lo * d))
         c.gemm(gather_h.buffers[kh], w["wqkv_local"], b["qkv"].view(T, 3 * dl), bias=w["bqkv_local"], gate=gather_h.gate())
         q, k, v = (b["qkv"][:, i].permute(1, 0, 2).unsqueeze(0) for i in range(3))
         ka = gather_att.next_buffer()
         c.attn_prefill_fanout(q, k, v, gather_att.dests(ka, self.rank * dl), gather_att.flags(), gather_att.state, (T * d, D, d),
-                              scale=1.0 / (D ** 0.5))
+                              scale=1.0 / (D ** 0.5), mcast=gather_att.mcast(ka, self.rank * dl))
         c.gemm(gather_att.buffers[ka][lo:hi], w["wo"], b["x1"], bias=w["bo"], residual=x_loc, gate=gather_att.gate())
         c.layernorm(b["x1"], w["ln2_g"], w["ln2_b"], b["h"], self.eps)
         c.gemm(b["h"], w["w1"], b["f"], bias=w["b1"], epilogue=capi.EPI_BIAS | capi.EPI_GELU_ERF)

@@ -6,6 +6,8 @@ where a head-sharded attention meets a replicated output projection).
 The reference has no multi-device code at all (single device, batch-1 planning, docs/LIMITATIONS.md:15-32)."""
 from __future__ import annotations
 
+import os
+
 
 def shard_range(n_units, rank, world):
     """Contiguous, balanced split of n_units over `world` ranks: the first n_units % world ranks get one extra."""
@@ -79,7 +81,7 @@ class PeerGather:
 
     FLAG_BYTES = 256
 
-    def __init__(self, ctx, rows, width, dtype, group=None):
+    def __init__(self, ctx, rows, width, dtype, group=None, multicast=True):
         import torch
         import torch.distributed as dist
         self.ctx, self.rows, self.width, self.dtype = ctx, rows, width, dtype
@@ -90,6 +92,59 @@ class PeerGather:
         self.buf_bytes = (rows * width * esize + 255) // 256 * 256
         self.block_bytes = 2 * self.buf_bytes + self.FLAG_BYTES
         self.device = torch.device("cuda", torch.cuda.current_device())
+        self.mcast_base, self._symm = 0, None
+        # First choice: a symmetric-memory block with an NVSwitch multicast mapping (the allocation, the exchange of handles and
+        # the multicast object are torch's; the stores are this library's kernels). One multimem store then reaches every rank,
+        # so a producer pushes its rows through NVLink once instead of once per peer. Every rank must take the same route, so
+        # the outcome is agreed on before anything is used; any failure falls back to plain peer mappings.
+        if multicast and self.world > 1 and os.environ.get("VKNN_PEER_MULTICAST", "1") != "0":
+            self._try_symmetric(group)
+        if self._symm is not None:
+            self.local = int(self.base[self.rank])
+        else:
+            self._plain_peer_mappings(ctx, group)
+        self.state = torch.zeros(2, dtype=torch.int32, device=self.device)
+        self.expected = torch.zeros(2, dtype=torch.int32, device=self.device)  # [0] fan-outs consumed so far, [1] CTA counter of a gated kernel
+        self.calls = 0
+        self.buffers = [tensor_at(self.local + k * self.buf_bytes, rows * width * esize, dtype, (rows, width), self.device) for k in range(2)]
+        self._esize = esize
+
+    def _try_symmetric(self, group):
+        import torch
+        import torch.distributed as dist
+
+        def agreed(flag):
+            oks = [None] * self.world
+            dist.all_gather_object(oks, bool(flag), group=group)
+            return all(oks)
+
+        t, hdl, ok = None, None, False
+        try:
+            import torch.distributed._symmetric_memory as symm_mem
+            from torch._C._distributed_c10d import _SymmetricMemory
+            from torch._C._autograd import DeviceType
+            ok = bool(_SymmetricMemory.has_multicast_support(DeviceType.CUDA, self.device.index))
+            if ok:
+                t = symm_mem.empty(self.block_bytes, dtype=torch.uint8, device=self.device)
+                t.zero_()
+                torch.cuda.synchronize()
+        except Exception:  # noqa: BLE001 - no symmetric memory on this system
+            ok = False
+        if not agreed(ok):  # every rank allocates, or none goes into the collective below
+            return
+        try:
+            hdl = symm_mem.rendezvous(t, group if group is not None else dist.group.WORLD)
+            ok = int(hdl.multicast_ptr) != 0 and len(hdl.buffer_ptrs) == self.world
+        except Exception:  # noqa: BLE001 - no multicast mapping could be made
+            ok = False
+        if agreed(ok):
+            self._symm = (t, hdl)
+            self.base = [int(p) for p in hdl.buffer_ptrs]
+            self.mcast_base = int(hdl.multicast_ptr)
+
+    def _plain_peer_mappings(self, ctx, group):
+        import torch
+        import torch.distributed as dist
         # Every rank takes part in both exchanges whatever happened locally, and all ranks then fail together: a rank that
         # raised on its own would leave the others waiting in a collective.
         self.local, self.base, handle, err = None, [], None, None
@@ -114,11 +169,10 @@ class PeerGather:
                 ctx.raw_free(self.local)
             raise RuntimeError("PeerGather: sharing the gather buffers failed on rank(s) %s%s"
                                % ([r for r, ok in enumerate(oks) if not ok], (": %s" % err) if err is not None else ""))
-        self.state = torch.zeros(2, dtype=torch.int32, device=self.device)
-        self.expected = torch.zeros(2, dtype=torch.int32, device=self.device)  # [0] fan-outs consumed so far, [1] CTA counter of a gated kernel
-        self.calls = 0
-        self.buffers = [tensor_at(self.local + k * self.buf_bytes, rows * width * esize, dtype, (rows, width), self.device) for k in range(2)]
-        self._esize = esize
+
+    def mcast(self, k, col_offset):
+        """Where this rank's columns start in buffer k of the multicast mapping (None without one)."""
+        return self.mcast_base + k * self.buf_bytes + col_offset * self._esize if self.mcast_base else None
 
     def next_buffer(self):
         """Index of the buffer the next fan-out writes (and the next wait makes readable)."""
@@ -142,8 +196,16 @@ class PeerGather:
         return (self.local + 2 * self.buf_bytes, self.world, self.expected)
 
     def close(self):
+        """Collective: every rank has finished using the buffers before any mapping goes away."""
         import torch
+        import torch.distributed as dist
         torch.cuda.synchronize()
+        if self._symm is not None:
+            dist.barrier()
+            torch.cuda.synchronize()
+            self.buffers, self._symm, self.mcast_base = [], None, 0
+            self.base = []
+            return
         for r, b in enumerate(self.base):
             if r != self.rank:
                 self.ctx.peer_close(b)

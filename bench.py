@@ -652,15 +652,15 @@ def plugin_e2e():
     try:
         rng = np.random.default_rng(1001)
         q, k, v = (rng.standard_normal((1, 12, 197, 64)).astype(np.float32) for _ in range(3))
-        _, cuda = vko.attention_graph(q, k, v, 0.125).run(backend="cuda", precision="low", iters=20, warmup=3)
-        _, cpu = vko.attention_graph(q, k, v, 0.125).run(backend="cpu", iters=10, warmup=1)
+        _, cuda = vko.attention_graph(q, k, v, 0.125).run(backend="cuda", precision="low", iters=20, warmup=3, timeout=300)
+        _, cpu = vko.attention_graph(q, k, v, 0.125).run(backend="cpu", iters=10, warmup=1, timeout=300)
         out["config1_attention"] = {"cuda_session_run_ms": cuda["median_ms"], "cpu_session_run_ms": cpu["median_ms"], "runs": 20,
                                     "io": "host fp32 in / out, f16 storage on the device"}
         rng = np.random.default_rng(1002)
         w = encoder_weights(rng, 768, 3072)
         x = rng.standard_normal((8, 197, 768)).astype(np.float32)
-        _, cuda = vko.encoder_layer_graph(x, w, 12).run(backend="cuda", precision="low", iters=20, warmup=3, tuning="fast")
-        _, cpu = vko.encoder_layer_graph(x[:1], w, 12).run(backend="cpu", iters=1, warmup=0)
+        _, cuda = vko.encoder_layer_graph(x, w, 12).run(backend="cuda", precision="low", iters=20, warmup=3, tuning="fast", timeout=300)
+        _, cpu = vko.encoder_layer_graph(x[:1], w, 12).run(backend="cpu", iters=1, warmup=0, timeout=300)
         out["config2_layer"] = {"cuda_session_run_ms": cuda["median_ms"], "tok_s": 8 * 197 / (cuda["median_ms"] * 1e-3), "runs": 20,
                                 "cpu_session_run_ms_one_image": cpu["median_ms"], "cpu_tok_s": 197 / (cpu["median_ms"] * 1e-3),
                                 "io": "host fp32 in / out (4.8 MB each way), fp16 weights and activations on the device"}

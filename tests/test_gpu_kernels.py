@@ -187,6 +187,39 @@ def test_attention_shapes(ctx, impl, causal, B, Hq, Hkv, Sq, Skv, D):
 
 
 @pytest.mark.parametrize("dt", ["f16", "bf16"])
+@pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("jump", [7.0, 12.0, 30.0, 100.0])
+def test_attention_maximum_grows_in_a_late_key_tile(ctx, dt, D, jump):
+    """The tensor-core kernel raises its running maximum lazily (only when a key tile exceeds it by more than 2^8) and rescales
+    the output accumulator in tensor memory when it does. A key in a later tile whose score exceeds everything before it by
+    `jump` nats must still give the oracle's answer, below and above that threshold, with and without the causal mask.
+    Different rows meet their dominant key in different tiles, some rows in none. Rows that lock onto one key return that
+    key's V row: the comparison is 1e-2 wherever |y| <= 2 and 3 ulps of the rounded oracle output above that (P itself is
+    rounded to the storage type)."""
+    tdt = DT[dt]
+    rng = np.random.default_rng(int(jump) * 10 + D)
+    B, H, S = 1, 2, 700
+    scale = 1.0 / np.sqrt(D)
+    q = rng.standard_normal((B, H, S, D)) * 0.5
+    k = rng.standard_normal((B, H, S, D)) * 0.5
+    v = rng.standard_normal((B, H, S, D)) * 0.5  # rows torn between two dominant keys see P's own rounding times |v1 - v2|
+    # dominant keys at positions 300 (third tile) and 650 (sixth): aligned with the queries of row groups so that the score of
+    # (row, key) exceeds the rest by about `jump`
+    for pos, rows in ((300, slice(0, 350)), (650, slice(200, 500))):
+        direction = rng.standard_normal(D)
+        direction /= np.linalg.norm(direction)
+        amp = np.sqrt(jump / scale)
+        k[:, :, pos] = direction * amp
+        q[:, :, rows] += direction * amp
+    q, k, v = (round_to(a, tdt) for a in (q, k, v))
+    ref = vko.attention(q, k, v, scale)
+    got = run_attn(ctx, q, k, v, scale, dt, impl=vknn_b200.IMPL_TCGEN05)
+    assert_storage(got, ref, dt, "late dominant key, jump %g" % jump, ulps=3, floor=2.0)
+    got = run_attn(ctx, q, k, v, scale, dt, causal=True, impl=vknn_b200.IMPL_TCGEN05)
+    assert_storage(got, vko.attention(q, k, v, scale, causal=True), dt, "late dominant key, causal, jump %g" % jump, ulps=3, floor=2.0)
+
+
+@pytest.mark.parametrize("dt", ["f16", "bf16"])
 @pytest.mark.parametrize("B,Hq,Hkv,Sq,Skv", [(1, 2, 2, 1100, 1100), (2, 4, 2, 777, 1303), (1, 16, 16, 300, 2738)])
 def test_attention_head64_key_range_split(ctx, dt, B, Hq, Hkv, Sq, Skv):
     """Head size 64, no mask, at least eight key tiles and a shallow grid: the tensor-core path cuts the key range in two

@@ -17,7 +17,7 @@ def test_null_context_is_refused_without_compute():
     lib = vknn_b200.load_library()
     assert lib.vkc_gemm(None, None, None, None, None, None, 1, 1, 1, 1, 0, 0, 0, 1, 1, 1, 0, 0, 0, None) == -1
     assert lib.vkc_layernorm(None, None, None, None, None, 1, 1, 1e-5, 0, None) == -1
-    assert lib.vkc_attn_decode_workspace_bytes(32, 32, 8, 8192, 128) == 32 * 32 * 16 * 130 * 4
+    assert lib.vkc_attn_decode_workspace_bytes(32, 32, 8, 8192, 128) == 32 * 32 * 18 * 130 * 4 + 32 * 8 * 4
     assert lib.vkc_attn_decode_workspace_bytes(0, 32, 8, 8192, 128) == 0
 
 

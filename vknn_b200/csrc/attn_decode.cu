@@ -14,7 +14,8 @@
 #include <cstdlib>
 
 int vkc_attn_decode_tcgen05(vkc_ctx *ctx, const void *Q, const void *Kc, const void *Vc, int64_t B, int64_t Hq, int64_t Hkv, int64_t Lmax, int64_t D,
-                            const int32_t *kv_len, float scale, float *part_ml, float *part_o, int chunk, int parts_stride, int dtype, cudaStream_t st);
+                            const int32_t *kv_len, float scale, float *part_ml, float *part_o, int *nslots, int min_tiles, int parts_stride, int dtype,
+                            cudaStream_t st);
 
 namespace {
 
@@ -26,9 +27,10 @@ namespace {
         return chunk;
     }
 
-    // Partial slots per (sequence, query head) the scratch must hold: enough for either kernel form (the
-    // tensor-core form uses chunks twice as long with two slots each).
-    __host__ __device__ inline int decode_slots(int64_t Lmax, int chunk) { return 2 * (int) ((Lmax + 2 * chunk - 1) / (2 * chunk)); }
+    // Partial slots per (sequence, query head) the scratch must hold: enough for either kernel form. The tensor-core
+    // form gives every CTA an equal run of at least 2 * chunk keys, wherever the run starts, so a (sequence, kv head)
+    // unit is cut into at most ceil(Lmax / (2 * chunk)) + 1 pieces, with two slots each.
+    __host__ __device__ inline int decode_slots(int64_t Lmax, int chunk) { return 2 * ((int) ((Lmax + 2 * chunk - 1) / (2 * chunk)) + 1); }
 
     template <typename T> __device__ __forceinline__ void unpack8(const uint4 &raw, float (&f)[8]);
     template <> __device__ __forceinline__ void unpack8<__half>(const uint4 &raw, float (&f)[8]) {
@@ -227,12 +229,13 @@ namespace {
     // One CTA per (sequence, query head): merges the per-chunk partials and writes the output row.
     template <typename T>
     __global__ void attn_decode_combine_kernel(const float *__restrict__ part_ml, const float *__restrict__ part_o, T *__restrict__ O,
-                                               const int32_t *__restrict__ kv_len, int64_t Hq, int64_t Lmax, int D, int chunk, int parts,
-                                               int max_splits) {
+                                               const int32_t *__restrict__ kv_len, int64_t Hq, int64_t Lmax, int D, int chunk,
+                                               const int *__restrict__ nslots, int G, int max_splits) {
         const int b = blockIdx.y, hq = blockIdx.x;
         int64_t   len = kv_len ? (int64_t) kv_len[b] : Lmax;
         if (len > Lmax) len = Lmax;
-        const int     ns  = parts * (int) ((len + chunk - 1) / chunk); // partial slots this sequence filled
+        // partial slots this (sequence, head) filled: one per chunk, or what the tensor-core form recorded for the kv head
+        const int     ns  = len <= 0 ? 0 : (nslots ? nslots[(int64_t) b * (Hq / G) + hq / G] : (int) ((len + chunk - 1) / chunk));
         const int64_t row = ((int64_t) b * Hq + hq) * max_splits;
         float         mt  = -INFINITY;
         for (int s = 0; s < ns; ++s) mt = fmaxf(mt, part_ml[(row + s) * 2]);
@@ -255,20 +258,16 @@ namespace {
         const int     chunk      = decode_chunk(B, Hkv, Lmax);
         const int     max_splits = decode_slots(Lmax, chunk); // slot stride; the SIMT form fills ceil(Lmax/chunk) of them
         constexpr int D          = CH * 64;
-        int           eff_chunk = chunk, parts = 1;
         float        *part_ml    = ws;
         float        *part_o     = ws + (size_t) B * Hq * max_splits * 2;
+        int          *nslots     = reinterpret_cast<int *>(part_o + (size_t) B * Hq * max_splits * D); // [B][Hkv], tensor-core form only
         const float   sl2        = scale * 1.4426950408889634f;
         dim3          grid((unsigned) max_splits, (unsigned) Hkv, (unsigned) B);
         bool          split_done = false;
         if (ctx->impl != VKC_IMPL_SIMT) {
             const int dtype = std::is_same<T, __half>::value ? VKC_F16 : VKC_BF16;
-            int       rc    = vkc_attn_decode_tcgen05(ctx, Q, Kc, Vc, B, Hq, Hkv, Lmax, D, kv_len, scale, part_ml, part_o, 2 * chunk, max_splits, dtype, st);
-            if (rc == VKC_OK) {
-                split_done = true;
-                eff_chunk  = 2 * chunk;
-                parts      = 2;
-            }
+            int       rc    = vkc_attn_decode_tcgen05(ctx, Q, Kc, Vc, B, Hq, Hkv, Lmax, D, kv_len, scale, part_ml, part_o, nslots, 2 * chunk / 128, max_splits, dtype, st);
+            if (rc == VKC_OK) split_done = true;
             else if (rc != VKC_ERR_UNSUPPORTED || ctx->impl == VKC_IMPL_TCGEN05) return rc;
         }
 #define VKC_DEC(G_)                                                                                                                    \
@@ -287,7 +286,8 @@ namespace {
             if (rc) return rc;
         }
         dim3 cgrid((unsigned) Hq, (unsigned) B);
-        attn_decode_combine_kernel<T><<<cgrid, D < 128 ? D : 128, 0, st>>>(part_ml, part_o, (T *) O, kv_len, Hq, Lmax, D, eff_chunk, parts, max_splits);
+        attn_decode_combine_kernel<T><<<cgrid, D < 128 ? D : 128, 0, st>>>(part_ml, part_o, (T *) O, kv_len, Hq, Lmax, D, chunk, split_done ? nslots : nullptr, G,
+                                                                           max_splits);
         return vkc_post_launch(ctx, "attn_decode_combine");
     }
 
@@ -307,7 +307,7 @@ extern "C" size_t vkc_attn_decode_workspace_bytes(int64_t B, int64_t Hq, int64_t
     if (B <= 0 || Hq <= 0 || Hkv <= 0 || Lmax <= 0 || D <= 0) return 0;
     const int    chunk      = decode_chunk(B, Hkv, Lmax);
     const size_t max_splits = (size_t) decode_slots(Lmax, chunk);
-    return (size_t) B * (size_t) Hq * max_splits * (size_t) (D + 2) * sizeof(float);
+    return (size_t) B * (size_t) Hq * max_splits * (size_t) (D + 2) * sizeof(float) + (size_t) B * (size_t) Hkv * sizeof(int);
 }
 
 extern "C" int vkc_attn_decode(vkc_ctx *ctx, const void *Q, const void *Kc, const void *Vc, void *O, int64_t B, int64_t Hq, int64_t Hkv,

@@ -8,7 +8,8 @@
 //   O^T [128 dims x 16]  += V_tile^T [128 dims x 128 keys] . P^T [128 keys x 16]   (A = V tile read MN-major)
 //
 // so one 128-key tile costs 16 small MMAs and the per-key work left for the CUDA cores is one exp2 per (key,
-// head). Persistent CTAs (one per SM) walk a static round-robin list of work items (sequence, chunk of the
+// head). Persistent CTAs (one per SM) each take an equal share of the key tiles of all (sequence, kv head) units,
+// cut into work items at the unit boundaries (sequence, stretch of the
 // cache, kv head); the TMA producer runs ahead across item boundaries through a 3-stage ring (192 KB in flight
 // per SM).
 //
@@ -59,42 +60,56 @@ namespace {
     struct DecParams {
         float         *part_ml, *part_o;
         const int32_t *kv_len;
-        int            B, Hkv, G, chunk, parts_stride; // parts_stride = partial slots per (sequence, query head)
+        int            B, Hkv, G, min_quota, parts_stride; // parts_stride = partial slots per (sequence, query head)
+        int           *nslots;                             // [B][Hkv]: partial slots the (sequence, kv head) filled
         int64_t        Lmax;
         float          scale_log2;
         int           *dev_err;
     };
 
-    // Work items are numbered sequence-major: item = prefix[b] + split * Hkv + hk. CTA c takes items c, c + grid, ...
+    // Work distribution. The 128-key tiles of all (sequence, kv head) units are numbered in one line, sequence-major
+    // (prefix[b] = tiles before sequence b; within a sequence kv head after kv head). CTA c takes the `quota` tiles
+    // [c * quota, (c + 1) * quota) of that line, so every CTA streams the same number of bytes whatever the sequence
+    // lengths are, and meets at most a handful of unit boundaries. An item is the stretch of a CTA's range that lies
+    // in one unit; its partials go to the unit's slot pair number (c - CTA of the unit's first tile).
     struct Item {
         int     b, hk, split, ntiles;
         int64_t start, end;
-        bool    valid;
+        bool    valid, last; // last: the item holds the unit's final tile
     };
     __device__ __forceinline__ int64_t seq_len(const DecParams &p, int b) {
         int64_t len = p.kv_len ? (int64_t) p.kv_len[b] : p.Lmax;
         if (len > p.Lmax) len = p.Lmax;
         return len < 0 ? 0 : len;
     }
-    __device__ __forceinline__ Item find_item(const DecParams &p, const int *prefix, int64_t idx) {
+    __device__ __forceinline__ int tile_quota(const DecParams &p, const int *prefix) {
+        const int q = (prefix[p.B] + (int) gridDim.x - 1) / (int) gridDim.x;
+        return q > p.min_quota ? q : p.min_quota;
+    }
+    // The item that starts at tile `pos` of the line; the CTA's range ends at `pos1`.
+    __device__ __forceinline__ Item find_item(const DecParams &p, const int *prefix, int pos, int pos1, int quota) {
         Item it;
         it.valid = false;
-        if (idx >= (int64_t) prefix[p.B]) return it;
-        int lo = 0, hi = p.B - 1; // last b with prefix[b] <= idx
+        if (pos >= pos1) return it;
+        int lo = 0, hi = p.B - 1; // last b with prefix[b] <= pos
         while (lo < hi) {
             const int mid = (lo + hi + 1) >> 1;
-            if ((int64_t) prefix[mid] <= idx) lo = mid;
+            if (prefix[mid] <= pos) lo = mid;
             else hi = mid - 1;
         }
-        const int64_t len = seq_len(p, lo);
-        const int64_t r   = idx - prefix[lo];
-        it.b      = lo;
-        it.split  = (int) (r / p.Hkv);
-        it.hk     = (int) (r % p.Hkv);
-        it.start  = (int64_t) it.split * p.chunk;
-        it.end    = it.start + p.chunk < len ? it.start + p.chunk : len;
-        it.ntiles = (int) ((it.end - it.start + TK - 1) / TK);
-        it.valid  = true;
+        const int64_t len   = seq_len(p, lo);
+        const int     tiles = (int) ((len + TK - 1) / TK);
+        const int     r     = pos - prefix[lo];
+        it.b                = lo;
+        it.hk               = r / tiles;
+        const int tile      = r - it.hk * tiles;
+        const int left      = tiles - tile, room = pos1 - pos;
+        it.ntiles           = left < room ? left : room;
+        it.last             = left <= room;
+        it.split            = pos / quota - (prefix[lo] + it.hk * tiles) / quota;
+        it.start            = (int64_t) tile * TK;
+        it.end              = it.start + (int64_t) it.ntiles * TK < len ? it.start + (int64_t) it.ntiles * TK : len;
+        it.valid            = true;
         return it;
     }
 
@@ -137,7 +152,7 @@ namespace {
             ptx::prefetch_tmap(&tmK);
             ptx::prefetch_tmap(&tmV);
         }
-        for (int b = threadIdx.x; b < p.B; b += kThreads) prefix[b + 1] = (int) (((seq_len(p, b) + p.chunk - 1) / p.chunk) * p.Hkv);
+        for (int b = threadIdx.x; b < p.B; b += kThreads) prefix[b + 1] = (int) (((seq_len(p, b) + TK - 1) / TK) * p.Hkv);
         if (warp == 1) {
             ptx::tmem_alloc(base + oCtl, kTmemCols);
             ptx::tmem_relinquish();
@@ -154,16 +169,21 @@ namespace {
         }
         __syncthreads();
         ptx::tc_fence_after();
-        const uint32_t tmem = (uint32_t) ctl[0];
+        const uint32_t tmem  = (uint32_t) ctl[0];
+        const int      quota = tile_quota(p, prefix);
+        const int      pos0  = (int) blockIdx.x * quota;
+        const int      pos1  = pos0 + quota < prefix[p.B] ? pos0 + quota : prefix[p.B];
 
         if (warp == 0) {
             // ------------------------------------------------------------------ producer
             if (ptx::elect_one()) {
                 int64_t g  = 0; // tile counter of this CTA, across items
                 bool    ok = true;
+                int     pos = pos0;
                 for (int64_t ii = 0; ok; ++ii) {
-                    const Item it = find_item(p, prefix, (int64_t) blockIdx.x + ii * gridDim.x);
+                    const Item it = find_item(p, prefix, pos, pos1, quota);
                     if (!it.valid) break;
+                    pos += it.ntiles;
                     const int qb = (int) (ii & 1);
                     ok = ptx::mbar_wait(bar(bQE + qb), ((ii >> 1) & 1) ^ 1, ctl + 1, p.dev_err);
                     if (!ok) break;
@@ -194,7 +214,7 @@ namespace {
                 struct Cur {
                     Item    it;
                     int64_t ii, g;
-                    int     t;
+                    int     t, pos; // pos: the item's first tile in the line
                 };
                 auto advance = [&](const Cur &c) -> Cur {
                     Cur n = c;
@@ -202,9 +222,10 @@ namespace {
                     if (c.t + 1 < c.it.ntiles) {
                         n.t = c.t + 1;
                     } else {
-                        n.ii = c.ii + 1;
-                        n.t  = 0;
-                        n.it = find_item(p, prefix, (int64_t) blockIdx.x + n.ii * gridDim.x);
+                        n.ii  = c.ii + 1;
+                        n.t   = 0;
+                        n.pos = c.pos + c.it.ntiles;
+                        n.it  = find_item(p, prefix, n.pos, pos1, quota);
                     }
                     return n;
                 };
@@ -251,8 +272,8 @@ namespace {
                 };
                 // Q.K^T runs two tiles ahead of P.V so that both softmax groups always have a tile to work on
                 Cur c0, c1, c2;
-                c0.ii = 0, c0.g = 0, c0.t = 0;
-                c0.it = find_item(p, prefix, (int64_t) blockIdx.x);
+                c0.ii = 0, c0.g = 0, c0.t = 0, c0.pos = pos0;
+                c0.it = find_item(p, prefix, pos0, pos1, quota);
                 bool ok = c0.it.valid && issue_qk(c0);
                 if (ok) {
                     c1 = advance(c0);
@@ -285,9 +306,12 @@ namespace {
             int            pc    = 0; // items this group has taken part in
             int64_t        cnt   = 0; // tiles this group has processed
             bool           ok    = true;
-            for (int64_t ii = 0; ok; ++ii) {
-                const Item it = find_item(p, prefix, (int64_t) blockIdx.x + ii * gridDim.x);
+            int            pos   = pos0;
+            while (ok) {
+                const Item it = find_item(p, prefix, pos, pos1, quota);
                 if (!it.valid) break;
+                pos += it.ntiles;
+                if (it.last && wg == 0 && r == 0) p.nslots[it.b * p.Hkv + it.hk] = 2 * (it.split + 1);
                 const int64_t prow = ((int64_t) it.b * Hq + (int64_t) it.hk * G) * p.parts_stride + (int64_t) it.split * 2 + wg;
                 if (wg >= it.ntiles) {
                     // this group has no tile in the item: an empty partial (weight 0 in the merge)
@@ -450,16 +474,20 @@ namespace {
 
 } // namespace
 
-// Launches the split kernel only; the caller runs the merge kernel. `chunk` keys per work item (a multiple of
-// 256), two partial slots per chunk (one per softmax group), `parts_stride` slots per (sequence, query head).
+// Launches the split kernel only; the caller runs the merge kernel. Every CTA takes at least `min_tiles` 128-key
+// tiles; a (sequence, kv head) unit is therefore cut into at most ceil(tiles / min_tiles) + 1 items, each of which fills
+// two partial slots (one per softmax group). `parts_stride` slots per (sequence, query head); nslots[b][hk] receives the
+// number of slots the unit filled (nothing is written for an empty sequence).
 // Returns VKC_ERR_UNSUPPORTED for shapes this form does not cover (the SIMT form then takes over).
 int vkc_attn_decode_tcgen05(vkc_ctx *ctx, const void *Q, const void *Kc, const void *Vc, int64_t B, int64_t Hq, int64_t Hkv, int64_t Lmax, int64_t D,
-                            const int32_t *kv_len, float scale, float *part_ml, float *part_o, int chunk, int parts_stride, int dtype,
-                            cudaStream_t st) {
+                            const int32_t *kv_len, float scale, float *part_ml, float *part_o, int *nslots, int min_tiles, int parts_stride,
+                            int dtype, cudaStream_t st) {
     const int64_t G = Hq / Hkv;
-    if (D != DH || G > NPAD || (dtype != VKC_F16 && dtype != VKC_BF16) || !(scale > 0.f) || chunk % TK != 0 || B > kMaxPrefix)
+    if (D != DH || G > NPAD || (dtype != VKC_F16 && dtype != VKC_BF16) || !(scale > 0.f) || min_tiles < 1 || B > kMaxPrefix)
         return vkc_fail(ctx, VKC_ERR_UNSUPPORTED, "attn_decode_tcgen05: needs head dim 128, at most 16 query heads per kv head, 16-bit storage");
-    if (Lmax > INT32_MAX - TK || B * Hq > INT32_MAX || B * Hkv * ((Lmax + chunk - 1) / chunk) > INT32_MAX)
+    const int64_t max_tiles = B * Hkv * ((Lmax + TK - 1) / TK);
+    if (Lmax > INT32_MAX - TK || B * Hq > INT32_MAX || max_tiles > INT32_MAX / 2 ||
+        2 * (((Lmax + TK - 1) / TK + min_tiles - 1) / min_tiles + 1) > parts_stride)
         return vkc_fail(ctx, VKC_ERR_UNSUPPORTED, "attn_decode_tcgen05: extent too large");
     CUtensorMap tq, tk, tv;
     int         rc;
@@ -478,11 +506,11 @@ int vkc_attn_decode_tcgen05(vkc_ctx *ctx, const void *Q, const void *Kc, const v
     }
     DecParams p;
     p.part_ml = part_ml, p.part_o = part_o, p.kv_len = kv_len;
-    p.B = (int) B, p.Hkv = (int) Hkv, p.G = (int) G, p.chunk = chunk, p.parts_stride = parts_stride, p.Lmax = Lmax;
+    p.B = (int) B, p.Hkv = (int) Hkv, p.G = (int) G, p.min_quota = min_tiles, p.nslots = nslots, p.parts_stride = parts_stride, p.Lmax = Lmax;
     p.scale_log2 = scale * 1.4426950408889634f;
     p.dev_err    = ctx->dev_err;
-    const int64_t max_items = B * Hkv * ((Lmax + chunk - 1) / chunk);
-    const int     grid      = (int) (max_items < ctx->sm_count ? max_items : ctx->sm_count);
+    const int64_t max_ctas = (max_tiles + min_tiles - 1) / min_tiles;
+    const int     grid     = (int) (max_ctas < ctx->sm_count ? max_ctas : ctx->sm_count);
 #define VKC_DTC(T_)                                                                                                  \
     do {                                                                                                             \
         auto kern_ = attn_decode_tc_kernel<T_>;                                                                      \

@@ -58,15 +58,104 @@ namespace {
         int            causal;
         const int32_t *kv_len;
         int           *dev_err;
-        // key-range splitting (shallow grids): CTA blockIdx.x % kv_splits handles its share of the key tiles and leaves a
-        // partial per row — the normalised output in the storage type and (running maximum, row sum) — for the merge kernel
-        int    kv_splits;
-        void  *part_o;  // [kv_splits][B][Hq][Sq][D] storage type
-        float *part_ml; // [kv_splits][B][Hq][Sq][2]
+        // Work distribution. A unit is one group of QT query tiles of one (batch, head), unit u = (b * Hq + h) * nq + group; it
+        // needs `steps` key tiles.
+        // balanced == 0: one CTA per unit, grid (groups, Hq, B).
+        // balanced == 1 (every unit needs the same number of key tiles: no causal mask, no per-sequence lengths): a
+        // one-dimensional grid of persistent CTAs. CTA c first takes `rounds` whole units, c, c + grid, c + 2 grid, ... (at any
+        // moment the CTAs work on neighbouring units, so the K and V tiles they stream are the same few heads' and stay in
+        // L2). The units left over, fewer than the grid has CTAs, are laid end to end as one line of `total` key-tile steps and
+        // CTA c takes the steps [c * quota, (c + 1) * quota) of it: the same amount of work for every CTA whatever the number
+        // of units is. The stretch of a CTA's range that lies in one unit is an item. An item that covers its whole unit stores
+        // final rows; otherwise it leaves a partial per row — the normalised output in the storage type and (running maximum,
+        // row sum) — in the CTA's slot 0 (the unit began in an earlier CTA's range) or slot 1 (it began in this one), and the
+        // merge kernel joins the partials of each left-over unit.
+        int     balanced, nq, steps, quota, rounds;
+        int     total;   // steps in the line of left-over units
+        void   *part_o;  // [CTAs][2][QT * BM][D] storage type
+        float  *part_ml; // [CTAs][2][QT * BM][2]
         // output fan-out (n_dest > 0): every output row goes to dest[0..n_dest) instead of O; when the grid's last block has
-        // stored, flag[d] (a word in destination d's memory) receives this rank's count of completed fan-outs
+        // stored (of the merge kernel in the balanced form), flag[d] (a word in destination d's memory) receives this rank's
+        // count of completed fan-outs
         FanOut fan;
     };
+
+    // One item of a CTA's work and what each of its query tiles has to do in it.
+    template <int QT> struct Work {
+        bool    valid, last; // last: the CTA has nothing to do after this item
+        int     b, h, qg;    // the unit
+        int     j0;       // first key tile of the item; tile counts below are relative to it
+        int     slot;     // partial slot of this CTA (0 or 1), or -1: the item covers the whole unit and stores final rows
+        int     adv;      // how far the item moves the CTA along the line
+        int64_t m0, len;  // first query row of the unit, visible key length
+        int     n_t[QT], n_max;
+    };
+    // `pos`: the key-tile steps the CTA has behind it when the item starts.
+    template <int QT> __device__ __forceinline__ Work<QT> work_at(const AttnParams &p, int pos) {
+        Work<QT> w;
+        int      cnt;
+        if (p.balanced) {
+            int       u;
+            const int lp0 = (int) blockIdx.x * p.quota; // this CTA's stretch of the line of left-over units: [lp0, lp1)
+            const int lp1 = lp0 + p.quota < p.total ? lp0 + p.quota : p.total;
+            if (pos < p.rounds * p.steps) { // a whole unit of the round-robin part
+                u      = (pos / p.steps) * (int) gridDim.x + (int) blockIdx.x;
+                w.j0   = 0;
+                cnt    = p.steps;
+                w.slot = -1;
+            } else {
+                const int lp  = lp0 + (pos - p.rounds * p.steps);
+                w.valid       = lp < lp1;
+                if (!w.valid) return w;
+                const int ur   = lp / p.steps;
+                w.j0           = lp - ur * p.steps;
+                const int left = p.steps - w.j0, room = lp1 - lp;
+                cnt            = left < room ? left : room;
+                w.slot         = cnt == p.steps ? -1 : (ur * p.steps < lp0 ? 0 : 1);
+                u              = p.rounds * (int) gridDim.x + ur;
+            }
+            w.valid      = true;
+            w.adv        = cnt;
+            w.last       = pos + cnt >= p.rounds * p.steps && lp0 + (pos + cnt - p.rounds * p.steps) >= lp1;
+            w.qg         = u % p.nq;
+            const int bh = u / p.nq;
+            w.h          = bh % (int) p.Hq;
+            w.b          = bh / (int) p.Hq;
+        } else {
+            w.valid = pos < 1;
+            if (!w.valid) return w;
+            w.b = blockIdx.z, w.h = blockIdx.y;
+            w.qg   = p.causal ? (int) gridDim.x - 1 - (int) blockIdx.x : (int) blockIdx.x; // heavy (late) query tiles first when causal
+            w.j0   = 0;
+            cnt    = INT32_MAX;
+            w.slot = -1;
+            w.adv  = 1;
+            w.last = true;
+        }
+        w.m0  = (int64_t) w.qg * (QT * BM);
+        w.len = p.kv_len ? (int64_t) p.kv_len[w.b] : p.Skv;
+        if (w.len > p.Skv) w.len = p.Skv;
+        if (w.len < 0) w.len = 0;
+        w.n_max = 0;
+#pragma unroll
+        for (int t = 0; t < QT; ++t) {
+            int64_t       kend  = w.len;
+            const int64_t first = w.m0 + (int64_t) t * BM;
+            if (first >= p.Sq) kend = 0; // tile entirely past the end of the query sequence
+            if (p.causal && kend > 0) {
+                int64_t last = first + BM - 1;
+                if (last > p.Sq - 1) last = p.Sq - 1;
+                const int64_t lim = last + (p.Skv - p.Sq) + 1;
+                if (lim < kend) kend = lim;
+                if (kend < 0) kend = 0;
+            }
+            int n    = (int) ((kend + BN - 1) / BN) - w.j0; // key tiles the query tile needs, from the item's first on
+            n        = n < 0 ? 0 : (n > cnt ? cnt : n);
+            w.n_t[t] = n;
+            w.n_max  = n > w.n_max ? n : w.n_max;
+        }
+        return w;
+    }
 
     template <int D, int KS, int VS, int QT> struct Smem {
         static constexpr uint32_t Q_BYTES  = BM * D * 2; // per query tile
@@ -75,8 +164,8 @@ namespace {
         static constexpr uint32_t oK   = oQ + QT * Q_BYTES;
         static constexpr uint32_t oV   = oK + KS * KV_BYTES;
         static constexpr uint32_t oBar = oV + VS * KV_BYTES;
-        // barriers: q_full, k_full[KS], k_empty[KS], v_full[VS], v_empty[VS], s_full[QT], p_full[QT][kPParts], o_final[QT]
-        static constexpr int nBar = 1 + 2 * KS + 2 * VS + QT * (2 + kPParts);
+        // barriers: q_full, q_read, q_staged, k_full[KS], k_empty[KS], v_full[VS], v_empty[VS], s_full[QT], p_full[QT][kPParts], o_final[QT]
+        static constexpr int nBar = 3 + 2 * KS + 2 * VS + QT * (2 + kPParts);
         static constexpr uint32_t oCtl  = oBar + 8 * nBar;
         static constexpr uint32_t total = oCtl + 16 + 1024;
     };
@@ -183,54 +272,15 @@ namespace {
         const uint32_t sQ = base + L::oQ, sK = base + L::oK, sV = base + L::oV, sBar = base + L::oBar;
         volatile int  *ctl = (volatile int *) (gbase + L::oCtl); // ctl[0] = tmem base, ctl[1] = abort flag
         auto           bar = [&](int i) { return sBar + 8u * (uint32_t) i; };
-        constexpr int  bQ = 0, bKF = 1, bKE = 1 + KS, bVF = 1 + 2 * KS, bVE = 1 + 2 * KS + VS, bSF = 1 + 2 * KS + 2 * VS, bPF = bSF + QT,
+        constexpr int  bQ = 0, bQE = 1, bQS = 2, bKF = 3, bKE = bKF + KS, bVF = bKE + KS, bVE = bVF + VS, bSF = bVE + VS, bPF = bSF + QT,
                       bOF = bPF + QT * kPParts;
 
         const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-        const int b = blockIdx.z, h = blockIdx.y, bx = (int) blockIdx.x / p.kv_splits;
-        const int split = (int) blockIdx.x % p.kv_splits, nbx = (int) gridDim.x / p.kv_splits;
-        const int hk = h / (int) (p.Hq / p.Hkv);
-        // heavy (late) query tiles first when causal
-        const int     mt = p.causal ? nbx - 1 - bx : bx;
-        const int64_t m0 = (int64_t) mt * (kQTiles * BM);
-
-        int64_t len = p.kv_len ? (int64_t) p.kv_len[b] : p.Skv;
-        if (len > p.Skv) len = p.Skv;
-        if (len < 0) len = 0;
-        // key tiles each query tile needs
-        int n_t[kQTiles];
-#pragma unroll
-        for (int t = 0; t < kQTiles; ++t) {
-            int64_t kend = len;
-            const int64_t first = m0 + (int64_t) t * BM;
-            if (first >= p.Sq) kend = 0; // tile entirely past the end of the query sequence
-            if (p.causal && kend > 0) {
-                int64_t last = first + BM - 1;
-                if (last > p.Sq - 1) last = p.Sq - 1;
-                const int64_t lim = last + (p.Skv - p.Sq) + 1;
-                if (lim < kend) kend = lim;
-                if (kend < 0) kend = 0;
-            }
-            n_t[t] = (int) ((kend + BN - 1) / BN);
-        }
-        int n_max = 0;
-#pragma unroll
-        for (int t = 0; t < kQTiles; ++t) n_max = n_t[t] > n_max ? n_t[t] : n_max;
-        // this CTA's share of the key tiles: [jb, jb + per); from here on tile counts and loop indices are local to it
-        int jb = 0;
-        if (p.kv_splits > 1) {
-            const int per = (n_max + p.kv_splits - 1) / p.kv_splits;
-            jb            = split * per;
-            n_max         = 0;
-#pragma unroll
-            for (int t = 0; t < kQTiles; ++t) {
-                n_t[t] = n_t[t] - jb < 0 ? 0 : (n_t[t] - jb > per ? per : n_t[t] - jb);
-                n_max  = n_t[t] > n_max ? n_t[t] : n_max;
-            }
-        }
+        const Work<QT> w_first = work_at<QT>(p, 0); // the first item, looked up while thread 0 sets the barriers up
 
         if (threadIdx.x == 0) {
-            for (int i = 0; i < L::nBar; ++i) ptx::mbar_init(bar(i), (i >= bPF && i < bOF) ? 4 : 1); // p_full: one arrival per softmax warp
+            for (int i = 0; i < L::nBar; ++i) // p_full: one arrival per softmax warp of the tile; q_staged: one per softmax warp
+                ptx::mbar_init(bar(i), (i >= bPF && i < bOF) ? 4 : (i == bQS ? 4 * QT : 1));
             ctl[1] = 0;
             ptx::fence_mbar_init();
             ptx::prefetch_tmap(&tmQ);
@@ -246,29 +296,50 @@ namespace {
         ptx::tc_fence_after();
         const uint32_t tmem = (uint32_t) ctl[0];
         vkc_grid_dep_wait(); // set-up above overlaps the previous kernel's tail; global memory from here on
-        vkc_grid_dep_launch();
+        if (!p.balanced) vkc_grid_dep_launch(); // (the balanced form is followed by its merge kernel, which has nothing to set up early)
 
         if (warp >= kWarpTma) {
           ptx::setmaxnreg_dec<kRegsControl>();
           if (warp == kWarpTma) {
             // ------------------------------------------------------------------ TMA producer
-            if (n_max > 0 && ptx::elect_one()) {
-                ptx::mbar_expect_tx(bar(bQ), kQTiles * L::Q_BYTES);
+            // Key tiles are numbered g = 0, 1, ... over all items of the CTA; ring stage g & 1, phase g >> 1. The Q tiles of the
+            // next item are loaded as soon as every Q.K^T MMA of the current one has read them (q_read) and the epilogue no
+            // longer uses their area for staging (q_staged) — normally a whole key tile before the current item ends.
+            if (ptx::elect_one()) {
+                int  cq = 0; // Q loads issued
+                int  g  = 0;
+                bool ok = true;
+                const int hq_per_kv = (int) (p.Hq / p.Hkv);
+                Work<QT>  w = w_first;
+                for (int pos = 0; ok; w = work_at<QT>(p, pos)) {
+                    if (!w.valid) break;
+                    pos += w.adv;
+                    const int hk = w.h / hq_per_kv;
+                    for (int j = 0; j < w.n_max; ++j, ++g) {
+                        const int      st = g & 1;
+                        const uint32_t ph = (uint32_t) ((g >> 1) & 1);
+                        if (!(ok = ptx::mbar_wait(bar(bKE + st), ph ^ 1, ctl + 1, p.dev_err))) break;
+                        ptx::mbar_expect_tx(bar(bKF + st), L::KV_BYTES);
 #pragma unroll
-                for (int t = 0; t < kQTiles; ++t)
+                        for (int c = 0; c < DCH; ++c) ptx::tma_load_4d(sK + st * L::KV_BYTES + c * (BN * 128), &tmK, c * 64, (w.j0 + j) * BN, hk, w.b, bar(bKF + st));
+                        if (j == 0) {
+                            if (cq > 0) {
+                                const uint32_t pq = (uint32_t) ((cq - 1) & 1);
+                                if (!(ok = ptx::mbar_wait(bar(bQE), pq, ctl + 1, p.dev_err) && ptx::mbar_wait(bar(bQS), pq, ctl + 1, p.dev_err))) break;
+                            }
+                            ptx::mbar_expect_tx(bar(bQ), kQTiles * L::Q_BYTES);
 #pragma unroll
-                    for (int c = 0; c < DCH; ++c)
-                        ptx::tma_load_4d(sQ + t * L::Q_BYTES + c * (BM * 128), &tmQ, c * 64, (int) (m0 + t * BM), h, b, bar(bQ));
-                for (int j = 0; j < n_max; ++j) {
-                    const int ks = j % KS, vs = j % VS;
-                    if (!ptx::mbar_wait(bar(bKE + ks), ((j / KS) & 1) ^ 1, ctl + 1, p.dev_err)) break;
-                    ptx::mbar_expect_tx(bar(bKF + ks), L::KV_BYTES);
+                            for (int t = 0; t < kQTiles; ++t)
 #pragma unroll
-                    for (int c = 0; c < DCH; ++c) ptx::tma_load_4d(sK + ks * L::KV_BYTES + c * (BN * 128), &tmK, c * 64, (jb + j) * BN, hk, b, bar(bKF + ks));
-                    if (!ptx::mbar_wait(bar(bVE + vs), ((j / VS) & 1) ^ 1, ctl + 1, p.dev_err)) break;
-                    ptx::mbar_expect_tx(bar(bVF + vs), L::KV_BYTES);
+                                for (int c = 0; c < DCH; ++c)
+                                    ptx::tma_load_4d(sQ + t * L::Q_BYTES + c * (BM * 128), &tmQ, c * 64, (int) (w.m0 + t * BM), w.h, w.b, bar(bQ));
+                            ++cq;
+                        }
+                        if (!(ok = ptx::mbar_wait(bar(bVE + st), ph ^ 1, ctl + 1, p.dev_err))) break;
+                        ptx::mbar_expect_tx(bar(bVF + st), L::KV_BYTES);
 #pragma unroll
-                    for (int c = 0; c < DCH; ++c) ptx::tma_load_4d(sV + vs * L::KV_BYTES + c * (BN * 128), &tmV, c * 64, (jb + j) * BN, hk, b, bar(bVF + vs));
+                        for (int c = 0; c < DCH; ++c) ptx::tma_load_4d(sV + st * L::KV_BYTES + c * (BN * 128), &tmV, c * 64, (w.j0 + j) * BN, hk, w.b, bar(bVF + st));
+                    }
                 }
             }
           } else if (warp == kWarpMma) {
@@ -278,14 +349,14 @@ namespace {
             // keeps the two tiles half a period apart, so that one tile's exponentials run under the other's MMAs
             // (an issuer per tile lets the tiles fall into step and share the exponential unit: 949 vs 1265 TFLOP/s).
             const bool leader = ptx::elect_one();
-            if (n_max > 0) {
+            {
                 // Base descriptors once; a step along K only moves the 14-bit start-address field (16-byte units).
                 const uint64_t dQ0 = ptx::smem_desc_sw128(sQ, 16, 1024), dQ1 = ptx::smem_desc_sw128(sQ + L::Q_BYTES, 16, 1024);
                 const uint64_t dK0 = ptx::smem_desc_sw128(sK, 16, 1024), dK1 = ptx::smem_desc_sw128(sK + L::KV_BYTES, 16, 1024);
                 const uint64_t dV0 = ptx::smem_desc_sw128(sV, BN * 128, 1024), dV1 = ptx::smem_desc_sw128(sV + L::KV_BYTES, BN * 128, 1024);
                 auto wait = [&](int barIdx, uint32_t parity) { return __all_sync(0xffffffffu, ptx::mbar_wait(bar(barIdx), parity, ctl + 1, p.dev_err)); };
-                auto issue_qk = [&](int t, int j) {
-                    const uint64_t aq = t ? dQ1 : dQ0, bk = (j & 1) ? dK1 : dK0;
+                auto issue_qk = [&](int t, int g) { // g: the key tile's number in the CTA (selects the ring stage)
+                    const uint64_t aq = t ? dQ1 : dQ0, bk = (g & 1) ? dK1 : dK0;
                     const uint32_t d  = tmem + kColS + t * BN;
 #pragma unroll
                     for (int k = 0; k < D / 16; ++k) {
@@ -294,57 +365,81 @@ namespace {
                     }
                     if (leader) ptx::tc_commit(bar(bSF + t));
                 };
-                auto issue_pv = [&](int t, int j, int part) {
+                auto issue_pv = [&](int t, int j, int g, int part) { // j: key tile within the item (0 starts a new O_t)
                     // V tile: D/64 spans of [128 keys x 128 B]; 16 keys per MMA step = 2048 B; `part` selects BN / kPParts keys
-                    const uint64_t bv = (j & 1) ? dV1 : dV0;
+                    const uint64_t bv = (g & 1) ? dV1 : dV0;
                     const uint32_t d = tmem + kColO + t * D, a = tmem + kColS + t * BN;
 #pragma unroll
                     for (int k = part * (8 / kPParts); k < (part + 1) * (8 / kPParts); ++k)
                         if (leader) ptx::mma_f16_ts(d, a + k * 8, bv + (uint64_t) (k * 128), kIdescPV, (j | k) != 0 ? 1u : 0u);
                 };
-                bool ok = wait(bQ, 0) && wait(bKF + 0, 0);
-                if (ok) {
+                int  cq = 0;      // items with work so far (phase of the Q barriers)
+                int  cs[kQTiles]; // key tiles each query tile has been through (phase of its S and P barriers)
+                int  g0 = 0;      // key tiles before this item
+                bool ok = true;
+#pragma unroll
+                for (int t = 0; t < kQTiles; ++t) cs[t] = 0;
+                Work<QT> w = w_first;
+                for (int pos = 0; ok; w = work_at<QT>(p, pos)) {
+                    if (!w.valid) break;
+                    pos += w.adv;
+                    if (w.n_max == 0) continue;
+                    const int n_max = w.n_max;
+                    ok = wait(bKF + (g0 & 1), (uint32_t) ((g0 >> 1) & 1)) && wait(bQ, (uint32_t) (cq & 1));
+                    if (!ok) break;
                     ptx::tc_fence_after();
+                    // O_t and S_t of the previous item are free: its P.V MMAs were issued before these, and the softmax warps
+                    // have read O_t before they can hand over the first P_t of this item.
 #pragma unroll
                     for (int t = 0; t < kQTiles; ++t)
-                        if (n_t[t] > 0) issue_qk(t, 0);
-                    if (leader) ptx::tc_commit(bar(bKE + 0));
-                }
-                for (int j = 0; j < n_max && ok; ++j) {
-                    const int vs = j % VS;
-                    ok = wait(bVF + vs, (j / VS) & 1);
-                    const bool more = j + 1 < n_max;
+                        if (w.n_t[t] > 0) issue_qk(t, g0);
+                    if (leader) {
+                        ptx::tc_commit(bar(bKE + (g0 & 1)));
+                        if (n_max == 1) ptx::tc_commit(bar(bQE));
+                    }
+                    for (int j = 0; j < n_max && ok; ++j) {
+                        const int g = g0 + j, vs = g & 1;
+                        ok = wait(bVF + vs, (uint32_t) ((g >> 1) & 1));
+                        const bool more = j + 1 < n_max;
 #pragma unroll
-                    for (int t = 0; t < kQTiles && ok; ++t) {
-                        if (j < n_t[t]) {
-                            ok = wait(bPF + kPParts * t, j & 1);
-                            if (!ok) break;
-                            ptx::tc_fence_after();
-                            issue_pv(t, j, 0);
-#pragma unroll
-                            for (int part = 1; part < kPParts && ok; ++part) {
-                                ok = wait(bPF + kPParts * t + part, j & 1);
-                                if (ok) {
-                                    ptx::tc_fence_after();
-                                    issue_pv(t, j, part);
-                                }
-                            }
-                            if (!ok) break;
-                            if (j + 1 < n_t[t]) {
-                                ok = wait(bKF + (j + 1) % KS, ((j + 1) / KS) & 1);
+                        for (int t = 0; t < kQTiles && ok; ++t) {
+                            if (j < w.n_t[t]) {
+                                const uint32_t pp = (uint32_t) (cs[t] & 1);
+                                ok = wait(bPF + kPParts * t, pp);
                                 if (!ok) break;
                                 ptx::tc_fence_after();
-                                issue_qk(t, j + 1);
-                            } else if (leader) {
-                                ptx::tc_commit(bar(bOF + t)); // O_t complete
+                                issue_pv(t, j, g, 0);
+#pragma unroll
+                                for (int part = 1; part < kPParts && ok; ++part) {
+                                    ok = wait(bPF + kPParts * t + part, pp);
+                                    if (ok) {
+                                        ptx::tc_fence_after();
+                                        issue_pv(t, j, g, part);
+                                    }
+                                }
+                                if (!ok) break;
+                                ++cs[t];
+                                if (j + 1 < w.n_t[t]) {
+                                    ok = wait(bKF + ((g + 1) & 1), (uint32_t) (((g + 1) >> 1) & 1));
+                                    if (!ok) break;
+                                    ptx::tc_fence_after();
+                                    issue_qk(t, g + 1);
+                                } else if (leader) {
+                                    ptx::tc_commit(bar(bOF + t)); // O_t complete
+                                }
+                            }
+                        }
+                        if (!ok) break;
+                        if (leader) {
+                            ptx::tc_commit(bar(bVE + vs));
+                            if (more) {
+                                ptx::tc_commit(bar(bKE + ((g + 1) & 1)));
+                                if (j + 2 == n_max) ptx::tc_commit(bar(bQE)); // the item's last Q.K^T MMAs are issued: Q may be replaced
                             }
                         }
                     }
-                    if (!ok) break;
-                    if (leader) {
-                        ptx::tc_commit(bar(bVE + vs));
-                        if (more) ptx::tc_commit(bar(bKE + (j + 1) % KS));
-                    }
+                    g0 += n_max;
+                    ++cq;
                 }
             }
           }
@@ -354,21 +449,48 @@ namespace {
             const int      t      = warp >> 2;             // query tile of this warpgroup
             const int      q      = warp & 3;              // TMEM lane quarter this warp may address
             const int      r      = q * 32 + lane;
-            const int64_t  row    = m0 + (int64_t) t * BM + r;
             const uint32_t tS     = tmem + ((uint32_t) (q * 32) << 16) + kColS + t * BN;
             const uint32_t tO     = tmem + ((uint32_t) (q * 32) << 16) + kColO + t * D;
-            const int64_t  my_lim = p.causal ? row + (p.Skv - p.Sq) : p.Skv; // keys <= my_lim visible
-            const int      n      = n_t[t];
+            int            cs = 0, co = 0; // key tiles / items with work this query tile has been through (barrier phases)
+            bool           ok = true;
+            // What the key-tile loop needs of an item is boiled down to four numbers, so that the item's description does not
+            // occupy registers next to a whole row of scores; the epilogue looks the item up again.
+            int  n = 0, kbase = 0, jm = 0, lim_row = 0;
+            bool have = false;
+            auto prepare = [&](const Work<QT> &w) {
+                have = w.valid;
+                if (!have) return;
+                n     = t ? w.n_t[QT - 1] : w.n_t[0]; // (a run-time index would put the whole description into local memory)
+                kbase = w.j0 * BN; // first key of the item
+                const int64_t first = w.m0 + (int64_t) t * BM, off = p.Skv - p.Sq;
+                // keys < lim_row are visible to this thread's row
+                int64_t lim = w.len;
+                if (p.causal && first + r + off + 1 < lim) lim = first + r + off + 1;
+                lim_row = lim < 0 ? 0 : (int) lim;
+                // key tiles from jm on (counted within the item) straddle kv_len or the causal diagonal and take the masked body
+                jm = (int) (w.len / BN) - w.j0;
+                if (p.causal) {
+                    const int64_t f1 = first + off + 1 < 0 ? 0 : first + off + 1;
+                    const int     j2 = (int) (f1 / BN) - w.j0;
+                    jm = j2 < jm ? j2 : jm;
+                }
+                // The epilogue stages the rows in the Q area when they go to other GPUs, and in the CTA's last item, where nothing
+                // waits for that area; every other item leaves the area alone, and says so at once, so that the next item's Q
+                // tiles can be fetched while this one is being computed.
+                const bool staged = w.n_max > 0 && (w.last || (w.slot < 0 && p.fan.n_dest > 0));
+                if (w.n_max > 0 && !staged && lane == 0) ptx::mbar_arrive(bar(bQS));
+            };
+            prepare(w_first);
+          for (int pos = 0; ok && have;) {
             float          m_used = -INFINITY, l = 0.f;
-            bool           ok     = true;
             // One key tile; kMask selects the body that replaces invisible scores by -inf (only the tiles that
             // straddle kv_len or the causal diagonal take it, every other tile runs free of any mask arithmetic).
             auto tile = [&](auto mask_tag, int j) -> bool {
                 constexpr bool kMask = decltype(mask_tag)::value;
-                const int64_t  kv0   = (int64_t) (jb + j) * BN;
-                ok = ptx::mbar_wait(bar(bSF + t), j & 1, ctl + 1, p.dev_err);
+                ok = ptx::mbar_wait(bar(bSF + t), (uint32_t) (cs & 1), ctl + 1, p.dev_err);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) return false;
+                ++cs;
                 ptx::tc_fence_after();
                 uint32_t s[4][32];
 #pragma unroll
@@ -376,9 +498,8 @@ namespace {
                 ptx::tc_wait_ld();
                 if (kMask) {
                     // visible columns of this row in this tile: [0, nvis)
-                    int64_t lim = len < my_lim + 1 ? len : my_lim + 1;
-                    lim -= kv0;
-                    const int nvis = lim < 0 ? 0 : (lim > BN ? BN : (int) lim);
+                    const int lim  = lim_row - (kbase + j * BN);
+                    const int nvis = lim < 0 ? 0 : (lim > BN ? BN : lim);
 #pragma unroll
                     for (int c = 0; c < 4; ++c)
 #pragma unroll
@@ -530,79 +651,103 @@ namespace {
                 return true;
             };
             for (int j = 0; j < n; ++j) {
-                const int64_t kv0       = (int64_t) (jb + j) * BN;
-                const bool    need_mask = (kv0 + BN > len) || (p.causal && kv0 + BN - 1 > m0 + (int64_t) t * BM + (p.Skv - p.Sq));
-                if (!(need_mask ? tile(std::true_type{}, j) : tile(std::false_type{}, j))) break;
+                if (!(j >= jm ? tile(std::true_type{}, j) : tile(std::false_type{}, j))) break;
             }
-            // epilogue
-            if (n > 0 && ok) {
-                ok = ptx::mbar_wait(bar(bOF + t), 0, ctl + 1, p.dev_err);
+            if (!ok) break;
+            const Work<QT> w = work_at<QT>(p, pos);
+            pos += w.adv;
+            const int      b = w.b, h = w.h;
+            const int64_t  m0 = w.m0, row = m0 + (int64_t) t * BM + r;
+            const int      ndest  = w.slot >= 0 ? 0 : p.fan.n_dest; // fan-out of final rows only (the launcher checked alignment)
+            const bool     staged = w.n_max > 0 && (w.last || ndest > 0);
+            // epilogue of the item
+            if (n > 0) {
+                ok = ptx::mbar_wait(bar(bOF + t), (uint32_t) (co & 1), ctl + 1, p.dev_err);
                 ok = __all_sync(0xffffffffu, ok);
+                ++co;
             }
-            if (ok) {
+            if (!ok) break;
+            {
                 ptx::tc_fence_after();
                 // a row with no visible key stores NaN like the reference's 0/0
                 float       inv    = (n > 0 && m_used == -INFINITY) ? __int_as_float(0x7fc00000) : 1.0f / l;
                 const int64_t ooff  = (int64_t) b * p.os[0] + (int64_t) h * p.os[1] + row * p.os[2];
                 T          *orow   = (T *) p.O + ooff;
                 bool        vec_ok = (p.os[0] % 8 == 0) && (p.os[1] % 8 == 0) && (p.os[2] % 8 == 0) && (((uintptr_t) p.O & 15) == 0);
-                const int   ndest  = p.kv_splits > 1 ? 0 : p.fan.n_dest; // fan-out of final rows only (the launcher checked alignment)
-                if (p.kv_splits > 1) {
-                    // partial of this key range: O / l in the storage type (bounded by max |v|, so 16 bits do not overflow),
-                    // weight data (m, l) in fp32; a range without a visible key for this row has weight 0
-                    const int64_t prow = (((int64_t) split * gridDim.z + b) * p.Hq + h) * p.Sq + row;
-                    const bool    none = n == 0 || m_used == -INFINITY;
+                const bool  partial = w.slot >= 0;
+                // rows of a partial: [CTA][slot][QT * BM]
+                const int64_t prow0 = ((int64_t) blockIdx.x * 2 + (partial ? w.slot : 0)) * (kQTiles * BM) + (int64_t) t * BM;
+                if (partial) {
+                    // partial of this stretch of the keys: O / l in the storage type (bounded by max |v|, so 16 bits do not
+                    // overflow), weight data (m, l) in fp32; a stretch without a visible key for this row has weight 0
+                    const bool none = n == 0 || m_used == -INFINITY;
                     inv    = none ? 0.f : 1.0f / l;
-                    orow   = (T *) p.part_o + prow * D;
+                    orow   = (T *) p.part_o + (prow0 + r) * D;
                     vec_ok = true;
                     if (row < p.Sq) {
-                        p.part_ml[prow * 2]     = none ? -INFINITY : m_used;
-                        p.part_ml[prow * 2 + 1] = none ? 0.f : l;
+                        p.part_ml[(prow0 + r) * 2]     = none ? -INFINITY : m_used;
+                        p.part_ml[(prow0 + r) * 2 + 1] = none ? 0.f : l;
                     }
                 }
                 if (vec_ok) {
-                    // Coalesced stores. Thread = row would write 16 bytes per row and instruction (32 scattered segments per
-                    // warp store: harmless in local memory, where L2 merges them, but every segment is its own NVLink packet
-                    // when the destination is a peer). The warp therefore stages its 32 rows in this tile's Q area, which is
-                    // idle once O is final (every MMA that read Q has completed), in 16-byte chunks XOR-swizzled by the row,
-                    // and then writes whole rows: 32 / CH rows of CH contiguous chunks per instruction.
-                    constexpr int  CH     = D / 8; // 16-byte chunks per row
-                    const uint32_t sStage = sQ + (uint32_t) t * L::Q_BYTES + (uint32_t) (q * 32) * (D * 2);
-#pragma unroll 1
-                    for (int c = 0; c < D / 32; ++c) {
-                        uint32_t v[32];
-                        if (n > 0) {
-                            ptx::tmem_ld_x32(tO + c * 32, v);
-                            ptx::tc_wait_ld();
-                        } else {
+                    // the whole row of O_t in one go (the score registers are free here)
+                    uint32_t v[D];
+                    if (n > 0) {
 #pragma unroll
-                            for (int i = 0; i < 32; ++i) v[i] = 0u;
-                        }
+                        for (int c = 0; c < D / 32; ++c) ptx::tmem_ld_x32(tO + c * 32, *reinterpret_cast<uint32_t(*)[32]>(v + c * 32));
+                        ptx::tc_wait_ld();
+                    } else {
 #pragma unroll
-                        for (int g = 0; g < 4; ++g) {
-                            uint32_t o32[4];
-#pragma unroll
-                            for (int i = 0; i < 4; ++i)
-                                o32[i] = pack2<T>(__uint_as_float(v[g * 8 + 2 * i]) * inv, __uint_as_float(v[g * 8 + 2 * i + 1]) * inv);
-                            ptx::st_shared_v4(sStage + (uint32_t) lane * (D * 2) + (uint32_t) (((c * 4 + g) ^ (lane & (CH - 1))) << 4), o32[0], o32[1], o32[2], o32[3]);
-                        }
+                        for (int i = 0; i < D; ++i) v[i] = 0u;
                     }
-                    __syncwarp();
-                    // partial rows are dense [.., Sq, D]; final rows follow the caller's output strides
-                    const int64_t row_stride = p.kv_splits > 1 ? (int64_t) D : p.os[2];
-                    const int64_t base_off   = p.kv_splits > 1 ? ((((int64_t) split * gridDim.z + b) * p.Hq + h) * p.Sq) * D
-                                                               : (int64_t) b * p.os[0] + (int64_t) h * p.os[1];
-                    T *const obase = p.kv_splits > 1 ? (T *) p.part_o : (T *) p.O;
-#pragma unroll 1
-                    for (int i = 0; i < CH; ++i) {
-                        const int     rr   = i * (32 / CH) + lane / CH, ch = lane % CH;
-                        const int64_t grow = m0 + (int64_t) t * BM + q * 32 + rr;
-                        const uint4   ov   = ptx::ld_shared_v4(sStage + (uint32_t) rr * (D * 2) + (uint32_t) ((ch ^ (rr & (CH - 1))) << 4));
-                        if (grow < p.Sq) {
-                            const int64_t off = base_off + grow * row_stride + ch * 8;
-                            if (ndest == 0) *reinterpret_cast<uint4 *>(obase + off) = ov;
-                            else vkc_fanout_store16<T>(p.fan, off, ov);
+                    auto packed = [&](int g) { // 16 bytes of the normalised row
+                        uint4 o;
+                        o.x = pack2<T>(__uint_as_float(v[g * 8 + 0]) * inv, __uint_as_float(v[g * 8 + 1]) * inv);
+                        o.y = pack2<T>(__uint_as_float(v[g * 8 + 2]) * inv, __uint_as_float(v[g * 8 + 3]) * inv);
+                        o.z = pack2<T>(__uint_as_float(v[g * 8 + 4]) * inv, __uint_as_float(v[g * 8 + 5]) * inv);
+                        o.w = pack2<T>(__uint_as_float(v[g * 8 + 6]) * inv, __uint_as_float(v[g * 8 + 7]) * inv);
+                        return o;
+                    };
+                    if (!staged) {
+                        // thread = row: 16-byte stores straight from the registers (L2 merges the halves of a sector)
+                        if (row < p.Sq) {
+#pragma unroll
+                            for (int g = 0; g < D / 8; ++g) {
+                                if (ndest == 0) *reinterpret_cast<uint4 *>(orow + g * 8) = packed(g);
+                                else vkc_fanout_store16<T>(p.fan, ooff + g * 8, packed(g)); // an item without keys: NaN rows, rare
+                            }
                         }
+                    } else {
+                        // Coalesced stores. Thread = row writes 16 bytes per row and instruction: 32 scattered segments per warp
+                        // store, each its own NVLink packet when the destination is a peer. The warp therefore stages its 32 rows
+                        // in this tile's Q area, which is idle once O is final (every MMA that read Q has completed, and the
+                        // producer waits for q_staged before it refills the area), in 16-byte chunks XOR-swizzled by the row, and
+                        // then writes whole rows: 32 / CH rows of CH contiguous chunks per instruction.
+                        constexpr int  CH     = D / 8; // 16-byte chunks per row
+                        const uint32_t sStage = sQ + (uint32_t) t * L::Q_BYTES + (uint32_t) (q * 32) * (D * 2);
+#pragma unroll
+                        for (int g = 0; g < CH; ++g) {
+                            const uint4 o = packed(g);
+                            ptx::st_shared_v4(sStage + (uint32_t) lane * (D * 2) + (uint32_t) ((g ^ (lane & (CH - 1))) << 4), o.x, o.y, o.z, o.w);
+                        }
+                        __syncwarp();
+                        // partial rows are dense [.., QT * BM, D]; final rows follow the caller's output strides
+                        const int64_t row_stride = partial ? (int64_t) D : p.os[2];
+                        const int64_t base_off   = partial ? (prow0 - (m0 + (int64_t) t * BM)) * D : (int64_t) b * p.os[0] + (int64_t) h * p.os[1];
+                        T *const      obase      = partial ? (T *) p.part_o : (T *) p.O;
+#pragma unroll 1
+                        for (int i = 0; i < CH; ++i) {
+                            const int     rr   = i * (32 / CH) + lane / CH, ch = lane % CH;
+                            const int64_t grow = m0 + (int64_t) t * BM + q * 32 + rr;
+                            const uint4   o4   = ptx::ld_shared_v4(sStage + (uint32_t) rr * (D * 2) + (uint32_t) ((ch ^ (rr & (CH - 1))) << 4));
+                            if (grow < p.Sq) {
+                                const int64_t off = base_off + grow * row_stride + ch * 8;
+                                if (ndest == 0) *reinterpret_cast<uint4 *>(obase + off) = o4;
+                                else vkc_fanout_store16<T>(p.fan, off, o4);
+                            }
+                        }
+                        __syncwarp();
+                        if (lane == 0) ptx::mbar_arrive(bar(bQS)); // this warp no longer reads the Q area
                     }
                 } else {
 #pragma unroll 1
@@ -621,108 +766,160 @@ namespace {
                         }
                     }
                 }
+                // O_t has been read: order those reads before the P_t hand-over of the next item, after which the tensor
+                // pipe starts a new O_t
+                ptx::tc_fence_before();
             }
+            prepare(work_at<QT>(p, pos));
+          }
         }
+        if (p.balanced) vkc_grid_dep_launch(); // this CTA's share is done: the merge kernel may be brought in
         if (ctl[1]) {
             for (int i = 0; i < 50; ++i) __nanosleep(20000); // aborted: let copies in flight land
         }
         ptx::tc_fence_before();
         __syncthreads();
         if (warp == kWarpMma) ptx::tmem_dealloc(tmem, kTmemCols);
-        if (p.kv_splits == 1 && p.fan.n_dest > 0) fanout_signal(p.fan, gridDim.x * gridDim.y * gridDim.z);
+        if (!p.balanced && p.fan.n_dest > 0) fanout_signal(p.fan, gridDim.x * gridDim.y * gridDim.z);
     }
 
-    // Merge of the key-range partials of one query row: weights l_s * 2^(m_s - m) over their sum (m_s are in the log2
-    // domain the kernel works in); a row without any visible key gets NaN like the reference's 0/0.
-    template <typename T, int D>
-    __global__ void __launch_bounds__(256) attn_prefill_merge_kernel(const T *__restrict__ part_o, const float *__restrict__ part_ml, T *__restrict__ O,
-                                                                     int64_t B, int64_t Hq, int64_t Sq, int splits, int64_t os0, int64_t os1, int64_t os2,
-                                                                     const FanOut fan) {
-        constexpr int TPRW = D / 8; // threads per row, 8 elements each
+    // Merge kernel of the balanced form: one thread per 16 bytes of an output row of the left-over units (`main_ctas` = grid
+    // size of the attention kernel, `left` = number of left-over units). A unit that one CTA covered alone already has its
+    // final rows. The others were cut at CTA boundaries: CTA c of the run [first, last] holds the unit's partial in its slot
+    // 0, except the first, where the unit began inside the CTA's range (slot 1). Each row gets the weights l_s * 2^(m_s - m)
+    // over their sum (m_s are in the log2 domain the kernel works in); a row without any visible key gets NaN like the
+    // reference's 0/0.
+    template <typename T, int D, int QT>
+    __global__ void __launch_bounds__(256) attn_prefill_merge_kernel(const AttnParams p, int main_ctas, int left) {
+        constexpr int TPRW = D / 8, ROWS = QT * BM; // threads per row (8 elements each), rows per unit
         const int64_t gid = (int64_t) blockIdx.x * blockDim.x + threadIdx.x;
-        const int64_t row = gid / TPRW, rows = B * Hq * Sq;
-        const int     c   = (int) (gid % TPRW) * 8;
+        const int     ur  = (int) (gid / (ROWS * TPRW)), rr = (int) (gid / TPRW) % ROWS, c = (int) (gid % TPRW) * 8;
         vkc_grid_dep_wait(); // launched with programmatic serialization: the partials are complete only after this
         vkc_grid_dep_launch();
-        if (row < rows) {
-            float m = -INFINITY;
-            for (int s = 0; s < splits; ++s) m = fmaxf(m, part_ml[((int64_t) s * rows + row) * 2]);
-            float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, wsum = 0.f;
-            for (int s = 0; s < splits; ++s) {
-                const float ms = part_ml[((int64_t) s * rows + row) * 2], ls = part_ml[((int64_t) s * rows + row) * 2 + 1];
-                const float w  = ms == -INFINITY ? 0.f : ls * exp2f(ms - m);
-                wsum += w;
-                const uint4 pv = *reinterpret_cast<const uint4 *>(part_o + ((int64_t) s * rows + row) * D + c);
-                const T    *pt = reinterpret_cast<const T *>(&pv);
+        if (ur < left) {
+            const int64_t u  = (int64_t) p.rounds * main_ctas + ur;
+            const int64_t s0 = (int64_t) ur * p.steps, s1 = s0 + p.steps - 1; // the unit's steps in the line
+            const int64_t ca = s0 / p.quota, cb = s1 / p.quota;
+            const int     qg = (int) (u % p.nq);
+            const int64_t bh = u / p.nq, h = bh % p.Hq, b = bh / p.Hq, grow = (int64_t) qg * ROWS + rr;
+            if (ca != cb && grow < p.Sq) {
+                const T *part_o = (const T *) p.part_o;
+                float    m      = -INFINITY;
+                for (int64_t cc = ca; cc <= cb; ++cc) {
+                    const int64_t prow = (cc * 2 + (s0 < cc * p.quota ? 0 : 1)) * ROWS + rr;
+                    m                  = fmaxf(m, p.part_ml[prow * 2]);
+                }
+                float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, wsum = 0.f;
+                for (int64_t cc = ca; cc <= cb; ++cc) {
+                    const int64_t prow = (cc * 2 + (s0 < cc * p.quota ? 0 : 1)) * ROWS + rr;
+                    const float   ms = p.part_ml[prow * 2], ls = p.part_ml[prow * 2 + 1];
+                    const float   wt = ms == -INFINITY ? 0.f : ls * exp2f(ms - m);
+                    wsum += wt;
+                    const uint4 pv = *reinterpret_cast<const uint4 *>(part_o + prow * D + c);
+                    const T    *pt = reinterpret_cast<const T *>(&pv);
 #pragma unroll
-                for (int i = 0; i < 8; ++i) acc[i] += w * St<T>::ld(pt + i);
-            }
-            const float inv = 1.0f / wsum; // 0/0 -> NaN for a row with no visible key
-            const int64_t b = row / (Hq * Sq), h = (row / Sq) % Hq, r = row % Sq;
-            const int64_t ooff = b * os0 + h * os1 + r * os2 + c;
-            if (fan.n_dest == 0) {
-                T *orow = O + ooff;
+                    for (int i = 0; i < 8; ++i) acc[i] += wt * St<T>::ld(pt + i);
+                }
+                const float   inv  = 1.0f / wsum; // 0/0 -> NaN for a row with no visible key
+                const int64_t ooff = b * p.os[0] + h * p.os[1] + grow * p.os[2] + c;
+                if (p.fan.n_dest == 0) {
+                    T *orow = (T *) p.O + ooff;
 #pragma unroll
-                for (int i = 0; i < 8; ++i) St<T>::st(orow + i, acc[i] * inv);
-            } else {
-                uint4 ov; // the launcher checked that every destination takes 16-byte stores
-                T    *ot = reinterpret_cast<T *>(&ov);
+                    for (int i = 0; i < 8; ++i) St<T>::st(orow + i, acc[i] * inv);
+                } else {
+                    uint4 ov; // the launcher checked that every destination takes 16-byte stores
+                    T    *ot = reinterpret_cast<T *>(&ov);
 #pragma unroll
-                for (int i = 0; i < 8; ++i) St<T>::st(ot + i, acc[i] * inv);
-                vkc_fanout_store16<T>(fan, ooff, ov);
+                    for (int i = 0; i < 8; ++i) St<T>::st(ot + i, acc[i] * inv);
+                    vkc_fanout_store16<T>(p.fan, ooff, ov);
+                }
             }
         }
-        if (fan.n_dest > 0) fanout_signal(fan, gridDim.x); // every thread of the block, also the ones past the last row
+        // every thread of every block; the rows that the attention kernel itself fanned out were complete before this kernel began
+        if (p.fan.n_dest > 0) fanout_signal(p.fan, gridDim.x);
+    }
+
+    // How the balanced form would cut the work of two-tile units, and a rough cost of both forms in key-tile steps of one CTA
+    // (a unit run by a CTA of its own pays about two steps for launch, set-up, first loads and the final stores; an item of a
+    // persistent CTA about one; the merge pass about three).
+    struct Plan {
+        int64_t ctas, rounds, left, total, quota;
+        double  cost_balanced, cost_per_unit;
+    };
+    inline Plan plan_balanced(int64_t units, int64_t steps, int64_t slots) {
+        Plan pl;
+        pl.ctas = units >= slots ? slots : (units * steps + 3) / 4; // at least four key tiles per CTA
+        if (pl.ctas > slots) pl.ctas = slots;
+        if (pl.ctas < 1) pl.ctas = 1;
+        pl.rounds = units / pl.ctas, pl.left = units - pl.rounds * pl.ctas, pl.total = pl.left * steps;
+        pl.quota  = (pl.total + pl.ctas - 1) / pl.ctas;
+        if (pl.quota < 4) pl.quota = 4;
+        pl.cost_balanced = (double) pl.rounds * (steps + 1.0) + (pl.left > 0 ? (double) pl.quota + 2.0 + 3.0 : 0.0);
+        pl.cost_per_unit = (double) ((units + slots - 1) / slots) * (steps + 2.0);
+        return pl;
     }
 
     template <typename T, int D, int QT>
-    int launch_attn_qt(vkc_ctx *ctx, const CUtensorMap &tq, const CUtensorMap &tk, const CUtensorMap &tv, const AttnParams &p, int64_t B, cudaStream_t st) {
+    int launch_attn_qt(vkc_ctx *ctx, const CUtensorMap &tq, const CUtensorMap &tk, const CUtensorMap &tv, AttnParams &p, int64_t B, bool balanced,
+                       cudaStream_t st) {
         auto          kern = attn_prefill_kernel<T, D, 2, QT>;
         constexpr int smem = (int) Smem<D, 2, 2, QT>::total;
         static_assert(smem * (QT == 1 && D == 64 ? 2 : 1) <= 227 * 1024, "shared memory budget");
         if (int rc = vkc_configure_smem(ctx, kern, smem)) return rc;
-        dim3 grid((unsigned) ((p.Sq + QT * BM - 1) / (QT * BM)) * (unsigned) p.kv_splits, (unsigned) p.Hq, (unsigned) B);
+        const int64_t nq = (p.Sq + QT * BM - 1) / (QT * BM), units = nq * p.Hq * B, steps = (p.Skv + BN - 1) / BN;
+        const int64_t slots = (int64_t) ctx->sm_count * (QT == 1 ? 2 : 1);
+        p.balanced = 0;
+        p.nq = (int) nq, p.steps = (int) steps, p.quota = 1, p.total = 0, p.rounds = 0;
+        if (balanced) {
+            const Plan   pl       = plan_balanced(units, steps, slots);
+            const size_t prows    = (size_t) pl.ctas * 2 * QT * BM;
+            const size_t ml_bytes = (prows * 2 * sizeof(float) + 255) & ~(size_t) 255;
+            if (vkc_ensure_scratch(ctx, ml_bytes + prows * D * 2 + 256, st) == VKC_OK) {
+                p.balanced = 1;
+                p.rounds   = (int) pl.rounds;
+                p.quota    = (int) pl.quota;
+                p.total    = (int) pl.total;
+                p.part_ml  = (float *) ctx->scratch;
+                p.part_o   = (char *) ctx->scratch + ml_bytes;
+                vkc_launch(ctx, kern, dim3((unsigned) pl.ctas), dim3(threads_for(QT)), smem, st, tq, tk, tv, p);
+                if (int rc = vkc_post_launch(ctx, "attn_prefill_tcgen05")) return rc;
+                if (pl.left == 0 && p.fan.n_dest == 0) return VKC_OK; // nothing was cut
+                // (with a fan-out the merge kernel also publishes the flags, so it runs even when it has nothing to join)
+                const int64_t threads = pl.left * QT * BM * (D / 8);
+                vkc_launch(ctx, attn_prefill_merge_kernel<T, D, QT>, dim3((unsigned) (threads > 0 ? (threads + 255) / 256 : 1)), dim3(256), 0, st, p,
+                           (int) pl.ctas, (int) pl.left);
+                return vkc_post_launch(ctx, "attn_prefill_merge");
+            }
+        }
+        dim3 grid((unsigned) nq, (unsigned) p.Hq, (unsigned) B);
         vkc_launch(ctx, kern, grid, dim3(threads_for(QT)), smem, st, tq, tk, tv, p);
-        if (int rc = vkc_post_launch(ctx, "attn_prefill_tcgen05")) return rc;
-        if (p.kv_splits == 1) return VKC_OK;
-        const int64_t threads = B * p.Hq * p.Sq * (D / 8);
-        vkc_launch(ctx, attn_prefill_merge_kernel<T, D>, dim3((unsigned) ((threads + 255) / 256)), dim3(256), 0, st, (const T *) p.part_o,
-                   (const float *) p.part_ml, (T *) p.O, B, p.Hq, p.Sq, p.kv_splits, p.os[0], p.os[1], p.os[2], p.fan);
-        return vkc_post_launch(ctx, "attn_prefill_merge");
+        return vkc_post_launch(ctx, "attn_prefill_tcgen05");
     }
     template <typename T, int D>
     int launch_attn(vkc_ctx *ctx, const CUtensorMap &tq, const CUtensorMap &tk, const CUtensorMap &tv, AttnParams &p, int64_t B, cudaStream_t st) {
-        if (D == 64) {
-            // two one-tile CTAs per SM unless the grid is many rounds deep anyway (then sharing K/V between two tiles wins)
-            const int64_t pairs = ((p.Sq + 2 * BM - 1) / (2 * BM)) * p.Hq * B;
-            if (pairs < 6 * (int64_t) ctx->sm_count) {
-                // One-tile CTAs, two per SM. When they do not even fill a few rounds of the 2 x SMs slots and the key sequence
-                // is long, the key range is also cut in two: the hardware block scheduler balances the finer units better
-                // (352 CTAs of 22 key tiles on 296 slots -> 704 CTAs of 11), at the price of a small merge pass.
-                const int64_t ctas = ((p.Sq + BM - 1) / BM) * p.Hq * B, slots = 2 * (int64_t) ctx->sm_count, ntiles = (p.Skv + BN - 1) / BN;
-                // Cost of a split factor: rounds over the slots x (key tiles per CTA + about 1.5 tiles of prologue and epilogue),
-                // plus a quarter tile per partial for the merge pass; 44 CTAs of 22 tiles (two heads of a head-sharded encoder)
-                // run as 264 CTAs of 4.
-                if (!p.causal && !p.kv_len && ntiles >= 8 && ctas < 3 * slots) {
-                    int    best = 1;
-                    double best_cost = (double) ((ctas + slots - 1) / slots) * ((double) ntiles + 1.5);
-                    for (int sf = 2; sf <= 8 && ntiles / sf >= 2; ++sf) {
-                        if ((sf - 1) * ((ntiles + sf - 1) / sf) >= ntiles) continue; // the last range would be empty
-                        const double cost = (double) ((sf * ctas + slots - 1) / slots) * ((double) ((ntiles + sf - 1) / sf) + 1.5) + 0.25 * sf;
-                        if (cost < best_cost - 1e-9) best_cost = cost, best = sf;
-                    }
-                    const size_t rows = (size_t) B * p.Hq * p.Sq;
-                    const size_t need = (size_t) best * rows * (64 * 2 + 2 * 4) + 256;
-                    if (best > 1 && vkc_ensure_scratch(ctx, need, st) == VKC_OK) {
-                        p.kv_splits = best;
-                        p.part_ml   = (float *) ctx->scratch;
-                        p.part_o    = (char *) ctx->scratch + (((size_t) best * rows * 2 * 4 + 255) & ~(size_t) 255);
-                    }
-                }
-                return launch_attn_qt<T, 64, 1>(ctx, tq, tk, tv, p, B, st);
+        const int64_t pairs = ((p.Sq + 2 * BM - 1) / (2 * BM)) * p.Hq * B, steps = (p.Skv + BN - 1) / BN, sms = ctx->sm_count;
+        // Head size 64: two one-tile CTAs fit an SM and their softmax and MMA phases overlap like the two tiles of the two-tile
+        // form do, at finer granularity; unless the grid is many rounds deep anyway (then sharing K/V between two tiles wins).
+        const bool one_tile = D == 64 && pairs < 6 * sms;
+        // The balanced form (two-tile units of equal length only: no causal mask, no per-sequence lengths) when its estimate
+        // is clearly the lower one.
+        bool balanced = false, one_tile_balanced = false;
+        if (!p.causal && !p.kv_len && pairs > 0 && steps >= 1 && pairs * steps < (1ll << 29)) {
+            const Plan pl = plan_balanced(pairs, steps, sms);
+            double     pu = pl.cost_per_unit, bal = pl.cost_balanced;
+            if (one_tile) { // one-tile units, two CTAs per SM, each about as fast as a two-tile CTA alone
+                const int64_t tiles = ((p.Sq + BM - 1) / BM) * p.Hq * B;
+                const Plan    p1    = plan_balanced(tiles, steps, 2 * sms);
+                pu                  = p1.cost_per_unit;
+                if (p1.cost_balanced < bal) bal = p1.cost_balanced, one_tile_balanced = true;
             }
+            balanced = bal < 0.985 * pu;
         }
-        return launch_attn_qt<T, D, 2>(ctx, tq, tk, tv, p, B, st);
+        const char *envb = getenv("VKNN_PREFILL_BALANCED"), *envq = getenv("VKNN_PREFILL_QT");
+        if (envb) balanced = balanced && atoi(envb) != 0;
+        if (envq && D == 64) one_tile_balanced = atoi(envq) == 1;
+        if (one_tile && (!balanced || one_tile_balanced)) return launch_attn_qt<T, 64, 1>(ctx, tq, tk, tv, p, B, balanced, st);
+        return launch_attn_qt<T, D, 2>(ctx, tq, tk, tv, p, B, balanced, st);
     }
 
     int make_qkv_map(vkc_ctx *ctx, CUtensorMap *map, int dtype, const void *base, int64_t B, int64_t H, int64_t S, int64_t D, const int64_t *str) {
@@ -764,7 +961,7 @@ int vkc_attn_prefill_tcgen05(vkc_ctx *ctx, const void *Q, const void *K, const v
     p.causal     = causal;
     p.kv_len     = kv_len;
     p.dev_err    = ctx->dev_err;
-    p.kv_splits  = 1;
+    p.balanced = 0;
     if (int frc = vkc_fan_to_dev(ctx, fan, &p.fan, "attn_prefill_fanout")) return frc;
     if (fan) {
         if ((os[0] % 8) || (os[1] % 8) || (os[2] % 8)) return vkc_fail(ctx, VKC_ERR_UNSUPPORTED, "attn_prefill_fanout: output strides must be multiples of 16 bytes");

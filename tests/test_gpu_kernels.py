@@ -236,6 +236,36 @@ def test_attention_head64_key_range_split(ctx, dt, B, Hq, Hkv, Sq, Skv):
     assert_low(got, ref, "attn split")
 
 
+@pytest.mark.parametrize("dt,B,H,Sq,Skv,D,merged", [
+    ("f16", 1, 16, 2738, 2738, 64, True),    # more units than SMs: a round of whole units, the left-over ones cut into pieces
+    ("f16", 1, 2, 2738, 2738, 64, True),     # a handful of units: every unit cut into pieces, one piece per CTA
+    ("bf16", 1, 6, 3072, 3072, 128, True),   # head size 128, units cut in two
+    ("bf16", 1, 40, 1200, 1200, 128, True),  # ragged last query group and key tile, a round of whole units plus pieces
+    ("bf16", 4, 16, 1024, 1024, 128, False), # two rounds of whole units through persistent CTAs, nothing to merge
+])
+def test_attention_balanced_forms(ctx, dt, B, H, Sq, Skv, D, merged):
+    """Without a mask every (batch, head, query group) unit needs the same number of key tiles and the tensor-core kernel runs
+    as persistent CTAs: whole units round-robin, then the left-over units cut into equal pieces whose partial rows a merge
+    kernel joins. Every output row is compared with the SIMT kernel (itself checked against the oracle by the other tests),
+    and 48 rows of every head — among them the first and last rows of query tiles and of the sequence — with the oracle."""
+    tdt = DT[dt]
+    rng = np.random.default_rng(B * 100000 + H * 1000 + Sq + D)
+    q = round_to(rng.standard_normal((B, H, Sq, D)), tdt)
+    k = round_to(rng.standard_normal((B, H, Skv, D)), tdt)
+    v = round_to(rng.standard_normal((B, H, Skv, D)), tdt)
+    scale = 1.0 / np.sqrt(D)
+    n0 = ctx.launch_count()
+    got = run_attn(ctx, q, k, v, scale, dt, impl=vknn_b200.IMPL_TCGEN05)
+    if ctx.device_info()[1] == 148:  # the plan depends on the number of SMs
+        assert ctx.launch_count() - n0 == (2 if merged else 1)
+    simt = run_attn(ctx, q, k, v, scale, dt, impl=vknn_b200.IMPL_SIMT)
+    assert np.isfinite(got).all()
+    assert float(np.abs(got - simt).max()) <= 4e-3, float(np.abs(got - simt).max())
+    rows = sorted(set([0, 1, 127, 128, 255, 256, 257, Sq // 2, Sq - 129, Sq - 128, Sq - 2, Sq - 1] + list(rng.integers(0, Sq, 36))))
+    ref = vko.attention(np.ascontiguousarray(q[:, :, rows]), k, v, scale)
+    assert_low(got[:, :, rows], ref, "balanced attention")
+
+
 def test_captured_graph_survives_scratch_growth():
     """A key-range-split attention keeps its partials in the context's scratch block, whose address a captured CUDA graph
     bakes in. A later, larger call makes the scratch grow; the block the graph points at must stay alive (it is retired,

@@ -1,10 +1,14 @@
 // K2 — fused prefill attention on the 5th-generation tensor cores (flash style: the score matrix never leaves
-// the SM). One CTA owns TWO 128-row query tiles (A and B) of one (batch, head) and walks the key/value
-// sequence in tiles of 128 keys; while the softmax warps of one query tile work, the tensor core runs the
-// MMAs of the other. For head size 64 and grids of only a few rounds a one-tile form runs instead, two CTAs per SM:
-// the same overlap happens between the co-resident CTAs and single tiles balance better over the 148 SMs; when even those
-// do not fill a few rounds of the SMs and the key sequence is long, each CTA takes half of the key tiles and a merge kernel
-// joins the two normalised partial outputs with their (maximum, sum) weights.
+// the SM). A CTA works on TWO 128-row query tiles (A and B) of one (batch, head) at a time — a unit — and walks the
+// key/value sequence in tiles of 128 keys; while the softmax warps of one query tile work, the tensor core runs the
+// MMAs of the other. For head size 64 and only a few units a one-tile form runs instead, two CTAs per SM: the same overlap
+// happens between the co-resident CTAs.
+// Work distribution: with a mask or per-sequence lengths one CTA per unit. Otherwise every unit needs the same number of key
+// tiles and the CTAs are persistent (one per SM): whole units round-robin, then the units left over cut into equal pieces of
+// their key range, one piece per CTA, whose normalised partial rows a merge kernel joins with their (maximum, sum) weights
+// (AttnParams says how). A persistent CTA runs its items back to back: the next item's Q tiles are fetched before the
+// current one ends, barrier phases and ring stages simply continue, and the output rows leave through a staging area of
+// their own.
 // Warp numbers below are those of the two-tile form.
 //
 //   warp 8     TMA producer: both Q tiles once, then K and V tiles through two independent 2-stage
@@ -22,7 +26,7 @@
 //              pipeline written in issue order, packed fp32 arithmetic (f32x2) around the MUFU ex2, and every fourth
 //              column pair takes a cubic-polynomial 2^x on the FMA pipes instead. The running maximum is raised
 //              only when it grows by more than 8 (factor 256), so O_t in TMEM is rescaled rarely; row sums stay in
-//              fp32. After the last key tile the same warps read O_t, divide by the row sum and store.
+//              fp32. After the last key tile of an item the same warps read O_t, divide by the row sum and store.
 //   warps 8-11 form the control warpgroup (8 = TMA, 9 = MMA); it gives registers up (setmaxnreg) so that the two
 //              softmax warpgroups hold a whole score row plus the packed probabilities without spilling.
 // Ordering notes: tcgen05.commit covers every MMA issued before it, so "S_t(j) ready" also means P.V_t(j-1) has
@@ -64,14 +68,15 @@ namespace {
         // balanced == 1 (every unit needs the same number of key tiles: no causal mask, no per-sequence lengths): a
         // one-dimensional grid of persistent CTAs. CTA c first takes `rounds` whole units, c, c + grid, c + 2 grid, ... (at any
         // moment the CTAs work on neighbouring units, so the K and V tiles they stream are the same few heads' and stay in
-        // L2). The units left over, fewer than the grid has CTAs, are laid end to end as one line of `total` key-tile steps and
-        // CTA c takes the steps [c * quota, (c + 1) * quota) of it: the same amount of work for every CTA whatever the number
-        // of units is. The stretch of a CTA's range that lies in one unit is an item. An item that covers its whole unit stores
-        // final rows; otherwise it leaves a partial per row — the normalised output in the storage type and (running maximum,
-        // row sum) — in the CTA's slot 0 (the unit began in an earlier CTA's range) or slot 1 (it began in this one), and the
-        // merge kernel joins the partials of each left-over unit.
-        int     balanced, nq, steps, quota, rounds;
-        int     total;   // steps in the line of left-over units
+        // L2). The units left over, fewer than the grid has CTAs, are each cut into as many equal pieces of `quota` key tiles as
+        // there are CTAs for: they are laid out on a line, unit r at [r * ustride, r * ustride + steps) with ustride a multiple
+        // of quota (so every cut falls on a piece boundary and the tail of a stride is padding), and CTA c takes the steps
+        // [c * quota, (c + 1) * quota) of the line. The stretch of a CTA's range that lies in one unit is an item. An item that
+        // covers its whole unit stores final rows; otherwise it leaves a partial per row — the normalised output in the storage
+        // type and (running maximum, row sum) — in the CTA's slot 0 (the unit began in an earlier CTA's range) or slot 1 (it
+        // began in this one), and the merge kernel joins the partials of each left-over unit.
+        int     balanced, nq, steps, quota, rounds, ustride;
+        int     total;   // length of the line of left-over units
         void   *part_o;  // [CTAs][2][QT * BM][D] storage type
         float  *part_ml; // [CTAs][2][QT * BM][2]
         // output fan-out (n_dest > 0): every output row goes to dest[0..n_dest) instead of O; when the grid's last block has
@@ -107,16 +112,20 @@ namespace {
                 const int lp  = lp0 + (pos - p.rounds * p.steps);
                 w.valid       = lp < lp1;
                 if (!w.valid) return w;
-                const int ur   = lp / p.steps;
-                w.j0           = lp - ur * p.steps;
+                const int ur   = lp / p.ustride;
+                w.j0           = lp - ur * p.ustride;
+                w.valid        = w.j0 < p.steps; // (else: the padding behind the unit's last piece)
+                if (!w.valid) return w;
                 const int left = p.steps - w.j0, room = lp1 - lp;
                 cnt            = left < room ? left : room;
-                w.slot         = cnt == p.steps ? -1 : (ur * p.steps < lp0 ? 0 : 1);
+                w.slot         = cnt == p.steps ? -1 : (ur * p.ustride < lp0 ? 0 : 1);
                 u              = p.rounds * (int) gridDim.x + ur;
             }
             w.valid      = true;
             w.adv        = cnt;
-            w.last       = pos + cnt >= p.rounds * p.steps && lp0 + (pos + cnt - p.rounds * p.steps) >= lp1;
+            // what comes after this item: another whole unit, a piece of a left-over unit, or nothing
+            const int np  = pos + cnt - p.rounds * p.steps, lpn = lp0 + np;
+            w.last        = !(np < 0 || (lpn < lp1 && lpn % p.ustride < p.steps));
             w.qg         = u % p.nq;
             const int bh = u / p.nq;
             w.h          = bh % (int) p.Hq;
@@ -163,9 +172,10 @@ namespace {
         static constexpr uint32_t oQ   = 0;
         static constexpr uint32_t oK   = oQ + QT * Q_BYTES;
         static constexpr uint32_t oV   = oK + KS * KV_BYTES;
-        static constexpr uint32_t oBar = oV + VS * KV_BYTES;
-        // barriers: q_full, q_read, q_staged, k_full[KS], k_empty[KS], v_full[VS], v_empty[VS], s_full[QT], p_full[QT][kPParts], o_final[QT]
-        static constexpr int nBar = 3 + 2 * KS + 2 * VS + QT * (2 + kPParts);
+        static constexpr uint32_t oStage = oV + VS * KV_BYTES; // output staging: 32 rows x 128 bytes per softmax warp
+        static constexpr uint32_t oBar = oStage + QT * 4 * 4096;
+        // barriers: q_full, q_read, k_full[KS], k_empty[KS], v_full[VS], v_empty[VS], s_full[QT], p_full[QT][kPParts], o_final[QT]
+        static constexpr int nBar = 2 + 2 * KS + 2 * VS + QT * (2 + kPParts);
         static constexpr uint32_t oCtl  = oBar + 8 * nBar;
         static constexpr uint32_t total = oCtl + 16 + 1024;
     };
@@ -272,15 +282,14 @@ namespace {
         const uint32_t sQ = base + L::oQ, sK = base + L::oK, sV = base + L::oV, sBar = base + L::oBar;
         volatile int  *ctl = (volatile int *) (gbase + L::oCtl); // ctl[0] = tmem base, ctl[1] = abort flag
         auto           bar = [&](int i) { return sBar + 8u * (uint32_t) i; };
-        constexpr int  bQ = 0, bQE = 1, bQS = 2, bKF = 3, bKE = bKF + KS, bVF = bKE + KS, bVE = bVF + VS, bSF = bVE + VS, bPF = bSF + QT,
+        constexpr int  bQ = 0, bQE = 1, bKF = 2, bKE = bKF + KS, bVF = bKE + KS, bVE = bVF + VS, bSF = bVE + VS, bPF = bSF + QT,
                       bOF = bPF + QT * kPParts;
 
         const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
         const Work<QT> w_first = work_at<QT>(p, 0); // the first item, looked up while thread 0 sets the barriers up
 
         if (threadIdx.x == 0) {
-            for (int i = 0; i < L::nBar; ++i) // p_full: one arrival per softmax warp of the tile; q_staged: one per softmax warp
-                ptx::mbar_init(bar(i), (i >= bPF && i < bOF) ? 4 : (i == bQS ? 4 * QT : 1));
+            for (int i = 0; i < L::nBar; ++i) ptx::mbar_init(bar(i), (i >= bPF && i < bOF) ? 4 : 1); // p_full: one arrival per softmax warp of the tile
             ctl[1] = 0;
             ptx::fence_mbar_init();
             ptx::prefetch_tmap(&tmQ);
@@ -296,15 +305,15 @@ namespace {
         ptx::tc_fence_after();
         const uint32_t tmem = (uint32_t) ctl[0];
         vkc_grid_dep_wait(); // set-up above overlaps the previous kernel's tail; global memory from here on
-        if (!p.balanced) vkc_grid_dep_launch(); // (the balanced form is followed by its merge kernel, which has nothing to set up early)
+        vkc_grid_dep_launch();
 
         if (warp >= kWarpTma) {
           ptx::setmaxnreg_dec<kRegsControl>();
           if (warp == kWarpTma) {
             // ------------------------------------------------------------------ TMA producer
             // Key tiles are numbered g = 0, 1, ... over all items of the CTA; ring stage g & 1, phase g >> 1. The Q tiles of the
-            // next item are loaded as soon as every Q.K^T MMA of the current one has read them (q_read) and the epilogue no
-            // longer uses their area for staging (q_staged) — normally a whole key tile before the current item ends.
+            // next item are loaded as soon as every Q.K^T MMA of the current one has read them (q_read) — normally a whole key
+            // tile before the current item ends.
             if (ptx::elect_one()) {
                 int  cq = 0; // Q loads issued
                 int  g  = 0;
@@ -325,7 +334,7 @@ namespace {
                         if (j == 0) {
                             if (cq > 0) {
                                 const uint32_t pq = (uint32_t) ((cq - 1) & 1);
-                                if (!(ok = ptx::mbar_wait(bar(bQE), pq, ctl + 1, p.dev_err) && ptx::mbar_wait(bar(bQS), pq, ctl + 1, p.dev_err))) break;
+                                if (!(ok = ptx::mbar_wait(bar(bQE), pq, ctl + 1, p.dev_err))) break;
                             }
                             ptx::mbar_expect_tx(bar(bQ), kQTiles * L::Q_BYTES);
 #pragma unroll
@@ -456,10 +465,12 @@ namespace {
             // What the key-tile loop needs of an item is boiled down to four numbers, so that the item's description does not
             // occupy registers next to a whole row of scores; the epilogue looks the item up again.
             int  n = 0, kbase = 0, jm = 0, lim_row = 0;
+            int  iadv = 0, ib = 0, ih = 0, imisc = 0; // the item's length along the line and what the epilogue needs: batch, head, and group | (slot + 1) << 26 | last << 28 | (n_max > 0) << 29
             bool have = false;
             auto prepare = [&](const Work<QT> &w) {
                 have = w.valid;
                 if (!have) return;
+                iadv = w.adv, ib = w.b, ih = w.h, imisc = w.qg | ((w.slot + 1) << 26) | (w.last ? 1 << 28 : 0) | (w.n_max > 0 ? 1 << 29 : 0);
                 n     = t ? w.n_t[QT - 1] : w.n_t[0]; // (a run-time index would put the whole description into local memory)
                 kbase = w.j0 * BN; // first key of the item
                 const int64_t first = w.m0 + (int64_t) t * BM, off = p.Skv - p.Sq;
@@ -474,11 +485,6 @@ namespace {
                     const int     j2 = (int) (f1 / BN) - w.j0;
                     jm = j2 < jm ? j2 : jm;
                 }
-                // The epilogue stages the rows in the Q area when they go to other GPUs, and in the CTA's last item, where nothing
-                // waits for that area; every other item leaves the area alone, and says so at once, so that the next item's Q
-                // tiles can be fetched while this one is being computed.
-                const bool staged = w.n_max > 0 && (w.last || (w.slot < 0 && p.fan.n_dest > 0));
-                if (w.n_max > 0 && !staged && lane == 0) ptx::mbar_arrive(bar(bQS));
             };
             prepare(w_first);
           for (int pos = 0; ok && have;) {
@@ -654,12 +660,12 @@ namespace {
                 if (!(j >= jm ? tile(std::true_type{}, j) : tile(std::false_type{}, j))) break;
             }
             if (!ok) break;
-            const Work<QT> w = work_at<QT>(p, pos);
-            pos += w.adv;
-            const int      b = w.b, h = w.h;
-            const int64_t  m0 = w.m0, row = m0 + (int64_t) t * BM + r;
+            struct { int slot; bool last; int n_max; } w; // (n_max: only whether the item had work)
+            w.slot = ((imisc >> 26) & 3) - 1, w.last = (imisc >> 28) & 1, w.n_max = (imisc >> 29) & 1;
+            pos += iadv;
+            const int      b = ib, h = ih;
+            const int64_t  m0 = (int64_t) (imisc & ((1 << 26) - 1)) * (QT * BM), row = m0 + (int64_t) t * BM + r;
             const int      ndest  = w.slot >= 0 ? 0 : p.fan.n_dest; // fan-out of final rows only (the launcher checked alignment)
-            const bool     staged = w.n_max > 0 && (w.last || ndest > 0);
             // epilogue of the item
             if (n > 0) {
                 ok = ptx::mbar_wait(bar(bOF + t), (uint32_t) (co & 1), ctl + 1, p.dev_err);
@@ -690,64 +696,48 @@ namespace {
                     }
                 }
                 if (vec_ok) {
-                    // the whole row of O_t in one go (the score registers are free here)
-                    uint32_t v[D];
-                    if (n > 0) {
+                    // Coalesced stores. Thread = row would write 16 bytes per row and instruction: 32 scattered segments per warp
+                    // store (partly filled sectors in local memory, and each its own NVLink packet when the destination is a
+                    // peer). The warp therefore stages 64 columns of its 32 rows (128 bytes per row) in its own 4 KB of shared
+                    // memory, in 16-byte chunks XOR-swizzled by the row, and then writes whole 128-byte lines: 4 rows per
+                    // instruction.
+                    const uint32_t sStage = base + L::oStage + (uint32_t) (t * 4 + q) * 4096;
+                    // partial rows are dense [.., QT * BM, D]; final rows follow the caller's output strides
+                    const int64_t row_stride = partial ? (int64_t) D : p.os[2];
+                    const int64_t base_off   = partial ? (prow0 - (m0 + (int64_t) t * BM)) * D : (int64_t) b * p.os[0] + (int64_t) h * p.os[1];
+                    T *const      obase      = partial ? (T *) p.part_o : (T *) p.O;
+#pragma unroll 1
+                    for (int c = 0; c < D / 64; ++c) {
+                        uint32_t v[64];
+                        if (n > 0) {
+                            ptx::tmem_ld_x32(tO + c * 64, *reinterpret_cast<uint32_t(*)[32]>(v));
+                            ptx::tmem_ld_x32(tO + c * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(v + 32));
+                            ptx::tc_wait_ld();
+                        } else {
 #pragma unroll
-                        for (int c = 0; c < D / 32; ++c) ptx::tmem_ld_x32(tO + c * 32, *reinterpret_cast<uint32_t(*)[32]>(v + c * 32));
-                        ptx::tc_wait_ld();
-                    } else {
-#pragma unroll
-                        for (int i = 0; i < D; ++i) v[i] = 0u;
-                    }
-                    auto packed = [&](int g) { // 16 bytes of the normalised row
-                        uint4 o;
-                        o.x = pack2<T>(__uint_as_float(v[g * 8 + 0]) * inv, __uint_as_float(v[g * 8 + 1]) * inv);
-                        o.y = pack2<T>(__uint_as_float(v[g * 8 + 2]) * inv, __uint_as_float(v[g * 8 + 3]) * inv);
-                        o.z = pack2<T>(__uint_as_float(v[g * 8 + 4]) * inv, __uint_as_float(v[g * 8 + 5]) * inv);
-                        o.w = pack2<T>(__uint_as_float(v[g * 8 + 6]) * inv, __uint_as_float(v[g * 8 + 7]) * inv);
-                        return o;
-                    };
-                    if (!staged) {
-                        // thread = row: 16-byte stores straight from the registers (L2 merges the halves of a sector)
-                        if (row < p.Sq) {
-#pragma unroll
-                            for (int g = 0; g < D / 8; ++g) {
-                                if (ndest == 0) *reinterpret_cast<uint4 *>(orow + g * 8) = packed(g);
-                                else vkc_fanout_store16<T>(p.fan, ooff + g * 8, packed(g)); // an item without keys: NaN rows, rare
-                            }
+                            for (int i = 0; i < 64; ++i) v[i] = 0u;
                         }
-                    } else {
-                        // Coalesced stores. Thread = row writes 16 bytes per row and instruction: 32 scattered segments per warp
-                        // store, each its own NVLink packet when the destination is a peer. The warp therefore stages its 32 rows
-                        // in this tile's Q area, which is idle once O is final (every MMA that read Q has completed, and the
-                        // producer waits for q_staged before it refills the area), in 16-byte chunks XOR-swizzled by the row, and
-                        // then writes whole rows: 32 / CH rows of CH contiguous chunks per instruction.
-                        constexpr int  CH     = D / 8; // 16-byte chunks per row
-                        const uint32_t sStage = sQ + (uint32_t) t * L::Q_BYTES + (uint32_t) (q * 32) * (D * 2);
 #pragma unroll
-                        for (int g = 0; g < CH; ++g) {
-                            const uint4 o = packed(g);
-                            ptx::st_shared_v4(sStage + (uint32_t) lane * (D * 2) + (uint32_t) ((g ^ (lane & (CH - 1))) << 4), o.x, o.y, o.z, o.w);
+                        for (int g = 0; g < 8; ++g) {
+                            uint32_t o32[4];
+#pragma unroll
+                            for (int i = 0; i < 4; ++i)
+                                o32[i] = pack2<T>(__uint_as_float(v[g * 8 + 2 * i]) * inv, __uint_as_float(v[g * 8 + 2 * i + 1]) * inv);
+                            ptx::st_shared_v4(sStage + (uint32_t) lane * 128 + (uint32_t) ((g ^ (lane & 7)) << 4), o32[0], o32[1], o32[2], o32[3]);
                         }
                         __syncwarp();
-                        // partial rows are dense [.., QT * BM, D]; final rows follow the caller's output strides
-                        const int64_t row_stride = partial ? (int64_t) D : p.os[2];
-                        const int64_t base_off   = partial ? (prow0 - (m0 + (int64_t) t * BM)) * D : (int64_t) b * p.os[0] + (int64_t) h * p.os[1];
-                        T *const      obase      = partial ? (T *) p.part_o : (T *) p.O;
-#pragma unroll 1
-                        for (int i = 0; i < CH; ++i) {
-                            const int     rr   = i * (32 / CH) + lane / CH, ch = lane % CH;
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            const int     rr   = i * 4 + (lane >> 3), ch = lane & 7;
                             const int64_t grow = m0 + (int64_t) t * BM + q * 32 + rr;
-                            const uint4   o4   = ptx::ld_shared_v4(sStage + (uint32_t) rr * (D * 2) + (uint32_t) ((ch ^ (rr & (CH - 1))) << 4));
+                            const uint4   o4   = ptx::ld_shared_v4(sStage + (uint32_t) rr * 128 + (uint32_t) ((ch ^ (rr & 7)) << 4));
                             if (grow < p.Sq) {
-                                const int64_t off = base_off + grow * row_stride + ch * 8;
+                                const int64_t off = base_off + grow * row_stride + c * 64 + ch * 8;
                                 if (ndest == 0) *reinterpret_cast<uint4 *>(obase + off) = o4;
                                 else vkc_fanout_store16<T>(p.fan, off, o4);
                             }
                         }
-                        __syncwarp();
-                        if (lane == 0) ptx::mbar_arrive(bar(bQS)); // this warp no longer reads the Q area
+                        __syncwarp(); // the staging lines are rewritten by the next 64 columns
                     }
                 } else {
 #pragma unroll 1
@@ -770,10 +760,10 @@ namespace {
                 // pipe starts a new O_t
                 ptx::tc_fence_before();
             }
+            if (w.last) break;
             prepare(work_at<QT>(p, pos));
           }
         }
-        if (p.balanced) vkc_grid_dep_launch(); // this CTA's share is done: the merge kernel may be brought in
         if (ctl[1]) {
             for (int i = 0; i < 50; ++i) __nanosleep(20000); // aborted: let copies in flight land
         }
@@ -798,7 +788,7 @@ namespace {
         vkc_grid_dep_launch();
         if (ur < left) {
             const int64_t u  = (int64_t) p.rounds * main_ctas + ur;
-            const int64_t s0 = (int64_t) ur * p.steps, s1 = s0 + p.steps - 1; // the unit's steps in the line
+            const int64_t s0 = (int64_t) ur * p.ustride, s1 = s0 + p.steps - 1; // the unit's steps in the line
             const int64_t ca = s0 / p.quota, cb = s1 / p.quota;
             const int     qg = (int) (u % p.nq);
             const int64_t bh = u / p.nq, h = bh % p.Hq, b = bh / p.Hq, grow = (int64_t) qg * ROWS + rr;
@@ -839,22 +829,29 @@ namespace {
         if (p.fan.n_dest > 0) fanout_signal(p.fan, gridDim.x);
     }
 
-    // How the balanced form would cut the work of two-tile units, and a rough cost of both forms in key-tile steps of one CTA
-    // (a unit run by a CTA of its own pays about two steps for launch, set-up, first loads and the final stores; an item of a
-    // persistent CTA about one; the merge pass about three).
+    // How the balanced form would distribute `units` units of `steps` key tiles over `slots` resident CTAs, and a rough cost of
+    // both forms in key-tile steps of one CTA (a unit run by a CTA of its own pays about two steps for launch, set-up, first
+    // loads and the final stores; an item of a persistent CTA about one; cut units pay about three more for the merge pass).
     struct Plan {
-        int64_t ctas, rounds, left, total, quota;
+        int64_t ctas, rounds, left, total, quota, ustride, pieces;
         double  cost_balanced, cost_per_unit;
     };
     inline Plan plan_balanced(int64_t units, int64_t steps, int64_t slots) {
         Plan pl;
-        pl.ctas = units >= slots ? slots : (units * steps + 3) / 4; // at least four key tiles per CTA
-        if (pl.ctas > slots) pl.ctas = slots;
+        pl.rounds = units / slots, pl.left = units - pl.rounds * slots;
+        pl.pieces = 1, pl.quota = steps, pl.ustride = steps;
+        if (pl.left > 0) { // pieces of at least three key tiles, as many per unit as there are CTAs for
+            int64_t want = slots / pl.left;
+            if (want > steps / 3) want = steps / 3;
+            if (want < 1) want = 1;
+            pl.quota   = (steps + want - 1) / want;
+            pl.pieces  = (steps + pl.quota - 1) / pl.quota;
+            pl.ustride = pl.pieces * pl.quota;
+        }
+        pl.total = pl.left * pl.ustride;
+        pl.ctas  = pl.rounds > 0 ? slots : pl.left * pl.pieces;
         if (pl.ctas < 1) pl.ctas = 1;
-        pl.rounds = units / pl.ctas, pl.left = units - pl.rounds * pl.ctas, pl.total = pl.left * steps;
-        pl.quota  = (pl.total + pl.ctas - 1) / pl.ctas;
-        if (pl.quota < 4) pl.quota = 4;
-        pl.cost_balanced = (double) pl.rounds * (steps + 1.0) + (pl.left > 0 ? (double) pl.quota + 2.0 + 3.0 : 0.0);
+        pl.cost_balanced = (double) pl.rounds * (steps + 1.0) + (pl.left > 0 ? (double) pl.quota + (pl.pieces > 1 ? 2.0 + 3.0 : 1.0) : 0.0);
         pl.cost_per_unit = (double) ((units + slots - 1) / slots) * (steps + 2.0);
         return pl;
     }
@@ -869,21 +866,23 @@ namespace {
         const int64_t nq = (p.Sq + QT * BM - 1) / (QT * BM), units = nq * p.Hq * B, steps = (p.Skv + BN - 1) / BN;
         const int64_t slots = (int64_t) ctx->sm_count * (QT == 1 ? 2 : 1);
         p.balanced = 0;
-        p.nq = (int) nq, p.steps = (int) steps, p.quota = 1, p.total = 0, p.rounds = 0;
+        p.nq = (int) nq, p.steps = (int) steps, p.quota = 1, p.total = 0, p.rounds = 0, p.ustride = (int) steps;
         if (balanced) {
             const Plan   pl       = plan_balanced(units, steps, slots);
+            const bool   plain    = pl.rounds == 0 && pl.pieces == 1; // one whole unit per CTA: the three-dimensional grid does the same
             const size_t prows    = (size_t) pl.ctas * 2 * QT * BM;
             const size_t ml_bytes = (prows * 2 * sizeof(float) + 255) & ~(size_t) 255;
-            if (vkc_ensure_scratch(ctx, ml_bytes + prows * D * 2 + 256, st) == VKC_OK) {
+            if (!plain && vkc_ensure_scratch(ctx, ml_bytes + prows * D * 2 + 256, st) == VKC_OK) {
                 p.balanced = 1;
                 p.rounds   = (int) pl.rounds;
                 p.quota    = (int) pl.quota;
+                p.ustride  = (int) pl.ustride;
                 p.total    = (int) pl.total;
                 p.part_ml  = (float *) ctx->scratch;
                 p.part_o   = (char *) ctx->scratch + ml_bytes;
                 vkc_launch(ctx, kern, dim3((unsigned) pl.ctas), dim3(threads_for(QT)), smem, st, tq, tk, tv, p);
                 if (int rc = vkc_post_launch(ctx, "attn_prefill_tcgen05")) return rc;
-                if (pl.left == 0 && p.fan.n_dest == 0) return VKC_OK; // nothing was cut
+                if ((pl.left == 0 || pl.pieces == 1) && p.fan.n_dest == 0) return VKC_OK; // nothing was cut
                 // (with a fan-out the merge kernel also publishes the flags, so it runs even when it has nothing to join)
                 const int64_t threads = pl.left * QT * BM * (D / 8);
                 vkc_launch(ctx, attn_prefill_merge_kernel<T, D, QT>, dim3((unsigned) (threads > 0 ? (threads + 255) / 256 : 1)), dim3(256), 0, st, p,
@@ -911,13 +910,11 @@ namespace {
                 const int64_t tiles = ((p.Sq + BM - 1) / BM) * p.Hq * B;
                 const Plan    p1    = plan_balanced(tiles, steps, 2 * sms);
                 pu                  = p1.cost_per_unit;
-                if (p1.cost_balanced < bal) bal = p1.cost_balanced, one_tile_balanced = true;
+                // (on a tie the two-tile form when whole rounds of units dominate, the one-tile form for a handful of units)
+                if (p1.cost_balanced < bal || (p1.cost_balanced == bal && p1.rounds == 0)) bal = p1.cost_balanced, one_tile_balanced = true;
             }
             balanced = bal < 0.985 * pu;
         }
-        const char *envb = getenv("VKNN_PREFILL_BALANCED"), *envq = getenv("VKNN_PREFILL_QT");
-        if (envb) balanced = balanced && atoi(envb) != 0;
-        if (envq && D == 64) one_tile_balanced = atoi(envq) == 1;
         if (one_tile && (!balanced || one_tile_balanced)) return launch_attn_qt<T, 64, 1>(ctx, tq, tk, tv, p, B, balanced, st);
         return launch_attn_qt<T, D, 2>(ctx, tq, tk, tv, p, B, balanced, st);
     }

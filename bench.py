@@ -38,12 +38,12 @@ L2_BYTES = 126 * 1024 * 1024
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 # DRAM traffic per unit (dram__bytes_read.sum + dram__bytes_write.sum) from one ncu capture per kernel:
-#   prefill  : 114.56 MB for 4 x 16 x 2048 (batch, head, query row) units; K/V re-reads are served by L2, so DRAM traffic
+#   prefill  : 111.72 MB for 4 x 16 x 2048 (batch, head, query row) units; K/V re-reads are served by L2, so DRAM traffic
 #              grows with the number of row units;
-#   decode   : 1.0266 x the algorithmic bytes of the launch;
+#   decode   : 1.021 x the algorithmic bytes of the launch;
 #   layernorm: 1.0 x (the capture moved the algorithmic bytes; hit rate 3.6 %).
-NCU_PREFILL_DRAM_BYTES_PER_ROW_UNIT = 874.0
-NCU_DECODE_DRAM_OVER_ALGORITHMIC = 1.0266
+NCU_PREFILL_DRAM_BYTES_PER_ROW_UNIT = 852.4
+NCU_DECODE_DRAM_OVER_ALGORITHMIC = 1.021
 
 PREFILL = dict(B=4, H=16, S=8192, D=128, causal=False, dtype="bf16", seed=1005)
 DECODE = dict(B=32, Hq=32, Hkv=8, L=8192, D=128, seed=1005)

@@ -123,9 +123,10 @@ namespace {
             }
             w.valid      = true;
             w.adv        = cnt;
-            // what comes after this item: another whole unit, a piece of a left-over unit, or nothing
-            const int np  = pos + cnt - p.rounds * p.steps, lpn = lp0 + np;
-            w.last        = !(np < 0 || (lpn < lp1 && lpn % p.ustride < p.steps));
+            // what comes after this item: another whole unit, a piece of a left-over unit, or nothing (the item ends j0 + cnt
+            // steps into its unit's stride: at its end the next unit begins, past `steps` lies padding)
+            const int np = pos + cnt - p.rounds * p.steps, nj = w.j0 + cnt;
+            w.last       = !(np < 0 || (lp0 + np < lp1 && (np == 0 || nj == p.ustride || nj < p.steps)));
             w.qg         = u % p.nq;
             const int bh = u / p.nq;
             w.h          = bh % (int) p.Hq;
@@ -286,9 +287,8 @@ namespace {
                       bOF = bPF + QT * kPParts;
 
         const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-        const Work<QT> w_first = work_at<QT>(p, 0); // the first item, looked up while thread 0 sets the barriers up
 
-        if (threadIdx.x == 0) {
+        if (threadIdx.x == (kWarpMma + 1) * 32) { // a thread of an idle warp, so that the set-up runs beside the look-up above
             for (int i = 0; i < L::nBar; ++i) ptx::mbar_init(bar(i), (i >= bPF && i < bOF) ? 4 : 1); // p_full: one arrival per softmax warp of the tile
             ctl[1] = 0;
             ptx::fence_mbar_init();
@@ -300,6 +300,14 @@ namespace {
             ptx::tmem_alloc(base + L::oCtl, kTmemCols);
             ptx::tmem_relinquish();
         }
+        const Work<QT> w_first = work_at<QT>(p, 0); // the first item, looked up while the barriers are being set up
+        // the item after `cur` (which began at step `pos` minus its length); none behind the CTA's last
+        auto next_work = [&](const Work<QT> &cur, int pos) {
+            if (!cur.last) return work_at<QT>(p, pos);
+            Work<QT> none;
+            none.valid = false;
+            return none;
+        };
         ptx::tc_fence_before();
         __syncthreads();
         ptx::tc_fence_after();
@@ -320,7 +328,7 @@ namespace {
                 bool ok = true;
                 const int hq_per_kv = (int) (p.Hq / p.Hkv);
                 Work<QT>  w = w_first;
-                for (int pos = 0; ok; w = work_at<QT>(p, pos)) {
+                for (int pos = 0; ok; w = next_work(w, pos)) {
                     if (!w.valid) break;
                     pos += w.adv;
                     const int hk = w.h / hq_per_kv;
@@ -389,7 +397,7 @@ namespace {
 #pragma unroll
                 for (int t = 0; t < kQTiles; ++t) cs[t] = 0;
                 Work<QT> w = w_first;
-                for (int pos = 0; ok; w = work_at<QT>(p, pos)) {
+                for (int pos = 0; ok; w = next_work(w, pos)) {
                     if (!w.valid) break;
                     pos += w.adv;
                     if (w.n_max == 0) continue;

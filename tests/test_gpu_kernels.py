@@ -410,6 +410,53 @@ def test_decode(ctx, impl, dt, B, Hq, Hkv, L, D):
     assert torch.equal(O, O2)
 
 
+@pytest.mark.parametrize("case", ["many_short", "zeros_between", "all_empty", "one_long", "tile_edges"])
+def test_decode_equal_runs_of_tiles(ctx, case):
+    """The tensor-core decode kernel lays the 128-key tiles of all (sequence, kv head) units end to end and gives every CTA an
+    equal run of that line. Cases that stress the cuts: many short sequences (a CTA's run spans several units and several
+    sequences), empty sequences between full ones (units without a tile; their rows are NaN like the reference's 0/0), a
+    batch with nothing in it, a single long unit cut into many pieces, and lengths on both sides of every tile edge."""
+    rng = np.random.default_rng(len(case))
+    D, dt = 128, "f16"
+    if case == "many_short":
+        B, Hq, Hkv, L = 40, 16, 4, 640
+        kv_len = rng.integers(0, L + 1, B)
+    elif case == "zeros_between":
+        B, Hq, Hkv, L = 9, 8, 2, 1500
+        kv_len = np.array([L, 0, 1, 0, 0, 777, L, 0, 129])
+    elif case == "all_empty":
+        B, Hq, Hkv, L = 3, 8, 2, 300
+        kv_len = np.zeros(B)
+    elif case == "one_long":
+        B, Hq, Hkv, L = 1, 4, 1, 8192
+        kv_len = np.array([8191])
+    else:
+        B, Hq, Hkv, L = 12, 32, 8, 1024
+        kv_len = np.array([127, 128, 129, 255, 256, 257, 511, 512, 513, 1023, 1024, 1])
+    kv_len = kv_len.astype(np.int32)
+    q = round_to(rng.standard_normal((B, Hq, D)), DT[dt])
+    k = round_to(rng.standard_normal((B, Hkv, L, D)), DT[dt])
+    v = round_to(rng.standard_normal((B, Hkv, L, D)), DT[dt])
+    scale = 1.0 / np.sqrt(D)
+    Kd, Vd = dev(k, DT[dt]), dev(v, DT[dt])
+    for b in range(B):
+        Kd[b, :, int(kv_len[b]):] = float("nan")
+        Vd[b, :, int(kv_len[b]):] = float("nan")
+    O = torch.full((B, Hq, D), 7.0, dtype=DT[dt], device="cuda")
+    ctx.set_impl(vknn_b200.IMPL_TCGEN05)
+    try:
+        ctx.attn_decode(dev(q, DT[dt]), Kd, Vd, O, scale, kv_len=torch.from_numpy(kv_len).cuda())
+        ctx.sync()
+    finally:
+        ctx.set_impl(vknn_b200.IMPL_AUTO)
+    got = host(O)
+    full = kv_len > 0
+    assert np.isnan(got[~full]).all()  # a sequence without keys: 0/0
+    if full.any():
+        ref = vko.attention(q[full][:, :, None, :], k[full], v[full], scale, kv_len=kv_len[full])[:, :, 0, :]
+        assert_low(got[full], ref, "decode %s" % case)
+
+
 def test_decode_config5_shape_slice(ctx):
     """Config 5 geometry (32 q / 8 kv heads, D=128, cache 8192, kv_len in [1024, 8192]) on 4 sequences."""
     rng = np.random.default_rng(1005)

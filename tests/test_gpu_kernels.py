@@ -266,6 +266,39 @@ def test_attention_balanced_forms(ctx, dt, B, H, Sq, Skv, D, merged):
     assert_low(got[:, :, rows], ref, "balanced attention")
 
 
+def test_attention_balanced_forms_random_shapes(ctx):
+    """Forty random unmasked shapes (1 to 400 units of 1 to 24 key tiles, both head sizes, ragged ends, Sq != Skv), so that the
+    work distribution of the persistent form meets many combinations of rounds, left-over units and pieces. The output buffer
+    starts as NaN: a row that no item wrote shows. Compared with the SIMT kernel of the same library."""
+    rng = np.random.default_rng(4242)
+    for case in range(40):
+        D = int(rng.choice([64, 128]))
+        dt = "f16" if case % 2 else "bf16"
+        tdt = DT[dt]
+        Sq = int(rng.integers(1, 1400))
+        Skv = Sq if case % 3 else int(rng.integers(1, 3000))
+        groups = (Sq + 255) // 256
+        bh = max(1, int(rng.integers(1, 401)) // groups)
+        H = int(rng.choice([h for h in (1, 2, 3, 4, 6, 8, 12, 16) if h <= bh]))
+        B = max(1, bh // H)
+        q = torch.randn(B, H, Sq, D, device="cuda").to(tdt)
+        k = torch.randn(B, H, Skv, D, device="cuda").to(tdt)
+        v = torch.randn(B, H, Skv, D, device="cuda").to(tdt)
+        outs = []
+        for impl in (vknn_b200.IMPL_TCGEN05, vknn_b200.IMPL_SIMT):
+            o = torch.full_like(q, float("nan"))
+            ctx.set_impl(impl)
+            try:
+                ctx.attn_prefill(q, k, v, o, D ** -0.5)
+                ctx.sync()
+            finally:
+                ctx.set_impl(vknn_b200.IMPL_AUTO)
+            outs.append(o.float())
+        what = "case %d: B=%d H=%d Sq=%d Skv=%d D=%d %s" % (case, B, H, Sq, Skv, D, dt)
+        assert torch.isfinite(outs[0]).all(), what
+        assert float((outs[0] - outs[1]).abs().max()) <= (4e-3 if dt == "f16" else 2e-2), what
+
+
 def test_captured_graph_survives_scratch_growth():
     """A key-range-split attention keeps its partials in the context's scratch block, whose address a captured CUDA graph
     bakes in. A later, larger call makes the scratch grow; the block the graph points at must stay alive (it is retired,

@@ -222,8 +222,8 @@ def test_attention_maximum_grows_in_a_late_key_tile(ctx, dt, D, jump):
 @pytest.mark.parametrize("dt", ["f16", "bf16"])
 @pytest.mark.parametrize("B,Hq,Hkv,Sq,Skv", [(1, 2, 2, 1100, 1100), (2, 4, 2, 777, 1303), (1, 16, 16, 300, 2738)])
 def test_attention_head64_key_range_split(ctx, dt, B, Hq, Hkv, Sq, Skv):
-    """Head size 64, no mask, at least eight key tiles and a shallow grid: the tensor-core path cuts the key range in two
-    and merges the halves (ragged last key tile, GQA, ragged query tiles, Sq != Skv)."""
+    """Head size 64, no mask, at least eight key tiles and only a few units: the tensor-core path cuts every unit into pieces
+    of its key range, one per CTA, and merges them (ragged last key tile, GQA, ragged query tiles, Sq != Skv)."""
     tdt = torch.float16 if dt == "f16" else torch.bfloat16
     rng = np.random.default_rng(B + Sq + Skv)
     q = round_to(rng.standard_normal((B, Hq, Sq, 64)), tdt)
@@ -232,7 +232,7 @@ def test_attention_head64_key_range_split(ctx, dt, B, Hq, Hkv, Sq, Skv):
     ref = vko.attention(q, k, v, 0.125)
     n0 = ctx.launch_count()
     got = run_attn(ctx, q, k, v, 0.125, dt, impl=vknn_b200.IMPL_TCGEN05)
-    assert ctx.launch_count() - n0 == 2  # the attention kernel and the merge of the two key ranges
+    assert ctx.launch_count() - n0 == 2  # the attention kernel and the merge of the pieces
     assert_low(got, ref, "attn split")
 
 

@@ -88,13 +88,21 @@ namespace {
     }
     __host__ __device__ constexpr int tmem_cols(int bn) { return bn <= 32 ? 32 : bn <= 64 ? 64 : bn <= 128 ? 128 : 256; } // power of two >= BN
 
+    // Epilogue warps of the one-tile form: eight (two per tensor-memory lane quarter, taking the tile's 64-column slabs
+    // alternately) where one CTA has the SM to itself and K is not split, else four. The epilogue of this form is not hidden
+    // behind anything, and a slab is a chain of latencies: 0.7 us each with one warp per quarter.
+    __host__ __device__ constexpr int epi_warps(int ctas_per_sm, int split) { return ctas_per_sm == 1 && split == 1 ? 8 : 4; }
+    __host__ __device__ constexpr int threads_of(int ctas_per_sm, int split) { return 64 + 32 * epi_warps(ctas_per_sm, split); }
+
     template <int BN, int kStages, int kCtasPerSm, typename T, bool B_KN, int kSplit = 1>
-    __global__ void __launch_bounds__(kThreads, kCtasPerSm)
+    __global__ void __launch_bounds__(threads_of(kCtasPerSm, kSplit), kCtasPerSm)
         gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmD,
                             const __grid_constant__ CUtensorMap tmR, GemmParams p) {
         static_assert((BN / 64 + (BN % 64 != 0)) * 16384 <= kStages * (BM * BK * 2 + BN * BK * 2), "epilogue staging must fit in the operand ring");
         static_assert(kSplit == 1 || 65536 + ((BN + 63) / 64 - ((BN + 63) / 64) / kSplit) * 32768 <= kStages * (BM * BK * 2 + BN * BK * 2),
                       "split-K send staging must fit in the operand ring behind the epilogue staging");
+        constexpr int kEpiW = epi_warps(kCtasPerSm, kSplit), kThr = threads_of(kCtasPerSm, kSplit);
+        static_assert(8 * (2 * kStages + 2 + kEpiW) <= 256, "barrier area");
         constexpr uint32_t A_BYTES = BM * BK * 2;
         constexpr uint32_t B_BYTES = BN * BK * 2;
         constexpr bool     kBf16   = std::is_same<T, __nv_bfloat16>::value;
@@ -130,7 +138,7 @@ namespace {
                 ptx::mbar_init(sBar + 8 * (kStages + s), 1);
             }
             ptx::mbar_init(sBar + 8 * 2 * kStages, 1);
-            for (int w = 0; w < 4; ++w) ptx::mbar_init(sBar + 8 * (2 * kStages + 2 + w), 1); // residual tile landed, per epilogue warp
+            for (int w = 0; w < kEpiW; ++w) ptx::mbar_init(sBar + 8 * (2 * kStages + 2 + w), 1); // residual tile landed, per epilogue warp
             if (kSplit > 1) ptx::mbar_init(sRecvBar, 1); // this CTA's own arrival; the partials arrive as transaction bytes
             ctl[1] = 0;
             ptx::fence_mbar_init();
@@ -153,7 +161,7 @@ namespace {
         vkc_grid_dep_wait(); // everything above overlapped the previous kernel's tail; global memory from here on
         vkc_grid_dep_launch();
         if (warp >= 2 && (p.epilogue & VKC_EPI_BIAS)) {
-            for (int j = threadIdx.x - 64; j < BN; j += kThreads - 64) sbias[j] = (int64_t) n0 + j < p.N ? __ldg(p.bias + n0 + j) : 0.f;
+            for (int j = threadIdx.x - 64; j < BN; j += kThr - 64) sbias[j] = (int64_t) n0 + j < p.N ? __ldg(p.bias + n0 + j) : 0.f;
         }
         ptx::tc_fence_before();
         __syncthreads();
@@ -261,24 +269,26 @@ namespace {
                     constexpr int kSlabs = (BN + 63) / 64;
                     const int      row0  = m0 + q * 32;
                     const bool     rows_in = row0 < p.M; // warp-uniform
-                    const uint32_t rbar  = sBar + 8 * (2 * kStages + 2 + q);
-                    int            nslab = 0, nmine = 0; // slabs inside N; of those, the ones this CTA finishes
+                    // this warp's slabs: first, first + step, ... (split-K: the slabs this CTA owns; eight warps: alternate slabs)
+                    const int      first = kEpiW == 8 ? (warp - 2) >> 2 : krank, step = kEpiW == 8 ? 2 : kSplit;
+                    const uint32_t rbar  = sBar + 8 * (2 * kStages + 2 + (warp - 2));
+                    int            nslab = 0, nmine = 0; // slabs inside N; of those, the ones this warp finishes
                     for (int sl = 0; sl < kSlabs; ++sl)
                         if ((int64_t) n0 + sl * 64 < p.N) {
                             nslab = sl + 1;
-                            if (sl % kSplit == krank) ++nmine;
+                            if (sl % step == first) ++nmine;
                         }
                     bool rok = true;
                     if ((p.epilogue & VKC_EPI_RESIDUAL) && rows_in && nmine > 0) {
                         if (lane == 0) {
                             ptx::mbar_expect_tx(rbar, (uint32_t) nmine * 4096u);
-                            for (int sl = krank; sl < nslab; sl += kSplit) ptx::tma_load_3d(base + sl * 16384 + q * 4096, &tmR, n0 + sl * 64, row0, bz, rbar);
+                            for (int sl = first; sl < nslab; sl += step) ptx::tma_load_3d(base + sl * 16384 + q * 4096, &tmR, n0 + sl * 64, row0, bz, rbar);
                         }
                         rok = ptx::mbar_wait(rbar, 0, ctl + 1, p.dev_err);
                         rok = __all_sync(0xffffffffu, rok);
                     }
 #pragma unroll 1
-                    for (int sl = krank; sl < nslab && rok; sl += kSplit) {
+                    for (int sl = first; sl < nslab && rok; sl += step) {
                         uint8_t *blk = gbase + sl * 16384 + q * 4096 + lane * 128;
                         // both 32-column halves are fetched before the single wait, so that their arithmetic interleaves
                         uint32_t r2[2][32];
@@ -342,7 +352,7 @@ namespace {
                     }
                     if (lane == 0) ptx::bulk_wait_group_read_0();
                     __syncwarp();
-                } else
+                } else if (warp < 6) // (plain stores, unaligned outputs: one warp per lane quarter does all columns)
 #pragma unroll 1
                 for (int c = 0; c < BN / 32; ++c) {
                     const int64_t nb = (int64_t) n0 + c * 32;
@@ -413,7 +423,7 @@ namespace {
         static_assert(8 * (2 * kStages + 7) <= 256, "barrier area");
         if (int rc = vkc_configure_smem(ctx, kern, smem)) return rc;
         dim3 grid((unsigned) ((p.M + BM - 1) / BM) * kSplit, (unsigned) ((p.N + BN - 1) / BN), (unsigned) batch);
-        vkc_launch_cluster(ctx, kern, grid, dim3(kThreads), smem, st, (unsigned) kSplit, tmA, tmB, tmD, tmR, p);
+        vkc_launch_cluster(ctx, kern, grid, dim3(threads_of(kCtasPerSm, kSplit)), smem, st, (unsigned) kSplit, tmA, tmB, tmD, tmR, p);
         return vkc_post_launch(ctx, "gemm_tcgen05");
     }
 

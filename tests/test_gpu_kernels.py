@@ -266,6 +266,41 @@ def test_attention_balanced_forms(ctx, dt, B, H, Sq, Skv, D, merged):
     assert_low(got[:, :, rows], ref, "balanced attention")
 
 
+@pytest.mark.parametrize("dt,B,H,S,D", [("bf16", 7, 16, 1536, 128), ("f16", 3, 40, 2048, 64), ("bf16", 5, 64, 512, 128)])
+def test_attention_causal_paired_blocks(ctx, dt, B, H, S, D):
+    """Causal mask with Sq = Skv a multiple of 256 and enough work for more than two rounds of the SMs: the persistent form
+    pairs the query groups (n - 1 - k, k) of a head into blocks of equal length, runs whole blocks round-robin and cuts the
+    left-over blocks into pieces (a piece may hold the end of the long group and the start of the short one). Every row is
+    compared with the SIMT kernel, 40 rows of every head with the oracle; the output starts as NaN."""
+    tdt = DT[dt]
+    rng = np.random.default_rng(B * 1000 + H + S + D)
+    q = round_to(rng.standard_normal((B, H, S, D)), tdt)
+    k = round_to(rng.standard_normal((B, H, S, D)), tdt)
+    v = round_to(rng.standard_normal((B, H, S, D)), tdt)
+    scale = 1.0 / np.sqrt(D)
+    Q, K, V = dev(q, tdt), dev(k, tdt), dev(v, tdt)
+    outs = []
+    for impl in (vknn_b200.IMPL_TCGEN05, vknn_b200.IMPL_SIMT):
+        O = torch.full_like(Q, float("nan"))
+        ctx.set_impl(impl)
+        try:
+            ctx.attn_prefill(Q, K, V, O, scale, causal=True)
+            ctx.sync()
+        finally:
+            ctx.set_impl(vknn_b200.IMPL_AUTO)
+        outs.append(host(O))
+    assert np.isfinite(outs[0]).all()
+    assert float(np.abs(outs[0] - outs[1]).max()) <= (4e-3 if dt == "f16" else 3e-2)
+    rows = sorted(set([0, 1, 127, 128, 255, 256, 257, S // 2, S - 257, S - 256, S - 129, S - 128, S - 2, S - 1] + list(rng.integers(0, S, 26))))
+    mask = np.zeros((len(rows), S), np.float32)
+    for i, r in enumerate(rows):
+        mask[i, r + 1:] = -np.inf
+    ref = vko.attention(np.ascontiguousarray(q[:, :, rows]), k, v, scale, mask=mask)
+    # the first rows see a handful of keys and return (nearly) a V row, |y| up to 4: 1e-2 wherever |y| <= 2, 3 ulps of the rounded
+    # oracle output above that (cut units pass through partials in the storage type)
+    assert_storage(outs[0][:, :, rows], ref, dt, "causal paired blocks", ulps=3, floor=2.0)
+
+
 def test_attention_balanced_forms_random_shapes(ctx):
     """Forty random unmasked shapes (1 to 400 units of 1 to 24 key tiles, both head sizes, ragged ends, Sq != Skv), so that the
     work distribution of the persistent form meets many combinations of rounds, left-over units and pieces. The output buffer

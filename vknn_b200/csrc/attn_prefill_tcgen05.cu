@@ -3,8 +3,9 @@
 // key/value sequence in tiles of 128 keys; while the softmax warps of one query tile work, the tensor core runs the
 // MMAs of the other. For head size 64 and only a few units a one-tile form runs instead, two CTAs per SM: the same overlap
 // happens between the co-resident CTAs.
-// Work distribution: with a mask or per-sequence lengths one CTA per unit. Otherwise every unit needs the same number of key
-// tiles and the CTAs are persistent (one per SM): whole units round-robin, then the units left over cut into equal pieces of
+// Work distribution: with per-sequence lengths (or a causal mask on a small or ragged problem) one CTA per unit. Otherwise the
+// work comes in blocks of equal length — a unit without a mask; with a causal mask the pair of query groups (n-1-k, k) of a
+// head — and the CTAs are persistent (one per SM): whole blocks round-robin, then the blocks left over cut into equal pieces of
 // their key range, one piece per CTA, whose normalised partial rows a merge kernel joins with their (maximum, sum) weights
 // (AttnParams says how). A persistent CTA runs its items back to back: the next item's Q tiles are fetched before the
 // current one ends, barrier phases and ring stages simply continue, and the output rows leave through a staging area of
@@ -65,8 +66,11 @@ namespace {
         // Work distribution. A unit is one group of QT query tiles of one (batch, head), unit u = (b * Hq + h) * nq + group; it
         // needs `steps` key tiles.
         // balanced == 0: one CTA per unit, grid (groups, Hq, B).
-        // balanced == 1 (every unit needs the same number of key tiles: no causal mask, no per-sequence lengths): a
-        // one-dimensional grid of persistent CTAs. CTA c first takes `rounds` whole units, c, c + grid, c + 2 grid, ... (at any
+        // balanced == 1 (no per-sequence lengths): a one-dimensional grid of persistent CTAs over blocks of work of equal length,
+        // `steps` key tiles each. Without a causal mask every unit needs the same number of key tiles and a block is a unit.
+        // With one (pairing == 1, Sq = Skv) the groups of a head differ, and a block is the pair of groups (nq - 1 - k, k), the
+        // long one first: their lengths add up to the same for every k (the launcher checks it). "Unit" below then reads
+        // "block" for the distribution; an item still lies in ONE unit. CTA c first takes `rounds` whole units, c, c + grid, c + 2 grid, ... (at any
         // moment the CTAs work on neighbouring units, so the K and V tiles they stream are the same few heads' and stay in
         // L2). The units left over, fewer than the grid has CTAs, are each cut into as many equal pieces of `quota` key tiles as
         // there are CTAs for: they are laid out on a line, unit r at [r * ustride, r * ustride + steps) with ustride a multiple
@@ -75,7 +79,7 @@ namespace {
         // covers its whole unit stores final rows; otherwise it leaves a partial per row — the normalised output in the storage
         // type and (running maximum, row sum) — in the CTA's slot 0 (the unit began in an earlier CTA's range) or slot 1 (it
         // began in this one), and the merge kernel joins the partials of each left-over unit.
-        int     balanced, nq, steps, quota, rounds, ustride;
+        int     balanced, pairing, nq, steps, quota, rounds, ustride;
         int     total;   // length of the line of left-over units
         void   *part_o;  // [CTAs][2][QT * BM][D] storage type
         float  *part_ml; // [CTAs][2][QT * BM][2]
@@ -84,6 +88,30 @@ namespace {
         // count of completed fan-outs
         FanOut fan;
     };
+
+    // Key tiles the 128-row query tile that starts at row `first` needs when `len` keys are visible to the sequence.
+    __host__ __device__ inline int tile_steps(int64_t Sq, int64_t Skv, int causal, int64_t first, int64_t len) {
+        int64_t kend = len;
+        if (first >= Sq) kend = 0; // tile entirely past the end of the query sequence
+        if (causal && kend > 0) {
+            int64_t last = first + BM - 1;
+            if (last > Sq - 1) last = Sq - 1;
+            const int64_t lim = last + (Skv - Sq) + 1;
+            if (lim < kend) kend = lim;
+            if (kend < 0) kend = 0;
+        }
+        return (int) ((kend + BN - 1) / BN);
+    }
+    // ... and the group of QT tiles number `qg` (its longest tile), all Skv keys visible
+    template <int QT> __host__ __device__ inline int unit_steps(int64_t Sq, int64_t Skv, int causal, int qg) {
+        int n = 0;
+#pragma unroll
+        for (int t = 0; t < QT; ++t) {
+            const int nt = tile_steps(Sq, Skv, causal, (int64_t) qg * (QT * BM) + (int64_t) t * BM, Skv);
+            n            = nt > n ? nt : n;
+        }
+        return n;
+    }
 
     // One item of a CTA's work and what each of its query tiles has to do in it.
     template <int QT> struct Work {
@@ -100,35 +128,49 @@ namespace {
         Work<QT> w;
         int      cnt;
         if (p.balanced) {
-            int       u;
-            const int lp0 = (int) blockIdx.x * p.quota; // this CTA's stretch of the line of left-over units: [lp0, lp1)
+            int       blk, j, room, bstart;                  // block, step inside it, steps left of the CTA's claim, block start in the line
+            const int lp0 = (int) blockIdx.x * p.quota; // this CTA's stretch of the line of left-over blocks: [lp0, lp1)
             const int lp1 = lp0 + p.quota < p.total ? lp0 + p.quota : p.total;
-            if (pos < p.rounds * p.steps) { // a whole unit of the round-robin part
-                u      = (pos / p.steps) * (int) gridDim.x + (int) blockIdx.x;
-                w.j0   = 0;
-                cnt    = p.steps;
-                w.slot = -1;
+            const bool whole = pos < p.rounds * p.steps; // a whole block of the round-robin part
+            if (whole) {
+                const int k = pos / p.steps;
+                blk         = k * (int) gridDim.x + (int) blockIdx.x;
+                j           = pos - k * p.steps;
+                room        = p.steps - j;
+                bstart      = 0;
             } else {
-                const int lp  = lp0 + (pos - p.rounds * p.steps);
-                w.valid       = lp < lp1;
+                const int lp = lp0 + (pos - p.rounds * p.steps);
+                w.valid      = lp < lp1;
                 if (!w.valid) return w;
-                const int ur   = lp / p.ustride;
-                w.j0           = lp - ur * p.ustride;
-                w.valid        = w.j0 < p.steps; // (else: the padding behind the unit's last piece)
+                const int br = lp / p.ustride;
+                j            = lp - br * p.ustride;
+                w.valid      = j < p.steps; // (else: the padding behind the block's last piece)
                 if (!w.valid) return w;
-                const int left = p.steps - w.j0, room = lp1 - lp;
-                cnt            = left < room ? left : room;
-                w.slot         = cnt == p.steps ? -1 : (ur * p.ustride < lp0 ? 0 : 1);
-                u              = p.rounds * (int) gridDim.x + ur;
+                room   = lp1 - lp;
+                bstart = br * p.ustride;
+                blk    = p.rounds * (int) gridDim.x + br;
             }
-            w.valid      = true;
-            w.adv        = cnt;
-            // what comes after this item: another whole unit, a piece of a left-over unit, or nothing (the item ends j0 + cnt
-            // steps into its unit's stride: at its end the next unit begins, past `steps` lies padding)
-            const int np = pos + cnt - p.rounds * p.steps, nj = w.j0 + cnt;
+            // the unit of the block that step j lies in: [uoff, uoff + nu)
+            const int nb = p.pairing ? p.nq / 2 : p.nq; // blocks per (batch, head)
+            const int bh = blk / nb, k2 = blk - bh * nb;
+            int       nu = p.steps, uoff = 0;
+            w.qg         = k2;
+            if (p.pairing) {
+                const int n_hi = unit_steps<QT>(p.Sq, p.Skv, 1, p.nq - 1 - k2);
+                if (j < n_hi) w.qg = p.nq - 1 - k2, nu = n_hi;
+                else uoff = n_hi, nu = p.steps - n_hi;
+            }
+            w.j0           = j - uoff;
+            const int left = nu - w.j0;
+            cnt            = left < room ? left : room;
+            w.slot         = (w.j0 == 0 && cnt == nu) ? -1 : (whole || bstart + uoff >= lp0 ? 1 : 0);
+            w.valid        = true;
+            w.adv          = cnt;
+            // what comes after this item: more of this block or another whole block, a piece of a left-over block, or nothing
+            // (the item ends j + cnt steps into its block's stride: at the stride's end the next block begins, past `steps` lies
+            // padding)
+            const int np = pos + cnt - p.rounds * p.steps, nj = j + cnt;
             w.last       = !(np < 0 || (lp0 + np < lp1 && (np == 0 || nj == p.ustride || nj < p.steps)));
-            w.qg         = u % p.nq;
-            const int bh = u / p.nq;
             w.h          = bh % (int) p.Hq;
             w.b          = bh / (int) p.Hq;
         } else {
@@ -149,17 +191,7 @@ namespace {
         w.n_max = 0;
 #pragma unroll
         for (int t = 0; t < QT; ++t) {
-            int64_t       kend  = w.len;
-            const int64_t first = w.m0 + (int64_t) t * BM;
-            if (first >= p.Sq) kend = 0; // tile entirely past the end of the query sequence
-            if (p.causal && kend > 0) {
-                int64_t last = first + BM - 1;
-                if (last > p.Sq - 1) last = p.Sq - 1;
-                const int64_t lim = last + (p.Skv - p.Sq) + 1;
-                if (lim < kend) kend = lim;
-                if (kend < 0) kend = 0;
-            }
-            int n    = (int) ((kend + BN - 1) / BN) - w.j0; // key tiles the query tile needs, from the item's first on
+            int n    = tile_steps(p.Sq, p.Skv, p.causal, w.m0 + (int64_t) t * BM, w.len) - w.j0; // key tiles the query tile needs, from the item's first on
             n        = n < 0 ? 0 : (n > cnt ? cnt : n);
             w.n_t[t] = n;
             w.n_max  = n > w.n_max ? n : w.n_max;
@@ -781,26 +813,35 @@ namespace {
         if (!p.balanced && p.fan.n_dest > 0) fanout_signal(p.fan, gridDim.x * gridDim.y * gridDim.z);
     }
 
-    // Merge kernel of the balanced form: one thread per 16 bytes of an output row of the left-over units (`main_ctas` = grid
-    // size of the attention kernel, `left` = number of left-over units). A unit that one CTA covered alone already has its
-    // final rows. The others were cut at CTA boundaries: CTA c of the run [first, last] holds the unit's partial in its slot
-    // 0, except the first, where the unit began inside the CTA's range (slot 1). Each row gets the weights l_s * 2^(m_s - m)
-    // over their sum (m_s are in the log2 domain the kernel works in); a row without any visible key gets NaN like the
-    // reference's 0/0.
+    // Merge kernel of the balanced form: one thread per 16 bytes of an output row of the units in the left-over blocks
+    // (`main_ctas` = grid size of the attention kernel, `left` = number of left-over blocks). A unit that one CTA covered alone
+    // already has its final rows. The others were cut at CTA boundaries: CTA c of the run [first, last] holds the unit's
+    // partial in its slot 0, except the first if the unit began inside that CTA's range (slot 1). Each row gets the weights
+    // l_s * 2^(m_s - m) over their sum (m_s are in the log2 domain the kernel works in); a row without any visible key gets NaN
+    // like the reference's 0/0.
     template <typename T, int D, int QT>
     __global__ void __launch_bounds__(256) attn_prefill_merge_kernel(const AttnParams p, int main_ctas, int left) {
         constexpr int TPRW = D / 8, ROWS = QT * BM; // threads per row (8 elements each), rows per unit
-        const int64_t gid = (int64_t) blockIdx.x * blockDim.x + threadIdx.x;
-        const int     ur  = (int) (gid / (ROWS * TPRW)), rr = (int) (gid / TPRW) % ROWS, c = (int) (gid % TPRW) * 8;
+        const int     upb  = p.pairing ? 2 : 1;     // units per block
+        const int64_t gid  = (int64_t) blockIdx.x * blockDim.x + threadIdx.x;
+        const int     ui   = (int) (gid / (ROWS * TPRW)), rr = (int) (gid / TPRW) % ROWS, c = (int) (gid % TPRW) * 8;
+        const int     br = ui / upb, which = ui - br * upb;
         vkc_grid_dep_wait(); // launched with programmatic serialization: the partials are complete only after this
         vkc_grid_dep_launch();
-        if (ur < left) {
-            const int64_t u  = (int64_t) p.rounds * main_ctas + ur;
-            const int64_t s0 = (int64_t) ur * p.ustride, s1 = s0 + p.steps - 1; // the unit's steps in the line
+        if (br < left) {
+            const int     nb  = p.pairing ? p.nq / 2 : p.nq;
+            const int64_t blk = (int64_t) p.rounds * main_ctas + br, bh = blk / nb;
+            const int     k2  = (int) (blk - bh * nb);
+            int           qg = k2, nu = p.steps, uoff = 0;
+            if (p.pairing) {
+                const int n_hi = unit_steps<QT>(p.Sq, p.Skv, 1, p.nq - 1 - k2);
+                if (which == 0) qg = p.nq - 1 - k2, nu = n_hi;
+                else uoff = n_hi, nu = p.steps - n_hi;
+            }
+            const int64_t s0 = (int64_t) br * p.ustride + uoff, s1 = s0 + nu - 1; // the unit's steps in the line
             const int64_t ca = s0 / p.quota, cb = s1 / p.quota;
-            const int     qg = (int) (u % p.nq);
-            const int64_t bh = u / p.nq, h = bh % p.Hq, b = bh / p.Hq, grow = (int64_t) qg * ROWS + rr;
-            if (ca != cb && grow < p.Sq) {
+            const int64_t h = bh % p.Hq, b = bh / p.Hq, grow = (int64_t) qg * ROWS + rr;
+            if (nu > 0 && ca != cb && grow < p.Sq) {
                 const T *part_o = (const T *) p.part_o;
                 float    m      = -INFINITY;
                 for (int64_t cc = ca; cc <= cb; ++cc) {
@@ -871,11 +912,16 @@ namespace {
         constexpr int smem = (int) Smem<D, 2, 2, QT>::total;
         static_assert(smem * (QT == 1 && D == 64 ? 2 : 1) <= 227 * 1024, "shared memory budget");
         if (int rc = vkc_configure_smem(ctx, kern, smem)) return rc;
-        const int64_t nq = (p.Sq + QT * BM - 1) / (QT * BM), units = nq * p.Hq * B, steps = (p.Skv + BN - 1) / BN;
+        const int64_t nq    = (p.Sq + QT * BM - 1) / (QT * BM);
         const int64_t slots = (int64_t) ctx->sm_count * (QT == 1 ? 2 : 1);
-        p.balanced = 0;
+        // blocks of equal length: the units themselves, or with a causal mask the pairs of groups (nq - 1 - k, k)
+        const int     pairing = balanced && p.causal ? 1 : 0;
+        const int64_t units   = (pairing ? nq / 2 : nq) * p.Hq * B;
+        const int64_t steps   = pairing ? unit_steps<QT>(p.Sq, p.Skv, 1, (int) nq - 1) + unit_steps<QT>(p.Sq, p.Skv, 1, 0) : (p.Skv + BN - 1) / BN;
+        p.balanced = 0, p.pairing = 0;
         p.nq = (int) nq, p.steps = (int) steps, p.quota = 1, p.total = 0, p.rounds = 0, p.ustride = (int) steps;
         if (balanced) {
+            p.pairing             = pairing;
             const Plan   pl       = plan_balanced(units, steps, slots);
             const bool   plain    = pl.rounds == 0 && pl.pieces == 1; // one whole unit per CTA: the three-dimensional grid does the same
             const size_t prows    = (size_t) pl.ctas * 2 * QT * BM;
@@ -892,11 +938,12 @@ namespace {
                 if (int rc = vkc_post_launch(ctx, "attn_prefill_tcgen05")) return rc;
                 if ((pl.left == 0 || pl.pieces == 1) && p.fan.n_dest == 0) return VKC_OK; // nothing was cut
                 // (with a fan-out the merge kernel also publishes the flags, so it runs even when it has nothing to join)
-                const int64_t threads = pl.left * QT * BM * (D / 8);
+                const int64_t threads = pl.left * (pairing ? 2 : 1) * QT * BM * (D / 8);
                 vkc_launch(ctx, attn_prefill_merge_kernel<T, D, QT>, dim3((unsigned) (threads > 0 ? (threads + 255) / 256 : 1)), dim3(256), 0, st, p,
                            (int) pl.ctas, (int) pl.left);
                 return vkc_post_launch(ctx, "attn_prefill_merge");
             }
+            p.pairing = 0;
         }
         dim3 grid((unsigned) nq, (unsigned) p.Hq, (unsigned) B);
         vkc_launch(ctx, kern, grid, dim3(threads_for(QT)), smem, st, tq, tk, tv, p);
@@ -911,6 +958,24 @@ namespace {
         // The balanced form (two-tile units of equal length only: no causal mask, no per-sequence lengths) when its estimate
         // is clearly the lower one.
         bool balanced = false, one_tile_balanced = false;
+        if (p.causal && !p.kv_len && !one_tile && p.Sq == p.Skv && pairs > 0 && pairs * steps < (1ll << 29)) {
+            // Causal: blocks are pairs of query groups (nq - 1 - k, k). The form needs every pair to add up to the same number of
+            // key tiles (true whenever the sequence is a multiple of 256 rows) and an even number of groups.
+            const int64_t nq = (p.Sq + 2 * BM - 1) / (2 * BM);
+            int64_t       lo = INT64_MAX, hi = 0, work = 0, longest = unit_steps<2>(p.Sq, p.Skv, 1, (int) nq - 1);
+            for (int64_t k = 0; k < nq / 2; ++k) {
+                const int64_t sum = unit_steps<2>(p.Sq, p.Skv, 1, (int) (nq - 1 - k)) + unit_steps<2>(p.Sq, p.Skv, 1, (int) k);
+                lo = sum < lo ? sum : lo, hi = sum > hi ? sum : hi, work += sum;
+            }
+            if (nq % 2 == 0 && nq >= 2 && lo == hi) {
+                const Plan   pl = plan_balanced((nq / 2) * p.Hq * B, hi, sms);
+                // one CTA per unit: the heavy units start first, which leaves about half of the longest unit as a tail
+                const double pu = (double) (work * p.Hq * B) / (double) sms + 2.0 * (double) ((pairs + sms - 1) / sms) + 0.5 * (double) longest;
+                // (a block holds two items; measured: 1171 -> 1227 TFLOP/s at S = 8192 and 1207 -> 1289 at 16384 with six and
+                // more rounds of blocks, nothing at three, and a loss when the blocks do not even fill the SMs twice)
+                balanced = pl.rounds >= 2 && pl.cost_balanced + (double) pl.rounds < 0.985 * pu;
+            }
+        }
         if (!p.causal && !p.kv_len && pairs > 0 && steps >= 1 && pairs * steps < (1ll << 29)) {
             const Plan pl = plan_balanced(pairs, steps, sms);
             double     pu = pl.cost_per_unit, bal = pl.cost_balanced;

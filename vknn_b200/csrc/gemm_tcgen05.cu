@@ -102,6 +102,12 @@ namespace {
         static_assert(kSplit == 1 || 65536 + ((BN + 63) / 64 - ((BN + 63) / 64) / kSplit) * 32768 <= kStages * (BM * BK * 2 + BN * BK * 2),
                       "split-K send staging must fit in the operand ring behind the epilogue staging");
         constexpr int kEpiW = epi_warps(kCtasPerSm, kSplit), kThr = threads_of(kCtasPerSm, kSplit);
+        // Residual epilogue without split-K: the residual slabs are fetched by the producer thread while the last K steps still
+        // run, into the A stages of the ring that have seen their last use (slab i into the stage that K step num_kb + i would
+        // take), instead of by the epilogue warps after the accumulator is complete (1.4 us of exposed latency). The output is
+        // staged in the same blocks. Needs more stages than slabs.
+        constexpr bool kEarlyRes = kSplit == 1 && kStages > (BN + 63) / 64;
+        static_assert(BM * BK * 2 == 16384, "a slab's staging (4 warps x 4 KB) is exactly one A stage");
         static_assert(8 * (2 * kStages + 2 + kEpiW) <= 256, "barrier area");
         constexpr uint32_t A_BYTES = BM * BK * 2;
         constexpr uint32_t B_BYTES = BN * BK * 2;
@@ -191,6 +197,28 @@ namespace {
                         for (int c = 0; c < BN / 64; ++c) ptx::tma_load_3d(sB + s * B_BYTES + c * (BK * 128), &tmB, n0 + c * 64, kx, zb, full);
                     }
                 }
+                if (kEarlyRes && gate_ok && !ctl[1] && p.tma_out && (p.epilogue & VKC_EPI_RESIDUAL)) {
+                    int nslab = 0;
+                    for (int sl = 0; sl < (BN + 63) / 64; ++sl)
+                        if ((int64_t) n0 + sl * 64 < p.N) nslab = sl + 1;
+                    // one arrival with the byte count per epilogue warp (warp ew handles lane quarter (ew + 2) & 3 and, with eight
+                    // warps, the slabs of parity ew / 4)
+                    for (int ew = 0; ew < kEpiW; ++ew) {
+                        const int q = (ew + 2) & 3, first = kEpiW == 8 ? ew >> 2 : 0, step = kEpiW == 8 ? 2 : 1;
+                        int       mine = 0;
+                        for (int sl = first; sl < nslab; sl += step) ++mine;
+                        if (m0 + q * 32 < p.M && mine > 0) ptx::mbar_expect_tx(sBar + 8 * (2 * kStages + 2 + ew), (uint32_t) mine * 4096u);
+                    }
+                    for (int sl = 0; sl < nslab; ++sl) {
+                        const int kbp = num_kb + sl, s = kbp % kStages;
+                        if (!ptx::mbar_wait(sBar + 8 * (kStages + s), (uint32_t) (((kbp / kStages) & 1) ^ 1), ctl + 1, p.dev_err)) break;
+                        for (int q = 0; q < 4; ++q) {
+                            const int ew = (kEpiW == 8 ? (sl & 1) * 4 : 0) + ((q + 2) & 3);
+                            if (m0 + q * 32 < p.M)
+                                ptx::tma_load_3d(sA + s * A_BYTES + q * 4096, &tmR, n0 + sl * 64, m0 + q * 32, bz, sBar + 8 * (2 * kStages + 2 + ew));
+                        }
+                    }
+                }
             }
             if (kSplit > 1) ptx::cluster_wait();
         } else if (warp == 1) {
@@ -278,18 +306,21 @@ namespace {
                             nslab = sl + 1;
                             if (sl % step == first) ++nmine;
                         }
+                    // staging block of slab sl: A stage sl, or (residual fetched early) the A stage that K step num_kb + sl would take
+                    const bool early = kEarlyRes && (p.epilogue & VKC_EPI_RESIDUAL);
+                    auto       blk_of = [&](int sl) { return (uint32_t) ((early ? (num_kb + sl) % kStages : sl) * 16384 + q * 4096); };
                     bool rok = true;
                     if ((p.epilogue & VKC_EPI_RESIDUAL) && rows_in && nmine > 0) {
-                        if (lane == 0) {
+                        if (lane == 0 && !early) {
                             ptx::mbar_expect_tx(rbar, (uint32_t) nmine * 4096u);
-                            for (int sl = first; sl < nslab; sl += step) ptx::tma_load_3d(base + sl * 16384 + q * 4096, &tmR, n0 + sl * 64, row0, bz, rbar);
+                            for (int sl = first; sl < nslab; sl += step) ptx::tma_load_3d(base + blk_of(sl), &tmR, n0 + sl * 64, row0, bz, rbar);
                         }
                         rok = ptx::mbar_wait(rbar, 0, ctl + 1, p.dev_err);
                         rok = __all_sync(0xffffffffu, rok);
                     }
 #pragma unroll 1
                     for (int sl = first; sl < nslab && rok; sl += step) {
-                        uint8_t *blk = gbase + sl * 16384 + q * 4096 + lane * 128;
+                        uint8_t *blk = gbase + blk_of(sl) + lane * 128;
                         // both 32-column halves are fetched before the single wait, so that their arithmetic interleaves
                         uint32_t r2[2][32];
                         ptx::tmem_ld_x32(tmem + ((uint32_t) (q * 32) << 16) + (uint32_t) (sl * 64), r2[0]);
@@ -346,7 +377,7 @@ namespace {
                         ptx::fence_proxy_async();
                         __syncwarp();
                         if (lane == 0 && rows_in) {
-                            ptx::tma_store_3d(&tmD, base + sl * 16384 + q * 4096, n0 + sl * 64, row0, bz);
+                            ptx::tma_store_3d(&tmD, base + blk_of(sl), n0 + sl * 64, row0, bz);
                             ptx::bulk_commit_group();
                         }
                     }

@@ -164,15 +164,20 @@ namespace {
             }
             ptx::cluster_arrive(); // barriers exist; the matching wait sits in front of each role's first use of a peer
         }
-        vkc_grid_dep_wait(); // everything above overlapped the previous kernel's tail; global memory from here on
-        vkc_grid_dep_launch();
-        if (warp >= 2 && (p.epilogue & VKC_EPI_BIAS)) {
-            for (int j = threadIdx.x - 64; j < BN; j += kThr - 64) sbias[j] = (int64_t) n0 + j < p.N ? __ldg(p.bias + n0 + j) : 0.f;
-        }
         ptx::tc_fence_before();
         __syncthreads();
         ptx::tc_fence_after();
         const uint32_t tmem = (uint32_t) ctl[0];
+        // Everything above overlapped the previous kernel's tail; global memory from here on. (The set-up barrier comes first so
+        // that nothing but the wait itself stands between the previous kernel's end and the producer's first TMA load.)
+        vkc_grid_dep_wait();
+        vkc_grid_dep_launch();
+        if (warp >= 2 && (p.epilogue & VKC_EPI_BIAS)) {
+            // The bias goes to shared memory behind the set-up barrier and is published among the epilogue warps only (named
+            // barrier 1): in front of that barrier its load latency would sit between the producer thread and its first TMA load.
+            for (int j = threadIdx.x - 64; j < BN; j += kThr - 64) sbias[j] = (int64_t) n0 + j < p.N ? __ldg(p.bias + n0 + j) : 0.f;
+            asm volatile("bar.sync 1, %0;" ::"n"(kThr - 64) : "memory");
+        }
 
         if (warp == 0) {
             if (ptx::elect_one()) {
@@ -525,12 +530,12 @@ namespace {
             ptx::tmem_alloc(sSlot, 2 * acc_stride(BN));
             ptx::tmem_relinquish();
         }
-        vkc_grid_dep_wait();
-        vkc_grid_dep_launch();
         ptx::tc_fence_before();
         __syncthreads();
         ptx::tc_fence_after();
         const uint32_t tmem = (uint32_t) ctl[0];
+        vkc_grid_dep_wait(); // behind the set-up barrier: only the wait stands between the previous kernel's end and the first TMA load
+        vkc_grid_dep_launch();
 
         // tile t -> (row tile fastest, then column tile, then batch): concurrently running CTAs share few B tiles
         auto tile_of = [&](int t, int &m0, int &n0, int &bz) {

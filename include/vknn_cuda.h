@@ -116,6 +116,27 @@ VKC_API int vkc_attn_prefill(vkc_ctx *ctx, const void *Q, const void *K, const v
                              const int64_t *v_strides, const int64_t *o_strides, float scale, int causal, const float *mask,
                              const int32_t *kv_len, int dtype, vkc_stream stream);
 
+/* How vkc_attn_prefill's tensor-core kernel (16-bit storage, D in {64,128}, no additive mask) spreads a shape over a GPU
+ * with sm_count SMs. Host arithmetic only: no device, no context; the launcher runs the same code. The reference's
+ * counterpart is the fixed group count of its dispatches (one workgroup per output tile / per row:
+ * src/backend/vulkan/ops/matmul.cpp:172, softmax.cpp:36); here the grid is planned, so the plan can be inspected.
+ *   plan[0] form: 0 = one CTA per unit on a (query groups, Hq, B) grid, 1 = persistent CTAs that each run a list of items
+ *   plan[1] query tiles of 128 rows a CTA works on at a time (1 or 2)
+ *   plan[2] CTAs launched
+ *   plan[3] rounds of whole blocks a CTA takes before the left-over blocks (form 1)
+ *   plan[4] left-over blocks, cut into plan[5] pieces each of at most plan[6] key tiles of 128 keys
+ *   plan[7] key tiles per block
+ * A block is one unit (a query group of one batch and head) or, with a causal mask in form 1, the pair of query groups
+ * (nq-1-k, k) of one batch and head. vkc_attn_prefill_items lists the items CTA `cta` runs, in order, eight numbers each:
+ * batch, head, query group, first key tile, key tiles of query tile 0, of query tile 1, partial-result slot (0 or 1; -1
+ * when the item is a whole unit and writes O directly), 1 on the CTA's final item. It returns the number of items (which
+ * may exceed max_items; only max_items are written) or a negative VKC_ERR code. has_kv_len: per-sequence lengths will be
+ * passed (they rule out form 1; the listed key-tile counts are those of full-length sequences). ---- */
+VKC_API int vkc_attn_prefill_plan(int sm_count, int64_t B, int64_t Hq, int64_t Sq, int64_t Skv, int64_t D, int causal, int has_kv_len,
+                                  int32_t *plan);
+VKC_API int vkc_attn_prefill_items(int sm_count, int64_t B, int64_t Hq, int64_t Sq, int64_t Skv, int64_t D, int causal, int has_kv_len, int cta,
+                                   int32_t *items, int max_items);
+
 /* ---- prefill attention with its output fanned out to several GPUs (the all-gather at the attention-output boundary of a
  * head-sharded encoder, done by the kernel that produces the tiles instead of a collective after it). The reference has no
  * multi-device path (docs/LIMITATIONS.md:15-32); the arithmetic is vkc_attn_prefill's (MatMulCpu / SoftmaxCpu chain,

@@ -77,6 +77,8 @@ def load_library():
     L.vkc_peer_export.argtypes = [vp, vp, C.c_char_p]
     L.vkc_peer_open.argtypes = [vp, C.c_char_p, C.POINTER(vp)]
     L.vkc_peer_close.argtypes = [vp, vp]
+    L.vkc_attn_prefill_plan.argtypes = [i32] + [i64] * 5 + [i32, i32, C.POINTER(C.c_int32)]
+    L.vkc_attn_prefill_items.argtypes = [i32] + [i64] * 5 + [i32, i32, i32, C.POINTER(C.c_int32), i32]
     L.vkc_attn_decode_workspace_bytes.argtypes = [i64] * 5
     L.vkc_attn_decode_workspace_bytes.restype = sz
     L.vkc_attn_decode.argtypes = [vp, vp, vp, vp, vp] + [i64] * 5 + [vp, f32, vp, sz, i32, vp]
@@ -133,6 +135,32 @@ PEER_HANDLE_BYTES = 64
 
 def _i64arr(vals):
     return (C.c_int64 * len(vals))(*[int(v) for v in vals])
+
+
+PLAN_FIELDS = ("form", "query_tiles", "ctas", "rounds", "left", "pieces", "quota", "steps")
+ITEM_FIELDS = ("b", "h", "qg", "j0", "n_t0", "n_t1", "slot", "last")
+
+
+def attn_prefill_plan(sm_count, B, Hq, Sq, Skv, D, causal=False, has_kv_len=False):
+    """How vkc_attn_prefill's tensor-core kernel spreads the shape over `sm_count` SMs (host arithmetic; needs no GPU)."""
+    out = (C.c_int32 * 8)()
+    rc = load_library().vkc_attn_prefill_plan(sm_count, B, Hq, Sq, Skv, D, int(bool(causal)), int(bool(has_kv_len)), out)
+    if rc != 0:
+        raise VkcError(rc, "vkc_attn_prefill_plan")
+    return dict(zip(PLAN_FIELDS, out))
+
+
+def attn_prefill_items(sm_count, B, Hq, Sq, Skv, D, cta, causal=False, has_kv_len=False):
+    """The items CTA `cta` of that plan runs, in order, as dicts over ITEM_FIELDS."""
+    lib, cap = load_library(), 64
+    while True:
+        buf = (C.c_int32 * (8 * cap))()
+        n = lib.vkc_attn_prefill_items(sm_count, B, Hq, Sq, Skv, D, int(bool(causal)), int(bool(has_kv_len)), cta, buf, cap)
+        if n < 0:
+            raise VkcError(n, "vkc_attn_prefill_items")
+        if n <= cap:
+            return [dict(zip(ITEM_FIELDS, buf[8 * i:8 * i + 8])) for i in range(n)]
+        cap = n
 
 
 class Context:

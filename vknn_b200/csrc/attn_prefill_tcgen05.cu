@@ -123,18 +123,22 @@ namespace {
         int64_t m0, len;  // first query row of the unit, visible key length
         int     n_t[QT], n_max;
     };
+    // Which CTA of which grid (the kernel passes blockIdx / gridDim.x; the host walks the same arithmetic for its plan report).
+    struct CtaId {
+        int x, y, z, nx;
+    };
     // `pos`: the key-tile steps the CTA has behind it when the item starts.
-    template <int QT> __device__ __forceinline__ Work<QT> work_at(const AttnParams &p, int pos) {
+    template <int QT> __host__ __device__ __forceinline__ Work<QT> work_at(const AttnParams &p, int pos, const CtaId c) {
         Work<QT> w;
         int      cnt;
         if (p.balanced) {
             int       blk, j, room, bstart;                  // block, step inside it, steps left of the CTA's claim, block start in the line
-            const int lp0 = (int) blockIdx.x * p.quota; // this CTA's stretch of the line of left-over blocks: [lp0, lp1)
+            const int lp0 = c.x * p.quota; // this CTA's stretch of the line of left-over blocks: [lp0, lp1)
             const int lp1 = lp0 + p.quota < p.total ? lp0 + p.quota : p.total;
             const bool whole = pos < p.rounds * p.steps; // a whole block of the round-robin part
             if (whole) {
                 const int k = pos / p.steps;
-                blk         = k * (int) gridDim.x + (int) blockIdx.x;
+                blk         = k * c.nx + c.x;
                 j           = pos - k * p.steps;
                 room        = p.steps - j;
                 bstart      = 0;
@@ -148,7 +152,7 @@ namespace {
                 if (!w.valid) return w;
                 room   = lp1 - lp;
                 bstart = br * p.ustride;
-                blk    = p.rounds * (int) gridDim.x + br;
+                blk    = p.rounds * c.nx + br;
             }
             // the unit of the block that step j lies in: [uoff, uoff + nu)
             const int nb = p.pairing ? p.nq / 2 : p.nq; // blocks per (batch, head)
@@ -176,8 +180,8 @@ namespace {
         } else {
             w.valid = pos < 1;
             if (!w.valid) return w;
-            w.b = blockIdx.z, w.h = blockIdx.y;
-            w.qg   = p.causal ? (int) gridDim.x - 1 - (int) blockIdx.x : (int) blockIdx.x; // heavy (late) query tiles first when causal
+            w.b = c.z, w.h = c.y;
+            w.qg   = p.causal ? c.nx - 1 - c.x : c.x; // heavy (late) query tiles first when causal
             w.j0   = 0;
             cnt    = INT32_MAX;
             w.slot = -1;
@@ -185,7 +189,10 @@ namespace {
             w.last = true;
         }
         w.m0  = (int64_t) w.qg * (QT * BM);
-        w.len = p.kv_len ? (int64_t) p.kv_len[w.b] : p.Skv;
+        w.len = p.Skv;
+#ifdef __CUDA_ARCH__
+        if (p.kv_len) w.len = (int64_t) p.kv_len[w.b];
+#endif
         if (w.len > p.Skv) w.len = p.Skv;
         if (w.len < 0) w.len = 0;
         w.n_max = 0;
@@ -318,7 +325,8 @@ namespace {
         constexpr int  bQ = 0, bQE = 1, bKF = 2, bKE = bKF + KS, bVF = bKE + KS, bVE = bVF + VS, bSF = bVE + VS, bPF = bSF + QT,
                       bOF = bPF + QT * kPParts;
 
-        const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+        const int   warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+        const CtaId cta {(int) blockIdx.x, (int) blockIdx.y, (int) blockIdx.z, (int) gridDim.x};
 
         if (threadIdx.x == (kWarpMma + 1) * 32) { // a thread of an idle warp, so that the set-up runs beside the look-up above
             for (int i = 0; i < L::nBar; ++i) ptx::mbar_init(bar(i), (i >= bPF && i < bOF) ? 4 : 1); // p_full: one arrival per softmax warp of the tile
@@ -332,10 +340,10 @@ namespace {
             ptx::tmem_alloc(base + L::oCtl, kTmemCols);
             ptx::tmem_relinquish();
         }
-        const Work<QT> w_first = work_at<QT>(p, 0); // the first item, looked up while the barriers are being set up
+        const Work<QT> w_first = work_at<QT>(p, 0, cta); // the first item, looked up while the barriers are being set up
         // the item after `cur` (which began at step `pos` minus its length); none behind the CTA's last
         auto next_work = [&](const Work<QT> &cur, int pos) {
-            if (!cur.last) return work_at<QT>(p, pos);
+            if (!cur.last) return work_at<QT>(p, pos, cta);
             Work<QT> none;
             none.valid = false;
             return none;
@@ -801,7 +809,7 @@ namespace {
                 ptx::tc_fence_before();
             }
             if (w.last) break;
-            prepare(work_at<QT>(p, pos));
+            prepare(work_at<QT>(p, pos, cta));
           }
         }
         if (ctl[1]) {
@@ -905,58 +913,43 @@ namespace {
         return pl;
     }
 
-    template <typename T, int D, int QT>
-    int launch_attn_qt(vkc_ctx *ctx, const CUtensorMap &tq, const CUtensorMap &tk, const CUtensorMap &tv, AttnParams &p, int64_t B, bool balanced,
-                       cudaStream_t st) {
-        auto          kern = attn_prefill_kernel<T, D, 2, QT>;
-        constexpr int smem = (int) Smem<D, 2, 2, QT>::total;
-        static_assert(smem * (QT == 1 && D == 64 ? 2 : 1) <= 227 * 1024, "shared memory budget");
-        if (int rc = vkc_configure_smem(ctx, kern, smem)) return rc;
-        const int64_t nq    = (p.Sq + QT * BM - 1) / (QT * BM);
-        const int64_t slots = (int64_t) ctx->sm_count * (QT == 1 ? 2 : 1);
+    // The distribution of one call: which form, and the fields of AttnParams that describe it (everything but the scratch
+    // pointers). Pure arithmetic on the shape and the SM count, shared by the launcher and by vkc_attn_prefill_plan / _items.
+    struct Distribution {
+        int     qt;       // query tiles per CTA
+        bool    balanced; // persistent CTAs over blocks (else one CTA per unit on a (groups, Hq, B) grid)
+        Plan    pl;       // meaningful when balanced
+        int64_t nq;       // query groups per (batch, head)
+    };
+    // fills p.balanced / pairing / nq / steps / quota / rounds / ustride / total for `qt` query tiles per CTA
+    template <int QT> Distribution distribute_qt(AttnParams &p, int64_t B, bool want_balanced, int64_t sms) {
+        Distribution d;
+        d.qt = QT, d.balanced = false;
+        d.nq = (p.Sq + QT * BM - 1) / (QT * BM);
+        const int64_t slots = sms * (QT == 1 ? 2 : 1);
         // blocks of equal length: the units themselves, or with a causal mask the pairs of groups (nq - 1 - k, k)
-        const int     pairing = balanced && p.causal ? 1 : 0;
-        const int64_t units   = (pairing ? nq / 2 : nq) * p.Hq * B;
-        const int64_t steps   = pairing ? unit_steps<QT>(p.Sq, p.Skv, 1, (int) nq - 1) + unit_steps<QT>(p.Sq, p.Skv, 1, 0) : (p.Skv + BN - 1) / BN;
+        const int     pairing = want_balanced && p.causal ? 1 : 0;
+        const int64_t units   = (pairing ? d.nq / 2 : d.nq) * p.Hq * B;
+        const int64_t steps   = pairing ? unit_steps<QT>(p.Sq, p.Skv, 1, (int) d.nq - 1) + unit_steps<QT>(p.Sq, p.Skv, 1, 0) : (p.Skv + BN - 1) / BN;
         p.balanced = 0, p.pairing = 0;
-        p.nq = (int) nq, p.steps = (int) steps, p.quota = 1, p.total = 0, p.rounds = 0, p.ustride = (int) steps;
-        if (balanced) {
-            p.pairing             = pairing;
-            const Plan   pl       = plan_balanced(units, steps, slots);
-            const bool   plain    = pl.rounds == 0 && pl.pieces == 1; // one whole unit per CTA: the three-dimensional grid does the same
-            const size_t prows    = (size_t) pl.ctas * 2 * QT * BM;
-            const size_t ml_bytes = (prows * 2 * sizeof(float) + 255) & ~(size_t) 255;
-            if (!plain && vkc_ensure_scratch(ctx, ml_bytes + prows * D * 2 + 256, st) == VKC_OK) {
-                p.balanced = 1;
-                p.rounds   = (int) pl.rounds;
-                p.quota    = (int) pl.quota;
-                p.ustride  = (int) pl.ustride;
-                p.total    = (int) pl.total;
-                p.part_ml  = (float *) ctx->scratch;
-                p.part_o   = (char *) ctx->scratch + ml_bytes;
-                vkc_launch(ctx, kern, dim3((unsigned) pl.ctas), dim3(threads_for(QT)), smem, st, tq, tk, tv, p);
-                if (int rc = vkc_post_launch(ctx, "attn_prefill_tcgen05")) return rc;
-                if ((pl.left == 0 || pl.pieces == 1) && p.fan.n_dest == 0) return VKC_OK; // nothing was cut
-                // (with a fan-out the merge kernel also publishes the flags, so it runs even when it has nothing to join)
-                const int64_t threads = pl.left * (pairing ? 2 : 1) * QT * BM * (D / 8);
-                vkc_launch(ctx, attn_prefill_merge_kernel<T, D, QT>, dim3((unsigned) (threads > 0 ? (threads + 255) / 256 : 1)), dim3(256), 0, st, p,
-                           (int) pl.ctas, (int) pl.left);
-                return vkc_post_launch(ctx, "attn_prefill_merge");
+        p.nq = (int) d.nq, p.steps = (int) steps, p.quota = 1, p.total = 0, p.rounds = 0, p.ustride = (int) steps;
+        if (want_balanced) {
+            d.pl = plan_balanced(units, steps, slots);
+            if (!(d.pl.rounds == 0 && d.pl.pieces == 1)) { // (one whole unit per CTA in a single round: the three-dimensional grid does the same)
+                d.balanced = true;
+                p.balanced = 1, p.pairing = pairing;
+                p.rounds = (int) d.pl.rounds, p.quota = (int) d.pl.quota, p.ustride = (int) d.pl.ustride, p.total = (int) d.pl.total;
             }
-            p.pairing = 0;
         }
-        dim3 grid((unsigned) nq, (unsigned) p.Hq, (unsigned) B);
-        vkc_launch(ctx, kern, grid, dim3(threads_for(QT)), smem, st, tq, tk, tv, p);
-        return vkc_post_launch(ctx, "attn_prefill_tcgen05");
+        return d;
     }
-    template <typename T, int D>
-    int launch_attn(vkc_ctx *ctx, const CUtensorMap &tq, const CUtensorMap &tk, const CUtensorMap &tv, AttnParams &p, int64_t B, cudaStream_t st) {
-        const int64_t pairs = ((p.Sq + 2 * BM - 1) / (2 * BM)) * p.Hq * B, steps = (p.Skv + BN - 1) / BN, sms = ctx->sm_count;
+    // which form for the shape in p (Sq, Skv, Hq, causal, kv_len) and head size D
+    Distribution distribute(AttnParams &p, int64_t B, int D, int64_t sms) {
+        const int64_t pairs = ((p.Sq + 2 * BM - 1) / (2 * BM)) * p.Hq * B, steps = (p.Skv + BN - 1) / BN;
         // Head size 64: two one-tile CTAs fit an SM and their softmax and MMA phases overlap like the two tiles of the two-tile
         // form do, at finer granularity; unless the grid is many rounds deep anyway (then sharing K/V between two tiles wins).
         const bool one_tile = D == 64 && pairs < 6 * sms;
-        // The balanced form (two-tile units of equal length only: no causal mask, no per-sequence lengths) when its estimate
-        // is clearly the lower one.
+        // The balanced form (no per-sequence lengths) when its estimate is clearly the lower one.
         bool balanced = false, one_tile_balanced = false;
         if (p.causal && !p.kv_len && !one_tile && p.Sq == p.Skv && pairs > 0 && pairs * steps < (1ll << 29)) {
             // Causal: blocks are pairs of query groups (nq - 1 - k, k). The form needs every pair to add up to the same number of
@@ -988,8 +981,44 @@ namespace {
             }
             balanced = bal < 0.985 * pu;
         }
-        if (one_tile && (!balanced || one_tile_balanced)) return launch_attn_qt<T, 64, 1>(ctx, tq, tk, tv, p, B, balanced, st);
-        return launch_attn_qt<T, D, 2>(ctx, tq, tk, tv, p, B, balanced, st);
+        if (one_tile && (!balanced || one_tile_balanced)) return distribute_qt<1>(p, B, balanced, sms);
+        return distribute_qt<2>(p, B, balanced, sms);
+    }
+
+    template <typename T, int D, int QT>
+    int launch_attn_qt(vkc_ctx *ctx, const CUtensorMap &tq, const CUtensorMap &tk, const CUtensorMap &tv, AttnParams &p, int64_t B, Distribution d,
+                       cudaStream_t st) {
+        auto          kern = attn_prefill_kernel<T, D, 2, QT>;
+        constexpr int smem = (int) Smem<D, 2, 2, QT>::total;
+        static_assert(smem * (QT == 1 && D == 64 ? 2 : 1) <= 227 * 1024, "shared memory budget");
+        if (int rc = vkc_configure_smem(ctx, kern, smem)) return rc;
+        if (d.balanced) {
+            const Plan  &pl       = d.pl;
+            const size_t prows    = (size_t) pl.ctas * 2 * QT * BM;
+            const size_t ml_bytes = (prows * 2 * sizeof(float) + 255) & ~(size_t) 255;
+            if (vkc_ensure_scratch(ctx, ml_bytes + prows * D * 2 + 256, st) == VKC_OK) {
+                p.part_ml = (float *) ctx->scratch;
+                p.part_o  = (char *) ctx->scratch + ml_bytes;
+                vkc_launch(ctx, kern, dim3((unsigned) pl.ctas), dim3(threads_for(QT)), smem, st, tq, tk, tv, p);
+                if (int rc = vkc_post_launch(ctx, "attn_prefill_tcgen05")) return rc;
+                if ((pl.left == 0 || pl.pieces == 1) && p.fan.n_dest == 0) return VKC_OK; // nothing was cut
+                // (with a fan-out the merge kernel also publishes the flags, so it runs even when it has nothing to join)
+                const int64_t threads = pl.left * (p.pairing ? 2 : 1) * QT * BM * (D / 8);
+                vkc_launch(ctx, attn_prefill_merge_kernel<T, D, QT>, dim3((unsigned) (threads > 0 ? (threads + 255) / 256 : 1)), dim3(256), 0, st, p,
+                           (int) pl.ctas, (int) pl.left);
+                return vkc_post_launch(ctx, "attn_prefill_merge");
+            }
+            distribute_qt<QT>(p, B, false, ctx->sm_count); // no scratch to be had: one CTA per unit
+        }
+        dim3 grid((unsigned) d.nq, (unsigned) p.Hq, (unsigned) B);
+        vkc_launch(ctx, kern, grid, dim3(threads_for(QT)), smem, st, tq, tk, tv, p);
+        return vkc_post_launch(ctx, "attn_prefill_tcgen05");
+    }
+    template <typename T, int D>
+    int launch_attn(vkc_ctx *ctx, const CUtensorMap &tq, const CUtensorMap &tk, const CUtensorMap &tv, AttnParams &p, int64_t B, cudaStream_t st) {
+        const Distribution d = distribute(p, B, D, ctx->sm_count);
+        if (D == 64 && d.qt == 1) return launch_attn_qt<T, 64, 1>(ctx, tq, tk, tv, p, B, d, st);
+        return launch_attn_qt<T, D, 2>(ctx, tq, tk, tv, p, B, d, st);
     }
 
     int make_qkv_map(vkc_ctx *ctx, CUtensorMap *map, int dtype, const void *base, int64_t B, int64_t H, int64_t S, int64_t D, const int64_t *str) {
@@ -1041,4 +1070,71 @@ int vkc_attn_prefill_tcgen05(vkc_ctx *ctx, const void *Q, const void *K, const v
     p.part_ml    = nullptr;
     if (dtype == VKC_F16) return D == 64 ? launch_attn<__half, 64>(ctx, tq, tk, tv, p, B, st) : launch_attn<__half, 128>(ctx, tq, tk, tv, p, B, st);
     return D == 64 ? launch_attn<__nv_bfloat16, 64>(ctx, tq, tk, tv, p, B, st) : launch_attn<__nv_bfloat16, 128>(ctx, tq, tk, tv, p, B, st);
+}
+
+// ---- introspection of the work distribution (host arithmetic only: no device, no context) -------------------------------
+namespace {
+    void plan_params(AttnParams &p, int64_t Hq, int64_t Sq, int64_t Skv, int causal, int has_kv_len) {
+        p = AttnParams();
+        p.Sq = Sq, p.Skv = Skv, p.Hq = Hq, p.Hkv = Hq;
+        p.causal = causal;
+        p.kv_len = has_kv_len ? reinterpret_cast<const int32_t *>(uintptr_t(1)) : nullptr; // only ever tested for null on the host
+    }
+} // namespace
+
+extern "C" int vkc_attn_prefill_plan(int sm_count, int64_t B, int64_t Hq, int64_t Sq, int64_t Skv, int64_t D, int causal, int has_kv_len,
+                                      int32_t *plan) {
+    if (sm_count < 1 || B < 1 || Hq < 1 || Sq < 1 || Skv < 0 || (D != 64 && D != 128) || !plan) return VKC_ERR_INVALID;
+    AttnParams p;
+    plan_params(p, Hq, Sq, Skv, causal, has_kv_len);
+    const Distribution d = distribute(p, B, (int) D, sm_count);
+    plan[0] = d.balanced ? 1 : 0;
+    plan[1] = d.qt;
+    plan[2] = d.balanced ? (int32_t) d.pl.ctas : (int32_t) (d.nq * Hq * B);
+    plan[3] = p.rounds;
+    plan[4] = d.balanced ? (int32_t) d.pl.left : 0;
+    plan[5] = d.balanced ? (int32_t) d.pl.pieces : 1;
+    plan[6] = p.quota;
+    plan[7] = p.steps;
+    return VKC_OK;
+}
+
+extern "C" int vkc_attn_prefill_items(int sm_count, int64_t B, int64_t Hq, int64_t Sq, int64_t Skv, int64_t D, int causal, int has_kv_len, int cta,
+                                       int32_t *items, int max_items) {
+    if (sm_count < 1 || B < 1 || Hq < 1 || Sq < 1 || Skv < 0 || (D != 64 && D != 128) || cta < 0 || (!items && max_items > 0)) return VKC_ERR_INVALID;
+    AttnParams p;
+    plan_params(p, Hq, Sq, Skv, causal, has_kv_len);
+    const Distribution d = distribute(p, B, (int) D, sm_count);
+    p.kv_len = nullptr; // (per-sequence lengths only shorten the items of the one-CTA-per-unit form)
+    CtaId c;
+    if (d.balanced) {
+        if (cta >= d.pl.ctas) return VKC_ERR_INVALID;
+        c = CtaId {cta, 0, 0, (int) d.pl.ctas};
+    } else {
+        if (cta >= d.nq * Hq * B) return VKC_ERR_INVALID;
+        c = CtaId {(int) (cta % d.nq), (int) ((cta / d.nq) % Hq), (int) (cta / (d.nq * Hq)), (int) d.nq};
+    }
+    int n = 0;
+    for (int pos = 0;;) {
+        int32_t row[8];
+        bool    last;
+        int     adv;
+        if (d.qt == 1) {
+            const Work<1> w = work_at<1>(p, pos, c);
+            if (!w.valid) break;
+            row[0] = w.b, row[1] = w.h, row[2] = w.qg, row[3] = w.j0, row[4] = w.n_t[0], row[5] = 0, row[6] = w.slot, row[7] = w.last;
+            last = w.last, adv = w.adv;
+        } else {
+            const Work<2> w = work_at<2>(p, pos, c);
+            if (!w.valid) break;
+            row[0] = w.b, row[1] = w.h, row[2] = w.qg, row[3] = w.j0, row[4] = w.n_t[0], row[5] = w.n_t[1], row[6] = w.slot, row[7] = w.last;
+            last = w.last, adv = w.adv;
+        }
+        if (n < max_items)
+            for (int i = 0; i < 8; ++i) items[n * 8 + i] = row[i];
+        ++n;
+        pos += adv;
+        if (last) break;
+    }
+    return n;
 }

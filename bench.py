@@ -849,7 +849,7 @@ def main():
             extra["raster"] = rs
         if args.workload == "prefill" and not args.seq:
             sweep, weak = {}, {}
-            n = max(3, k // 2)
+            n = max(5, k)
             for S, causal in ((4096, False), (16384, False), (8192, True), (16384, True)):
                 c2 = dict(cfg, S=S, causal=causal)
                 s = bench_prefill(ctx, c2, n, 3, rank, world)
@@ -857,6 +857,10 @@ def main():
                 tf = s["flops_step_rank"] * world * n / (s["total_ms"] * 1e-3) / 1e12
                 sweep[name] = {"TFLOP/s": tf, "roofline": tensor_roofline(s["flops_step_rank"], s["per_launch_ms"], pk, kernel="attn_prefill_kernel",
                                                                          traffic=NCU_PREFILL_DRAM_BYTES_PER_ROW_UNIT * c2["B"] * c2["H"] * S)}
+                if rank == 0:  # these legs run late in a long job: say at which clock and under which cap they were taken
+                    w = sampler.window(*s["window"])
+                    sweep[name]["clocks"] = {"sm_mhz": w["sm_mhz"], "reasons": w["reasons"], "power_w_max": w.get("power_w_max"), "samples": w["samples"]}
+                    sweep[name]["roofline"]["frac_of_sustained"] = sweep[name]["roofline"]["achieved"] / pk["bf16_tflops_sustained"]
             extra["prefill_sweep"] = dict(sweep, note="every rank runs the whole named configuration (weak scaling); aggregate TFLOP/s, per-launch roofline of rank 0")
             if world > 1:
                 s = bench_prefill(ctx, cfg, n, 3, rank, world)

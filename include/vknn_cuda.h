@@ -203,6 +203,15 @@ VKC_API int vkc_peer_close(vkc_ctx *ctx, void *dptr);
  *   workspace: device scratch of at least vkc_attn_decode_workspace_bytes(...) bytes holding the per-split
  *   partial (max, sum, o) triples; NULL lets the context keep (and grow) its own. ---- */
 VKC_API size_t vkc_attn_decode_workspace_bytes(int64_t B, int64_t Hq, int64_t Hkv, int64_t Lmax, int64_t D);
+/* The split kernel's work distribution for a set of sequence lengths, walked on the host (no device, no context):
+ * kv_len_host = HOST array of B lengths or NULL for Lmax everywhere. Lists the items of CTA `cta`, six numbers each:
+ * sequence, kv head, first key, end key, slot pair (the item's partials are slots 2*pair and 2*pair+1 of its query
+ * heads), 1 when the item holds the unit's final key tile. plan (3 numbers or NULL) receives the grid size, the partial
+ * slots the workspace holds per (sequence, query head), and the least number of 128-key tiles a CTA takes. Returns the
+ * number of items (which may exceed max_items), VKC_ERR_UNSUPPORTED for a shape the tensor-core form does not take,
+ * VKC_ERR_INVALID for bad arguments. Used by the CPU test that checks exact coverage and the slot bound. */
+VKC_API int vkc_attn_decode_items(int sm_count, int64_t B, int64_t Hq, int64_t Hkv, int64_t Lmax, int64_t D, const int32_t *kv_len_host, int cta,
+                                  int32_t *items, int max_items, int32_t *plan);
 VKC_API int    vkc_attn_decode(vkc_ctx *ctx, const void *Q, const void *Kc, const void *Vc, void *O, int64_t B, int64_t Hq, int64_t Hkv,
                                int64_t Lmax, int64_t D, const int32_t *kv_len, float scale, void *workspace, size_t workspace_bytes,
                                int dtype, vkc_stream stream);

@@ -1,7 +1,8 @@
-"""CPU tests of the prefill attention kernel's work distribution. vkc_attn_prefill_plan / vkc_attn_prefill_items run, on the
-host, the arithmetic the launcher and the kernel use to decide which CTA computes which key tiles of which query tiles. The
-tests walk every CTA of a plan and check that the items cover every (batch, head, query tile, key tile) exactly once, that
-partial results land where the merge kernel looks for them, and that every CTA's list ends with its `last` mark."""
+"""CPU tests of the attention kernels' work distribution (prefill first, decode at the end). vkc_attn_prefill_plan,
+vkc_attn_prefill_items and vkc_attn_decode_items run, on the host, the arithmetic the launchers and the kernels use to decide
+which CTA computes which key tiles of which query tiles. The tests walk every CTA of a plan and check that the items cover
+every (batch, head, query tile, key tile) exactly once, that partial results land where the merge kernels look for them, and
+that every CTA's list ends with its `last` mark."""
 import random
 
 import pytest
@@ -175,3 +176,66 @@ def test_bad_arguments_are_refused():
     assert lib.vkc_attn_prefill_plan(148, 1, 1, 128, 128, 64, 0, 0, None) == -1
     assert lib.vkc_attn_prefill_items(148, 1, 1, 128, 128, 64, 0, 0, 5, out, 1) == -1  # the plan has one CTA
     assert lib.vkc_attn_prefill_items(148, 1, 1, 128, 128, 64, 0, 0, 0, None, 0) == 1  # count only
+
+
+# ---- decode: equal runs of key tiles over the CTAs -------------------------------------------------------------------
+def check_decode(B, Hq, Hkv, Lmax, lens):
+    plan, per_cta = capi.attn_decode_items(SMS, B, Hq, Hkv, Lmax, 128, lens)
+    where = "B=%d Hq=%d Hkv=%d Lmax=%d plan=%s" % (B, Hq, Hkv, Lmax, plan)
+    assert 1 <= plan["grid"] <= SMS and len(per_cta) == plan["grid"], where
+    eff = [min(max(l, 0), Lmax) for l in (lens if lens is not None else [Lmax] * B)]
+    total_tiles = sum((l + 127) // 128 for l in eff) * Hkv
+    quota = max(plan["min_tiles"], (total_tiles + plan["grid"] - 1) // plan["grid"])
+    pieces = {}
+    for c, items in enumerate(per_cta):
+        tiles = 0
+        for it in items:
+            assert 0 <= it["b"] < B and 0 <= it["hk"] < Hkv and it["start"] % 128 == 0 and it["start"] < it["end"] <= eff[it["b"]], (where, c, it)
+            assert 0 <= 2 * it["pair"] + 1 < plan["slots"], (where, c, it)  # the partials stay inside the workspace
+            tiles += (it["end"] - it["start"] + 127) // 128
+            pieces.setdefault((it["b"], it["hk"]), []).append(it)
+        assert tiles <= quota, (where, c)  # equal runs: no CTA streams more than its share
+    for b in range(B):
+        for hk in range(Hkv):
+            got = sorted(pieces.get((b, hk), []), key=lambda it: it["start"])
+            if eff[b] == 0:
+                assert not got, where  # an empty sequence has no item (the merge kernel writes its NaN rows)
+                continue
+            pos = 0
+            for i, it in enumerate(got):
+                assert it["start"] == pos and it["pair"] == i, (where, (b, hk), got)  # contiguous keys, slot pairs 0, 1, 2, ...
+                assert it["last"] == (1 if i == len(got) - 1 else 0), (where, (b, hk), got)
+                pos = it["end"]
+            assert pos == eff[b], (where, (b, hk), got)
+    return plan
+
+
+def test_decode_every_key_once_and_slots_in_bounds():
+    rng = random.Random(3)
+    plan = check_decode(32, 32, 8, 8192, [rng.randint(1024, 8192) for _ in range(32)])  # the bench's decode configuration
+    assert plan["grid"] == SMS
+    check_decode(32, 32, 8, 8192, None)
+    for _ in range(150):
+        Hkv = rng.choice((1, 2, 4, 8))
+        Hq = Hkv * rng.choice((1, 2, 4, 8, 16))
+        B = rng.choice((1, 2, 3, 8, 17, 32, 64, 200))
+        Lmax = rng.choice((1, 100, 128, 129, 1000, 4096, 8192, 20000, 65536))
+        kind = rng.random()
+        if kind < 0.15:
+            lens = None
+        elif kind < 0.3:
+            lens = [rng.choice((0, 1, Lmax, Lmax + 5, -3)) for _ in range(B)]  # empty, over-long and negative lengths are clamped
+        elif kind < 0.45:
+            lens = [Lmax if i == 0 else rng.randint(0, 3) for i in range(B)]   # one long sequence among nearly empty ones
+        else:
+            lens = [rng.randint(0, Lmax) for _ in range(B)]
+        check_decode(B, Hq, Hkv, Lmax, lens)
+
+
+def test_decode_items_refuses_what_the_kernel_does_not_take():
+    with pytest.raises(capi.VkcError):
+        capi.attn_decode_items(SMS, 4, 8, 8, 1024, 64)      # head size 64: the SIMT form's
+    with pytest.raises(capi.VkcError):
+        capi.attn_decode_items(SMS, 4, 64, 2, 1024, 128)    # 32 query heads per kv head
+    with pytest.raises(capi.VkcError):
+        capi.attn_decode_items(SMS, 4, 8, 3, 1024, 128)     # Hq not a multiple of Hkv

@@ -80,6 +80,7 @@ def load_library():
     L.vkc_attn_prefill_plan.argtypes = [i32] + [i64] * 5 + [i32, i32, C.POINTER(C.c_int32)]
     L.vkc_attn_prefill_items.argtypes = [i32] + [i64] * 5 + [i32, i32, i32, C.POINTER(C.c_int32), i32]
     L.vkc_attn_decode_workspace_bytes.argtypes = [i64] * 5
+    L.vkc_attn_decode_items.argtypes = [i32] + [i64] * 5 + [C.POINTER(C.c_int32), i32, C.POINTER(C.c_int32), i32, C.POINTER(C.c_int32)]
     L.vkc_attn_decode_workspace_bytes.restype = sz
     L.vkc_attn_decode.argtypes = [vp, vp, vp, vp, vp] + [i64] * 5 + [vp, f32, vp, sz, i32, vp]
     L.vkc_attn_decode_noalloc_max_bytes.argtypes = []
@@ -161,6 +162,30 @@ def attn_prefill_items(sm_count, B, Hq, Sq, Skv, D, cta, causal=False, has_kv_le
         if n <= cap:
             return [dict(zip(ITEM_FIELDS, buf[8 * i:8 * i + 8])) for i in range(n)]
         cap = n
+
+
+DECODE_ITEM_FIELDS = ("b", "hk", "start", "end", "pair", "last")
+
+
+def attn_decode_items(sm_count, B, Hq, Hkv, Lmax, D, kv_len=None):
+    """The items of every CTA of the decode split kernel for host lengths `kv_len` (list or None), and the plan
+    {"grid", "slots", "min_tiles"}. Host arithmetic; needs no GPU. Raises VkcError for a shape the tensor-core form does not take."""
+    lib = load_library()
+    lens = (C.c_int32 * B)(*kv_len) if kv_len is not None else None
+    plan, cap = (C.c_int32 * 3)(), 64
+    per_cta, cta = [], 0
+    while True:
+        buf = (C.c_int32 * (6 * cap))()
+        n = lib.vkc_attn_decode_items(sm_count, B, Hq, Hkv, Lmax, D, lens, cta, buf, cap, plan)
+        if n < 0:
+            raise VkcError(n, "vkc_attn_decode_items")
+        if n > cap:
+            cap = n
+            continue
+        per_cta.append([dict(zip(DECODE_ITEM_FIELDS, buf[6 * i:6 * i + 6])) for i in range(n)])
+        cta += 1
+        if cta >= plan[0]:
+            return dict(grid=plan[0], slots=plan[1], min_tiles=plan[2]), per_cta
 
 
 class Context:

@@ -310,6 +310,19 @@ extern "C" size_t vkc_attn_decode_workspace_bytes(int64_t B, int64_t Hq, int64_t
     return (size_t) B * (size_t) Hq * max_splits * (size_t) (D + 2) * sizeof(float) + (size_t) B * (size_t) Hkv * sizeof(int);
 }
 
+int vkc_attn_decode_tc_items(int sm_count, int64_t B, int64_t Hq, int64_t Hkv, int64_t Lmax, int64_t D, const int32_t *kv_len, int min_tiles,
+                             int parts_stride, int cta, int32_t *items, int max_items, int *grid_out);
+
+extern "C" int vkc_attn_decode_items(int sm_count, int64_t B, int64_t Hq, int64_t Hkv, int64_t Lmax, int64_t D, const int32_t *kv_len_host, int cta,
+                                     int32_t *items, int max_items, int32_t *plan) {
+    if (sm_count < 1 || B < 1 || Hq < 1 || Hkv < 1 || Lmax < 1 || Hq % Hkv || (!items && max_items > 0)) return VKC_ERR_INVALID;
+    const int chunk = decode_chunk(B, Hkv, Lmax), slots = decode_slots(Lmax, chunk);
+    int       grid  = 0;
+    const int n     = vkc_attn_decode_tc_items(sm_count, B, Hq, Hkv, Lmax, D, kv_len_host, 2 * chunk / 128, slots, cta, items, max_items, &grid);
+    if (plan) plan[0] = grid, plan[1] = slots, plan[2] = 2 * chunk / 128;
+    return n < 0 ? (grid > 0 ? VKC_ERR_INVALID : VKC_ERR_UNSUPPORTED) : n;
+}
+
 extern "C" int vkc_attn_decode(vkc_ctx *ctx, const void *Q, const void *Kc, const void *Vc, void *O, int64_t B, int64_t Hq, int64_t Hkv,
                                int64_t Lmax, int64_t D, const int32_t *kv_len, float scale, void *workspace, size_t workspace_bytes, int dtype,
                                vkc_stream stream) {

@@ -77,17 +77,19 @@ namespace {
         int64_t start, end;
         bool    valid, last; // last: the item holds the unit's final tile
     };
-    __device__ __forceinline__ int64_t seq_len(const DecParams &p, int b) {
+    // (find_item and its helpers are host/device: the kernel and vkc_attn_decode_tc_items, which walks a host copy of the
+    // lengths, run the same arithmetic)
+    __host__ __device__ __forceinline__ int64_t seq_len(const DecParams &p, int b) {
         int64_t len = p.kv_len ? (int64_t) p.kv_len[b] : p.Lmax;
         if (len > p.Lmax) len = p.Lmax;
         return len < 0 ? 0 : len;
     }
-    __device__ __forceinline__ int tile_quota(const DecParams &p, const int *prefix) {
-        const int q = (prefix[p.B] + (int) gridDim.x - 1) / (int) gridDim.x;
+    __host__ __device__ __forceinline__ int tile_quota(const DecParams &p, const int *prefix, int grid) {
+        const int q = (prefix[p.B] + grid - 1) / grid;
         return q > p.min_quota ? q : p.min_quota;
     }
     // The item that starts at tile `pos` of the line; the CTA's range ends at `pos1`.
-    __device__ __forceinline__ Item find_item(const DecParams &p, const int *prefix, int pos, int pos1, int quota) {
+    __host__ __device__ __forceinline__ Item find_item(const DecParams &p, const int *prefix, int pos, int pos1, int quota) {
         Item it;
         it.valid = false;
         if (pos >= pos1) return it;
@@ -170,7 +172,7 @@ namespace {
         __syncthreads();
         ptx::tc_fence_after();
         const uint32_t tmem  = (uint32_t) ctl[0];
-        const int      quota = tile_quota(p, prefix);
+        const int      quota = tile_quota(p, prefix, (int) gridDim.x);
         const int      pos0  = (int) blockIdx.x * quota;
         const int      pos1  = pos0 + quota < prefix[p.B] ? pos0 + quota : prefix[p.B];
 
@@ -472,7 +474,46 @@ namespace {
         if (warp == 1) ptx::tmem_dealloc(tmem, kTmemCols);
     }
 
+    inline int decode_grid(int64_t max_tiles, int min_tiles, int sm_count) {
+        const int64_t max_ctas = (max_tiles + min_tiles - 1) / min_tiles;
+        return (int) (max_ctas < sm_count ? max_ctas : sm_count);
+    }
+
 } // namespace
+
+// Host walk of the split kernel's work distribution (no device): kv_len is a HOST array of B lengths or NULL. Writes the
+// items of CTA `cta`, six numbers each — sequence, kv head, first key, end key, slot pair, 1 if the item holds the unit's
+// final tile — and returns their number (which may exceed max_items), -1 for a shape the kernel does not take. *grid_out
+// receives the grid size.
+int vkc_attn_decode_tc_items(int sm_count, int64_t B, int64_t Hq, int64_t Hkv, int64_t Lmax, int64_t D, const int32_t *kv_len, int min_tiles,
+                             int parts_stride, int cta, int32_t *items, int max_items, int *grid_out) {
+    const int64_t G = Hq / Hkv, max_tiles = B * Hkv * ((Lmax + TK - 1) / TK);
+    if (D != DH || G > NPAD || min_tiles < 1 || B > kMaxPrefix || B < 1 || Lmax > INT32_MAX - TK || max_tiles > INT32_MAX / 2 ||
+        2 * (((Lmax + TK - 1) / TK + min_tiles - 1) / min_tiles + 1) > parts_stride)
+        return -1;
+    DecParams p = {};
+    p.kv_len = kv_len, p.B = (int) B, p.Hkv = (int) Hkv, p.G = (int) G, p.min_quota = min_tiles, p.parts_stride = parts_stride, p.Lmax = Lmax;
+    const int grid = decode_grid(max_tiles, min_tiles, sm_count);
+    if (grid_out) *grid_out = grid;
+    if (cta < 0 || cta >= grid) return -1;
+    static thread_local int prefix[kMaxPrefix + 1];
+    prefix[0] = 0;
+    for (int b = 0; b < p.B; ++b) prefix[b + 1] = prefix[b] + (int) (((seq_len(p, b) + TK - 1) / TK) * p.Hkv);
+    const int quota = tile_quota(p, prefix, grid), pos0 = cta * quota;
+    const int pos1  = pos0 + quota < prefix[p.B] ? pos0 + quota : prefix[p.B];
+    int       n     = 0;
+    for (int pos = pos0;;) {
+        const Item it = find_item(p, prefix, pos, pos1, quota);
+        if (!it.valid) break;
+        if (n < max_items) {
+            int32_t *row = items + 6 * n;
+            row[0] = it.b, row[1] = it.hk, row[2] = (int32_t) it.start, row[3] = (int32_t) it.end, row[4] = it.split, row[5] = it.last;
+        }
+        ++n;
+        pos += it.ntiles;
+    }
+    return n;
+}
 
 // Launches the split kernel only; the caller runs the merge kernel. Every CTA takes at least `min_tiles` 128-key
 // tiles; a (sequence, kv head) unit is therefore cut into at most ceil(tiles / min_tiles) + 1 items, each of which fills
@@ -509,8 +550,7 @@ int vkc_attn_decode_tcgen05(vkc_ctx *ctx, const void *Q, const void *Kc, const v
     p.B = (int) B, p.Hkv = (int) Hkv, p.G = (int) G, p.min_quota = min_tiles, p.nslots = nslots, p.parts_stride = parts_stride, p.Lmax = Lmax;
     p.scale_log2 = scale * 1.4426950408889634f;
     p.dev_err    = ctx->dev_err;
-    const int64_t max_ctas = (max_tiles + min_tiles - 1) / min_tiles;
-    const int     grid     = (int) (max_ctas < ctx->sm_count ? max_ctas : ctx->sm_count);
+    const int grid = decode_grid(max_tiles, min_tiles, ctx->sm_count);
 #define VKC_DTC(T_)                                                                                                  \
     do {                                                                                                             \
         auto kern_ = attn_decode_tc_kernel<T_>;                                                                      \

@@ -766,6 +766,7 @@ def main():
     ap.add_argument("--no-extra", action="store_true", help="skip the decode / encoder / sweep extras")
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline and plug-in legs")
     ap.add_argument("--no-tune", action="store_true", help="encoder workloads: keep the built-in GEMM configurations (no per-shape timing)")
+    ap.add_argument("--cooldown", type=float, default=1.0, help="idle seconds before each leg of the prefill sweep")
     ap.add_argument("--sustained", type=float, default=2.2, help="seconds of the back-to-back run of the headline kernel (0: skip)")
     args = ap.parse_args()
     global NO_TUNE
@@ -852,6 +853,13 @@ def main():
             n = max(5, k)
             for S, causal in ((4096, False), (16384, False), (8192, True), (16384, True)):
                 c2 = dict(cfg, S=S, causal=causal)
+                # Like the headline, each leg is a burst from an idle GPU: after tens of milliseconds of back-to-back attention
+                # launches the power management already holds the kernel back (seq 8192 causal: 0.90 ms per launch from idle,
+                # 1.05 ms right after forty launches of the unmasked shape, the sampled clock still at its maximum).
+                import torch
+                torch.cuda.synchronize()
+                time.sleep(args.cooldown)
+                barrier(world)
                 s = bench_prefill(ctx, c2, n, 3, rank, world)
                 name = "S%d%s" % (S, "_causal" if causal else "")
                 tf = s["flops_step_rank"] * world * n / (s["total_ms"] * 1e-3) / 1e12
@@ -861,7 +869,9 @@ def main():
                     w = sampler.window(*s["window"])
                     sweep[name]["clocks"] = {"sm_mhz": w["sm_mhz"], "reasons": w["reasons"], "power_w_max": w.get("power_w_max"), "samples": w["samples"]}
                     sweep[name]["roofline"]["frac_of_sustained"] = sweep[name]["roofline"]["achieved"] / pk["bf16_tflops_sustained"]
-            extra["prefill_sweep"] = dict(sweep, note="every rank runs the whole named configuration (weak scaling); aggregate TFLOP/s, per-launch roofline of rank 0")
+            extra["prefill_sweep"] = dict(sweep, cooldown_s=args.cooldown,
+                                          note="every rank runs the whole named configuration (weak scaling); aggregate TFLOP/s, per-launch roofline of rank 0; "
+                                               "the GPU idles cooldown_s before each leg, so each is a burst like the headline")
             if world > 1:
                 s = bench_prefill(ctx, cfg, n, 3, rank, world)
                 weak["prefill_TFLOP/s"] = s["flops_step_rank"] * world * n / (s["total_ms"] * 1e-3) / 1e12

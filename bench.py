@@ -766,7 +766,7 @@ def main():
     ap.add_argument("--no-extra", action="store_true", help="skip the decode / encoder / sweep extras")
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline and plug-in legs")
     ap.add_argument("--no-tune", action="store_true", help="encoder workloads: keep the built-in GEMM configurations (no per-shape timing)")
-    ap.add_argument("--cooldown", type=float, default=1.0, help="idle seconds before each leg of the prefill sweep")
+    ap.add_argument("--cooldown", type=float, default=1.0, help="idle seconds before each leg of the prefill sweep and before the delivered step at N > 1")
     ap.add_argument("--sustained", type=float, default=2.2, help="seconds of the back-to-back run of the headline kernel (0: skip)")
     args = ap.parse_args()
     global NO_TUNE
@@ -801,6 +801,12 @@ def main():
         r = bench_prefill(ctx, cfg, args.steps, args.warmup, rank, world, e2e_steps=args.steps, heads_per_rank=Hl,
                           sustained_s=args.sustained, sampler=sampler)
         if world > 1:
+            # the delivered step is the headline at N > 1: like the one-GPU headline it starts from an idle GPU, not from the
+            # power state the sustained leg above leaves behind
+            import torch
+            torch.cuda.synchronize()
+            time.sleep(args.cooldown)
+            barrier(world)
             strong = bench_prefill_delivered(ctx, cfg, args.steps, args.warmup, rank, world)
     elif args.workload == "decode":
         r = bench_decode(ctx, DECODE, args.steps, args.warmup, rank, world)
